@@ -1,0 +1,206 @@
+/*
+ * jitllm_b200.h -- C ABI of libjitllm_b200.so
+ *
+ * A B200 (sm_100a) implementation of jitllm's quantized-matmul hot path, sitting
+ * behind the seam the reference already has for accelerators: engine/nn's
+ * Device.MatVec (engine/nn/device.go:23-31), the JIT.MatMul call site
+ * (engine/nn/matmul.go:27) and the mixture-of-experts call sites
+ * (engine/model/moe.go:502-760). Plain pointers and sizes only; a Go caller
+ * reaches it through cgo or a dlopen FFI.
+ *
+ * Conventions
+ *   - Every function returns a jl_status: 0 = served, 1 = DECLINED (a supported
+ *     answer: the caller runs its own path, engine/nn/jit.go:935-940), < 0 = error.
+ *   - The library never aborts, traps or reads the environment. Why the last
+ *     call declined or failed is jl_last_error() (ErrReporter.Err,
+ *     engine/nn/device.go:1592-1593).
+ *   - Calls on one jl_ctx are serialised internally (the reference holds a
+ *     per-device mutex across a matvec, jit/gpu/tier/tier.go:2842); different
+ *     contexts are independent.
+ *   - The caller owns every host buffer. The library owns device copies of
+ *     weights and frees them on jl_forget / jl_weight_free / jl_close.
+ *   - Quantized weights are RAW ggml blocks, row-major: nrows x (k / block_elems
+ *     * block_bytes) bytes (format/quant/types.go:61-85).
+ */
+#ifndef JITLLM_B200_H
+#define JITLLM_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define JL_ABI_VERSION 1
+
+/* ggml type ids, format/quant/types.go:12-55. */
+#define JL_TYPE_F32 0u
+#define JL_TYPE_F16 1u
+#define JL_TYPE_Q8_0 8u   /* 32 elements in 34 bytes  {f16 d; i8 qs[32]}              */
+#define JL_TYPE_Q4_K 12u  /* 256 elements in 144 bytes {f16 d,dmin; u8 sc[12]; u8 qs[128]} */
+#define JL_TYPE_BF16 30u
+#define JL_TYPE_MXFP4 39u /* 32 elements in 17 bytes  {u8 e; u8 qs[16]}               */
+
+typedef enum jl_status {
+    JL_OK = 0,          /* served */
+    JL_DECLINED = 1,    /* not an error: unsupported type/shape, too small to pay */
+    JL_EINVAL = -1,
+    JL_ECUDA = -2,      /* a CUDA call failed; the context reports unhealthy */
+    JL_ENOMEM = -3,
+    JL_EDEVICE = -4,    /* injected device failure (jl_test_fail_at) */
+    JL_ETIMEDOUT = -5,  /* a bounded device-side wait ran out */
+    JL_ENOTSUP = -6,
+    JL_ECOMM = -7
+} jl_status;
+
+/* Element types of activations / outputs on the batched entry points. */
+typedef enum jl_dtype { JL_DT_F32 = 0, JL_DT_F16 = 1, JL_DT_BF16 = 2 } jl_dtype;
+
+/* Kernel families, reported by jl_select and pinnable through jl_opts: the
+ * reference's per-shape selection (jit/gpu/tier/layer.go:10953-11016 batchMV,
+ * jit/gpu/tier/tier.go:124-137 chooseSplit) maps onto these. */
+typedef enum jl_kernel {
+    JL_K_AUTO = 0,
+    JL_K_SIMT = 1,   /* one warp per row, f32 FMA: every shape, the check kernel     */
+    JL_K_MMA = 2,    /* register dequant -> mma.sync f16, f32 accumulate: decode      */
+    JL_K_TC5 = 3     /* TMA -> smem dequant -> tcgen05.mma, TMEM accumulators: prefill */
+} jl_kernel;
+
+/* Gated activations of the mixture layer, jit/gpu/kernels/actkind.go:13-39. */
+typedef enum jl_act { JL_ACT_SILU = 0, JL_ACT_SWIGLU_OAI = 1 } jl_act;
+
+/* Options: the reference's libraries read no environment, every knob is a
+ * With...() option (engine/nn/options.go:7-13). Zero-initialise, set
+ * struct_size = sizeof(jl_opts), then override. */
+typedef struct jl_opts {
+    uint32_t struct_size;
+    int32_t pin_kernel;        /* jl_kernel; JL_K_AUTO = per-shape selection          */
+    int32_t pin_warps;         /* warps per CTA of the decode kernel; 0 = selected    */
+    uint64_t min_weight_bytes; /* jl_matvec declines smaller weights (the reference's
+                                  mvPays break-even, jit/gpu/tier/tier.go:2404-2424);
+                                  0 = serve everything                                */
+    uint64_t max_resident_bytes; /* cap on device copies kept for host-pointer calls;
+                                  0 = no cap                                          */
+    uint32_t flags;            /* reserved, 0 */
+} jl_opts;
+
+typedef struct jl_ctx jl_ctx;
+typedef struct jl_weight jl_weight;
+
+/* What would run for a shape (jl_select). */
+typedef struct jl_choice {
+    int32_t kernel;   /* jl_kernel */
+    int32_t warps;    /* warps per CTA */
+    int32_t rows_per_cta;
+    int32_t split_k;  /* how many partial sums meet per output row */
+    int32_t tile_m, tile_n, tile_k; /* tensor-core tile (rows, tokens, k) or 0 */
+    int32_t grid;     /* CTAs launched */
+} jl_choice;
+
+/* Counters, the tier's Stats (jit/gpu/tier/tier.go:1246,2330). */
+typedef struct jl_stats {
+    uint64_t served, declined, errors;
+    uint64_t uploads, upload_bytes, resident_bytes, forgets;
+    uint64_t launches;       /* kernels this context launched */
+    uint64_t injected;       /* failures injected by jl_test_fail_at */
+} jl_stats;
+
+const char *jl_version(void);
+int jl_abi_version(void);
+
+/* ---- context: tier.OpenWith (jit/gpu/tier/open.go:94) ------------------- */
+int jl_open(int device, const jl_opts *opts, jl_ctx **out);
+void jl_close(jl_ctx *ctx);
+/* Device.Reserve (engine/nn/device.go:1169-1175): pre-size staging so nothing
+ * grows on the serving path. */
+int jl_reserve(jl_ctx *ctx, int max_rows, int max_k, int max_tok);
+/* ErrReporter.Err (engine/nn/device.go:1592-1593). Valid until the next call on ctx. */
+const char *jl_last_error(jl_ctx *ctx);
+int jl_stats_get(jl_ctx *ctx, jl_stats *out);
+
+/* ---- the decode operator: nn.Device.MatVec (engine/nn/device.go:23-31) --- */
+/* out[0:nrows] = W x. w: raw ggml blocks on the HOST; x, out: host f32. The
+ * device copy of w is keyed on (w, w_bytes): the first call uploads (and may
+ * repack, bit-exactly), later calls reuse it. The caller guarantees the bytes
+ * at w stay unchanged until jl_forget covers them. Types: Q4_K, Q8_0, MXFP4. */
+int jl_matvec(jl_ctx *ctx, float *out, uint32_t type, const void *w, size_t w_bytes,
+              const float *x, int nrows, int k);
+/* CopyForgetter.Forget (engine/nn/device.go:1570-1581): drop every device copy
+ * whose host range lies in [p, p+n). Any thread; never waits on device work
+ * the caller did not start. */
+int jl_forget(jl_ctx *ctx, const void *p, size_t n);
+
+/* ---- the batched operator: JIT.MatMul (engine/nn/matmul.go:27) ----------- */
+/* x is [ntok][k], out is [ntok][nrows], both token-major, host memory.
+ * x_dtype / out_dtype: f32, f16 or bf16. Accumulation is f32. */
+int jl_matmul(jl_ctx *ctx, void *out, int out_dtype, uint32_t type, const void *w, size_t w_bytes,
+              const void *x, int x_dtype, int nrows, int k, int ntok);
+
+/* ---- the mixture layer: State.moeBatch (engine/model/moe.go:502-760) ----- */
+/* Banks are [n_expert][rows][k/32*17] raw blocks (MXFP4; Q4_K/Q8_0 accepted):
+ * gate, up: rows = ffn, k = hidden; down: rows = hidden, k = ffn. */
+typedef struct jl_moe_desc {
+    uint32_t struct_size;
+    uint32_t type;                 /* bank block type */
+    int32_t n_expert, top_k, hidden, ffn;
+    int32_t act;                   /* jl_act */
+    int32_t norm;                  /* renormalise by the selected sum (+1e-20), moetopk.go:137 */
+    float scale;                   /* routed_scaling_factor; 0 or 1 = none */
+    const void *gate, *up, *down;  /* host banks (jl_moe) or jl_weight handles (jl_moe_dev) */
+    size_t gate_bytes, up_bytes, down_bytes;
+    const float *gate_bias, *up_bias, *down_bias; /* [n_expert][rows] f32 or NULL */
+    const float *router_bias;      /* added to the logits before the gate (gpt-oss) or NULL */
+} jl_moe_desc;
+/* out[ntok][hidden] f32 += sum over each row's top_k experts, ascending expert
+ * id, of w_e * down_e(act(gate_e h, up_e h)). logits [ntok][n_expert] f32 are
+ * the router's raw outputs: softmax, lexicographic top-k (ties to the lowest
+ * id), divisor summed in selection order (engine/nn/moetopk.go:316-385).
+ * h is [ntok][hidden] in h_dtype. sel_out/wt_out ([ntok][top_k], selection
+ * order) may be NULL. */
+int jl_moe(jl_ctx *ctx, float *out, const void *h, int h_dtype, const float *logits, int ntok,
+           const jl_moe_desc *desc, int32_t *sel_out, float *wt_out);
+
+/* ---- per-shape selection: batchMV / chooseSplit -------------------------- */
+int jl_select(jl_ctx *ctx, uint32_t type, int nrows, int k, int ntok, jl_choice *out);
+
+/* ---- integer view of the blocks: kernels.extract (jit/gpu/kernels/pack.go:252-386)
+ * One record per 32-element sub-block: q[32] codes (Q4_K 0..15, Q8_0 -128..127,
+ * MXFP4 raw e2m1 code 0..15), raw f16 bits of d (MXFP4: the stored byte e-1,
+ * pack.go:388-395) and dmin, the 6-bit sc and m. n_blocks counts format blocks.
+ * jl_unpack runs on the host; jl_unpack_resident reads the DEVICE-RESIDENT
+ * (possibly repacked) copy back through a kernel, which is how a repack is
+ * shown to be bit-exact. Host output buffers in both. */
+int jl_unpack(uint32_t type, const void *blocks, size_t n_blocks, int8_t *q, uint16_t *d_bits,
+              uint16_t *dmin_bits, uint8_t *sc, uint8_t *m);
+int jl_unpack_resident(jl_ctx *ctx, const jl_weight *w, int8_t *q, uint16_t *d_bits,
+                       uint16_t *dmin_bits, uint8_t *sc, uint8_t *m);
+
+/* ---- device-pointer twins: no host round trip ----------------------------
+ * What tier.resident() does inside the reference (jit/gpu/tier/tier.go:2831-2903):
+ * the weight lives on the device, activations and outputs are device pointers,
+ * the launch goes on `stream` (a cudaStream_t; NULL = the context's own). */
+int jl_weight_upload(jl_ctx *ctx, uint32_t type, const void *w_host, size_t w_bytes, int nrows,
+                     int k, jl_weight **out);
+/* As jl_weight_upload for a bank of n_expert equal matrices. */
+int jl_weight_upload_bank(jl_ctx *ctx, uint32_t type, const void *w_host, size_t w_bytes,
+                          int n_expert, int nrows, int k, jl_weight **out);
+void jl_weight_free(jl_ctx *ctx, jl_weight *w);
+/* x_dev [ntok][k] f32, out_dev [ntok][nrows] f32. ntok = 1 is the decode matvec. */
+int jl_matvec_dev(jl_ctx *ctx, float *out_dev, const jl_weight *w, const float *x_dev, int ntok,
+                  void *stream);
+int jl_matmul_dev(jl_ctx *ctx, void *out_dev, int out_dtype, const jl_weight *w, const void *x_dev,
+                  int x_dtype, int ntok, void *stream);
+/* desc->gate/up/down are jl_weight* banks; biases and all other pointers are device pointers. */
+int jl_moe_dev(jl_ctx *ctx, float *out_dev, const void *h_dev, int h_dtype, const float *logits_dev,
+               int ntok, const jl_moe_desc *desc, int32_t *sel_out_dev, float *wt_out_dev, void *stream);
+
+/* ---- host-side fault injection: JITLLM_DEVICE_FAIL_AT (jit/gpu/tier/fault.go:12-58)
+ * The n-th, ... serving calls on ctx (1-based ordinals, counted from this call)
+ * fail with JL_EDEVICE before anything is launched. n = 0 disarms. Test-only. */
+int jl_test_fail_at(jl_ctx *ctx, const int *ordinals, int n);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* JITLLM_B200_H */

@@ -1,0 +1,99 @@
+"""ctypes binding of libjitllm_b200.so -- the same symbols a cgo/goffi shim binds.
+
+There is no fallback: if the shared library is missing the import fails, and if
+no B200 is present jl_open fails. Nothing here computes on the CPU.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libjitllm_b200.so")
+
+# ggml type ids (include/jitllm_b200.h)
+F32, F16, Q8_0, Q4_K, BF16, MXFP4 = 0, 1, 8, 12, 30, 39
+DT_F32, DT_F16, DT_BF16 = 0, 1, 2
+K_AUTO, K_SIMT, K_MMA, K_TC5 = 0, 1, 2, 3
+ACT_SILU, ACT_SWIGLU_OAI = 0, 1
+OK, DECLINED = 0, 1
+EINVAL, ECUDA, ENOMEM, EDEVICE, ETIMEDOUT, ENOTSUP, ECOMM = -1, -2, -3, -4, -5, -6, -7
+
+BLOCK = {Q8_0: (32, 34), Q4_K: (256, 144), MXFP4: (32, 17), F32: (1, 4), F16: (1, 2), BF16: (1, 2)}
+
+
+def row_bytes(t: int, k: int) -> int:
+    be, bb = BLOCK[t]
+    return k // be * bb
+
+
+class Opts(C.Structure):
+    _fields_ = [("struct_size", C.c_uint32), ("pin_kernel", C.c_int32), ("pin_warps", C.c_int32),
+                ("min_weight_bytes", C.c_uint64), ("max_resident_bytes", C.c_uint64), ("flags", C.c_uint32)]
+
+
+class Choice(C.Structure):
+    _fields_ = [("kernel", C.c_int32), ("warps", C.c_int32), ("rows_per_cta", C.c_int32),
+                ("split_k", C.c_int32), ("tile_m", C.c_int32), ("tile_n", C.c_int32), ("tile_k", C.c_int32),
+                ("grid", C.c_int32)]
+
+
+class Stats(C.Structure):
+    _fields_ = [(n, C.c_uint64) for n in ("served", "declined", "errors", "uploads", "upload_bytes",
+                                           "resident_bytes", "forgets", "launches", "injected")]
+
+
+class MoeDesc(C.Structure):
+    _fields_ = [("struct_size", C.c_uint32), ("type", C.c_uint32), ("n_expert", C.c_int32),
+                ("top_k", C.c_int32), ("hidden", C.c_int32), ("ffn", C.c_int32), ("act", C.c_int32),
+                ("norm", C.c_int32), ("scale", C.c_float),
+                ("gate", C.c_void_p), ("up", C.c_void_p), ("down", C.c_void_p),
+                ("gate_bytes", C.c_size_t), ("up_bytes", C.c_size_t), ("down_bytes", C.c_size_t),
+                ("gate_bias", C.c_void_p), ("up_bias", C.c_void_p), ("down_bias", C.c_void_p),
+                ("router_bias", C.c_void_p)]
+
+
+# Every symbol include/jitllm_b200.h declares: (restype, argtypes).
+_VP, _I, _SZ, _U32 = C.c_void_p, C.c_int, C.c_size_t, C.c_uint32
+SYMBOLS = {
+    "jl_version": (C.c_char_p, []),
+    "jl_abi_version": (_I, []),
+    "jl_open": (_I, [_I, C.POINTER(Opts), C.POINTER(_VP)]),
+    "jl_close": (None, [_VP]),
+    "jl_reserve": (_I, [_VP, _I, _I, _I]),
+    "jl_last_error": (C.c_char_p, [_VP]),
+    "jl_stats_get": (_I, [_VP, C.POINTER(Stats)]),
+    "jl_matvec": (_I, [_VP, _VP, _U32, _VP, _SZ, _VP, _I, _I]),
+    "jl_forget": (_I, [_VP, _VP, _SZ]),
+    "jl_matmul": (_I, [_VP, _VP, _I, _U32, _VP, _SZ, _VP, _I, _I, _I, _I]),
+    "jl_moe": (_I, [_VP, _VP, _VP, _I, _VP, _I, C.POINTER(MoeDesc), _VP, _VP]),
+    "jl_select": (_I, [_VP, _U32, _I, _I, _I, C.POINTER(Choice)]),
+    "jl_unpack": (_I, [_U32, _VP, _SZ, _VP, _VP, _VP, _VP, _VP]),
+    "jl_unpack_resident": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _VP]),
+    "jl_weight_upload": (_I, [_VP, _U32, _VP, _SZ, _I, _I, C.POINTER(_VP)]),
+    "jl_weight_upload_bank": (_I, [_VP, _U32, _VP, _SZ, _I, _I, _I, C.POINTER(_VP)]),
+    "jl_weight_free": (None, [_VP, _VP]),
+    "jl_matvec_dev": (_I, [_VP, _VP, _VP, _VP, _I, _VP]),
+    "jl_matmul_dev": (_I, [_VP, _VP, _I, _VP, _VP, _I, _I, _VP]),
+    "jl_moe_dev": (_I, [_VP, _VP, _VP, _I, _VP, _I, C.POINTER(MoeDesc), _VP, _VP, _VP]),
+    "jl_test_fail_at": (_I, [_VP, C.POINTER(C.c_int), _I]),
+}
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """dlopen the library and bind every declared symbol. Raises if it is missing."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(
+                f"{LIB_PATH} is missing: build it with `python -m jitllm_b200.build` "
+                "(there is no CPU or PyTorch fallback for this path)")
+        L = C.CDLL(LIB_PATH)
+        for name, (res, args) in SYMBOLS.items():
+            fn = getattr(L, name)  # AttributeError if the symbol is not exported
+            fn.restype = res
+            fn.argtypes = args
+        _lib = L
+    return _lib

@@ -1,0 +1,345 @@
+// The C ABI: contexts, residency keyed on host addresses, the host-pointer and
+// device-pointer entry points, selection, statistics, host-side fault injection.
+#include "jl_internal.cuh"
+
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <algorithm>
+
+int jl_set_err(jl_ctx *ctx, int code, const char *fmt, ...) {
+    if (ctx) {
+        char buf[512];
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(buf, sizeof buf, fmt, ap);
+        va_end(ap);
+        ctx->err = buf;
+        if (code == JL_DECLINED) ctx->st.declined++;
+        else if (code < 0) ctx->st.errors++;
+    }
+    return code;
+}
+
+JL_EXPORT const char *jl_version(void) { return "jitllm_b200 0.1 (sm_100a)"; }
+JL_EXPORT int jl_abi_version(void) { return JL_ABI_VERSION; }
+
+JL_EXPORT int jl_open(int device, const jl_opts *opts, jl_ctx **out) {
+    if (!out) return JL_EINVAL;
+    *out = nullptr;
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess || device < 0 || device >= n) {
+        cudaGetLastError();
+        return JL_ECUDA;  // no usable device: there is deliberately no CPU fallback
+    }
+    if (cudaSetDevice(device) != cudaSuccess) return JL_ECUDA;
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) return JL_ECUDA;
+    if (prop.major != 10) return JL_ENOTSUP;  // built for sm_100a only
+    jl_ctx *c = new jl_ctx();
+    c->device = device;
+    memset(&c->opts, 0, sizeof c->opts);
+    if (opts) memcpy(&c->opts, opts, std::min<size_t>(opts->struct_size, sizeof(jl_opts)));
+    c->unhealthy = false;
+    memset(&c->st, 0, sizeof c->st);
+    c->sm_count = prop.multiProcessorCount;
+    c->x_dev = c->o_dev = c->scratch = c->x_pin = c->o_pin = nullptr;
+    c->x_cap = c->o_cap = c->scratch_cap = c->x_pin_cap = c->o_pin_cap = 0;
+    c->call_ordinal = 0;
+    if (cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) != cudaSuccess) {
+        delete c;
+        return JL_ECUDA;
+    }
+    *out = c;
+    return JL_OK;
+}
+
+JL_EXPORT void jl_close(jl_ctx *ctx) {
+    if (!ctx) return;
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    for (auto &kv : ctx->cache) jl_weight_release(kv.second);
+    ctx->cache.clear();
+    if (ctx->x_dev) cudaFree(ctx->x_dev);
+    if (ctx->o_dev) cudaFree(ctx->o_dev);
+    if (ctx->scratch) cudaFree(ctx->scratch);
+    if (ctx->x_pin) cudaFreeHost(ctx->x_pin);
+    if (ctx->o_pin) cudaFreeHost(ctx->o_pin);
+    cudaStreamDestroy(ctx->stream);
+    delete ctx;
+}
+
+JL_EXPORT const char *jl_last_error(jl_ctx *ctx) { return ctx ? ctx->err.c_str() : "no context"; }
+
+JL_EXPORT int jl_stats_get(jl_ctx *ctx, jl_stats *out) {
+    if (!ctx || !out) return JL_EINVAL;
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    *out = ctx->st;
+    return JL_OK;
+}
+
+static int grow_dev(jl_ctx *ctx, void **p, size_t *cap, size_t need) {
+    if (*cap >= need) return JL_OK;
+    if (*p) { cudaFree(*p); *p = nullptr; *cap = 0; }
+    cudaError_t e = cudaMalloc(p, need);
+    if (e != cudaSuccess) { cudaGetLastError(); return jl_set_err(ctx, JL_ENOMEM, "cudaMalloc(%zu): %s", need, cudaGetErrorString(e)); }
+    *cap = need;
+    return JL_OK;
+}
+static int grow_pin(jl_ctx *ctx, void **p, size_t *cap, size_t need) {
+    if (*cap >= need) return JL_OK;
+    if (*p) { cudaFreeHost(*p); *p = nullptr; *cap = 0; }
+    cudaError_t e = cudaMallocHost(p, need);
+    if (e != cudaSuccess) { cudaGetLastError(); return jl_set_err(ctx, JL_ENOMEM, "cudaMallocHost(%zu): %s", need, cudaGetErrorString(e)); }
+    *cap = need;
+    return JL_OK;
+}
+
+static int reserve_locked(jl_ctx *ctx, size_t x_bytes, size_t o_bytes) {
+    int rc;
+    if ((rc = grow_dev(ctx, &ctx->x_dev, &ctx->x_cap, x_bytes))) return rc;
+    if ((rc = grow_dev(ctx, &ctx->o_dev, &ctx->o_cap, o_bytes))) return rc;
+    if ((rc = grow_pin(ctx, &ctx->x_pin, &ctx->x_pin_cap, x_bytes))) return rc;
+    if ((rc = grow_pin(ctx, &ctx->o_pin, &ctx->o_pin_cap, o_bytes))) return rc;
+    return JL_OK;
+}
+
+JL_EXPORT int jl_reserve(jl_ctx *ctx, int max_rows, int max_k, int max_tok) {
+    if (!ctx || max_rows < 1 || max_k < 1 || max_tok < 1) return JL_EINVAL;
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    JL_CUDA(ctx, cudaSetDevice(ctx->device));
+    return reserve_locked(ctx, (size_t)max_tok * max_k * 4, (size_t)max_tok * max_rows * 4);
+}
+
+// Serving calls share this prologue: health, fault injection.
+static int serving_prologue(jl_ctx *ctx) {
+    if (ctx->unhealthy) return jl_set_err(ctx, JL_ECUDA, "context is unhealthy after an earlier CUDA error");
+    ctx->call_ordinal++;
+    for (int o : ctx->fail_at)
+        if (o == ctx->call_ordinal) {
+            ctx->st.injected++;
+            return jl_set_err(ctx, JL_EDEVICE, "injected device failure at call %d", o);
+        }
+    return JL_OK;
+}
+
+JL_EXPORT int jl_test_fail_at(jl_ctx *ctx, const int *ordinals, int n) {
+    if (!ctx || n < 0 || (n > 0 && !ordinals)) return JL_EINVAL;
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    ctx->fail_at.assign(ordinals, ordinals + n);
+    ctx->call_ordinal = 0;
+    return JL_OK;
+}
+
+// ---------------------------------------------------------------- residency
+
+static void evict_for(jl_ctx *ctx, size_t incoming) {
+    uint64_t cap = ctx->opts.max_resident_bytes;
+    if (!cap) return;
+    while (!ctx->lru.empty() && ctx->st.resident_bytes + incoming > cap) {
+        uintptr_t key = ctx->lru.front();
+        ctx->lru.erase(ctx->lru.begin());
+        auto it = ctx->cache.find(key);
+        if (it == ctx->cache.end()) continue;
+        ctx->st.resident_bytes -= it->second->raw_bytes;
+        jl_weight_release(it->second);
+        ctx->cache.erase(it);
+    }
+}
+
+static void touch(jl_ctx *ctx, uintptr_t key) {
+    auto it = std::find(ctx->lru.begin(), ctx->lru.end(), key);
+    if (it != ctx->lru.end()) ctx->lru.erase(it);
+    ctx->lru.push_back(key);
+}
+
+// The device copy of a host tensor, keyed on its address (Device.MatVec's
+// contract, engine/nn/device.go:25-30). A different shape or type at a known
+// address means the caller reused the memory without telling us: re-upload.
+static int resident(jl_ctx *ctx, uint32_t type, const void *w, size_t w_bytes, int n_expert, int nrows,
+                    int k, jl_weight **out) {
+    uintptr_t key = (uintptr_t)w;
+    auto it = ctx->cache.find(key);
+    if (it != ctx->cache.end()) {
+        jl_weight *c = it->second;
+        if (c->type == type && c->nrows == nrows && c->k == k && c->n_expert == n_expert) {
+            touch(ctx, key);
+            *out = c;
+            return JL_OK;
+        }
+        ctx->st.resident_bytes -= c->raw_bytes;
+        jl_weight_release(c);
+        ctx->cache.erase(it);
+    }
+    size_t need = (size_t)n_expert * nrows * jl_row_bytes(type, k);
+    evict_for(ctx, need);
+    jl_weight *nw = nullptr;
+    int rc = jl_repack_upload(ctx, type, w, w_bytes, n_expert, nrows, k, &nw);
+    if (rc) return rc;
+    nw->host_key = w;
+    ctx->cache[key] = nw;
+    touch(ctx, key);
+    ctx->st.resident_bytes += nw->raw_bytes;
+    *out = nw;
+    return JL_OK;
+}
+
+JL_EXPORT int jl_forget(jl_ctx *ctx, const void *p, size_t n) {
+    if (!ctx) return JL_EINVAL;
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    cudaSetDevice(ctx->device);
+    uintptr_t lo = (uintptr_t)p, hi = lo + n;
+    // Every copy whose host range intersects [p, p+n).
+    for (auto it = ctx->cache.begin(); it != ctx->cache.end();) {
+        uintptr_t a = it->first, b = a + it->second->raw_bytes;
+        if (a < hi && b > lo) {
+            ctx->st.resident_bytes -= it->second->raw_bytes;
+            auto l = std::find(ctx->lru.begin(), ctx->lru.end(), a);
+            if (l != ctx->lru.end()) ctx->lru.erase(l);
+            jl_weight_release(it->second);
+            it = ctx->cache.erase(it);
+            ctx->st.forgets++;
+        } else {
+            ++it;
+        }
+    }
+    return JL_OK;
+}
+
+JL_EXPORT int jl_weight_upload_bank(jl_ctx *ctx, uint32_t type, const void *w_host, size_t w_bytes,
+                                    int n_expert, int nrows, int k, jl_weight **out) {
+    if (!ctx || !w_host || !out) return JL_EINVAL;
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    JL_CUDA(ctx, cudaSetDevice(ctx->device));
+    int rc = jl_repack_upload(ctx, type, w_host, w_bytes, n_expert, nrows, k, out);
+    if (rc == JL_OK) ctx->st.resident_bytes += (*out)->raw_bytes;
+    return rc;
+}
+
+JL_EXPORT int jl_weight_upload(jl_ctx *ctx, uint32_t type, const void *w_host, size_t w_bytes, int nrows,
+                               int k, jl_weight **out) {
+    return jl_weight_upload_bank(ctx, type, w_host, w_bytes, 1, nrows, k, out);
+}
+
+JL_EXPORT void jl_weight_free(jl_ctx *ctx, jl_weight *w) {
+    if (!ctx || !w) return;
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    ctx->st.resident_bytes -= w->raw_bytes;
+    jl_weight_release(w);
+}
+
+// ---------------------------------------------------------------- selection
+
+static int choose(jl_ctx *ctx, uint32_t type, int nrows, int k, int ntok, jl_choice *out) {
+    int pin = ctx->opts.pin_kernel;
+    if ((pin == JL_K_TC5 || (pin == JL_K_AUTO && ntok >= 16)) && jl_gemm_tc5_supported(type, nrows, k, ntok))
+        return jl_gemm_tc5_choice(ctx, type, nrows, k, ntok, out);
+    if (pin == JL_K_TC5) return JL_DECLINED;
+    return jl_gemv_choice(ctx, type, nrows, k, ntok, out);
+}
+
+JL_EXPORT int jl_select(jl_ctx *ctx, uint32_t type, int nrows, int k, int ntok, jl_choice *out) {
+    if (!ctx || !out) return JL_EINVAL;
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    int be = jl_block_elems(type);
+    if ((type != JL_TYPE_Q4_K && type != JL_TYPE_Q8_0 && type != JL_TYPE_MXFP4) || nrows < 1 || k < be ||
+        k % be || ntok < 1)
+        return jl_set_err(ctx, JL_DECLINED, "no kernel for type %u, %d x %d, %d token(s)", type, nrows, k, ntok);
+    return choose(ctx, type, nrows, k, ntok, out);
+}
+
+// ------------------------------------------------------------ device twins
+
+static int matmul_dev_locked(jl_ctx *ctx, void *out_dev, int out_dtype, const jl_weight *w, int expert,
+                             const void *x_dev, int x_dtype, int ntok, cudaStream_t s) {
+    jl_choice ch;
+    int rc = choose(ctx, w->type, w->nrows, w->k, ntok, &ch);
+    if (rc) return rc == JL_DECLINED ? jl_set_err(ctx, JL_DECLINED, "pinned kernel cannot serve this shape") : rc;
+    if (ch.kernel == JL_K_TC5)
+        return jl_launch_gemm_tc5(ctx, out_dev, out_dtype, w, expert, x_dev, x_dtype, ntok, s);
+    if (x_dtype != JL_DT_F32 || out_dtype != JL_DT_F32)
+        return jl_set_err(ctx, JL_DECLINED, "the decode kernels take f32 activations and outputs");
+    return jl_launch_gemv(ctx, (float *)out_dev, w, expert, (const float *)x_dev, ntok, ch.kernel, ch.warps, s);
+}
+
+JL_EXPORT int jl_matvec_dev(jl_ctx *ctx, float *out_dev, const jl_weight *w, const float *x_dev, int ntok,
+                            void *stream) {
+    if (!ctx || !out_dev || !w || !x_dev || ntok < 1) return JL_EINVAL;
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    int rc = serving_prologue(ctx);
+    if (rc) return rc;
+    JL_CUDA(ctx, cudaSetDevice(ctx->device));
+    rc = matmul_dev_locked(ctx, out_dev, JL_DT_F32, w, 0, x_dev, JL_DT_F32, ntok,
+                           stream ? (cudaStream_t)stream : ctx->stream);
+    if (rc == JL_OK) ctx->st.served++;
+    return rc;
+}
+
+JL_EXPORT int jl_matmul_dev(jl_ctx *ctx, void *out_dev, int out_dtype, const jl_weight *w, const void *x_dev,
+                            int x_dtype, int ntok, void *stream) {
+    if (!ctx || !out_dev || !w || !x_dev || ntok < 1) return JL_EINVAL;
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    int rc = serving_prologue(ctx);
+    if (rc) return rc;
+    JL_CUDA(ctx, cudaSetDevice(ctx->device));
+    rc = matmul_dev_locked(ctx, out_dev, out_dtype, w, 0, x_dev, x_dtype, ntok,
+                           stream ? (cudaStream_t)stream : ctx->stream);
+    if (rc == JL_OK) ctx->st.served++;
+    return rc;
+}
+
+// ------------------------------------------------------- host entry points
+
+static size_t dtype_bytes(int dt) { return dt == JL_DT_F32 ? 4 : 2; }
+
+static int matmul_host(jl_ctx *ctx, void *out, int out_dtype, uint32_t type, const void *w, size_t w_bytes,
+                       const void *x, int x_dtype, int nrows, int k, int ntok) {
+    int be = jl_block_elems(type);
+    if (type != JL_TYPE_Q4_K && type != JL_TYPE_Q8_0 && type != JL_TYPE_MXFP4)
+        return jl_set_err(ctx, JL_DECLINED, "type %u is not served", type);
+    if (nrows < 1 || k < be || k % be || ntok < 1)
+        return jl_set_err(ctx, JL_DECLINED, "shape %d x %d x %d tokens does not tile %d-element blocks", nrows, k, ntok, be);
+    size_t need = (size_t)nrows * jl_row_bytes(type, k);
+    if (w_bytes < need) return jl_set_err(ctx, JL_EINVAL, "weight has %zu bytes, shape needs %zu", w_bytes, need);
+    if (ctx->opts.min_weight_bytes && need < ctx->opts.min_weight_bytes)
+        return jl_set_err(ctx, JL_DECLINED, "%zu weight bytes is below the %llu-byte break-even", need,
+                          (unsigned long long)ctx->opts.min_weight_bytes);
+    int rc = serving_prologue(ctx);
+    if (rc) return rc;
+    JL_CUDA(ctx, cudaSetDevice(ctx->device));
+    jl_weight *dw = nullptr;
+    if ((rc = resident(ctx, type, w, w_bytes, 1, nrows, k, &dw))) return rc;
+    size_t xb = (size_t)ntok * k * dtype_bytes(x_dtype), ob = (size_t)ntok * nrows * dtype_bytes(out_dtype);
+    if ((rc = reserve_locked(ctx, xb, ob))) return rc;
+    memcpy(ctx->x_pin, x, xb);
+    JL_CUDA(ctx, cudaMemcpyAsync(ctx->x_dev, ctx->x_pin, xb, cudaMemcpyHostToDevice, ctx->stream));
+    rc = matmul_dev_locked(ctx, ctx->o_dev, out_dtype, dw, 0, ctx->x_dev, x_dtype, ntok, ctx->stream);
+    if (rc) return rc;
+    JL_CUDA(ctx, cudaMemcpyAsync(ctx->o_pin, ctx->o_dev, ob, cudaMemcpyDeviceToHost, ctx->stream));
+    cudaError_t e = cudaStreamSynchronize(ctx->stream);
+    if (e != cudaSuccess) {
+        ctx->unhealthy = true;
+        return jl_set_err(ctx, JL_ECUDA, "kernel or copy failed: %s", cudaGetErrorString(e));
+    }
+    memcpy(out, ctx->o_pin, ob);
+    ctx->st.served++;
+    return JL_OK;
+}
+
+JL_EXPORT int jl_matvec(jl_ctx *ctx, float *out, uint32_t type, const void *w, size_t w_bytes, const float *x,
+                        int nrows, int k) {
+    if (!ctx || !out || !w || !x) return JL_EINVAL;
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    return matmul_host(ctx, out, JL_DT_F32, type, w, w_bytes, x, JL_DT_F32, nrows, k, 1);
+}
+
+JL_EXPORT int jl_matmul(jl_ctx *ctx, void *out, int out_dtype, uint32_t type, const void *w, size_t w_bytes,
+                        const void *x, int x_dtype, int nrows, int k, int ntok) {
+    if (!ctx || !out || !w || !x) return JL_EINVAL;
+    if (out_dtype < 0 || out_dtype > 2 || x_dtype < 0 || x_dtype > 2) return JL_EINVAL;
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    return matmul_host(ctx, out, out_dtype, type, w, w_bytes, x, x_dtype, nrows, k, ntok);
+}

@@ -1,0 +1,114 @@
+// Internal declarations shared by the translation units of libjitllm_b200.so.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+#include <map>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/jitllm_b200.h"
+
+#define JL_EXPORT extern "C" __attribute__((visibility("default")))
+
+// Block geometry, format/quant/types.go:61-85.
+static inline int jl_block_elems(uint32_t t) {
+    switch (t) {
+    case JL_TYPE_Q8_0: return 32;
+    case JL_TYPE_Q4_K: return 256;
+    case JL_TYPE_MXFP4: return 32;
+    case JL_TYPE_F32: case JL_TYPE_F16: case JL_TYPE_BF16: return 1;
+    }
+    return 0;
+}
+static inline int jl_block_bytes(uint32_t t) {
+    switch (t) {
+    case JL_TYPE_Q8_0: return 34;
+    case JL_TYPE_Q4_K: return 144;
+    case JL_TYPE_MXFP4: return 17;
+    case JL_TYPE_F32: return 4;
+    case JL_TYPE_F16: case JL_TYPE_BF16: return 2;
+    }
+    return 0;
+}
+static inline size_t jl_row_bytes(uint32_t t, int k) {
+    return (size_t)(k / jl_block_elems(t)) * (size_t)jl_block_bytes(t);
+}
+
+// A weight (or a bank of n_expert equal weights) resident on the device.
+//
+// Resident layouts (every repack is a byte permutation, shown bit-exact by
+// jl_unpack_resident):
+//   Q4_K   data = the raw 144-byte super-blocks, untouched. Rows are 16-byte
+//          multiples, so every super-block is nine aligned 16-byte chunks.
+//   Q8_0   data = int8 codes, [row][k/64 spans][4 lanes][16 B]; lane t's 16
+//          bytes are four words: block 2s codes [4t,4t+4), block 2s codes
+//          [16+4t,16+4t+4), then the same two of block 2s+1 -- the order in
+//          which one mma.sync lane consumes them. scales = f16 d, [row][k/32].
+//   MXFP4  data = the 16 code bytes of each block, [row][k/32][16];
+//          scales = the e8m0 byte of each block, [row][scale_stride].
+struct jl_weight {
+    uint32_t type;
+    int n_expert, nrows, k;
+    size_t raw_bytes;       // bytes of the raw ggml tensor this came from
+    uint8_t *data;
+    uint8_t *scales;
+    size_t data_bytes, scales_bytes;
+    int scale_stride;       // elements per row of the scales plane
+    const void *host_key;   // host address it was uploaded from (cache identity) or NULL
+};
+
+struct jl_ctx {
+    int device;
+    jl_opts opts;
+    cudaStream_t stream;
+    std::mutex mu;
+    std::string err;
+    bool unhealthy;
+    jl_stats st;
+    int sm_count;
+    // host-pointer residency: keyed on the host address (Device.MatVec's contract).
+    std::map<uintptr_t, jl_weight *> cache;
+    std::vector<uintptr_t> lru;
+    // staging for the host entry points (grown by jl_reserve or on demand).
+    void *x_dev; size_t x_cap;
+    void *o_dev; size_t o_cap;
+    void *scratch; size_t scratch_cap;
+    void *x_pin; size_t x_pin_cap;
+    void *o_pin; size_t o_pin_cap;
+    // fault injection
+    std::vector<int> fail_at;
+    int call_ordinal;
+};
+
+#define JL_CUDA(ctx, call)                                                           \
+    do {                                                                             \
+        cudaError_t e__ = (call);                                                    \
+        if (e__ != cudaSuccess) {                                                    \
+            jl_set_err((ctx), JL_ECUDA, "%s:%d %s: %s", __FILE__, __LINE__, #call,   \
+                       cudaGetErrorString(e__));                                     \
+            return JL_ECUDA;                                                         \
+        }                                                                            \
+    } while (0)
+
+int jl_set_err(jl_ctx *ctx, int code, const char *fmt, ...);
+
+// formats.cu
+int jl_repack_upload(jl_ctx *ctx, uint32_t type, const void *w_host, size_t w_bytes, int n_expert,
+                     int nrows, int k, jl_weight **out);
+void jl_weight_release(jl_weight *w);
+
+// gemv.cu -- decode kernels. x_dev [ntok][k] f32, out_dev [ntok][nrows] f32.
+int jl_launch_gemv(jl_ctx *ctx, float *out_dev, const jl_weight *w, int expert, const float *x_dev,
+                   int ntok, int kernel, int warps, cudaStream_t s);
+int jl_gemv_choice(jl_ctx *ctx, uint32_t type, int nrows, int k, int ntok, jl_choice *out);
+
+// gemm_tc5.cu -- prefill kernels (tcgen05).
+int jl_launch_gemm_tc5(jl_ctx *ctx, void *out_dev, int out_dtype, const jl_weight *w, int expert,
+                       const void *x_dev, int x_dtype, int ntok, cudaStream_t s);
+int jl_gemm_tc5_supported(uint32_t type, int nrows, int k, int ntok);
+int jl_gemm_tc5_choice(jl_ctx *ctx, uint32_t type, int nrows, int k, int ntok, jl_choice *out);

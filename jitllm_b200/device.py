@@ -1,0 +1,206 @@
+"""Host-side mirror of the reference's accelerator seam.
+
+`Device` has the methods jitllm's `nn.Device`, `CopyForgetter`, `ErrReporter`
+and `Reserve` declare (engine/nn/device.go:23-31,1169-1175,1570-1593) with the
+same argument meaning and the same error behaviour -- `MatVec`/`MatMul` return
+False to decline, and `Err()` says why -- so a test written against the
+reference's interface reads the same here. Every method is one call into
+libjitllm_b200.so; nothing is computed in Python.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import _lib
+from ._lib import Choice, MoeDesc, Opts, Stats
+
+
+class DeviceError(RuntimeError):
+    def __init__(self, status: int, msg: str):
+        super().__init__(f"jitllm_b200: status {status}: {msg}")
+        self.status = status
+
+
+def _ptr(a) -> int:
+    """Address of a numpy array, a torch tensor, a ctypes buffer or a raw int."""
+    if a is None:
+        return 0
+    if isinstance(a, int):
+        return a
+    if isinstance(a, np.ndarray):
+        if not a.flags["C_CONTIGUOUS"]:
+            raise ValueError("array must be C-contiguous")
+        return a.ctypes.data
+    if hasattr(a, "data_ptr"):
+        if not a.is_contiguous():
+            raise ValueError("tensor must be contiguous")
+        return a.data_ptr()
+    return C.addressof(a)
+
+
+def _nbytes(a) -> int:
+    if isinstance(a, np.ndarray):
+        return a.nbytes
+    if hasattr(a, "element_size"):
+        return a.numel() * a.element_size()
+    return C.sizeof(a)
+
+
+def _dtype_code(a) -> int:
+    name = str(a.dtype)
+    if name.endswith("float32"):
+        return _lib.DT_F32
+    if name.endswith("bfloat16"):
+        return _lib.DT_BF16
+    if name.endswith("float16"):
+        return _lib.DT_F16
+    raise ValueError(f"unsupported element type {a.dtype}")
+
+
+class Weight:
+    """A weight (or expert bank) resident on the device: jl_weight."""
+
+    def __init__(self, dev: "Device", handle: int, t: int, nrows: int, k: int, n_expert: int = 1):
+        self.dev, self.handle, self.type, self.nrows, self.k, self.n_expert = dev, handle, t, nrows, k, n_expert
+
+    def free(self) -> None:
+        if self.handle and self.dev.ctx:
+            self.dev.lib.jl_weight_free(self.dev.ctx, self.handle)
+        self.handle = 0
+
+    def unpack(self):
+        """Integer view of the RESIDENT copy: (q, d_bits, dmin_bits, sc, m) per 32-sub-block."""
+        nsub = self.n_expert * self.nrows * (self.k // 32)
+        q = np.empty(nsub * 32, np.int8)
+        d = np.empty(nsub, np.uint16)
+        dm = np.empty(nsub, np.uint16)
+        sc = np.empty(nsub, np.uint8)
+        m = np.empty(nsub, np.uint8)
+        self.dev._check(self.dev.lib.jl_unpack_resident(self.dev.ctx, self.handle, _ptr(q), _ptr(d), _ptr(dm),
+                                                        _ptr(sc), _ptr(m)))
+        return q, d, dm, sc, m
+
+
+class Device:
+    """One B200, behind the reference's `nn.Device` surface."""
+
+    def __init__(self, device: int = 0, pin_kernel: int = _lib.K_AUTO, pin_warps: int = 0,
+                 min_weight_bytes: int = 0, max_resident_bytes: int = 0):
+        self.lib = _lib.load()
+        self.ctx = C.c_void_p()
+        o = Opts(struct_size=C.sizeof(Opts), pin_kernel=pin_kernel, pin_warps=pin_warps,
+                 min_weight_bytes=min_weight_bytes, max_resident_bytes=max_resident_bytes, flags=0)
+        rc = self.lib.jl_open(device, C.byref(o), C.byref(self.ctx))
+        if rc != _lib.OK:
+            self.ctx = None
+            raise DeviceError(rc, "jl_open failed: no B200 (sm_100) visible as device %d; "
+                                  "this path has no CPU fallback" % device)
+        self.last_status = _lib.OK
+
+    # -- lifetime -----------------------------------------------------------
+    def Close(self) -> None:
+        if self.ctx:
+            self.lib.jl_close(self.ctx)
+            self.ctx = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.Close()
+
+    def __del__(self):
+        try:
+            self.Close()
+        except Exception:
+            pass
+
+    # -- reference surface ----------------------------------------------------
+    def MatVec(self, out, t: int, w, x, nrows: int, k: int) -> bool:
+        """nn.Device.MatVec: out[0:nrows] = W x, or False to decline. Host arrays."""
+        self.last_status = self.lib.jl_matvec(self.ctx, _ptr(out), t, _ptr(w), _nbytes(w), _ptr(x), nrows, k)
+        return self.last_status == _lib.OK
+
+    def MatMul(self, out, t: int, w, x, nrows: int, k: int, ntok: int) -> bool:
+        """JIT.MatMul: x [ntok][k] -> out [ntok][nrows], token-major. Host arrays; f32/f16/bf16
+        (16-bit types as numpy uint16 views are passed with explicit dtype codes via MatMulRaw)."""
+        return self.MatMulRaw(out, _dtype_code(out), t, w, x, _dtype_code(x), nrows, k, ntok)
+
+    def MatMulRaw(self, out, out_dtype: int, t: int, w, x, x_dtype: int, nrows: int, k: int, ntok: int) -> bool:
+        self.last_status = self.lib.jl_matmul(self.ctx, _ptr(out), out_dtype, t, _ptr(w), _nbytes(w), _ptr(x),
+                                              x_dtype, nrows, k, ntok)
+        return self.last_status == _lib.OK
+
+    def Forget(self, p, n: int | None = None) -> None:
+        """CopyForgetter.Forget: drop device copies of host bytes [p, p+n)."""
+        self.lib.jl_forget(self.ctx, _ptr(p), _nbytes(p) if n is None else n)
+
+    def Err(self) -> str:
+        """ErrReporter.Err: why the last call declined or failed."""
+        return self.lib.jl_last_error(self.ctx).decode()
+
+    def Reserve(self, max_rows: int, max_k: int, max_tok: int = 1) -> None:
+        self._check(self.lib.jl_reserve(self.ctx, max_rows, max_k, max_tok))
+
+    # -- selection, statistics, fault injection --------------------------------
+    def Select(self, t: int, nrows: int, k: int, ntok: int = 1) -> Choice | None:
+        ch = Choice()
+        rc = self.lib.jl_select(self.ctx, t, nrows, k, ntok, C.byref(ch))
+        self.last_status = rc
+        return ch if rc == _lib.OK else None
+
+    def Stats(self) -> Stats:
+        s = Stats()
+        self._check(self.lib.jl_stats_get(self.ctx, C.byref(s)))
+        return s
+
+    def FailAt(self, ordinals) -> None:
+        arr = (C.c_int * len(ordinals))(*ordinals)
+        self._check(self.lib.jl_test_fail_at(self.ctx, arr, len(ordinals)))
+
+    # -- device-pointer twins ----------------------------------------------------
+    def Upload(self, t: int, w, nrows: int, k: int, n_expert: int = 1) -> Weight:
+        h = C.c_void_p()
+        self._check(self.lib.jl_weight_upload_bank(self.ctx, t, _ptr(w), _nbytes(w), n_expert, nrows, k,
+                                                   C.byref(h)))
+        return Weight(self, h.value, t, nrows, k, n_expert)
+
+    def MatVecDev(self, out, weight: Weight, x, ntok: int = 1, stream: int = 0) -> None:
+        """Device tensors: x [ntok][k] f32 -> out [ntok][nrows] f32, on `stream`."""
+        self._check(self.lib.jl_matvec_dev(self.ctx, _ptr(out), weight.handle, _ptr(x), ntok, stream))
+
+    def MatMulDev(self, out, weight: Weight, x, ntok: int, stream: int = 0) -> None:
+        self._check(self.lib.jl_matmul_dev(self.ctx, _ptr(out), _dtype_code(out), weight.handle, _ptr(x),
+                                           _dtype_code(x), ntok, stream))
+
+    def Moe(self, out, h, logits, ntok: int, desc: MoeDesc, sel_out=None, wt_out=None) -> bool:
+        """State.moeBatch on host arrays. False = declined."""
+        self.last_status = self.lib.jl_moe(self.ctx, _ptr(out), _ptr(h), _dtype_code(h), _ptr(logits), ntok,
+                                           C.byref(desc), _ptr(sel_out), _ptr(wt_out))
+        return self.last_status == _lib.OK
+
+    def MoeDev(self, out, h, logits, ntok: int, desc: MoeDesc, sel_out=None, wt_out=None, stream: int = 0) -> None:
+        self._check(self.lib.jl_moe_dev(self.ctx, _ptr(out), _ptr(h), _dtype_code(h), _ptr(logits), ntok,
+                                        C.byref(desc), _ptr(sel_out), _ptr(wt_out), stream))
+
+    def _check(self, rc: int) -> None:
+        self.last_status = rc
+        if rc != _lib.OK:
+            raise DeviceError(rc, self.Err() if self.ctx else "")
+
+
+def unpack_host(t: int, blocks, n_blocks: int):
+    """jl_unpack: the host implementation of kernels.extract over raw blocks."""
+    lib = _lib.load()
+    nsub = n_blocks * (_lib.BLOCK[t][0] // 32)
+    q = np.empty(nsub * 32, np.int8)
+    d = np.empty(nsub, np.uint16)
+    dm = np.empty(nsub, np.uint16)
+    sc = np.empty(nsub, np.uint8)
+    m = np.empty(nsub, np.uint8)
+    rc = lib.jl_unpack(t, _ptr(blocks), n_blocks, _ptr(q), _ptr(d), _ptr(dm), _ptr(sc), _ptr(m))
+    if rc != _lib.OK:
+        raise DeviceError(rc, "jl_unpack")
+    return q, d, dm, sc, m

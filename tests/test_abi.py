@@ -1,0 +1,73 @@
+"""The C-ABI boundary without a GPU: the library loads, exports every symbol the
+header declares, refuses to open without a B200 (no CPU fallback), and its
+host-side integer unpack equals the oracle's restatement of kernels.extract."""
+import ctypes as C
+import os
+import re
+
+import numpy as np
+import pytest
+
+from conftest import ROOT
+from jitllm_b200 import _lib, synth
+from jitllm_b200.device import unpack_host
+
+
+def _declared():
+    text = open(os.path.join(ROOT, "include", "jitllm_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(jl_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_and_binding_name_the_same_symbols():
+    assert _declared() == sorted(_lib.SYMBOLS)
+
+
+def test_library_exports_every_declared_symbol():
+    lib = _lib.load()
+    for name in _declared():
+        assert hasattr(lib, name), name
+    assert lib.jl_abi_version() == 1
+    assert b"sm_100a" in lib.jl_version()
+
+
+def test_struct_sizes_match_the_header_layout():
+    # natural C layout of the structs in include/jitllm_b200.h
+    assert C.sizeof(_lib.Opts) == 40
+    assert C.sizeof(_lib.Choice) == 32
+    assert C.sizeof(_lib.Stats) == 72
+    assert C.sizeof(_lib.MoeDesc) == 120
+
+
+@pytest.mark.skipif(os.path.exists("/dev/nvidiactl"), reason="a GPU is present")
+def test_open_fails_loudly_without_a_gpu():
+    from jitllm_b200 import Device, DeviceError
+    with pytest.raises(DeviceError):
+        Device(0)
+
+
+@pytest.mark.parametrize("t", [_lib.Q4_K, _lib.Q8_0, _lib.MXFP4])
+def test_host_unpack_equals_the_oracle(orc, t):
+    rng = synth.rng_for(100 + t)
+    w = synth.matrix(rng, t, 5, 768 if t != _lib.Q4_K else 1024)
+    nb = w.size // _lib.BLOCK[t][1]
+    got = unpack_host(t, w, nb)
+    want = orc.unpack(t, w, nb)
+    for g, x in zip(got, want):
+        assert np.array_equal(g, x)
+
+
+def test_host_unpack_on_reference_goldens(orc, golden):
+    for name, t in [("q4_k_tiny", 12), ("q8_0_gemma", 8), ("mxfp4", 39)]:
+        blocks = golden[name + "_blocks"]
+        nb = blocks.size // _lib.BLOCK[t][1]
+        for g, x in zip(unpack_host(t, blocks, nb), orc.unpack(t, blocks, nb)):
+            assert np.array_equal(g, x)
+
+
+def test_unpack_rejects_unknown_types():
+    lib = _lib.load()
+    b = np.zeros(64, np.uint8)
+    o = np.zeros(64, np.uint8)
+    assert lib.jl_unpack(2, b.ctypes.data, 1, o.ctypes.data, o.ctypes.data, o.ctypes.data, o.ctypes.data,
+                         o.ctypes.data) == _lib.ENOTSUP

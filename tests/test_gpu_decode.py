@@ -1,0 +1,188 @@
+"""Decode-operator parity on a B200, through the C ABI, against the CPU oracle."""
+import numpy as np
+import pytest
+
+from conftest import nmse, parity_err
+from jitllm_b200 import DECLINED, K_MMA, K_SIMT, MXFP4, Q4_K, Q8_0, Device, synth
+
+pytestmark = pytest.mark.gpu
+
+BAR = 2e-3  # max_i |got-ref| / max(|ref_i|, rms(ref)), f32 accumulate
+
+
+def _check(dev, orc, t, nrows, k, seed, x=None):
+    rng = synth.rng_for(seed)
+    w = synth.matrix(rng, t, nrows, k)
+    if x is None:
+        x = synth.activations(rng, 1, k)[0]
+    out = np.full(nrows, np.nan, np.float32)  # poisoned: every row must be written
+    assert dev.MatVec(out, t, w, x, nrows, k), dev.Err()
+    ref = orc.matmul_f64(t, w, x, nrows, k, 1)[0]
+    assert np.isfinite(out).all()
+    err = parity_err(out, ref)
+    assert err <= BAR, (err, nmse(out, ref))
+    dev.Forget(w)
+    return out, ref, w, x
+
+
+@pytest.mark.parametrize("t", [Q4_K, Q8_0, MXFP4])
+@pytest.mark.parametrize("nrows,k", [(16, 256), (1, 256), (37, 512), (256, 2048), (4096, 4096)])
+def test_matvec_check_kernel_matches_oracle(orc, t, nrows, k):
+    with Device(0, pin_kernel=K_SIMT) as d:
+        out, ref, _, _ = _check(d, orc, t, nrows, k, 0xB200 + nrows + k + t)
+        assert nmse(out, ref) < 1e-10
+
+
+@pytest.mark.parametrize("warps", [4, 8, 16])
+@pytest.mark.parametrize("nrows,k", [(16, 256), (16, 512), (5, 256), (100, 1024), (4096, 4096), (1024, 4096),
+                                      (4096, 14336), (14336, 4096)])
+def test_q4k_tensor_core_decode_matches_oracle(orc, warps, nrows, k):
+    with Device(0, pin_kernel=K_MMA, pin_warps=warps) as d:
+        ch = d.Select(Q4_K, nrows, k, 1)
+        assert ch is not None and ch.kernel == K_MMA
+        out, ref, _, _ = _check(d, orc, Q4_K, nrows, k, 0xB200 + nrows * 3 + k + warps)
+        assert nmse(out, ref) < 1e-10  # the reference's bar for the same quantity (matvec_test.go:135)
+
+
+def test_q4k_decode_equals_oracle_matvec_config0(dev, orc):
+    """BASELINE config 0 verbatim: 4096x4096 Q4_K, x ~ N(0,1) f32, one seed."""
+    rng = synth.rng_for(0xB200)
+    w = synth.q4k_matrix(rng, 4096, 4096)
+    x = synth.activations(rng, 1, 4096)[0]
+    out = np.full(4096, np.nan, np.float32)
+    assert dev.MatVec(out, Q4_K, w, x, 4096, 4096), dev.Err()
+    ref32 = orc.matvec(Q4_K, w, x, 4096, 4096)          # oracle.MatVec, compensated f32
+    ref64 = orc.matmul_f64(Q4_K, w, x, 4096, 4096, 1)[0]
+    assert parity_err(out, ref64) <= BAR
+    assert parity_err(out, ref32) <= BAR
+    assert nmse(out, ref64) < 1e-10
+    # same bits twice: the cross-warp reduction has a fixed order
+    out2 = np.empty_like(out)
+    assert dev.MatVec(out2, Q4_K, w, x, 4096, 4096)
+    assert np.array_equal(out.view(np.uint32), out2.view(np.uint32))
+    # the reference's int8-activation CPU path sits ~1e-5 NMSE away (reported, not gated there)
+    twin = orc.matmul_int8(Q4_K, w, x, 4096, 4096, 1, window=256)[0]
+    assert nmse(twin, ref64) < 2e-4
+    dev.Forget(w)
+
+
+@pytest.mark.parametrize("dist", ["uniform", "student_t", "one_huge", "tiny", "huge", "zeros"])
+def test_q4k_decode_input_distributions(dev, orc, dist):
+    # jit/cpu/matvec_test.go:56-115 runs four activation distributions; the scaled hi/lo split
+    # must also survive ranges f16 alone cannot hold.
+    rng = synth.rng_for(77)
+    k = 2048
+    if dist == "uniform":
+        x = rng.uniform(-1, 1, k)
+    elif dist == "student_t":
+        x = rng.standard_t(3, k)
+    elif dist == "one_huge":
+        x = rng.standard_normal(k); x[::32] *= 1000.0
+    elif dist == "tiny":
+        x = rng.standard_normal(k) * 1e-9
+    elif dist == "huge":
+        x = rng.standard_normal(k) * 1e9
+    else:
+        x = np.zeros(k)
+    out, ref, _, _ = _check(dev, orc, Q4_K, 64, k, 78, x=x.astype(np.float32))
+    if dist == "zeros":
+        assert not out.any()
+
+
+def test_planted_scales(dev, orc):
+    # quant.PlantScales (format/quant/types.go:158-216): subnormal and extreme f16 super-scales.
+    rng = synth.rng_for(9)
+    n, k = 32, 1024
+    nb = n * k // 256
+    scales = synth.planted_f16_scales()
+    blk = synth.q4k_from_parts(np.resize(scales, nb), np.resize(scales[::-1], nb),
+                               rng.integers(0, 64, (nb, 8)), rng.integers(0, 64, (nb, 8)),
+                               rng.integers(0, 16, (nb, 256))).reshape(n, -1)
+    x = synth.activations(rng, 1, k)[0]
+    for pin in (K_SIMT, K_MMA):
+        with Device(0, pin_kernel=pin) as d:
+            out = np.full(n, np.nan, np.float32)
+            assert d.MatVec(out, Q4_K, blk, x, n, k), d.Err()
+            ref = orc.matmul_f64(Q4_K, blk, x, n, k, 1)[0]
+            assert parity_err(out, ref) <= BAR
+
+
+def test_small_batch_matmul_matches_oracle(dev, orc):
+    rng = synth.rng_for(55)
+    for t, nrows, k, ntok in [(Q4_K, 128, 1024, 3), (Q8_0, 96, 512, 5), (MXFP4, 64, 320 * 2, 2)]:
+        w = synth.matrix(rng, t, nrows, k)
+        x = synth.activations(rng, ntok, k)
+        out = np.full((ntok, nrows), np.nan, np.float32)
+        assert dev.MatMul(out, t, w, x, nrows, k, ntok), dev.Err()
+        ref = orc.matmul_f64(t, w, x, nrows, k, ntok)
+        assert parity_err(out, ref) <= BAR
+        dev.Forget(w)
+
+
+@pytest.mark.parametrize("t", [Q4_K, Q8_0, MXFP4])
+def test_resident_copy_unpacks_bit_exact(dev, orc, t):
+    # the repack at upload is a permutation: codes, scales and raw d bits survive it exactly
+    rng = synth.rng_for(200 + t)
+    nrows, k = 24, 1024 if t == Q4_K else 640
+    w = synth.matrix(rng, t, nrows, k)
+    h = dev.Upload(t, w, nrows, k)
+    got = h.unpack()
+    want = orc.unpack(t, w, w.size // {Q4_K: 144, Q8_0: 34, MXFP4: 17}[t])
+    for g, x in zip(got, want):
+        assert np.array_equal(g, x)
+    h.free()
+
+
+def test_declines_and_errors_follow_the_reference_contract(dev):
+    out = np.zeros(8, np.float32)
+    x = np.zeros(100, np.float32)
+    w = np.zeros(4096, np.uint8)
+    assert not dev.MatVec(out, 2, w, x, 8, 64)          # Q4_0: unsupported type declines
+    assert dev.last_status == DECLINED and "not served" in dev.Err()
+    assert not dev.MatVec(out, Q4_K, w, x, 8, 100)      # ragged k declines
+    assert dev.last_status == DECLINED
+    assert not dev.MatVec(out, Q4_K, w[:100], x, 8, 256)  # short weight is an error, not a decline
+    assert dev.last_status < 0
+
+
+def test_residency_is_keyed_on_the_host_pointer_and_forget_drops_it(orc):
+    rng = synth.rng_for(3)
+    w = synth.q4k_matrix(rng, 64, 512)
+    x = synth.activations(rng, 1, 512)[0]
+    out = np.zeros(64, np.float32)
+    with Device(0) as d:
+        assert d.MatVec(out, Q4_K, w, x, 64, 512)
+        assert d.MatVec(out, Q4_K, w, x, 64, 512)
+        s = d.Stats()
+        assert s.uploads == 1 and s.served == 2 and s.resident_bytes == w.nbytes
+        first = out.copy()
+        # the caller rewrites the bytes in place and says so
+        w[:] = synth.q4k_matrix(rng, 64, 512)
+        d.Forget(w)
+        assert d.Stats().resident_bytes == 0 and d.Stats().forgets == 1
+        assert d.MatVec(out, Q4_K, w, x, 64, 512)
+        assert d.Stats().uploads == 2
+        assert not np.array_equal(out, first)
+        assert parity_err(out, orc.matmul_f64(Q4_K, w, x, 64, 512, 1)[0]) <= BAR
+
+
+def test_min_weight_bytes_declines_small_weights():
+    w = synth.q4k_matrix(synth.rng_for(1), 16, 256)
+    with Device(0, min_weight_bytes=1 << 20) as d:
+        assert not d.MatVec(np.zeros(16, np.float32), Q4_K, w, np.zeros(256, np.float32), 16, 256)
+        assert d.last_status == DECLINED and "break-even" in d.Err()
+
+
+def test_host_side_fault_injection(orc):
+    # jit/gpu/tier/fault.go:12-58: fail the n-th call on the host; the caller sees an error and
+    # the context stays usable.
+    w = synth.q4k_matrix(synth.rng_for(1), 16, 256)
+    x = synth.activations(synth.rng_for(2), 1, 256)[0]
+    out = np.zeros(16, np.float32)
+    with Device(0) as d:
+        d.FailAt([2])
+        assert d.MatVec(out, Q4_K, w, x, 16, 256)
+        assert not d.MatVec(out, Q4_K, w, x, 16, 256)
+        assert d.last_status == -4 and "injected" in d.Err()
+        assert d.MatVec(out, Q4_K, w, x, 16, 256)
+        assert d.Stats().injected == 1
