@@ -82,8 +82,14 @@ typedef struct jl_opts {
                                   0 = serve everything                                */
     uint64_t max_resident_bytes; /* cap on device copies kept for host-pointer calls;
                                   0 = no cap                                          */
-    uint32_t flags;            /* reserved, 0 */
+    uint32_t flags;            /* JL_FLAG_* */
 } jl_opts;
+
+/* Launch decode kernels without programmatic dependent launch (by default a decode kernel
+ * starts fetching its weights while its predecessor in the stream is still draining). */
+#define JL_FLAG_NO_PDL 1u
+/* Stream decode weights with per-lane 128-bit loads instead of TMA tile copies. */
+#define JL_FLAG_NO_TMA 2u
 
 typedef struct jl_ctx jl_ctx;
 typedef struct jl_weight jl_weight;

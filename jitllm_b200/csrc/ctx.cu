@@ -51,6 +51,12 @@ JL_EXPORT int jl_open(int device, const jl_opts *opts, jl_ctx **out) {
         delete c;
         return JL_ECUDA;
     }
+    c->dev_status = nullptr;
+    if (cudaMalloc(&c->dev_status, sizeof(int)) != cudaSuccess || cudaMemset(c->dev_status, 0, sizeof(int)) != cudaSuccess) {
+        cudaStreamDestroy(c->stream);
+        delete c;
+        return JL_ECUDA;
+    }
     *out = c;
     return JL_OK;
 }
@@ -64,6 +70,7 @@ JL_EXPORT void jl_close(jl_ctx *ctx) {
     if (ctx->x_dev) cudaFree(ctx->x_dev);
     if (ctx->o_dev) cudaFree(ctx->o_dev);
     if (ctx->scratch) cudaFree(ctx->scratch);
+    if (ctx->dev_status) cudaFree(ctx->dev_status);
     if (ctx->x_pin) cudaFreeHost(ctx->x_pin);
     if (ctx->o_pin) cudaFreeHost(ctx->o_pin);
     cudaStreamDestroy(ctx->stream);
@@ -96,6 +103,16 @@ static int grow_pin(jl_ctx *ctx, void **p, size_t *cap, size_t need) {
     return JL_OK;
 }
 
+// Device scratch of the decode kernels (the prepared activation operand). It only ever
+// grows, and only here: at weight upload, in jl_reserve and before a host-pointer call,
+// never inside a device-pointer call (which may be under stream capture).
+int jl_grow_scratch(jl_ctx *ctx, size_t need) {
+    if (ctx->scratch_cap >= need) return JL_OK;
+    cudaError_t e = cudaDeviceSynchronize();  // an earlier launch may still read the old buffer
+    if (e != cudaSuccess) return jl_set_err(ctx, JL_ECUDA, "cudaDeviceSynchronize: %s", cudaGetErrorString(e));
+    return grow_dev(ctx, &ctx->scratch, &ctx->scratch_cap, need);
+}
+
 static int reserve_locked(jl_ctx *ctx, size_t x_bytes, size_t o_bytes) {
     int rc;
     if ((rc = grow_dev(ctx, &ctx->x_dev, &ctx->x_cap, x_bytes))) return rc;
@@ -109,6 +126,8 @@ JL_EXPORT int jl_reserve(jl_ctx *ctx, int max_rows, int max_k, int max_tok) {
     if (!ctx || max_rows < 1 || max_k < 1 || max_tok < 1) return JL_EINVAL;
     std::lock_guard<std::mutex> lk(ctx->mu);
     JL_CUDA(ctx, cudaSetDevice(ctx->device));
+    int rc = jl_grow_scratch(ctx, jl_gemv_scratch_bytes(JL_TYPE_Q4_K, (max_k + 255) / 256 * 256, max_tok));
+    if (rc) return rc;
     return reserve_locked(ctx, (size_t)max_tok * max_k * 4, (size_t)max_tok * max_rows * 4);
 }
 
@@ -212,7 +231,9 @@ JL_EXPORT int jl_weight_upload_bank(jl_ctx *ctx, uint32_t type, const void *w_ho
     if (!ctx || !w_host || !out) return JL_EINVAL;
     std::lock_guard<std::mutex> lk(ctx->mu);
     JL_CUDA(ctx, cudaSetDevice(ctx->device));
-    int rc = jl_repack_upload(ctx, type, w_host, w_bytes, n_expert, nrows, k, out);
+    int rc = jl_grow_scratch(ctx, jl_gemv_scratch_bytes(type, k, 8));
+    if (rc) return rc;
+    rc = jl_repack_upload(ctx, type, w_host, w_bytes, n_expert, nrows, k, out);
     if (rc == JL_OK) ctx->st.resident_bytes += (*out)->raw_bytes;
     return rc;
 }
@@ -262,7 +283,8 @@ static int matmul_dev_locked(jl_ctx *ctx, void *out_dev, int out_dtype, const jl
         return jl_launch_gemm_tc5(ctx, out_dev, out_dtype, w, expert, x_dev, x_dtype, ntok, s);
     if (x_dtype != JL_DT_F32 || out_dtype != JL_DT_F32)
         return jl_set_err(ctx, JL_DECLINED, "the decode kernels take f32 activations and outputs");
-    return jl_launch_gemv(ctx, (float *)out_dev, w, expert, (const float *)x_dev, ntok, ch.kernel, ch.warps, s);
+    int warps = ctx->opts.pin_warps > 0 ? ctx->opts.pin_warps : ch.warps;
+    return jl_launch_gemv(ctx, (float *)out_dev, w, expert, (const float *)x_dev, ntok, ch.kernel, warps, s);
 }
 
 JL_EXPORT int jl_matvec_dev(jl_ctx *ctx, float *out_dev, const jl_weight *w, const float *x_dev, int ntok,
@@ -314,6 +336,7 @@ static int matmul_host(jl_ctx *ctx, void *out, int out_dtype, uint32_t type, con
     if ((rc = resident(ctx, type, w, w_bytes, 1, nrows, k, &dw))) return rc;
     size_t xb = (size_t)ntok * k * dtype_bytes(x_dtype), ob = (size_t)ntok * nrows * dtype_bytes(out_dtype);
     if ((rc = reserve_locked(ctx, xb, ob))) return rc;
+    if ((rc = jl_grow_scratch(ctx, jl_gemv_scratch_bytes(type, k, ntok)))) return rc;
     memcpy(ctx->x_pin, x, xb);
     JL_CUDA(ctx, cudaMemcpyAsync(ctx->x_dev, ctx->x_pin, xb, cudaMemcpyHostToDevice, ctx->stream));
     rc = matmul_dev_locked(ctx, ctx->o_dev, out_dtype, dw, 0, ctx->x_dev, x_dtype, ntok, ctx->stream);
@@ -323,6 +346,12 @@ static int matmul_host(jl_ctx *ctx, void *out, int out_dtype, uint32_t type, con
     if (e != cudaSuccess) {
         ctx->unhealthy = true;
         return jl_set_err(ctx, JL_ECUDA, "kernel or copy failed: %s", cudaGetErrorString(e));
+    }
+    int dstat = 0;
+    JL_CUDA(ctx, cudaMemcpy(&dstat, ctx->dev_status, sizeof(int), cudaMemcpyDeviceToHost));
+    if (dstat) {
+        cudaMemset(ctx->dev_status, 0, sizeof(int));
+        return jl_set_err(ctx, JL_ETIMEDOUT, "a bounded device-side wait ran out (code %d)", dstat);
     }
     memcpy(out, ctx->o_pin, ob);
     ctx->st.served++;

@@ -4,6 +4,7 @@
 // Layout knowledge restated from format/quant/dequant.go:148-174,360-397 and
 // jit/gpu/kernels/pack.go:252-386 (extract).
 #include "jl_internal.cuh"
+#include "tma.cuh"
 
 #include <stdlib.h>
 #include <string.h>
@@ -135,6 +136,9 @@ int jl_repack_upload(jl_ctx *ctx, uint32_t type, const void *w_host, size_t w_by
         w->data_bytes = need;
         if ((e = cudaMalloc(&w->data, need + 16)) != cudaSuccess) goto oom;
         if ((e = cudaMemcpyAsync(w->data, w_host, need, cudaMemcpyHostToDevice, ctx->stream)) != cudaSuccess) goto fail;
+        w->has_map_sb16 = jl_make_tmap_2d(&w->map_sb16, w->data, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1,
+                                          jl_row_bytes(type, k), rows, jl_row_bytes(type, k), 144, 16,
+                                          CU_TENSOR_MAP_SWIZZLE_NONE);
     } else {
         uint8_t *raw = nullptr;
         if ((e = cudaMalloc(&raw, need)) != cudaSuccess) goto oom;

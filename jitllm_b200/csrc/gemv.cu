@@ -22,6 +22,7 @@
 //                  rows and meet through shared memory in fixed order, so the
 //                  result is run-to-run bit-stable.
 #include "jl_internal.cuh"
+#include "tma.cuh"
 
 #include <stdio.h>
 
@@ -112,244 +113,246 @@ __global__ void __launch_bounds__(256) gemv_simt_kernel(const uint8_t *__restric
 }
 
 // ---------------------------------------------------------------- MMA family
+//
+// Q4_K decode on the tensor cores, one token.
+//
+// A warp-task is 16 rows x one 256-element super-block (2304 bytes of weights).
+// Lane (g, t) of the warp owns rows g and g+8 and the 32 code bytes of 64-element
+// group t, i.e. sub-blocks 2t (low nibbles) and 2t+1 (high nibbles).
+//
+//   weights      one TMA copy per task (2-D tensor map over the raw bytes, box =
+//                144 B x 16 rows) into a per-warp shared-memory ring; the first STAGES
+//                tasks of every warp are requested in the kernel's first instructions,
+//                before it waits for its predecessor in the stream.
+//   A operand    the 4-bit codes as unsigned bytes: (w & 0x0F0F0F0F) and
+//                ((w >> 4) & 0x0F0F0F0F), three ALU ops per eight weights.
+//   activations  made once per matvec by q4k_xprep_kernel: per super-block a scale
+//                s = 32512 / amax and two int8 digits, x*s ~ 256 q1 + q2 (|err| <= 0.5,
+//                i.e. 1.5e-5 of the super-block's amax), already laid out as MMA B
+//                fragments, plus the integer sum of 256 q1 + q2 over each sub-block.
+//   B operand    block-diagonal: column 2t carries digit 1 and column 2t+1 digit 2 of
+//                group t, all other columns are zero, so the eight columns of one
+//                accumulator collect four sub-block sums separately (even sub-blocks
+//                in `ce`, odd in `co`) instead of seven columns idling.
+//   mma.sync     m16n8k32 u8 x s8 -> s32: exact. Eight per task.
+//   fold         lane (g, t) ends with the integer dot products of sub-blocks 2t and
+//                2t+1 for its two rows; sc, m enter as integers (IMAD), d, dmin and
+//                1/s in f32: out += (d (sc_e P_e + sc_o P_o) - dmin (m_e S_e + m_o S_o)) / s.
+//   reduce       the t lanes by shuffle, the warps of a CTA (which hold different
+//                super-blocks of the same 16 rows) through shared memory in fixed
+//                order: run-to-run bit-stable.
 
-__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+__device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-__device__ __forceinline__ uint32_t hfma2u(uint32_t a, uint32_t b, uint32_t c) {
-    uint32_t d;
-    asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-    return d;
-}
-__device__ __forceinline__ uint32_t hmul2u(uint32_t a, uint32_t b) {
-    uint32_t d;
-    asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-    return d;
-}
-__device__ __forceinline__ uint32_t hsub2u(uint32_t a, uint32_t b) {
-    uint32_t d;
-    asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-    return d;
-}
-__device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
-    __half2 h = __floats2half2_rn(lo, hi);
-    return *reinterpret_cast<uint32_t *>(&h);
+// Prepared activation operand, per (token, super-block): Q4K_XP_SB_BYTES bytes.
+//   [0, 576)    4 groups x 144 B (128 used; 144 staggers the shared-memory banks):
+//               slot (hl, cp) at hl*64 + cp*16 = {digit1[8], digit2[8]} for the 8
+//               activations that code words 2cp and 2cp+1 of nibble half hl multiply
+//   [576, 640)  4 x {int32 S[2t], int32 S[2t+1], float 1/s, 0}
+// followed, after all super-blocks of all tokens, by 128 zero bytes (the B fragment
+// of the lanes that feed a zero column).
+#define Q4K_XP_GROUP_BYTES 144
+#define Q4K_XP_AUX_OFS 576
+#define Q4K_XP_SB_BYTES 640
+#define Q4K_XP_ZERO_BYTES 128
+static size_t q4k_xprep_bytes(int nsb, int ntok) {
+    return (size_t)ntok * nsb * Q4K_XP_SB_BYTES + Q4K_XP_ZERO_BYTES;
 }
 
-// Shared-memory geometry of the Q4_K decode kernel, per super-block:
-//   xfrag  4 lanes x 17 slots x 16 B (16 used; the 17th staggers the banks):
-//          slot (t, hl*8 + c) = {hi(x0,x2), hi(x1,x3), lo(x0,x2), lo(x1,x3)} of the
-//          four activations e0..e0+3, e0 = 256 sb + 64 t + 32 hl + 4 c -- what the
-//          lane holding code word c of group t multiplies against.
-//   sxfrag 4 lanes x 8 B: {hi(S[2t], S[2t+1]), lo(...)}, S = sub-block sums / 64.
-#define Q4K_XF_SB_BYTES (4 * 17 * 16)
-#define Q4K_SX_SB_BYTES (4 * 8)
-
-// Per-lane constants of one row's super-block: multipliers that turn the
-// "nibble OR 1024.0" patterns into sc*q, and the minimum pair as f16.
-struct q4k_rowk {
-    uint32_t me, ae, mo, ao;  // half2 broadcast: even sub-block (low nibbles), odd (high nibbles)
-    uint32_t hm;              // half2 (m[2t], m[2t+1])
-    float d, dmin;
-};
-
-__device__ __forceinline__ q4k_rowk q4k_prepare(const uint4 &h, int t) {
-    // h.x = d | dmin << 16; h.y, h.z, h.w = the twelve scale bytes q[0..11].
-    // Sub-blocks 2t and 2t+1 (format/quant/dequant.go:360-365):
-    //   j < 4 : sc = q[j] & 63,                      m = q[j+4] & 63
-    //   j >= 4: sc = (q[j+4] & 15) | (q[j-4] >> 6) << 4,  m = (q[j+4] >> 4) | (q[j] >> 6) << 4
-    int sh = (t & 1) * 16;
-    uint32_t a = h.y >> sh, b = h.z >> sh, c = h.w >> sh;
-    uint32_t scp, mp;
-    if (t < 2) {
-        scp = a & 0x3F3Fu;
-        mp = b & 0x3F3Fu;
-    } else {
-        scp = (c & 0x0F0Fu) | ((a >> 2) & 0x3030u);
-        mp = ((c >> 4) & 0x0F0Fu) | ((b >> 2) & 0x3030u);
+// One warp per (super-block, token). Lane l and l+32 each take one code word's worth
+// (4 consecutive activations).
+__global__ void __launch_bounds__(128)
+q4k_xprep_kernel(const float *__restrict__ X, uint8_t *__restrict__ scratch, int nsb, int ntok) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // x comes from the previous kernel
+    const int lane = threadIdx.x & 31;
+    const int sb = blockIdx.x * 4 + (threadIdx.x >> 5), tok = blockIdx.y;
+    if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x < Q4K_XP_ZERO_BYTES / 4)
+        reinterpret_cast<uint32_t *>(scratch + (size_t)ntok * nsb * Q4K_XP_SB_BYTES)[threadIdx.x] = 0u;
+    if (sb >= nsb) return;
+    uint8_t *out = scratch + ((size_t)tok * nsb + sb) * Q4K_XP_SB_BYTES;
+    const float4 *x4 = reinterpret_cast<const float4 *>(X + ((size_t)tok * nsb + sb) * 256);
+    float4 v0 = __ldg(x4 + lane), v1 = __ldg(x4 + 32 + lane);
+    float amax = fmaxf(fmaxf(fmaxf(fabsf(v0.x), fabsf(v0.y)), fmaxf(fabsf(v0.z), fabsf(v0.w))),
+                       fmaxf(fmaxf(fabsf(v1.x), fabsf(v1.y)), fmaxf(fabsf(v1.z), fabsf(v1.w))));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const bool live = amax > 0.f && amax < __int_as_float(0x7f800000);
+    const float scale = live ? 32512.f / amax : 0.f;
+    const float inv_scale = live ? amax / 32512.f : 0.f;
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        const float4 v = h ? v1 : v0;
+        const int q = lane + 32 * h;             // quad index: element 4q = 64 t + 32 hl + 4 c
+        const int t = q >> 4, hl = (q >> 3) & 1, c = q & 7;
+        const float xs[4] = {v.x * scale, v.y * scale, v.z * scale, v.w * scale};
+        uint32_t d1 = 0, d2 = 0;
+        int sum = 0;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const float q1f = rintf(xs[j] * (1.f / 256.f));
+            const int q1 = (int)q1f;
+            int q2 = (int)rintf(xs[j] - 256.f * q1f);
+            q2 = max(-127, min(127, q2));
+            d1 |= (uint32_t)(q1 & 0xFF) << (8 * j);
+            d2 |= (uint32_t)(q2 & 0xFF) << (8 * j);
+            sum += 256 * q1 + q2;
+        }
+        uint8_t *slot = out + t * Q4K_XP_GROUP_BYTES + hl * 64 + (c >> 1) * 16 + (c & 1) * 4;
+        *reinterpret_cast<uint32_t *>(slot) = d1;
+        *reinterpret_cast<uint32_t *>(slot + 8) = d2;
+        // the 8 lanes sharing (t, hl) hold one 32-element sub-block
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+        const int other = __shfl_xor_sync(0xffffffffu, sum, 8);  // the other nibble half
+        if ((q & 15) == 0)
+            *reinterpret_cast<int4 *>(out + Q4K_XP_AUX_OFS + t * 16) =
+                make_int4(sum, other, __float_as_int(inv_scale), 0);
     }
-    const uint32_t k1024 = 0x64006400u;          // half2(1024, 1024)
-    const uint32_t kscl = 0x2C003C00u;           // half2(1, 1/16)
-    const uint32_t kneg = 0xE400E400u;           // half2(-1024, -1024)
-    uint32_t hs = hsub2u(__byte_perm(scp, 0x64646464u, 0x4140), k1024);  // (sc_e, sc_o)
-    hs = hmul2u(hs, kscl);                                                // (sc_e, sc_o / 16)
-    q4k_rowk r;
-    r.me = __byte_perm(hs, hs, 0x1010);
-    r.mo = __byte_perm(hs, hs, 0x3232);
-    r.ae = hmul2u(r.me, kneg);
-    r.ao = hmul2u(r.mo, kneg);
-    r.hm = hsub2u(__byte_perm(mp, 0x64646464u, 0x4140), k1024);
-    __half2 dd = *reinterpret_cast<const __half2 *>(&h.x);
-    float2 f = __half22float2(dd);
-    r.d = f.x;
-    r.dmin = f.y;
-    return r;
 }
 
-// Power-of-two scale that brings amax into [2^14, 2^15): the f16 hi/lo split
-// then keeps ~22 bits relative to the largest activation, whatever its range.
-__device__ __forceinline__ float pow2_scale_for(float amax, float *inv) {
-    int e = (int)((__float_as_uint(amax) >> 23) & 0xFF) - 127;  // floor(log2 amax)
-    int s = 14 - e;
-    if (amax == 0.f || amax != amax) s = 0;
-    s = max(-100, min(100, s));
-    *inv = __uint_as_float((uint32_t)(127 - s) << 23);
-    return __uint_as_float((uint32_t)(127 + s) << 23);
-}
-
-template <int WARPS>
-__global__ void __launch_bounds__(WARPS * 32)
-gemv_q4k_mma_kernel(const uint8_t *__restrict__ W, const float *__restrict__ X, float *__restrict__ Y,
-                    int nrows, int nsb, int ntok) {
-    extern __shared__ __align__(16) uint8_t smem[];
-    uint8_t *xfrag = smem;
-    uint8_t *sxfrag = smem + (size_t)nsb * Q4K_XF_SB_BYTES;
-    float *red = reinterpret_cast<float *>(sxfrag + (size_t)nsb * Q4K_SX_SB_BYTES);  // [WARPS][16]
-    float *bcast = red + WARPS * 16;                                                // [WARPS] amax partials
-
+#define Q4K_TILE_BYTES (16 * 144)
+template <int WARPS, int STAGES, int MINB>
+__global__ void __launch_bounds__(WARPS * 32, MINB)
+gemv_q4k_tma_kernel(const __grid_constant__ CUtensorMap wmap, int row0, const uint8_t *__restrict__ scratch,
+                    float *__restrict__ Y, int nrows, int nsb, int ntok, int *status) {
+    extern __shared__ __align__(128) uint8_t smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int rg = blockIdx.x, tok = blockIdx.y;
-    const int k = nsb * 256;
-    const size_t row_bytes = (size_t)nsb * 144;
-    const int rowA = min(rg * 16 + g, nrows - 1), rowB = min(rg * 16 + g + 8, nrows - 1);
-    const uint8_t *pA = W + (size_t)rowA * row_bytes, *pB = W + (size_t)rowB * row_bytes;
+    // shared memory: [WARPS][STAGES] weight tiles | activation operand (nsb x 640 B + 128 zero)
+    //                | red[WARPS][16] | barriers [WARPS][STAGES] + 1
+    uint8_t *tiles = smem + (size_t)warp * STAGES * Q4K_TILE_BYTES;
+    uint8_t *xop = smem + (size_t)WARPS * STAGES * Q4K_TILE_BYTES;
+    const uint32_t xop_bytes = (uint32_t)nsb * Q4K_XP_SB_BYTES;
+    float *red = reinterpret_cast<float *>(xop + xop_bytes + Q4K_XP_ZERO_BYTES);
+    uint64_t *bars_all = reinterpret_cast<uint64_t *>(red + WARPS * 16);
+    uint64_t *bars = bars_all + warp * STAGES;
+    uint64_t *xbar = bars_all + WARPS * STAGES;
 
-    // 1. Put this warp's first super-block in flight before anything else: the
-    //    weights do not depend on the activations.
-    int sb = warp;
-    uint4 hA, qA0, qA1, hB, qB0, qB1;
-    if (sb < nsb) {
-        const uint8_t *a = pA + (size_t)sb * 144, *b = pB + (size_t)sb * 144;
-        hA = ldg16(a); qA0 = ldg16(a + 16 + 32 * t); qA1 = ldg16(a + 32 + 32 * t);
-        hB = ldg16(b); qB0 = ldg16(b + 16 + 32 * t); qB1 = ldg16(b + 32 + 32 * t);
-    }
-
-    // 2. Activations: amax -> power-of-two scale -> f16 hi/lo fragments + sub-block sums.
-    const float4 *x4 = reinterpret_cast<const float4 *>(X + (size_t)tok * k);
-    const int nquad = k / 4;
-    float amax = 0.f;
-    for (int q = tid; q < nquad; q += WARPS * 32) {
-        float4 v = __ldg(x4 + q);
-        amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
-    }
+    // The weight ring and its barriers are private to the warp: requested at once.
+    if (lane == 0) {
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-    if (lane == 0) bcast[warp] = amax;
-    __syncthreads();
-    amax = bcast[0];
+        for (int s = 0; s < STAGES; s++) mbar_init(smem_u32(bars + s), 1);
+        if (warp == 0) mbar_init(smem_u32(xbar), 1);
+        mbar_init_fence();
 #pragma unroll
-    for (int w = 1; w < WARPS; w++) amax = fmaxf(amax, bcast[w]);
-    float inv_scale;
-    const float scale = pow2_scale_for(amax, &inv_scale);
-
-    for (int q = tid; q < nquad; q += WARPS * 32) {  // nquad is a multiple of 64: whole warps stay together
-        float4 v = __ldg(x4 + q);
-        v.x *= scale; v.y *= scale; v.z *= scale; v.w *= scale;
-        __half2 h02 = __floats2half2_rn(v.x, v.z), h13 = __floats2half2_rn(v.y, v.w);
-        float2 f02 = __half22float2(h02), f13 = __half22float2(h13);
-        uint4 slot;
-        slot.x = *reinterpret_cast<uint32_t *>(&h02);
-        slot.y = *reinterpret_cast<uint32_t *>(&h13);
-        slot.z = pack_h2(v.x - f02.x, v.z - f02.y);
-        slot.w = pack_h2(v.y - f13.x, v.w - f13.y);
-        // q = 64 sb + 16 t + 8 hl + c
-        int qsb = q >> 6, qt = (q >> 4) & 3, qi = q & 15;
-        *reinterpret_cast<uint4 *>(xfrag + (size_t)qsb * Q4K_XF_SB_BYTES + (qt * 17 + qi) * 16) = slot;
-        // sub-block sum: the 8 lanes that share (sb, t, hl).
-        float s = (v.x + v.y) + (v.z + v.w);
-        s += __shfl_xor_sync(0xffffffffu, s, 1);
-        s += __shfl_xor_sync(0xffffffffu, s, 2);
-        s += __shfl_xor_sync(0xffffffffu, s, 4);
-        float so = __shfl_xor_sync(0xffffffffu, s, 8);  // the other nibble half's sub-block
-        if ((q & 15) == 0) {                           // hl == 0, c == 0: s = S[2t], so = S[2t+1]
-            float s0 = s * 0.015625f, s1 = so * 0.015625f;
-            __half2 hh = __floats2half2_rn(s0, s1);
-            float2 fh = __half22float2(hh);
-            uint2 sx;
-            sx.x = *reinterpret_cast<uint32_t *>(&hh);
-            sx.y = pack_h2(s0 - fh.x, s1 - fh.y);
-            *reinterpret_cast<uint2 *>(sxfrag + (size_t)qsb * Q4K_SX_SB_BYTES + qt * 8) = sx;
+        for (int s = 0; s < STAGES; s++) {
+            const int sbi = warp + s * WARPS;
+            if (sbi < nsb) {
+                mbar_arrive_expect_tx(smem_u32(bars + s), Q4K_TILE_BYTES);
+                tma_load_2d(smem_u32(tiles + s * Q4K_TILE_BYTES), &wmap, sbi * 144, row0 + rg * 16,
+                            smem_u32(bars + s));
+            }
         }
     }
-    __syncthreads();
+    if (tid < Q4K_XP_ZERO_BYTES / 4) reinterpret_cast<uint32_t *>(xop + xop_bytes)[tid] = 0u;
+    __syncthreads();  // xbar initialised, zero fragment written
+    // Programmatic dependent launch: the next kernel in the stream may start now; this one
+    // waits for its predecessor (the activation prep) only before it copies the operand.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (tid == 0) {
+        mbar_arrive_expect_tx(smem_u32(xbar), xop_bytes);
+        bulk_load_1d(smem_u32(xop), scratch + (size_t)tok * xop_bytes, xop_bytes, smem_u32(xbar));
+    }
+    bool lost = !__all_sync(0xffffffffu, mbar_wait(smem_u32(xbar), 0));
 
-    // 3. This warp's super-blocks.
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    const bool bcol = (g == 0);  // lanes that hold B-fragment column 0 (the one token)
-    while (sb < nsb) {
-        uint4 nhA, nqA0, nqA1, nhB, nqB0, nqB1;
-        const int nsbi = sb + WARPS;
-        if (nsbi < nsb) {  // next super-block in flight while this one is consumed
-            const uint8_t *a = pA + (size_t)nsbi * 144, *b = pB + (size_t)nsbi * 144;
-            nhA = ldg16(a); nqA0 = ldg16(a + 16 + 32 * t); nqA1 = ldg16(a + 32 + 32 * t);
-            nhB = ldg16(b); nqB0 = ldg16(b + 16 + 32 * t); nqB1 = ldg16(b + 32 + 32 * t);
+    const bool bsel = ((g >> 1) == t);  // lanes that feed a non-zero B column: digit (g & 1) of group t
+    const uint8_t *zero = xop + xop_bytes;
+    const int sh = 8 * (2 * (t & 1));   // bit offset of this lane's scale bytes inside a header word
+    float accA = 0.f, accB = 0.f;
+
+    for (int it = 0, sb = warp; sb < nsb && !lost; it++, sb += WARPS) {
+        const int s = it % STAGES;
+        const uint32_t parity = (uint32_t)(it / STAGES) & 1u;
+        const uint8_t *xsb = xop + (size_t)sb * Q4K_XP_SB_BYTES;
+        const uint8_t *xf = bsel ? xsb + t * Q4K_XP_GROUP_BYTES + (g & 1) * 8 : zero;
+        const int4 ax = *reinterpret_cast<const int4 *>(xsb + Q4K_XP_AUX_OFS + t * 16);
+        if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(bars + s), parity))) { lost = true; break; }
+        const uint8_t *tile = tiles + s * Q4K_TILE_BYTES;
+        const uint4 hA = *reinterpret_cast<const uint4 *>(tile + g * 144);
+        const uint4 qA0 = *reinterpret_cast<const uint4 *>(tile + g * 144 + 16 + 32 * t);
+        const uint4 qA1 = *reinterpret_cast<const uint4 *>(tile + g * 144 + 32 + 32 * t);
+        const uint4 hB = *reinterpret_cast<const uint4 *>(tile + (g + 8) * 144);
+        const uint4 qB0 = *reinterpret_cast<const uint4 *>(tile + (g + 8) * 144 + 16 + 32 * t);
+        const uint4 qB1 = *reinterpret_cast<const uint4 *>(tile + (g + 8) * 144 + 32 + 32 * t);
+        __syncwarp();  // every lane holds its share: the stage may be refilled
+        if (lane == 0) {
+            const int nx = sb + STAGES * WARPS;
+            if (nx < nsb) {
+                mbar_arrive_expect_tx(smem_u32(bars + s), Q4K_TILE_BYTES);
+                tma_load_2d(smem_u32(tiles + s * Q4K_TILE_BYTES), &wmap, nx * 144, row0 + rg * 16,
+                            smem_u32(bars + s));
+            }
         }
-        const q4k_rowk ka = q4k_prepare(hA, t), kb = q4k_prepare(hB, t);
+
         const uint32_t wa[8] = {qA0.x, qA0.y, qA0.z, qA0.w, qA1.x, qA1.y, qA1.z, qA1.w};
         const uint32_t wb[8] = {qB0.x, qB0.y, qB0.z, qB0.w, qB1.x, qB1.y, qB1.z, qB1.w};
-        const uint8_t *xf = xfrag + (size_t)sb * Q4K_XF_SB_BYTES + t * 17 * 16;
-        float c[4] = {0.f, 0.f, 0.f, 0.f};
-        const uint32_t k1024 = 0x64006400u;
+        int ce[4] = {0, 0, 0, 0}, co[4] = {0, 0, 0, 0};
+        const uint32_t m4 = 0x0F0F0F0Fu;
 #pragma unroll
-        for (int cw = 0; cw < 8; cw++) {
-            const uint32_t a = wa[cw], b = wb[cw];
-            const uint32_t a8 = a >> 8, b8 = b >> 8;
-            uint4 fl = make_uint4(0, 0, 0, 0), fh = make_uint4(0, 0, 0, 0);
-            if (bcol) {
-                fl = *reinterpret_cast<const uint4 *>(xf + cw * 16);
-                fh = *reinterpret_cast<const uint4 *>(xf + (8 + cw) * 16);
-            }
-            // low nibbles: sub-block 2t
-            uint32_t r0 = hfma2u((a & 0x000F000Fu) | k1024, ka.me, ka.ae);
-            uint32_t r2 = hfma2u((a8 & 0x000F000Fu) | k1024, ka.me, ka.ae);
-            uint32_t r1 = hfma2u((b & 0x000F000Fu) | k1024, kb.me, kb.ae);
-            uint32_t r3 = hfma2u((b8 & 0x000F000Fu) | k1024, kb.me, kb.ae);
-            mma16816(c, r0, r1, r2, r3, fl.x, fl.y);
-            mma16816(c, r0, r1, r2, r3, fl.z, fl.w);
-            // high nibbles: sub-block 2t+1 (pattern is 1024 + 16 q)
-            r0 = hfma2u((a & 0x00F000F0u) | k1024, ka.mo, ka.ao);
-            r2 = hfma2u((a8 & 0x00F000F0u) | k1024, ka.mo, ka.ao);
-            r1 = hfma2u((b & 0x00F000F0u) | k1024, kb.mo, kb.ao);
-            r3 = hfma2u((b8 & 0x00F000F0u) | k1024, kb.mo, kb.ao);
-            mma16816(c, r0, r1, r2, r3, fh.x, fh.y);
-            mma16816(c, r0, r1, r2, r3, fh.z, fh.w);
+        for (int cp = 0; cp < 4; cp++) {
+            const uint2 fe = *reinterpret_cast<const uint2 *>(xf + cp * 16);
+            const uint2 fo = *reinterpret_cast<const uint2 *>(xf + 64 + cp * 16);
+            const uint32_t a0 = wa[2 * cp], a2 = wa[2 * cp + 1], a1 = wb[2 * cp], a3 = wb[2 * cp + 1];
+            mma_u8s8(ce, a0 & m4, a1 & m4, a2 & m4, a3 & m4, fe.x, fe.y);
+            mma_u8s8(co, (a0 >> 4) & m4, (a1 >> 4) & m4, (a2 >> 4) & m4, (a3 >> 4) & m4, fo.x, fo.y);
         }
-        // minimums: sum_g m_g * S_g through one more MMA pair (k slots 2t, 2t+1).
-        float c2[4] = {0.f, 0.f, 0.f, 0.f};
-        uint2 sx = make_uint2(0, 0);
-        if (bcol) sx = *reinterpret_cast<const uint2 *>(sxfrag + (size_t)sb * Q4K_SX_SB_BYTES + t * 8);
-        mma16816(c2, ka.hm, kb.hm, 0u, 0u, sx.x, 0u);
-        mma16816(c2, ka.hm, kb.hm, 0u, 0u, sx.y, 0u);
-        acc[0] += ka.d * c[0] - ka.dmin * 64.f * c2[0];
-        acc[1] += ka.d * c[1] - ka.dmin * 64.f * c2[1];
-        acc[2] += kb.d * c[2] - kb.dmin * 64.f * c2[2];
-        acc[3] += kb.d * c[3] - kb.dmin * 64.f * c2[3];
-        sb = nsbi;
-        if (sb < nsb) { hA = nhA; qA0 = nqA0; qA1 = nqA1; hB = nhB; qB0 = nqB0; qB1 = nqB1; }
-    }
 
-    // 4. Column 0 lives in lanes t == 0: c[0] = row g, c[2] = row g + 8.
+        // sub-blocks e = 2t and o = 2t+1 (format/quant/dequant.go:360-365):
+        //   j < 4 : sc = q[j] & 63,                          m = q[j+4] & 63
+        //   j >= 4: sc = (q[j+4] & 15) | (q[j-4] >> 6) << 4, m = (q[j+4] >> 4) | (q[j] >> 6) << 4
+        const float inv_scale = __int_as_float(ax.z);
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+            const uint4 &h = r ? hB : hA;
+            const uint32_t a = h.y >> sh, b = h.z >> sh, c = h.w >> sh;
+            uint32_t scp, mp;
+            if (t < 2) { scp = a & 0x3F3Fu; mp = b & 0x3F3Fu; }
+            else { scp = (c & 0x0F0Fu) | ((a >> 2) & 0x3030u); mp = ((c >> 4) & 0x0F0Fu) | ((b >> 2) & 0x3030u); }
+            const int pe = (ce[2 * r] << 8) + ce[2 * r + 1];   // sum q (256 q1 + q2), sub-block e
+            const int po = (co[2 * r] << 8) + co[2 * r + 1];
+            const int dotq = (int)(scp & 0xFF) * pe + (int)(scp >> 8) * po;      // < 2^31: 2 * 63 * 15 * 32 * 32639
+            const int dotm = (int)(mp & 0xFF) * ax.x + (int)(mp >> 8) * ax.y;
+            const float2 dd = __half22float2(*reinterpret_cast<const __half2 *>(&h.x));
+            const float v = (dd.x * (float)dotq - dd.y * (float)dotm) * inv_scale;
+            if (r) accB += v; else accA += v;
+        }
+    }
+    if (lost && lane == 0) atomicExch(status, 1);  // a copy never landed: say so, never spin on
+
+    accA += __shfl_xor_sync(0xffffffffu, accA, 1);
+    accA += __shfl_xor_sync(0xffffffffu, accA, 2);
+    accB += __shfl_xor_sync(0xffffffffu, accB, 1);
+    accB += __shfl_xor_sync(0xffffffffu, accB, 2);
     if (t == 0) {
-        red[warp * 16 + g] = acc[0];
-        red[warp * 16 + g + 8] = acc[2];
+        red[warp * 16 + g] = accA;
+        red[warp * 16 + g + 8] = accB;
     }
     __syncthreads();
-    if (tid < 16) {
-        float s = 0.f;
+    if (tid < 16) {  // fixed order over the warps: run-to-run bit-stable
+        float sum = 0.f;
 #pragma unroll
-        for (int w = 0; w < WARPS; w++) s += red[w * 16 + tid];
+        for (int w = 0; w < WARPS; w++) sum += red[w * 16 + tid];
         int row = rg * 16 + tid;
-        if (row < nrows) Y[(size_t)tok * nrows + row] = s * inv_scale;
+        if (row < nrows) Y[(size_t)tok * nrows + row] = sum;
     }
 }
+static size_t q4k_tma_smem(int warps, int stages, int nsb) {
+    return (size_t)warps * stages * Q4K_TILE_BYTES + (size_t)nsb * Q4K_XP_SB_BYTES + Q4K_XP_ZERO_BYTES +
+           (size_t)warps * 16 * 4 + (size_t)(warps * stages + 1) * 8;
+}
 
-static size_t q4k_mma_smem(int nsb, int warps) {
-    return (size_t)nsb * (Q4K_XF_SB_BYTES + Q4K_SX_SB_BYTES) + (size_t)warps * 16 * 4 + (size_t)warps * 4;
+// Scratch the Q4_K tensor-core decode needs for a shape (the prepared activation operand).
+size_t jl_gemv_scratch_bytes(uint32_t type, int k, int ntok) {
+    return type == JL_TYPE_Q4_K && k % 256 == 0 ? q4k_xprep_bytes(k / 256, ntok) : 0;
 }
 
 // ------------------------------------------------------------------ dispatch
@@ -362,15 +365,16 @@ int jl_gemv_choice(jl_ctx *ctx, uint32_t type, int nrows, int k, int ntok, jl_ch
     jl_choice c = {};
     int pin = ctx ? ctx->opts.pin_kernel : JL_K_AUTO;
     int warps = ctx && ctx->opts.pin_warps > 0 ? ctx->opts.pin_warps : 8;
-    if (warps != 4 && warps != 8 && warps != 16) warps = 8;
-    bool mma_ok = type == JL_TYPE_Q4_K && k % 256 == 0 && q4k_mma_smem(k / 256, warps) <= 200 * 1024;
+    if (warps != 2 && warps != 4 && warps != 8 && warps != 16 && warps != 104 && warps != 108) warps = 8;
+    // the activation operand of the whole row must fit one CTA's shared memory
+    bool mma_ok = type == JL_TYPE_Q4_K && k % 256 == 0 && q4k_tma_smem(8, 4, k / 256) <= 200 * 1024;
     if (pin == JL_K_SIMT || !mma_ok) {
         if (pin == JL_K_MMA || pin == JL_K_TC5) return JL_DECLINED;
         c.kernel = JL_K_SIMT; c.warps = 8; c.rows_per_cta = 8; c.split_k = 1;
         c.grid = (nrows + 7) / 8 * ntok;
     } else {
-        c.kernel = JL_K_MMA; c.warps = warps; c.rows_per_cta = 16;
-        c.split_k = warps < k / 256 ? warps : k / 256;
+        c.kernel = JL_K_MMA; c.warps = warps % 100; c.rows_per_cta = 16;
+        c.split_k = c.warps < k / 256 ? c.warps : k / 256;
         c.tile_m = 16; c.tile_n = 8; c.tile_k = 16;
         c.grid = (nrows + 15) / 16 * ntok;
     }
@@ -388,21 +392,51 @@ int jl_launch_gemv(jl_ctx *ctx, float *out_dev, const jl_weight *w, int expert, 
     else if (w->type == JL_TYPE_Q8_0) { data += rows_off * (size_t)k; scales += rows_off * (size_t)w->scale_stride * 2; }
     else { data += rows_off * (size_t)(k / 32) * 16; scales += rows_off * (size_t)w->scale_stride; }
 
+    if (kernel == JL_K_MMA && (!w->has_map_sb16 || (ctx->opts.flags & JL_FLAG_NO_TMA))) {
+        if (ctx->opts.pin_kernel == JL_K_MMA)
+            return jl_set_err(ctx, JL_DECLINED, "the tensor-core decode kernel needs the weight's tensor map");
+        kernel = JL_K_SIMT;
+    }
     if (kernel == JL_K_MMA && w->type == JL_TYPE_Q4_K) {
         int nsb = k / 256;
-        size_t smem = q4k_mma_smem(nsb, warps);
+        size_t need = q4k_xprep_bytes(nsb, ntok);
+        if (ctx->scratch_cap < need)
+            return jl_set_err(ctx, JL_ENOMEM, "decode scratch holds %zu bytes, %d x %d token(s) need %zu "
+                              "(jl_reserve sizes it)", ctx->scratch_cap, k, ntok, need);
+        uint8_t *scratch = (uint8_t *)ctx->scratch;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[0].val.programmaticStreamSerializationAllowed = 1;
+        const int nattr = (ctx->opts.flags & JL_FLAG_NO_PDL) ? 0 : 1;
+        {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3((nsb + 3) / 4, ntok); cfg.blockDim = dim3(128); cfg.stream = s;
+            cfg.attrs = at; cfg.numAttrs = nattr;
+            JL_CUDA(ctx, cudaLaunchKernelEx(&cfg, q4k_xprep_kernel, x_dev, scratch, nsb, ntok));
+            ctx->st.launches++;
+        }
         dim3 grid((nrows + 15) / 16, ntok);
-#define LAUNCH_Q4K(WP)                                                                                  \
+#define LAUNCH_Q4K_TMA(WP, ST, MB)                                                                      \
     do {                                                                                                \
+        size_t smem = q4k_tma_smem(WP, ST, nsb);                                                        \
         if (smem > 48 * 1024)                                                                           \
-            JL_CUDA(ctx, cudaFuncSetAttribute(gemv_q4k_mma_kernel<WP>,                                  \
+            JL_CUDA(ctx, cudaFuncSetAttribute(gemv_q4k_tma_kernel<WP, ST, MB>,                          \
                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-        gemv_q4k_mma_kernel<WP><<<grid, WP * 32, smem, s>>>(data, x_dev, out_dev, nrows, nsb, ntok);    \
+        cudaLaunchConfig_t cfg = {};                                                                    \
+        cfg.gridDim = grid; cfg.blockDim = dim3(WP * 32); cfg.dynamicSmemBytes = smem; cfg.stream = s;  \
+        cfg.attrs = at; cfg.numAttrs = nattr;                                                           \
+        JL_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemv_q4k_tma_kernel<WP, ST, MB>, w->map_sb16,             \
+                                        expert * nrows, (const uint8_t *)scratch, out_dev, nrows, nsb,  \
+                                        ntok, ctx->dev_status));                                        \
     } while (0)
-        if (warps == 4) LAUNCH_Q4K(4);
-        else if (warps == 16) LAUNCH_Q4K(16);
-        else LAUNCH_Q4K(8);
-#undef LAUNCH_Q4K
+        // (warps per CTA, ring stages per warp, CTAs per SM the registers are held to)
+        if (warps == 2) LAUNCH_Q4K_TMA(2, 8, 8);
+        else if (warps == 4) LAUNCH_Q4K_TMA(4, 4, 4);
+        else if (warps == 104) LAUNCH_Q4K_TMA(4, 4, 6);
+        else if (warps == 16) LAUNCH_Q4K_TMA(16, 1, 1);
+        else if (warps == 108) LAUNCH_Q4K_TMA(8, 4, 2);
+        else LAUNCH_Q4K_TMA(8, 2, 2);
+#undef LAUNCH_Q4K_TMA
     } else {
         dim3 grid((nrows + 7) / 8, ntok);
         if (w->type == JL_TYPE_Q4_K)

@@ -1,6 +1,7 @@
 // Internal declarations shared by the translation units of libjitllm_b200.so.
 #pragma once
 
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <cuda_fp16.h>
 #include <cuda_bf16.h>
@@ -60,6 +61,10 @@ struct jl_weight {
     size_t data_bytes, scales_bytes;
     int scale_stride;       // elements per row of the scales plane
     const void *host_key;   // host address it was uploaded from (cache identity) or NULL
+    // Q4_K: 2-D tensor map over the raw bytes, [n_expert * nrows][row_bytes] u8, box 144 B x 16
+    // rows = one super-block of 16 rows per TMA copy (decode kernel).
+    alignas(64) CUtensorMap map_sb16;
+    bool has_map_sb16;
 };
 
 struct jl_ctx {
@@ -80,6 +85,7 @@ struct jl_ctx {
     void *scratch; size_t scratch_cap;
     void *x_pin; size_t x_pin_cap;
     void *o_pin; size_t o_pin_cap;
+    int *dev_status;        // device word a kernel sets when a bounded wait ran out
     // fault injection
     std::vector<int> fail_at;
     int call_ordinal;
@@ -106,6 +112,8 @@ void jl_weight_release(jl_weight *w);
 int jl_launch_gemv(jl_ctx *ctx, float *out_dev, const jl_weight *w, int expert, const float *x_dev,
                    int ntok, int kernel, int warps, cudaStream_t s);
 int jl_gemv_choice(jl_ctx *ctx, uint32_t type, int nrows, int k, int ntok, jl_choice *out);
+size_t jl_gemv_scratch_bytes(uint32_t type, int k, int ntok);
+int jl_grow_scratch(jl_ctx *ctx, size_t need);
 
 // gemm_tc5.cu -- prefill kernels (tcgen05).
 int jl_launch_gemm_tc5(jl_ctx *ctx, void *out_dev, int out_dtype, const jl_weight *w, int expert,

@@ -87,11 +87,11 @@ class Device:
     """One B200, behind the reference's `nn.Device` surface."""
 
     def __init__(self, device: int = 0, pin_kernel: int = _lib.K_AUTO, pin_warps: int = 0,
-                 min_weight_bytes: int = 0, max_resident_bytes: int = 0):
+                 min_weight_bytes: int = 0, max_resident_bytes: int = 0, flags: int = 0):
         self.lib = _lib.load()
         self.ctx = C.c_void_p()
         o = Opts(struct_size=C.sizeof(Opts), pin_kernel=pin_kernel, pin_warps=pin_warps,
-                 min_weight_bytes=min_weight_bytes, max_resident_bytes=max_resident_bytes, flags=0)
+                 min_weight_bytes=min_weight_bytes, max_resident_bytes=max_resident_bytes, flags=flags)
         rc = self.lib.jl_open(device, C.byref(o), C.byref(self.ctx))
         if rc != _lib.OK:
             self.ctx = None
