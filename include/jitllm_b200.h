@@ -90,6 +90,10 @@ typedef struct jl_opts {
 #define JL_FLAG_NO_PDL 1u
 /* Stream decode weights with per-lane 128-bit loads instead of TMA tile copies. */
 #define JL_FLAG_NO_TMA 2u
+/* Pin the form of the tensor-core decode: activations converted inside the decode kernel
+ * (one launch, shortest dependency chain) or by a separate prep kernel (least work). */
+#define JL_FLAG_DECODE_FUSED 4u
+#define JL_FLAG_DECODE_SPLIT 8u
 
 typedef struct jl_ctx jl_ctx;
 typedef struct jl_weight jl_weight;

@@ -126,7 +126,11 @@ JL_EXPORT int jl_reserve(jl_ctx *ctx, int max_rows, int max_k, int max_tok) {
     if (!ctx || max_rows < 1 || max_k < 1 || max_tok < 1) return JL_EINVAL;
     std::lock_guard<std::mutex> lk(ctx->mu);
     JL_CUDA(ctx, cudaSetDevice(ctx->device));
-    int rc = jl_grow_scratch(ctx, jl_gemv_scratch_bytes(JL_TYPE_Q4_K, (max_k + 255) / 256 * 256, max_tok));
+    const int k256 = (max_k + 255) / 256 * 256;
+    size_t need = jl_gemv_scratch_bytes(JL_TYPE_Q4_K, k256, max_tok < 8 ? max_tok : 8);
+    const size_t need_gemm = jl_gemm_tc5_scratch_bytes(k256, max_tok, JL_DT_F32);
+    if (max_tok > 8 && need_gemm > need) need = need_gemm;
+    int rc = jl_grow_scratch(ctx, need);
     if (rc) return rc;
     return reserve_locked(ctx, (size_t)max_tok * max_k * 4, (size_t)max_tok * max_rows * 4);
 }
@@ -256,7 +260,7 @@ JL_EXPORT void jl_weight_free(jl_ctx *ctx, jl_weight *w) {
 
 static int choose(jl_ctx *ctx, uint32_t type, int nrows, int k, int ntok, jl_choice *out) {
     int pin = ctx->opts.pin_kernel;
-    if ((pin == JL_K_TC5 || (pin == JL_K_AUTO && ntok >= 16)) && jl_gemm_tc5_supported(type, nrows, k, ntok))
+    if ((pin == JL_K_TC5 || (pin == JL_K_AUTO && ntok > 8)) && jl_gemm_tc5_supported(type, nrows, k, ntok))
         return jl_gemm_tc5_choice(ctx, type, nrows, k, ntok, out);
     if (pin == JL_K_TC5) return JL_DECLINED;
     return jl_gemv_choice(ctx, type, nrows, k, ntok, out);
@@ -283,7 +287,7 @@ static int matmul_dev_locked(jl_ctx *ctx, void *out_dev, int out_dtype, const jl
         return jl_launch_gemm_tc5(ctx, out_dev, out_dtype, w, expert, x_dev, x_dtype, ntok, s);
     if (x_dtype != JL_DT_F32 || out_dtype != JL_DT_F32)
         return jl_set_err(ctx, JL_DECLINED, "the decode kernels take f32 activations and outputs");
-    int warps = ctx->opts.pin_warps > 0 ? ctx->opts.pin_warps : ch.warps;
+    int warps = ctx->opts.pin_warps > 0 ? ctx->opts.pin_warps : 0;
     return jl_launch_gemv(ctx, (float *)out_dev, w, expert, (const float *)x_dev, ntok, ch.kernel, warps, s);
 }
 
@@ -336,7 +340,12 @@ static int matmul_host(jl_ctx *ctx, void *out, int out_dtype, uint32_t type, con
     if ((rc = resident(ctx, type, w, w_bytes, 1, nrows, k, &dw))) return rc;
     size_t xb = (size_t)ntok * k * dtype_bytes(x_dtype), ob = (size_t)ntok * nrows * dtype_bytes(out_dtype);
     if ((rc = reserve_locked(ctx, xb, ob))) return rc;
-    if ((rc = jl_grow_scratch(ctx, jl_gemv_scratch_bytes(type, k, ntok)))) return rc;
+    {
+        size_t need = jl_gemv_scratch_bytes(type, k, ntok);
+        const size_t need_gemm = jl_gemm_tc5_scratch_bytes(k, ntok, x_dtype);
+        if (need_gemm > need) need = need_gemm;
+        if ((rc = jl_grow_scratch(ctx, need))) return rc;
+    }
     memcpy(ctx->x_pin, x, xb);
     JL_CUDA(ctx, cudaMemcpyAsync(ctx->x_dev, ctx->x_pin, xb, cudaMemcpyHostToDevice, ctx->stream));
     rc = matmul_dev_locked(ctx, ctx->o_dev, out_dtype, dw, 0, ctx->x_dev, x_dtype, ntok, ctx->stream);

@@ -164,19 +164,10 @@ static size_t q4k_xprep_bytes(int nsb, int ntok) {
     return (size_t)ntok * nsb * Q4K_XP_SB_BYTES + Q4K_XP_ZERO_BYTES;
 }
 
-// One warp per (super-block, token). Lane l and l+32 each take one code word's worth
-// (4 consecutive activations).
-__global__ void __launch_bounds__(128)
-q4k_xprep_kernel(const float *__restrict__ X, uint8_t *__restrict__ scratch, int nsb, int ntok) {
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");  // x comes from the previous kernel
-    const int lane = threadIdx.x & 31;
-    const int sb = blockIdx.x * 4 + (threadIdx.x >> 5), tok = blockIdx.y;
-    if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x < Q4K_XP_ZERO_BYTES / 4)
-        reinterpret_cast<uint32_t *>(scratch + (size_t)ntok * nsb * Q4K_XP_SB_BYTES)[threadIdx.x] = 0u;
-    if (sb >= nsb) return;
-    uint8_t *out = scratch + ((size_t)tok * nsb + sb) * Q4K_XP_SB_BYTES;
-    const float4 *x4 = reinterpret_cast<const float4 *>(X + ((size_t)tok * nsb + sb) * 256);
+// The activation operand of one super-block, by one warp: x4 points at its 64 float4,
+// out at its Q4K_XP_SB_BYTES (global scratch or shared memory). Lanes l and l+32 each take
+// one code word's worth (4 consecutive activations).
+__device__ __forceinline__ void q4k_prep_sb(const float4 *__restrict__ x4, uint8_t *out, int lane) {
     float4 v0 = __ldg(x4 + lane), v1 = __ldg(x4 + 32 + lane);
     float amax = fmaxf(fmaxf(fmaxf(fabsf(v0.x), fabsf(v0.y)), fmaxf(fabsf(v0.z), fabsf(v0.w))),
                        fmaxf(fmaxf(fabsf(v1.x), fabsf(v1.y)), fmaxf(fabsf(v1.z), fabsf(v1.w))));
@@ -217,10 +208,26 @@ q4k_xprep_kernel(const float *__restrict__ X, uint8_t *__restrict__ scratch, int
     }
 }
 
+// One warp per (super-block, token): the operand of a whole matvec, made once.
+__global__ void __launch_bounds__(128)
+q4k_xprep_kernel(const float *__restrict__ X, uint8_t *__restrict__ scratch, int nsb, int ntok) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // x comes from the previous kernel
+    const int sb = blockIdx.x * 4 + (threadIdx.x >> 5), tok = blockIdx.y;
+    if (sb >= nsb) return;
+    q4k_prep_sb(reinterpret_cast<const float4 *>(X + ((size_t)tok * nsb + sb) * 256),
+                scratch + ((size_t)tok * nsb + sb) * Q4K_XP_SB_BYTES, threadIdx.x & 31);
+}
+
 #define Q4K_TILE_BYTES (16 * 144)
-template <int WARPS, int STAGES, int MINB>
+// FUSED = the warp makes the operand of each super-block it consumes itself, in shared
+// memory, from X: no prep kernel in front and no kernel boundary in the dependency chain
+// (what a latency-bound shape wants), at the price of every 16-row CTA redoing the
+// conversion (what a throughput-bound shape does not want). `xsrc` is X when FUSED, the
+// prepared scratch otherwise.
+template <int WARPS, int STAGES, int MINB, bool FUSED>
 __global__ void __launch_bounds__(WARPS * 32, MINB)
-gemv_q4k_tma_kernel(const __grid_constant__ CUtensorMap wmap, int row0, const uint8_t *__restrict__ scratch,
+gemv_q4k_tma_kernel(const __grid_constant__ CUtensorMap wmap, int row0, const void *__restrict__ xsrc,
                     float *__restrict__ Y, int nrows, int nsb, int ntok, int *status) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -230,7 +237,7 @@ gemv_q4k_tma_kernel(const __grid_constant__ CUtensorMap wmap, int row0, const ui
     //                | red[WARPS][16] | barriers [WARPS][STAGES] + 1
     uint8_t *tiles = smem + (size_t)warp * STAGES * Q4K_TILE_BYTES;
     uint8_t *xop = smem + (size_t)WARPS * STAGES * Q4K_TILE_BYTES;
-    const uint32_t xop_bytes = (uint32_t)nsb * Q4K_XP_SB_BYTES;
+    const uint32_t xop_bytes = (uint32_t)(FUSED ? WARPS : nsb) * Q4K_XP_SB_BYTES;
     float *red = reinterpret_cast<float *>(xop + xop_bytes + Q4K_XP_ZERO_BYTES);
     uint64_t *bars_all = reinterpret_cast<uint64_t *>(red + WARPS * 16);
     uint64_t *bars = bars_all + warp * STAGES;
@@ -258,11 +265,15 @@ gemv_q4k_tma_kernel(const __grid_constant__ CUtensorMap wmap, int row0, const ui
     // waits for its predecessor (the activation prep) only before it copies the operand.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    if (tid == 0) {
-        mbar_arrive_expect_tx(smem_u32(xbar), xop_bytes);
-        bulk_load_1d(smem_u32(xop), scratch + (size_t)tok * xop_bytes, xop_bytes, smem_u32(xbar));
+    bool lost = false;
+    if (!FUSED) {
+        if (tid == 0) {
+            mbar_arrive_expect_tx(smem_u32(xbar), xop_bytes);
+            bulk_load_1d(smem_u32(xop), static_cast<const uint8_t *>(xsrc) + (size_t)tok * xop_bytes, xop_bytes,
+                         smem_u32(xbar));
+        }
+        lost = !__all_sync(0xffffffffu, mbar_wait(smem_u32(xbar), 0));
     }
-    bool lost = !__all_sync(0xffffffffu, mbar_wait(smem_u32(xbar), 0));
 
     const bool bsel = ((g >> 1) == t);  // lanes that feed a non-zero B column: digit (g & 1) of group t
     const uint8_t *zero = xop + xop_bytes;
@@ -272,7 +283,13 @@ gemv_q4k_tma_kernel(const __grid_constant__ CUtensorMap wmap, int row0, const ui
     for (int it = 0, sb = warp; sb < nsb && !lost; it++, sb += WARPS) {
         const int s = it % STAGES;
         const uint32_t parity = (uint32_t)(it / STAGES) & 1u;
-        const uint8_t *xsb = xop + (size_t)sb * Q4K_XP_SB_BYTES;
+        uint8_t *xsb = xop + (size_t)(FUSED ? warp : sb) * Q4K_XP_SB_BYTES;
+        if (FUSED) {
+            __syncwarp();  // the previous super-block's operand has been consumed
+            q4k_prep_sb(reinterpret_cast<const float4 *>(static_cast<const float *>(xsrc) +
+                                                          ((size_t)tok * nsb + sb) * 256), xsb, lane);
+            __syncwarp();
+        }
         const uint8_t *xf = bsel ? xsb + t * Q4K_XP_GROUP_BYTES + (g & 1) * 8 : zero;
         const int4 ax = *reinterpret_cast<const int4 *>(xsb + Q4K_XP_AUX_OFS + t * 16);
         if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(bars + s), parity))) { lost = true; break; }
@@ -345,8 +362,8 @@ gemv_q4k_tma_kernel(const __grid_constant__ CUtensorMap wmap, int row0, const ui
         if (row < nrows) Y[(size_t)tok * nrows + row] = sum;
     }
 }
-static size_t q4k_tma_smem(int warps, int stages, int nsb) {
-    return (size_t)warps * stages * Q4K_TILE_BYTES + (size_t)nsb * Q4K_XP_SB_BYTES + Q4K_XP_ZERO_BYTES +
+static size_t q4k_tma_smem(int warps, int stages, int nsb, bool fused = false) {
+    return (size_t)warps * stages * Q4K_TILE_BYTES + (size_t)(fused ? warps : nsb) * Q4K_XP_SB_BYTES + Q4K_XP_ZERO_BYTES +
            (size_t)warps * 16 * 4 + (size_t)(warps * stages + 1) * 8;
 }
 
@@ -364,8 +381,8 @@ size_t jl_gemv_scratch_bytes(uint32_t type, int k, int ntok) {
 int jl_gemv_choice(jl_ctx *ctx, uint32_t type, int nrows, int k, int ntok, jl_choice *out) {
     jl_choice c = {};
     int pin = ctx ? ctx->opts.pin_kernel : JL_K_AUTO;
-    int warps = ctx && ctx->opts.pin_warps > 0 ? ctx->opts.pin_warps : 8;
-    if (warps != 2 && warps != 4 && warps != 8 && warps != 16 && warps != 104 && warps != 108) warps = 8;
+    int warps = ctx && ctx->opts.pin_warps > 0 ? ctx->opts.pin_warps : 0;
+    if (warps != 2 && warps != 4 && warps != 8 && warps != 16 && warps != 108 && warps != 116) warps = 0;
     // the activation operand of the whole row must fit one CTA's shared memory
     bool mma_ok = type == JL_TYPE_Q4_K && k % 256 == 0 && q4k_tma_smem(8, 4, k / 256) <= 200 * 1024;
     if (pin == JL_K_SIMT || !mma_ok) {
@@ -373,6 +390,9 @@ int jl_gemv_choice(jl_ctx *ctx, uint32_t type, int nrows, int k, int ntok, jl_ch
         c.kernel = JL_K_SIMT; c.warps = 8; c.rows_per_cta = 8; c.split_k = 1;
         c.grid = (nrows + 7) / 8 * ntok;
     } else {
+        const long tasks = (long)((nrows + 15) / 16) * (k / 256) * ntok;
+        const bool fused = ctx && tasks <= 2L * ctx->sm_count * 32;
+        if (!warps) warps = fused ? 8 : 4;
         c.kernel = JL_K_MMA; c.warps = warps % 100; c.rows_per_cta = 16;
         c.split_k = c.warps < k / 256 ? c.warps : k / 256;
         c.tile_m = 16; c.tile_n = 8; c.tile_k = 16;
@@ -408,34 +428,45 @@ int jl_launch_gemv(jl_ctx *ctx, float *out_dev, const jl_weight *w, int expert, 
         at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         at[0].val.programmaticStreamSerializationAllowed = 1;
         const int nattr = (ctx->opts.flags & JL_FLAG_NO_PDL) ? 0 : 1;
-        {
+        // Latency-bound shapes (about one wave of warp-tasks or less) take the fused form.
+        const long tasks = (long)((nrows + 15) / 16) * nsb * ntok;
+        bool fused = tasks <= 2L * ctx->sm_count * 32;
+        if (ctx->opts.flags & JL_FLAG_DECODE_FUSED) fused = true;
+        if (ctx->opts.flags & JL_FLAG_DECODE_SPLIT) fused = false;
+        if (!fused) {
             cudaLaunchConfig_t cfg = {};
             cfg.gridDim = dim3((nsb + 3) / 4, ntok); cfg.blockDim = dim3(128); cfg.stream = s;
             cfg.attrs = at; cfg.numAttrs = nattr;
             JL_CUDA(ctx, cudaLaunchKernelEx(&cfg, q4k_xprep_kernel, x_dev, scratch, nsb, ntok));
             ctx->st.launches++;
         }
+        const void *xsrc = fused ? (const void *)x_dev : (const void *)scratch;
         dim3 grid((nrows + 15) / 16, ntok);
-#define LAUNCH_Q4K_TMA(WP, ST, MB)                                                                      \
+#define LAUNCH_Q4K_TMA(WP, ST, MB, FU)                                                                  \
     do {                                                                                                \
-        size_t smem = q4k_tma_smem(WP, ST, nsb);                                                        \
+        size_t smem = q4k_tma_smem(WP, ST, nsb, FU);                                                    \
         if (smem > 48 * 1024)                                                                           \
-            JL_CUDA(ctx, cudaFuncSetAttribute(gemv_q4k_tma_kernel<WP, ST, MB>,                          \
+            JL_CUDA(ctx, cudaFuncSetAttribute(gemv_q4k_tma_kernel<WP, ST, MB, FU>,                      \
                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
         cudaLaunchConfig_t cfg = {};                                                                    \
         cfg.gridDim = grid; cfg.blockDim = dim3(WP * 32); cfg.dynamicSmemBytes = smem; cfg.stream = s;  \
         cfg.attrs = at; cfg.numAttrs = nattr;                                                           \
-        JL_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemv_q4k_tma_kernel<WP, ST, MB>, w->map_sb16,             \
-                                        expert * nrows, (const uint8_t *)scratch, out_dev, nrows, nsb,  \
-                                        ntok, ctx->dev_status));                                        \
+        JL_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemv_q4k_tma_kernel<WP, ST, MB, FU>, w->map_sb16,         \
+                                        expert * nrows, xsrc, out_dev, nrows, nsb, ntok,                \
+                                        ctx->dev_status));                                              \
     } while (0)
-        // (warps per CTA, ring stages per warp, CTAs per SM the registers are held to)
-        if (warps == 2) LAUNCH_Q4K_TMA(2, 8, 8);
-        else if (warps == 4) LAUNCH_Q4K_TMA(4, 4, 4);
-        else if (warps == 104) LAUNCH_Q4K_TMA(4, 4, 6);
-        else if (warps == 16) LAUNCH_Q4K_TMA(16, 1, 1);
-        else if (warps == 108) LAUNCH_Q4K_TMA(8, 4, 2);
-        else LAUNCH_Q4K_TMA(8, 2, 2);
+        // (warps per CTA, ring stages per warp, CTAs per SM the registers are held to, fused)
+        if (fused) {
+            if (warps == 4) LAUNCH_Q4K_TMA(4, 4, 4, true);
+            else if (warps == 16) LAUNCH_Q4K_TMA(16, 1, 1, true);
+            else if (warps == 116) LAUNCH_Q4K_TMA(16, 2, 1, true);
+            else LAUNCH_Q4K_TMA(8, 2, 2, true);
+        } else {
+            if (warps == 2) LAUNCH_Q4K_TMA(2, 8, 8, false);
+            else if (warps == 8) LAUNCH_Q4K_TMA(8, 2, 2, false);
+            else if (warps == 108) LAUNCH_Q4K_TMA(8, 4, 2, false);
+            else LAUNCH_Q4K_TMA(4, 4, 4, false);
+        }
 #undef LAUNCH_Q4K_TMA
     } else {
         dim3 grid((nrows + 7) / 8, ntok);

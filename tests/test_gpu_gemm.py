@@ -1,0 +1,107 @@
+"""Prefill GEMM (tcgen05) parity on a B200, through the C ABI, against the CPU oracle.
+
+Bar (f32 accumulator): max_i |got-ref| / max(|ref_i|, rms(ref)) <= 2e-3; the reference's own
+bar for its f16 tensor-core GEMM is NMSE <= 1e-5 (jit/gpu/backend/mmavolta_test.go:278)."""
+import numpy as np
+import pytest
+
+from conftest import nmse, parity_err
+from jitllm_b200 import DT_BF16, DT_F32, K_TC5, Q4_K, Device, synth
+
+pytestmark = pytest.mark.gpu
+BAR = 2e-3
+
+
+def _bf16_inputs(rng, ntok, k):
+    bits = synth.to_bf16_bits(synth.activations(rng, ntok, k))
+    return bits, synth.bf16_bits_to_f32(bits)  # the bf16 values, exactly, as f32
+
+
+def _run(dev, orc, nrows, k, ntok, seed, x_dtype=DT_BF16, out_dtype=DT_F32, rows=None):
+    rng = synth.rng_for(seed)
+    w = synth.q4k_matrix(rng, nrows, k)
+    if x_dtype == DT_BF16:
+        xin, xval = _bf16_inputs(rng, ntok, k)
+    else:
+        xval = synth.activations(rng, ntok, k)
+        xin = xval
+    out = np.full((ntok, nrows), np.nan, np.float32) if out_dtype == DT_F32 else np.full((ntok, nrows), 0x7FC0, np.uint16)
+    assert dev.MatMulRaw(out, out_dtype, Q4_K, w, xin, x_dtype, nrows, k, ntok), dev.Err()
+    if rows is None:
+        ref = orc.matmul_f64_blas(Q4_K, w, xval, nrows, k, ntok)
+        got = out
+    else:
+        rb = k // 256 * 144
+        ref = np.concatenate([orc.matmul_f64_blas(Q4_K, w[a:b].reshape(-1), xval, b - a, k, ntok) for a, b in rows], axis=1)
+        got = np.concatenate([out[:, a:b] for a, b in rows], axis=1)
+    dev.Forget(w)
+    return got, ref
+
+
+@pytest.mark.parametrize("nrows,k,ntok", [(128, 256, 16), (128, 512, 64), (200, 512, 40), (512, 1024, 512),
+                                           (256, 2048, 130), (1024, 4096, 300)])
+def test_q4k_bf16_gemm_matches_oracle(orc, nrows, k, ntok):
+    with Device(0, pin_kernel=K_TC5) as d:
+        ch = d.Select(Q4_K, nrows, k, ntok)
+        assert ch is not None and ch.kernel == K_TC5 and ch.tile_m == 128
+        got, ref = _run(d, orc, nrows, k, ntok, 0xB201 + nrows + k + ntok)
+        assert np.isfinite(got).all()
+        assert parity_err(got, ref) <= BAR, (parity_err(got, ref), nmse(got, ref))
+        assert nmse(got, ref) <= 1e-6
+
+
+def test_f32_activations_take_the_hi_lo_split(orc):
+    # config 2's activations are f32: two f16 rows per token keep ~22 bits of each activation,
+    # so the only rounding left is the weights' single f16 rounding.
+    with Device(0, pin_kernel=K_TC5) as d:
+        got, ref = _run(d, orc, 256, 1024, 32, 11, x_dtype=DT_F32)
+        assert parity_err(got, ref) <= BAR
+        got2, ref2 = _run(d, orc, 384, 512, 33, 12, x_dtype=DT_F32)
+        assert parity_err(got2, ref2) <= BAR
+
+
+def test_bf16_output_is_the_rounded_accumulator(orc):
+    rng = synth.rng_for(5)
+    nrows, k, ntok = 256, 1024, 48
+    w = synth.q4k_matrix(rng, nrows, k)
+    xin, xval = _bf16_inputs(rng, ntok, k)
+    with Device(0, pin_kernel=K_TC5) as d:
+        f32 = np.empty((ntok, nrows), np.float32)
+        b16 = np.empty((ntok, nrows), np.uint16)
+        assert d.MatMulRaw(f32, DT_F32, Q4_K, w, xin, DT_BF16, nrows, k, ntok), d.Err()
+        assert d.MatMulRaw(b16, DT_BF16, Q4_K, w, xin, DT_BF16, nrows, k, ntok), d.Err()
+    assert np.array_equal(b16, synth.to_bf16_bits(f32)), "bf16 store must be RN_bf16(accumulator)"
+    ref = orc.matmul_f64_blas(Q4_K, w, xval, nrows, k, ntok)
+    refb = synth.to_bf16_bits(ref.astype(np.float32)).astype(np.int32)
+    # within one bf16 ulp of bf16(ref) wherever |ref| >= rms(ref): there the 2e-3 parity bar is
+    # below half a bf16 ulp (2^-8 relative)
+    big = np.abs(ref) >= np.sqrt(np.mean(ref * ref))
+    assert np.max(np.abs(b16.astype(np.int32)[big] - refb[big])) <= 1
+
+
+def test_activation_ranges_do_not_overflow_f16(orc):
+    rng = synth.rng_for(6)
+    nrows, k, ntok = 128, 512, 20
+    w = synth.q4k_matrix(rng, nrows, k)
+    x = synth.activations(rng, ntok, k)
+    x[0] *= 1e6
+    x[1] *= 1e-7
+    x[2] = 0
+    out = np.full((ntok, nrows), np.nan, np.float32)
+    with Device(0, pin_kernel=K_TC5) as d:
+        assert d.MatMul(out, Q4_K, w, x, nrows, k, ntok), d.Err()
+    ref = orc.matmul_f64_blas(Q4_K, w, x, nrows, k, ntok)
+    for t in range(ntok):
+        assert parity_err(out[t], ref[t]) <= BAR, t
+    assert not out[2].any()
+
+
+@pytest.mark.parametrize("nrows,k", [(14336, 4096), (4096, 14336)])
+def test_config1_full_size_sampled_rows(orc, nrows, k):
+    """BASELINE config 1 at full size (512 tokens, bf16 in): three 128-row bands against the f64 oracle."""
+    with Device(0) as d:
+        bands = [(0, 128), (nrows // 2 - 64, nrows // 2 + 64), (nrows - 128, nrows)]
+        got, ref = _run(d, orc, nrows, k, 512, 0xB201, rows=bands)
+        assert np.isfinite(got).all()
+        assert parity_err(got, ref) <= BAR, (parity_err(got, ref), nmse(got, ref))
+        assert nmse(got, ref) <= 1e-6
