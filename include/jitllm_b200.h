@@ -189,7 +189,8 @@ int jl_unpack_resident(jl_ctx *ctx, const jl_weight *w, int8_t *q, uint16_t *d_b
 /* ---- device-pointer twins: no host round trip ----------------------------
  * What tier.resident() does inside the reference (jit/gpu/tier/tier.go:2831-2903):
  * the weight lives on the device, activations and outputs are device pointers,
- * the launch goes on `stream` (a cudaStream_t; NULL = the context's own). */
+ * the launch goes on `stream` (a cudaStream_t; NULL is CUDA's default stream, as everywhere in
+ * CUDA). Launches are asynchronous: the caller orders them with its own stream operations. */
 int jl_weight_upload(jl_ctx *ctx, uint32_t type, const void *w_host, size_t w_bytes, int nrows,
                      int k, jl_weight **out);
 /* As jl_weight_upload for a bank of n_expert equal matrices. */

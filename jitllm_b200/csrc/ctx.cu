@@ -299,7 +299,7 @@ JL_EXPORT int jl_matvec_dev(jl_ctx *ctx, float *out_dev, const jl_weight *w, con
     if (rc) return rc;
     JL_CUDA(ctx, cudaSetDevice(ctx->device));
     rc = matmul_dev_locked(ctx, out_dev, JL_DT_F32, w, 0, x_dev, JL_DT_F32, ntok,
-                           stream ? (cudaStream_t)stream : ctx->stream);
+                           (cudaStream_t)stream);
     if (rc == JL_OK) ctx->st.served++;
     return rc;
 }
@@ -312,7 +312,7 @@ JL_EXPORT int jl_matmul_dev(jl_ctx *ctx, void *out_dev, int out_dtype, const jl_
     if (rc) return rc;
     JL_CUDA(ctx, cudaSetDevice(ctx->device));
     rc = matmul_dev_locked(ctx, out_dev, out_dtype, w, 0, x_dev, x_dtype, ntok,
-                           stream ? (cudaStream_t)stream : ctx->stream);
+                           (cudaStream_t)stream);
     if (rc == JL_OK) ctx->st.served++;
     return rc;
 }

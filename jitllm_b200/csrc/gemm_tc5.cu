@@ -9,7 +9,7 @@
 //   warp 4        TMA producer. Raw Q4_K tiles (128 rows x one 144-byte super-block, a 2-D
 //                 tensor map over the untouched ggml bytes) and activation tiles (NT tokens x
 //                 64 k, 128-byte swizzle) land in shared memory, completion on mbarriers.
-//   warps 6..9    dequant. Thread r owns row r of the tile: reads its 144 bytes, forms
+//   warps 6..13   dequant. Two threads per tile row (low-nibble / high-nibble sub-block): read the row's bytes, form
 //                 w = (d sc) q - dmin m in f32 (one FFMA per weight on a nibble placed in a
 //                 float's mantissa), rounds to f16 and stores the row's 128-byte k-block in
 //                 the K-major SWIZZLE_128B layout tcgen05.mma reads.
@@ -35,7 +35,8 @@
 #define TC5_KB 64           // k per shared-memory stage (128 bytes of f16: one swizzle atom)
 #define TC5_RAW_BYTES (TC5_M * 144)
 #define TC5_A_BYTES (TC5_M * TC5_KB * 2)
-#define TC5_THREADS 320     // 10 warps: 4 epilogue, producer, MMA, 4 dequant
+#define TC5_THREADS 448     // 14 warps: 4 epilogue, producer, MMA, 8 dequant
+#define TC5_DQ_THREADS 256  // two threads per tile row: low-nibble half, high-nibble half
 
 // ------------------------------------------------------------- activations
 
@@ -142,16 +143,29 @@ __device__ __forceinline__ bool tc5_wait(uint32_t bar, uint32_t parity, volatile
     return false;
 }
 
+// The same, for a role that is not on the critical path: backs off between polls so that it
+// does not take issue slots from the dequant warps it shares a scheduler with.
+__device__ __forceinline__ bool tc5_wait_relaxed(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+    for (uint32_t i = 0; i < (JL_SPIN_LIMIT >> 4); i++) {
+        if (mbar_try_wait(bar, parity)) return true;
+        __nanosleep(256);
+        if ((i & 63u) == 63u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    return false;
+}
+
 // ------------------------------------------------------------------- kernel
 
 struct tc5_params {
-    int nrows, k, ntok_eff;      // ntok_eff = MMA columns (2 x tokens when split)
+    int nrows, k, ntok, ntok_eff; // ntok_eff = MMA columns (2 x tokens when split)
     int split;                   // activations are hi/lo row pairs
     int row_tiles, tok_tiles;
     int out_dtype;
     void *out;                   // [ntok][nrows]
     const float *inv_scale;      // [ntok]
     int *status;
+    int debug;                   // timing experiments: 1 = skip the dequant math, 2 = skip the MMAs
 };
 
 template <int NT, int STAGES>
@@ -187,15 +201,15 @@ gemm_q4k_tc5_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
 
     if (tid == 0) {
         for (int s = 0; s < STAGES; s++) {
-            mbar_init(smem_u32(a_full + s), 128);
+            mbar_init(smem_u32(a_full + s), TC5_DQ_THREADS / 32);   // one arrival per dequant warp
             mbar_init(smem_u32(b_full + s), 1);
             mbar_init(smem_u32(empty + s), 1);
         }
         for (int i = 0; i < 2; i++) {
             mbar_init(smem_u32(raw_full + i), 1);
-            mbar_init(smem_u32(raw_empty + i), 128);
+            mbar_init(smem_u32(raw_empty + i), TC5_DQ_THREADS / 32);
             mbar_init(smem_u32(acc_full + i), 1);
-            mbar_init(smem_u32(acc_empty + i), 128);
+            mbar_init(smem_u32(acc_empty + i), 4);                      // one arrival per epilogue warp
         }
         *abort_flag = 0;
         mbar_init_fence();
@@ -252,7 +266,7 @@ gemm_q4k_tc5_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
                     const uint64_t bdesc = tc5_smem_desc(sbase + L::B_OFS + s * L::B_BYTES);
 #pragma unroll
                     for (int j = 0; j < TC5_KB / 16; j++)  // 32 bytes of K per instruction: +2 in 16-byte units
-                        tc5_mma_f16(d_tmem, adesc + 2 * j, bdesc + 2 * j, idesc, (kb | j) != 0);
+                        if (!(p.debug & 2)) tc5_mma_f16(d_tmem, adesc + 2 * j, bdesc + 2 * j, idesc, (kb | j) != 0);
                     tc5_commit(smem_u32(empty + s));      // stage reusable once these MMAs have read it
                 }
                 if (!ok) break;
@@ -260,8 +274,9 @@ gemm_q4k_tc5_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
             }
         }
     } else if (warp >= 6) {
-        // ------------------------------------------------ dequant: thread r owns tile row r
-        const int r = tid - 192;
+        // ------------------------------------------------ dequant: threads r and 128 + r own tile row r
+        const int r = (tid - 192) & 127;
+        const int nib = (tid - 192) >> 7;   // 0: low nibbles = sub-block 2j, 1: high nibbles = 2j+1
         const uint32_t swz = (uint32_t)(r & 7);
         uint32_t kb_it = 0, raw_it = 0;
         bool ok = true;
@@ -294,30 +309,20 @@ gemm_q4k_tc5_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
                     if (!ok) break;
                     uint8_t *arow = smem + L::A_OFS + s * TC5_A_BYTES + r * 128;
                     const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+                    const float ds = nib ? ds_o : ds_e, cc = nib ? c_o : c_e;
 #pragma unroll
-                    for (int c = 0; c < 8; c++) {        // 16-byte chunk c = k 8c..8c+7 of the k-block
-                        const uint32_t wa = w[(2 * c) & 7], wb = w[(2 * c + 1) & 7];
-                        const float ds = c < 4 ? ds_e : ds_o, cc = c < 4 ? c_e : c_o;
-                        float f[8];
-                        if (c < 4) {  // low nibbles of bytes 0..3 -> mantissa bits 19..22
-                            f[0] = __uint_as_float(((wa << 19) & 0x00780000u) | 0x3F800000u);
-                            f[1] = __uint_as_float(((wa << 11) & 0x00780000u) | 0x3F800000u);
-                            f[2] = __uint_as_float(((wa << 3) & 0x00780000u) | 0x3F800000u);
-                            f[3] = __uint_as_float(((wa >> 5) & 0x00780000u) | 0x3F800000u);
-                            f[4] = __uint_as_float(((wb << 19) & 0x00780000u) | 0x3F800000u);
-                            f[5] = __uint_as_float(((wb << 11) & 0x00780000u) | 0x3F800000u);
-                            f[6] = __uint_as_float(((wb << 3) & 0x00780000u) | 0x3F800000u);
-                            f[7] = __uint_as_float(((wb >> 5) & 0x00780000u) | 0x3F800000u);
-                        } else {      // high nibbles
-                            f[0] = __uint_as_float(((wa << 15) & 0x00780000u) | 0x3F800000u);
-                            f[1] = __uint_as_float(((wa << 7) & 0x00780000u) | 0x3F800000u);
-                            f[2] = __uint_as_float(((wa >> 1) & 0x00780000u) | 0x3F800000u);
-                            f[3] = __uint_as_float(((wa >> 9) & 0x00780000u) | 0x3F800000u);
-                            f[4] = __uint_as_float(((wb << 15) & 0x00780000u) | 0x3F800000u);
-                            f[5] = __uint_as_float(((wb << 7) & 0x00780000u) | 0x3F800000u);
-                            f[6] = __uint_as_float(((wb >> 1) & 0x00780000u) | 0x3F800000u);
-                            f[7] = __uint_as_float(((wb >> 9) & 0x00780000u) | 0x3F800000u);
-                        }
+                    for (int cq = 0; cq < ((p.debug & 1) ? 0 : 4); cq++) {     // 16-byte chunk c = 4 nib + cq: k 8c..8c+7 of the k-block
+                        uint32_t wa = w[2 * cq], wb = w[2 * cq + 1];
+                        if (nib) { wa >>= 4; wb >>= 4; }
+                        float f[8];                      // nibbles of bytes 0..3 -> mantissa bits 19..22
+                        f[0] = __uint_as_float(((wa << 19) & 0x00780000u) | 0x3F800000u);
+                        f[1] = __uint_as_float(((wa << 11) & 0x00780000u) | 0x3F800000u);
+                        f[2] = __uint_as_float(((wa << 3) & 0x00780000u) | 0x3F800000u);
+                        f[3] = __uint_as_float(((wa >> 5) & 0x00780000u) | 0x3F800000u);
+                        f[4] = __uint_as_float(((wb << 19) & 0x00780000u) | 0x3F800000u);
+                        f[5] = __uint_as_float(((wb << 11) & 0x00780000u) | 0x3F800000u);
+                        f[6] = __uint_as_float(((wb << 3) & 0x00780000u) | 0x3F800000u);
+                        f[7] = __uint_as_float(((wb >> 5) & 0x00780000u) | 0x3F800000u);
                         uint4 o;
                         __half2 h0 = __floats2half2_rn(fmaf(f[0], ds, cc), fmaf(f[1], ds, cc));
                         __half2 h1 = __floats2half2_rn(fmaf(f[2], ds, cc), fmaf(f[3], ds, cc));
@@ -325,13 +330,15 @@ gemm_q4k_tc5_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
                         __half2 h3 = __floats2half2_rn(fmaf(f[6], ds, cc), fmaf(f[7], ds, cc));
                         o.x = *reinterpret_cast<uint32_t *>(&h0); o.y = *reinterpret_cast<uint32_t *>(&h1);
                         o.z = *reinterpret_cast<uint32_t *>(&h2); o.w = *reinterpret_cast<uint32_t *>(&h3);
-                        *reinterpret_cast<uint4 *>(arow + (((uint32_t)c ^ swz) << 4)) = o;
+                        *reinterpret_cast<uint4 *>(arow + (((uint32_t)(4 * nib + cq) ^ swz) << 4)) = o;
                     }
                     fence_async_smem();                   // generic writes -> visible to tcgen05.mma
-                    mbar_arrive(smem_u32(a_full + s));
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(a_full + s));
                 }
                 if (!ok) break;
-                mbar_arrive(smem_u32(raw_empty + rs));
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(raw_empty + rs));
             }
         }
     } else {
@@ -340,7 +347,7 @@ gemm_q4k_tc5_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
         for (int tile = blockIdx.x; tile < ntiles && !*abort_flag; tile += gridDim.x, tile_it++) {
             const int rt = tile / p.tok_tiles, tt = tile % p.tok_tiles;
             const uint32_t ab = tile_it & 1, aph = (tile_it >> 1) & 1;
-            if (!tc5_wait(smem_u32(acc_full + ab), aph, abort_flag)) break;
+            if (!tc5_wait_relaxed(smem_u32(acc_full + ab), aph, abort_flag)) break;
             tc5_fence_after();
             const int row = rt * TC5_M + warp * 32 + lane;
             const uint32_t taddr = tmem_base + ab * NT + ((uint32_t)(warp * 32) << 16);
@@ -350,36 +357,40 @@ gemm_q4k_tc5_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
                 tc5_ld32(taddr + c0, v);
                 tc5_wait_ld();
                 const int col0 = tt * NT + c0;
-                if (row < p.nrows) {
-                    if (p.split) {
+                // the per-token scales of these 32 columns: one load per lane, broadcast by shuffle
+                const int mytok = p.split ? (col0 >> 1) + (lane & 15) : col0 + lane;
+                const float myscale = mytok < p.ntok ? __ldg(p.inv_scale + mytok) : 0.f;
+                if (p.split) {
 #pragma unroll
-                        for (int j = 0; j < 16; j++) {
-                            const int tok = (col0 >> 1) + j;
-                            if (2 * tok + 1 < p.ntok_eff) {
-                                const float acc = (__uint_as_float(v[2 * j]) + __uint_as_float(v[2 * j + 1])) * p.inv_scale[tok];
-                                const size_t o = (size_t)tok * p.nrows + row;
-                                if (p.out_dtype == JL_DT_F32) static_cast<float *>(p.out)[o] = acc;
-                                else if (p.out_dtype == JL_DT_BF16) static_cast<__nv_bfloat16 *>(p.out)[o] = __float2bfloat16_rn(acc);
-                                else static_cast<__half *>(p.out)[o] = __float2half_rn(acc);
-                            }
+                    for (int j = 0; j < 16; j++) {
+                        const int tok = (col0 >> 1) + j;
+                        const float sc = __shfl_sync(0xffffffffu, myscale, j);
+                        if (row < p.nrows && tok < p.ntok) {
+                            const float acc = (__uint_as_float(v[2 * j]) + __uint_as_float(v[2 * j + 1])) * sc;
+                            const size_t o = (size_t)tok * p.nrows + row;
+                            if (p.out_dtype == JL_DT_F32) static_cast<float *>(p.out)[o] = acc;
+                            else if (p.out_dtype == JL_DT_BF16) static_cast<__nv_bfloat16 *>(p.out)[o] = __float2bfloat16_rn(acc);
+                            else static_cast<__half *>(p.out)[o] = __float2half_rn(acc);
                         }
-                    } else {
+                    }
+                } else {
 #pragma unroll
-                        for (int j = 0; j < 32; j++) {
-                            const int tok = col0 + j;
-                            if (tok < p.ntok_eff) {
-                                const float acc = __uint_as_float(v[j]) * p.inv_scale[tok];
-                                const size_t o = (size_t)tok * p.nrows + row;
-                                if (p.out_dtype == JL_DT_F32) static_cast<float *>(p.out)[o] = acc;
-                                else if (p.out_dtype == JL_DT_BF16) static_cast<__nv_bfloat16 *>(p.out)[o] = __float2bfloat16_rn(acc);
-                                else static_cast<__half *>(p.out)[o] = __float2half_rn(acc);
-                            }
+                    for (int j = 0; j < 32; j++) {
+                        const int tok = col0 + j;
+                        const float sc = __shfl_sync(0xffffffffu, myscale, j);
+                        if (row < p.nrows && tok < p.ntok) {
+                            const float acc = __uint_as_float(v[j]) * sc;
+                            const size_t o = (size_t)tok * p.nrows + row;
+                            if (p.out_dtype == JL_DT_F32) static_cast<float *>(p.out)[o] = acc;
+                            else if (p.out_dtype == JL_DT_BF16) static_cast<__nv_bfloat16 *>(p.out)[o] = __float2bfloat16_rn(acc);
+                            else static_cast<__half *>(p.out)[o] = __float2half_rn(acc);
                         }
                     }
                 }
             }
             tc5_fence_before();
-            mbar_arrive(smem_u32(acc_empty + ab));
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(acc_empty + ab));
         }
     }
 
@@ -471,9 +482,10 @@ int jl_launch_gemm_tc5(jl_ctx *ctx, void *out_dev, int out_dtype, const jl_weigh
         return jl_set_err(ctx, JL_DECLINED, "the driver refused a tensor map for this shape");
 
     tc5_params p;
-    p.nrows = nrows; p.k = k; p.ntok_eff = ntok_eff; p.split = split;
+    p.nrows = nrows; p.k = k; p.ntok = ntok; p.ntok_eff = ntok_eff; p.split = split;
     p.row_tiles = (nrows + TC5_M - 1) / TC5_M; p.tok_tiles = (ntok_eff + nt - 1) / nt;
     p.out_dtype = out_dtype; p.out = out_dev; p.inv_scale = inv_scale; p.status = ctx->dev_status;
+    p.debug = (int)((ctx->opts.flags >> 16) & 3);
     const int tiles = p.row_tiles * p.tok_tiles;
     const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
     int rc;
