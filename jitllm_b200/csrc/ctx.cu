@@ -128,7 +128,9 @@ JL_EXPORT int jl_reserve(jl_ctx *ctx, int max_rows, int max_k, int max_tok) {
     JL_CUDA(ctx, cudaSetDevice(ctx->device));
     const int k256 = (max_k + 255) / 256 * 256;
     size_t need = jl_gemv_scratch_bytes(JL_TYPE_Q4_K, k256, max_tok < 8 ? max_tok : 8);
-    const size_t need_gemm = jl_gemm_tc5_scratch_bytes(k256, max_tok, JL_DT_F32);
+    size_t need_gemm = jl_gemm_tc5_scratch_bytes(max_rows, k256, max_tok, JL_DT_F32, ctx->sm_count);
+    const size_t need_gemm16 = jl_gemm_tc5_scratch_bytes(max_rows, k256, max_tok, JL_DT_BF16, ctx->sm_count);
+    if (need_gemm16 > need_gemm) need_gemm = need_gemm16;
     if (max_tok > 8 && need_gemm > need) need = need_gemm;
     int rc = jl_grow_scratch(ctx, need);
     if (rc) return rc;
@@ -342,7 +344,7 @@ static int matmul_host(jl_ctx *ctx, void *out, int out_dtype, uint32_t type, con
     if ((rc = reserve_locked(ctx, xb, ob))) return rc;
     {
         size_t need = jl_gemv_scratch_bytes(type, k, ntok);
-        const size_t need_gemm = jl_gemm_tc5_scratch_bytes(k, ntok, x_dtype);
+        const size_t need_gemm = jl_gemm_tc5_scratch_bytes(nrows, k, ntok, x_dtype, ctx->sm_count);
         if (need_gemm > need) need = need_gemm;
         if ((rc = jl_grow_scratch(ctx, need))) return rc;
     }

@@ -6,18 +6,19 @@
 // arithmetic contract -- weights rounded ONCE to f16 after an f32 dequant, activations
 // f16, f32 accumulate -- on Blackwell's own path:
 //
-//   warp 4        TMA producer. Raw Q4_K tiles (128 rows x one 144-byte super-block, a 2-D
-//                 tensor map over the untouched ggml bytes) and activation tiles (NT tokens x
-//                 64 k, 128-byte swizzle) land in shared memory, completion on mbarriers.
-//   warps 6..13   dequant. Two threads per tile row (low-nibble / high-nibble sub-block): read the row's bytes, form
-//                 w = (d sc) q - dmin m in f32 (one FFMA per weight on a nibble placed in a
-//                 float's mantissa), rounds to f16 and stores the row's 128-byte k-block in
+//   warp 4        TMA producer. Activation tiles (NT tokens x 64 k, 128-byte swizzle) land in a
+//                 deep shared-memory ring, completion on mbarriers.
+//   warps 6..13   dequant. Thread r owns row r of the 256-row tile: reads its raw ggml bytes
+//                 (128-bit loads, a super-block ahead of use) into registers, forms
+//                 w = (d sc) q - dmin m in f32 (a PRMT places the code in a float's mantissa, one
+//                 packed fma.rn.f32x2 per two weights), rounds to f16 and stores the row's 128-byte k-block in
 //                 the K-major SWIZZLE_128B layout tcgen05.mma reads.
 //   warp 5        MMA issuer. One elected lane issues tcgen05.mma.cta_group::1.kind::f16,
-//                 M = 128 rows, N = NT tokens, K = 16 per instruction, accumulators in
-//                 TMEM (two buffers of NT columns, so a tile's epilogue overlaps the next
-//                 tile's MMAs); tcgen05.commit releases shared-memory stages and publishes
-//                 finished accumulators.
+//                 M = 128 rows, N = NT tokens, K = 16 per instruction -- TWO per k step, one
+//                 for each 128-row half of the tile against the same activation tile, which
+//                 halves the activation bytes pulled through L2 per flop (the measured limit
+//                 of a 128-row tile). Accumulators live in TMEM (2 x NT columns per tile);
+//                 tcgen05.commit releases shared-memory stages and publishes accumulators.
 //   warps 0..3    epilogue. tcgen05.ld their 32-lane quarter of TMEM, undo the per-token
 //                 activation scale, convert and store out[tok][row].
 //
@@ -26,19 +27,46 @@
 // f32 input is split x = hi + lo into two f16 rows whose products the epilogue adds, which keeps
 // ~22 bits of the activation.
 //
+// When a shape has fewer tiles than SMs the K range is split across CTAs; each split writes an
+// f32 partial plane and tc5_reduce_kernel adds the planes in fixed order (bit-stable).
+//
 // Every wait on an mbarrier is bounded: when a limit runs out the kernel sets a status word,
 // raises a CTA-wide abort flag that every role polls, frees its TMEM and returns.
 #include "jl_internal.cuh"
 #include "tma.cuh"
 
-#define TC5_M 128           // weight rows per tile (the MMA's M)
+#define TC5_M 128           // rows of one MMA (tcgen05 cta_group::1 M)
+#define TC5_MS 2            // MMAs that share one activation tile: a CTA tile is 256 weight rows
+#define TC5_ROWS (TC5_M * TC5_MS)
 #define TC5_KB 64           // k per shared-memory stage (128 bytes of f16: one swizzle atom)
-#define TC5_RAW_BYTES (TC5_M * 144)
-#define TC5_A_BYTES (TC5_M * TC5_KB * 2)
+#define TC5_RAW_BYTES (TC5_ROWS * 144)
+#define TC5_A_BYTES (TC5_M * TC5_KB * 2)   // one 128-row operand
 #define TC5_THREADS 448     // 14 warps: 4 epilogue, producer, MMA, 8 dequant
-#define TC5_DQ_THREADS 256  // two threads per tile row: low-nibble half, high-nibble half
+#define TC5_DQ_THREADS 256  // one thread per tile row
 
 // ------------------------------------------------------------- activations
+
+// Eight consecutive activations of a token row as f32 (k is a multiple of 8).
+__device__ __forceinline__ void act_load8(const void *x, int x_dtype, size_t idx, float (&v)[8]) {
+    if (x_dtype == JL_DT_F32) {
+        const float4 a = __ldg(reinterpret_cast<const float4 *>(static_cast<const float *>(x) + idx));
+        const float4 b = __ldg(reinterpret_cast<const float4 *>(static_cast<const float *>(x) + idx) + 1);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    } else {
+        const uint4 u = __ldg(reinterpret_cast<const uint4 *>(static_cast<const uint16_t *>(x) + idx));
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            if (x_dtype == JL_DT_BF16) {
+                v[2 * i] = __uint_as_float(w[i] << 16);
+                v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+            } else {
+                const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[i]));
+                v[2 * i] = f.x; v[2 * i + 1] = f.y;
+            }
+        }
+    }
+}
 
 // One CTA per token row. dst rows: `split` ? (2 tok: hi, 2 tok + 1: lo) : tok.
 __global__ void __launch_bounds__(256)
@@ -48,13 +76,14 @@ act_to_f16_kernel(const void *__restrict__ x, int x_dtype, __half *__restrict__ 
     asm volatile("griddepcontrol.wait;" ::: "memory");
     __shared__ float wmax[8];
     const int tok = blockIdx.x, tid = threadIdx.x;
-    auto load = [&](int i) -> float {
-        if (x_dtype == JL_DT_F32) return static_cast<const float *>(x)[(size_t)tok * k + i];
-        if (x_dtype == JL_DT_BF16) return __bfloat162float(static_cast<const __nv_bfloat16 *>(x)[(size_t)tok * k + i]);
-        return __half2float(static_cast<const __half *>(x)[(size_t)tok * k + i]);
-    };
+    const size_t base = (size_t)tok * k;
     float amax = 0.f;
-    for (int i = tid; i < k; i += 256) amax = fmaxf(amax, fabsf(load(i)));
+    for (int c = tid; c < k / 8; c += 256) {
+        float v[8];
+        act_load8(x, x_dtype, base + (size_t)c * 8, v);
+#pragma unroll
+        for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(v[i]));
+    }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
     if ((tid & 31) == 0) wmax[tid >> 5] = amax;
@@ -70,11 +99,21 @@ act_to_f16_kernel(const void *__restrict__ x, int x_dtype, __half *__restrict__ 
     if (tid == 0) inv_scale[tok] = __uint_as_float((uint32_t)(127 - s) << 23);
     __half *hi = dst + (size_t)(split ? 2 * tok : tok) * k;
     __half *lo = hi + k;
-    for (int i = tid; i < k; i += 256) {
-        const float v = load(i) * scale;
-        const __half h = __float2half_rn(v);
-        hi[i] = h;
-        if (split) lo[i] = __float2half_rn(v - __half2float(h));
+    for (int c = tid; c < k / 8; c += 256) {
+        float v[8];
+        act_load8(x, x_dtype, base + (size_t)c * 8, v);
+        uint32_t h[4], l[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const float a = v[2 * i] * scale, b = v[2 * i + 1] * scale;
+            const __half2 hh = __floats2half2_rn(a, b);
+            const float2 back = __half22float2(hh);
+            const __half2 ll = __floats2half2_rn(a - back.x, b - back.y);
+            h[i] = *reinterpret_cast<const uint32_t *>(&hh);
+            l[i] = *reinterpret_cast<const uint32_t *>(&ll);
+        }
+        *reinterpret_cast<uint4 *>(hi + (size_t)c * 8) = make_uint4(h[0], h[1], h[2], h[3]);
+        if (split) *reinterpret_cast<uint4 *>(lo + (size_t)c * 8) = make_uint4(l[0], l[1], l[2], l[3]);
     }
 }
 
@@ -133,6 +172,28 @@ __host__ __device__ constexpr uint32_t tc5_idesc(int m, int n) {
     return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
+// Byte i of `codes` (0x80 | q) as the float 1 + q/128: 0x3F in byte 3, the code in byte 2.
+__device__ __forceinline__ float tc5_code_float(uint32_t codes, int i) {
+    return __uint_as_float(__byte_perm(codes, 0x3F000000u, 0x7054 | (i << 8)));
+}
+// Two f32 FMAs in one instruction (fma.rn.f32x2): d = a * b + c on both halves.
+__device__ __forceinline__ void tc5_fma2(float &d0, float &d1, float a0, float a1, float b, float c) {
+    asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\t"
+        "mov.b64 ra, {%2, %3};\n\t"
+        "mov.b64 rb, {%4, %4};\n\t"
+        "mov.b64 rc, {%5, %5};\n\t"
+        "fma.rn.f32x2 rd, ra, rb, rc;\n\t"
+        "mov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(d0), "=f"(d1)
+        : "f"(a0), "f"(a1), "f"(b), "f"(c));
+}
+
+__device__ __forceinline__ uint4 ldg_nc16(const void *p) {
+    uint4 v;
+    asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
 // Bounded wait that also gives up when another role of the CTA has aborted.
 __device__ __forceinline__ bool tc5_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
     for (uint32_t i = 0; i < JL_SPIN_LIMIT; i++) {
@@ -158,87 +219,143 @@ __device__ __forceinline__ bool tc5_wait_relaxed(uint32_t bar, uint32_t parity, 
 // ------------------------------------------------------------------- kernel
 
 struct tc5_params {
-    int nrows, k, ntok, ntok_eff; // ntok_eff = MMA columns (2 x tokens when split)
-    int split;                   // activations are hi/lo row pairs
-    int row_tiles, tok_tiles;
+    int nrows, k, ntok, ntok_eff; // ntok_eff = MMA columns (2 x tokens when the activations are hi/lo pairs)
+    int split;                    // activations are hi/lo row pairs
+    int row_tiles, tok_tiles, ksplit;
     int out_dtype;
-    void *out;                   // [ntok][nrows]
-    const float *inv_scale;      // [ntok]
+    void *out;                    // [ntok][nrows]
+    float *partial;               // ksplit > 1: [ksplit][ntok][nrows] f32
+    const float *inv_scale;       // [ntok]
+    const uint8_t *w;             // raw Q4_K rows of this weight (expert)
     int *status;
-    int debug;                   // timing experiments: 1 = skip the dequant math, 2 = skip the MMAs
+    int debug;                    // timing experiments: 1 = skip the dequant math, 2 = skip the MMAs
 };
 
-template <int NT, int STAGES>
+template <int NT, int SA, int SB>
 struct tc5_smem {
+    static constexpr int ACC_COLS = TC5_MS * NT;                       // TMEM columns of one tile
+    static constexpr int ACC_BUFS = ACC_COLS * 2 <= 512 ? 2 : 1;
     static constexpr int B_BYTES = NT * TC5_KB * 2;
-    static constexpr int A_OFS = 0;
-    static constexpr int B_OFS = STAGES * TC5_A_BYTES;
-    static constexpr int RAW_OFS = B_OFS + STAGES * B_BYTES;
-    static constexpr int BAR_OFS = RAW_OFS + 2 * TC5_RAW_BYTES;
-    // barriers: a_full[S] b_full[S] empty[S] raw_full[2] raw_empty[2] acc_full[2] acc_empty[2]
-    static constexpr int NBARS = 3 * STAGES + 8;
-    static constexpr int MISC_OFS = BAR_OFS + NBARS * 8;   // tmem address, abort flag
-    static constexpr int TOTAL = MISC_OFS + 16 + 1024;     // + slack to align the base to 1024
+    static constexpr int A_OFS = 0;                                    // [SA][MS] 128-row operands
+    static constexpr int B_OFS = SA * TC5_MS * TC5_A_BYTES;            // [SB] activation tiles
+    static constexpr int BAR_OFS = B_OFS + SB * B_BYTES;
+    // barriers: a_full[SA] a_empty[SA] b_full[SB] b_empty[SB] acc_full[2] acc_empty[2]
+    static constexpr int NBARS = 2 * SA + 2 * SB + 4;
+    static constexpr int MISC_OFS = BAR_OFS + NBARS * 8;               // tmem address, abort flag
+    static constexpr int TOTAL = MISC_OFS + 16 + 1024;                 // + slack to align the base to 1024
 };
 
-template <int NT, int STAGES>
+// Drains one finished tile from TMEM: lane quarter `q` (TMEM lanes 32q..32q+31 = tile rows), 32
+// columns (tokens) at a time; undoes the per-token scale, converts, stores out[tok][row].
+// part < 0: every 32-column job; part = 0,1,2: every third job (three warps share a quarter).
+template <int NT>
+__device__ __forceinline__ void tc5_epilogue(const tc5_params &p, int u, uint32_t tmem_acc, int q, int lane, int part) {
+    const int ks = u % p.ksplit, tt = (u / p.ksplit) % p.tok_tiles, rt = u / (p.ksplit * p.tok_tiles);
+    float *partial = p.ksplit > 1 ? p.partial + (size_t)ks * p.ntok * p.nrows : nullptr;
+    int job = 0;
+#pragma unroll 1
+    for (int ms = 0; ms < TC5_MS; ms++) {
+        const int row = rt * TC5_ROWS + ms * TC5_M + q * 32 + lane;
+        const uint32_t taddr = tmem_acc + ms * NT + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+        for (int c0 = 0; c0 < NT; c0 += 32, job++) {
+            if (part >= 0 && job % 3 != part) continue;
+            uint32_t v[32];
+            tc5_ld32(taddr + c0, v);
+            tc5_wait_ld();
+            const int col0 = tt * NT + c0;
+            // the per-token scales of these 32 columns: one load per lane, broadcast by shuffle
+            const int mytok = p.split ? (col0 >> 1) + (lane & 15) : col0 + lane;
+            const float myscale = mytok < p.ntok ? __ldg(p.inv_scale + mytok) : 0.f;
+            const int nj = p.split ? 16 : 32;
+#pragma unroll
+            for (int j = 0; j < 32; j++) {
+                if (j >= nj) break;
+                const int tok = p.split ? (col0 >> 1) + j : col0 + j;
+                const float sc = __shfl_sync(0xffffffffu, myscale, j);
+                const float raw = p.split ? __uint_as_float(v[(2 * j) & 31]) + __uint_as_float(v[(2 * j + 1) & 31])
+                                          : __uint_as_float(v[j]);
+                if (row < p.nrows && tok < p.ntok && !(p.debug & 8)) {
+                    const float acc = raw * sc;
+                    const size_t o = (size_t)tok * p.nrows + row;
+                    if (partial) partial[o] = acc;
+                    else if (p.out_dtype == JL_DT_F32) static_cast<float *>(p.out)[o] = acc;
+                    else if (p.out_dtype == JL_DT_BF16) static_cast<__nv_bfloat16 *>(p.out)[o] = __float2bfloat16_rn(acc);
+                    else static_cast<__half *>(p.out)[o] = __float2half_rn(acc);
+                }
+            }
+        }
+    }
+}
+
+// SA stages of dequantized weights, SB (deeper) stages of activations: an activation tile takes
+// ~2 us to arrive from L2, a weight stage is produced locally.
+template <int NT, int SA, int SB>
 __global__ void __launch_bounds__(TC5_THREADS, 1)
-gemm_q4k_tc5_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap,
-                    const tc5_params p) {
-    using L = tc5_smem<NT, STAGES>;
+gemm_q4k_tc5_kernel(const __grid_constant__ CUtensorMap xmap, const tc5_params p) {
+    using L = tc5_smem<NT, SA, SB>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const uint32_t sbase = smem_u32(smem);
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + L::BAR_OFS);
-    uint64_t *a_full = bars, *b_full = bars + STAGES, *empty = bars + 2 * STAGES;
-    uint64_t *raw_full = bars + 3 * STAGES, *raw_empty = raw_full + 2, *acc_full = raw_full + 4, *acc_empty = raw_full + 6;
+    uint64_t *a_full = bars, *a_empty = bars + SA, *b_full = bars + 2 * SA, *b_empty = b_full + SB;
+    uint64_t *acc_full = b_empty + SB, *acc_empty = acc_full + 2;
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + L::MISC_OFS);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L::MISC_OFS + 4);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nsb = p.k / 256;               // super-blocks per row
-    const int ntiles = p.row_tiles * p.tok_tiles;
+    const int nunits = p.row_tiles * p.tok_tiles * p.ksplit;
+    // unit u = (rt * tok_tiles + tt) * ksplit + ks; split ks covers super-blocks [sb0, sb1)
+#define TC5_UNIT(u)                                                        \
+    const int ks = (u) % p.ksplit, tt = ((u) / p.ksplit) % p.tok_tiles,    \
+              rt = (u) / (p.ksplit * p.tok_tiles);                         \
+    const int sb0 = (int)((long)ks * nsb / p.ksplit), sb1 = (int)((long)(ks + 1) * nsb / p.ksplit); \
+    const int nsbu = sb1 - sb0, rot = (rt * 5 + tt * 3) % nsbu;                                     \
+    (void)tt; (void)rt; (void)rot
 
     if (tid == 0) {
-        for (int s = 0; s < STAGES; s++) {
+        for (int s = 0; s < SA; s++) {
             mbar_init(smem_u32(a_full + s), TC5_DQ_THREADS / 32);   // one arrival per dequant warp
+            mbar_init(smem_u32(a_empty + s), 1);
+        }
+        for (int s = 0; s < SB; s++) {
             mbar_init(smem_u32(b_full + s), 1);
-            mbar_init(smem_u32(empty + s), 1);
+            mbar_init(smem_u32(b_empty + s), 1);
         }
         for (int i = 0; i < 2; i++) {
-            mbar_init(smem_u32(raw_full + i), 1);
-            mbar_init(smem_u32(raw_empty + i), TC5_DQ_THREADS / 32);
             mbar_init(smem_u32(acc_full + i), 1);
-            mbar_init(smem_u32(acc_empty + i), 4);                      // one arrival per epilogue warp
+            mbar_init(smem_u32(acc_empty + i), 4);                  // one arrival per epilogue warp
         }
         *abort_flag = 0;
         mbar_init_fence();
     }
-    if (warp == 5) tc5_alloc(smem_u32(const_cast<uint32_t *>(tmem_slot)), 2 * NT);
+    if (warp == 5) tc5_alloc(smem_u32(const_cast<uint32_t *>(tmem_slot)), L::ACC_COLS * L::ACC_BUFS);
     tc5_fence_before();
     __syncthreads();
     tc5_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    // The activation rows come from the kernel in front (act_to_f16_kernel).
+    // The activation rows and their scales come from the kernel in front (act_to_f16_kernel): only
+    // the roles that read them wait for it; the weights are converted meanwhile.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+#define TC5_DEP_WAIT() asm volatile("griddepcontrol.wait;" ::: "memory")
 
     if (warp == 4) {
-        // ------------------------------------------------ TMA producer
+        // ------------------------------------------------ TMA producer: activation tiles
+        TC5_DEP_WAIT();
         if (lane == 0) {
-            uint32_t kb_it = 0, raw_it = 0;
-            for (int tile = blockIdx.x; tile < ntiles && !*abort_flag; tile += gridDim.x) {
-                const int rt = tile / p.tok_tiles, tt = tile % p.tok_tiles;
-                for (int sb = 0; sb < nsb; sb++, raw_it++) {
-                    const uint32_t rs = raw_it & 1, rph = (raw_it >> 1) & 1;
-                    if (raw_it >= 2 && !tc5_wait(smem_u32(raw_empty + rs), rph ^ 1, abort_flag)) break;
-                    mbar_arrive_expect_tx(smem_u32(raw_full + rs), TC5_RAW_BYTES);
-                    tma_load_2d(sbase + L::RAW_OFS + rs * TC5_RAW_BYTES, &wmap, sb * 144, rt * TC5_M,
-                                smem_u32(raw_full + rs));
-                    for (int j = 0; j < 4; j++, kb_it++) {
-                        const uint32_t s = kb_it % STAGES, ph = (kb_it / STAGES) & 1;
-                        if (kb_it >= STAGES && !tc5_wait(smem_u32(empty + s), ph ^ 1, abort_flag)) break;
+            uint32_t kb_it = 0;
+            bool ok = true;
+            for (int u = blockIdx.x; u < nunits && ok && !*abort_flag; u += gridDim.x) {
+                TC5_UNIT(u);
+                for (int i = 0; i < nsbu && ok; i++) {
+                    const int sb = sb0 + (i + rot) % nsbu;   // every tile starts its K walk elsewhere
+                    for (int j = 0; j < 4 && ok; j++, kb_it++) {
+                        const uint32_t s = kb_it % SB, ph = (kb_it / SB) & 1;
+                        if (kb_it >= (uint32_t)SB) ok = tc5_wait(smem_u32(b_empty + s), ph ^ 1, abort_flag);
+                        if (!ok) break;
+                        if (p.debug & 16) { mbar_arrive(smem_u32(b_full + s)); continue; }
                         mbar_arrive_expect_tx(smem_u32(b_full + s), L::B_BYTES);
                         tma_load_2d(sbase + L::B_OFS + s * L::B_BYTES, &xmap, sb * 256 + j * TC5_KB, tt * NT,
                                     smem_u32(b_full + s));
@@ -250,43 +367,63 @@ gemm_q4k_tc5_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
         // ------------------------------------------------ MMA issuer
         if (lane == 0) {
             constexpr uint32_t idesc = tc5_idesc(TC5_M, NT);
-            uint32_t kb_it = 0, tile_it = 0;
-            for (int tile = blockIdx.x; tile < ntiles && !*abort_flag; tile += gridDim.x, tile_it++) {
-                const uint32_t ab = tile_it & 1, aph = (tile_it >> 1) & 1;
-                if (tile_it >= 2 && !tc5_wait(smem_u32(acc_empty + ab), aph ^ 1, abort_flag)) break;
+            uint32_t kb_it = 0, unit_it = 0;
+            bool ok = true;
+            for (int u = blockIdx.x; u < nunits && ok && !*abort_flag; u += gridDim.x, unit_it++) {
+                TC5_UNIT(u);
+                const uint32_t ab = unit_it % L::ACC_BUFS, aph = (unit_it / L::ACC_BUFS) & 1;
+                if (unit_it >= (uint32_t)L::ACC_BUFS) ok = tc5_wait(smem_u32(acc_empty + ab), aph ^ 1, abort_flag);
+                if (!ok) break;
                 tc5_fence_after();
-                const uint32_t d_tmem = tmem_base + ab * NT;
-                bool ok = true;
-                for (int kb = 0; kb < nsb * 4 && ok; kb++, kb_it++) {
-                    const uint32_t s = kb_it % STAGES, ph = (kb_it / STAGES) & 1;
-                    ok = tc5_wait(smem_u32(a_full + s), ph, abort_flag) && tc5_wait(smem_u32(b_full + s), ph, abort_flag);
+                const uint32_t d_tmem = tmem_base + ab * L::ACC_COLS;
+                const int nkb = nsbu * 4;
+                for (int kb = 0; kb < nkb && ok; kb++, kb_it++) {
+                    const uint32_t sa = kb_it % SA, pha = (kb_it / SA) & 1, s = kb_it % SB, ph = (kb_it / SB) & 1;
+                    ok = tc5_wait(smem_u32(a_full + sa), pha, abort_flag) && tc5_wait(smem_u32(b_full + s), ph, abort_flag);
                     if (!ok) break;
                     tc5_fence_after();
-                    const uint64_t adesc = tc5_smem_desc(sbase + L::A_OFS + s * TC5_A_BYTES);
                     const uint64_t bdesc = tc5_smem_desc(sbase + L::B_OFS + s * L::B_BYTES);
 #pragma unroll
-                    for (int j = 0; j < TC5_KB / 16; j++)  // 32 bytes of K per instruction: +2 in 16-byte units
-                        if (!(p.debug & 2)) tc5_mma_f16(d_tmem, adesc + 2 * j, bdesc + 2 * j, idesc, (kb | j) != 0);
-                    tc5_commit(smem_u32(empty + s));      // stage reusable once these MMAs have read it
+                    for (int ms = 0; ms < TC5_MS; ms++) {
+                        const uint64_t adesc = tc5_smem_desc(sbase + L::A_OFS + (sa * TC5_MS + ms) * TC5_A_BYTES);
+#pragma unroll
+                        for (int j = 0; j < TC5_KB / 16; j++)  // 32 bytes of K per instruction: +2 in 16-byte units
+                            if (!(p.debug & 2))
+                                tc5_mma_f16(d_tmem + ms * NT, adesc + 2 * j, bdesc + 2 * j, idesc, (kb | j) != 0);
+                    }
+                    tc5_commit(smem_u32(a_empty + sa));   // stages reusable once these MMAs have read them
+                    tc5_commit(smem_u32(b_empty + s));
                 }
                 if (!ok) break;
-                tc5_commit(smem_u32(acc_full + ab));      // accumulator complete
+                tc5_commit(smem_u32(acc_full + ab));      // accumulators complete
             }
         }
     } else if (warp >= 6) {
-        // ------------------------------------------------ dequant: threads r and 128 + r own tile row r
-        const int r = (tid - 192) & 127;
-        const int nib = (tid - 192) >> 7;   // 0: low nibbles = sub-block 2j, 1: high nibbles = 2j+1
+        // ------------------------------------------------ dequant: thread r owns tile row r
+        // The row's raw bytes come straight from global memory into registers: while super-block i
+        // is being converted, the 144 bytes of super-block i+1 are requested one 32-byte group per
+        // k-block, so they are a full super-block period (~2 us) ahead of their use.
+        const int r = tid - 192;
         const uint32_t swz = (uint32_t)(r & 7);
-        uint32_t kb_it = 0, raw_it = 0;
+        const int a_row_ofs = (r >> 7) * TC5_A_BYTES + (r & 127) * 128;   // which 128-row operand, which row
+        const size_t row_bytes = (size_t)nsb * 144;
+        uint32_t kb_it = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < ntiles && ok && !*abort_flag; tile += gridDim.x) {
-            for (int sb = 0; sb < nsb && ok; sb++, raw_it++) {
-                const uint32_t rs = raw_it & 1, rph = (raw_it >> 1) & 1;
-                ok = tc5_wait(smem_u32(raw_full + rs), rph, abort_flag);
-                if (!ok) break;
-                const uint8_t *row = smem + L::RAW_OFS + rs * TC5_RAW_BYTES + r * 144;
-                const uint4 h = *reinterpret_cast<const uint4 *>(row);
+        for (int u = blockIdx.x; u < nunits && ok && !*abort_flag; u += gridDim.x) {
+            TC5_UNIT(u);
+            const int grow = min(rt * TC5_ROWS + r, p.nrows - 1);          // rows past the end repeat the last
+            const uint8_t *wrow = p.w + (size_t)grow * row_bytes;
+            uint4 hcur, hnxt = make_uint4(0, 0, 0, 0), qcur[8], qnxt[8];
+            {
+                const uint8_t *b = wrow + (size_t)(sb0 + rot % nsbu) * 144;
+                hcur = ldg_nc16(b);
+#pragma unroll
+                for (int g = 0; g < 8; g++) qcur[g] = ldg_nc16(b + 16 + 16 * g);
+            }
+            for (int i = 0; i < nsbu && ok; i++) {
+                const bool more = i + 1 < nsbu;
+                const uint8_t *nb = wrow + (size_t)(sb0 + (i + 1 + rot) % nsbu) * 144;
+                const uint4 h = hcur;
                 const float2 dd = __half22float2(*reinterpret_cast<const __half2 *>(&h.x));
                 // sc, m of the 8 sub-blocks (format/quant/dequant.go:360-365), four per word
                 const uint32_t sc_lo = h.y & 0x3F3F3F3Fu, m_lo = h.z & 0x3F3F3F3Fu;
@@ -294,105 +431,87 @@ gemm_q4k_tc5_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
                 const uint32_t m_hi = ((h.w >> 4) & 0x0F0F0F0Fu) | ((h.z >> 2) & 0x30303030u);
 #pragma unroll
                 for (int j = 0; j < 4; j++, kb_it++) {   // k-block j = sub-blocks 2j (low nibbles), 2j+1 (high)
-                    const uint32_t s = kb_it % STAGES, ph = (kb_it / STAGES) & 1;
-                    const uint4 q0 = *reinterpret_cast<const uint4 *>(row + 16 + 32 * j);
-                    const uint4 q1 = *reinterpret_cast<const uint4 *>(row + 32 + 32 * j);
+                    const uint32_t s = kb_it % SA, ph = (kb_it / SA) & 1;
+                    const uint4 q0 = qcur[2 * j], q1 = qcur[2 * j + 1];
+                    if (more && !(p.debug & 32)) {       // next super-block: group j (and its header with j = 0)
+                        if (j == 0) hnxt = ldg_nc16(nb);
+                        qnxt[2 * j] = ldg_nc16(nb + 16 + 32 * j);
+                        qnxt[2 * j + 1] = ldg_nc16(nb + 32 + 32 * j);
+                    }
                     const uint32_t scw = j < 2 ? sc_lo : sc_hi, mw = j < 2 ? m_lo : m_hi;
                     const int b0 = (2 * j) & 3;
-                    // w = (16 d sc) (1 + q/16) - (16 d sc + dmin m): one FFMA on a nibble placed in the
+                    // w = (128 d sc) (1 + q/128) - (128 d sc + dmin m): one FMA on a code placed in the
                     // mantissa of 1.0; the products d sc and dmin m are exact in f32.
-                    const float ds_e = 16.f * dd.x * (float)((scw >> (8 * b0)) & 0xFF);
-                    const float ds_o = 16.f * dd.x * (float)((scw >> (8 * b0 + 8)) & 0xFF);
+                    const float ds_e = 128.f * dd.x * (float)((scw >> (8 * b0)) & 0xFF);
+                    const float ds_o = 128.f * dd.x * (float)((scw >> (8 * b0 + 8)) & 0xFF);
                     const float c_e = -(ds_e + dd.y * (float)((mw >> (8 * b0)) & 0xFF));
                     const float c_o = -(ds_o + dd.y * (float)((mw >> (8 * b0 + 8)) & 0xFF));
-                    if (kb_it >= STAGES) ok = tc5_wait(smem_u32(empty + s), ph ^ 1, abort_flag);
+                    if (kb_it >= (uint32_t)SA) ok = tc5_wait(smem_u32(a_empty + s), ph ^ 1, abort_flag);
                     if (!ok) break;
-                    uint8_t *arow = smem + L::A_OFS + s * TC5_A_BYTES + r * 128;
+                    uint8_t *arow = smem + L::A_OFS + s * TC5_MS * TC5_A_BYTES + a_row_ofs;
                     const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
-                    const float ds = nib ? ds_o : ds_e, cc = nib ? c_o : c_e;
+                    if (!(p.debug & 1)) {
 #pragma unroll
-                    for (int cq = 0; cq < ((p.debug & 1) ? 0 : 4); cq++) {     // 16-byte chunk c = 4 nib + cq: k 8c..8c+7 of the k-block
-                        uint32_t wa = w[2 * cq], wb = w[2 * cq + 1];
-                        if (nib) { wa >>= 4; wb >>= 4; }
-                        float f[8];                      // nibbles of bytes 0..3 -> mantissa bits 19..22
-                        f[0] = __uint_as_float(((wa << 19) & 0x00780000u) | 0x3F800000u);
-                        f[1] = __uint_as_float(((wa << 11) & 0x00780000u) | 0x3F800000u);
-                        f[2] = __uint_as_float(((wa << 3) & 0x00780000u) | 0x3F800000u);
-                        f[3] = __uint_as_float(((wa >> 5) & 0x00780000u) | 0x3F800000u);
-                        f[4] = __uint_as_float(((wb << 19) & 0x00780000u) | 0x3F800000u);
-                        f[5] = __uint_as_float(((wb << 11) & 0x00780000u) | 0x3F800000u);
-                        f[6] = __uint_as_float(((wb << 3) & 0x00780000u) | 0x3F800000u);
-                        f[7] = __uint_as_float(((wb >> 5) & 0x00780000u) | 0x3F800000u);
-                        uint4 o;
-                        __half2 h0 = __floats2half2_rn(fmaf(f[0], ds, cc), fmaf(f[1], ds, cc));
-                        __half2 h1 = __floats2half2_rn(fmaf(f[2], ds, cc), fmaf(f[3], ds, cc));
-                        __half2 h2 = __floats2half2_rn(fmaf(f[4], ds, cc), fmaf(f[5], ds, cc));
-                        __half2 h3 = __floats2half2_rn(fmaf(f[6], ds, cc), fmaf(f[7], ds, cc));
-                        o.x = *reinterpret_cast<uint32_t *>(&h0); o.y = *reinterpret_cast<uint32_t *>(&h1);
-                        o.z = *reinterpret_cast<uint32_t *>(&h2); o.w = *reinterpret_cast<uint32_t *>(&h3);
-                        *reinterpret_cast<uint4 *>(arow + (((uint32_t)(4 * nib + cq) ^ swz) << 4)) = o;
+                        for (int c = 0; c < 8; c++) {    // 16-byte chunk c = k 8c..8c+7 of the k-block
+                            const int nib = c >> 2, cq = c & 3;
+                            const float ds = nib ? ds_o : ds_e, cc = nib ? c_o : c_e;
+                            // four codes of a word -> bytes 0x80 | q: byte 2 of a float whose byte 3 is 0x3F,
+                            // i.e. 1 + q/128, picked out by one PRMT per weight
+                            const uint32_t ua = ((nib ? w[2 * cq] >> 4 : w[2 * cq]) & 0x0F0F0F0Fu) | 0x80808080u;
+                            const uint32_t ub = ((nib ? w[2 * cq + 1] >> 4 : w[2 * cq + 1]) & 0x0F0F0F0Fu) | 0x80808080u;
+                            float v[8];
+                            tc5_fma2(v[0], v[1], tc5_code_float(ua, 0), tc5_code_float(ua, 1), ds, cc);
+                            tc5_fma2(v[2], v[3], tc5_code_float(ua, 2), tc5_code_float(ua, 3), ds, cc);
+                            tc5_fma2(v[4], v[5], tc5_code_float(ub, 0), tc5_code_float(ub, 1), ds, cc);
+                            tc5_fma2(v[6], v[7], tc5_code_float(ub, 2), tc5_code_float(ub, 3), ds, cc);
+                            uint4 o;
+                            __half2 h0 = __floats2half2_rn(v[0], v[1]), h1 = __floats2half2_rn(v[2], v[3]);
+                            __half2 h2 = __floats2half2_rn(v[4], v[5]), h3 = __floats2half2_rn(v[6], v[7]);
+                            o.x = *reinterpret_cast<uint32_t *>(&h0); o.y = *reinterpret_cast<uint32_t *>(&h1);
+                            o.z = *reinterpret_cast<uint32_t *>(&h2); o.w = *reinterpret_cast<uint32_t *>(&h3);
+                            *reinterpret_cast<uint4 *>(arow + (((uint32_t)c ^ swz) << 4)) = o;
+                        }
                     }
-                    fence_async_smem();                   // generic writes -> visible to tcgen05.mma
+                    if (!(p.debug & 4)) fence_async_smem();   // generic writes -> visible to tcgen05.mma
                     __syncwarp();
                     if (lane == 0) mbar_arrive(smem_u32(a_full + s));
                 }
                 if (!ok) break;
-                __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(raw_empty + rs));
+                hcur = hnxt;
+#pragma unroll
+                for (int g = 0; g < 8; g++) qcur[g] = qnxt[g];
             }
         }
     } else {
         // ------------------------------------------------ epilogue: warp w reads TMEM lanes 32w..32w+31
-        uint32_t tile_it = 0;
-        for (int tile = blockIdx.x; tile < ntiles && !*abort_flag; tile += gridDim.x, tile_it++) {
-            const int rt = tile / p.tok_tiles, tt = tile % p.tok_tiles;
-            const uint32_t ab = tile_it & 1, aph = (tile_it >> 1) & 1;
+        TC5_DEP_WAIT();
+        uint32_t unit_it = 0;
+        for (int u = blockIdx.x; u < nunits && !*abort_flag; u += gridDim.x, unit_it++) {
+            const uint32_t ab = unit_it % L::ACC_BUFS, aph = (unit_it / L::ACC_BUFS) & 1;
             if (!tc5_wait_relaxed(smem_u32(acc_full + ab), aph, abort_flag)) break;
             tc5_fence_after();
-            const int row = rt * TC5_M + warp * 32 + lane;
-            const uint32_t taddr = tmem_base + ab * NT + ((uint32_t)(warp * 32) << 16);
-#pragma unroll 1
-            for (int c0 = 0; c0 < NT; c0 += 32) {
-                uint32_t v[32];
-                tc5_ld32(taddr + c0, v);
-                tc5_wait_ld();
-                const int col0 = tt * NT + c0;
-                // the per-token scales of these 32 columns: one load per lane, broadcast by shuffle
-                const int mytok = p.split ? (col0 >> 1) + (lane & 15) : col0 + lane;
-                const float myscale = mytok < p.ntok ? __ldg(p.inv_scale + mytok) : 0.f;
-                if (p.split) {
-#pragma unroll
-                    for (int j = 0; j < 16; j++) {
-                        const int tok = (col0 >> 1) + j;
-                        const float sc = __shfl_sync(0xffffffffu, myscale, j);
-                        if (row < p.nrows && tok < p.ntok) {
-                            const float acc = (__uint_as_float(v[2 * j]) + __uint_as_float(v[2 * j + 1])) * sc;
-                            const size_t o = (size_t)tok * p.nrows + row;
-                            if (p.out_dtype == JL_DT_F32) static_cast<float *>(p.out)[o] = acc;
-                            else if (p.out_dtype == JL_DT_BF16) static_cast<__nv_bfloat16 *>(p.out)[o] = __float2bfloat16_rn(acc);
-                            else static_cast<__half *>(p.out)[o] = __float2half_rn(acc);
-                        }
-                    }
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 32; j++) {
-                        const int tok = col0 + j;
-                        const float sc = __shfl_sync(0xffffffffu, myscale, j);
-                        if (row < p.nrows && tok < p.ntok) {
-                            const float acc = __uint_as_float(v[j]) * sc;
-                            const size_t o = (size_t)tok * p.nrows + row;
-                            if (p.out_dtype == JL_DT_F32) static_cast<float *>(p.out)[o] = acc;
-                            else if (p.out_dtype == JL_DT_BF16) static_cast<__nv_bfloat16 *>(p.out)[o] = __float2bfloat16_rn(acc);
-                            else static_cast<__half *>(p.out)[o] = __float2half_rn(acc);
-                        }
-                    }
-                }
-            }
+            // the CTA's last unit is shared with the dequant warps, which have nothing left to do
+            const bool last = u + (int)gridDim.x >= nunits;
+            tc5_epilogue<NT>(p, u, tmem_base + ab * L::ACC_COLS, warp, lane, last ? 0 : -1);
             tc5_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(acc_empty + ab));
         }
     }
+    if (warp >= 6 && !*abort_flag && (int)blockIdx.x < nunits) {
+        // ------------------------------------------------ dequant warps help drain the last accumulators
+        TC5_DEP_WAIT();
+        const int n_mine = (nunits - 1 - (int)blockIdx.x) / (int)gridDim.x + 1;
+        const uint32_t unit_it = (uint32_t)(n_mine - 1);
+        const int u = (int)blockIdx.x + (n_mine - 1) * (int)gridDim.x;
+        const uint32_t ab = unit_it % L::ACC_BUFS, aph = (unit_it / L::ACC_BUFS) & 1;
+        if (tc5_wait_relaxed(smem_u32(acc_full + ab), aph, abort_flag)) {
+            tc5_fence_after();
+            tc5_epilogue<NT>(p, u, tmem_base + ab * L::ACC_COLS, warp & 3, lane, 1 + ((warp - 6) >> 2));
+        }
+    }
+#undef TC5_UNIT
+#undef TC5_DEP_WAIT
 
     // teardown: everyone meets, the allocating warp frees TMEM
     tc5_fence_before();
@@ -400,7 +519,21 @@ gemm_q4k_tc5_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
     if (tid == 0 && *abort_flag) atomicExch(p.status, 2);
     if (warp == 5) {
         tc5_fence_after();
-        tc5_dealloc(tmem_base, 2 * NT);
+        tc5_dealloc(tmem_base, L::ACC_COLS * L::ACC_BUFS);
+    }
+}
+
+// out = sum over the K splits of their partial planes, in split order.
+__global__ void __launch_bounds__(256)
+tc5_reduce_kernel(const float *__restrict__ partial, void *__restrict__ out, int out_dtype, size_t n, int ksplit) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        float acc = partial[i];
+        for (int s = 1; s < ksplit; s++) acc += partial[(size_t)s * n + i];
+        if (out_dtype == JL_DT_F32) static_cast<float *>(out)[i] = acc;
+        else if (out_dtype == JL_DT_BF16) static_cast<__nv_bfloat16 *>(out)[i] = __float2bfloat16_rn(acc);
+        else static_cast<__half *>(out)[i] = __float2half_rn(acc);
     }
 }
 
@@ -412,29 +545,44 @@ int jl_gemm_tc5_supported(uint32_t type, int nrows, int k, int ntok) {
 
 static int tc5_pick_nt(int ntok_eff) { return ntok_eff > 128 ? 256 : (ntok_eff > 64 ? 128 : 64); }
 
+// How many CTAs share one tile's K range: only when the tiles alone would leave SMs idle.
+static int tc5_ksplit(int nrows, int ntok_eff, int k, int sms) {
+    const int nt = tc5_pick_nt(ntok_eff);
+    const int units = ((nrows + TC5_ROWS - 1) / TC5_ROWS) * ((ntok_eff + nt - 1) / nt);
+    int ks = sms / units;
+    if (ks > 8) ks = 8;
+    if (ks > k / 256) ks = k / 256;
+    return ks < 2 ? 1 : ks;
+}
+
 int jl_gemm_tc5_choice(jl_ctx *ctx, uint32_t type, int nrows, int k, int ntok, jl_choice *out) {
     if (!jl_gemm_tc5_supported(type, nrows, k, ntok)) return JL_DECLINED;
     jl_choice c = {};
-    int nt = tc5_pick_nt(ntok);
-    c.kernel = JL_K_TC5; c.warps = TC5_THREADS / 32; c.rows_per_cta = TC5_M; c.split_k = 1;
+    const int sms = ctx ? ctx->sm_count : 148;
+    const int nt = tc5_pick_nt(ntok);
+    c.kernel = JL_K_TC5; c.warps = TC5_THREADS / 32; c.rows_per_cta = TC5_ROWS;
+    c.split_k = tc5_ksplit(nrows, ntok, k, sms);
     c.tile_m = TC5_M; c.tile_n = nt; c.tile_k = TC5_KB;
-    int tiles = ((nrows + TC5_M - 1) / TC5_M) * ((ntok + nt - 1) / nt);
-    int sms = ctx ? ctx->sm_count : 148;
-    c.grid = tiles < sms ? tiles : sms;
+    const int units = ((nrows + TC5_ROWS - 1) / TC5_ROWS) * ((ntok + nt - 1) / nt) * c.split_k;
+    c.grid = units < sms ? units : sms;
     *out = c;
     return JL_OK;
 }
 
-size_t jl_gemm_tc5_scratch_bytes(int k, int ntok, int x_dtype) {
-    size_t rows = (size_t)ntok * (x_dtype == JL_DT_F32 ? 2 : 1);
-    return rows * (size_t)k * 2 + (size_t)ntok * 4 + 256;
+size_t jl_gemm_tc5_scratch_bytes(int nrows, int k, int ntok, int x_dtype, int sms) {
+    const int ntok_eff = ntok * (x_dtype == JL_DT_F32 ? 2 : 1);
+    size_t b = (((size_t)ntok_eff * k * 2 + 255) & ~(size_t)255) + (((size_t)ntok * 4 + 255) & ~(size_t)255);
+    const int ks = tc5_ksplit(nrows, ntok_eff, k, sms);
+    if (ks > 1) b += (size_t)ks * ntok * nrows * 4;
+    return b + 256;
 }
 
-template <int NT, int STAGES>
-static int tc5_launch(jl_ctx *ctx, const CUtensorMap &wmap, const CUtensorMap &xmap, const tc5_params &p, int grid,
+template <int NT, int SA, int SB>
+static int tc5_launch(jl_ctx *ctx, const CUtensorMap &xmap, const tc5_params &p, int grid,
                       cudaStream_t s) {
-    using L = tc5_smem<NT, STAGES>;
-    JL_CUDA(ctx, cudaFuncSetAttribute(gemm_q4k_tc5_kernel<NT, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    using L = tc5_smem<NT, SA, SB>;
+    static_assert(L::TOTAL <= 227 * 1024, "shared memory budget");
+    JL_CUDA(ctx, cudaFuncSetAttribute(gemm_q4k_tc5_kernel<NT, SA, SB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       L::TOTAL));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid); cfg.blockDim = dim3(TC5_THREADS); cfg.dynamicSmemBytes = L::TOTAL; cfg.stream = s;
@@ -442,7 +590,7 @@ static int tc5_launch(jl_ctx *ctx, const CUtensorMap &wmap, const CUtensorMap &x
     at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at; cfg.numAttrs = (ctx->opts.flags & JL_FLAG_NO_PDL) ? 0 : 1;
-    JL_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemm_q4k_tc5_kernel<NT, STAGES>, wmap, xmap, p));
+    JL_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemm_q4k_tc5_kernel<NT, SA, SB>, xmap, p));
     return JL_OK;
 }
 
@@ -453,47 +601,58 @@ int jl_launch_gemm_tc5(jl_ctx *ctx, void *out_dev, int out_dtype, const jl_weigh
         return jl_set_err(ctx, JL_DECLINED, "tcgen05 GEMM serves Q4_K with k %% 256 == 0");
     const int split = x_dtype == JL_DT_F32 ? 1 : 0;
     const int ntok_eff = ntok * (split ? 2 : 1);
-    const size_t need = jl_gemm_tc5_scratch_bytes(k, ntok, x_dtype);
+    const size_t need = jl_gemm_tc5_scratch_bytes(nrows, k, ntok, x_dtype, ctx->sm_count);
     if (ctx->scratch_cap < need)
-        return jl_set_err(ctx, JL_ENOMEM, "GEMM scratch holds %zu bytes, %d tokens x %d need %zu (jl_reserve sizes it)",
-                          ctx->scratch_cap, ntok, k, need);
-    __half *xh = (__half *)ctx->scratch;
-    float *inv_scale = (float *)((uint8_t *)ctx->scratch + (((size_t)ntok_eff * k * 2 + 255) & ~(size_t)255));
+        return jl_set_err(ctx, JL_ENOMEM, "GEMM scratch holds %zu bytes, %d tokens x %d x %d need %zu (jl_reserve sizes it)",
+                          ctx->scratch_cap, ntok, nrows, k, need);
+    uint8_t *sp = (uint8_t *)ctx->scratch;
+    __half *xh = (__half *)sp;
+    sp += ((size_t)ntok_eff * k * 2 + 255) & ~(size_t)255;
+    float *inv_scale = (float *)sp;
+    sp += ((size_t)ntok * 4 + 255) & ~(size_t)255;
+    float *partial = (float *)sp;
 
-    // activations -> scaled f16 rows
-    {
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    const int nattr = (ctx->opts.flags & JL_FLAG_NO_PDL) ? 0 : 1;
+    {   // activations -> scaled f16 rows
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(ntok); cfg.blockDim = dim3(256); cfg.stream = s;
-        cudaLaunchAttribute at[1];
-        at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        at[0].val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = at; cfg.numAttrs = (ctx->opts.flags & JL_FLAG_NO_PDL) ? 0 : 1;
+        cfg.attrs = at; cfg.numAttrs = nattr;
         JL_CUDA(ctx, cudaLaunchKernelEx(&cfg, act_to_f16_kernel, x_dev, x_dtype, xh, inv_scale, k, split));
         ctx->st.launches++;
     }
 
     const int nt = tc5_pick_nt(ntok_eff);
-    CUtensorMap wmap, xmap;
+    CUtensorMap xmap;
     const uint8_t *wbase = w->data + (size_t)expert * nrows * jl_row_bytes(w->type, k);
-    if (!jl_make_tmap_2d(&wmap, wbase, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, jl_row_bytes(w->type, k), (uint64_t)nrows,
-                         jl_row_bytes(w->type, k), 144, TC5_M, CU_TENSOR_MAP_SWIZZLE_NONE) ||
-        !jl_make_tmap_2d(&xmap, xh, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (uint64_t)k, (uint64_t)ntok_eff, (uint64_t)k * 2,
+    if (!jl_make_tmap_2d(&xmap, xh, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (uint64_t)k, (uint64_t)ntok_eff, (uint64_t)k * 2,
                          TC5_KB, nt, CU_TENSOR_MAP_SWIZZLE_128B))
         return jl_set_err(ctx, JL_DECLINED, "the driver refused a tensor map for this shape");
 
     tc5_params p;
     p.nrows = nrows; p.k = k; p.ntok = ntok; p.ntok_eff = ntok_eff; p.split = split;
-    p.row_tiles = (nrows + TC5_M - 1) / TC5_M; p.tok_tiles = (ntok_eff + nt - 1) / nt;
-    p.out_dtype = out_dtype; p.out = out_dev; p.inv_scale = inv_scale; p.status = ctx->dev_status;
-    p.debug = (int)((ctx->opts.flags >> 16) & 3);
-    const int tiles = p.row_tiles * p.tok_tiles;
-    const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
+    p.row_tiles = (nrows + TC5_ROWS - 1) / TC5_ROWS; p.tok_tiles = (ntok_eff + nt - 1) / nt;
+    p.ksplit = tc5_ksplit(nrows, ntok_eff, k, ctx->sm_count);
+    p.out_dtype = out_dtype; p.out = out_dev; p.partial = partial; p.inv_scale = inv_scale; p.w = wbase; p.status = ctx->dev_status;
+    p.debug = (int)((ctx->opts.flags >> 16) & 63);
+    const int units = p.row_tiles * p.tok_tiles * p.ksplit;
+    const int grid = units < ctx->sm_count ? units : ctx->sm_count;
     int rc;
-    if (nt == 256) rc = tc5_launch<256, 3>(ctx, wmap, xmap, p, grid, s);
-    else if (nt == 128) rc = tc5_launch<128, 4>(ctx, wmap, xmap, p, grid, s);
-    else rc = tc5_launch<64, 4>(ctx, wmap, xmap, p, grid, s);
+    if (nt == 256) rc = tc5_launch<256, 4, 3>(ctx, xmap, p, grid, s);
+    else if (nt == 128) rc = tc5_launch<128, 3, 6>(ctx, xmap, p, grid, s);
+    else rc = tc5_launch<64, 3, 8>(ctx, xmap, p, grid, s);
     if (rc) return rc;
     ctx->st.launches++;
+    if (p.ksplit > 1) {
+        const size_t n = (size_t)ntok * nrows;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)((n + 1023) / 1024 < 1184 ? (n + 1023) / 1024 : 1184)); cfg.blockDim = dim3(256);
+        cfg.stream = s; cfg.attrs = at; cfg.numAttrs = nattr;
+        JL_CUDA(ctx, cudaLaunchKernelEx(&cfg, tc5_reduce_kernel, (const float *)partial, out_dev, out_dtype, n, p.ksplit));
+        ctx->st.launches++;
+    }
     JL_CUDA(ctx, cudaGetLastError());
     return JL_OK;
 }

@@ -120,4 +120,4 @@ int jl_launch_gemm_tc5(jl_ctx *ctx, void *out_dev, int out_dtype, const jl_weigh
                        const void *x_dev, int x_dtype, int ntok, cudaStream_t s);
 int jl_gemm_tc5_supported(uint32_t type, int nrows, int k, int ntok);
 int jl_gemm_tc5_choice(jl_ctx *ctx, uint32_t type, int nrows, int k, int ntok, jl_choice *out);
-size_t jl_gemm_tc5_scratch_bytes(int k, int ntok, int x_dtype);
+size_t jl_gemm_tc5_scratch_bytes(int nrows, int k, int ntok, int x_dtype, int sms);
