@@ -206,6 +206,19 @@ int jl_matmul_dev(jl_ctx *ctx, void *out_dev, int out_dtype, const jl_weight *w,
 int jl_moe_dev(jl_ctx *ctx, float *out_dev, const void *h_dev, int h_dtype, const float *logits_dev,
                int ntok, const jl_moe_desc *desc, int32_t *sel_out_dev, float *wt_out_dev, void *stream);
 
+/* ---- allocation-free decode (no counterpart in the reference) -------------
+ * out_dev[0:nrows] = W x for Q4_K, for callers that must not allocate device memory (inside a
+ * stream capture, under a memory planner that forbids late cudaMalloc, in a latency-critical
+ * loop). No context: w_dev is the raw ggml Q4_K tensor ALREADY on the device (16-byte
+ * aligned), x_dev and out_dev are device f32, `stream` a cudaStream_t on the current device.
+ * The kernel's scratch is a fixed array inside the library, so k is limited to
+ * jl_noalloc_max_k() (16384); a larger k returns JL_ENOMEM. The call performs no cudaMalloc,
+ * cudaFree or other allocating call. The first call on each device looks up the array's
+ * address: make that call before starting a stream capture. All calls on a device share the
+ * array, so calls that can overlap on the GPU (different streams) race; use one stream. */
+int jl_noalloc_max_k(void);
+int jl_matvec_q4k_noalloc(float *out_dev, const void *w_dev, const float *x_dev, int nrows, int k, void *stream);
+
 /* ---- host-side fault injection: JITLLM_DEVICE_FAIL_AT (jit/gpu/tier/fault.go:12-58)
  * The n-th, ... serving calls on ctx (1-based ordinals, counted from this call)
  * fail with JL_EDEVICE before anything is launched. n = 0 disarms. Test-only. */

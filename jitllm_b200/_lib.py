@@ -77,6 +77,8 @@ SYMBOLS = {
     "jl_matmul_dev": (_I, [_VP, _VP, _I, _VP, _VP, _I, _I, _VP]),
     "jl_moe_dev": (_I, [_VP, _VP, _VP, _I, _VP, _I, C.POINTER(MoeDesc), _VP, _VP, _VP]),
     "jl_test_fail_at": (_I, [_VP, C.POINTER(C.c_int), _I]),
+    "jl_noalloc_max_k": (_I, []),
+    "jl_matvec_q4k_noalloc": (_I, [_VP, _VP, _VP, _I, _I, _VP]),
 }
 
 _lib = None

@@ -481,3 +481,89 @@ int jl_launch_gemv(jl_ctx *ctx, float *out_dev, const jl_weight *w, int expert, 
     JL_CUDA(ctx, cudaGetLastError());
     return JL_OK;
 }
+
+// ------------------------------------------------------ allocation-free entry point
+//
+// jl_matvec_q4k_noalloc is for callers that may not allocate device memory: code running
+// under a stream capture or inside another library's allocator callbacks, a runtime that
+// pre-plans every byte of HBM and forbids late cudaMalloc, a real-time serving loop where an
+// allocation would mean a device-wide synchronisation. It is the split form of the Q4_K
+// decode (activation prep kernel -> tensor-core kernel) with the prepared activation
+// operand kept in a fixed __device__ array instead of a context's scratch buffer.
+//
+// The array belongs to the loaded library: every GPU that loads it holds the
+// JL_NOALLOC_SCRATCH_BYTES until the process exits, every call on a device shares it (calls
+// whose kernels can overlap on the GPU race on it: keep them on one stream), and a call
+// finds the previous call's contents there -- the prep kernel rewrites every byte the
+// decode kernel reads, so nothing has to start at zero except the status word, which the
+// kernels only ever set.
+#define JL_NOALLOC_MAX_K 16384
+#define JL_NOALLOC_SCRATCH_BYTES ((JL_NOALLOC_MAX_K / 256) * Q4K_XP_SB_BYTES + Q4K_XP_ZERO_BYTES)
+static __device__ __align__(256) uint8_t jl_noalloc_scratch[JL_NOALLOC_SCRATCH_BYTES];
+static __device__ int jl_noalloc_status;
+
+// In host code the names above are only handles of the symbols; the device addresses are
+// asked for once per device, with that device current.
+static std::mutex jl_noalloc_mu;
+static uint8_t *jl_noalloc_scratch_addr[64];
+static int *jl_noalloc_status_addr[64];
+
+JL_EXPORT int jl_noalloc_max_k(void) { return JL_NOALLOC_MAX_K; }
+
+JL_EXPORT int jl_matvec_q4k_noalloc(float *out_dev, const void *w_dev, const float *x_dev, int nrows, int k,
+                                    void *stream) {
+    if (!out_dev || !w_dev || !x_dev || nrows < 1 || k < 256 || k % 256) return JL_EINVAL;
+    if (k > JL_NOALLOC_MAX_K) return JL_ENOMEM;   // beyond the fixed scratch: refuse, never grow
+    if (((uintptr_t)w_dev & 15) || ((uintptr_t)x_dev & 15)) return JL_EINVAL;
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return JL_ECUDA;
+    uint8_t *scratch;
+    int *status;
+    {
+        std::lock_guard<std::mutex> lk(jl_noalloc_mu);
+        if (!jl_noalloc_scratch_addr[dev]) {   // first call on this device: before any stream capture
+            void *p = nullptr, *q = nullptr;
+            if (cudaGetSymbolAddress(&p, jl_noalloc_scratch) != cudaSuccess) { cudaGetLastError(); return JL_ECUDA; }
+            if (cudaGetSymbolAddress(&q, jl_noalloc_status) != cudaSuccess) { cudaGetLastError(); return JL_ECUDA; }
+            jl_noalloc_scratch_addr[dev] = (uint8_t *)p;
+            jl_noalloc_status_addr[dev] = (int *)q;
+        }
+        scratch = jl_noalloc_scratch_addr[dev];
+        status = jl_noalloc_status_addr[dev];
+    }
+    const int nsb = k / 256;
+    const size_t row_bytes = (size_t)nsb * 144;
+    CUtensorMap map;   // encoded on the host into this stack object: no device memory involved
+    if (!jl_make_tmap_2d(&map, w_dev, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, row_bytes, (uint64_t)nrows, row_bytes, 144, 16,
+                         CU_TENSOR_MAP_SWIZZLE_NONE))
+        return JL_ENOTSUP;
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((nsb + 3) / 4, 1); cfg.blockDim = dim3(128); cfg.stream = s;
+        cfg.attrs = at; cfg.numAttrs = 1;
+        if (cudaLaunchKernelEx(&cfg, q4k_xprep_kernel, x_dev, scratch, nsb, 1) != cudaSuccess) {
+            cudaGetLastError();
+            return JL_ECUDA;
+        }
+    }
+    const size_t smem = q4k_tma_smem(4, 4, nsb, false);
+    if (smem > 48 * 1024 &&
+        cudaFuncSetAttribute(gemv_q4k_tma_kernel<4, 4, 4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)smem) != cudaSuccess) {
+        cudaGetLastError();
+        return JL_ECUDA;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((nrows + 15) / 16, 1); cfg.blockDim = dim3(128); cfg.dynamicSmemBytes = smem; cfg.stream = s;
+    cfg.attrs = at; cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, gemv_q4k_tma_kernel<4, 4, 4, false>, map, 0, (const void *)scratch, out_dev, nrows,
+                           nsb, 1, status) != cudaSuccess) {
+        cudaGetLastError();
+        return JL_ECUDA;
+    }
+    return JL_OK;
+}
