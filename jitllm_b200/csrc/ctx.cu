@@ -353,13 +353,14 @@ static int matmul_host(jl_ctx *ctx, void *out, int out_dtype, uint32_t type, con
     rc = matmul_dev_locked(ctx, ctx->o_dev, out_dtype, dw, 0, ctx->x_dev, x_dtype, ntok, ctx->stream);
     if (rc) return rc;
     JL_CUDA(ctx, cudaMemcpyAsync(ctx->o_pin, ctx->o_dev, ob, cudaMemcpyDeviceToHost, ctx->stream));
+    // the status word rides along (the pinned x buffer is free again: reuse its first word)
+    JL_CUDA(ctx, cudaMemcpyAsync(ctx->x_pin, ctx->dev_status, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
     cudaError_t e = cudaStreamSynchronize(ctx->stream);
     if (e != cudaSuccess) {
         ctx->unhealthy = true;
         return jl_set_err(ctx, JL_ECUDA, "kernel or copy failed: %s", cudaGetErrorString(e));
     }
-    int dstat = 0;
-    JL_CUDA(ctx, cudaMemcpy(&dstat, ctx->dev_status, sizeof(int), cudaMemcpyDeviceToHost));
+    const int dstat = *(const int *)ctx->x_pin;
     if (dstat) {
         cudaMemset(ctx->dev_status, 0, sizeof(int));
         return jl_set_err(ctx, JL_ETIMEDOUT, "a bounded device-side wait ran out (code %d)", dstat);

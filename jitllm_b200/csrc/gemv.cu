@@ -391,8 +391,8 @@ int jl_gemv_choice(jl_ctx *ctx, uint32_t type, int nrows, int k, int ntok, jl_ch
         c.grid = (nrows + 7) / 8 * ntok;
     } else {
         const long tasks = (long)((nrows + 15) / 16) * (k / 256) * ntok;
-        const bool fused = ctx && tasks <= 2L * ctx->sm_count * 32;
-        if (!warps) warps = fused ? 8 : 4;
+        const bool fused = ctx && tasks <= (long)ctx->sm_count * 16;
+        if (!warps) warps = fused ? 16 : 4;
         c.kernel = JL_K_MMA; c.warps = warps % 100; c.rows_per_cta = 16;
         c.split_k = c.warps < k / 256 ? c.warps : k / 256;
         c.tile_m = 16; c.tile_n = 8; c.tile_k = 16;
@@ -430,7 +430,7 @@ int jl_launch_gemv(jl_ctx *ctx, float *out_dev, const jl_weight *w, int expert, 
         const int nattr = (ctx->opts.flags & JL_FLAG_NO_PDL) ? 0 : 1;
         // Latency-bound shapes (about one wave of warp-tasks or less) take the fused form.
         const long tasks = (long)((nrows + 15) / 16) * nsb * ntok;
-        bool fused = tasks <= 2L * ctx->sm_count * 32;
+        bool fused = tasks <= (long)ctx->sm_count * 16;
         if (ctx->opts.flags & JL_FLAG_DECODE_FUSED) fused = true;
         if (ctx->opts.flags & JL_FLAG_DECODE_SPLIT) fused = false;
         if (!fused) {
@@ -458,9 +458,9 @@ int jl_launch_gemv(jl_ctx *ctx, float *out_dev, const jl_weight *w, int expert, 
         // (warps per CTA, ring stages per warp, CTAs per SM the registers are held to, fused)
         if (fused) {
             if (warps == 4) LAUNCH_Q4K_TMA(4, 4, 4, true);
-            else if (warps == 16) LAUNCH_Q4K_TMA(16, 1, 1, true);
             else if (warps == 116) LAUNCH_Q4K_TMA(16, 2, 1, true);
-            else LAUNCH_Q4K_TMA(8, 2, 2, true);
+            else if (warps == 8) LAUNCH_Q4K_TMA(8, 2, 2, true);
+            else LAUNCH_Q4K_TMA(16, 1, 1, true);
         } else {
             if (warps == 2) LAUNCH_Q4K_TMA(2, 8, 8, false);
             else if (warps == 8) LAUNCH_Q4K_TMA(8, 2, 2, false);
