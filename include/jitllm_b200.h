@@ -171,6 +171,10 @@ typedef struct jl_moe_desc {
 int jl_moe(jl_ctx *ctx, float *out, const void *h, int h_dtype, const float *logits, int ntok,
            const jl_moe_desc *desc, int32_t *sel_out, float *wt_out);
 
+/* Pre-size the mixture layer's scratch (token lists, gathered rows, intermediates) so that
+ * jl_moe_dev never needs more than it finds. */
+int jl_moe_reserve(jl_ctx *ctx, int ntok, int n_expert, int top_k, int hidden, int ffn);
+
 /* ---- per-shape selection: batchMV / chooseSplit -------------------------- */
 int jl_select(jl_ctx *ctx, uint32_t type, int nrows, int k, int ntok, jl_choice *out);
 

@@ -210,6 +210,11 @@ static int resident(jl_ctx *ctx, uint32_t type, const void *w, size_t w_bytes, i
     return JL_OK;
 }
 
+int jl_resident_bank(jl_ctx *ctx, uint32_t type, const void *w, size_t w_bytes, int n_expert, int nrows, int k,
+                     jl_weight **out) {
+    return resident(ctx, type, w, w_bytes, n_expert, nrows, k, out);
+}
+
 JL_EXPORT int jl_forget(jl_ctx *ctx, const void *p, size_t n) {
     if (!ctx) return JL_EINVAL;
     std::lock_guard<std::mutex> lk(ctx->mu);

@@ -130,6 +130,18 @@ int jl_repack_upload(jl_ctx *ctx, uint32_t type, const void *w_host, size_t w_by
     jl_weight *w = new jl_weight();
     memset(w, 0, sizeof(*w));
     w->type = type; w->n_expert = n_expert; w->nrows = nrows; w->k = k; w->raw_bytes = need;
+    w->emin = 255; w->emax = 0;
+    if (type == JL_TYPE_MXFP4) {   // the scale range decides whether f16 can hold the weights exactly
+        const uint8_t *b = (const uint8_t *)w_host;
+        for (size_t i = 0; i < need; i += 17) {
+            bool zero = true;
+            for (int j = 1; j < 17 && zero; j++) zero = (b[i + j] & 0x77) == 0;
+            if (zero) continue;
+            if (b[i] < w->emin) w->emin = b[i];
+            if (b[i] > w->emax) w->emax = b[i];
+        }
+        if (w->emin > w->emax) { w->emin = 127; w->emax = 127; }
+    }
     cudaError_t e;
     if (type == JL_TYPE_Q4_K) {
         // +16 so a kernel may over-read one aligned chunk past the end.

@@ -32,189 +32,8 @@
 //
 // Every wait on an mbarrier is bounded: when a limit runs out the kernel sets a status word,
 // raises a CTA-wide abort flag that every role polls, frees its TMEM and returns.
-#include "jl_internal.cuh"
-#include "tma.cuh"
+#include "tc5.cuh"
 
-#define TC5_M 128           // rows of one MMA (tcgen05 cta_group::1 M)
-#define TC5_MS 2            // MMAs that share one activation tile: a CTA tile is 256 weight rows
-#define TC5_ROWS (TC5_M * TC5_MS)
-#define TC5_KB 64           // k per shared-memory stage (128 bytes of f16: one swizzle atom)
-#define TC5_RAW_BYTES (TC5_ROWS * 144)
-#define TC5_A_BYTES (TC5_M * TC5_KB * 2)   // one 128-row operand
-#define TC5_THREADS 448     // 14 warps: 4 epilogue, producer, MMA, 8 dequant
-#define TC5_DQ_THREADS 256  // one thread per tile row
-
-// ------------------------------------------------------------- activations
-
-// Eight consecutive activations of a token row as f32 (k is a multiple of 8).
-__device__ __forceinline__ void act_load8(const void *x, int x_dtype, size_t idx, float (&v)[8]) {
-    if (x_dtype == JL_DT_F32) {
-        const float4 a = __ldg(reinterpret_cast<const float4 *>(static_cast<const float *>(x) + idx));
-        const float4 b = __ldg(reinterpret_cast<const float4 *>(static_cast<const float *>(x) + idx) + 1);
-        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-    } else {
-        const uint4 u = __ldg(reinterpret_cast<const uint4 *>(static_cast<const uint16_t *>(x) + idx));
-        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-            if (x_dtype == JL_DT_BF16) {
-                v[2 * i] = __uint_as_float(w[i] << 16);
-                v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
-            } else {
-                const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[i]));
-                v[2 * i] = f.x; v[2 * i + 1] = f.y;
-            }
-        }
-    }
-}
-
-// One CTA per token row. dst rows: `split` ? (2 tok: hi, 2 tok + 1: lo) : tok.
-__global__ void __launch_bounds__(256)
-act_to_f16_kernel(const void *__restrict__ x, int x_dtype, __half *__restrict__ dst, float *__restrict__ inv_scale,
-                  int k, int split) {
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    __shared__ float wmax[8];
-    const int tok = blockIdx.x, tid = threadIdx.x;
-    const size_t base = (size_t)tok * k;
-    float amax = 0.f;
-    for (int c = tid; c < k / 8; c += 256) {
-        float v[8];
-        act_load8(x, x_dtype, base + (size_t)c * 8, v);
-#pragma unroll
-        for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(v[i]));
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-    if ((tid & 31) == 0) wmax[tid >> 5] = amax;
-    __syncthreads();
-    amax = wmax[0];
-#pragma unroll
-    for (int w = 1; w < 8; w++) amax = fmaxf(amax, wmax[w]);
-    int e = (int)((__float_as_uint(amax) >> 23) & 0xFF) - 127;
-    int s = 14 - e;
-    if (amax == 0.f || !(amax < __int_as_float(0x7f800000))) s = 0;
-    s = max(-100, min(100, s));
-    const float scale = __uint_as_float((uint32_t)(127 + s) << 23);
-    if (tid == 0) inv_scale[tok] = __uint_as_float((uint32_t)(127 - s) << 23);
-    __half *hi = dst + (size_t)(split ? 2 * tok : tok) * k;
-    __half *lo = hi + k;
-    for (int c = tid; c < k / 8; c += 256) {
-        float v[8];
-        act_load8(x, x_dtype, base + (size_t)c * 8, v);
-        uint32_t h[4], l[4];
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-            const float a = v[2 * i] * scale, b = v[2 * i + 1] * scale;
-            const __half2 hh = __floats2half2_rn(a, b);
-            const float2 back = __half22float2(hh);
-            const __half2 ll = __floats2half2_rn(a - back.x, b - back.y);
-            h[i] = *reinterpret_cast<const uint32_t *>(&hh);
-            l[i] = *reinterpret_cast<const uint32_t *>(&ll);
-        }
-        *reinterpret_cast<uint4 *>(hi + (size_t)c * 8) = make_uint4(h[0], h[1], h[2], h[3]);
-        if (split) *reinterpret_cast<uint4 *>(lo + (size_t)c * 8) = make_uint4(l[0], l[1], l[2], l[3]);
-    }
-}
-
-// --------------------------------------------------------------- tcgen05 PTX
-
-__device__ __forceinline__ void tc5_alloc(uint32_t smem_dst, uint32_t ncols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tc5_dealloc(uint32_t taddr, uint32_t ncols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void tc5_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc5_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc5_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-// D[tmem] (+)= A[smem desc] * B[smem desc]; accumulate = 0 overwrites D.
-__device__ __forceinline__ void tc5_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                            uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-// 32 lanes x 32 columns of 32-bit: thread i of the warp gets lane (base + i), columns c..c+31.
-__device__ __forceinline__ void tc5_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr)
-        : "memory");
-}
-__device__ __forceinline__ void tc5_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory matrix descriptor, K-major, SWIZZLE_128B: rows of 128 bytes, 8-row atoms of
-// 1024 bytes (stride byte offset 1024), descriptor version 1 (sm_100).
-__device__ __forceinline__ uint64_t tc5_smem_desc(uint32_t smem_addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);   // start address, 16-byte units
-    d |= (uint64_t)1 << 16;                       // leading byte offset (unused for swizzled K-major)
-    d |= (uint64_t)(1024 >> 4) << 32;             // stride byte offset
-    d |= (uint64_t)1 << 46;                       // version
-    d |= (uint64_t)2 << 61;                       // SWIZZLE_128B
-    return d;
-}
-// Instruction descriptor, kind::f16: D f32, A and B f16, both K-major, M x N.
-__host__ __device__ constexpr uint32_t tc5_idesc(int m, int n) {
-    return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
-
-// Byte i of `codes` (0x80 | q) as the float 1 + q/128: 0x3F in byte 3, the code in byte 2.
-__device__ __forceinline__ float tc5_code_float(uint32_t codes, int i) {
-    return __uint_as_float(__byte_perm(codes, 0x3F000000u, 0x7054 | (i << 8)));
-}
-// Two f32 FMAs in one instruction (fma.rn.f32x2): d = a * b + c on both halves.
-__device__ __forceinline__ void tc5_fma2(float &d0, float &d1, float a0, float a1, float b, float c) {
-    asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\t"
-        "mov.b64 ra, {%2, %3};\n\t"
-        "mov.b64 rb, {%4, %4};\n\t"
-        "mov.b64 rc, {%5, %5};\n\t"
-        "fma.rn.f32x2 rd, ra, rb, rc;\n\t"
-        "mov.b64 {%0, %1}, rd;\n\t}"
-        : "=f"(d0), "=f"(d1)
-        : "f"(a0), "f"(a1), "f"(b), "f"(c));
-}
-
-__device__ __forceinline__ uint4 ldg_nc16(const void *p) {
-    uint4 v;
-    asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-    return v;
-}
-
-// Bounded wait that also gives up when another role of the CTA has aborted.
-__device__ __forceinline__ bool tc5_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
-    for (uint32_t i = 0; i < JL_SPIN_LIMIT; i++) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 255u) == 255u && *abort_flag) return false;
-    }
-    *abort_flag = 1;
-    return false;
-}
-
-// The same, for a role that is not on the critical path: backs off between polls so that it
-// does not take issue slots from the dequant warps it shares a scheduler with.
-__device__ __forceinline__ bool tc5_wait_relaxed(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
-    for (uint32_t i = 0; i < (JL_SPIN_LIMIT >> 4); i++) {
-        if (mbar_try_wait(bar, parity)) return true;
-        __nanosleep(256);
-        if ((i & 63u) == 63u && *abort_flag) return false;
-    }
-    *abort_flag = 1;
-    return false;
-}
 
 // ------------------------------------------------------------------- kernel
 
@@ -620,7 +439,7 @@ int jl_launch_gemm_tc5(jl_ctx *ctx, void *out_dev, int out_dtype, const jl_weigh
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(ntok); cfg.blockDim = dim3(256); cfg.stream = s;
         cfg.attrs = at; cfg.numAttrs = nattr;
-        JL_CUDA(ctx, cudaLaunchKernelEx(&cfg, act_to_f16_kernel, x_dev, x_dtype, xh, inv_scale, k, split));
+        JL_CUDA(ctx, cudaLaunchKernelEx(&cfg, act_to_f16_kernel, x_dev, x_dtype, xh, inv_scale, k, split, (const int *)nullptr));
         ctx->st.launches++;
     }
 

@@ -65,6 +65,7 @@ struct jl_weight {
     // rows = one super-block of 16 rows per TMA copy (decode kernel).
     alignas(64) CUtensorMap map_sb16;
     bool has_map_sb16;
+    int emin, emax;         // MXFP4: smallest / largest e8m0 byte of a block that is not all zeros
 };
 
 struct jl_ctx {
@@ -114,6 +115,9 @@ int jl_launch_gemv(jl_ctx *ctx, float *out_dev, const jl_weight *w, int expert, 
 int jl_gemv_choice(jl_ctx *ctx, uint32_t type, int nrows, int k, int ntok, jl_choice *out);
 size_t jl_gemv_scratch_bytes(uint32_t type, int k, int ntok);
 int jl_grow_scratch(jl_ctx *ctx, size_t need);
+// ctx.cu: device copy of a host bank keyed on its address (as jl_matvec does for one matrix)
+int jl_resident_bank(jl_ctx *ctx, uint32_t type, const void *w, size_t w_bytes, int n_expert, int nrows, int k,
+                     jl_weight **out);
 
 // gemm_tc5.cu -- prefill kernels (tcgen05).
 int jl_launch_gemm_tc5(jl_ctx *ctx, void *out_dev, int out_dtype, const jl_weight *w, int expert,

@@ -1,11 +1,632 @@
-// Mixture-of-experts layer. Placeholder until the kernels land.
-#include "jl_internal.cuh"
+// Mixture-of-experts layer: State.moeBatch (engine/model/moe.go:502-760).
+//
+//   route    softmax over the router logits, lexicographic top-k (ties to the lowest id, a NaN
+//            never eligible), weights = score / (sum in SELECTION order + 1e-20) * scale
+//            (engine/nn/moetopk.go:316-385, internal/oracle/moe.go:197-359)
+//   sort     stable counting sort of the (token, slot) pairs by expert: the per-expert token
+//            lists, on the device, with no host round trip (the reference reads one word home
+//            per chunk to size its grouped launches, jit/gpu/tier/moegroup.go:10-19; here the
+//            grids are sized by the static worst case and surplus work units exit)
+//   gather   token rows -> expert order, as scaled f16 rows (act_to_f16_kernel with a row map)
+//   gate|up  grouped tcgen05 GEMM over the token lists: a 256-row tile is 128 gate rows + 128
+//            up rows of one expert against the same activation tile, so the epilogue holds g
+//            and u of one (row, token) in one thread and writes act(g, u)
+//   down     grouped tcgen05 GEMM, y = down_e act
+//   combine  out[token] += w_e y_e over the token's experts in ASCENDING expert id
+//            (engine/model/moe.go:127-134): a fixed order, so the result is bit-stable
+//
+// MXFP4 weights are exact in f16 (e2m1 times a power of two), activations are split hi + lo into
+// two f16 rows, accumulation is f32: the only rounding left is the f32 -> (hi, lo) split.
+#include "tc5.cuh"
 
-JL_EXPORT int jl_moe(jl_ctx *ctx, float *, const void *, int, const float *, int, const jl_moe_desc *,
-                     int32_t *, float *) {
-    return jl_set_err(ctx, JL_DECLINED, "mixture layer not built");
+#include <math.h>
+
+// ------------------------------------------------------------------ route
+
+// One warp per token. n_expert <= 256.
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const float *__restrict__ logits, const float *__restrict__ router_bias, int ntok, int n_expert,
+                 int top_k, int norm, float scale, int32_t *__restrict__ sel, float *__restrict__ wt) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int tok = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (tok >= ntok) return;
+    float lg[8], pr[8];
+    double mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const int e = lane + 32 * i;
+        lg[i] = e < n_expert ? logits[(size_t)tok * n_expert + e] + (router_bias ? router_bias[e] : 0.f) : -INFINITY;
+        if (lg[i] == lg[i]) mx = fmax(mx, (double)lg[i]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmax(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    double ex[8], sum = 0;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        ex[i] = (lane + 32 * i < n_expert) ? exp((double)lg[i] - mx) : 0.0;
+        sum += ex[i];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+#pragma unroll
+    for (int i = 0; i < 8; i++) pr[i] = (float)(ex[i] / sum);   // a NaN logit stays a NaN score
+
+    // k rounds of "largest score, lowest index"; picked entries are retired
+    bool taken[8] = {false, false, false, false, false, false, false, false};
+    float wsum = 0.f;
+    float mywt = 0.f;     // lane j keeps the j-th selected weight
+    int mysel = -1;
+    for (int j = 0; j < top_k; j++) {
+        float best = -INFINITY;
+        int bi = 0x7fffffff;
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const int e = lane + 32 * i;
+            if (e < n_expert && !taken[i] && pr[i] == pr[i] && (bi == 0x7fffffff || pr[i] > best)) { best = pr[i]; bi = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (oi != 0x7fffffff && (bi == 0x7fffffff || ob > best || (ob == best && oi < bi))) { best = ob; bi = oi; }
+        }
+        if (bi == 0x7fffffff) break;                 // nothing eligible is left
+#pragma unroll
+        for (int i = 0; i < 8; i++) if (lane + 32 * i == bi) taken[i] = true;
+        wsum += best;                                // selection order, one addition at a time
+        if (lane == j) { mywt = best; mysel = bi; }
+    }
+    const float div = norm ? wsum + 1e-20f : 1.f;
+    if (lane < top_k) {
+        float w = mywt / div;
+        if (scale != 0.f && scale != 1.f) w *= scale;
+        sel[(size_t)tok * top_k + lane] = mysel;
+        wt[(size_t)tok * top_k + lane] = w;
+    }
 }
-JL_EXPORT int jl_moe_dev(jl_ctx *ctx, float *, const void *, int, const float *, int, const jl_moe_desc *,
-                         int32_t *, float *, void *) {
-    return jl_set_err(ctx, JL_DECLINED, "mixture layer not built");
+
+// ------------------------------------------------------------------- sort
+
+// Stable counting sort of the pairs by expert; one CTA, thread e owns expert e.
+//   cnt[e], off[e] (exclusive), perm_tok[pos] = token of sorted position pos,
+//   pos_of[tok * k + slot] = sorted position of that pair (or -1 for an unfilled slot)
+__global__ void __launch_bounds__(256)
+moe_sort_kernel(const int32_t *__restrict__ sel, int npairs, int top_k, int n_expert, int *__restrict__ cnt,
+                int *__restrict__ off, int *__restrict__ perm_tok, int *__restrict__ pos_of) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    __shared__ int s_cnt[256], s_off[257];
+    const int e = threadIdx.x;
+    int c = 0;
+    if (e < n_expert)
+        for (int i = 0; i < npairs; i++) c += (sel[i] == e);
+    s_cnt[e] = e < n_expert ? c : 0;
+    __syncthreads();
+    if (e == 0) {
+        int acc = 0;
+        for (int i = 0; i < n_expert; i++) { s_off[i] = acc; acc += s_cnt[i]; }
+        s_off[n_expert] = acc;
+    }
+    __syncthreads();
+    if (e < n_expert) {
+        cnt[e] = s_cnt[e];
+        off[e] = s_off[e];
+        int p = s_off[e];
+        for (int i = 0; i < npairs; i++)
+            if (sel[i] == e) { perm_tok[p] = i / top_k; pos_of[i] = p; p++; }
+    }
+    if (e == 0) off[n_expert] = s_off[n_expert];
+    for (int i = e; i < npairs; i += blockDim.x)
+        if (sel[i] < 0 || sel[i] >= n_expert) pos_of[i] = -1;
+}
+
+// ---------------------------------------------------------------- combine
+
+// out[tok][d] += sum over the token's experts, ascending id, of wt * y[pos][d].
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(float *__restrict__ out, const float *__restrict__ y, const int32_t *__restrict__ sel,
+                   const float *__restrict__ wt, const int *__restrict__ pos_of, int ntok, int top_k, int hidden) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int tok = blockIdx.x;
+    __shared__ int s_pos[32];
+    __shared__ float s_w[32];
+    if (threadIdx.x == 0) {
+        // insertion sort of the slots by expert id (top_k <= 32)
+        int ids[32], n = 0;
+        for (int j = 0; j < top_k; j++) {
+            const int id = sel[(size_t)tok * top_k + j];
+            if (id < 0) continue;
+            int q = n++;
+            while (q > 0 && ids[q - 1] > id) { ids[q] = ids[q - 1]; s_pos[q] = s_pos[q - 1]; s_w[q] = s_w[q - 1]; q--; }
+            ids[q] = id; s_pos[q] = pos_of[(size_t)tok * top_k + j]; s_w[q] = wt[(size_t)tok * top_k + j];
+        }
+        for (int j = n; j < 32; j++) s_pos[j] = -1;
+    }
+    __syncthreads();
+    for (int d = threadIdx.x; d < hidden; d += blockDim.x) {
+        float acc = out[(size_t)tok * hidden + d];
+        for (int j = 0; j < top_k && s_pos[j] >= 0; j++) acc += s_w[j] * y[(size_t)s_pos[j] * hidden + d];
+        out[(size_t)tok * hidden + d] = acc;
+    }
+}
+
+// ------------------------------------------------------------ grouped GEMM
+
+struct moe_gemm_params {
+    int mode;                    // 0: gate|up -> act(g, u);  1: down
+    int n_expert, rows, k;       // rows, k of ONE expert matrix (mode 0: ffn x hidden; mode 1: hidden x ffn)
+    int row_tiles, max_tok_tiles, split, act;
+    const uint8_t *c0, *c1;      // code planes [E][rows][k/32][16]: mode 0 gate, up; mode 1 down, -
+    const uint8_t *e0, *e1;      // e8m0 planes [E][rows][e_stride]
+    int e_stride;
+    const float *b0, *b1;        // biases [E][rows] or NULL
+    const int *cnt, *off;        // pairs per expert, exclusive offsets (device)
+    const float *inv_scale;      // [npairs] scale of each gathered activation row
+    float *outp;                 // [npairs][rows] f32
+    int npairs;
+    int *status;
+};
+
+// Two e2m1 codes of one byte -> two f16 (low nibble first).
+__device__ __forceinline__ uint32_t e2m1x2_to_h2(uint32_t byte) {
+    uint32_t r;
+    asm("{\n\t.reg .b8 lo, hi;\n\t.reg .b16 t;\n\t"
+        "cvt.u16.u32 t, %1;\n\t"
+        "mov.b16 {lo, hi}, t;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %0, lo;\n\t}"
+        : "=r"(r)
+        : "r"(byte));
+    return r;
+}
+// 2^(e - 127) as an f16 pair (e in [104, 140]: exact, subnormal below 113).
+__device__ __forceinline__ uint32_t e8m0_to_h2(uint32_t e) {
+    const uint32_t h = e >= 113 ? (e - 112) << 10 : 1u << (e - 103);
+    return h | (h << 16);
+}
+__device__ __forceinline__ float moe_act(int kind, float g, float u) {
+    if (kind == JL_ACT_SWIGLU_OAI) {   // jit/gpu/kernels/actkind.go:13-39
+        const float x = fminf(g, 7.f), y = fmaxf(fminf(u, 7.f), -7.f);
+        return x / (1.f + expf(-1.702f * x)) * (y + 1.f);
+    }
+    return g / (1.f + expf(-g)) * u;   // SiLU gate
+}
+
+template <int NT, int SA, int SB>
+struct moe_smem {
+    static constexpr int ACC_COLS = TC5_MS * NT;
+    static constexpr int ACC_BUFS = ACC_COLS * 2 <= 512 ? 2 : 1;
+    static constexpr int B_BYTES = NT * TC5_KB * 2;
+    static constexpr int A_OFS = 0;
+    static constexpr int B_OFS = SA * TC5_MS * TC5_A_BYTES;
+    static constexpr int BAR_OFS = B_OFS + SB * B_BYTES;
+    static constexpr int NBARS = 2 * SA + 2 * SB + 4;
+    static constexpr int MISC_OFS = BAR_OFS + NBARS * 8;
+    static constexpr int TOTAL = MISC_OFS + 16 + 1024;
+};
+
+// Same roles as the dense prefill GEMM (gemm_tc5.cu): warps 0..3 epilogue, 4 TMA producer
+// (activation tiles of the expert's token list), 5 MMA issuer, 6..13 dequant (thread r owns tile
+// row r). A work unit is (expert, row tile, token tile); units past an expert's list exit.
+template <int NT, int SA, int SB>
+__global__ void __launch_bounds__(TC5_THREADS, 1)
+moe_gemm_kernel(const __grid_constant__ CUtensorMap xmap, const moe_gemm_params p) {
+    using L = moe_smem<NT, SA, SB>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const uint32_t sbase = smem_u32(smem);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + L::BAR_OFS);
+    uint64_t *a_full = bars, *a_empty = bars + SA, *b_full = bars + 2 * SA, *b_empty = b_full + SB;
+    uint64_t *acc_full = b_empty + SB, *acc_empty = acc_full + 2;
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + L::MISC_OFS);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L::MISC_OFS + 4);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int nkb = p.k / TC5_KB;
+    const int nunits = p.n_expert * p.row_tiles * p.max_tok_tiles;
+    const int mult = p.split ? 2 : 1;
+
+    if (tid == 0) {
+        for (int s = 0; s < SA; s++) { mbar_init(smem_u32(a_full + s), TC5_DQ_THREADS / 32); mbar_init(smem_u32(a_empty + s), 1); }
+        for (int s = 0; s < SB; s++) { mbar_init(smem_u32(b_full + s), 1); mbar_init(smem_u32(b_empty + s), 1); }
+        for (int i = 0; i < 2; i++) { mbar_init(smem_u32(acc_full + i), 1); mbar_init(smem_u32(acc_empty + i), 4); }
+        *abort_flag = 0;
+        mbar_init_fence();
+    }
+    if (warp == 5) tc5_alloc(smem_u32(const_cast<uint32_t *>(tmem_slot)), L::ACC_COLS * L::ACC_BUFS);
+    tc5_fence_before();
+    __syncthreads();
+    tc5_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");   // token lists and activation rows come from the kernels in front
+
+    // unit -> (expert, row tile, token tile); live iff the token tile starts inside the expert's list
+#define MOE_UNIT(u)                                                                   \
+    const int e = (u) / (p.row_tiles * p.max_tok_tiles);                              \
+    const int rt = ((u) / p.max_tok_tiles) % p.row_tiles, tt = (u) % p.max_tok_tiles; \
+    const int m_eff = p.cnt[e] * mult, col0 = p.off[e] * mult + tt * NT;              \
+    const bool live = tt * NT < m_eff;                                                \
+    (void)rt; (void)col0; (void)m_eff
+
+    if (warp == 4) {
+        if (lane == 0) {
+            uint32_t kb_it = 0;
+            bool ok = true;
+            for (int u = blockIdx.x; u < nunits && ok && !*abort_flag; u += gridDim.x) {
+                MOE_UNIT(u);
+                if (!live) continue;
+                for (int kb = 0; kb < nkb && ok; kb++, kb_it++) {
+                    const uint32_t s = kb_it % SB, ph = (kb_it / SB) & 1;
+                    if (kb_it >= (uint32_t)SB) ok = tc5_wait(smem_u32(b_empty + s), ph ^ 1, abort_flag);
+                    if (!ok) break;
+                    mbar_arrive_expect_tx(smem_u32(b_full + s), L::B_BYTES);
+                    tma_load_2d(sbase + L::B_OFS + s * L::B_BYTES, &xmap, kb * TC5_KB, col0, smem_u32(b_full + s));
+                }
+            }
+        }
+    } else if (warp == 5) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = tc5_idesc(TC5_M, NT);
+            uint32_t kb_it = 0, unit_it = 0;
+            bool ok = true;
+            for (int u = blockIdx.x; u < nunits && ok && !*abort_flag; u += gridDim.x) {
+                MOE_UNIT(u);
+                if (!live) continue;
+                const uint32_t ab = unit_it % L::ACC_BUFS, aph = (unit_it / L::ACC_BUFS) & 1;
+                if (unit_it >= (uint32_t)L::ACC_BUFS) ok = tc5_wait(smem_u32(acc_empty + ab), aph ^ 1, abort_flag);
+                if (!ok) break;
+                tc5_fence_after();
+                const uint32_t d_tmem = tmem_base + ab * L::ACC_COLS;
+                for (int kb = 0; kb < nkb && ok; kb++, kb_it++) {
+                    const uint32_t sa = kb_it % SA, pha = (kb_it / SA) & 1, s = kb_it % SB, ph = (kb_it / SB) & 1;
+                    ok = tc5_wait(smem_u32(a_full + sa), pha, abort_flag) && tc5_wait(smem_u32(b_full + s), ph, abort_flag);
+                    if (!ok) break;
+                    tc5_fence_after();
+                    const uint64_t bdesc = tc5_smem_desc(sbase + L::B_OFS + s * L::B_BYTES);
+#pragma unroll
+                    for (int ms = 0; ms < TC5_MS; ms++) {
+                        const uint64_t adesc = tc5_smem_desc(sbase + L::A_OFS + (sa * TC5_MS + ms) * TC5_A_BYTES);
+#pragma unroll
+                        for (int j = 0; j < TC5_KB / 16; j++)
+                            tc5_mma_f16(d_tmem + ms * NT, adesc + 2 * j, bdesc + 2 * j, idesc, (kb | j) != 0);
+                    }
+                    tc5_commit(smem_u32(a_empty + sa));
+                    tc5_commit(smem_u32(b_empty + s));
+                }
+                if (!ok) break;
+                tc5_commit(smem_u32(acc_full + ab));
+                unit_it++;
+            }
+        }
+    } else if (warp >= 6) {
+        // ---- dequant: thread r owns tile row r. mode 0: rows 0..127 gate, 128..255 up (same row index);
+        //      mode 1: 256 consecutive rows of down.
+        const int r = tid - 192;
+        const uint32_t swz = (uint32_t)(r & 7);
+        const int a_row_ofs = (r >> 7) * TC5_A_BYTES + (r & 127) * 128;
+        const int nblk = p.k / 32;
+        uint32_t kb_it = 0;
+        bool ok = true;
+        for (int u = blockIdx.x; u < nunits && ok && !*abort_flag; u += gridDim.x) {
+            MOE_UNIT(u);
+            if (!live) continue;
+            const bool second = p.mode == 0 && r >= 128;
+            const int row = p.mode == 0 ? min(rt * TC5_M + (r & 127), p.rows - 1) : min(rt * TC5_ROWS + r, p.rows - 1);
+            const size_t grow = (size_t)e * p.rows + row;
+            const uint8_t *codes = (second ? p.c1 : p.c0) + grow * nblk * 16;
+            const uint8_t *ebytes = (second ? p.e1 : p.e0) + grow * p.e_stride;
+            uint4 q0 = ldg_nc16(codes), q1 = ldg_nc16(codes + 16);
+            uint32_t ee = *reinterpret_cast<const uint16_t *>(ebytes);
+            for (int kb = 0; kb < nkb && ok; kb++, kb_it++) {
+                const uint32_t s = kb_it % SA, ph = (kb_it / SA) & 1;
+                const uint4 c0 = q0, c1 = q1;
+                const uint32_t e_lo = ee & 0xFF, e_hi = ee >> 8;
+                if (kb + 1 < nkb) {                     // next k-block's two blocks
+                    q0 = ldg_nc16(codes + (size_t)(kb + 1) * 32);
+                    q1 = ldg_nc16(codes + (size_t)(kb + 1) * 32 + 16);
+                    ee = *reinterpret_cast<const uint16_t *>(ebytes + 2 * (kb + 1));
+                }
+                if (kb_it >= (uint32_t)SA) ok = tc5_wait(smem_u32(a_empty + s), ph ^ 1, abort_flag);
+                if (!ok) break;
+                uint8_t *arow = smem + L::A_OFS + s * TC5_MS * TC5_A_BYTES + a_row_ofs;
+#pragma unroll
+                for (int b = 0; b < 2; b++) {           // block b of the k-block: k 32b..32b+31
+                    const uint4 cw = b ? c1 : c0;
+                    const uint32_t sc = e8m0_to_h2(b ? e_hi : e_lo);
+                    const uint32_t w[4] = {cw.x, cw.y, cw.z, cw.w};
+                    uint32_t lo[8], hi[8];              // f16 pairs: elements 2i,2i+1 (low nibbles) and 16+2i,16+2i+1
+#pragma unroll
+                    for (int i = 0; i < 8; i++) {       // bytes 2i, 2i+1: byte j holds element j (low) and j+16 (high)
+                        const uint32_t wv = w[i >> 1] >> (16 * (i & 1));
+                        const uint32_t a = e2m1x2_to_h2(wv & 0xFF), bb = e2m1x2_to_h2((wv >> 8) & 0xFF);
+                        lo[i] = hmul2u(__byte_perm(a, bb, 0x5410), sc);
+                        hi[i] = hmul2u(__byte_perm(a, bb, 0x7632), sc);
+                    }
+                    // chunks 4b..4b+3: elements 0-7, 8-15 (low nibbles), 16-23, 24-31 (high nibbles)
+                    *reinterpret_cast<uint4 *>(arow + (((uint32_t)(4 * b + 0) ^ swz) << 4)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                    *reinterpret_cast<uint4 *>(arow + (((uint32_t)(4 * b + 1) ^ swz) << 4)) = make_uint4(lo[4], lo[5], lo[6], lo[7]);
+                    *reinterpret_cast<uint4 *>(arow + (((uint32_t)(4 * b + 2) ^ swz) << 4)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                    *reinterpret_cast<uint4 *>(arow + (((uint32_t)(4 * b + 3) ^ swz) << 4)) = make_uint4(hi[4], hi[5], hi[6], hi[7]);
+                }
+                fence_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(a_full + s));
+            }
+        }
+    } else {
+        // ---- epilogue: warp w reads TMEM lanes 32w..32w+31 (tile rows), 32 token columns at a time
+        uint32_t unit_it = 0;
+        for (int u = blockIdx.x; u < nunits && !*abort_flag; u += gridDim.x) {
+            MOE_UNIT(u);
+            if (!live) continue;
+            const uint32_t ab = unit_it % L::ACC_BUFS, aph = (unit_it / L::ACC_BUFS) & 1;
+            if (!tc5_wait_relaxed(smem_u32(acc_full + ab), aph, abort_flag)) break;
+            tc5_fence_after();
+            const uint32_t tacc = tmem_base + ab * L::ACC_COLS + ((uint32_t)(warp * 32) << 16);
+            const int pos_end = p.off[e] + p.cnt[e];
+            const int nj = p.split ? 16 : 32;
+#pragma unroll 1
+            for (int c0 = 0; c0 < NT; c0 += 32) {
+                const int pos0 = (col0 + c0) / mult;
+                const int mypos = pos0 + (p.split ? (lane & 15) : lane);
+                const float myscale = mypos < pos_end ? __ldg(p.inv_scale + mypos) : 0.f;
+                if (p.mode == 0) {
+                    uint32_t vg[32], vu[32];
+                    tc5_ld32(tacc + c0, vg);
+                    tc5_ld32(tacc + NT + c0, vu);
+                    tc5_wait_ld();
+                    const int row = rt * TC5_M + warp * 32 + lane;
+                    const float bg = (p.b0 && row < p.rows) ? p.b0[(size_t)e * p.rows + row] : 0.f;
+                    const float bu = (p.b1 && row < p.rows) ? p.b1[(size_t)e * p.rows + row] : 0.f;
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        if (j >= nj) break;
+                        const int pos = pos0 + j;
+                        const float sc = __shfl_sync(0xffffffffu, myscale, j);
+                        const float g = (p.split ? __uint_as_float(vg[(2 * j) & 31]) + __uint_as_float(vg[(2 * j + 1) & 31])
+                                                 : __uint_as_float(vg[j])) * sc + bg;
+                        const float uu = (p.split ? __uint_as_float(vu[(2 * j) & 31]) + __uint_as_float(vu[(2 * j + 1) & 31])
+                                                  : __uint_as_float(vu[j])) * sc + bu;
+                        if (row < p.rows && pos < pos_end) p.outp[(size_t)pos * p.rows + row] = moe_act(p.act, g, uu);
+                    }
+                } else {
+#pragma unroll 1
+                    for (int ms = 0; ms < TC5_MS; ms++) {
+                        uint32_t v[32];
+                        tc5_ld32(tacc + ms * NT + c0, v);
+                        tc5_wait_ld();
+                        const int row = rt * TC5_ROWS + ms * TC5_M + warp * 32 + lane;
+                        const float bd = (p.b0 && row < p.rows) ? p.b0[(size_t)e * p.rows + row] : 0.f;
+#pragma unroll
+                        for (int j = 0; j < 32; j++) {
+                            if (j >= nj) break;
+                            const int pos = pos0 + j;
+                            const float sc = __shfl_sync(0xffffffffu, myscale, j);
+                            const float y = (p.split ? __uint_as_float(v[(2 * j) & 31]) + __uint_as_float(v[(2 * j + 1) & 31])
+                                                     : __uint_as_float(v[j])) * sc + bd;
+                            if (row < p.rows && pos < pos_end) p.outp[(size_t)pos * p.rows + row] = y;
+                        }
+                    }
+                }
+            }
+            tc5_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(acc_empty + ab));
+            unit_it++;
+        }
+    }
+#undef MOE_UNIT
+    tc5_fence_before();
+    __syncthreads();
+    if (tid == 0 && *abort_flag) atomicExch(p.status, 3);
+    if (warp == 5) {
+        tc5_fence_after();
+        tc5_dealloc(tmem_base, L::ACC_COLS * L::ACC_BUFS);
+    }
+}
+
+// --------------------------------------------------------------------- host
+
+static size_t al256(size_t n) { return (n + 255) & ~(size_t)255; }
+
+size_t jl_moe_scratch_bytes(int ntok, int n_expert, int top_k, int hidden, int ffn) {
+    const size_t np = (size_t)ntok * top_k;
+    return al256(np * 4) * 4 + al256((size_t)(n_expert + 1) * 4) * 2 +          // sel wt perm pos_of, cnt off
+           al256(np * 2 * hidden * 2) + al256(np * 4) * 2 +                       // xs (hi/lo), two scale arrays
+           al256(np * ffn * 4) + al256(np * 2 * ffn * 2) + al256(np * hidden * 4) + 4096;
+}
+
+template <int NT, int SA, int SB>
+static int moe_launch(jl_ctx *ctx, const CUtensorMap &xmap, const moe_gemm_params &p, cudaStream_t s, int nattr,
+                      cudaLaunchAttribute *at) {
+    using L = moe_smem<NT, SA, SB>;
+    static_assert(L::TOTAL <= 227 * 1024, "shared memory budget");
+    JL_CUDA(ctx, cudaFuncSetAttribute(moe_gemm_kernel<NT, SA, SB>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
+    const int units = p.n_expert * p.row_tiles * p.max_tok_tiles;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(units < ctx->sm_count ? units : ctx->sm_count); cfg.blockDim = dim3(TC5_THREADS);
+    cfg.dynamicSmemBytes = L::TOTAL; cfg.stream = s; cfg.attrs = at; cfg.numAttrs = nattr;
+    JL_CUDA(ctx, cudaLaunchKernelEx(&cfg, moe_gemm_kernel<NT, SA, SB>, xmap, p));
+    ctx->st.launches++;
+    return JL_OK;
+}
+
+// One grouped GEMM over the sorted activation rows `xs` ([npairs * mult][k] f16).
+static int moe_grouped(jl_ctx *ctx, moe_gemm_params p, const __half *xs, int ntok, cudaStream_t s, int nattr,
+                       cudaLaunchAttribute *at) {
+    const int mult = p.split ? 2 : 1;
+    const int nt = p.split ? 128 : 64;
+    p.max_tok_tiles = (ntok * mult + nt - 1) / nt;
+    CUtensorMap xmap;
+    if (!jl_make_tmap_2d(&xmap, xs, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (uint64_t)p.k, (uint64_t)p.npairs * mult,
+                         (uint64_t)p.k * 2, TC5_KB, nt, CU_TENSOR_MAP_SWIZZLE_128B))
+        return jl_set_err(ctx, JL_DECLINED, "the driver refused a tensor map for the mixture's activations");
+    return p.split ? moe_launch<128, 3, 6>(ctx, xmap, p, s, nattr, at) : moe_launch<64, 3, 8>(ctx, xmap, p, s, nattr, at);
+}
+
+static int moe_dev_locked(jl_ctx *ctx, float *out_dev, const void *h_dev, int h_dtype, const float *logits_dev, int ntok,
+                          const jl_moe_desc *d, int32_t *sel_out, float *wt_out, cudaStream_t s) {
+    const jl_weight *wg = (const jl_weight *)d->gate, *wu = (const jl_weight *)d->up, *wd = (const jl_weight *)d->down;
+    const int E = d->n_expert, K = d->top_k, H = d->hidden, F = d->ffn;
+    if (!wg || !wu || !wd || d->type != JL_TYPE_MXFP4 || wg->type != JL_TYPE_MXFP4 || wu->type != JL_TYPE_MXFP4 ||
+        wd->type != JL_TYPE_MXFP4)
+        return jl_set_err(ctx, JL_DECLINED, "the mixture layer serves MXFP4 expert banks");
+    if (E < 1 || E > 256 || K < 1 || K > 32 || K > E || H % 64 || F % 64 || ntok < 1)
+        return jl_set_err(ctx, JL_DECLINED, "mixture shape not served: %d experts, top %d, hidden %d, ffn %d", E, K, H, F);
+    if (wg->n_expert != E || wu->n_expert != E || wd->n_expert != E || wg->nrows != F || wg->k != H || wu->nrows != F ||
+        wu->k != H || wd->nrows != H || wd->k != F)
+        return jl_set_err(ctx, JL_EINVAL, "expert banks do not match the descriptor's shape");
+    if (wg->emin < 104 || wg->emax > 140 || wu->emin < 104 || wu->emax > 140 || wd->emin < 104 || wd->emax > 140)
+        return jl_set_err(ctx, JL_DECLINED, "an MXFP4 block scale lies outside 2^-23..2^13, where f16 holds the weights exactly");
+    const size_t need = jl_moe_scratch_bytes(ntok, E, K, H, F);
+    if (ctx->scratch_cap < need)
+        return jl_set_err(ctx, JL_ENOMEM, "mixture scratch holds %zu bytes, this layer needs %zu (jl_moe_reserve sizes it)",
+                          ctx->scratch_cap, need);
+    const int np = ntok * K;
+    uint8_t *sp = (uint8_t *)ctx->scratch;
+    auto take = [&](size_t n) { uint8_t *r = sp; sp += al256(n); return r; };
+    int32_t *sel = (int32_t *)take((size_t)np * 4);
+    float *wt = (float *)take((size_t)np * 4);
+    int *perm = (int *)take((size_t)np * 4), *pos_of = (int *)take((size_t)np * 4);
+    int *cnt = (int *)take((size_t)(E + 1) * 4), *off = (int *)take((size_t)(E + 1) * 4);
+    __half *xs = (__half *)take((size_t)np * 2 * H * 2);
+    float *xs_scale = (float *)take((size_t)np * 4), *as_scale = (float *)take((size_t)np * 4);
+    float *act = (float *)take((size_t)np * F * 4);
+    __half *as = (__half *)take((size_t)np * 2 * F * 2);
+    float *y = (float *)take((size_t)np * H * 4);
+    if (sel_out) sel = sel_out;
+    if (wt_out) wt = wt_out;
+
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    const int nattr = (ctx->opts.flags & JL_FLAG_NO_PDL) ? 0 : 1;
+    auto cfg_of = [&](dim3 g, dim3 b) { cudaLaunchConfig_t c = {}; c.gridDim = g; c.blockDim = b; c.stream = s; c.attrs = at; c.numAttrs = nattr; return c; };
+    {
+        cudaLaunchConfig_t c = cfg_of(dim3((ntok + 3) / 4), dim3(128));
+        JL_CUDA(ctx, cudaLaunchKernelEx(&c, moe_route_kernel, logits_dev, d->router_bias, ntok, E, K, d->norm, d->scale, sel, wt));
+        c = cfg_of(dim3(1), dim3(256));
+        JL_CUDA(ctx, cudaLaunchKernelEx(&c, moe_sort_kernel, (const int32_t *)sel, np, K, E, cnt, off, perm, pos_of));
+        ctx->st.launches += 2;
+    }
+    const int hsplit = h_dtype == JL_DT_F32 ? 1 : 0;
+    {
+        cudaLaunchConfig_t c = cfg_of(dim3(np), dim3(256));
+        JL_CUDA(ctx, cudaLaunchKernelEx(&c, act_to_f16_kernel, h_dev, h_dtype, xs, xs_scale, H, hsplit, (const int *)perm));
+        ctx->st.launches++;
+    }
+    moe_gemm_params p = {};
+    p.n_expert = E; p.cnt = cnt; p.off = off; p.npairs = np; p.status = ctx->dev_status; p.act = d->act;
+    // gate | up -> act
+    p.mode = 0; p.rows = F; p.k = H; p.row_tiles = (F + TC5_M - 1) / TC5_M; p.split = hsplit;
+    p.c0 = wg->data; p.c1 = wu->data; p.e0 = wg->scales; p.e1 = wu->scales; p.e_stride = wg->scale_stride;
+    p.b0 = d->gate_bias; p.b1 = d->up_bias; p.inv_scale = xs_scale; p.outp = act;
+    int rc = moe_grouped(ctx, p, xs, ntok, s, nattr, at);
+    if (rc) return rc;
+    {
+        cudaLaunchConfig_t c = cfg_of(dim3(np), dim3(256));
+        JL_CUDA(ctx, cudaLaunchKernelEx(&c, act_to_f16_kernel, (const void *)act, (int)JL_DT_F32, as, as_scale, F, 1, (const int *)nullptr));
+        ctx->st.launches++;
+    }
+    // down
+    p.mode = 1; p.rows = H; p.k = F; p.row_tiles = (H + TC5_ROWS - 1) / TC5_ROWS; p.split = 1;
+    p.c0 = wd->data; p.c1 = nullptr; p.e0 = wd->scales; p.e1 = nullptr; p.e_stride = wd->scale_stride;
+    p.b0 = d->down_bias; p.b1 = nullptr; p.inv_scale = as_scale; p.outp = y;
+    if ((rc = moe_grouped(ctx, p, as, ntok, s, nattr, at))) return rc;
+    {
+        cudaLaunchConfig_t c = cfg_of(dim3(ntok), dim3(256));
+        JL_CUDA(ctx, cudaLaunchKernelEx(&c, moe_combine_kernel, out_dev, (const float *)y, (const int32_t *)sel, (const float *)wt,
+                                        (const int *)pos_of, ntok, K, H));
+        ctx->st.launches++;
+    }
+    JL_CUDA(ctx, cudaGetLastError());
+    return JL_OK;
+}
+
+JL_EXPORT int jl_moe_reserve(jl_ctx *ctx, int ntok, int n_expert, int top_k, int hidden, int ffn) {
+    if (!ctx || ntok < 1 || n_expert < 1 || top_k < 1 || hidden < 1 || ffn < 1) return JL_EINVAL;
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    JL_CUDA(ctx, cudaSetDevice(ctx->device));
+    return jl_grow_scratch(ctx, jl_moe_scratch_bytes(ntok, n_expert, top_k, hidden, ffn));
+}
+
+JL_EXPORT int jl_moe_dev(jl_ctx *ctx, float *out_dev, const void *h_dev, int h_dtype, const float *logits_dev, int ntok,
+                         const jl_moe_desc *desc, int32_t *sel_out_dev, float *wt_out_dev, void *stream) {
+    if (!ctx || !out_dev || !h_dev || !logits_dev || !desc) return JL_EINVAL;
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    if (ctx->unhealthy) return jl_set_err(ctx, JL_ECUDA, "context is unhealthy after an earlier CUDA error");
+    JL_CUDA(ctx, cudaSetDevice(ctx->device));
+    int rc = moe_dev_locked(ctx, out_dev, h_dev, h_dtype, logits_dev, ntok, desc, sel_out_dev, wt_out_dev, (cudaStream_t)stream);
+    if (rc == JL_OK) ctx->st.served++;
+    return rc;
+}
+
+// Host buffers in and out; the banks are uploaded (and kept, keyed on their host address) on first use.
+JL_EXPORT int jl_moe(jl_ctx *ctx, float *out, const void *h, int h_dtype, const float *logits, int ntok,
+                     const jl_moe_desc *desc, int32_t *sel_out, float *wt_out) {
+    if (!ctx || !out || !h || !logits || !desc) return JL_EINVAL;
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    if (ctx->unhealthy) return jl_set_err(ctx, JL_ECUDA, "context is unhealthy after an earlier CUDA error");
+    JL_CUDA(ctx, cudaSetDevice(ctx->device));
+    const int E = desc->n_expert, K = desc->top_k, H = desc->hidden, F = desc->ffn;
+    if (desc->type != JL_TYPE_MXFP4 || E < 1 || K < 1 || H < 64 || F < 64 || H % 64 || F % 64 || ntok < 1)
+        return jl_set_err(ctx, JL_DECLINED, "the mixture layer serves MXFP4 banks with hidden and ffn multiples of 64");
+    jl_weight *wg = nullptr, *wu = nullptr, *wd = nullptr;
+    int rc;
+    if ((rc = jl_resident_bank(ctx, desc->type, desc->gate, desc->gate_bytes, E, F, H, &wg))) return rc;
+    if ((rc = jl_resident_bank(ctx, desc->type, desc->up, desc->up_bytes, E, F, H, &wu))) return rc;
+    if ((rc = jl_resident_bank(ctx, desc->type, desc->down, desc->down_bytes, E, H, F, &wd))) return rc;
+    if ((rc = jl_grow_scratch(ctx, jl_moe_scratch_bytes(ntok, E, K, H, F)))) return rc;
+
+    const size_t hb = (size_t)ntok * H * (h_dtype == JL_DT_F32 ? 4 : 2), ob = (size_t)ntok * H * 4;
+    const size_t np = (size_t)ntok * K;
+    uint8_t *buf = nullptr;   // one temporary block: h | logits | out | sel | wt | biases
+    const size_t nb_g = desc->gate_bias ? (size_t)E * F * 4 : 0, nb_u = desc->up_bias ? (size_t)E * F * 4 : 0;
+    const size_t nb_d = desc->down_bias ? (size_t)E * H * 4 : 0, nb_r = desc->router_bias ? (size_t)E * 4 : 0;
+    const size_t total = al256(hb) + al256((size_t)ntok * E * 4) + al256(ob) + al256(np * 4) * 2 + al256(nb_g) +
+                         al256(nb_u) + al256(nb_d) + al256(nb_r);
+    cudaError_t ce = cudaMalloc(&buf, total);
+    if (ce != cudaSuccess) { cudaGetLastError(); return jl_set_err(ctx, JL_ENOMEM, "cudaMalloc(%zu): %s", total, cudaGetErrorString(ce)); }
+    uint8_t *sp = buf;
+    auto take = [&](size_t n) { uint8_t *r = sp; sp += al256(n); return r; };
+    void *h_d = take(hb);
+    float *lg_d = (float *)take((size_t)ntok * E * 4), *out_d = (float *)take(ob);
+    int32_t *sel_d = (int32_t *)take(np * 4);
+    float *wt_d = (float *)take(np * 4);
+    float *bg = (float *)take(nb_g), *bu = (float *)take(nb_u), *bd = (float *)take(nb_d), *br = (float *)take(nb_r);
+    cudaStream_t s = ctx->stream;
+    ce = cudaMemcpyAsync(h_d, h, hb, cudaMemcpyHostToDevice, s);
+    if (ce == cudaSuccess) ce = cudaMemcpyAsync(lg_d, logits, (size_t)ntok * E * 4, cudaMemcpyHostToDevice, s);
+    if (ce == cudaSuccess) ce = cudaMemcpyAsync(out_d, out, ob, cudaMemcpyHostToDevice, s);   // the layer ADDS into out
+    if (ce == cudaSuccess && nb_g) ce = cudaMemcpyAsync(bg, desc->gate_bias, nb_g, cudaMemcpyHostToDevice, s);
+    if (ce == cudaSuccess && nb_u) ce = cudaMemcpyAsync(bu, desc->up_bias, nb_u, cudaMemcpyHostToDevice, s);
+    if (ce == cudaSuccess && nb_d) ce = cudaMemcpyAsync(bd, desc->down_bias, nb_d, cudaMemcpyHostToDevice, s);
+    if (ce == cudaSuccess && nb_r) ce = cudaMemcpyAsync(br, desc->router_bias, nb_r, cudaMemcpyHostToDevice, s);
+    rc = JL_OK;
+    if (ce == cudaSuccess) {
+        jl_moe_desc dd = *desc;
+        dd.gate = wg; dd.up = wu; dd.down = wd;
+        dd.gate_bias = nb_g ? bg : nullptr; dd.up_bias = nb_u ? bu : nullptr; dd.down_bias = nb_d ? bd : nullptr;
+        dd.router_bias = nb_r ? br : nullptr;
+        rc = moe_dev_locked(ctx, out_d, h_d, h_dtype, lg_d, ntok, &dd, sel_d, wt_d, s);
+    }
+    if (ce == cudaSuccess && rc == JL_OK) ce = cudaMemcpyAsync(out, out_d, ob, cudaMemcpyDeviceToHost, s);
+    if (ce == cudaSuccess && rc == JL_OK && sel_out) ce = cudaMemcpyAsync(sel_out, sel_d, np * 4, cudaMemcpyDeviceToHost, s);
+    if (ce == cudaSuccess && rc == JL_OK && wt_out) ce = cudaMemcpyAsync(wt_out, wt_d, np * 4, cudaMemcpyDeviceToHost, s);
+    int dstat = 0;
+    if (ce == cudaSuccess) ce = cudaMemcpyAsync(&dstat, ctx->dev_status, sizeof(int), cudaMemcpyDeviceToHost, s);
+    if (ce == cudaSuccess) ce = cudaStreamSynchronize(s);
+    cudaFree(buf);
+    if (ce != cudaSuccess) {
+        ctx->unhealthy = true;
+        return jl_set_err(ctx, JL_ECUDA, "mixture layer: %s", cudaGetErrorString(ce));
+    }
+    if (rc) return rc;
+    if (dstat) {
+        cudaMemset(ctx->dev_status, 0, sizeof(int));
+        return jl_set_err(ctx, JL_ETIMEDOUT, "a bounded device-side wait ran out (code %d)", dstat);
+    }
+    ctx->st.served++;
+    return JL_OK;
 }

@@ -177,9 +177,25 @@ class Device:
 
     def Moe(self, out, h, logits, ntok: int, desc: MoeDesc, sel_out=None, wt_out=None) -> bool:
         """State.moeBatch on host arrays. False = declined."""
-        self.last_status = self.lib.jl_moe(self.ctx, _ptr(out), _ptr(h), _dtype_code(h), _ptr(logits), ntok,
+        h_dtype = _lib.DT_BF16 if str(h.dtype) == "uint16" else _dtype_code(h)   # uint16 arrays carry bf16 bits
+        self.last_status = self.lib.jl_moe(self.ctx, _ptr(out), _ptr(h), h_dtype, _ptr(logits), ntok,
                                            C.byref(desc), _ptr(sel_out), _ptr(wt_out))
         return self.last_status == _lib.OK
+
+    def MoeHost(self, out, h, logits, gate, up, down, n_expert: int, top_k: int, hidden: int, ffn: int,
+                act: int = _lib.ACT_SILU, norm: bool = True, scale: float = 1.0, t: int = _lib.MXFP4,
+                gate_bias=None, up_bias=None, down_bias=None, router_bias=None, sel_out=None, wt_out=None) -> bool:
+        """State.moeBatch with every operand in host memory (numpy). out is ADDED to. False = declined."""
+        ntok = logits.shape[0]
+        d = MoeDesc(struct_size=C.sizeof(MoeDesc), type=t, n_expert=n_expert, top_k=top_k, hidden=hidden, ffn=ffn,
+                    act=act, norm=int(norm), scale=scale, gate=_ptr(gate), up=_ptr(up), down=_ptr(down),
+                    gate_bytes=_nbytes(gate), up_bytes=_nbytes(up), down_bytes=_nbytes(down),
+                    gate_bias=_ptr(gate_bias), up_bias=_ptr(up_bias), down_bias=_ptr(down_bias),
+                    router_bias=_ptr(router_bias))
+        return self.Moe(out, h, logits, ntok, d, sel_out, wt_out)
+
+    def MoeReserve(self, ntok: int, n_expert: int, top_k: int, hidden: int, ffn: int) -> None:
+        self._check(self.lib.jl_moe_reserve(self.ctx, ntok, n_expert, top_k, hidden, ffn))
 
     def MoeDev(self, out, h, logits, ntok: int, desc: MoeDesc, sel_out=None, wt_out=None, stream: int = 0) -> None:
         self._check(self.lib.jl_moe_dev(self.ctx, _ptr(out), _ptr(h), _dtype_code(h), _ptr(logits), ntok,
