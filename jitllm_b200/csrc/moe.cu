@@ -88,37 +88,52 @@ moe_route_kernel(const float *__restrict__ logits, const float *__restrict__ rou
 
 // ------------------------------------------------------------------- sort
 
-// Stable counting sort of the pairs by expert; one CTA, thread e owns expert e.
+// Stable counting sort of the pairs by expert, one CTA of 256 threads.
 //   cnt[e], off[e] (exclusive), perm_tok[pos] = token of sorted position pos,
 //   pos_of[tok * k + slot] = sorted position of that pair (or -1 for an unfilled slot)
+// Counts by shared-memory atomics; placement by ONE warp walking the pairs 32 at a time in
+// order, ranking equal ids inside a chunk with __match_any_sync, so positions keep token order.
 __global__ void __launch_bounds__(256)
 moe_sort_kernel(const int32_t *__restrict__ sel, int npairs, int top_k, int n_expert, int *__restrict__ cnt,
                 int *__restrict__ off, int *__restrict__ perm_tok, int *__restrict__ pos_of) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    __shared__ int s_cnt[256], s_off[257];
-    const int e = threadIdx.x;
-    int c = 0;
-    if (e < n_expert)
-        for (int i = 0; i < npairs; i++) c += (sel[i] == e);
-    s_cnt[e] = e < n_expert ? c : 0;
+    __shared__ int s_cnt[256], s_base[257];
+    const int tid = threadIdx.x;
+    s_cnt[tid] = 0;
     __syncthreads();
-    if (e == 0) {
+    for (int i = tid; i < npairs; i += blockDim.x) {
+        const int id = sel[i];
+        if (id >= 0 && id < n_expert) atomicAdd(&s_cnt[id], 1);
+        else pos_of[i] = -1;
+    }
+    __syncthreads();
+    if (tid == 0) {
         int acc = 0;
-        for (int i = 0; i < n_expert; i++) { s_off[i] = acc; acc += s_cnt[i]; }
-        s_off[n_expert] = acc;
+        for (int i = 0; i < n_expert; i++) { s_base[i] = acc; acc += s_cnt[i]; }
+        s_base[n_expert] = acc;
     }
     __syncthreads();
-    if (e < n_expert) {
-        cnt[e] = s_cnt[e];
-        off[e] = s_off[e];
-        int p = s_off[e];
-        for (int i = 0; i < npairs; i++)
-            if (sel[i] == e) { perm_tok[p] = i / top_k; pos_of[i] = p; p++; }
+    if (tid <= n_expert) off[tid] = s_base[tid];
+    if (tid < n_expert) cnt[tid] = s_cnt[tid];
+    __syncthreads();
+    if (tid < 32) {
+        for (int c = 0; c < npairs; c += 32) {
+            const int i = c + tid;
+            const int id = i < npairs ? sel[i] : -1;
+            const bool ok = id >= 0 && id < n_expert;
+            const unsigned same = __match_any_sync(0xffffffffu, ok ? id : -1 - tid);   // invalid ids match nobody
+            if (ok) {
+                const int rank = __popc(same & ((1u << tid) - 1));
+                const int p = s_base[id] + rank;
+                perm_tok[p] = i / top_k;
+                pos_of[i] = p;
+            }
+            __syncwarp();
+            if (ok && (same & ((1u << tid) - 1)) == 0) s_base[id] += __popc(same);     // the chunk's first lane of this id
+            __syncwarp();
+        }
     }
-    if (e == 0) off[n_expert] = s_off[n_expert];
-    for (int i = e; i < npairs; i += blockDim.x)
-        if (sel[i] < 0 || sel[i] >= n_expert) pos_of[i] = -1;
 }
 
 // ---------------------------------------------------------------- combine
@@ -145,10 +160,17 @@ moe_combine_kernel(float *__restrict__ out, const float *__restrict__ y, const i
         for (int j = n; j < 32; j++) s_pos[j] = -1;
     }
     __syncthreads();
-    for (int d = threadIdx.x; d < hidden; d += blockDim.x) {
-        float acc = out[(size_t)tok * hidden + d];
-        for (int j = 0; j < top_k && s_pos[j] >= 0; j++) acc += s_w[j] * y[(size_t)s_pos[j] * hidden + d];
-        out[(size_t)tok * hidden + d] = acc;
+    int n = 0;
+    while (n < top_k && s_pos[n] >= 0) n++;
+    float4 *o4 = reinterpret_cast<float4 *>(out + (size_t)tok * hidden);   // hidden is a multiple of 64
+    for (int d = threadIdx.x; d < hidden / 4; d += blockDim.x) {
+        float4 acc = o4[d];
+        for (int j = 0; j < n; j++) {                                       // ascending expert id
+            const float4 v = __ldg(reinterpret_cast<const float4 *>(y + (size_t)s_pos[j] * hidden) + d);
+            const float w = s_w[j];
+            acc.x += w * v.x; acc.y += w * v.y; acc.z += w * v.z; acc.w += w * v.w;
+        }
+        o4[d] = acc;
     }
 }
 
@@ -243,8 +265,9 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap xmap, const moe_gemm_params 
 
     // unit -> (expert, row tile, token tile); live iff the token tile starts inside the expert's list
 #define MOE_UNIT(u)                                                                   \
-    const int e = (u) / (p.row_tiles * p.max_tok_tiles);                              \
-    const int rt = ((u) / p.max_tok_tiles) % p.row_tiles, tt = (u) % p.max_tok_tiles; \
+    const int tt = (u) / (p.n_expert * p.row_tiles);   /* slowest: the live units (first token    \
+                                                          tiles) are contiguous, spread over CTAs */ \
+    const int e = ((u) / p.row_tiles) % p.n_expert, rt = (u) % p.row_tiles;           \
     const int m_eff = p.cnt[e] * mult, col0 = p.off[e] * mult + tt * NT;              \
     const bool live = tt * NT < m_eff;                                                \
     (void)rt; (void)col0; (void)m_eff
@@ -316,16 +339,31 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap xmap, const moe_gemm_params 
             const size_t grow = (size_t)e * p.rows + row;
             const uint8_t *codes = (second ? p.c1 : p.c0) + grow * nblk * 16;
             const uint8_t *ebytes = (second ? p.e1 : p.e0) + grow * p.e_stride;
-            uint4 q0 = ldg_nc16(codes), q1 = ldg_nc16(codes + 16);
-            uint32_t ee = *reinterpret_cast<const uint16_t *>(ebytes);
-            for (int kb = 0; kb < nkb && ok; kb++, kb_it++) {
+            // raw codes run four k-blocks (256 k) ahead of their use, in registers
+            uint4 qc[8], qn[8];
+            uint32_t ec[4], en[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                qc[2 * j] = qc[2 * j + 1] = make_uint4(0, 0, 0, 0); ec[j] = 0x7F7F;
+                if (j < nkb) {
+                    qc[2 * j] = ldg_nc16(codes + (size_t)j * 32);
+                    qc[2 * j + 1] = ldg_nc16(codes + (size_t)j * 32 + 16);
+                    ec[j] = *reinterpret_cast<const uint16_t *>(ebytes + 2 * j);
+                }
+            }
+            for (int kb0 = 0; kb0 < nkb && ok; kb0 += 4) {
+#pragma unroll
+              for (int j = 0; j < 4; j++) {
+                const int kb = kb0 + j;
+                if (kb >= nkb) break;
                 const uint32_t s = kb_it % SA, ph = (kb_it / SA) & 1;
-                const uint4 c0 = q0, c1 = q1;
-                const uint32_t e_lo = ee & 0xFF, e_hi = ee >> 8;
-                if (kb + 1 < nkb) {                     // next k-block's two blocks
-                    q0 = ldg_nc16(codes + (size_t)(kb + 1) * 32);
-                    q1 = ldg_nc16(codes + (size_t)(kb + 1) * 32 + 16);
-                    ee = *reinterpret_cast<const uint16_t *>(ebytes + 2 * (kb + 1));
+                const uint4 c0 = qc[2 * j], c1 = qc[2 * j + 1];
+                const uint32_t e_lo = ec[j] & 0xFF, e_hi = ec[j] >> 8;
+                qn[2 * j] = qn[2 * j + 1] = make_uint4(0, 0, 0, 0); en[j] = 0x7F7F;
+                if (kb + 4 < nkb) {
+                    qn[2 * j] = ldg_nc16(codes + (size_t)(kb + 4) * 32);
+                    qn[2 * j + 1] = ldg_nc16(codes + (size_t)(kb + 4) * 32 + 16);
+                    en[j] = *reinterpret_cast<const uint16_t *>(ebytes + 2 * (kb + 4));
                 }
                 if (kb_it >= (uint32_t)SA) ok = tc5_wait(smem_u32(a_empty + s), ph ^ 1, abort_flag);
                 if (!ok) break;
@@ -352,6 +390,12 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap xmap, const moe_gemm_params 
                 fence_async_smem();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(a_full + s));
+                kb_it++;
+              }
+#pragma unroll
+              for (int j = 0; j < 8; j++) qc[j] = qn[j];
+#pragma unroll
+              for (int j = 0; j < 4; j++) ec[j] = en[j];
             }
         }
     } else {
