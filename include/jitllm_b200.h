@@ -171,6 +171,17 @@ typedef struct jl_moe_desc {
 int jl_moe(jl_ctx *ctx, float *out, const void *h, int h_dtype, const float *logits, int ntok,
            const jl_moe_desc *desc, int32_t *sel_out, float *wt_out);
 
+/* The router alone (softmax, lexicographic top-k, renormalised weights), device pointers:
+ * engine/nn/moetopk.go:316-385. sel/wt are [ntok][top_k] in selection order. */
+int jl_moe_route_dev(jl_ctx *ctx, const float *logits_dev, int ntok, const jl_moe_desc *desc,
+                     int32_t *sel_out_dev, float *wt_out_dev, void *stream);
+/* The experts alone over rows that are ALREADY routed: y[i] = down_e(act(gate_e h_i, up_e h_i)) with
+ * e = expert_ids[i] (local index into the banks), written in the caller's row order. This is what an
+ * expert-parallel rank runs on the rows it received (cf. LayerWeights.HostExpertsRows,
+ * engine/nn/device.go:275-279). Scratch as jl_moe_reserve(nrows, n_expert, 1, hidden, ffn). */
+int jl_moe_experts_dev(jl_ctx *ctx, float *y_dev, const void *h_dev, int h_dtype, const int32_t *expert_ids_dev,
+                       int nrows, const jl_moe_desc *desc, void *stream);
+
 /* Pre-size the mixture layer's scratch (token lists, gathered rows, intermediates) so that
  * jl_moe_dev never needs more than it finds. */
 int jl_moe_reserve(jl_ctx *ctx, int ntok, int n_expert, int top_k, int hidden, int ffn);

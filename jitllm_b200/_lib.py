@@ -67,6 +67,8 @@ SYMBOLS = {
     "jl_forget": (_I, [_VP, _VP, _SZ]),
     "jl_matmul": (_I, [_VP, _VP, _I, _U32, _VP, _SZ, _VP, _I, _I, _I, _I]),
     "jl_moe": (_I, [_VP, _VP, _VP, _I, _VP, _I, C.POINTER(MoeDesc), _VP, _VP]),
+    "jl_moe_route_dev": (_I, [_VP, _VP, _I, C.POINTER(MoeDesc), _VP, _VP, _VP]),
+    "jl_moe_experts_dev": (_I, [_VP, _VP, _VP, _I, _VP, _I, C.POINTER(MoeDesc), _VP]),
     "jl_moe_reserve": (_I, [_VP, _I, _I, _I, _I, _I]),
     "jl_select": (_I, [_VP, _U32, _I, _I, _I, C.POINTER(Choice)]),
     "jl_unpack": (_I, [_U32, _VP, _SZ, _VP, _VP, _VP, _VP, _VP]),

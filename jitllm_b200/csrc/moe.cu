@@ -187,6 +187,7 @@ struct moe_gemm_params {
     const int *cnt, *off;        // pairs per expert, exclusive offsets (device)
     const float *inv_scale;      // [npairs] scale of each gathered activation row
     float *outp;                 // [npairs][rows] f32
+    const int *out_rowmap;       // mode 1: row of outp that sorted position pos is written to (NULL: pos)
     int npairs;
     int *status;
 };
@@ -449,7 +450,8 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap xmap, const moe_gemm_params 
                             const float sc = __shfl_sync(0xffffffffu, myscale, j);
                             const float y = (p.split ? __uint_as_float(v[(2 * j) & 31]) + __uint_as_float(v[(2 * j + 1) & 31])
                                                      : __uint_as_float(v[j])) * sc + bd;
-                            if (row < p.rows && pos < pos_end) p.outp[(size_t)pos * p.rows + row] = y;
+                            if (row < p.rows && pos < pos_end)
+                                p.outp[(size_t)(p.out_rowmap ? p.out_rowmap[pos] : pos) * p.rows + row] = y;
                         }
                     }
                 }
@@ -509,10 +511,14 @@ static int moe_grouped(jl_ctx *ctx, moe_gemm_params p, const __half *xs, int nto
     return p.split ? moe_launch<128, 3, 6>(ctx, xmap, p, s, nattr, at) : moe_launch<64, 3, 8>(ctx, xmap, p, s, nattr, at);
 }
 
+// given_ids != NULL: no router and no combine -- row i goes through expert given_ids[i] and
+// out_dev[i] = down(act(gate h_i, up h_i)) is WRITTEN in the caller's row order (the expert-parallel
+// path: rows arrive from other ranks already routed). Otherwise the whole layer, ADDED into out_dev.
 static int moe_dev_locked(jl_ctx *ctx, float *out_dev, const void *h_dev, int h_dtype, const float *logits_dev, int ntok,
-                          const jl_moe_desc *d, int32_t *sel_out, float *wt_out, cudaStream_t s) {
+                          const jl_moe_desc *d, int32_t *sel_out, float *wt_out, cudaStream_t s,
+                          const int32_t *given_ids = nullptr) {
     const jl_weight *wg = (const jl_weight *)d->gate, *wu = (const jl_weight *)d->up, *wd = (const jl_weight *)d->down;
-    const int E = d->n_expert, K = d->top_k, H = d->hidden, F = d->ffn;
+    const int E = d->n_expert, K = given_ids ? 1 : d->top_k, H = d->hidden, F = d->ffn;
     if (!wg || !wu || !wd || d->type != JL_TYPE_MXFP4 || wg->type != JL_TYPE_MXFP4 || wu->type != JL_TYPE_MXFP4 ||
         wd->type != JL_TYPE_MXFP4)
         return jl_set_err(ctx, JL_DECLINED, "the mixture layer serves MXFP4 expert banks");
@@ -541,6 +547,7 @@ static int moe_dev_locked(jl_ctx *ctx, float *out_dev, const void *h_dev, int h_
     float *y = (float *)take((size_t)np * H * 4);
     if (sel_out) sel = sel_out;
     if (wt_out) wt = wt_out;
+    if (given_ids) sel = const_cast<int32_t *>(given_ids);
 
     cudaLaunchAttribute at[1];
     at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -549,10 +556,13 @@ static int moe_dev_locked(jl_ctx *ctx, float *out_dev, const void *h_dev, int h_
     auto cfg_of = [&](dim3 g, dim3 b) { cudaLaunchConfig_t c = {}; c.gridDim = g; c.blockDim = b; c.stream = s; c.attrs = at; c.numAttrs = nattr; return c; };
     {
         cudaLaunchConfig_t c = cfg_of(dim3((ntok + 3) / 4), dim3(128));
-        JL_CUDA(ctx, cudaLaunchKernelEx(&c, moe_route_kernel, logits_dev, d->router_bias, ntok, E, K, d->norm, d->scale, sel, wt));
+        if (!given_ids) {
+            JL_CUDA(ctx, cudaLaunchKernelEx(&c, moe_route_kernel, logits_dev, d->router_bias, ntok, E, K, d->norm, d->scale, sel, wt));
+            ctx->st.launches++;
+        }
         c = cfg_of(dim3(1), dim3(256));
         JL_CUDA(ctx, cudaLaunchKernelEx(&c, moe_sort_kernel, (const int32_t *)sel, np, K, E, cnt, off, perm, pos_of));
-        ctx->st.launches += 2;
+        ctx->st.launches++;
     }
     const int hsplit = h_dtype == JL_DT_F32 ? 1 : 0;
     {
@@ -577,8 +587,9 @@ static int moe_dev_locked(jl_ctx *ctx, float *out_dev, const void *h_dev, int h_
     p.mode = 1; p.rows = H; p.k = F; p.row_tiles = (H + TC5_ROWS - 1) / TC5_ROWS; p.split = 1;
     p.c0 = wd->data; p.c1 = nullptr; p.e0 = wd->scales; p.e1 = nullptr; p.e_stride = wd->scale_stride;
     p.b0 = d->down_bias; p.b1 = nullptr; p.inv_scale = as_scale; p.outp = y;
+    if (given_ids) { p.outp = out_dev; p.out_rowmap = perm; }   // top_k = 1: perm[pos] is the caller's row
     if ((rc = moe_grouped(ctx, p, as, ntok, s, nattr, at))) return rc;
-    {
+    if (!given_ids) {
         cudaLaunchConfig_t c = cfg_of(dim3(ntok), dim3(256));
         JL_CUDA(ctx, cudaLaunchKernelEx(&c, moe_combine_kernel, out_dev, (const float *)y, (const int32_t *)sel, (const float *)wt,
                                         (const int *)pos_of, ntok, K, H));
@@ -602,6 +613,34 @@ JL_EXPORT int jl_moe_dev(jl_ctx *ctx, float *out_dev, const void *h_dev, int h_d
     if (ctx->unhealthy) return jl_set_err(ctx, JL_ECUDA, "context is unhealthy after an earlier CUDA error");
     JL_CUDA(ctx, cudaSetDevice(ctx->device));
     int rc = moe_dev_locked(ctx, out_dev, h_dev, h_dtype, logits_dev, ntok, desc, sel_out_dev, wt_out_dev, (cudaStream_t)stream);
+    if (rc == JL_OK) ctx->st.served++;
+    return rc;
+}
+
+JL_EXPORT int jl_moe_route_dev(jl_ctx *ctx, const float *logits_dev, int ntok, const jl_moe_desc *desc,
+                               int32_t *sel_out_dev, float *wt_out_dev, void *stream) {
+    if (!ctx || !logits_dev || !desc || !sel_out_dev || !wt_out_dev || ntok < 1) return JL_EINVAL;
+    if (desc->n_expert < 1 || desc->n_expert > 256 || desc->top_k < 1 || desc->top_k > 32 || desc->top_k > desc->n_expert)
+        return JL_EINVAL;
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    JL_CUDA(ctx, cudaSetDevice(ctx->device));
+    moe_route_kernel<<<(ntok + 3) / 4, 128, 0, (cudaStream_t)stream>>>(logits_dev, desc->router_bias, ntok, desc->n_expert,
+                                                                     desc->top_k, desc->norm, desc->scale, sel_out_dev,
+                                                                     wt_out_dev);
+    ctx->st.launches++;
+    JL_CUDA(ctx, cudaGetLastError());
+    return JL_OK;
+}
+
+JL_EXPORT int jl_moe_experts_dev(jl_ctx *ctx, float *y_dev, const void *h_dev, int h_dtype, const int32_t *expert_ids_dev,
+                                 int nrows, const jl_moe_desc *desc, void *stream) {
+    if (!ctx || !y_dev || !h_dev || !expert_ids_dev || !desc) return JL_EINVAL;
+    if (nrows < 1) return JL_OK;
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    if (ctx->unhealthy) return jl_set_err(ctx, JL_ECUDA, "context is unhealthy after an earlier CUDA error");
+    JL_CUDA(ctx, cudaSetDevice(ctx->device));
+    int rc = moe_dev_locked(ctx, y_dev, h_dev, h_dtype, nullptr, nrows, desc, nullptr, nullptr, (cudaStream_t)stream,
+                            expert_ids_dev);
     if (rc == JL_OK) ctx->st.served++;
     return rc;
 }

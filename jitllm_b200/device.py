@@ -194,6 +194,16 @@ class Device:
                     router_bias=_ptr(router_bias))
         return self.Moe(out, h, logits, ntok, d, sel_out, wt_out)
 
+    def MoeRouteDev(self, logits, ntok: int, desc: MoeDesc, sel_out, wt_out, stream: int = 0) -> None:
+        """The router alone on device tensors: sel/wt [ntok][top_k] in selection order."""
+        self._check(self.lib.jl_moe_route_dev(self.ctx, _ptr(logits), ntok, C.byref(desc), _ptr(sel_out), _ptr(wt_out),
+                                              stream))
+
+    def MoeExpertsDev(self, y, h, expert_ids, nrows: int, desc: MoeDesc, stream: int = 0) -> None:
+        """The experts alone over already-routed rows (device tensors); y [nrows][hidden] f32 is written."""
+        self._check(self.lib.jl_moe_experts_dev(self.ctx, _ptr(y), _ptr(h), _dtype_code(h), _ptr(expert_ids), nrows,
+                                                C.byref(desc), stream))
+
     def MoeReserve(self, ntok: int, n_expert: int, top_k: int, hidden: int, ffn: int) -> None:
         self._check(self.lib.jl_moe_reserve(self.ctx, ntok, n_expert, top_k, hidden, ffn))
 

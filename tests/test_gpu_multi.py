@@ -1,0 +1,111 @@
+"""The sharded path on 2+ B200s: column / row parallel decode with an NCCL all-reduce and the
+expert-parallel mixture layer with NCCL all-to-all, against the UNSHARDED CPU oracle.
+One process per GPU (spawned here). Skipped on a single-GPU box."""
+import ctypes as C
+import os
+
+import numpy as np
+import pytest
+
+from conftest import nmse, parity_err
+from jitllm_b200 import parallel, synth
+from jitllm_b200._lib import MXFP4, Q4_K, MoeDesc
+
+pytestmark = pytest.mark.gpu
+BAR = 2e-3
+
+
+def _worker(rank, world, port, tmp):
+    import torch
+    import torch.distributed as dist
+
+    import oracle
+    from jitllm_b200 import Device
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        dev = Device(rank)
+        stream = torch.cuda.current_stream().cuda_stream
+        rng = synth.rng_for(11)
+        # ---- tensor parallel decode: column-parallel 4096 -> 1024*world... then row-parallel back
+        nrows, k = 2048, 4096
+        w = synth.q4k_matrix(rng, nrows, k)
+        x = synth.activations(rng, 1, k)
+        ref = oracle.matmul_f64(Q4_K, w, x, nrows, k, 1)
+        wr, n = parallel.shard_rows(w, Q4_K, nrows, k, rank, world)
+        hcol = dev.Upload(Q4_K, wr, n, k)
+        x_dev = torch.from_numpy(x).cuda()
+
+        def col_mm(xx):
+            o = torch.empty(1, n, device="cuda")
+            dev.MatVecDev(o, hcol, xx, 1, stream)
+            return o
+        col = parallel.ColumnParallel(col_mm, n)
+        full = col.gather(col.forward(x_dev))
+        assert parity_err(full.cpu().numpy(), ref) <= BAR
+        wk, kl = parallel.shard_k(w, Q4_K, nrows, k, rank, world)
+        hrow = dev.Upload(Q4_K, wk, nrows, kl)
+
+        def row_mm(xx):
+            o = torch.empty(1, nrows, device="cuda")
+            dev.MatVecDev(o, hrow, xx, 1, stream)
+            return o
+        out = parallel.RowParallel(row_mm).forward(x_dev[:, rank * kl:(rank + 1) * kl].contiguous())
+        assert parity_err(out.cpu().numpy(), ref) <= BAR
+        # ---- expert parallel mixture layer, tokens data-parallel
+        E, topk, hidden, ffn, ntok_all = 8, 2, 128, 192, 24
+        gate = synth.mxfp4_matrix(rng, E * ffn, hidden)
+        up = synth.mxfp4_matrix(rng, E * ffn, hidden)
+        down = synth.mxfp4_matrix(rng, E * hidden, ffn)
+        h = synth.activations(rng, ntok_all, hidden) * np.float32(0.25)
+        logits = synth.activations(rng, ntok_all, E)
+        sel_all = np.zeros((ntok_all, topk), np.int32)
+        wt_all = np.zeros((ntok_all, topk), np.float32)
+        for i in range(ntok_all):
+            s_, _, w_, _, _ = oracle.moe_router(oracle.softmax(logits[i]), topk)
+            sel_all[i], wt_all[i] = s_, w_
+        want = oracle.moe_layer(h, MXFP4, gate, up, down, sel_all, wt_all, E, hidden, ffn)
+        g_l, epr = parallel.shard_experts(gate, MXFP4, E, ffn, hidden, rank, world)
+        u_l, _ = parallel.shard_experts(up, MXFP4, E, ffn, hidden, rank, world)
+        d_l, _ = parallel.shard_experts(down, MXFP4, E, hidden, ffn, rank, world)
+        hg, hu, hd = (dev.Upload(MXFP4, g_l, ffn, hidden, epr), dev.Upload(MXFP4, u_l, ffn, hidden, epr),
+                      dev.Upload(MXFP4, d_l, hidden, ffn, epr))
+        dev.MoeReserve(ntok_all * topk, E, topk, hidden, ffn)
+        d_route = MoeDesc(struct_size=C.sizeof(MoeDesc), type=MXFP4, n_expert=E, top_k=topk, hidden=hidden, ffn=ffn,
+                          act=0, norm=1, scale=1.0)
+        d_local = MoeDesc(struct_size=C.sizeof(MoeDesc), type=MXFP4, n_expert=epr, top_k=1, hidden=hidden, ffn=ffn,
+                          act=0, norm=1, scale=1.0, gate=hg.handle, up=hu.handle, down=hd.handle)
+        lo, hi = rank * ntok_all // world, (rank + 1) * ntok_all // world
+
+        def route(lg):
+            sel = torch.empty(lg.shape[0], topk, dtype=torch.int32, device="cuda")
+            wt = torch.empty(lg.shape[0], topk, dtype=torch.float32, device="cuda")
+            dev.MoeRouteDev(lg, lg.shape[0], d_route, sel, wt, stream)
+            return sel, wt
+
+        def experts(rows, ids):
+            y = torch.empty(rows.shape[0], hidden, dtype=torch.float32, device="cuda")
+            dev.MoeExpertsDev(y, rows.contiguous(), ids.contiguous(), rows.shape[0], d_local, stream)
+            return y
+        moe = parallel.ExpertParallelMoE(route, experts, E, topk, hidden)
+        got = moe.forward(torch.zeros(hi - lo, hidden, device="cuda"), torch.from_numpy(h[lo:hi]).cuda(),
+                          torch.from_numpy(logits[lo:hi]).cuda())
+        torch.cuda.synchronize()
+        assert parity_err(got.cpu().numpy(), want[lo:hi]) <= BAR, nmse(got.cpu().numpy(), want[lo:hi])
+        open(os.path.join(tmp, f"ok{rank}"), "w").write("ok")
+        dev.Close()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_tensor_and_expert_parallel_on_all_visible_gpus(orc, tmp_path):
+    import torch
+    import torch.multiprocessing as mp
+    world = torch.cuda.device_count()
+    if world < 2:
+        pytest.skip("needs at least 2 GPUs in one box")
+    world = 2 if world < 4 else (4 if world < 8 else 8)
+    port = 29500 + os.getpid() % 2000
+    mp.spawn(_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    assert all((tmp_path / f"ok{r}").exists() for r in range(world))
