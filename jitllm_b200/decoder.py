@@ -1,0 +1,167 @@
+"""Llama-3-8B-shaped decoder harness for the quantized-matmul path.
+
+Every matmul (q|k|v, o, gate|up, down, lm_head) goes through libjitllm_b200.so on Q4_K weights;
+the steps around them -- RMSNorm, RoPE, the KV cache, attention, SiLU*up, the residual adds and
+the greedy argmax -- are plain PyTorch ops, because they are neighbours of the path, not the
+path. Weights are random-init Q4_K blocks of the right shapes (no checkpoint can be fetched);
+q|k|v and gate|up are stored as one row-concatenated matrix each, as the reference's
+`MatVecSegments` fuses them (docs/kernel-inventory.md:83).
+
+Tensor parallel over `world` ranks: q|k|v and gate|up are column-parallel (whole heads / matching
+gate-up rows per rank), o and down are row-parallel followed by an all-reduce of the [batch][4096]
+f32 partial sums, lm_head is column-parallel with an all-gather before the argmax.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+from . import synth
+from ._lib import Q4_K
+
+
+class Config:
+    def __init__(self, n_layer=32, hidden=4096, n_head=32, n_kv=8, head_dim=128, ffn=14336, vocab=128256,
+                 rope_theta=500000.0, eps=1e-5):
+        self.n_layer, self.hidden, self.n_head, self.n_kv, self.head_dim = n_layer, hidden, n_head, n_kv, head_dim
+        self.ffn, self.vocab, self.rope_theta, self.eps = ffn, vocab, rope_theta, eps
+
+
+def random_q4k(rng: np.random.Generator, nrows: int, k: int) -> np.ndarray:
+    """Fast random Q4_K tensor: uniform random payload bytes (codes U{0..15}, 6-bit fields uniform),
+    d and dmin = f16(|N(0, 0.02)|) -- the distribution BASELINE config 0 states."""
+    nb = nrows * (k // 256)
+    blk = rng.integers(0, 256, (nb, 144), dtype=np.uint8)
+    dd = np.abs(rng.normal(0.0, 0.02, (nb, 2))).astype(np.float16).view(np.uint16)
+    blk[:, 0:4] = dd.view(np.uint8).reshape(nb, 4)
+    return blk.reshape(nrows, (k // 256) * 144)
+
+
+class Decoder:
+    def __init__(self, dev, cfg: Config, max_batch: int, max_len: int, rank: int = 0, world: int = 1, seed: int = 0xB204,
+                 group=None, max_prefill: int = 2048, keep_host: bool = False):
+        import torch
+        self.torch, self.dev, self.cfg, self.rank, self.world, self.group = torch, dev, cfg, rank, world, group
+        c = cfg
+        assert c.n_head % world == 0 and c.n_kv % world == 0 and c.ffn % (world * 256) == 0 and c.vocab % world == 0
+        self.hq, self.hkv = c.n_head // world, c.n_kv // world
+        self.ffn_l, self.vocab_l = c.ffn // world, c.vocab // world
+        self.max_batch, self.max_len = max_batch, max_len
+        rng = synth.rng_for(seed + rank)
+        d = c.head_dim
+        self.layers, self.host = [], []          # host: the raw blocks, kept only for tests
+
+        def make(nrows, k):
+            raw = random_q4k(rng, nrows, k)
+            if keep_host:
+                self.host.append(raw)
+            return dev.Upload(Q4_K, raw, nrows, k)
+
+        for _ in range(c.n_layer):
+            self.layers.append(dict(qkv=make((self.hq + 2 * self.hkv) * d, c.hidden), o=make(c.hidden, self.hq * d),
+                                    gu=make(2 * self.ffn_l, c.hidden), down=make(c.hidden, self.ffn_l)))
+        self.head = make(self.vocab_l, c.hidden)
+        g = torch.Generator(device="cuda").manual_seed(seed)       # same on every rank
+        self.emb = (torch.randn(c.vocab, c.hidden, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+        self.norm_w = torch.ones(c.hidden, device="cuda")
+        self.k_cache = torch.zeros(c.n_layer, max_batch, self.hkv, max_len, d, device="cuda", dtype=torch.bfloat16)
+        self.v_cache = torch.zeros_like(self.k_cache)
+        inv = 1.0 / (c.rope_theta ** (torch.arange(0, d, 2, device="cuda").float() / d))
+        ang = torch.arange(max_len, device="cuda").float()[:, None] * inv[None, :]
+        self.cos, self.sin = ang.cos(), ang.sin()
+        dev.Reserve(max(2 * self.ffn_l, self.vocab_l, c.hidden), max(c.hidden, self.ffn_l, self.hq * d), max(max_batch, max_prefill))
+        self.weight_bytes = sum(w.nrows * (w.k // 256) * 144 for l in self.layers for w in l.values()) + \
+            self.head.nrows * (self.head.k // 256) * 144
+
+    # -- the path -------------------------------------------------------------
+    def mm(self, w, x):
+        """x [n][k] f32 or bf16 -> [n][rows] f32 through the library (decode kernel for few rows, tcgen05 GEMM above)."""
+        torch = self.torch
+        n = x.shape[0]
+        out = torch.empty(n, w.nrows, device="cuda", dtype=torch.float32)
+        stream = torch.cuda.current_stream().cuda_stream
+        if n == 1 and x.dtype == torch.float32:
+            self.dev.MatVecDev(out, w, x.contiguous(), 1, stream)
+        else:
+            self.dev.MatMulDev(out, w, x.contiguous(), n, stream)      # the library picks the kernel by n
+        return out
+
+    def _allreduce(self, t):
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.all_reduce(t, group=self.group)
+        return t
+
+    # -- neighbours of the path (PyTorch) ---------------------------------------
+    def _rms(self, x):
+        return x * self.torch.rsqrt((x * x).mean(-1, keepdim=True) + self.cfg.eps) * self.norm_w
+
+    def _rope(self, t, pos):
+        """t [n][heads][d]; pos [n] int64 positions."""
+        cos, sin = self.cos[pos][:, None, :], self.sin[pos][:, None, :]
+        a, b = t[..., 0::2], t[..., 1::2]
+        return self.torch.stack((a * cos - b * sin, a * sin + b * cos), dim=-1).flatten(-2)
+
+    def _layers(self, x, pos, attend):
+        """The layer stack over n rows x [n][hidden] f32. pos [n] int64 gives each row's position (RoPE);
+        attend(li, q [n][hq][d], k [n][hkv][d], v [n][hkv][d]) -> [n][hq*d] stores k, v and attends."""
+        torch, c = self.torch, self.cfg
+        import torch.nn.functional as F
+        n, d = x.shape[0], c.head_dim
+        for li, l in enumerate(self.layers):
+            qkv = self.mm(l["qkv"], self._rms(x))
+            q = self._rope(qkv[:, :self.hq * d].view(n, self.hq, d), pos)
+            k = self._rope(qkv[:, self.hq * d:(self.hq + self.hkv) * d].view(n, self.hkv, d), pos)
+            v = qkv[:, (self.hq + self.hkv) * d:].view(n, self.hkv, d)
+            att = attend(li, q.to(torch.bfloat16), k.to(torch.bfloat16), v.to(torch.bfloat16))
+            x = x + self._allreduce(self.mm(l["o"], att.float()))
+            gu = self.mm(l["gu"], self._rms(x))
+            x = x + self._allreduce(self.mm(l["down"], F.silu(gu[:, :self.ffn_l]) * gu[:, self.ffn_l:]))
+        return x
+
+    def _argmax(self, x):
+        torch = self.torch
+        logits = self.last_logits = self.mm(self.head, self._rms(x))
+        if self.world > 1:
+            import torch.distributed as dist
+            parts = [torch.empty_like(logits) for _ in range(self.world)]
+            dist.all_gather(parts, logits, group=self.group)
+            logits = torch.cat(parts, dim=-1)
+        return logits.argmax(-1)
+
+    def prefill(self, tokens):
+        """One prompt tokens [T] int64, causal attention; its keys/values are written to EVERY
+        sequence slot of the cache (all sequences of the batch share the prompt). Returns the next token."""
+        torch = self.torch
+        import torch.nn.functional as F
+        T = tokens.shape[0]
+        pos = torch.arange(T, device="cuda")
+        g = self.hq // self.hkv
+
+        def attend(li, q, k, v):
+            self.k_cache[li, :, :, :T] = k.transpose(0, 1)[None]
+            self.v_cache[li, :, :, :T] = v.transpose(0, 1)[None]
+            o = F.scaled_dot_product_attention(q.transpose(0, 1)[None], k.transpose(0, 1)[None], v.transpose(0, 1)[None],
+                                               is_causal=True, enable_gqa=True)       # query head h uses kv head h // g
+            return o[0].transpose(0, 1).reshape(T, -1)
+
+        x = self._layers(self.emb[tokens].float(), pos, attend)
+        return self._argmax(x[-1:])
+
+    def decode_step(self, tokens, pos_dev):
+        """tokens [B] int64, one per sequence, all at position pos_dev (a 1-element int64 DEVICE tensor,
+        so that the step can be replayed from a CUDA graph). Returns the next tokens [B]."""
+        torch = self.torch
+        import torch.nn.functional as F
+        B = tokens.shape[0]
+        g = self.hq // self.hkv
+        mask = (torch.arange(self.max_len, device="cuda") <= pos_dev)[None, None, None, :]
+
+        def attend(li, q, k, v):
+            self.k_cache[li, :B].index_copy_(2, pos_dev, k[:, :, None, :])
+            self.v_cache[li, :B].index_copy_(2, pos_dev, v[:, :, None, :])
+            o = F.scaled_dot_product_attention(q.view(B, self.hkv, g, -1), self.k_cache[li, :B], self.v_cache[li, :B],
+                                               attn_mask=mask)
+            return o.reshape(B, -1)
+
+        x = self._layers(self.emb[tokens].float(), pos_dev.expand(B), attend)
+        return self._argmax(x)
