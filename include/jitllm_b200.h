@@ -234,6 +234,28 @@ int jl_moe_dev(jl_ctx *ctx, float *out_dev, const void *h_dev, int h_dtype, cons
 int jl_noalloc_max_k(void);
 int jl_matvec_q4k_noalloc(float *out_dev, const void *w_dev, const float *x_dev, int nrows, int k, void *stream);
 
+/* ---- decode-step neighbours (no seam in the reference: its CPU engine runs these as Go loops,
+ * engine/model/forward.go:2785 rmsnorm, engine/nn/ropetable.go:71 RopeTable) ----------------
+ * Short device-pointer kernels that sit between two matvecs of a decode step, so that a caller
+ * which keeps activations on the GPU chains the path with one launch in between: residual add +
+ * RMSNorm, RoPE + KV-cache append, single-query attention over the cache, SiLU(gate)*up. They
+ * join the same dependent-launch chain as the matvec kernels and allocate nothing.
+ *   caches: bf16 [n][hkv][max_len][d]; *pos_dev: the position of the new token, read on the device
+ *   (so a captured graph can be replayed while the caller increments it); cos/sin: f32 [max_len][d/2],
+ *   adjacent-pair rotation; jl_aux_attn_decode needs d == 128 and a scratch of
+ *   jl_aux_attn_scratch_bytes() bytes that was zero-filled once. */
+int jl_aux_add_rmsnorm(float *x_io, const float *delta /* or NULL */, const float *w /* or NULL */, float eps,
+                       float *out, int n, int h, void *stream);
+int jl_aux_silu_mul(float *out, const float *gate_up /* [n][2*ffn] */, int n, int ffn, void *stream);
+int jl_aux_argmax(long long *out /* [n] */, const float *x /* [n][v] */, int n, int v, void *stream);
+int jl_aux_rope_kv(void *q_out_bf16, const float *qkv, void *k_cache_bf16, void *v_cache_bf16,
+                   const long long *pos_dev, const float *cos_t, const float *sin_t, int n, int hq, int hkv, int d,
+                   int max_len, void *stream);
+size_t jl_aux_attn_scratch_bytes(int n, int hq, int hkv, int max_len);
+int jl_aux_attn_decode(float *out, const void *q_bf16, const void *k_cache_bf16, const void *v_cache_bf16,
+                       const long long *pos_dev, void *scratch_zeroed_once, int n, int hq, int hkv, int d, int max_len,
+                       void *stream);
+
 /* ---- host-side fault injection: JITLLM_DEVICE_FAIL_AT (jit/gpu/tier/fault.go:12-58)
  * The n-th, ... serving calls on ctx (1-based ordinals, counted from this call)
  * fail with JL_EDEVICE before anything is launched. n = 0 disarms. Test-only. */

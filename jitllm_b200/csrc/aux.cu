@@ -1,0 +1,341 @@
+// Neighbours of the matmul path that a decode step runs between two matmuls: residual-add + RMSNorm,
+// RoPE + KV-cache append, single-query attention over the cache, SiLU(gate)*up. They exist so that a
+// decoder harness can chain the quantized matvecs with ONE short launch between them (each joins the
+// programmatic-dependent-launch chain the matvec kernels use); they are not part of the drop-in seam.
+#include "jl_internal.cuh"
+#include <cuda_bf16.h>
+
+#define AUX_PDL()                                                   \
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); \
+    asm volatile("griddepcontrol.wait;" ::: "memory")
+
+template <typename... Args>
+static int aux_launch(void (*kern)(Args...), dim3 grid, dim3 block, cudaStream_t s, Args... args) {
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.stream = s; cfg.attrs = at; cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, kern, args...) != cudaSuccess) { cudaGetLastError(); return JL_ECUDA; }
+    return JL_OK;
+}
+
+__device__ __forceinline__ float aux_block_sum(float v, float *red) {
+    for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    const int w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[w] = v;
+    __syncthreads();
+    float t = 0.f;
+    for (int i = 0; i < nw; ++i) t += red[i];      // fixed order: bit-stable
+    return t;
+}
+
+// x_io[row] += delta[row] (when delta != NULL); out[row] = x_io[row] * rsqrt(mean(x^2) + eps) * w.
+__global__ void __launch_bounds__(256) aux_add_rmsnorm_kernel(float *x_io, const float *delta, const float *w, float eps,
+                                                               float *out, int h) {
+    __shared__ float red[8];
+    AUX_PDL();
+    float4 *x4 = (float4 *)(x_io + (size_t)blockIdx.x * h);
+    const float4 *d4 = delta ? (const float4 *)(delta + (size_t)blockIdx.x * h) : nullptr;
+    float4 *o4 = (float4 *)(out + (size_t)blockIdx.x * h);
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < h / 4; i += 256) {
+        float4 v = x4[i];
+        if (d4) {
+            float4 d = d4[i];
+            v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+            x4[i] = v;
+        }
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    const float r = rsqrtf(aux_block_sum(ss, red) / (float)h + eps);
+    for (int i = threadIdx.x; i < h / 4; i += 256) {
+        float4 v = x4[i];                                        // this thread's own writes
+        float4 g = w ? ((const float4 *)w)[i] : make_float4(1.f, 1.f, 1.f, 1.f);
+        o4[i] = make_float4(v.x * r * g.x, v.y * r * g.y, v.z * r * g.z, v.w * r * g.w);
+    }
+}
+
+__global__ void __launch_bounds__(256) aux_silu_mul_kernel(float *out, const float *gu, int ffn) {
+    AUX_PDL();
+    const float4 *g4 = (const float4 *)(gu + (size_t)blockIdx.y * 2 * ffn);
+    const float4 *u4 = g4 + ffn / 4;
+    float4 *o4 = (float4 *)(out + (size_t)blockIdx.y * ffn);
+    for (int i = blockIdx.x * 256 + threadIdx.x; i < ffn / 4; i += gridDim.x * 256) {
+        float4 g = g4[i], u = u4[i];
+        o4[i] = make_float4(g.x / (1.f + __expf(-g.x)) * u.x, g.y / (1.f + __expf(-g.y)) * u.y,
+                            g.z / (1.f + __expf(-g.z)) * u.z, g.w / (1.f + __expf(-g.w)) * u.w);
+    }
+}
+
+// qkv [n][(hq + 2 hkv) * d] f32 -> q_out [n][hq][d] bf16 (rotated), k (rotated) and v appended to the
+// caches [n][hkv][max_len][d] bf16 at position *pos. Adjacent-pair rotation; cos/sin are [max_len][d/2].
+__global__ void __launch_bounds__(64) aux_rope_kv_kernel(__nv_bfloat16 *q_out, const float *qkv, __nv_bfloat16 *k_cache,
+                                                          __nv_bfloat16 *v_cache, const long long *pos_dev, const float *cos_t,
+                                                          const float *sin_t, int hq, int hkv, int d, int max_len) {
+    AUX_PDL();
+    const int row = blockIdx.y, hd = blockIdx.x;
+    const long long pos = *pos_dev;
+    if (pos < 0 || pos >= max_len) return;
+    const float *src = qkv + (size_t)row * (hq + 2 * hkv) * d + (size_t)hd * d;
+    for (int j = threadIdx.x; j < d / 2; j += 64) {
+        float a = src[2 * j], b = src[2 * j + 1];
+        __nv_bfloat162 o;
+        if (hd < hq + hkv) {
+            const float c = cos_t[pos * (d / 2) + j], s = sin_t[pos * (d / 2) + j];
+            o = __floats2bfloat162_rn(a * c - b * s, a * s + b * c);
+        } else {
+            o = __floats2bfloat162_rn(a, b);
+        }
+        __nv_bfloat16 *dst;
+        if (hd < hq) dst = q_out + ((size_t)row * hq + hd) * d;
+        else if (hd < hq + hkv) dst = k_cache + (((size_t)row * hkv + (hd - hq)) * max_len + pos) * d;
+        else dst = v_cache + (((size_t)row * hkv + (hd - hq - hkv)) * max_len + pos) * d;
+        ((__nv_bfloat162 *)dst)[j] = o;
+    }
+}
+
+// ------------------------------------------------------------------ single-query attention over the cache
+// One CTA = one (sequence, kv head, chunk of ATT_CHUNK cache positions), all G query heads of the kv head
+// at once (K and V rows are read once for the group). Partial (max, sum, weighted V) triples go to scratch;
+// the CTA that takes the last ticket of its (sequence, kv head) merges them -- no CTA waits for another.
+#define ATT_CHUNK 64
+#define ATT_D 128
+#define ATT_ROW 272   // bytes of one staged row: 256 + 16 of padding, so that rows start in different banks
+
+__device__ __forceinline__ void aux_bf16x8(const uint4 &v, float *f) {
+    const __nv_bfloat162 *p = (const __nv_bfloat162 *)&v;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float2 t = __bfloat1622float2(p[i]);
+        f[2 * i] = t.x; f[2 * i + 1] = t.y;
+    }
+}
+
+template <int G>
+__global__ void __launch_bounds__(128) aux_attn_decode_kernel(float *out, const __nv_bfloat16 *q, const __nv_bfloat16 *k_cache,
+                                                              const __nv_bfloat16 *v_cache, const long long *pos_dev,
+                                                              float *part, unsigned *tickets, int hkv, int max_len, int nsplit) {
+    constexpr int STRIDE = G * (ATT_D + 2);
+    // K and V tiles of the chunk, staged with coalesced 16-byte loads (all in flight at once); the
+    // cross-group reduction buffer red[8][G][128] reuses the tiles once they have been consumed.
+    __shared__ __align__(16) uint8_t tiles[2 * ATT_CHUNK * ATT_ROW];
+    static_assert(8 * G * ATT_D * 4 <= 2 * ATT_CHUNK * ATT_ROW, "reduction buffer must fit in the tiles");
+    __shared__ float qs[G][ATT_D];
+    __shared__ float sc[G][ATT_CHUNK];
+    __shared__ float mred[4][G], lred[4][G];
+    __shared__ unsigned last;
+    const int split = blockIdx.x, kv = blockIdx.y, row = blockIdx.z, t = threadIdx.x, hq = hkv * G;
+    AUX_PDL();
+    long long len = *pos_dev + 1;
+    if (len > max_len) len = max_len;
+    const int s0 = split * ATT_CHUNK;
+    const int cnt = len - s0 < 0 ? 0 : (len - s0 > ATT_CHUNK ? ATT_CHUNK : (int)(len - s0));
+    float *my = part + (((size_t)row * hkv + kv) * nsplit + split) * STRIDE;
+    if (cnt > 0) {
+        const size_t base_row = ((size_t)row * hkv + kv) * max_len + s0;
+        const uint4 *kg = (const uint4 *)(k_cache + base_row * ATT_D), *vg = (const uint4 *)(v_cache + base_row * ATT_D);
+        uint4 kreg[8], vreg[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {                            // 1024 16-byte pieces per tile, 8 per thread
+            const int piece = i * 128 + t;
+            kreg[i] = (piece >> 4) < cnt ? kg[piece] : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int piece = i * 128 + t;
+            vreg[i] = (piece >> 4) < cnt ? vg[piece] : make_uint4(0, 0, 0, 0);
+        }
+        for (int i = t; i < G * ATT_D; i += 128)
+            qs[i / ATT_D][i % ATT_D] = __bfloat162float(q[((size_t)row * hq + kv * G) * ATT_D + i]) * 0.08838834764831845f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int piece = i * 128 + t;
+            *(uint4 *)(tiles + (piece >> 4) * ATT_ROW + (piece & 15) * 16) = kreg[i];
+            *(uint4 *)(tiles + (ATT_CHUNK + (piece >> 4)) * ATT_ROW + (piece & 15) * 16) = vreg[i];
+        }
+        __syncthreads();
+        // scores: two threads per position, 64 dims each
+        const int p1 = t >> 1, half = t & 1;
+        float s[G];
+#pragma unroll
+        for (int h = 0; h < G; ++h) s[h] = 0.f;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            float f[8];
+            aux_bf16x8(*(const uint4 *)(tiles + p1 * ATT_ROW + (half * 8 + c) * 16), f);
+#pragma unroll
+            for (int h = 0; h < G; ++h)
+#pragma unroll
+                for (int e = 0; e < 8; ++e) s[h] = fmaf(f[e], qs[h][(half * 8 + c) * 8 + e], s[h]);
+        }
+#pragma unroll
+        for (int h = 0; h < G; ++h) {
+            s[h] += __shfl_xor_sync(0xffffffffu, s[h], 1);
+            if (p1 >= cnt) s[h] = -INFINITY;
+            float m = s[h];
+            for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+            if ((t & 31) == 0) mred[t >> 5][h] = m;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int h = 0; h < G; ++h) {
+            const float M = fmaxf(fmaxf(mred[0][h], mred[1][h]), fmaxf(mred[2][h], mred[3][h]));
+            float p = (p1 < cnt && half == 0) ? __expf(s[h] - M) : 0.f;
+            if (half == 0) sc[h][p1] = p;
+            for (int o = 16; o; o >>= 1) p += __shfl_xor_sync(0xffffffffu, p, o);
+            if ((t & 31) == 0) lred[t >> 5][h] = p;
+        }
+        __syncthreads();
+        if (t < G) {
+            my[t] = fmaxf(fmaxf(mred[0][t], mred[1][t]), fmaxf(mred[2][t], mred[3][t]));
+            my[G + t] = lred[0][t] + lred[1][t] + lred[2][t] + lred[3][t];
+        }
+        // weighted V: 16 threads per row (8 dims each), 8 position groups
+        const int dg = t & 15, pg = t >> 4;
+        float acc[G][8];
+#pragma unroll
+        for (int h = 0; h < G; ++h)
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[h][e] = 0.f;
+#pragma unroll
+        for (int i = 0; i < ATT_CHUNK / 8; ++i) {
+            const int p = pg + 8 * i;                            // rows past cnt hold zeros and weight 0
+            float f[8];
+            aux_bf16x8(*(const uint4 *)(tiles + (ATT_CHUNK + p) * ATT_ROW + dg * 16), f);
+#pragma unroll
+            for (int h = 0; h < G; ++h) {
+                const float w = sc[h][p];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) acc[h][e] = fmaf(w, f[e], acc[h][e]);
+            }
+        }
+        __syncthreads();                                        // tiles consumed: reuse them
+        float(*red)[G][ATT_D] = (float(*)[G][ATT_D])tiles;
+#pragma unroll
+        for (int h = 0; h < G; ++h)
+#pragma unroll
+            for (int e = 0; e < 8; ++e) red[pg][h][dg * 8 + e] = acc[h][e];
+        __syncthreads();
+#pragma unroll
+        for (int h = 0; h < G; ++h) {
+            float o = 0.f;
+#pragma unroll
+            for (int g8 = 0; g8 < 8; ++g8) o += red[g8][h][t];
+            my[2 * G + h * ATT_D + t] = o;
+        }
+    } else if (t < G) {
+        my[t] = -INFINITY;
+        my[G + t] = 0.f;
+    }
+    __threadfence();
+    __syncthreads();
+    if (t == 0) last = atomicAdd(&tickets[row * hkv + kv], 1u) == (unsigned)(nsplit - 1);
+    __syncthreads();
+    if (!last) return;
+    __threadfence();
+    const float *base = part + ((size_t)row * hkv + kv) * nsplit * STRIDE;
+    const int nlive = (int)((len + ATT_CHUNK - 1) / ATT_CHUNK);   // chunks past the sequence hold nothing
+#pragma unroll
+    for (int h = 0; h < G; ++h) {
+        float M = -INFINITY;
+        for (int s = 0; s < nlive; ++s) M = fmaxf(M, __ldcg(base + (size_t)s * STRIDE + h));
+        float L = 0.f, o = 0.f;
+        for (int s = 0; s < nlive; ++s) {                      // ascending chunk order: bit-stable
+            const float e = __expf(__ldcg(base + (size_t)s * STRIDE + h) - M);
+            L = fmaf(__ldcg(base + (size_t)s * STRIDE + G + h), e, L);
+            o = fmaf(__ldcg(base + (size_t)s * STRIDE + 2 * G + h * ATT_D + t), e, o);
+        }
+        out[(size_t)row * hq * ATT_D + (size_t)(kv * G + h) * ATT_D + t] = L > 0.f ? o / L : 0.f;
+    }
+    if (t == 0) tickets[row * hkv + kv] = 0;                    // ready for the next launch
+}
+
+// First index of the row maximum (ties: the lowest index, as a sequential scan gives).
+__global__ void __launch_bounds__(1024) aux_argmax_kernel(long long *out, const float *x, int v) {
+    __shared__ float bm[32];
+    __shared__ int bi[32];
+    AUX_PDL();
+    const float *r = x + (size_t)blockIdx.x * v;
+    float m = -INFINITY;
+    int mi = 0x7fffffff;
+    for (int i = threadIdx.x; i < v; i += 1024) {
+        const float f = r[i];
+        if (f > m || (f == m && i < mi)) { m = f; mi = i; }
+    }
+    for (int o = 16; o; o >>= 1) {
+        const float om = __shfl_xor_sync(0xffffffffu, m, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, mi, o);
+        if (om > m || (om == m && oi < mi)) { m = om; mi = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { bm[threadIdx.x >> 5] = m; bi[threadIdx.x >> 5] = mi; }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        m = bm[threadIdx.x]; mi = bi[threadIdx.x];
+        for (int o = 16; o; o >>= 1) {
+            const float om = __shfl_xor_sync(0xffffffffu, m, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, mi, o);
+            if (om > m || (om == m && oi < mi)) { m = om; mi = oi; }
+        }
+        if (threadIdx.x == 0) out[blockIdx.x] = mi == 0x7fffffff ? 0 : mi;
+    }
+}
+
+static size_t aux_attn_ticket_bytes(int n, int hkv) { return (((size_t)n * hkv * 4) + 255) & ~(size_t)255; }
+
+// ------------------------------------------------------------------ C ABI
+JL_EXPORT int jl_aux_add_rmsnorm(float *x_io, const float *delta, const float *w, float eps, float *out, int n, int h,
+                                 void *stream) {
+    if (!x_io || !out || n < 1 || h < 4 || h % 4) return JL_EINVAL;
+    return aux_launch(aux_add_rmsnorm_kernel, dim3(n), dim3(256), (cudaStream_t)stream, x_io, delta, w, eps, out, h);
+}
+
+JL_EXPORT int jl_aux_silu_mul(float *out, const float *gu, int n, int ffn, void *stream) {
+    if (!out || !gu || n < 1 || ffn < 4 || ffn % 4) return JL_EINVAL;
+    int gx = (ffn / 4 + 255) / 256;
+    if (gx > 64) gx = 64;
+    return aux_launch(aux_silu_mul_kernel, dim3(gx, n), dim3(256), (cudaStream_t)stream, out, gu, ffn);
+}
+
+JL_EXPORT int jl_aux_argmax(long long *out, const float *x, int n, int v, void *stream) {
+    if (!out || !x || n < 1 || v < 1) return JL_EINVAL;
+    return aux_launch(aux_argmax_kernel, dim3(n), dim3(1024), (cudaStream_t)stream, out, x, v);
+}
+
+JL_EXPORT int jl_aux_rope_kv(void *q_out_bf16, const float *qkv, void *k_cache_bf16, void *v_cache_bf16,
+                             const long long *pos_dev, const float *cos_t, const float *sin_t, int n, int hq, int hkv, int d,
+                             int max_len, void *stream) {
+    if (!q_out_bf16 || !qkv || !k_cache_bf16 || !v_cache_bf16 || !pos_dev || !cos_t || !sin_t) return JL_EINVAL;
+    if (n < 1 || hq < 1 || hkv < 1 || d < 2 || d % 2 || max_len < 1) return JL_EINVAL;
+    return aux_launch(aux_rope_kv_kernel, dim3(hq + 2 * hkv, n), dim3(64), (cudaStream_t)stream,
+                      (__nv_bfloat16 *)q_out_bf16, qkv, (__nv_bfloat16 *)k_cache_bf16, (__nv_bfloat16 *)v_cache_bf16, pos_dev,
+                      cos_t, sin_t, hq, hkv, d, max_len);
+}
+
+JL_EXPORT size_t jl_aux_attn_scratch_bytes(int n, int hq, int hkv, int max_len) {
+    if (n < 1 || hq < 1 || hkv < 1 || hq % hkv || max_len < 1) return 0;
+    const int g = hq / hkv, nsplit = (max_len + ATT_CHUNK - 1) / ATT_CHUNK;
+    return aux_attn_ticket_bytes(n, hkv) + (size_t)n * hkv * nsplit * g * (ATT_D + 2) * sizeof(float);
+}
+
+JL_EXPORT int jl_aux_attn_decode(float *out, const void *q_bf16, const void *k_cache_bf16, const void *v_cache_bf16,
+                                 const long long *pos_dev, void *scratch_zeroed_once, int n, int hq, int hkv, int d, int max_len,
+                                 void *stream) {
+    if (!out || !q_bf16 || !k_cache_bf16 || !v_cache_bf16 || !pos_dev || !scratch_zeroed_once) return JL_EINVAL;
+    if (n < 1 || hkv < 1 || hq % hkv || d != ATT_D || max_len < 1) return JL_EINVAL;
+    const int g = hq / hkv, nsplit = (max_len + ATT_CHUNK - 1) / ATT_CHUNK;
+    unsigned *tickets = (unsigned *)scratch_zeroed_once;
+    float *part = (float *)((uint8_t *)scratch_zeroed_once + aux_attn_ticket_bytes(n, hkv));
+    const dim3 grid(nsplit, hkv, n), block(128);
+    cudaStream_t s = (cudaStream_t)stream;
+    const __nv_bfloat16 *q = (const __nv_bfloat16 *)q_bf16, *kc = (const __nv_bfloat16 *)k_cache_bf16,
+                        *vc = (const __nv_bfloat16 *)v_cache_bf16;
+    switch (g) {
+    case 1: return aux_launch(aux_attn_decode_kernel<1>, grid, block, s, out, q, kc, vc, pos_dev, part, tickets, hkv, max_len, nsplit);
+    case 2: return aux_launch(aux_attn_decode_kernel<2>, grid, block, s, out, q, kc, vc, pos_dev, part, tickets, hkv, max_len, nsplit);
+    case 4: return aux_launch(aux_attn_decode_kernel<4>, grid, block, s, out, q, kc, vc, pos_dev, part, tickets, hkv, max_len, nsplit);
+    case 8: return aux_launch(aux_attn_decode_kernel<8>, grid, block, s, out, q, kc, vc, pos_dev, part, tickets, hkv, max_len, nsplit);
+    }
+    return JL_ENOTSUP;
+}

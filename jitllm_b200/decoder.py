@@ -38,7 +38,7 @@ def random_q4k(rng: np.random.Generator, nrows: int, k: int) -> np.ndarray:
 
 class Decoder:
     def __init__(self, dev, cfg: Config, max_batch: int, max_len: int, rank: int = 0, world: int = 1, seed: int = 0xB204,
-                 group=None, max_prefill: int = 2048, keep_host: bool = False):
+                 group=None, max_prefill: int = 2048, keep_host: bool = False, share_full: bool = False):
         import torch
         self.torch, self.dev, self.cfg, self.rank, self.world, self.group = torch, dev, cfg, rank, world, group
         c = cfg
@@ -46,20 +46,45 @@ class Decoder:
         self.hq, self.hkv = c.n_head // world, c.n_kv // world
         self.ffn_l, self.vocab_l = c.ffn // world, c.vocab // world
         self.max_batch, self.max_len = max_batch, max_len
-        rng = synth.rng_for(seed + rank)
+        self._att_scratch, self._att_scratch_rows = None, 0
+        rng = synth.rng_for(seed if share_full else seed + rank)
         d = c.head_dim
         self.layers, self.host = [], []          # host: the raw blocks, kept only for tests
+        w_ = world
 
-        def make(nrows, k):
-            raw = random_q4k(rng, nrows, k)
+        def make(segments, k_full, k_split=False):
+            """One resident matrix. segments: row counts of the UNSHARDED matrix's parts (q|k|v, gate|up);
+            each part is column-parallel (rows [rank/world) of the part), or with k_split the whole
+            matrix is row-parallel (k-range [rank/world) of every row, cut at super-block boundaries).
+            share_full: every rank draws the same unsharded matrix and keeps its slice (parity tests);
+            otherwise each rank draws only its own slice."""
+            if share_full:
+                full = random_q4k(rng, sum(segments), k_full).reshape(sum(segments), k_full // 256, 144)
+                parts, r0 = [], 0
+                for n in segments:
+                    part = full[r0:r0 + n]
+                    r0 += n
+                    if k_split:
+                        nb = k_full // 256 // w_
+                        parts.append(part[:, rank * nb:(rank + 1) * nb])
+                    else:
+                        parts.append(part[rank * (n // w_):(rank + 1) * (n // w_)])
+                raw = np.ascontiguousarray(np.concatenate(parts, axis=0))
+                nrows, k = raw.shape[0], raw.shape[1] * 256
+                raw = raw.reshape(nrows, -1)
+            else:
+                nrows = sum(segments) if k_split else sum(n // w_ for n in segments)
+                k = k_full // w_ if k_split else k_full
+                raw = random_q4k(rng, nrows, k)
             if keep_host:
                 self.host.append(raw)
             return dev.Upload(Q4_K, raw, nrows, k)
 
         for _ in range(c.n_layer):
-            self.layers.append(dict(qkv=make((self.hq + 2 * self.hkv) * d, c.hidden), o=make(c.hidden, self.hq * d),
-                                    gu=make(2 * self.ffn_l, c.hidden), down=make(c.hidden, self.ffn_l)))
-        self.head = make(self.vocab_l, c.hidden)
+            self.layers.append(dict(qkv=make([c.n_head * d, c.n_kv * d, c.n_kv * d], c.hidden),
+                                    o=make([c.hidden], c.n_head * d, k_split=True),
+                                    gu=make([c.ffn, c.ffn], c.hidden), down=make([c.hidden], c.ffn, k_split=True)))
+        self.head = make([c.vocab], c.hidden)
         g = torch.Generator(device="cuda").manual_seed(seed)       # same on every rank
         self.emb = (torch.randn(c.vocab, c.hidden, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
         self.norm_w = torch.ones(c.hidden, device="cuda")
@@ -149,7 +174,54 @@ class Decoder:
 
     def decode_step(self, tokens, pos_dev):
         """tokens [B] int64, one per sequence, all at position pos_dev (a 1-element int64 DEVICE tensor,
-        so that the step can be replayed from a CUDA graph). Returns the next tokens [B]."""
+        so that the step can be replayed from a CUDA graph). Returns the next tokens [B].
+        Between two matmuls runs ONE library kernel (jl_aux_*: add+RMSNorm, RoPE+cache append,
+        attention over the cache, SiLU*up), all on the matvec kernels' dependent-launch chain."""
+        torch, c, lib = self.torch, self.cfg, self.dev.lib
+        B, d = tokens.shape[0], c.head_dim
+        st = torch.cuda.current_stream().cuda_stream
+        f32 = dict(device="cuda", dtype=torch.float32)
+        if self._att_scratch is None or self._att_scratch_rows < B:
+            nbytes = lib.jl_aux_attn_scratch_bytes(B, self.hq, self.hkv, self.max_len)
+            self._att_scratch, self._att_scratch_rows = torch.zeros(nbytes, device="cuda", dtype=torch.uint8), B
+
+        def ok(rc):
+            if rc != 0:
+                raise RuntimeError(f"jl_aux call failed with status {rc}")
+
+        def norm(delta):
+            ok(lib.jl_aux_add_rmsnorm(x.data_ptr(), delta.data_ptr() if delta is not None else None, self.norm_w.data_ptr(),
+                                      c.eps, h.data_ptr(), B, c.hidden, st))
+
+        x = self.emb[tokens].float()
+        h = torch.empty_like(x)
+        qb = torch.empty(B, self.hq, d, device="cuda", dtype=torch.bfloat16)
+        att = torch.empty(B, self.hq * d, **f32)
+        a = torch.empty(B, self.ffn_l, **f32)
+        norm(None)
+        for li, l in enumerate(self.layers):
+            qkv = self.mm(l["qkv"], h)
+            kc, vc = self.k_cache[li], self.v_cache[li]
+            ok(lib.jl_aux_rope_kv(qb.data_ptr(), qkv.data_ptr(), kc.data_ptr(), vc.data_ptr(), pos_dev.data_ptr(),
+                                  self.cos.data_ptr(), self.sin.data_ptr(), B, self.hq, self.hkv, d, self.max_len, st))
+            ok(lib.jl_aux_attn_decode(att.data_ptr(), qb.data_ptr(), kc.data_ptr(), vc.data_ptr(), pos_dev.data_ptr(),
+                                      self._att_scratch.data_ptr(), B, self.hq, self.hkv, d, self.max_len, st))
+            norm(self._allreduce(self.mm(l["o"], att)))
+            ok(lib.jl_aux_silu_mul(a.data_ptr(), self.mm(l["gu"], h).data_ptr(), B, self.ffn_l, st))
+            norm(self._allreduce(self.mm(l["down"], a)))          # also the next layer's (or the final) norm
+        torch = self.torch
+        logits = self.last_logits = self.mm(self.head, h)
+        if self.world > 1:
+            import torch.distributed as dist
+            parts = [torch.empty_like(logits) for _ in range(self.world)]
+            dist.all_gather(parts, logits, group=self.group)
+            logits = torch.cat(parts, dim=-1)
+        nxt = torch.empty(B, device="cuda", dtype=torch.int64)
+        ok(lib.jl_aux_argmax(nxt.data_ptr(), logits.data_ptr(), B, logits.shape[1], st))
+        return nxt
+
+    def decode_step_torch(self, tokens, pos_dev):
+        """The same step with PyTorch ops between the matmuls (the check of decode_step)."""
         torch = self.torch
         import torch.nn.functional as F
         B = tokens.shape[0]

@@ -60,8 +60,12 @@ def test_decoder_matches_float_restatement(dev, orc, T):
         assert float((got_prefill - ref[T - 1]).abs().max() / scale) < 3e-2       # bf16 attention operands
         # the next token through the decode path, three sequences sharing the prompt
         pos = torch.tensor([T], device="cuda")
-        dec.decode_step(tokens[T:T + 1].expand(3).contiguous(), pos)
+        nxt = dec.decode_step(tokens[T:T + 1].expand(3).contiguous(), pos)
         got_dec = dec.last_logits.double()
+        assert torch.equal(nxt, dec.last_logits.argmax(-1))
         assert torch.isfinite(got_dec).all()
         assert float((got_dec - ref[T][None]).abs().max() / scale) < 3e-2
         assert float((got_dec[0] - got_dec[2]).abs().max()) == 0.0                 # same inputs, same bits
+        # the PyTorch-glue form of the same step agrees with the fused-neighbour form
+        dec.decode_step_torch(tokens[T:T + 1].expand(3).contiguous(), pos)
+        assert float((dec.last_logits.double() - got_dec).abs().max() / scale) < 1e-2

@@ -15,6 +15,13 @@ pytestmark = pytest.mark.gpu
 BAR = 2e-3
 
 
+def _gather(dist, t):
+    import torch
+    parts = [torch.empty_like(t) for _ in range(dist.get_world_size())]
+    dist.all_gather(parts, t.contiguous())
+    return parts
+
+
 def _worker(rank, world, port, tmp):
     import torch
     import torch.distributed as dist
@@ -53,6 +60,24 @@ def _worker(rank, world, port, tmp):
             return o
         out = parallel.RowParallel(row_mm).forward(x_dev[:, rank * kl:(rank + 1) * kl].contiguous())
         assert parity_err(out.cpu().numpy(), ref) <= BAR
+        # ---- tensor-parallel decoder harness against the unsharded one (same full matrices, sliced per rank)
+        from jitllm_b200.decoder import Config, Decoder
+        cfg = Config(n_layer=2, hidden=512, n_head=8, n_kv=8, head_dim=128, ffn=2048, vocab=2048)
+        one = Decoder(dev, cfg, max_batch=2, max_len=48, max_prefill=16, share_full=True, seed=5)
+        tp = Decoder(dev, cfg, max_batch=2, max_len=48, max_prefill=16, share_full=True, seed=5, rank=rank, world=world)
+        prompt = torch.arange(7, device="cuda") * 37 % cfg.vocab
+        with torch.no_grad():
+            a = one.prefill(prompt)
+            la = one.last_logits.double()
+            b = tp.prefill(prompt)
+            lb = torch.cat([t_ for t_ in _gather(dist, tp.last_logits)], dim=-1).double()
+            assert float((la - lb).abs().max() / la.abs().max()) < 1e-2
+            pos = torch.tensor([7], device="cuda")
+            one.decode_step(a.expand(2).contiguous(), pos)
+            la = one.last_logits.double()
+            tp.decode_step(a.expand(2).contiguous(), pos)
+            lb = torch.cat([t_ for t_ in _gather(dist, tp.last_logits)], dim=-1).double()
+            assert float((la - lb).abs().max() / la.abs().max()) < 1e-2
         # ---- expert parallel mixture layer, tokens data-parallel
         E, topk, hidden, ffn, ntok_all = 8, 2, 128, 192, 24
         gate = synth.mxfp4_matrix(rng, E * ffn, hidden)
