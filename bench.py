@@ -352,8 +352,18 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="q4k_gemv_4096", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="q4k_gemv_4096",
+                    choices=sorted(WORKLOADS) + ["q4k_gemm_prefill", "mxfp4_moe_gptoss", "llama8b_q4k_decode"])
+    ap.add_argument("--batch", type=int, default=1, help="llama8b_q4k_decode: sequences decoded together")
+    ap.add_argument("--prompt", type=int, default=2048, help="llama8b_q4k_decode: prompt length")
     args = ap.parse_args()
+    if args.workload not in WORKLOADS:
+        import bench_workloads as bw
+        if args.impl == "reference":
+            bw.run_reference(args)
+        else:
+            {"q4k_gemm_prefill": bw.run_gemm, "mxfp4_moe_gptoss": bw.run_moe, "llama8b_q4k_decode": bw.run_decode}[args.workload](args)
+        return
     if args.impl == "reference":
         run_reference(args, args.workload)
     else:

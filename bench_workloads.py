@@ -1,0 +1,341 @@
+"""The other measured workloads of the quantized-matmul path, behind `bench.py --workload ...`:
+
+  q4k_gemm_prefill     Q4_K x bf16 GEMM, 512 tokens, 14336x4096 and 4096x14336       (TFLOP/s, tensor roofline)
+  mxfp4_moe_gptoss     MXFP4 mixture layer 32 experts / top-4 / 2880 / 256 tokens     (layers/s + weight GB/s, HBM roofline)
+  llama8b_q4k_decode   Llama-3-8B-shaped Q4_K decoder, 2048-token prompt, greedy decode (tok/s; tensor-parallel under torchrun)
+
+Each prints one JSON line with the same keys as the headline workload. Inputs are seeded synthetic tensors
+of the stated shapes; every timed region is a CUDA-graph replay timed with CUDA events on the launching stream,
+with working sets larger than L2.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import json
+import os
+import time
+
+import numpy as np
+
+
+def _env():
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    return world, int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
+
+
+def _peaks():
+    import bench
+    p = os.path.join(bench.ROOT, "MEASURED_PEAKS.json")
+    d = json.load(open(p)) if os.path.exists(p) else {}
+    return (float(d.get("hbm_gbs", bench.FALLBACK_HBM_GBS)), float(d.get("bf16_tflops", 1590.0)),
+            float(d.get("bf16_tflops_sustained", 1400.0)), "measured" if d else "fallback")
+
+
+def _timed_replays(torch, graph, steps, warmup, local):
+    import bench
+    for _ in range(max(warmup, 3)):
+        graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with bench.ClockSampler(local) as clk:
+        e0.record()
+        for _ in range(steps):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+    return e0.elapsed_time(e1), clk.summary()
+
+
+# ------------------------------------------------------------------ prefill GEMM
+GEMM_SHAPES = [(14336, 4096), (4096, 14336)]
+GEMM_NTOK, GEMM_COPIES = 512, 6          # 6 distinct weight copies per shape: 198 MB > L2
+
+
+def run_gemm(args):
+    import torch
+    from jitllm_b200 import Device, synth
+    from jitllm_b200._lib import Q4_K
+    world, rank, local = _env()
+    if rank != 0:
+        return          # single-GPU workload: replicas would only repeat it
+    torch.cuda.set_device(local)
+    dev = Device(local)
+    rng = synth.rng_for(0xB201)
+    sh = torch.cuda.current_stream().cuda_stream
+    sets, flops = [], 0.0
+    for nrows, k in GEMM_SHAPES:
+        dev.Reserve(nrows, k, GEMM_NTOK)
+        hs = [dev.Upload(Q4_K, synth.q4k_matrix(rng, nrows, k), nrows, k) for _ in range(GEMM_COPIES)]
+        x = torch.randn(GEMM_NTOK, k, device="cuda").to(torch.bfloat16)
+        out = torch.empty(GEMM_NTOK, nrows, device="cuda", dtype=torch.bfloat16)
+        for h in hs:
+            dev.MatMulDev(out, h, x, GEMM_NTOK, sh)
+        sets.append((hs, x, out))
+        flops += 2.0 * GEMM_NTOK * nrows * k * GEMM_COPIES
+    torch.cuda.synchronize()
+    n0 = dev.Stats().launches
+    g, cap = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+    with torch.cuda.graph(g, stream=cap):
+        c = torch.cuda.current_stream().cuda_stream
+        for hs, x, out in sets:
+            for h in hs:
+                dev.MatMulDev(out, h, x, GEMM_NTOK, c)
+    per_replay = dev.Stats().launches - n0
+    ms, clocks = _timed_replays(torch, g, args.steps, args.warmup, local)
+    tf = flops * args.steps / (ms * 1e-3) / 1e12
+    # end to end: host bf16 activations in, host bf16 outputs back, weights resident (keyed on the host pointer)
+    nrows, k = GEMM_SHAPES[0]
+    w_host = synth.q4k_matrix(rng, nrows, k)
+    x_host = synth.to_bf16_bits(synth.activations(rng, GEMM_NTOK, k))
+    out_host = np.empty((GEMM_NTOK, nrows), np.uint16)
+    assert dev.MatMulRaw(out_host, 2, Q4_K, w_host, x_host, 2, nrows, k, GEMM_NTOK), dev.Err()
+    n_e2e = 20
+    t0 = time.perf_counter()
+    for _ in range(n_e2e):
+        dev.MatMulRaw(out_host, 2, Q4_K, w_host, x_host, 2, nrows, k, GEMM_NTOK)
+    e2e_tf = 2.0 * GEMM_NTOK * nrows * k * n_e2e / (time.perf_counter() - t0) / 1e12
+    hbm, burst, sustained, which = _peaks()
+    ngemm = len(GEMM_SHAPES) * GEMM_COPIES
+    print(json.dumps({
+        "metric": "q4k_gemm_tflops", "value": tf, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "Q4_K -> f16 weights x bf16->f16 activations, f32 accumulate (tcgen05 kind::f16), bf16 out",
+        "data": "synthetic",
+        "config": {"workload": "q4k_gemm_prefill", "ntok": GEMM_NTOK, "shapes": GEMM_SHAPES, "copies_per_shape": GEMM_COPIES,
+                   "l2": "6 distinct weight copies per shape (198 MB) cycle through: larger than L2",
+                   "us_per_gemm": ms * 1e3 / args.steps / ngemm},
+        "roofline": {"bound": "tensor", "achieved": tf, "peak": burst, "unit": "TFLOP/s", "frac": tf / burst, "of": which,
+                     "frac_of_sustained": tf / sustained, "kernel": "gemm_q4k_tc5_kernel", "traffic": None},
+        "e2e": {"value": e2e_tf, "unit": "TFLOP/s", "h2d_bytes_per_step": GEMM_NTOK * k * 2,
+                "d2h_bytes_per_step": GEMM_NTOK * nrows * 2, "note": "jl_matmul host-pointer call, 14336x4096, wall clock"},
+        "gpu_launches": int(per_replay * args.steps), "clocks": clocks}), flush=True)
+    dev.Close()
+
+
+# ------------------------------------------------------------------ mixture layer
+MOE = dict(E=32, topk=4, hidden=2880, ffn=2880, ntok=256, layers=2)   # 2 distinct layers: 846 MB of experts > L2
+
+
+def run_moe(args):
+    import torch
+    from jitllm_b200 import Device, synth
+    from jitllm_b200._lib import MXFP4, MoeDesc
+    world, rank, local = _env()
+    if rank != 0:
+        return
+    torch.cuda.set_device(local)
+    E, topk, hidden, ffn, ntok = MOE["E"], MOE["topk"], MOE["hidden"], MOE["ffn"], MOE["ntok"]
+    rng = synth.rng_for(0xB203)
+    dev = Device(local)
+    dev.MoeReserve(ntok, E, topk, hidden, ffn)
+    descs, keep = [], []
+    for _ in range(MOE["layers"]):
+        hs = [dev.Upload(MXFP4, synth.mxfp4_matrix(rng, E * r, kk), r, kk, E) for r, kk in ((ffn, hidden), (ffn, hidden), (hidden, ffn))]
+        keep.append(hs)
+        descs.append(MoeDesc(struct_size=C.sizeof(MoeDesc), type=MXFP4, n_expert=E, top_k=topk, hidden=hidden, ffn=ffn,
+                             act=0, norm=1, scale=1.0, gate=hs[0].handle, up=hs[1].handle, down=hs[2].handle))
+    h = torch.randn(ntok, hidden, device="cuda").to(torch.bfloat16)
+    logits = torch.randn(ntok, E, device="cuda")
+    out = torch.zeros(ntok, hidden, device="cuda")
+
+    def run(s):
+        for d in descs:
+            dev.MoeDev(out, h, logits, ntok, d, None, None, s)
+    run(torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    n0 = dev.Stats().launches
+    g, cap = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+    with torch.cuda.graph(g, stream=cap):
+        run(torch.cuda.current_stream().cuda_stream)
+    per_replay = dev.Stats().launches - n0
+    ms, clocks = _timed_replays(torch, g, args.steps, args.warmup, local)
+    us = ms * 1e3 / (args.steps * MOE["layers"])
+    wbytes = E * 3 * hidden * (ffn // 32) * 17
+    abytes = wbytes + ntok * hidden * 2 + ntok * E * 4 + ntok * hidden * 4
+    fl = ntok * topk * 3 * 2.0 * hidden * ffn
+    # end to end: the host-pointer call (activations and logits in, mixed output back; experts resident after call 1)
+    hg, hu, hd = (synth.mxfp4_matrix(rng, E * ffn, hidden), synth.mxfp4_matrix(rng, E * ffn, hidden),
+                  synth.mxfp4_matrix(rng, E * hidden, ffn))
+    h_host = synth.to_bf16_bits(synth.activations(rng, ntok, hidden))
+    lg_host = synth.activations(rng, ntok, E)
+    out_host = np.zeros((ntok, hidden), np.float32)
+    assert dev.MoeHost(out_host, h_host, lg_host, hg, hu, hd, E, topk, hidden, ffn), dev.Err()
+    n_e2e = 10
+    t0 = time.perf_counter()
+    for _ in range(n_e2e):
+        dev.MoeHost(out_host, h_host, lg_host, hg, hu, hd, E, topk, hidden, ffn)
+    e2e_layers = n_e2e / (time.perf_counter() - t0)
+    hbm, burst, sustained, which = _peaks()
+    print(json.dumps({
+        "metric": "mxfp4_moe_layers_per_s", "value": 1e6 / us, "unit": "layers/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "MXFP4 -> f16 (cvt e2m1x2), bf16->f16 activations, f32 accumulate (tcgen05 kind::f16)",
+        "data": "synthetic",
+        "config": {"workload": "mxfp4_moe_gptoss", **MOE, "us_per_layer": us, "useful_tflops": fl / us / 1e6,
+                   "l2": "2 distinct layers of experts (846 MB) alternate: larger than L2"},
+        "roofline": {"bound": "hbm", "achieved": abytes / us / 1e3, "peak": hbm, "unit": "GB/s", "frac": abytes / us / 1e3 / hbm,
+                     "of": which, "kernel": "moe_gemm_kernel (gate|up, down)", "traffic": None,
+                     "algorithmic_bytes_per_layer": abytes},
+        "e2e": {"value": e2e_layers, "unit": "layers/s", "h2d_bytes_per_step": ntok * hidden * 2 + ntok * E * 4,
+                "d2h_bytes_per_step": ntok * hidden * 4, "note": "jl_moe host-pointer call, wall clock"},
+        "gpu_launches": int(per_replay * args.steps), "clocks": clocks}), flush=True)
+    dev.Close()
+
+
+# ------------------------------------------------------------------ decoder
+def run_decode(args):
+    """Llama-3-8B-shaped Q4_K decoder: prompt prefill (GEMM path), then greedy decode steps replayed from a CUDA
+    graph. Under torchrun the model is tensor-parallel over the ranks (strong scaling: one model, N GPUs)."""
+    import torch
+    from jitllm_b200 import Device
+    from jitllm_b200.decoder import Config, Decoder
+    world, rank, local = _env()
+    torch.cuda.set_device(local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    B, T = args.batch, args.prompt
+    steps = args.steps
+    dev = Device(local)
+    dec = Decoder(dev, Config(), max_batch=B, max_len=T + (max(args.warmup, 3) + steps) + 16, rank=rank, world=world,
+                  max_prefill=T)
+    prompt = torch.randint(0, 128256, (T,), device="cuda", generator=torch.Generator(device="cuda").manual_seed(7))
+    with torch.no_grad():
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        nxt = dec.prefill(prompt)
+        torch.cuda.synchronize()
+        prefill_s = time.perf_counter() - t0
+        tok = nxt.expand(B).contiguous()
+        pos = torch.tensor([T], device="cuda")
+        for _ in range(2):
+            dec.decode_step(tok, pos)                      # eager warm-up (sizes the attention scratch)
+        torch.cuda.synchronize()
+        n0 = dev.Stats().launches
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            out = dec.decode_step(tok, pos)
+            tok.copy_(out)
+            pos.add_(1)
+        matmul_launches = dev.Stats().launches - n0
+        aux_launches = 1 + 6 * dec.cfg.n_layer + 1            # norms, rope, attention, silu per layer; first norm; argmax
+        import bench
+        for _ in range(max(args.warmup, 3)):
+            g.replay()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with bench.ClockSampler(local) as clk:
+            e0.record()
+            for _ in range(steps):
+                g.replay()
+            e1.record()
+            torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        # end to end: the token ids cross the host boundary every step (ids in from pinned memory, next ids out)
+        tok_pin = torch.empty(B, dtype=torch.int64).pin_memory()
+        tok_pin.copy_(tok)
+        n_e2e = min(steps, 16)
+        pos.fill_(T)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(n_e2e):
+            tok.copy_(tok_pin, non_blocking=True)
+            g.replay()
+            tok_pin.copy_(tok, non_blocking=True)
+            torch.cuda.synchronize()
+        e2e_s = time.perf_counter() - t0
+    if world > 1:
+        tt = torch.tensor([ms, e2e_s], device="cuda", dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms, e2e_s = float(tt[0]), float(tt[1])
+    ms_step = ms / steps
+    hbm, burst, sustained, which = _peaks()
+    wb = dec.weight_bytes                                       # per rank
+    if rank == 0:
+        print(json.dumps({
+            "metric": "decode_tok_s", "value": B * 1e3 / ms_step, "unit": "tok/s", "n_gpus": world, "steps": steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "Q4_K weights, f32 activations (int8-digit MMA decode / f16 tcgen05 GEMM), bf16 KV",
+            "data": "synthetic (random-init Q4_K weights, random prompt ids)",
+            "config": {"workload": "llama8b_q4k_decode", "batch": B, "prompt": T, "layers": 32, "hidden": 4096, "heads": "32q/8kv x128",
+                       "ffn": 14336, "vocab": 128256, "parallelism": f"tp{world}", "prefill_tok_s": T / prefill_s,
+                       "l2": f"weights per rank {wb / 1e9:.2f} GB stream every step: larger than L2",
+                       "weight_roofline_tok_s": B * hbm * 1e9 / (wb * world) * world},
+            "roofline": {"bound": "hbm", "achieved": wb / ms_step / 1e6, "peak": hbm, "unit": "GB/s",
+                         "frac": wb / ms_step / 1e6 / hbm, "of": which, "kernel": "whole decode step, weight bytes per rank only",
+                         "traffic": None},
+            "e2e": {"value": B * n_e2e / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": B * 8, "d2h_bytes_per_step": B * 8,
+                    "note": "token ids in from pinned host memory and next ids back to the host every step, wall clock"},
+            "gpu_launches": int((matmul_launches + aux_launches) * steps), "clocks": clk.summary()}), flush=True)
+    del g
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+        os._exit(0)      # a process group whose collectives were captured in a graph can stall in its destructor
+
+
+
+# ------------------------------------------------------------------ reference arm (CPU restatement, host cores)
+def run_reference(args):
+    """The reference's CPU path for the same workloads: its int8-activation integer-dot arithmetic for the dense
+    matmuls, its expert-major mixture layer for the MoE, restated in oracle/jl_oracle.c (the reference is Go and
+    cannot be built here). Every step is a bounded sample of the workload, stated in `sample`."""
+    import oracle
+    from jitllm_b200 import synth
+    from jitllm_b200._lib import MXFP4, Q4_K
+    world, rank, local = _env()
+    if rank != 0:
+        return
+    oracle.build()
+    cores = os.cpu_count() or 1
+    name = args.workload
+    rng = synth.rng_for(0xB2FF)
+
+    def timed(step):
+        for _ in range(args.warmup):
+            step()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            step()
+        return (time.perf_counter() - t0) / args.steps
+
+    if name == "q4k_gemm_prefill":
+        nrows, k, ntok = 14336, 4096, 64
+        w, x = synth.q4k_matrix(rng, nrows, k), synth.activations(rng, ntok, k)
+        dt = timed(lambda: oracle.matmul_int8(Q4_K, w, x, nrows, k, ntok, window=256, nthreads=cores))
+        metric, unit, val = "q4k_gemm_tflops", "TFLOP/s", 2.0 * ntok * nrows * k / dt / 1e12
+        sample = f"step = one {ntok}-token slice of the 512x{nrows}x{k} GEMM, {cores} threads"
+    elif name == "mxfp4_moe_gptoss":
+        E, topk, hidden, ffn, ntok = MOE["E"], MOE["topk"], MOE["hidden"], MOE["ffn"], 16
+        g, u, d = (synth.mxfp4_matrix(rng, E * ffn, hidden), synth.mxfp4_matrix(rng, E * ffn, hidden),
+                   synth.mxfp4_matrix(rng, E * hidden, ffn))
+        h, lg = synth.activations(rng, ntok, hidden), synth.activations(rng, ntok, E)
+        sel, wt = np.zeros((ntok, topk), np.int32), np.zeros((ntok, topk), np.float32)
+        for i in range(ntok):
+            s_, _, w_, _, _ = oracle.moe_router(oracle.softmax(lg[i]), topk)
+            sel[i], wt[i] = s_, w_
+        dt = timed(lambda: oracle.moe_layer(h, MXFP4, g, u, d, sel, wt, E, hidden, ffn, nthreads=cores))
+        metric, unit, val = "mxfp4_moe_layers_per_s", "layers/s", (ntok / MOE["ntok"]) / dt
+        sample = f"step = {ntok} of the layer's {MOE['ntok']} tokens (rate scaled by {ntok}/{MOE['ntok']}), {cores} threads"
+    else:
+        shapes = [(6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336)]
+        ws = [synth.q4k_matrix(rng, r, kk) for r, kk in shapes]
+        xs = [synth.activations(rng, args.batch, kk) for _, kk in shapes]
+
+        def layer():
+            for (r, kk), w, x in zip(shapes, ws, xs):
+                oracle.matmul_int8(Q4_K, w, x, r, kk, args.batch, window=256, nthreads=cores)
+        dt = timed(layer)
+        head = 128256 * 4096 / sum(r * kk for r, kk in shapes)      # lm_head in units of one layer's weights
+        metric, unit, val = "decode_tok_s", "tok/s", args.batch / (dt * (32 + head))
+        sample = (f"step = the four matmuls of ONE layer at batch {args.batch}; tok/s = batch / (32 + {head:.2f}) layer times "
+                  f"(matmuls only: attention, norms and sampling are not timed), {cores} threads")
+    print(json.dumps({
+        "impl": "reference", "metric": metric, "value": val, "unit": unit, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int8 activations x quantized weights -> f32", "data": "synthetic",
+        "config": {"workload": name, "note": "CPU restatement of the reference's arithmetic (oracle/jl_oracle.c)"},
+        "cpu_baseline": {"value": val, "unit": unit, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}), flush=True)
