@@ -45,7 +45,9 @@ struct tc5_params {
     void *out;                    // [ntok][nrows]
     float *partial;               // ksplit > 1: [ksplit][ntok][nrows] f32
     const float *inv_scale;       // [ntok]
-    const uint8_t *w;             // raw Q4_K rows of this weight (expert)
+    const uint8_t *w;             // Q4_K: raw rows of this weight (expert); Q8_0: its resident code plane [row][k]
+    const uint16_t *w_d;          // Q8_0: f16 block scales [row][w_d_stride]
+    int w_d_stride;
     int *status;
     int debug;                    // timing experiments: 1 = skip the dequant math, 2 = skip the MMAs
 };
@@ -109,7 +111,9 @@ __device__ __forceinline__ void tc5_epilogue(const tc5_params &p, int u, uint32_
 
 // SA stages of dequantized weights, SB (deeper) stages of activations: an activation tile takes
 // ~2 us to arrive from L2, a weight stage is produced locally.
-template <int NT, int SA, int SB>
+// WT selects the weight format the dequant warps read: 0 = Q4_K (raw super-blocks), 1 = Q8_0 (resident
+// code plane in 64-element span order + f16 scale plane). Everything else is shared.
+template <int WT, int NT, int SA, int SB>
 __global__ void __launch_bounds__(TC5_THREADS, 1)
 gemm_q4k_tc5_kernel(const __grid_constant__ CUtensorMap xmap, const tc5_params p) {
     using L = tc5_smem<NT, SA, SB>;
@@ -225,80 +229,144 @@ gemm_q4k_tc5_kernel(const __grid_constant__ CUtensorMap xmap, const tc5_params p
         const int r = tid - 192;
         const uint32_t swz = (uint32_t)(r & 7);
         const int a_row_ofs = (r >> 7) * TC5_A_BYTES + (r & 127) * 128;   // which 128-row operand, which row
-        const size_t row_bytes = (size_t)nsb * 144;
-        uint32_t kb_it = 0;
-        bool ok = true;
-        for (int u = blockIdx.x; u < nunits && ok && !*abort_flag; u += gridDim.x) {
-            TC5_UNIT(u);
-            const int grow = min(rt * TC5_ROWS + r, p.nrows - 1);          // rows past the end repeat the last
-            const uint8_t *wrow = p.w + (size_t)grow * row_bytes;
-            uint4 hcur, hnxt = make_uint4(0, 0, 0, 0), qcur[8], qnxt[8];
-            {
-                const uint8_t *b = wrow + (size_t)(sb0 + rot % nsbu) * 144;
-                hcur = ldg_nc16(b);
+        if constexpr (WT == 1) {
+            // Q8_0: a "super-block" here is 256 k = four 64-element spans of the code plane (4 x 64 B) and
+            // eight f16 scales (16 B). Span j of the NEXT super-block is requested into the registers of
+            // span j as soon as span j of this one has been converted: four k-block periods ahead of use.
+            uint32_t kb_it = 0;
+            bool ok = true;
+            for (int u = blockIdx.x; u < nunits && ok && !*abort_flag; u += gridDim.x) {
+                TC5_UNIT(u);
+                const int grow = min(rt * TC5_ROWS + r, p.nrows - 1);
+                const uint8_t *crow = p.w + (size_t)grow * p.k;
+                const uint8_t *drow = reinterpret_cast<const uint8_t *>(p.w_d + (size_t)grow * p.w_d_stride);
+                uint4 q[4][4], dcur, dnxt = make_uint4(0, 0, 0, 0);
+                {
+                    const int sb = sb0 + rot % nsbu;
+                    dcur = ldg_nc16(drow + (size_t)sb * 16);
 #pragma unroll
-                for (int g = 0; g < 8; g++) qcur[g] = ldg_nc16(b + 16 + 16 * g);
-            }
-            for (int i = 0; i < nsbu && ok; i++) {
-                const bool more = i + 1 < nsbu;
-                const uint8_t *nb = wrow + (size_t)(sb0 + (i + 1 + rot) % nsbu) * 144;
-                const uint4 h = hcur;
-                const float2 dd = __half22float2(*reinterpret_cast<const __half2 *>(&h.x));
-                // sc, m of the 8 sub-blocks (format/quant/dequant.go:360-365), four per word
-                const uint32_t sc_lo = h.y & 0x3F3F3F3Fu, m_lo = h.z & 0x3F3F3F3Fu;
-                const uint32_t sc_hi = (h.w & 0x0F0F0F0Fu) | ((h.y >> 2) & 0x30303030u);
-                const uint32_t m_hi = ((h.w >> 4) & 0x0F0F0F0Fu) | ((h.z >> 2) & 0x30303030u);
+                    for (int j = 0; j < 4; j++)
 #pragma unroll
-                for (int j = 0; j < 4; j++, kb_it++) {   // k-block j = sub-blocks 2j (low nibbles), 2j+1 (high)
-                    const uint32_t s = kb_it % SA, ph = (kb_it / SA) & 1;
-                    const uint4 q0 = qcur[2 * j], q1 = qcur[2 * j + 1];
-                    if (more && !(p.debug & 32)) {       // next super-block: group j (and its header with j = 0)
-                        if (j == 0) hnxt = ldg_nc16(nb);
-                        qnxt[2 * j] = ldg_nc16(nb + 16 + 32 * j);
-                        qnxt[2 * j + 1] = ldg_nc16(nb + 32 + 32 * j);
-                    }
-                    const uint32_t scw = j < 2 ? sc_lo : sc_hi, mw = j < 2 ? m_lo : m_hi;
-                    const int b0 = (2 * j) & 3;
-                    // w = (128 d sc) (1 + q/128) - (128 d sc + dmin m): one FMA on a code placed in the
-                    // mantissa of 1.0; the products d sc and dmin m are exact in f32.
-                    const float ds_e = 128.f * dd.x * (float)((scw >> (8 * b0)) & 0xFF);
-                    const float ds_o = 128.f * dd.x * (float)((scw >> (8 * b0 + 8)) & 0xFF);
-                    const float c_e = -(ds_e + dd.y * (float)((mw >> (8 * b0)) & 0xFF));
-                    const float c_o = -(ds_o + dd.y * (float)((mw >> (8 * b0 + 8)) & 0xFF));
-                    if (kb_it >= (uint32_t)SA) ok = tc5_wait(smem_u32(a_empty + s), ph ^ 1, abort_flag);
-                    if (!ok) break;
-                    uint8_t *arow = smem + L::A_OFS + s * TC5_MS * TC5_A_BYTES + a_row_ofs;
-                    const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
-                    if (!(p.debug & 1)) {
+                        for (int t = 0; t < 4; t++) q[j][t] = ldg_nc16(crow + (size_t)sb * 256 + j * 64 + t * 16);
+                }
+                for (int i = 0; i < nsbu && ok; i++) {
+                    const bool more = i + 1 < nsbu;
+                    const int nsbi = sb0 + (i + 1 + rot) % nsbu;
+                    const uint32_t dw[4] = {dcur.x, dcur.y, dcur.z, dcur.w};
 #pragma unroll
-                        for (int c = 0; c < 8; c++) {    // 16-byte chunk c = k 8c..8c+7 of the k-block
-                            const int nib = c >> 2, cq = c & 3;
-                            const float ds = nib ? ds_o : ds_e, cc = nib ? c_o : c_e;
-                            // four codes of a word -> bytes 0x80 | q: byte 2 of a float whose byte 3 is 0x3F,
-                            // i.e. 1 + q/128, picked out by one PRMT per weight
-                            const uint32_t ua = ((nib ? w[2 * cq] >> 4 : w[2 * cq]) & 0x0F0F0F0Fu) | 0x80808080u;
-                            const uint32_t ub = ((nib ? w[2 * cq + 1] >> 4 : w[2 * cq + 1]) & 0x0F0F0F0Fu) | 0x80808080u;
-                            float v[8];
-                            tc5_fma2(v[0], v[1], tc5_code_float(ua, 0), tc5_code_float(ua, 1), ds, cc);
-                            tc5_fma2(v[2], v[3], tc5_code_float(ua, 2), tc5_code_float(ua, 3), ds, cc);
-                            tc5_fma2(v[4], v[5], tc5_code_float(ub, 0), tc5_code_float(ub, 1), ds, cc);
-                            tc5_fma2(v[6], v[7], tc5_code_float(ub, 2), tc5_code_float(ub, 3), ds, cc);
+                    for (int j = 0; j < 4; j++, kb_it++) {
+                        const uint32_t s = kb_it % SA, ph = (kb_it / SA) & 1;
+                        if (kb_it >= (uint32_t)SA) ok = tc5_wait(smem_u32(a_empty + s), ph ^ 1, abort_flag);
+                        if (!ok) break;
+                        uint8_t *arow = smem + L::A_OFS + s * TC5_MS * TC5_A_BYTES + a_row_ofs;
+                        // the two block scales of this span, each broadcast to both halves of a half2
+                        const uint32_t d0 = __byte_perm(dw[j], 0, 0x1010), d1 = __byte_perm(dw[j], 0, 0x3232);
+                        const uint32_t bias = 0x64806480u;   // half2(1152, 1152): 1024 + the 128 that made the code unsigned
+#pragma unroll
+                        for (int c = 0; c < 8; c++) {       // 16-byte chunk c = k 8c..8c+7 of the span
+                            const int wi = c >> 1, ta = 2 * (c & 1);
+                            const uint4 pa = q[j][ta], pb = q[j][ta + 1];
+                            const uint32_t wa = (wi == 0 ? pa.x : wi == 1 ? pa.y : wi == 2 ? pa.z : pa.w) ^ 0x80808080u;
+                            const uint32_t wb = (wi == 0 ? pb.x : wi == 1 ? pb.y : wi == 2 ? pb.z : pb.w) ^ 0x80808080u;
+                            const uint32_t dd = (c >> 2) ? d1 : d0;
+                            // byte u -> f16 0x6400 | u = 1024 + u (exact), minus 1152 = the signed code (exact),
+                            // times d: ONE rounding, to f16
                             uint4 o;
-                            __half2 h0 = __floats2half2_rn(v[0], v[1]), h1 = __floats2half2_rn(v[2], v[3]);
-                            __half2 h2 = __floats2half2_rn(v[4], v[5]), h3 = __floats2half2_rn(v[6], v[7]);
-                            o.x = *reinterpret_cast<uint32_t *>(&h0); o.y = *reinterpret_cast<uint32_t *>(&h1);
-                            o.z = *reinterpret_cast<uint32_t *>(&h2); o.w = *reinterpret_cast<uint32_t *>(&h3);
+                            o.x = hmul2u(hsub2u(__byte_perm(wa, 0x64646464u, 0x4140), bias), dd);
+                            o.y = hmul2u(hsub2u(__byte_perm(wa, 0x64646464u, 0x4342), bias), dd);
+                            o.z = hmul2u(hsub2u(__byte_perm(wb, 0x64646464u, 0x4140), bias), dd);
+                            o.w = hmul2u(hsub2u(__byte_perm(wb, 0x64646464u, 0x4342), bias), dd);
                             *reinterpret_cast<uint4 *>(arow + (((uint32_t)c ^ swz) << 4)) = o;
                         }
-                    }
-                    if (!(p.debug & 4)) fence_async_smem();   // generic writes -> visible to tcgen05.mma
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(smem_u32(a_full + s));
-                }
-                if (!ok) break;
-                hcur = hnxt;
+                        if (more) {
+                            if (j == 0) dnxt = ldg_nc16(drow + (size_t)nsbi * 16);
 #pragma unroll
-                for (int g = 0; g < 8; g++) qcur[g] = qnxt[g];
+                            for (int t = 0; t < 4; t++) q[j][t] = ldg_nc16(crow + (size_t)nsbi * 256 + j * 64 + t * 16);
+                        }
+                        fence_async_smem();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(smem_u32(a_full + s));
+                    }
+                    if (!ok) break;
+                    dcur = dnxt;
+                }
+            }
+        } else {
+            const size_t row_bytes = (size_t)nsb * 144;
+            uint32_t kb_it = 0;
+            bool ok = true;
+            for (int u = blockIdx.x; u < nunits && ok && !*abort_flag; u += gridDim.x) {
+                TC5_UNIT(u);
+                const int grow = min(rt * TC5_ROWS + r, p.nrows - 1);          // rows past the end repeat the last
+                const uint8_t *wrow = p.w + (size_t)grow * row_bytes;
+                uint4 hcur, hnxt = make_uint4(0, 0, 0, 0), qcur[8], qnxt[8];
+                {
+                    const uint8_t *b = wrow + (size_t)(sb0 + rot % nsbu) * 144;
+                    hcur = ldg_nc16(b);
+    #pragma unroll
+                    for (int g = 0; g < 8; g++) qcur[g] = ldg_nc16(b + 16 + 16 * g);
+                }
+                for (int i = 0; i < nsbu && ok; i++) {
+                    const bool more = i + 1 < nsbu;
+                    const uint8_t *nb = wrow + (size_t)(sb0 + (i + 1 + rot) % nsbu) * 144;
+                    const uint4 h = hcur;
+                    const float2 dd = __half22float2(*reinterpret_cast<const __half2 *>(&h.x));
+                    // sc, m of the 8 sub-blocks (format/quant/dequant.go:360-365), four per word
+                    const uint32_t sc_lo = h.y & 0x3F3F3F3Fu, m_lo = h.z & 0x3F3F3F3Fu;
+                    const uint32_t sc_hi = (h.w & 0x0F0F0F0Fu) | ((h.y >> 2) & 0x30303030u);
+                    const uint32_t m_hi = ((h.w >> 4) & 0x0F0F0F0Fu) | ((h.z >> 2) & 0x30303030u);
+    #pragma unroll
+                    for (int j = 0; j < 4; j++, kb_it++) {   // k-block j = sub-blocks 2j (low nibbles), 2j+1 (high)
+                        const uint32_t s = kb_it % SA, ph = (kb_it / SA) & 1;
+                        const uint4 q0 = qcur[2 * j], q1 = qcur[2 * j + 1];
+                        if (more && !(p.debug & 32)) {       // next super-block: group j (and its header with j = 0)
+                            if (j == 0) hnxt = ldg_nc16(nb);
+                            qnxt[2 * j] = ldg_nc16(nb + 16 + 32 * j);
+                            qnxt[2 * j + 1] = ldg_nc16(nb + 32 + 32 * j);
+                        }
+                        const uint32_t scw = j < 2 ? sc_lo : sc_hi, mw = j < 2 ? m_lo : m_hi;
+                        const int b0 = (2 * j) & 3;
+                        // w = (128 d sc) (1 + q/128) - (128 d sc + dmin m): one FMA on a code placed in the
+                        // mantissa of 1.0; the products d sc and dmin m are exact in f32.
+                        const float ds_e = 128.f * dd.x * (float)((scw >> (8 * b0)) & 0xFF);
+                        const float ds_o = 128.f * dd.x * (float)((scw >> (8 * b0 + 8)) & 0xFF);
+                        const float c_e = -(ds_e + dd.y * (float)((mw >> (8 * b0)) & 0xFF));
+                        const float c_o = -(ds_o + dd.y * (float)((mw >> (8 * b0 + 8)) & 0xFF));
+                        if (kb_it >= (uint32_t)SA) ok = tc5_wait(smem_u32(a_empty + s), ph ^ 1, abort_flag);
+                        if (!ok) break;
+                        uint8_t *arow = smem + L::A_OFS + s * TC5_MS * TC5_A_BYTES + a_row_ofs;
+                        const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+                        if (!(p.debug & 1)) {
+    #pragma unroll
+                            for (int c = 0; c < 8; c++) {    // 16-byte chunk c = k 8c..8c+7 of the k-block
+                                const int nib = c >> 2, cq = c & 3;
+                                const float ds = nib ? ds_o : ds_e, cc = nib ? c_o : c_e;
+                                // four codes of a word -> bytes 0x80 | q: byte 2 of a float whose byte 3 is 0x3F,
+                                // i.e. 1 + q/128, picked out by one PRMT per weight
+                                const uint32_t ua = ((nib ? w[2 * cq] >> 4 : w[2 * cq]) & 0x0F0F0F0Fu) | 0x80808080u;
+                                const uint32_t ub = ((nib ? w[2 * cq + 1] >> 4 : w[2 * cq + 1]) & 0x0F0F0F0Fu) | 0x80808080u;
+                                float v[8];
+                                tc5_fma2(v[0], v[1], tc5_code_float(ua, 0), tc5_code_float(ua, 1), ds, cc);
+                                tc5_fma2(v[2], v[3], tc5_code_float(ua, 2), tc5_code_float(ua, 3), ds, cc);
+                                tc5_fma2(v[4], v[5], tc5_code_float(ub, 0), tc5_code_float(ub, 1), ds, cc);
+                                tc5_fma2(v[6], v[7], tc5_code_float(ub, 2), tc5_code_float(ub, 3), ds, cc);
+                                uint4 o;
+                                __half2 h0 = __floats2half2_rn(v[0], v[1]), h1 = __floats2half2_rn(v[2], v[3]);
+                                __half2 h2 = __floats2half2_rn(v[4], v[5]), h3 = __floats2half2_rn(v[6], v[7]);
+                                o.x = *reinterpret_cast<uint32_t *>(&h0); o.y = *reinterpret_cast<uint32_t *>(&h1);
+                                o.z = *reinterpret_cast<uint32_t *>(&h2); o.w = *reinterpret_cast<uint32_t *>(&h3);
+                                *reinterpret_cast<uint4 *>(arow + (((uint32_t)c ^ swz) << 4)) = o;
+                            }
+                        }
+                        if (!(p.debug & 4)) fence_async_smem();   // generic writes -> visible to tcgen05.mma
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(smem_u32(a_full + s));
+                    }
+                    if (!ok) break;
+                    hcur = hnxt;
+    #pragma unroll
+                    for (int g = 0; g < 8; g++) qcur[g] = qnxt[g];
+                }
             }
         }
     } else {
@@ -359,7 +427,7 @@ tc5_reduce_kernel(const float *__restrict__ partial, void *__restrict__ out, int
 // --------------------------------------------------------------------- host
 
 int jl_gemm_tc5_supported(uint32_t type, int nrows, int k, int ntok) {
-    return type == JL_TYPE_Q4_K && k % 256 == 0 && nrows >= 1 && ntok >= 1;
+    return (type == JL_TYPE_Q4_K || type == JL_TYPE_Q8_0) && k % 256 == 0 && nrows >= 1 && ntok >= 1;
 }
 
 static int tc5_pick_nt(int ntok_eff) { return ntok_eff > 128 ? 256 : (ntok_eff > 64 ? 128 : 64); }
@@ -396,12 +464,12 @@ size_t jl_gemm_tc5_scratch_bytes(int nrows, int k, int ntok, int x_dtype, int sm
     return b + 256;
 }
 
-template <int NT, int SA, int SB>
+template <int WT, int NT, int SA, int SB>
 static int tc5_launch(jl_ctx *ctx, const CUtensorMap &xmap, const tc5_params &p, int grid,
                       cudaStream_t s) {
     using L = tc5_smem<NT, SA, SB>;
     static_assert(L::TOTAL <= 227 * 1024, "shared memory budget");
-    JL_CUDA(ctx, cudaFuncSetAttribute(gemm_q4k_tc5_kernel<NT, SA, SB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    JL_CUDA(ctx, cudaFuncSetAttribute(gemm_q4k_tc5_kernel<WT, NT, SA, SB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       L::TOTAL));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid); cfg.blockDim = dim3(TC5_THREADS); cfg.dynamicSmemBytes = L::TOTAL; cfg.stream = s;
@@ -409,7 +477,7 @@ static int tc5_launch(jl_ctx *ctx, const CUtensorMap &xmap, const tc5_params &p,
     at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at; cfg.numAttrs = (ctx->opts.flags & JL_FLAG_NO_PDL) ? 0 : 1;
-    JL_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemm_q4k_tc5_kernel<NT, SA, SB>, xmap, p));
+    JL_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemm_q4k_tc5_kernel<WT, NT, SA, SB>, xmap, p));
     return JL_OK;
 }
 
@@ -417,7 +485,7 @@ int jl_launch_gemm_tc5(jl_ctx *ctx, void *out_dev, int out_dtype, const jl_weigh
                        const void *x_dev, int x_dtype, int ntok, cudaStream_t s) {
     const int nrows = w->nrows, k = w->k;
     if (!jl_gemm_tc5_supported(w->type, nrows, k, ntok))
-        return jl_set_err(ctx, JL_DECLINED, "tcgen05 GEMM serves Q4_K with k %% 256 == 0");
+        return jl_set_err(ctx, JL_DECLINED, "tcgen05 GEMM serves Q4_K and Q8_0 with k %% 256 == 0");
     const int split = x_dtype == JL_DT_F32 ? 1 : 0;
     const int ntok_eff = ntok * (split ? 2 : 1);
     const size_t need = jl_gemm_tc5_scratch_bytes(nrows, k, ntok, x_dtype, ctx->sm_count);
@@ -445,7 +513,8 @@ int jl_launch_gemm_tc5(jl_ctx *ctx, void *out_dev, int out_dtype, const jl_weigh
 
     const int nt = tc5_pick_nt(ntok_eff);
     CUtensorMap xmap;
-    const uint8_t *wbase = w->data + (size_t)expert * nrows * jl_row_bytes(w->type, k);
+    const bool q8 = w->type == JL_TYPE_Q8_0;
+    const uint8_t *wbase = w->data + (size_t)expert * nrows * (q8 ? (size_t)k : jl_row_bytes(w->type, k));
     if (!jl_make_tmap_2d(&xmap, xh, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (uint64_t)k, (uint64_t)ntok_eff, (uint64_t)k * 2,
                          TC5_KB, nt, CU_TENSOR_MAP_SWIZZLE_128B))
         return jl_set_err(ctx, JL_DECLINED, "the driver refused a tensor map for this shape");
@@ -455,13 +524,21 @@ int jl_launch_gemm_tc5(jl_ctx *ctx, void *out_dev, int out_dtype, const jl_weigh
     p.row_tiles = (nrows + TC5_ROWS - 1) / TC5_ROWS; p.tok_tiles = (ntok_eff + nt - 1) / nt;
     p.ksplit = tc5_ksplit(nrows, ntok_eff, k, ctx->sm_count);
     p.out_dtype = out_dtype; p.out = out_dev; p.partial = partial; p.inv_scale = inv_scale; p.w = wbase; p.status = ctx->dev_status;
+    p.w_d = q8 ? reinterpret_cast<const uint16_t *>(w->scales) + (size_t)expert * nrows * w->scale_stride : nullptr;
+    p.w_d_stride = w->scale_stride;
     p.debug = (int)((ctx->opts.flags >> 16) & 63);
     const int units = p.row_tiles * p.tok_tiles * p.ksplit;
     const int grid = units < ctx->sm_count ? units : ctx->sm_count;
     int rc;
-    if (nt == 256) rc = tc5_launch<256, 4, 3>(ctx, xmap, p, grid, s);
-    else if (nt == 128) rc = tc5_launch<128, 3, 6>(ctx, xmap, p, grid, s);
-    else rc = tc5_launch<64, 3, 8>(ctx, xmap, p, grid, s);
+    if (q8) {
+        if (nt == 256) rc = tc5_launch<1, 256, 4, 3>(ctx, xmap, p, grid, s);
+        else if (nt == 128) rc = tc5_launch<1, 128, 3, 6>(ctx, xmap, p, grid, s);
+        else rc = tc5_launch<1, 64, 3, 8>(ctx, xmap, p, grid, s);
+    } else {
+        if (nt == 256) rc = tc5_launch<0, 256, 4, 3>(ctx, xmap, p, grid, s);
+        else if (nt == 128) rc = tc5_launch<0, 128, 3, 6>(ctx, xmap, p, grid, s);
+        else rc = tc5_launch<0, 64, 3, 8>(ctx, xmap, p, grid, s);
+    }
     if (rc) return rc;
     ctx->st.launches++;
     if (p.ksplit > 1) {

@@ -1,0 +1,182 @@
+// Q8_0 decode (1..8 tokens) on the int8 tensor-core path.
+//
+// Q8_0 weights ARE int8, so they feed mma.sync.m16n8k32.s32.s8.s8 unconverted: one MMA covers 16 rows
+// x one 32-element block, whose f16 scale d is applied to the integer sum afterwards. Activations are
+// prepared once per matvec as two int8 digits per value (x * s ~ 256 q1 + q2 with s = 32512 / amax of the
+// 256-element group, error <= 1.5e-5 of that amax); the 8 MMA columns are (token j, digit) pairs, so one
+// instruction serves up to four tokens and a lane ends up holding exactly the two digit sums of "its"
+// token: y[row][tok] += d[row][blk] * (1/s)[tok][group] * (256 * C1 + C2).
+//
+// The resident code plane is stored in 64-element spans whose 16-byte piece t holds what lane t of a quad
+// feeds to the two MMAs of the span (formats.cu: q8_span_pos), so a lane's A fragments for two blocks are
+// ONE 16-byte load per row. A warp's unit of work is 16 rows x 256 elements (4 KB of codes): all of its
+// loads are issued before the first is used; warps of a CTA take different 256-element groups of the same
+// 16 rows and meet in shared memory in fixed order (bit-stable).
+#include "jl_internal.cuh"
+
+// Prepared activation operand of one token: k/64 spans x [digit 2][t 4] x 16 B, then k/256 f32 (1/s).
+static inline size_t q8_xp_token_bytes(int k) { return (size_t)k * 2 + (size_t)(k / 256) * 4; }
+size_t jl_gemv_q8_scratch_bytes(int k, int ntok) { return ((q8_xp_token_bytes(k) + 255) & ~(size_t)255) * ntok; }
+
+// One warp per (256-element group, token).
+__global__ void __launch_bounds__(128) q8_xprep_kernel(const float *__restrict__ X, uint8_t *__restrict__ scratch, int k,
+                                                       size_t tok_stride) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int lane = threadIdx.x & 31, grp = blockIdx.x * 4 + (threadIdx.x >> 5), tok = blockIdx.y;
+    if (grp >= k / 256) return;
+    // lane = (span s of the group, quad lane t, block hb of the span): k offsets 4t..4t+3 and 16+4t..16+4t+3
+    const int s = lane >> 3, t = (lane >> 1) & 3, hb = lane & 1;
+    const float *x = X + (size_t)tok * k + (size_t)grp * 256 + s * 64 + hb * 32;
+    const float4 v0 = __ldg(reinterpret_cast<const float4 *>(x + 4 * t));
+    const float4 v1 = __ldg(reinterpret_cast<const float4 *>(x + 16 + 4 * t));
+    float amax = fmaxf(fmaxf(fmaxf(fabsf(v0.x), fabsf(v0.y)), fmaxf(fabsf(v0.z), fabsf(v0.w))),
+                       fmaxf(fmaxf(fabsf(v1.x), fabsf(v1.y)), fmaxf(fabsf(v1.z), fabsf(v1.w))));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const bool live = amax > 0.f && amax < __int_as_float(0x7f800000);
+    const float scale = live ? 32512.f / amax : 0.f;
+    const float xs[8] = {v0.x * scale, v0.y * scale, v0.z * scale, v0.w * scale,
+                         v1.x * scale, v1.y * scale, v1.z * scale, v1.w * scale};
+    uint32_t d1[2] = {0, 0}, d2[2] = {0, 0};
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        const float q1f = rintf(xs[j] * (1.f / 256.f));
+        const int q1 = (int)q1f;
+        int q2 = (int)rintf(xs[j] - 256.f * q1f);
+        q2 = max(-127, min(127, q2));
+        d1[j >> 2] |= (uint32_t)(q1 & 0xFF) << (8 * (j & 3));
+        d2[j >> 2] |= (uint32_t)(q2 & 0xFF) << (8 * (j & 3));
+    }
+    uint8_t *base = scratch + (size_t)tok * tok_stride;
+    uint8_t *span = base + ((size_t)grp * 4 + s) * 128;
+    *reinterpret_cast<uint2 *>(span + t * 16 + hb * 8) = make_uint2(d1[0], d1[1]);        // digit 1
+    *reinterpret_cast<uint2 *>(span + 64 + t * 16 + hb * 8) = make_uint2(d2[0], d2[1]);   // digit 2
+    if (lane == 0) reinterpret_cast<float *>(base + (size_t)k * 2)[grp] = live ? amax / 32512.f : 0.f;
+}
+
+__device__ __forceinline__ void q8_mma(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                       uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+                 : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0), "r"(0), "r"(0), "r"(0));
+}
+
+__device__ __forceinline__ uint4 q8_ldg16(const void *p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+// grid (row groups of 16, token groups of 4); WARPS warps split the 256-element groups of the row.
+template <int WARPS>
+__global__ void __launch_bounds__(WARPS * 32) gemv_q8_mma_kernel(const uint8_t *__restrict__ codes, const uint16_t *__restrict__ dplane,
+                                                                 int d_stride, const uint8_t *__restrict__ xop, size_t tok_stride,
+                                                                 float *__restrict__ Y, int nrows, int k, int ntok) {
+    __shared__ float red[WARPS][16][4];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int row_a = min((int)blockIdx.x * 16 + g, nrows - 1), row_b = min((int)blockIdx.x * 16 + g + 8, nrows - 1);
+    const int tok0 = blockIdx.y * 4;
+    const int ngrp = k / 256;
+    const uint8_t *ca = codes + (size_t)row_a * k + t * 16, *cb = codes + (size_t)row_b * k + t * 16;
+    const uint8_t *da = reinterpret_cast<const uint8_t *>(dplane + (size_t)row_a * d_stride);
+    const uint8_t *db = reinterpret_cast<const uint8_t *>(dplane + (size_t)row_b * d_stride);
+    // this lane's B column: token tok0 + (g >> 1), digit g & 1; its accumulators: token tok0 + t
+    const int btok = tok0 + (g >> 1);
+    const bool blive = btok < ntok;
+    const uint8_t *xb = xop + (size_t)(blive ? btok : 0) * tok_stride + (g & 1) * 64 + t * 16;
+    const int mytok = tok0 + t;
+    const float *inv_s = reinterpret_cast<const float *>(xop + (size_t)(mytok < ntok ? mytok : 0) * tok_stride + (size_t)k * 2);
+
+    // weights first: they do not depend on the kernel in front
+    uint4 wa[4], wb[4], dda, ddb;
+    int grp = warp;
+    if (grp < ngrp) {
+#pragma unroll
+        for (int s = 0; s < 4; s++) {
+            wa[s] = q8_ldg16(ca + (size_t)grp * 256 + s * 64);
+            wb[s] = q8_ldg16(cb + (size_t)grp * 256 + s * 64);
+        }
+        dda = q8_ldg16(da + (size_t)grp * 16);
+        ddb = q8_ldg16(db + (size_t)grp * 16);
+    }
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");   // the prepared activations come from the kernel in front
+
+    float acc_a = 0.f, acc_b = 0.f;
+    for (; grp < ngrp; grp += WARPS) {
+        uint4 xv[4];
+#pragma unroll
+        for (int s = 0; s < 4; s++)
+            xv[s] = blive ? *reinterpret_cast<const uint4 *>(xb + ((size_t)grp * 4 + s) * 128) : make_uint4(0, 0, 0, 0);
+        const float is = mytok < ntok ? inv_s[grp] : 0.f;
+        const uint4 ua[4] = {wa[0], wa[1], wa[2], wa[3]}, ub[4] = {wb[0], wb[1], wb[2], wb[3]};
+        const uint32_t dwa[4] = {dda.x, dda.y, dda.z, dda.w}, dwb[4] = {ddb.x, ddb.y, ddb.z, ddb.w};
+        const int nx = grp + WARPS;
+        if (nx < ngrp) {                                   // the next unit's loads fly while this one is multiplied
+#pragma unroll
+            for (int s = 0; s < 4; s++) {
+                wa[s] = q8_ldg16(ca + (size_t)nx * 256 + s * 64);
+                wb[s] = q8_ldg16(cb + (size_t)nx * 256 + s * 64);
+            }
+            dda = q8_ldg16(da + (size_t)nx * 16);
+            ddb = q8_ldg16(db + (size_t)nx * 16);
+        }
+        float ga = 0.f, gb = 0.f;
+#pragma unroll
+        for (int s = 0; s < 4; s++) {
+            int c0[4], c1[4];
+            q8_mma(c0, ua[s].x, ub[s].x, ua[s].y, ub[s].y, xv[s].x, xv[s].y);     // block 2s
+            q8_mma(c1, ua[s].z, ub[s].z, ua[s].w, ub[s].w, xv[s].z, xv[s].w);     // block 2s + 1
+            const float2 fa = __half22float2(*reinterpret_cast<const __half2 *>(&dwa[s]));
+            const float2 fb = __half22float2(*reinterpret_cast<const __half2 *>(&dwb[s]));
+            ga = fmaf(fa.x, (float)(256 * c0[0] + c0[1]), ga);
+            gb = fmaf(fb.x, (float)(256 * c0[2] + c0[3]), gb);
+            ga = fmaf(fa.y, (float)(256 * c1[0] + c1[1]), ga);
+            gb = fmaf(fb.y, (float)(256 * c1[2] + c1[3]), gb);
+        }
+        acc_a = fmaf(ga, is, acc_a);
+        acc_b = fmaf(gb, is, acc_b);
+    }
+    red[warp][g][t] = acc_a;
+    red[warp][g + 8][t] = acc_b;
+    __syncthreads();
+    for (int i = tid; i < 64; i += WARPS * 32) {
+        const int r = i >> 2, j = i & 3;
+        float sum = 0.f;
+#pragma unroll
+        for (int w = 0; w < WARPS; w++) sum += red[w][r][j];      // fixed order
+        const int row = blockIdx.x * 16 + r, tok = tok0 + j;
+        if (row < nrows && tok < ntok) Y[(size_t)tok * nrows + row] = sum;
+    }
+}
+
+int jl_launch_gemv_q8(jl_ctx *ctx, float *out_dev, const uint8_t *codes, const uint8_t *scales, int d_stride,
+                      const float *x_dev, int nrows, int k, int ntok, cudaStream_t s) {
+    const size_t tok_stride = (q8_xp_token_bytes(k) + 255) & ~(size_t)255;
+    const size_t need = tok_stride * ntok;
+    if (ctx->scratch_cap < need)
+        return jl_set_err(ctx, JL_ENOMEM, "decode scratch holds %zu bytes, %d x %d token(s) need %zu (jl_reserve sizes it)",
+                          ctx->scratch_cap, k, ntok, need);
+    uint8_t *scratch = (uint8_t *)ctx->scratch;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    const int nattr = (ctx->opts.flags & JL_FLAG_NO_PDL) ? 0 : 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((k / 256 + 3) / 4, ntok); cfg.blockDim = dim3(128); cfg.stream = s; cfg.attrs = at; cfg.numAttrs = nattr;
+    JL_CUDA(ctx, cudaLaunchKernelEx(&cfg, q8_xprep_kernel, x_dev, scratch, k, tok_stride));
+    ctx->st.launches++;
+    const int ngrp = k / 256;
+    const int warps = ngrp >= 8 ? 8 : (ngrp >= 4 ? 4 : (ngrp >= 2 ? 2 : 1));
+    cfg.gridDim = dim3((nrows + 15) / 16, (ntok + 3) / 4); cfg.blockDim = dim3(warps * 32);
+    const uint16_t *dpl = reinterpret_cast<const uint16_t *>(scales);
+    const uint8_t *xop = scratch;
+    if (warps == 8) JL_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemv_q8_mma_kernel<8>, codes, dpl, d_stride, xop, tok_stride, out_dev, nrows, k, ntok));
+    else if (warps == 4) JL_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemv_q8_mma_kernel<4>, codes, dpl, d_stride, xop, tok_stride, out_dev, nrows, k, ntok));
+    else if (warps == 2) JL_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemv_q8_mma_kernel<2>, codes, dpl, d_stride, xop, tok_stride, out_dev, nrows, k, ntok));
+    else JL_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemv_q8_mma_kernel<1>, codes, dpl, d_stride, xop, tok_stride, out_dev, nrows, k, ntok));
+    return JL_OK;
+}

@@ -110,6 +110,9 @@ int jl_repack_upload(jl_ctx *ctx, uint32_t type, const void *w_host, size_t w_by
 void jl_weight_release(jl_weight *w);
 
 // gemv.cu -- decode kernels. x_dev [ntok][k] f32, out_dev [ntok][nrows] f32.
+size_t jl_gemv_q8_scratch_bytes(int k, int ntok);
+int jl_launch_gemv_q8(jl_ctx *ctx, float *out_dev, const uint8_t *codes, const uint8_t *scales, int d_stride,
+                      const float *x_dev, int nrows, int k, int ntok, cudaStream_t s);
 int jl_launch_gemv(jl_ctx *ctx, float *out_dev, const jl_weight *w, int expert, const float *x_dev,
                    int ntok, int kernel, int warps, cudaStream_t s);
 int jl_gemv_choice(jl_ctx *ctx, uint32_t type, int nrows, int k, int ntok, jl_choice *out);

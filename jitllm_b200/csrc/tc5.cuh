@@ -171,6 +171,12 @@ __device__ __forceinline__ uint32_t hmul2u(uint32_t a, uint32_t b) {
     return d;
 }
 
+__device__ __forceinline__ uint32_t hsub2u(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+
 // Bounded wait that also gives up when another role of the CTA has aborted.
 __device__ __forceinline__ bool tc5_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
     for (uint32_t i = 0; i < JL_SPIN_LIMIT; i++) {

@@ -188,3 +188,44 @@ def test_host_side_fault_injection(orc):
         assert d.last_status == -4 and "injected" in d.Err()
         assert d.MatVec(out, Q4_K, w, x, 16, 256)
         assert d.Stats().injected == 1
+
+
+@pytest.mark.parametrize("ntok", [1, 3, 4, 7, 8])
+@pytest.mark.parametrize("nrows,k", [(16, 256), (5, 512), (100, 1024), (4096, 4096), (1024, 4096), (14336, 4096)])
+def test_q8_0_tensor_core_decode_matches_oracle(orc, nrows, k, ntok):
+    """Q8_0 decode: int8 codes straight into mma.sync.s8.s8, activations as two int8 digits."""
+    if ntok > 1 and nrows > 4096:
+        pytest.skip("the large shape is covered at one token")
+    rng = synth.rng_for(0xB280 + nrows + k + ntok)
+    w = synth.q8_0_matrix(rng, nrows, k)
+    x = synth.activations(rng, ntok, k)
+    with Device(0, pin_kernel=K_MMA) as d:
+        ch = d.Select(Q8_0, nrows, k, ntok)
+        assert ch is not None and ch.kernel == K_MMA and ch.tile_k == 32
+        out = np.full((ntok, nrows), np.nan, np.float32)
+        assert d.MatMul(out, Q8_0, w, x, nrows, k, ntok), d.Err()
+        ref = orc.matmul_f64(Q8_0, w, x, nrows, k, ntok)
+        assert np.isfinite(out).all()
+        assert parity_err(out, ref) <= BAR, parity_err(out, ref)
+        assert nmse(out, ref) < 1e-8
+        out2 = np.empty_like(out)
+        assert d.MatMul(out2, Q8_0, w, x, nrows, k, ntok)
+        assert np.array_equal(out.view(np.uint32), out2.view(np.uint32))      # fixed reduction order
+
+
+def test_q8_0_decode_survives_extreme_activations(orc):
+    rng = synth.rng_for(41)
+    nrows, k = 64, 1024
+    w = synth.q8_0_matrix(rng, nrows, k)
+    for scale in (1e-30, 1.0, 1e30):
+        x = (synth.activations(rng, 1, k) * np.float32(scale)).astype(np.float32)
+        x[0, 5] = 0.0
+        with Device(0) as d:
+            out = np.full((1, nrows), np.nan, np.float32)
+            assert d.MatMul(out, Q8_0, w, x, nrows, k, 1), d.Err()
+        ref = orc.matmul_f64(Q8_0, w, x, nrows, k, 1)
+        assert parity_err(out, ref) <= BAR
+    with Device(0) as d:
+        out = np.full((1, nrows), np.nan, np.float32)
+        assert d.MatMul(out, Q8_0, w, np.zeros((1, k), np.float32), nrows, k, 1)
+        assert not out.any()

@@ -105,3 +105,48 @@ def test_config1_full_size_sampled_rows(orc, nrows, k):
         assert np.isfinite(got).all()
         assert parity_err(got, ref) <= BAR, (parity_err(got, ref), nmse(got, ref))
         assert nmse(got, ref) <= 1e-6
+
+
+# ---- Q8_0 through the same kernel (batched decode, BASELINE config 2: f32 activations, batch 32)
+
+def _run_q8(dev, orc, nrows, k, ntok, seed, x_dtype):
+    from jitllm_b200 import Q8_0
+    rng = synth.rng_for(seed)
+    w = synth.q8_0_matrix(rng, nrows, k)
+    if x_dtype == DT_BF16:
+        xin, xval = _bf16_inputs(rng, ntok, k)
+    else:
+        xval = synth.activations(rng, ntok, k)
+        xin = xval
+    out = np.full((ntok, nrows), np.nan, np.float32)
+    assert dev.MatMulRaw(out, DT_F32, Q8_0, w, xin, x_dtype, nrows, k, ntok), dev.Err()
+    ref = orc.matmul_f64_blas(Q8_0, w, xval, nrows, k, ntok)
+    dev.Forget(w)
+    return out, ref
+
+
+@pytest.mark.parametrize("nrows,k,ntok,x_dtype", [(4096, 4096, 32, DT_F32), (1024, 4096, 32, DT_F32), (14336, 4096, 32, DT_F32),
+                                                   (200, 512, 9, DT_F32), (256, 256, 64, DT_BF16), (520, 1024, 300, DT_BF16)])
+def test_q8_0_batched_gemm_matches_oracle(orc, nrows, k, ntok, x_dtype):
+    from jitllm_b200 import Q8_0
+    with Device(0) as d:                      # selection on its own: more than 8 tokens -> the tcgen05 GEMM
+        ch = d.Select(Q8_0, nrows, k, ntok)
+        assert ch is not None and ch.kernel == K_TC5
+        got, ref = _run_q8(d, orc, nrows, k, ntok, 0xB208 + nrows + ntok, x_dtype)
+        assert np.isfinite(got).all()
+        assert parity_err(got, ref) <= BAR, (parity_err(got, ref), nmse(got, ref))
+        assert nmse(got, ref) <= 1e-6
+
+
+def test_q8_0_gemm_agrees_with_the_simt_check_kernel(orc):
+    from jitllm_b200 import K_SIMT, Q8_0
+    rng = synth.rng_for(77)
+    nrows, k, ntok = 384, 1024, 24
+    w = synth.q8_0_matrix(rng, nrows, k)
+    x = synth.activations(rng, ntok, k)
+    a, b = np.empty((ntok, nrows), np.float32), np.empty((ntok, nrows), np.float32)
+    with Device(0) as d:
+        assert d.MatMulRaw(a, DT_F32, Q8_0, w, x, DT_F32, nrows, k, ntok), d.Err()
+    with Device(0, pin_kernel=K_SIMT) as d:
+        assert d.MatMulRaw(b, DT_F32, Q8_0, w, x, DT_F32, nrows, k, ntok), d.Err()
+    assert parity_err(a, b.astype(np.float64)) <= BAR
