@@ -353,7 +353,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="q4k_gemv_4096",
-                    choices=sorted(WORKLOADS) + ["q4k_gemm_prefill", "mxfp4_moe_gptoss", "llama8b_q4k_decode"])
+                    choices=sorted(WORKLOADS) + ["q4k_gemm_prefill", "q8_0_batch32", "mxfp4_moe_gptoss", "llama8b_q4k_decode"])
     ap.add_argument("--batch", type=int, default=1, help="llama8b_q4k_decode: sequences decoded together")
     ap.add_argument("--prompt", type=int, default=2048, help="llama8b_q4k_decode: prompt length")
     args = ap.parse_args()
@@ -362,7 +362,7 @@ def main():
         if args.impl == "reference":
             bw.run_reference(args)
         else:
-            {"q4k_gemm_prefill": bw.run_gemm, "mxfp4_moe_gptoss": bw.run_moe, "llama8b_q4k_decode": bw.run_decode}[args.workload](args)
+            {"q4k_gemm_prefill": bw.run_gemm, "q8_0_batch32": bw.run_q8_batch, "mxfp4_moe_gptoss": bw.run_moe, "llama8b_q4k_decode": bw.run_decode}[args.workload](args)
         return
     if args.impl == "reference":
         run_reference(args, args.workload)

@@ -1,6 +1,7 @@
 """The other measured workloads of the quantized-matmul path, behind `bench.py --workload ...`:
 
   q4k_gemm_prefill     Q4_K x bf16 GEMM, 512 tokens, 14336x4096 and 4096x14336       (TFLOP/s, tensor roofline)
+  q8_0_batch32         Q8_0 batched decode, 32 tokens, 4096->4096 / 1024 / 14336          (weight GB/s; column-sharded under torchrun)
   mxfp4_moe_gptoss     MXFP4 mixture layer 32 experts / top-4 / 2880 / 256 tokens     (layers/s + weight GB/s, HBM roofline)
   llama8b_q4k_decode   Llama-3-8B-shaped Q4_K decoder, 2048-token prompt, greedy decode (tok/s; tensor-parallel under torchrun)
 
@@ -110,6 +111,85 @@ def run_gemm(args):
                 "d2h_bytes_per_step": GEMM_NTOK * nrows * 2, "note": "jl_matmul host-pointer call, 14336x4096, wall clock"},
         "gpu_launches": int(per_replay * args.steps), "clocks": clocks}), flush=True)
     dev.Close()
+
+
+# ------------------------------------------------------------------ Q8_0 batched decode
+Q8_SHAPES = [(4096, 4096), (1024, 4096), (14336, 4096)]
+Q8_NTOK = 32
+
+
+def run_q8_batch(args):
+    """Q8_0 batch-32 decode matmuls (f32 activations), the three shapes back to back over rings of distinct
+    weight copies. Under torchrun the rows are column-sharded over the ranks (strong scaling, no collective)."""
+    import torch
+    from jitllm_b200 import Device, synth
+    from jitllm_b200._lib import Q8_0
+    world, rank, local = _env()
+    torch.cuda.set_device(local)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    dev = Device(local)
+    rng = synth.rng_for(0xB202 + rank)
+    sh = torch.cuda.current_stream().cuda_stream
+    sets, wbytes, flops = [], 0, 0.0
+    for nrows_full, k in Q8_SHAPES:
+        nrows = nrows_full // world
+        copies = max(2, int(200e6 / (nrows * k * 34 / 32)) + 1)           # each ring beyond L2
+        dev.Reserve(nrows, k, Q8_NTOK)
+        hs = [dev.Upload(Q8_0, synth.q8_0_matrix(rng, nrows, k), nrows, k) for _ in range(copies)]
+        x = torch.randn(Q8_NTOK, k, device="cuda")
+        out = torch.empty(Q8_NTOK, nrows, device="cuda")
+        for h in hs:
+            dev.MatMulDev(out, h, x, Q8_NTOK, sh)
+        sets.append((hs, x, out))
+        wbytes += copies * (nrows * k * 34 // 32 + Q8_NTOK * (k + nrows) * 4)
+        flops += 2.0 * Q8_NTOK * nrows * k * copies
+    torch.cuda.synchronize()
+    n0 = dev.Stats().launches
+    g, cap = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+    with torch.cuda.graph(g, stream=cap):
+        c = torch.cuda.current_stream().cuda_stream
+        for hs, x, out in sets:
+            for h in hs:
+                dev.MatMulDev(out, h, x, Q8_NTOK, c)
+    per_replay = dev.Stats().launches - n0
+    if world > 1:
+        dist.barrier()
+    ms, clocks = _timed_replays(torch, g, args.steps, args.warmup, local)
+    if world > 1:
+        tt = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms = float(tt)
+    gbs = wbytes * args.steps / (ms * 1e-3) / 1e9          # per rank
+    # end to end on the 4096x4096 shard: host activations in, host outputs back
+    nrows, k = Q8_SHAPES[0][0] // world, Q8_SHAPES[0][1]
+    w_host, x_host = synth.q8_0_matrix(rng, nrows, k), synth.activations(rng, Q8_NTOK, k)
+    out_host = np.empty((Q8_NTOK, nrows), np.float32)
+    assert dev.MatMul(out_host, Q8_0, w_host, x_host, nrows, k, Q8_NTOK), dev.Err()
+    t0 = time.perf_counter()
+    for _ in range(50):
+        dev.MatMul(out_host, Q8_0, w_host, x_host, nrows, k, Q8_NTOK)
+    e2e = 50 * (nrows * k * 34 // 32 + Q8_NTOK * (k + nrows) * 4) / (time.perf_counter() - t0) / 1e9
+    hbm, burst, sustained, which = _peaks()
+    if rank == 0:
+        print(json.dumps({
+            "metric": "q8_0_batch32_gbs", "value": gbs * world, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "Q8_0 -> f16 weights (one rounding), f32 activations as f16 hi+lo, f32 accumulate (tcgen05)",
+            "data": "synthetic",
+            "config": {"workload": "q8_0_batch32", "ntok": Q8_NTOK, "shapes": Q8_SHAPES, "parallelism": f"column-parallel x{world}",
+                       "l2": "a ring of distinct weight copies per shape, each ring > 200 MB: larger than L2",
+                       "tflops": flops * args.steps / (ms * 1e-3) / 1e12 * world},
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm, "unit": "GB/s", "frac": gbs / hbm, "of": which,
+                         "kernel": "gemm_q4k_tc5_kernel<1,...> (Q8_0 dequant)", "traffic": None},
+            "e2e": {"value": e2e * world, "unit": "GB/s", "h2d_bytes_per_step": Q8_NTOK * k * 4, "d2h_bytes_per_step": Q8_NTOK * nrows * 4,
+                    "note": "jl_matmul host-pointer call on the 4096x4096 shard, wall clock"},
+            "gpu_launches": int(per_replay * args.steps), "clocks": clocks}), flush=True)
+    dev.Close()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
 
 
 # ------------------------------------------------------------------ mixture layer
@@ -307,6 +387,18 @@ def run_reference(args):
         dt = timed(lambda: oracle.matmul_int8(Q4_K, w, x, nrows, k, ntok, window=256, nthreads=cores))
         metric, unit, val = "q4k_gemm_tflops", "TFLOP/s", 2.0 * ntok * nrows * k / dt / 1e12
         sample = f"step = one {ntok}-token slice of the 512x{nrows}x{k} GEMM, {cores} threads"
+    elif name == "q8_0_batch32":
+        from jitllm_b200._lib import Q8_0
+        ws = [synth.q8_0_matrix(rng, r, kk) for r, kk in Q8_SHAPES]
+        xs = [synth.activations(rng, Q8_NTOK, kk) for _, kk in Q8_SHAPES]
+
+        def q8step():
+            for (r, kk), w, x in zip(Q8_SHAPES, ws, xs):
+                oracle.matmul_int8(Q8_0, w, x, r, kk, Q8_NTOK, window=32, nthreads=cores)
+        dt = timed(q8step)
+        nbytes = sum(r * kk * 34 // 32 + Q8_NTOK * (kk + r) * 4 for r, kk in Q8_SHAPES)
+        metric, unit, val = "q8_0_batch32_gbs", "GB/s", nbytes / dt / 1e9
+        sample = f"step = the three batch-32 matmuls once each (one weight copy per shape), {cores} threads"
     elif name == "mxfp4_moe_gptoss":
         E, topk, hidden, ffn, ntok = MOE["E"], MOE["topk"], MOE["hidden"], MOE["ffn"], 16
         g, u, d = (synth.mxfp4_matrix(rng, E * ffn, hidden), synth.mxfp4_matrix(rng, E * ffn, hidden),

@@ -245,16 +245,26 @@ int jl_matvec_q4k_noalloc(float *out_dev, const void *w_dev, const float *x_dev,
  *   adjacent-pair rotation; jl_aux_attn_decode needs d == 128 and a scratch of
  *   jl_aux_attn_scratch_bytes() bytes that was zero-filled once. */
 int jl_aux_add_rmsnorm(float *x_io, const float *delta /* or NULL */, const float *w /* or NULL */, float eps,
-                       float *out, int n, int h, void *stream);
-int jl_aux_silu_mul(float *out, const float *gate_up /* [n][2*ffn] */, int n, int ffn, void *stream);
+                       float *out /* or NULL when operand_out is given */, void *operand_out, int n, int h, void *stream);
+int jl_aux_silu_mul(float *out /* or NULL when operand_out is given */, void *operand_out,
+                    const float *gate_up /* [n][2*ffn] */, int n, int ffn, void *stream);
 int jl_aux_argmax(long long *out /* [n] */, const float *x /* [n][v] */, int n, int v, void *stream);
 int jl_aux_rope_kv(void *q_out_bf16, const float *qkv, void *k_cache_bf16, void *v_cache_bf16,
                    const long long *pos_dev, const float *cos_t, const float *sin_t, int n, int hq, int hkv, int d,
                    int max_len, void *stream);
 size_t jl_aux_attn_scratch_bytes(int n, int hq, int hkv, int max_len);
-int jl_aux_attn_decode(float *out, const void *q_bf16, const void *k_cache_bf16, const void *v_cache_bf16,
-                       const long long *pos_dev, void *scratch_zeroed_once, int n, int hq, int hkv, int d, int max_len,
-                       void *stream);
+int jl_aux_attn_decode(float *out /* or NULL when operand_out is given */, void *operand_out, const void *q_bf16,
+                       const void *k_cache_bf16, const void *v_cache_bf16, const long long *pos_dev,
+                       void *scratch_zeroed_once, int n, int hq, int hkv, int d, int max_len, void *stream);
+
+/* A producer can hand its result to the next Q4_K matvec without a conversion launch in between:
+ * jl_decode_operand(ctx, w, ntok) names the place (inside ctx's scratch) where the decode kernel for weight
+ * `w` expects its prepared activation operand, or NULL when that weight / token count has no such form;
+ * the jl_aux_* kernels write it when given as `operand_out` (n must equal ntok, the row length w's k, a
+ * multiple of 256; attention needs an even number of query heads per kv head); jl_matvec_dev_prepared then
+ * runs the matvec on it. One operand per context at a time: produce, consume, then produce the next. */
+void *jl_decode_operand(jl_ctx *ctx, const jl_weight *w, int ntok);
+int jl_matvec_dev_prepared(jl_ctx *ctx, float *out_dev, const jl_weight *w, int ntok, void *stream);
 
 /* ---- host-side fault injection: JITLLM_DEVICE_FAIL_AT (jit/gpu/tier/fault.go:12-58)
  * The n-th, ... serving calls on ctx (1-based ordinals, counted from this call)

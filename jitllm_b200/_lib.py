@@ -82,12 +82,14 @@ SYMBOLS = {
     "jl_test_fail_at": (_I, [_VP, C.POINTER(C.c_int), _I]),
     "jl_noalloc_max_k": (_I, []),
     "jl_matvec_q4k_noalloc": (_I, [_VP, _VP, _VP, _I, _I, _VP]),
-    "jl_aux_add_rmsnorm": (_I, [_VP, _VP, _VP, C.c_float, _VP, _I, _I, _VP]),
-    "jl_aux_silu_mul": (_I, [_VP, _VP, _I, _I, _VP]),
+    "jl_aux_add_rmsnorm": (_I, [_VP, _VP, _VP, C.c_float, _VP, _VP, _I, _I, _VP]),
+    "jl_aux_silu_mul": (_I, [_VP, _VP, _VP, _I, _I, _VP]),
     "jl_aux_argmax": (_I, [_VP, _VP, _I, _I, _VP]),
     "jl_aux_rope_kv": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _VP]),
     "jl_aux_attn_scratch_bytes": (C.c_size_t, [_I, _I, _I, _I]),
-    "jl_aux_attn_decode": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _VP]),
+    "jl_aux_attn_decode": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _VP]),
+    "jl_decode_operand": (_VP, [_VP, _VP, _I]),
+    "jl_matvec_dev_prepared": (_I, [_VP, _VP, _VP, _I, _VP]),
 }
 
 _lib = None

@@ -3,6 +3,7 @@
 // decoder harness can chain the quantized matvecs with ONE short launch between them (each joins the
 // programmatic-dependent-launch chain the matvec kernels use); they are not part of the drop-in seam.
 #include "jl_internal.cuh"
+#include "q4k_prep.cuh"
 #include <cuda_bf16.h>
 
 #define AUX_PDL()                                                   \
@@ -55,6 +56,62 @@ __global__ void __launch_bounds__(256) aux_add_rmsnorm_kernel(float *x_io, const
         float4 g = w ? ((const float4 *)w)[i] : make_float4(1.f, 1.f, 1.f, 1.f);
         o4[i] = make_float4(v.x * r * g.x, v.y * r * g.y, v.z * r * g.z, v.w * r * g.w);
     }
+}
+
+// The same for rows that are whole 256-element super-blocks: a warp owns a super-block in both passes, so it
+// can also write the next Q4_K matvec's prepared activation operand (operand != NULL) with no launch between.
+__global__ void __launch_bounds__(256) aux_add_rmsnorm_sb_kernel(float *x_io, const float *delta, const float *w, float eps,
+                                                                  float *out, uint8_t *operand, int h) {
+    __shared__ float red[8];
+    AUX_PDL();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nsb = h / 256, row = blockIdx.x;
+    float4 *x4 = (float4 *)(x_io + (size_t)row * h);
+    const float4 *d4 = delta ? (const float4 *)(delta + (size_t)row * h) : nullptr;
+    float ss = 0.f;
+    for (int sb = warp; sb < nsb; sb += 8)
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+            const int i = sb * 64 + hf * 32 + lane;
+            float4 v = x4[i];
+            if (d4) {
+                const float4 d = d4[i];
+                v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+                x4[i] = v;
+            }
+            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+    const float r = rsqrtf(aux_block_sum(ss, red) / (float)h + eps);
+    for (int sb = warp; sb < nsb; sb += 8) {
+        float4 v[2];
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+            const int i = sb * 64 + hf * 32 + lane;
+            const float4 a = x4[i];                              // this thread's own writes
+            const float4 g = w ? ((const float4 *)w)[i] : make_float4(1.f, 1.f, 1.f, 1.f);
+            v[hf] = make_float4(a.x * r * g.x, a.y * r * g.y, a.z * r * g.z, a.w * r * g.w);
+            if (out) ((float4 *)(out + (size_t)row * h))[i] = v[hf];
+        }
+        if (operand) q4k_prep_sb_vals(v[0], v[1], operand + ((size_t)row * nsb + sb) * Q4K_XP_SB_BYTES, lane);
+    }
+}
+
+// One warp per 256 outputs: out and/or the prepared operand of the matvec that consumes them.
+__global__ void __launch_bounds__(128) aux_silu_mul_sb_kernel(float *out, uint8_t *operand, const float *gu, int ffn) {
+    AUX_PDL();
+    const int lane = threadIdx.x & 31, sb = blockIdx.x * 4 + (threadIdx.x >> 5), row = blockIdx.y, nsb = ffn / 256;
+    if (sb >= nsb) return;
+    const float4 *g4 = (const float4 *)(gu + (size_t)row * 2 * ffn);
+    const float4 *u4 = g4 + ffn / 4;
+    float4 v[2];
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+        const int i = sb * 64 + hf * 32 + lane;
+        const float4 g = g4[i], u = u4[i];
+        v[hf] = make_float4(g.x / (1.f + __expf(-g.x)) * u.x, g.y / (1.f + __expf(-g.y)) * u.y,
+                            g.z / (1.f + __expf(-g.z)) * u.z, g.w / (1.f + __expf(-g.w)) * u.w);
+        if (out) ((float4 *)(out + (size_t)row * ffn))[i] = v[hf];
+    }
+    if (operand) q4k_prep_sb_vals(v[0], v[1], operand + ((size_t)row * nsb + sb) * Q4K_XP_SB_BYTES, lane);
 }
 
 __global__ void __launch_bounds__(256) aux_silu_mul_kernel(float *out, const float *gu, int ffn) {
@@ -114,10 +171,12 @@ __device__ __forceinline__ void aux_bf16x8(const uint4 &v, float *f) {
 }
 
 template <int G>
-__global__ void __launch_bounds__(128) aux_attn_decode_kernel(float *out, const __nv_bfloat16 *q, const __nv_bfloat16 *k_cache,
-                                                              const __nv_bfloat16 *v_cache, const long long *pos_dev,
-                                                              float *part, unsigned *tickets, int hkv, int max_len, int nsplit) {
-    constexpr int STRIDE = G * (ATT_D + 2);
+__global__ void __launch_bounds__(128) aux_attn_decode_kernel(float *out, uint8_t *operand, const __nv_bfloat16 *q,
+                                                              const __nv_bfloat16 *k_cache, const __nv_bfloat16 *v_cache,
+                                                              const long long *pos_dev, float *part, unsigned *tickets, int hkv,
+                                                              int max_len, int nsplit) {
+    constexpr int HDR = (2 * G + 3) & ~3;              // max[G], sum[G], padded so that the V part is 16-byte aligned
+    constexpr int STRIDE = HDR + G * ATT_D;
     // K and V tiles of the chunk, staged with coalesced 16-byte loads (all in flight at once); the
     // cross-group reduction buffer red[8][G][128] reuses the tiles once they have been consumed.
     __shared__ __align__(16) uint8_t tiles[2 * ATT_CHUNK * ATT_ROW];
@@ -223,7 +282,7 @@ __global__ void __launch_bounds__(128) aux_attn_decode_kernel(float *out, const 
             float o = 0.f;
 #pragma unroll
             for (int g8 = 0; g8 < 8; ++g8) o += red[g8][h][t];
-            my[2 * G + h * ATT_D + t] = o;
+            my[HDR + h * ATT_D + t] = o;
         }
     } else if (t < G) {
         my[t] = -INFINITY;
@@ -237,19 +296,62 @@ __global__ void __launch_bounds__(128) aux_attn_decode_kernel(float *out, const 
     __threadfence();
     const float *base = part + ((size_t)row * hkv + kv) * nsplit * STRIDE;
     const int nlive = (int)((len + ATT_CHUNK - 1) / ATT_CHUNK);   // chunks past the sequence hold nothing
+    // Merge: warp w takes heads w, w+4, ...; its lanes first scan the chunks' (max, sum) pairs side by side,
+    // then each lane owns four output dims and walks the chunks in ascending order (bit-stable) with the
+    // loads of eight chunks in flight at a time.
+    {
+        const int warp = t >> 5, lane = t & 31;
+        for (int h = warp; h < G; h += 4) {
+            float M = -INFINITY;
+            for (int s = lane; s < nlive; s += 32) M = fmaxf(M, __ldcg(base + (size_t)s * STRIDE + h));
+            for (int o = 16; o; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+            float L = 0.f;
+            for (int s = lane; s < nlive; s += 32)
+                L += __ldcg(base + (size_t)s * STRIDE + G + h) * __expf(__ldcg(base + (size_t)s * STRIDE + h) - M);
+            for (int o = 16; o; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            const float *ob = base + HDR + h * ATT_D + 4 * lane;
+            int s = 0;
+            for (; s + 8 <= nlive; s += 8) {
+                float4 v[8];
+                float e[8];
 #pragma unroll
-    for (int h = 0; h < G; ++h) {
-        float M = -INFINITY;
-        for (int s = 0; s < nlive; ++s) M = fmaxf(M, __ldcg(base + (size_t)s * STRIDE + h));
-        float L = 0.f, o = 0.f;
-        for (int s = 0; s < nlive; ++s) {                      // ascending chunk order: bit-stable
-            const float e = __expf(__ldcg(base + (size_t)s * STRIDE + h) - M);
-            L = fmaf(__ldcg(base + (size_t)s * STRIDE + G + h), e, L);
-            o = fmaf(__ldcg(base + (size_t)s * STRIDE + 2 * G + h * ATT_D + t), e, o);
+                for (int u = 0; u < 8; ++u) {
+                    v[u] = __ldcg(reinterpret_cast<const float4 *>(ob + (size_t)(s + u) * STRIDE));
+                    e[u] = __ldcg(base + (size_t)(s + u) * STRIDE + h);
+                }
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const float w = __expf(e[u] - M);
+                    acc.x = fmaf(v[u].x, w, acc.x); acc.y = fmaf(v[u].y, w, acc.y);
+                    acc.z = fmaf(v[u].z, w, acc.z); acc.w = fmaf(v[u].w, w, acc.w);
+                }
+            }
+            for (; s < nlive; ++s) {
+                const float4 v = __ldcg(reinterpret_cast<const float4 *>(ob + (size_t)s * STRIDE));
+                const float w = __expf(__ldcg(base + (size_t)s * STRIDE + h) - M);
+                acc.x = fmaf(v.x, w, acc.x); acc.y = fmaf(v.y, w, acc.y);
+                acc.z = fmaf(v.z, w, acc.z); acc.w = fmaf(v.w, w, acc.w);
+            }
+            const float inv = L > 0.f ? 1.f / L : 0.f;
+            const float4 res = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+            if (out) *reinterpret_cast<float4 *>(out + (size_t)row * hq * ATT_D + (size_t)(kv * G + h) * ATT_D + 4 * lane) = res;
+            if (operand) reinterpret_cast<float4 *>(tiles)[h * (ATT_D / 4) + lane] = res;
         }
-        out[(size_t)row * hq * ATT_D + (size_t)(kv * G + h) * ATT_D + t] = L > 0.f ? o / L : 0.f;
     }
     if (t == 0) tickets[row * hkv + kv] = 0;                    // ready for the next launch
+    if constexpr (G % 2 == 0) {
+        if (operand) {
+            // two heads = one 256-element super-block of the output projection's input: write its prepared operand
+            __syncthreads();
+            const int warp = t >> 5, lane = t & 31;
+            if (warp < G / 2) {
+                const float4 *c4 = reinterpret_cast<const float4 *>(tiles) + warp * 64;
+                q4k_prep_sb_vals(c4[lane], c4[32 + lane],
+                                 operand + ((size_t)row * (hq / 2) + kv * (G / 2) + warp) * Q4K_XP_SB_BYTES, lane);
+            }
+        }
+    }
 }
 
 // First index of the row maximum (ties: the lowest index, as a sequential scan gives).
@@ -285,14 +387,22 @@ __global__ void __launch_bounds__(1024) aux_argmax_kernel(long long *out, const 
 static size_t aux_attn_ticket_bytes(int n, int hkv) { return (((size_t)n * hkv * 4) + 255) & ~(size_t)255; }
 
 // ------------------------------------------------------------------ C ABI
-JL_EXPORT int jl_aux_add_rmsnorm(float *x_io, const float *delta, const float *w, float eps, float *out, int n, int h,
-                                 void *stream) {
-    if (!x_io || !out || n < 1 || h < 4 || h % 4) return JL_EINVAL;
+JL_EXPORT int jl_aux_add_rmsnorm(float *x_io, const float *delta, const float *w, float eps, float *out, void *operand_out,
+                                 int n, int h, void *stream) {
+    if (!x_io || (!out && !operand_out) || n < 1 || h < 4 || h % 4) return JL_EINVAL;
+    if (h % 256 == 0)
+        return aux_launch(aux_add_rmsnorm_sb_kernel, dim3(n), dim3(256), (cudaStream_t)stream, x_io, delta, w, eps, out,
+                          (uint8_t *)operand_out, h);
+    if (operand_out || !out) return JL_EINVAL;          // the prepared operand is made of whole super-blocks
     return aux_launch(aux_add_rmsnorm_kernel, dim3(n), dim3(256), (cudaStream_t)stream, x_io, delta, w, eps, out, h);
 }
 
-JL_EXPORT int jl_aux_silu_mul(float *out, const float *gu, int n, int ffn, void *stream) {
-    if (!out || !gu || n < 1 || ffn < 4 || ffn % 4) return JL_EINVAL;
+JL_EXPORT int jl_aux_silu_mul(float *out, void *operand_out, const float *gu, int n, int ffn, void *stream) {
+    if ((!out && !operand_out) || !gu || n < 1 || ffn < 4 || ffn % 4) return JL_EINVAL;
+    if (ffn % 256 == 0)
+        return aux_launch(aux_silu_mul_sb_kernel, dim3((ffn / 256 + 3) / 4, n), dim3(128), (cudaStream_t)stream, out,
+                          (uint8_t *)operand_out, gu, ffn);
+    if (operand_out || !out) return JL_EINVAL;
     int gx = (ffn / 4 + 255) / 256;
     if (gx > 64) gx = 64;
     return aux_launch(aux_silu_mul_kernel, dim3(gx, n), dim3(256), (cudaStream_t)stream, out, gu, ffn);
@@ -316,26 +426,28 @@ JL_EXPORT int jl_aux_rope_kv(void *q_out_bf16, const float *qkv, void *k_cache_b
 JL_EXPORT size_t jl_aux_attn_scratch_bytes(int n, int hq, int hkv, int max_len) {
     if (n < 1 || hq < 1 || hkv < 1 || hq % hkv || max_len < 1) return 0;
     const int g = hq / hkv, nsplit = (max_len + ATT_CHUNK - 1) / ATT_CHUNK;
-    return aux_attn_ticket_bytes(n, hkv) + (size_t)n * hkv * nsplit * g * (ATT_D + 2) * sizeof(float);
+    return aux_attn_ticket_bytes(n, hkv) + (size_t)n * hkv * nsplit * (((2 * g + 3) & ~3) + g * ATT_D) * sizeof(float);
 }
 
-JL_EXPORT int jl_aux_attn_decode(float *out, const void *q_bf16, const void *k_cache_bf16, const void *v_cache_bf16,
-                                 const long long *pos_dev, void *scratch_zeroed_once, int n, int hq, int hkv, int d, int max_len,
-                                 void *stream) {
-    if (!out || !q_bf16 || !k_cache_bf16 || !v_cache_bf16 || !pos_dev || !scratch_zeroed_once) return JL_EINVAL;
+JL_EXPORT int jl_aux_attn_decode(float *out, void *operand_out, const void *q_bf16, const void *k_cache_bf16,
+                                 const void *v_cache_bf16, const long long *pos_dev, void *scratch_zeroed_once, int n, int hq,
+                                 int hkv, int d, int max_len, void *stream) {
+    if ((!out && !operand_out) || !q_bf16 || !k_cache_bf16 || !v_cache_bf16 || !pos_dev || !scratch_zeroed_once) return JL_EINVAL;
     if (n < 1 || hkv < 1 || hq % hkv || d != ATT_D || max_len < 1) return JL_EINVAL;
     const int g = hq / hkv, nsplit = (max_len + ATT_CHUNK - 1) / ATT_CHUNK;
+    if (operand_out && (g & 1)) return JL_EINVAL;      // a super-block of the operand is two heads
     unsigned *tickets = (unsigned *)scratch_zeroed_once;
     float *part = (float *)((uint8_t *)scratch_zeroed_once + aux_attn_ticket_bytes(n, hkv));
     const dim3 grid(nsplit, hkv, n), block(128);
     cudaStream_t s = (cudaStream_t)stream;
+    uint8_t *op = (uint8_t *)operand_out;
     const __nv_bfloat16 *q = (const __nv_bfloat16 *)q_bf16, *kc = (const __nv_bfloat16 *)k_cache_bf16,
                         *vc = (const __nv_bfloat16 *)v_cache_bf16;
     switch (g) {
-    case 1: return aux_launch(aux_attn_decode_kernel<1>, grid, block, s, out, q, kc, vc, pos_dev, part, tickets, hkv, max_len, nsplit);
-    case 2: return aux_launch(aux_attn_decode_kernel<2>, grid, block, s, out, q, kc, vc, pos_dev, part, tickets, hkv, max_len, nsplit);
-    case 4: return aux_launch(aux_attn_decode_kernel<4>, grid, block, s, out, q, kc, vc, pos_dev, part, tickets, hkv, max_len, nsplit);
-    case 8: return aux_launch(aux_attn_decode_kernel<8>, grid, block, s, out, q, kc, vc, pos_dev, part, tickets, hkv, max_len, nsplit);
+    case 1: return aux_launch(aux_attn_decode_kernel<1>, grid, block, s, out, op, q, kc, vc, pos_dev, part, tickets, hkv, max_len, nsplit);
+    case 2: return aux_launch(aux_attn_decode_kernel<2>, grid, block, s, out, op, q, kc, vc, pos_dev, part, tickets, hkv, max_len, nsplit);
+    case 4: return aux_launch(aux_attn_decode_kernel<4>, grid, block, s, out, op, q, kc, vc, pos_dev, part, tickets, hkv, max_len, nsplit);
+    case 8: return aux_launch(aux_attn_decode_kernel<8>, grid, block, s, out, op, q, kc, vc, pos_dev, part, tickets, hkv, max_len, nsplit);
     }
     return JL_ENOTSUP;
 }

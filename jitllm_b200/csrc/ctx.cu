@@ -311,6 +311,34 @@ JL_EXPORT int jl_matvec_dev(jl_ctx *ctx, float *out_dev, const jl_weight *w, con
     return rc;
 }
 
+// Where a producer kernel writes the decode kernel's prepared activation operand for weight `w`, or NULL
+// when this weight / token count is not served by the Q4_K tensor-core decode kernel's split form.
+JL_EXPORT void *jl_decode_operand(jl_ctx *ctx, const jl_weight *w, int ntok) {
+    if (!ctx || !w || ntok < 1 || ntok > 8) return nullptr;
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    jl_choice ch;
+    if (w->type != JL_TYPE_Q4_K || !w->has_map_sb16 || (ctx->opts.flags & JL_FLAG_NO_TMA)) return nullptr;
+    if (choose(ctx, w->type, w->nrows, w->k, ntok, &ch) != JL_OK || ch.kernel != JL_K_MMA) return nullptr;
+    if (ctx->scratch_cap < jl_gemv_scratch_bytes(w->type, w->k, ntok)) return nullptr;
+    return ctx->scratch;
+}
+
+JL_EXPORT int jl_matvec_dev_prepared(jl_ctx *ctx, float *out_dev, const jl_weight *w, int ntok, void *stream) {
+    if (!ctx || !out_dev || !w || ntok < 1 || ntok > 8) return JL_EINVAL;
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    int rc = serving_prologue(ctx);
+    if (rc) return rc;
+    JL_CUDA(ctx, cudaSetDevice(ctx->device));
+    jl_choice ch;
+    if (w->type != JL_TYPE_Q4_K || !w->has_map_sb16 || (ctx->opts.flags & JL_FLAG_NO_TMA) ||
+        choose(ctx, w->type, w->nrows, w->k, ntok, &ch) != JL_OK || ch.kernel != JL_K_MMA)
+        return jl_set_err(ctx, JL_DECLINED, "no prepared-operand form for this weight (jl_decode_operand returned NULL)");
+    int warps = ctx->opts.pin_warps > 0 ? ctx->opts.pin_warps : 0;
+    rc = jl_launch_gemv(ctx, out_dev, w, 0, nullptr, ntok, JL_K_MMA, warps, (cudaStream_t)stream);
+    if (rc == JL_OK) ctx->st.served++;
+    return rc;
+}
+
 JL_EXPORT int jl_matmul_dev(jl_ctx *ctx, void *out_dev, int out_dtype, const jl_weight *w, const void *x_dev,
                             int x_dtype, int ntok, void *stream) {
     if (!ctx || !out_dev || !w || !x_dev || ntok < 1) return JL_EINVAL;

@@ -189,9 +189,24 @@ class Decoder:
             if rc != 0:
                 raise RuntimeError(f"jl_aux call failed with status {rc}")
 
+        ctx = self.dev.ctx
+        l0 = self.layers[0]
+        # With few sequences every producer writes the next matvec's prepared activation operand itself
+        # (no conversion launch in between); otherwise f32 rows go to the GEMM path.
+        ops = [lib.jl_decode_operand(ctx, w.handle, B) for w in (l0["qkv"], l0["o"], l0["gu"], l0["down"], self.head)]
+        prep = B <= 8 and all(ops) and (self.hq // self.hkv) % 2 == 0
+        op = ops[0] if prep else None
+
+        def mv(w, x_f32):
+            if not prep:
+                return self.mm(w, x_f32)
+            out = torch.empty(B, w.nrows, **f32)
+            ok(lib.jl_matvec_dev_prepared(ctx, out.data_ptr(), w.handle, B, st))
+            return out
+
         def norm(delta):
             ok(lib.jl_aux_add_rmsnorm(x.data_ptr(), delta.data_ptr() if delta is not None else None, self.norm_w.data_ptr(),
-                                      c.eps, h.data_ptr(), B, c.hidden, st))
+                                      c.eps, None if prep else h.data_ptr(), op, B, c.hidden, st))
 
         x = self.emb[tokens].float()
         h = torch.empty_like(x)
@@ -200,17 +215,16 @@ class Decoder:
         a = torch.empty(B, self.ffn_l, **f32)
         norm(None)
         for li, l in enumerate(self.layers):
-            qkv = self.mm(l["qkv"], h)
+            qkv = mv(l["qkv"], h)
             kc, vc = self.k_cache[li], self.v_cache[li]
             ok(lib.jl_aux_rope_kv(qb.data_ptr(), qkv.data_ptr(), kc.data_ptr(), vc.data_ptr(), pos_dev.data_ptr(),
                                   self.cos.data_ptr(), self.sin.data_ptr(), B, self.hq, self.hkv, d, self.max_len, st))
-            ok(lib.jl_aux_attn_decode(att.data_ptr(), qb.data_ptr(), kc.data_ptr(), vc.data_ptr(), pos_dev.data_ptr(),
-                                      self._att_scratch.data_ptr(), B, self.hq, self.hkv, d, self.max_len, st))
-            norm(self._allreduce(self.mm(l["o"], att)))
-            ok(lib.jl_aux_silu_mul(a.data_ptr(), self.mm(l["gu"], h).data_ptr(), B, self.ffn_l, st))
-            norm(self._allreduce(self.mm(l["down"], a)))          # also the next layer's (or the final) norm
-        torch = self.torch
-        logits = self.last_logits = self.mm(self.head, h)
+            ok(lib.jl_aux_attn_decode(None if prep else att.data_ptr(), op, qb.data_ptr(), kc.data_ptr(), vc.data_ptr(),
+                                      pos_dev.data_ptr(), self._att_scratch.data_ptr(), B, self.hq, self.hkv, d, self.max_len, st))
+            norm(self._allreduce(mv(l["o"], att)))
+            ok(lib.jl_aux_silu_mul(None if prep else a.data_ptr(), op, mv(l["gu"], h).data_ptr(), B, self.ffn_l, st))
+            norm(self._allreduce(mv(l["down"], a)))             # also the next layer's (or the final) norm
+        logits = self.last_logits = mv(self.head, h)
         if self.world > 1:
             import torch.distributed as dist
             parts = [torch.empty_like(logits) for _ in range(self.world)]
