@@ -94,6 +94,12 @@ typedef struct jl_opts {
  * (one launch, shortest dependency chain) or by a separate prep kernel (least work). */
 #define JL_FLAG_DECODE_FUSED 4u
 #define JL_FLAG_DECODE_SPLIT 8u
+/* The caller keeps several independent matvecs in flight on this GPU (streams, graph branches, experts): the
+ * Q4_K decode then takes the variant with the most weight bytes in flight per SM (small CTAs, weight tiles
+ * only in shared memory, the prepared activations read through L1) instead of the one with the shortest
+ * single-launch latency. The arithmetic is the same; only the order in which the warps' f32 partial sums
+ * meet can differ (each variant is run-to-run bit-stable). */
+#define JL_FLAG_DECODE_CONCURRENT 16u
 
 typedef struct jl_ctx jl_ctx;
 typedef struct jl_weight jl_weight;

@@ -16,6 +16,8 @@ F32, F16, Q8_0, Q4_K, BF16, MXFP4 = 0, 1, 8, 12, 30, 39
 DT_F32, DT_F16, DT_BF16 = 0, 1, 2
 K_AUTO, K_SIMT, K_MMA, K_TC5 = 0, 1, 2, 3
 ACT_SILU, ACT_SWIGLU_OAI = 0, 1
+# jl_opts.flags
+FLAG_NO_PDL, FLAG_NO_TMA, FLAG_DECODE_FUSED, FLAG_DECODE_SPLIT, FLAG_DECODE_CONCURRENT = 1, 2, 4, 8, 16
 OK, DECLINED = 0, 1
 EINVAL, ECUDA, ENOMEM, EDEVICE, ETIMEDOUT, ENOTSUP, ECOMM = -1, -2, -3, -4, -5, -6, -7
 

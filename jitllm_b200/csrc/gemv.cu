@@ -171,7 +171,10 @@ q4k_xprep_kernel(const float *__restrict__ X, uint8_t *__restrict__ scratch, int
 // (what a latency-bound shape wants), at the price of every 16-row CTA redoing the
 // conversion (what a throughput-bound shape does not want). `xsrc` is X when FUSED, the
 // prepared scratch otherwise.
-template <int WARPS, int STAGES, int MINB, bool FUSED>
+// XG = the prepared operand is read from global memory (it stays in L1: every CTA of an SM reads the same
+// few KB) instead of being staged in each CTA's shared memory, which then holds weight tiles only: more CTAs
+// per SM, i.e. more weight bytes in flight.
+template <int WARPS, int STAGES, int MINB, bool FUSED, bool XG = false>
 __global__ void __launch_bounds__(WARPS * 32, MINB)
 gemv_q4k_tma_kernel(const __grid_constant__ CUtensorMap wmap, int row0, const void *__restrict__ xsrc,
                     float *__restrict__ Y, int nrows, int nsb, int ntok, int *status) {
@@ -183,7 +186,7 @@ gemv_q4k_tma_kernel(const __grid_constant__ CUtensorMap wmap, int row0, const vo
     //                | red[WARPS][16] | barriers [WARPS][STAGES] + 1
     uint8_t *tiles = smem + (size_t)warp * STAGES * Q4K_TILE_BYTES;
     uint8_t *xop = smem + (size_t)WARPS * STAGES * Q4K_TILE_BYTES;
-    const uint32_t xop_bytes = (uint32_t)(FUSED ? WARPS : nsb) * Q4K_XP_SB_BYTES;
+    const uint32_t xop_bytes = XG ? 0u : (uint32_t)(FUSED ? WARPS : nsb) * Q4K_XP_SB_BYTES;
     float *red = reinterpret_cast<float *>(xop + xop_bytes + Q4K_XP_ZERO_BYTES);
     uint64_t *bars_all = reinterpret_cast<uint64_t *>(red + WARPS * 16);
     uint64_t *bars = bars_all + warp * STAGES;
@@ -212,7 +215,7 @@ gemv_q4k_tma_kernel(const __grid_constant__ CUtensorMap wmap, int row0, const vo
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     bool lost = false;
-    if (!FUSED) {
+    if (!FUSED && !XG) {
         if (tid == 0) {
             mbar_arrive_expect_tx(smem_u32(xbar), xop_bytes);
             bulk_load_1d(smem_u32(xop), static_cast<const uint8_t *>(xsrc) + (size_t)tok * xop_bytes, xop_bytes,
@@ -229,7 +232,8 @@ gemv_q4k_tma_kernel(const __grid_constant__ CUtensorMap wmap, int row0, const vo
     for (int it = 0, sb = warp; sb < nsb && !lost; it++, sb += WARPS) {
         const int s = it % STAGES;
         const uint32_t parity = (uint32_t)(it / STAGES) & 1u;
-        uint8_t *xsb = xop + (size_t)(FUSED ? warp : sb) * Q4K_XP_SB_BYTES;
+        uint8_t *xsb = XG ? const_cast<uint8_t *>(static_cast<const uint8_t *>(xsrc)) + ((size_t)tok * nsb + sb) * Q4K_XP_SB_BYTES
+                          : xop + (size_t)(FUSED ? warp : sb) * Q4K_XP_SB_BYTES;
         if (FUSED) {
             __syncwarp();  // the previous super-block's operand has been consumed
             q4k_prep_sb(reinterpret_cast<const float4 *>(static_cast<const float *>(xsrc) +
@@ -237,7 +241,16 @@ gemv_q4k_tma_kernel(const __grid_constant__ CUtensorMap wmap, int row0, const vo
             __syncwarp();
         }
         const uint8_t *xf = bsel ? xsb + t * Q4K_XP_GROUP_BYTES + (g & 1) * 8 : zero;
-        const int4 ax = *reinterpret_cast<const int4 *>(xsb + Q4K_XP_AUX_OFS + t * 16);
+        const int4 ax = XG ? __ldg(reinterpret_cast<const int4 *>(xsb + Q4K_XP_AUX_OFS + t * 16))
+                           : *reinterpret_cast<const int4 *>(xsb + Q4K_XP_AUX_OFS + t * 16);
+        uint2 xfe[4], xfo[4];
+        if (XG) {
+#pragma unroll
+            for (int cp = 0; cp < 4; cp++) {
+                xfe[cp] = bsel ? __ldg(reinterpret_cast<const uint2 *>(xf + cp * 16)) : make_uint2(0u, 0u);
+                xfo[cp] = bsel ? __ldg(reinterpret_cast<const uint2 *>(xf + 64 + cp * 16)) : make_uint2(0u, 0u);
+            }
+        }
         if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(bars + s), parity))) { lost = true; break; }
         const uint8_t *tile = tiles + s * Q4K_TILE_BYTES;
         const uint4 hA = *reinterpret_cast<const uint4 *>(tile + g * 144);
@@ -262,8 +275,8 @@ gemv_q4k_tma_kernel(const __grid_constant__ CUtensorMap wmap, int row0, const vo
         const uint32_t m4 = 0x0F0F0F0Fu;
 #pragma unroll
         for (int cp = 0; cp < 4; cp++) {
-            const uint2 fe = *reinterpret_cast<const uint2 *>(xf + cp * 16);
-            const uint2 fo = *reinterpret_cast<const uint2 *>(xf + 64 + cp * 16);
+            const uint2 fe = XG ? xfe[cp] : *reinterpret_cast<const uint2 *>(xf + cp * 16);
+            const uint2 fo = XG ? xfo[cp] : *reinterpret_cast<const uint2 *>(xf + 64 + cp * 16);
             const uint32_t a0 = wa[2 * cp], a2 = wa[2 * cp + 1], a1 = wb[2 * cp], a3 = wb[2 * cp + 1];
             mma_u8s8(ce, a0 & m4, a1 & m4, a2 & m4, a3 & m4, fe.x, fe.y);
             mma_u8s8(co, (a0 >> 4) & m4, (a1 >> 4) & m4, (a2 >> 4) & m4, (a3 >> 4) & m4, fo.x, fo.y);
@@ -308,8 +321,8 @@ gemv_q4k_tma_kernel(const __grid_constant__ CUtensorMap wmap, int row0, const vo
         if (row < nrows) Y[(size_t)tok * nrows + row] = sum;
     }
 }
-static size_t q4k_tma_smem(int warps, int stages, int nsb, bool fused = false) {
-    return (size_t)warps * stages * Q4K_TILE_BYTES + (size_t)(fused ? warps : nsb) * Q4K_XP_SB_BYTES + Q4K_XP_ZERO_BYTES +
+static size_t q4k_tma_smem(int warps, int stages, int nsb, bool fused = false, bool xg = false) {
+    return (size_t)warps * stages * Q4K_TILE_BYTES + (xg ? 0 : (size_t)(fused ? warps : nsb) * Q4K_XP_SB_BYTES) + Q4K_XP_ZERO_BYTES +
            (size_t)warps * 16 * 4 + (size_t)(warps * stages + 1) * 8;
 }
 
@@ -329,7 +342,7 @@ int jl_gemv_choice(jl_ctx *ctx, uint32_t type, int nrows, int k, int ntok, jl_ch
     jl_choice c = {};
     int pin = ctx ? ctx->opts.pin_kernel : JL_K_AUTO;
     int warps = ctx && ctx->opts.pin_warps > 0 ? ctx->opts.pin_warps : 0;
-    if (warps != 2 && warps != 4 && warps != 8 && warps != 16 && warps != 108 && warps != 116) warps = 0;
+    if (warps != 2 && warps != 4 && warps != 8 && warps != 16 && warps != 108 && warps != 116 && (warps < 200 || warps > 299)) warps = 0;
     // the activation operand of the whole row must fit one CTA's shared memory
     bool mma_ok = type == JL_TYPE_Q4_K && k % 256 == 0 && q4k_tma_smem(8, 4, k / 256) <= 200 * 1024;
     if (type == JL_TYPE_Q8_0 && k % 256 == 0 && pin != JL_K_SIMT) {
@@ -393,7 +406,12 @@ int jl_launch_gemv(jl_ctx *ctx, float *out_dev, const jl_weight *w, int expert, 
         if (ctx->opts.flags & JL_FLAG_DECODE_FUSED) fused = true;
         if (ctx->opts.flags & JL_FLAG_DECODE_SPLIT) fused = false;
         const bool prepared = x_dev == nullptr;   // the caller's kernels wrote the operand into the scratch already
-        if (prepared) fused = false;
+        if (!warps && (ctx->opts.flags & JL_FLAG_DECODE_CONCURRENT) && !(ctx->opts.flags & JL_FLAG_DECODE_FUSED)) {
+            // many short-lived CTAs pay for their launch: two warps x eight-plus super-blocks each once a
+            // launch has enough row groups to fill the GPU by itself, four warps otherwise
+            warps = (nrows + 15) / 16 >= 512 ? 223 : 243;
+        }
+        if (prepared || warps >= 200) fused = false;
         if (!fused && !prepared) {
             cudaLaunchConfig_t cfg = {};
             cfg.gridDim = dim3((nsb + 3) / 4, ntok); cfg.blockDim = dim3(128); cfg.stream = s;
@@ -403,30 +421,40 @@ int jl_launch_gemv(jl_ctx *ctx, float *out_dev, const jl_weight *w, int expert, 
         }
         const void *xsrc = fused ? (const void *)x_dev : (const void *)scratch;
         dim3 grid((nrows + 15) / 16, ntok);
-#define LAUNCH_Q4K_TMA(WP, ST, MB, FU)                                                                  \
+#define LAUNCH_Q4K_TMA(WP, ST, MB, FU, XG)                                                               \
     do {                                                                                                \
-        size_t smem = q4k_tma_smem(WP, ST, nsb, FU);                                                    \
+        size_t smem = q4k_tma_smem(WP, ST, nsb, FU, XG);                                                    \
         if (smem > 48 * 1024)                                                                           \
-            JL_CUDA(ctx, cudaFuncSetAttribute(gemv_q4k_tma_kernel<WP, ST, MB, FU>,                      \
+            JL_CUDA(ctx, cudaFuncSetAttribute(gemv_q4k_tma_kernel<WP, ST, MB, FU, XG>,                      \
                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
         cudaLaunchConfig_t cfg = {};                                                                    \
         cfg.gridDim = grid; cfg.blockDim = dim3(WP * 32); cfg.dynamicSmemBytes = smem; cfg.stream = s;  \
         cfg.attrs = at; cfg.numAttrs = nattr;                                                           \
-        JL_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemv_q4k_tma_kernel<WP, ST, MB, FU>, w->map_sb16,         \
+        JL_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemv_q4k_tma_kernel<WP, ST, MB, FU, XG>, w->map_sb16,         \
                                         expert * nrows, xsrc, out_dev, nrows, nsb, ntok,                \
                                         ctx->dev_status));                                              \
     } while (0)
         // (warps per CTA, ring stages per warp, CTAs per SM the registers are held to, fused)
         if (fused) {
-            if (warps == 4) LAUNCH_Q4K_TMA(4, 4, 4, true);
-            else if (warps == 116) LAUNCH_Q4K_TMA(16, 2, 1, true);
-            else if (warps == 8) LAUNCH_Q4K_TMA(8, 2, 2, true);
-            else LAUNCH_Q4K_TMA(16, 1, 1, true);
+            if (warps == 4) LAUNCH_Q4K_TMA(4, 4, 4, true, false);
+            else if (warps == 116) LAUNCH_Q4K_TMA(16, 2, 1, true, false);
+            else if (warps == 8) LAUNCH_Q4K_TMA(8, 2, 2, true, false);
+            else LAUNCH_Q4K_TMA(16, 1, 1, true, false);
         } else {
-            if (warps == 2) LAUNCH_Q4K_TMA(2, 8, 8, false);
-            else if (warps == 8) LAUNCH_Q4K_TMA(8, 2, 2, false);
-            else if (warps == 108) LAUNCH_Q4K_TMA(8, 4, 2, false);
-            else LAUNCH_Q4K_TMA(4, 4, 4, false);
+            if (warps == 243) LAUNCH_Q4K_TMA(4, 3, 8, false, true);
+            else if (warps == 244) LAUNCH_Q4K_TMA(4, 4, 5, false, true);
+            else if (warps == 282) LAUNCH_Q4K_TMA(8, 2, 5, false, true);
+            else if (warps == 228) LAUNCH_Q4K_TMA(2, 8, 5, false, true);
+            else if (warps == 224) LAUNCH_Q4K_TMA(2, 4, 12, false, true);
+            else if (warps == 242) LAUNCH_Q4K_TMA(4, 2, 12, false, true);
+            else if (warps == 226) LAUNCH_Q4K_TMA(2, 6, 8, false, true);
+            else if (warps == 223) LAUNCH_Q4K_TMA(2, 3, 16, false, true);
+            else if (warps == 218) LAUNCH_Q4K_TMA(1, 8, 12, false, true);
+            else if (warps == 216) LAUNCH_Q4K_TMA(1, 16, 6, false, true);
+            else if (warps == 2) LAUNCH_Q4K_TMA(2, 8, 8, false, false);
+            else if (warps == 8) LAUNCH_Q4K_TMA(8, 2, 2, false, false);
+            else if (warps == 108) LAUNCH_Q4K_TMA(8, 4, 2, false, false);
+            else LAUNCH_Q4K_TMA(4, 4, 4, false, false);
         }
 #undef LAUNCH_Q4K_TMA
     } else {

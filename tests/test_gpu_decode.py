@@ -229,3 +229,19 @@ def test_q8_0_decode_survives_extreme_activations(orc):
         out = np.full((1, nrows), np.nan, np.float32)
         assert d.MatMul(out, Q8_0, w, np.zeros((1, k), np.float32), nrows, k, 1)
         assert not out.any()
+
+
+@pytest.mark.parametrize("nrows,k", [(16, 256), (100, 1024), (4096, 4096), (8192, 4096), (4096, 14336)])
+def test_q4k_concurrent_variant_matches_oracle(orc, nrows, k):
+    """JL_FLAG_DECODE_CONCURRENT: small CTAs, weight tiles only in shared memory, operand through L1."""
+    from jitllm_b200._lib import FLAG_DECODE_CONCURRENT
+    with Device(0, flags=FLAG_DECODE_CONCURRENT) as d:
+        out, ref, w, x = _check(d, orc, Q4_K, nrows, k, 0xB2C0 + nrows + k)
+        assert nmse(out, ref) < 1e-8
+        out2 = np.empty_like(out)
+        assert d.MatVec(out2, Q4_K, w, x, nrows, k)
+        assert np.array_equal(out.view(np.uint32), out2.view(np.uint32))
+    with Device(0) as d:
+        out3 = np.empty_like(out)
+        assert d.MatVec(out3, Q4_K, w, x, nrows, k)
+        assert parity_err(out3, out.astype(np.float64)) < 1e-5          # same arithmetic, summation order only
