@@ -302,32 +302,49 @@ __global__ void __launch_bounds__(128) aux_attn_decode_kernel(float *out, uint8_
     {
         const int warp = t >> 5, lane = t & 31;
         for (int h = warp; h < G; h += 4) {
-            float M = -INFINITY;
-            for (int s = lane; s < nlive; s += 32) M = fmaxf(M, __ldcg(base + (size_t)s * STRIDE + h));
+            // every lane keeps the (max, sum) of chunks lane, lane+32, ... (up to MAXR of them) in registers:
+            // one round trip to L2 for all of them, then the weights exp(m_s - M) are handed round by shuffle
+            constexpr int MAXR = 4;                             // 128 chunks = 8192 cached positions per merge pass
+            float mr[MAXR], lr[MAXR];
+#pragma unroll
+            for (int r = 0; r < MAXR; ++r) {
+                const int s = lane + 32 * r;
+                mr[r] = s < nlive ? __ldcg(base + (size_t)s * STRIDE + h) : -INFINITY;
+                lr[r] = s < nlive ? __ldcg(base + (size_t)s * STRIDE + G + h) : 0.f;
+            }
+            float M = fmaxf(fmaxf(mr[0], mr[1]), fmaxf(mr[2], mr[3]));
+            for (int s = lane + 32 * MAXR; s < nlive; s += 32) M = fmaxf(M, __ldcg(base + (size_t)s * STRIDE + h));
             for (int o = 16; o; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
             float L = 0.f;
-            for (int s = lane; s < nlive; s += 32)
+#pragma unroll
+            for (int r = 0; r < MAXR; ++r) {
+                mr[r] = __expf(mr[r] - M);                      // now the chunk's weight (0 for chunks that do not exist)
+                L = fmaf(lr[r], mr[r], L);
+            }
+            for (int s = lane + 32 * MAXR; s < nlive; s += 32)
                 L += __ldcg(base + (size_t)s * STRIDE + G + h) * __expf(__ldcg(base + (size_t)s * STRIDE + h) - M);
             for (int o = 16; o; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
             float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
             const float *ob = base + HDR + h * ATT_D + 4 * lane;
+            const int nreg = nlive < 32 * MAXR ? nlive : 32 * MAXR;
             int s = 0;
-            for (; s + 8 <= nlive; s += 8) {
-                float4 v[8];
-                float e[8];
 #pragma unroll
-                for (int u = 0; u < 8; ++u) {
-                    v[u] = __ldcg(reinterpret_cast<const float4 *>(ob + (size_t)(s + u) * STRIDE));
-                    e[u] = __ldcg(base + (size_t)(s + u) * STRIDE + h);
-                }
+            for (int r = 0; r < MAXR; ++r) {
+                for (int s0b = 32 * r; s0b < nreg && s0b < 32 * (r + 1); s0b += 16) {   // ascending chunk order: bit-stable
+                    float4 v[16];
 #pragma unroll
-                for (int u = 0; u < 8; ++u) {
-                    const float w = __expf(e[u] - M);
-                    acc.x = fmaf(v[u].x, w, acc.x); acc.y = fmaf(v[u].y, w, acc.y);
-                    acc.z = fmaf(v[u].z, w, acc.z); acc.w = fmaf(v[u].w, w, acc.w);
+                    for (int u = 0; u < 16; ++u)
+                        v[u] = s0b + u < nreg ? __ldcg(reinterpret_cast<const float4 *>(ob + (size_t)(s0b + u) * STRIDE))
+                                              : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                    for (int u = 0; u < 16; ++u) {
+                        const float w = __shfl_sync(0xffffffffu, mr[r], (s0b + u) & 31);
+                        acc.x = fmaf(v[u].x, w, acc.x); acc.y = fmaf(v[u].y, w, acc.y);
+                        acc.z = fmaf(v[u].z, w, acc.z); acc.w = fmaf(v[u].w, w, acc.w);
+                    }
                 }
             }
-            for (; s < nlive; ++s) {
+            for (s = nreg; s < nlive; ++s) {                    // very long sequences: the plain walk
                 const float4 v = __ldcg(reinterpret_cast<const float4 *>(ob + (size_t)s * STRIDE));
                 const float w = __expf(__ldcg(base + (size_t)s * STRIDE + h) - M);
                 acc.x = fmaf(v.x, w, acc.x); acc.y = fmaf(v.y, w, acc.y);

@@ -176,6 +176,9 @@ moe_combine_kernel(float *__restrict__ out, const float *__restrict__ y, const i
 
 // ------------------------------------------------------------ grouped GEMM
 
+#ifndef MOE_PF
+#define MOE_PF 4
+#endif
 struct moe_gemm_params {
     int mode;                    // 0: gate|up -> act(g, u);  1: down
     int n_expert, rows, k;       // rows, k of ONE expert matrix (mode 0: ffn x hidden; mode 1: hidden x ffn)
@@ -189,6 +192,7 @@ struct moe_gemm_params {
     float *outp;                 // [npairs][rows] f32
     const int *out_rowmap;       // mode 1: row of outp that sorted position pos is written to (NULL: pos)
     int npairs;
+    int bitdq;                   // every block scale byte is in [104, 128]: the conversion-free dequant applies
     int *status;
 };
 
@@ -205,6 +209,7 @@ __device__ __forceinline__ uint32_t e2m1x2_to_h2(uint32_t byte) {
 }
 // 2^(e - 127) as an f16 pair (e in [104, 140]: exact, subnormal below 113).
 __device__ __forceinline__ uint32_t e8m0_to_h2(uint32_t e) {
+    e = min(max(e, 104u), 140u);   // only an all-zero block can be outside (the upload checked the others)
     const uint32_t h = e >= 113 ? (e - 112) << 10 : 1u << (e - 103);
     return h | (h << 16);
 }
@@ -340,31 +345,31 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap xmap, const moe_gemm_params 
             const size_t grow = (size_t)e * p.rows + row;
             const uint8_t *codes = (second ? p.c1 : p.c0) + grow * nblk * 16;
             const uint8_t *ebytes = (second ? p.e1 : p.e0) + grow * p.e_stride;
-            // raw codes run four k-blocks (256 k) ahead of their use, in registers
-            uint4 qc[8], qn[8];
-            uint32_t ec[4], en[4];
+            // raw codes run MOE_PF k-blocks (64 k = 32 B of the row each) ahead of their use, in registers: slot j is
+            // refilled with k-block kb+MOE_PF the moment k-block kb has been copied out of it
+            uint4 q[2 * MOE_PF];
+            uint32_t ec[MOE_PF];
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-                qc[2 * j] = qc[2 * j + 1] = make_uint4(0, 0, 0, 0); ec[j] = 0x7F7F;
+            for (int j = 0; j < MOE_PF; j++) {
+                q[2 * j] = q[2 * j + 1] = make_uint4(0, 0, 0, 0); ec[j] = 0x7F7F;
                 if (j < nkb) {
-                    qc[2 * j] = ldg_nc16(codes + (size_t)j * 32);
-                    qc[2 * j + 1] = ldg_nc16(codes + (size_t)j * 32 + 16);
+                    q[2 * j] = ldg_nc16(codes + (size_t)j * 32);
+                    q[2 * j + 1] = ldg_nc16(codes + (size_t)j * 32 + 16);
                     ec[j] = *reinterpret_cast<const uint16_t *>(ebytes + 2 * j);
                 }
             }
-            for (int kb0 = 0; kb0 < nkb && ok; kb0 += 4) {
+            for (int kb0 = 0; kb0 < nkb && ok; kb0 += MOE_PF) {
 #pragma unroll
-              for (int j = 0; j < 4; j++) {
+              for (int j = 0; j < MOE_PF; j++) {
                 const int kb = kb0 + j;
                 if (kb >= nkb) break;
                 const uint32_t s = kb_it % SA, ph = (kb_it / SA) & 1;
-                const uint4 c0 = qc[2 * j], c1 = qc[2 * j + 1];
+                const uint4 c0 = q[2 * j], c1 = q[2 * j + 1];
                 const uint32_t e_lo = ec[j] & 0xFF, e_hi = ec[j] >> 8;
-                qn[2 * j] = qn[2 * j + 1] = make_uint4(0, 0, 0, 0); en[j] = 0x7F7F;
-                if (kb + 4 < nkb) {
-                    qn[2 * j] = ldg_nc16(codes + (size_t)(kb + 4) * 32);
-                    qn[2 * j + 1] = ldg_nc16(codes + (size_t)(kb + 4) * 32 + 16);
-                    en[j] = *reinterpret_cast<const uint16_t *>(ebytes + 2 * (kb + 4));
+                if (kb + MOE_PF < nkb) {
+                    q[2 * j] = ldg_nc16(codes + (size_t)(kb + MOE_PF) * 32);
+                    q[2 * j + 1] = ldg_nc16(codes + (size_t)(kb + MOE_PF) * 32 + 16);
+                    ec[j] = *reinterpret_cast<const uint16_t *>(ebytes + 2 * (kb + MOE_PF));
                 }
                 if (kb_it >= (uint32_t)SA) ok = tc5_wait(smem_u32(a_empty + s), ph ^ 1, abort_flag);
                 if (!ok) break;
@@ -372,15 +377,36 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap xmap, const moe_gemm_params 
 #pragma unroll
                 for (int b = 0; b < 2; b++) {           // block b of the k-block: k 32b..32b+31
                     const uint4 cw = b ? c1 : c0;
-                    const uint32_t sc = e8m0_to_h2(b ? e_hi : e_lo);
+                    const uint32_t eb = b ? e_hi : e_lo;
                     const uint32_t w[4] = {cw.x, cw.y, cw.z, cw.w};
                     uint32_t lo[8], hi[8];              // f16 pairs: elements 2i,2i+1 (low nibbles) and 16+2i,16+2i+1
+                    if (p.bitdq) {
+                        // An e2m1 code s|e1 e0|m IS the top of an f16 with exponent field e1 e0 and mantissa m...:
+                        // high byte s<<7 | (e1 e0 m)<<1 reads as value * 2^-14, subnormals included (0, 0.5). One
+                        // packed multiply by 2^14 * 2^(e-127) finishes the weight -- no conversion instruction,
+                        // whose unit the eight dequant warps saturate.
+                        // 2^(e - 113), e in [104, 128]: exponent field 6..30 (an all-zero block may carry any byte: clamp)
+                        const uint32_t mh = (min(max(eb, 104u), 128u) - 98u) << 10;
+                        const uint32_t mult = mh | (mh << 16);
 #pragma unroll
-                    for (int i = 0; i < 8; i++) {       // bytes 2i, 2i+1: byte j holds element j (low) and j+16 (high)
-                        const uint32_t wv = w[i >> 1] >> (16 * (i & 1));
-                        const uint32_t a = e2m1x2_to_h2(wv & 0xFF), bb = e2m1x2_to_h2((wv >> 8) & 0xFF);
-                        lo[i] = hmul2u(__byte_perm(a, bb, 0x5410), sc);
-                        hi[i] = hmul2u(__byte_perm(a, bb, 0x7632), sc);
+                        for (int q = 0; q < 4; q++) {
+                            const uint32_t v = w[q], vl = v << 4;
+                            const uint32_t hh = ((v & 0x70707070u) >> 3) | (v & 0x80808080u);     // elements 16+4q..16+4q+3
+                            const uint32_t hl = ((vl & 0x70707070u) >> 3) | (vl & 0x80808080u);   // elements 4q..4q+3
+                            lo[2 * q] = hmul2u(__byte_perm(hl, 0u, 0x1404), mult);
+                            lo[2 * q + 1] = hmul2u(__byte_perm(hl, 0u, 0x3424), mult);
+                            hi[2 * q] = hmul2u(__byte_perm(hh, 0u, 0x1404), mult);
+                            hi[2 * q + 1] = hmul2u(__byte_perm(hh, 0u, 0x3424), mult);
+                        }
+                    } else {
+                        const uint32_t sc = e8m0_to_h2(eb);
+#pragma unroll
+                        for (int i = 0; i < 8; i++) {       // bytes 2i, 2i+1: byte j holds element j (low) and j+16 (high)
+                            const uint32_t wv = w[i >> 1] >> (16 * (i & 1));
+                            const uint32_t a = e2m1x2_to_h2(wv & 0xFF), bb = e2m1x2_to_h2((wv >> 8) & 0xFF);
+                            lo[i] = hmul2u(__byte_perm(a, bb, 0x5410), sc);
+                            hi[i] = hmul2u(__byte_perm(a, bb, 0x7632), sc);
+                        }
                     }
                     // chunks 4b..4b+3: elements 0-7, 8-15 (low nibbles), 16-23, 24-31 (high nibbles)
                     *reinterpret_cast<uint4 *>(arow + (((uint32_t)(4 * b + 0) ^ swz) << 4)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
@@ -393,10 +419,6 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap xmap, const moe_gemm_params 
                 if (lane == 0) mbar_arrive(smem_u32(a_full + s));
                 kb_it++;
               }
-#pragma unroll
-              for (int j = 0; j < 8; j++) qc[j] = qn[j];
-#pragma unroll
-              for (int j = 0; j < 4; j++) ec[j] = en[j];
             }
         }
     } else {
@@ -572,6 +594,7 @@ static int moe_dev_locked(jl_ctx *ctx, float *out_dev, const void *h_dev, int h_
     }
     moe_gemm_params p = {};
     p.n_expert = E; p.cnt = cnt; p.off = off; p.npairs = np; p.status = ctx->dev_status; p.act = d->act;
+    p.bitdq = wg->emax <= 128 && wu->emax <= 128;
     // gate | up -> act
     p.mode = 0; p.rows = F; p.k = H; p.row_tiles = (F + TC5_M - 1) / TC5_M; p.split = hsplit;
     p.c0 = wg->data; p.c1 = wu->data; p.e0 = wg->scales; p.e1 = wu->scales; p.e_stride = wg->scale_stride;
@@ -585,6 +608,7 @@ static int moe_dev_locked(jl_ctx *ctx, float *out_dev, const void *h_dev, int h_
     }
     // down
     p.mode = 1; p.rows = H; p.k = F; p.row_tiles = (H + TC5_ROWS - 1) / TC5_ROWS; p.split = 1;
+    p.bitdq = wd->emax <= 128;
     p.c0 = wd->data; p.c1 = nullptr; p.e0 = wd->scales; p.e1 = nullptr; p.e_stride = wd->scale_stride;
     p.b0 = d->down_bias; p.b1 = nullptr; p.inv_scale = as_scale; p.outp = y;
     if (given_ids) { p.outp = out_dev; p.out_rowmap = perm; }   // top_k = 1: perm[pos] is the caller's row

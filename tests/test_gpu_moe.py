@@ -108,3 +108,23 @@ def test_declines(dev):
     out = np.zeros((1, 32), np.float32)
     assert not dev.MoeHost(out, np.zeros((1, 32), np.float32), np.zeros((1, 2), np.float32), z, z, z, 2, 1, 32, 32)
     assert dev.last_status == 1   # hidden not a multiple of 64: declined, not an error
+
+
+@pytest.mark.parametrize("e_lo,e_hi", [(-23, -10), (-6, 1), (2, 12), (-20, 10)])
+def test_moe_scale_ranges_cover_both_dequant_forms(dev, orc, e_lo, e_hi):
+    """Block scales up to 2^1 take the conversion-free dequant (code bits read as an f16, one multiply); larger
+    ones the e2m1 conversion. Both must be exact in f16, down to the subnormal end of the range."""
+    rng = synth.rng_for(4000 + e_hi)
+    E, topk, hidden, ffn, ntok = 4, 2, 128, 128, 12
+    gate, up, down = (synth.mxfp4_matrix(rng, E * ffn, hidden, e_lo, e_hi), synth.mxfp4_matrix(rng, E * ffn, hidden, e_lo, e_hi),
+                      synth.mxfp4_matrix(rng, E * hidden, ffn, e_lo, e_hi))
+    # keep the layer's output in f32 range whatever the scales are
+    h = synth.activations(rng, ntok, hidden) * np.float32(2.0 ** (-(e_lo + e_hi) // 2 - 2))
+    logits = synth.activations(rng, ntok, E)
+    out = np.zeros((ntok, hidden), np.float32)
+    assert dev.MoeHost(out, h, logits, gate, up, down, E, topk, hidden, ffn), dev.Err()
+    ref, _, _ = _oracle(orc, h, logits, gate, up, down, E, topk, hidden, ffn)
+    assert np.isfinite(out).all() and np.isfinite(ref).all()
+    assert parity_err(out, ref) <= BAR, (parity_err(out, ref), nmse(out, ref))
+    for w in (gate, up, down):
+        dev.Forget(w)
