@@ -62,7 +62,7 @@ def _worker(rank, world, port, tmp):
         assert parity_err(out.cpu().numpy(), ref) <= BAR
         # ---- tensor-parallel decoder harness against the unsharded one (same full matrices, sliced per rank)
         from jitllm_b200.decoder import Config, Decoder
-        cfg = Config(n_layer=2, hidden=512, n_head=8, n_kv=8, head_dim=128, ffn=2048, vocab=2048)
+        cfg = Config(n_layer=2, hidden=512, n_head=16, n_kv=8, head_dim=128, ffn=2048, vocab=2048)   # 8 ranks: 2 q heads = one 256-wide block each
         one = Decoder(dev, cfg, max_batch=2, max_len=48, max_prefill=16, share_full=True, seed=5)
         tp = Decoder(dev, cfg, max_batch=2, max_len=48, max_prefill=16, share_full=True, seed=5, rank=rank, world=world)
         prompt = torch.arange(7, device="cuda") * 37 % cfg.vocab
