@@ -127,7 +127,12 @@ JL_EXPORT int jl_reserve(jl_ctx *ctx, int max_rows, int max_k, int max_tok) {
     std::lock_guard<std::mutex> lk(ctx->mu);
     JL_CUDA(ctx, cudaSetDevice(ctx->device));
     const int k256 = (max_k + 255) / 256 * 256;
-    size_t need = jl_gemv_scratch_bytes(JL_TYPE_Q4_K, k256, max_tok < 8 ? max_tok : 8);
+    const int dtok = max_tok < 8 ? max_tok : 8;
+    size_t need = jl_gemv_scratch_bytes(JL_TYPE_Q4_K, k256, dtok);      // the decode kernels' operand, any format
+    for (uint32_t t : {JL_TYPE_Q8_0, JL_TYPE_MXFP4}) {
+        const size_t n = jl_gemv_scratch_bytes(t, k256, dtok);
+        if (n > need) need = n;
+    }
     size_t need_gemm = jl_gemm_tc5_scratch_bytes(max_rows, k256, max_tok, JL_DT_F32, ctx->sm_count);
     const size_t need_gemm16 = jl_gemm_tc5_scratch_bytes(max_rows, k256, max_tok, JL_DT_BF16, ctx->sm_count);
     if (need_gemm16 > need_gemm) need_gemm = need_gemm16;

@@ -329,6 +329,7 @@ static size_t q4k_tma_smem(int warps, int stages, int nsb, bool fused = false, b
 // Scratch the Q4_K tensor-core decode needs for a shape (the prepared activation operand).
 size_t jl_gemv_scratch_bytes(uint32_t type, int k, int ntok) {
     if (type == JL_TYPE_Q8_0 && k % 256 == 0) return jl_gemv_q8_scratch_bytes(k, ntok);
+    if (type == JL_TYPE_MXFP4 && k % 64 == 0) return jl_gemv_mxfp4_scratch_bytes(k, ntok);
     return type == JL_TYPE_Q4_K && k % 256 == 0 ? q4k_xprep_bytes(k / 256, ntok) : 0;
 }
 
@@ -345,6 +346,16 @@ int jl_gemv_choice(jl_ctx *ctx, uint32_t type, int nrows, int k, int ntok, jl_ch
     if (warps != 2 && warps != 4 && warps != 8 && warps != 16 && warps != 108 && warps != 116 && (warps < 200 || warps > 299)) warps = 0;
     // the activation operand of the whole row must fit one CTA's shared memory
     bool mma_ok = type == JL_TYPE_Q4_K && k % 256 == 0 && q4k_tma_smem(8, 4, k / 256) <= 200 * 1024;
+    if (type == JL_TYPE_MXFP4 && k % 64 == 0 && pin != JL_K_SIMT) {
+        // e2m1 codes become f16 A fragments by bit placement; mma.sync.m16n8k16, four tokens per launch row
+        if (pin == JL_K_TC5) return JL_DECLINED;
+        const int nspan = k / 64;
+        c.kernel = JL_K_MMA; c.warps = nspan >= 32 ? 8 : (nspan >= 16 ? 4 : (nspan >= 8 ? 2 : 1)); c.rows_per_cta = 16;
+        c.split_k = c.warps; c.tile_m = 16; c.tile_n = 8; c.tile_k = 16;
+        c.grid = (nrows + 15) / 16 * ((ntok + 3) / 4);
+        *out = c;
+        return JL_OK;
+    }
     if (type == JL_TYPE_Q8_0 && k % 256 == 0 && pin != JL_K_SIMT) {
         // int8 codes feed mma.sync.m16n8k32.s8.s8 as they are; four tokens per launch row
         if (pin == JL_K_TC5) return JL_DECLINED;
@@ -382,6 +393,8 @@ int jl_launch_gemv(jl_ctx *ctx, float *out_dev, const jl_weight *w, int expert, 
     else if (w->type == JL_TYPE_Q8_0) { data += rows_off * (size_t)k; scales += rows_off * (size_t)w->scale_stride * 2; }
     else { data += rows_off * (size_t)(k / 32) * 16; scales += rows_off * (size_t)w->scale_stride; }
 
+    if (kernel == JL_K_MMA && w->type == JL_TYPE_MXFP4)
+        return jl_launch_gemv_mxfp4(ctx, out_dev, data, scales, w->scale_stride, x_dev, nrows, k, ntok, s);
     if (kernel == JL_K_MMA && w->type == JL_TYPE_Q8_0)
         return jl_launch_gemv_q8(ctx, out_dev, data, scales, w->scale_stride, x_dev, nrows, k, ntok, s);
     if (kernel == JL_K_MMA && (!w->has_map_sb16 || (ctx->opts.flags & JL_FLAG_NO_TMA))) {

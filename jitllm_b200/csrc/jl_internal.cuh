@@ -111,6 +111,9 @@ void jl_weight_release(jl_weight *w);
 
 // gemv.cu -- decode kernels. x_dev [ntok][k] f32, out_dev [ntok][nrows] f32.
 size_t jl_gemv_q8_scratch_bytes(int k, int ntok);
+size_t jl_gemv_mxfp4_scratch_bytes(int k, int ntok);
+int jl_launch_gemv_mxfp4(jl_ctx *ctx, float *out_dev, const uint8_t *codes, const uint8_t *eplane, int e_stride,
+                         const float *x_dev, int nrows, int k, int ntok, cudaStream_t s);
 int jl_launch_gemv_q8(jl_ctx *ctx, float *out_dev, const uint8_t *codes, const uint8_t *scales, int d_stride,
                       const float *x_dev, int nrows, int k, int ntok, cudaStream_t s);
 int jl_launch_gemv(jl_ctx *ctx, float *out_dev, const jl_weight *w, int expert, const float *x_dev,

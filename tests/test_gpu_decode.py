@@ -245,3 +245,41 @@ def test_q4k_concurrent_variant_matches_oracle(orc, nrows, k):
         out3 = np.empty_like(out)
         assert d.MatVec(out3, Q4_K, w, x, nrows, k)
         assert parity_err(out3, out.astype(np.float64)) < 1e-5          # same arithmetic, summation order only
+
+
+@pytest.mark.parametrize("ntok", [1, 3, 4, 8])
+@pytest.mark.parametrize("nrows,k", [(16, 64), (5, 128), (100, 1024), (2880, 2880), (4096, 4096)])
+def test_mxfp4_tensor_core_decode_matches_oracle(orc, nrows, k, ntok):
+    """MXFP4 decode: e2m1 codes placed bit-wise into f16 A fragments (value * 2^-14, subnormals for 0 and 0.5),
+    block scales folded in f32 after the MMAs. Exercises every code and scales 2^-8..2^0."""
+    rng = synth.rng_for(0xB2F0 + nrows + k + ntok)
+    w = synth.mxfp4_matrix(rng, nrows, k)
+    x = synth.activations(rng, ntok, k)
+    with Device(0, pin_kernel=K_MMA) as d:
+        ch = d.Select(MXFP4, nrows, k, ntok)
+        assert ch is not None and ch.kernel == K_MMA and ch.tile_k == 16
+        out = np.full((ntok, nrows), np.nan, np.float32)
+        assert d.MatMul(out, MXFP4, w, x, nrows, k, ntok), d.Err()
+        ref = orc.matmul_f64(MXFP4, w, x, nrows, k, ntok)
+        assert np.isfinite(out).all()
+        assert parity_err(out, ref) <= BAR, parity_err(out, ref)
+        assert nmse(out, ref) < 1e-8
+        out2 = np.empty_like(out)
+        assert d.MatMul(out2, MXFP4, w, x, nrows, k, ntok)
+        assert np.array_equal(out.view(np.uint32), out2.view(np.uint32))
+
+
+def test_mxfp4_decode_half_codes_and_wide_scales(orc):
+    """Only the codes +-0.5 (the f16-subnormal images) and +-6, with block scales from 2^-40 to 2^+40."""
+    rng = synth.rng_for(17)
+    nrows, k = 48, 256
+    nb = nrows * k // 32
+    codes = rng.choice(np.array([1, 9, 7, 15], np.uint8), (nb, 32))
+    e = (127 + rng.integers(-40, 41, nb)).astype(np.uint8)
+    w = synth.mxfp4_from_parts(e, codes).reshape(nrows, -1)
+    x = synth.activations(rng, 2, k)
+    with Device(0) as d:
+        out = np.full((2, nrows), np.nan, np.float32)
+        assert d.MatMul(out, MXFP4, w, x, nrows, k, 2), d.Err()
+    ref = orc.matmul_f64(MXFP4, w, x, nrows, k, 2)
+    assert parity_err(out, ref) <= BAR
