@@ -130,7 +130,7 @@ JL_EXPORT int jl_reserve(jl_ctx *ctx, int max_rows, int max_k, int max_tok) {
     const int dtok = max_tok < 8 ? max_tok : 8;
     size_t need = jl_gemv_scratch_bytes(JL_TYPE_Q4_K, k256, dtok);      // the decode kernels' operand, any format
     for (uint32_t t : {JL_TYPE_Q8_0, JL_TYPE_MXFP4}) {
-        const size_t n = jl_gemv_scratch_bytes(t, k256, dtok);
+        const size_t n = jl_gemv_scratch_bytes(t, k256, t == JL_TYPE_Q8_0 ? (max_tok < 32 ? max_tok : 32) : dtok);
         if (n > need) need = n;
     }
     size_t need_gemm = jl_gemm_tc5_scratch_bytes(max_rows, k256, max_tok, JL_DT_F32, ctx->sm_count);
@@ -247,7 +247,7 @@ JL_EXPORT int jl_weight_upload_bank(jl_ctx *ctx, uint32_t type, const void *w_ho
     if (!ctx || !w_host || !out) return JL_EINVAL;
     std::lock_guard<std::mutex> lk(ctx->mu);
     JL_CUDA(ctx, cudaSetDevice(ctx->device));
-    int rc = jl_grow_scratch(ctx, jl_gemv_scratch_bytes(type, k, 8));
+    int rc = jl_grow_scratch(ctx, jl_gemv_scratch_bytes(type, k, type == JL_TYPE_Q8_0 ? 32 : 8));
     if (rc) return rc;
     rc = jl_repack_upload(ctx, type, w_host, w_bytes, n_expert, nrows, k, out);
     if (rc == JL_OK) ctx->st.resident_bytes += (*out)->raw_bytes;
@@ -272,7 +272,10 @@ JL_EXPORT void jl_weight_free(jl_ctx *ctx, jl_weight *w) {
 
 static int choose(jl_ctx *ctx, uint32_t type, int nrows, int k, int ntok, jl_choice *out) {
     int pin = ctx->opts.pin_kernel;
-    if ((pin == JL_K_TC5 || (pin == JL_K_AUTO && ntok > 8)) && jl_gemm_tc5_supported(type, nrows, k, ntok))
+    // the decode kernels serve up to 8 tokens; measured at 16 and 32 tokens the Q8_0 one (which loops over
+    // token groups with the weights in registers) only ties with or loses to the GEMM
+    const int decode_max = 8;
+    if ((pin == JL_K_TC5 || (pin == JL_K_AUTO && ntok > decode_max)) && jl_gemm_tc5_supported(type, nrows, k, ntok))
         return jl_gemm_tc5_choice(ctx, type, nrows, k, ntok, out);
     if (pin == JL_K_TC5) return JL_DECLINED;
     return jl_gemv_choice(ctx, type, nrows, k, ntok, out);
@@ -297,8 +300,12 @@ static int matmul_dev_locked(jl_ctx *ctx, void *out_dev, int out_dtype, const jl
     if (rc) return rc == JL_DECLINED ? jl_set_err(ctx, JL_DECLINED, "pinned kernel cannot serve this shape") : rc;
     if (ch.kernel == JL_K_TC5)
         return jl_launch_gemm_tc5(ctx, out_dev, out_dtype, w, expert, x_dev, x_dtype, ntok, s);
-    if (x_dtype != JL_DT_F32 || out_dtype != JL_DT_F32)
+    if (x_dtype != JL_DT_F32 || out_dtype != JL_DT_F32) {
+        // 16-bit activations or outputs: the GEMM converts them, the decode kernels do not
+        if (ctx->opts.pin_kernel == JL_K_AUTO && jl_gemm_tc5_supported(w->type, w->nrows, w->k, ntok))
+            return jl_launch_gemm_tc5(ctx, out_dev, out_dtype, w, expert, x_dev, x_dtype, ntok, s);
         return jl_set_err(ctx, JL_DECLINED, "the decode kernels take f32 activations and outputs");
+    }
     int warps = ctx->opts.pin_warps > 0 ? ctx->opts.pin_warps : 0;
     return jl_launch_gemv(ctx, (float *)out_dev, w, expert, (const float *)x_dev, ntok, ch.kernel, warps, s);
 }

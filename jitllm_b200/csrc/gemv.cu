@@ -362,7 +362,8 @@ int jl_gemv_choice(jl_ctx *ctx, uint32_t type, int nrows, int k, int ntok, jl_ch
         const int ngrp = k / 256;
         c.kernel = JL_K_MMA; c.warps = ngrp >= 8 ? 8 : (ngrp >= 4 ? 4 : (ngrp >= 2 ? 2 : 1)); c.rows_per_cta = 16;
         c.split_k = c.warps; c.tile_m = 16; c.tile_n = 8; c.tile_k = 32;
-        c.grid = (nrows + 15) / 16 * ((ntok + 3) / 4);
+        const int tgroups = (ntok + 3) / 4, ntg = tgroups >= 4 ? 4 : (tgroups >= 2 ? 2 : 1);
+        c.grid = (nrows + 15) / 16 * ((tgroups + ntg - 1) / ntg);
         *out = c;
         return JL_OK;
     }

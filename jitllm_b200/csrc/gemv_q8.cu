@@ -1,4 +1,4 @@
-// Q8_0 decode (1..8 tokens) on the int8 tensor-core path.
+// Q8_0 decode and small batches (1..32 tokens) on the int8 tensor-core path.
 //
 // Q8_0 weights ARE int8, so they feed mma.sync.m16n8k32.s32.s8.s8 unconverted: one MMA covers 16 rows
 // x one 32-element block, whose f16 scale d is applied to the integer sum afterwards. Activations are
@@ -69,27 +69,25 @@ __device__ __forceinline__ uint4 q8_ldg16(const void *p) {
     return v;
 }
 
-// grid (row groups of 16, token groups of 4); WARPS warps split the 256-element groups of the row.
-template <int WARPS>
+// grid (row groups of 16, sets of NTG token groups of 4); WARPS warps split the 256-element groups of the row.
+// NTG > 1 (batches of 5..32 tokens): the A fragments of a unit stay in registers while the CTA walks its token
+// groups, so the weights are read once per 4 * NTG tokens.
+template <int WARPS, int NTG>
 __global__ void __launch_bounds__(WARPS * 32) gemv_q8_mma_kernel(const uint8_t *__restrict__ codes, const uint16_t *__restrict__ dplane,
                                                                  int d_stride, const uint8_t *__restrict__ xop, size_t tok_stride,
                                                                  float *__restrict__ Y, int nrows, int k, int ntok) {
-    __shared__ float red[WARPS][16][4];
+    __shared__ float red[WARPS][NTG][16][4];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int row_a = min((int)blockIdx.x * 16 + g, nrows - 1), row_b = min((int)blockIdx.x * 16 + g + 8, nrows - 1);
-    const int tok0 = blockIdx.y * 4;
+    const int tok0 = blockIdx.y * 4 * NTG;
     const int ngrp = k / 256;
     const uint8_t *ca = codes + (size_t)row_a * k + t * 16, *cb = codes + (size_t)row_b * k + t * 16;
     const uint8_t *da = reinterpret_cast<const uint8_t *>(dplane + (size_t)row_a * d_stride);
     const uint8_t *db = reinterpret_cast<const uint8_t *>(dplane + (size_t)row_b * d_stride);
-    // this lane's B column: token tok0 + (g >> 1), digit g & 1; its accumulators: token tok0 + t
-    const int btok = tok0 + (g >> 1);
-    const bool blive = btok < ntok;
-    const uint8_t *xb = xop + (size_t)(blive ? btok : 0) * tok_stride + (g & 1) * 64 + t * 16;
-    const int mytok = tok0 + t;
-    const float *inv_s = reinterpret_cast<const float *>(xop + (size_t)(mytok < ntok ? mytok : 0) * tok_stride + (size_t)k * 2);
-
+    // this lane's B column in token group tg: token tok0 + 4 tg + (g >> 1), digit g & 1; its accumulators: token
+    // tok0 + 4 tg + t
+    const size_t lane_xofs = (size_t)(g & 1) * 64 + t * 16;
     // weights first: they do not depend on the kernel in front
     uint4 wa[4], wb[4], dda, ddb;
     int grp = warp;
@@ -105,13 +103,10 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_q8_mma_kernel(const uint8_t *
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");   // the prepared activations come from the kernel in front
 
-    float acc_a = 0.f, acc_b = 0.f;
-    for (; grp < ngrp; grp += WARPS) {
-        uint4 xv[4];
+    float acc_a[NTG], acc_b[NTG];
 #pragma unroll
-        for (int s = 0; s < 4; s++)
-            xv[s] = blive ? *reinterpret_cast<const uint4 *>(xb + ((size_t)grp * 4 + s) * 128) : make_uint4(0, 0, 0, 0);
-        const float is = mytok < ntok ? inv_s[grp] : 0.f;
+    for (int tg = 0; tg < NTG; tg++) acc_a[tg] = acc_b[tg] = 0.f;
+    for (; grp < ngrp; grp += WARPS) {
         const uint4 ua[4] = {wa[0], wa[1], wa[2], wa[3]}, ub[4] = {wb[0], wb[1], wb[2], wb[3]};
         const uint32_t dwa[4] = {dda.x, dda.y, dda.z, dda.w}, dwb[4] = {ddb.x, ddb.y, ddb.z, ddb.w};
         const int nx = grp + WARPS;
@@ -124,31 +119,49 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_q8_mma_kernel(const uint8_t *
             dda = q8_ldg16(da + (size_t)nx * 16);
             ddb = q8_ldg16(db + (size_t)nx * 16);
         }
-        float ga = 0.f, gb = 0.f;
+        float2 fa[4], fb[4];
 #pragma unroll
         for (int s = 0; s < 4; s++) {
-            int c0[4], c1[4];
-            q8_mma(c0, ua[s].x, ub[s].x, ua[s].y, ub[s].y, xv[s].x, xv[s].y);     // block 2s
-            q8_mma(c1, ua[s].z, ub[s].z, ua[s].w, ub[s].w, xv[s].z, xv[s].w);     // block 2s + 1
-            const float2 fa = __half22float2(*reinterpret_cast<const __half2 *>(&dwa[s]));
-            const float2 fb = __half22float2(*reinterpret_cast<const __half2 *>(&dwb[s]));
-            ga = fmaf(fa.x, (float)(256 * c0[0] + c0[1]), ga);
-            gb = fmaf(fb.x, (float)(256 * c0[2] + c0[3]), gb);
-            ga = fmaf(fa.y, (float)(256 * c1[0] + c1[1]), ga);
-            gb = fmaf(fb.y, (float)(256 * c1[2] + c1[3]), gb);
+            fa[s] = __half22float2(*reinterpret_cast<const __half2 *>(&dwa[s]));
+            fb[s] = __half22float2(*reinterpret_cast<const __half2 *>(&dwb[s]));
         }
-        acc_a = fmaf(ga, is, acc_a);
-        acc_b = fmaf(gb, is, acc_b);
+#pragma unroll
+        for (int tg = 0; tg < NTG; tg++) {
+            const int btok = tok0 + 4 * tg + (g >> 1), mytok = tok0 + 4 * tg + t;
+            const bool blive = btok < ntok;
+            const uint8_t *xb = xop + (size_t)(blive ? btok : 0) * tok_stride + lane_xofs;
+            uint4 xv[4];
+#pragma unroll
+            for (int s = 0; s < 4; s++)
+                xv[s] = blive ? *reinterpret_cast<const uint4 *>(xb + ((size_t)grp * 4 + s) * 128) : make_uint4(0, 0, 0, 0);
+            const float is = mytok < ntok ? reinterpret_cast<const float *>(xop + (size_t)mytok * tok_stride + (size_t)k * 2)[grp] : 0.f;
+            float ga = 0.f, gb = 0.f;
+#pragma unroll
+            for (int s = 0; s < 4; s++) {
+                int c0[4], c1[4];
+                q8_mma(c0, ua[s].x, ub[s].x, ua[s].y, ub[s].y, xv[s].x, xv[s].y);     // block 2s
+                q8_mma(c1, ua[s].z, ub[s].z, ua[s].w, ub[s].w, xv[s].z, xv[s].w);     // block 2s + 1
+                ga = fmaf(fa[s].x, (float)(256 * c0[0] + c0[1]), ga);
+                gb = fmaf(fb[s].x, (float)(256 * c0[2] + c0[3]), gb);
+                ga = fmaf(fa[s].y, (float)(256 * c1[0] + c1[1]), ga);
+                gb = fmaf(fb[s].y, (float)(256 * c1[2] + c1[3]), gb);
+            }
+            acc_a[tg] = fmaf(ga, is, acc_a[tg]);
+            acc_b[tg] = fmaf(gb, is, acc_b[tg]);
+        }
     }
-    red[warp][g][t] = acc_a;
-    red[warp][g + 8][t] = acc_b;
+#pragma unroll
+    for (int tg = 0; tg < NTG; tg++) {
+        red[warp][tg][g][t] = acc_a[tg];
+        red[warp][tg][g + 8][t] = acc_b[tg];
+    }
     __syncthreads();
-    for (int i = tid; i < 64; i += WARPS * 32) {
-        const int r = i >> 2, j = i & 3;
+    for (int i = tid; i < 64 * NTG; i += WARPS * 32) {
+        const int tg = i >> 6, r = (i >> 2) & 15, j = i & 3;
         float sum = 0.f;
 #pragma unroll
-        for (int w = 0; w < WARPS; w++) sum += red[w][r][j];      // fixed order
-        const int row = blockIdx.x * 16 + r, tok = tok0 + j;
+        for (int w = 0; w < WARPS; w++) sum += red[w][tg][r][j];      // fixed order
+        const int row = blockIdx.x * 16 + r, tok = tok0 + 4 * tg + j;
         if (row < nrows && tok < ntok) Y[(size_t)tok * nrows + row] = sum;
     }
 }
@@ -171,12 +184,19 @@ int jl_launch_gemv_q8(jl_ctx *ctx, float *out_dev, const uint8_t *codes, const u
     ctx->st.launches++;
     const int ngrp = k / 256;
     const int warps = ngrp >= 8 ? 8 : (ngrp >= 4 ? 4 : (ngrp >= 2 ? 2 : 1));
-    cfg.gridDim = dim3((nrows + 15) / 16, (ntok + 3) / 4); cfg.blockDim = dim3(warps * 32);
+    const int tgroups = (ntok + 3) / 4;
+    const int ntg = tgroups >= 4 ? 4 : (tgroups >= 2 ? 2 : 1);
+    cfg.gridDim = dim3((nrows + 15) / 16, (tgroups + ntg - 1) / ntg); cfg.blockDim = dim3(warps * 32);
     const uint16_t *dpl = reinterpret_cast<const uint16_t *>(scales);
     const uint8_t *xop = scratch;
-    if (warps == 8) JL_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemv_q8_mma_kernel<8>, codes, dpl, d_stride, xop, tok_stride, out_dev, nrows, k, ntok));
-    else if (warps == 4) JL_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemv_q8_mma_kernel<4>, codes, dpl, d_stride, xop, tok_stride, out_dev, nrows, k, ntok));
-    else if (warps == 2) JL_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemv_q8_mma_kernel<2>, codes, dpl, d_stride, xop, tok_stride, out_dev, nrows, k, ntok));
-    else JL_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemv_q8_mma_kernel<1>, codes, dpl, d_stride, xop, tok_stride, out_dev, nrows, k, ntok));
+#define Q8_LAUNCH(WP, TG) JL_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemv_q8_mma_kernel<WP, TG>, codes, dpl, d_stride, xop, tok_stride, out_dev, nrows, k, ntok))
+#define Q8_LAUNCH_W(WP) do { if (ntg == 4) Q8_LAUNCH(WP, 4); else if (ntg == 2) Q8_LAUNCH(WP, 2); else Q8_LAUNCH(WP, 1); } while (0)
+    if (warps == 8) Q8_LAUNCH_W(8);
+    else if (warps == 4) Q8_LAUNCH_W(4);
+    else if (warps == 2) Q8_LAUNCH_W(2);
+    else Q8_LAUNCH_W(1);
+#undef Q8_LAUNCH_W
+#undef Q8_LAUNCH
+    ctx->st.launches++;
     return JL_OK;
 }

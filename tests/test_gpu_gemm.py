@@ -126,9 +126,11 @@ def _run_q8(dev, orc, nrows, k, ntok, seed, x_dtype):
 
 
 @pytest.mark.parametrize("nrows,k,ntok,x_dtype", [(4096, 4096, 32, DT_F32), (1024, 4096, 32, DT_F32), (14336, 4096, 32, DT_F32),
-                                                   (200, 512, 9, DT_F32), (256, 256, 64, DT_BF16), (520, 1024, 300, DT_BF16)])
+                                                   (200, 512, 9, DT_F32), (256, 256, 64, DT_BF16), (520, 1024, 300, DT_BF16),
+                                                   (300, 512, 40, DT_F32), (128, 256, 17, DT_F32)])
 def test_q8_0_batched_gemm_matches_oracle(orc, nrows, k, ntok, x_dtype):
     from jitllm_b200 import Q8_0
+    from jitllm_b200 import K_MMA
     with Device(0) as d:                      # selection on its own: more than 8 tokens -> the tcgen05 GEMM
         ch = d.Select(Q8_0, nrows, k, ntok)
         assert ch is not None and ch.kernel == K_TC5
@@ -150,3 +152,12 @@ def test_q8_0_gemm_agrees_with_the_simt_check_kernel(orc):
     with Device(0, pin_kernel=K_SIMT) as d:
         assert d.MatMulRaw(b, DT_F32, Q8_0, w, x, DT_F32, nrows, k, ntok), d.Err()
     assert parity_err(a, b.astype(np.float64)) <= BAR
+
+
+def test_q8_0_int8_kernel_serves_up_to_32_tokens_when_pinned(orc):
+    """The int8 MMA kernel walks token groups with the weights in registers: reachable above 8 tokens by pinning it."""
+    from jitllm_b200 import K_MMA, Q8_0
+    with Device(0, pin_kernel=K_MMA) as d:
+        for ntok in (9, 16, 32):
+            got, ref = _run_q8(d, orc, 200, 1024, ntok, 0xB299 + ntok, DT_F32)
+            assert parity_err(got, ref) <= BAR
