@@ -9,7 +9,7 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libjitllm_b200.so")
+LIB_PATH = os.environ.get("JITLLM_B200_LIB") or os.path.join(HERE, "libjitllm_b200.so")   # the override is for A/B builds
 
 # ggml type ids (include/jitllm_b200.h)
 F32, F16, Q8_0, Q4_K, BF16, MXFP4 = 0, 1, 8, 12, 30, 39
