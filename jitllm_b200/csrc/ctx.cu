@@ -133,9 +133,17 @@ JL_EXPORT int jl_reserve(jl_ctx *ctx, int max_rows, int max_k, int max_tok) {
         const size_t n = jl_gemv_scratch_bytes(t, k256, t == JL_TYPE_Q8_0 ? (max_tok < 32 ? max_tok : 32) : dtok);
         if (n > need) need = n;
     }
-    size_t need_gemm = jl_gemm_tc5_scratch_bytes(max_rows, k256, max_tok, JL_DT_F32, ctx->sm_count);
-    const size_t need_gemm16 = jl_gemm_tc5_scratch_bytes(max_rows, k256, max_tok, JL_DT_BF16, ctx->sm_count);
-    if (need_gemm16 > need_gemm) need_gemm = need_gemm16;
+    // The GEMM's split-K partial planes are largest for SMALL row counts (few tiles -> many K splits), so the
+    // worst case over every row count up to max_rows is taken, for both activation widths.
+    size_t need_gemm = 0;
+    for (int r = 256;; r += 256) {
+        const int rows = r < max_rows ? r : max_rows;
+        for (int dt : {JL_DT_F32, JL_DT_BF16}) {
+            const size_t n = jl_gemm_tc5_scratch_bytes(rows, k256, max_tok, dt, ctx->sm_count);
+            if (n > need_gemm) need_gemm = n;
+        }
+        if (rows == max_rows) break;
+    }
     if (max_tok > 8 && need_gemm > need) need = need_gemm;
     int rc = jl_grow_scratch(ctx, need);
     if (rc) return rc;

@@ -161,3 +161,22 @@ def test_q8_0_int8_kernel_serves_up_to_32_tokens_when_pinned(orc):
         for ntok in (9, 16, 32):
             got, ref = _run_q8(d, orc, 200, 1024, ntok, 0xB299 + ntok, DT_F32)
             assert parity_err(got, ref) <= BAR
+
+
+def test_reserve_covers_smaller_row_counts(orc):
+    """jl_reserve(max_rows, ...) must also cover shapes with FEWER rows, whose split-K partial planes are larger."""
+    import torch
+    from jitllm_b200 import Q4_K as T
+    rng = synth.rng_for(3)
+    with Device(0) as d:
+        d.Reserve(16384, 1024, 600)
+        for nrows in (768, 256, 4096):
+            w = synth.q4k_matrix(rng, nrows, 1024)
+            h = d.Upload(T, w, nrows, 1024)
+            x = torch.from_numpy(synth.activations(rng, 600, 1024)).cuda()
+            out = torch.empty(600, nrows, device="cuda")
+            d.MatMulDev(out, h, x, 600, torch.cuda.current_stream().cuda_stream)     # raises if the scratch is short
+            torch.cuda.synchronize()
+            ref = orc.matmul_f64_blas(T, w, x.cpu().numpy(), nrows, 1024, 600)
+            assert parity_err(out.cpu().numpy(), ref) <= BAR, (nrows, parity_err(out.cpu().numpy(), ref))
+            h.free()
