@@ -174,14 +174,20 @@ q4k_xprep_kernel(const float *__restrict__ X, uint8_t *__restrict__ scratch, int
 // XG = the prepared operand is read from global memory (it stays in L1: every CTA of an SM reads the same
 // few KB) instead of being staged in each CTA's shared memory, which then holds weight tiles only: more CTAs
 // per SM, i.e. more weight bytes in flight.
-template <int WARPS, int STAGES, int MINB, bool FUSED, bool XG = false>
+// RG > 1 (with CPREP) = one launch per matvec without the per-16-row redundancy of FUSED: the CTA covers RG row
+// groups (WARPS / RG warps each), converts the WHOLE activation row into its shared memory once, then runs the
+// split form's loop on it. `xsrc` is X. For callers that overlap many matvecs the kernel-launch rate, not HBM, is
+// what two launches per matvec run into.
+template <int WARPS, int STAGES, int MINB, bool FUSED, bool XG = false, int RG = 1, bool CPREP = false>
 __global__ void __launch_bounds__(WARPS * 32, MINB)
 gemv_q4k_tma_kernel(const __grid_constant__ CUtensorMap wmap, int row0, const void *__restrict__ xsrc,
                     float *__restrict__ Y, int nrows, int nsb, int ntok, int *status) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
-    const int rg = blockIdx.x, tok = blockIdx.y;
+    constexpr int WPR = WARPS / RG;             // warps per row group
+    const int rgi = warp / WPR, wq = warp % WPR;
+    const int rg = blockIdx.x * RG + rgi, tok = blockIdx.y;
     // shared memory: [WARPS][STAGES] weight tiles | activation operand (nsb x 640 B + 128 zero)
     //                | red[WARPS][16] | barriers [WARPS][STAGES] + 1
     uint8_t *tiles = smem + (size_t)warp * STAGES * Q4K_TILE_BYTES;
@@ -200,7 +206,7 @@ gemv_q4k_tma_kernel(const __grid_constant__ CUtensorMap wmap, int row0, const vo
         mbar_init_fence();
 #pragma unroll
         for (int s = 0; s < STAGES; s++) {
-            const int sbi = warp + s * WARPS;
+            const int sbi = wq + s * WPR;
             if (sbi < nsb) {
                 mbar_arrive_expect_tx(smem_u32(bars + s), Q4K_TILE_BYTES);
                 tma_load_2d(smem_u32(tiles + s * Q4K_TILE_BYTES), &wmap, sbi * 144, row0 + rg * 16,
@@ -215,7 +221,12 @@ gemv_q4k_tma_kernel(const __grid_constant__ CUtensorMap wmap, int row0, const vo
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     bool lost = false;
-    if (!FUSED && !XG) {
+    if (CPREP) {
+        for (int sb = warp; sb < nsb; sb += WARPS)
+            q4k_prep_sb(reinterpret_cast<const float4 *>(static_cast<const float *>(xsrc) + ((size_t)tok * nsb + sb) * 256),
+                        xop + (size_t)sb * Q4K_XP_SB_BYTES, lane);
+        __syncthreads();
+    } else if (!FUSED && !XG) {
         if (tid == 0) {
             mbar_arrive_expect_tx(smem_u32(xbar), xop_bytes);
             bulk_load_1d(smem_u32(xop), static_cast<const uint8_t *>(xsrc) + (size_t)tok * xop_bytes, xop_bytes,
@@ -229,7 +240,7 @@ gemv_q4k_tma_kernel(const __grid_constant__ CUtensorMap wmap, int row0, const vo
     const int sh = 8 * (2 * (t & 1));   // bit offset of this lane's scale bytes inside a header word
     float accA = 0.f, accB = 0.f;
 
-    for (int it = 0, sb = warp; sb < nsb && !lost; it++, sb += WARPS) {
+    for (int it = 0, sb = wq; sb < nsb && !lost; it++, sb += WPR) {
         const int s = it % STAGES;
         const uint32_t parity = (uint32_t)(it / STAGES) & 1u;
         uint8_t *xsb = XG ? const_cast<uint8_t *>(static_cast<const uint8_t *>(xsrc)) + ((size_t)tok * nsb + sb) * Q4K_XP_SB_BYTES
@@ -261,7 +272,7 @@ gemv_q4k_tma_kernel(const __grid_constant__ CUtensorMap wmap, int row0, const vo
         const uint4 qB1 = *reinterpret_cast<const uint4 *>(tile + (g + 8) * 144 + 32 + 32 * t);
         __syncwarp();  // every lane holds its share: the stage may be refilled
         if (lane == 0) {
-            const int nx = sb + STAGES * WARPS;
+            const int nx = sb + STAGES * WPR;
             if (nx < nsb) {
                 mbar_arrive_expect_tx(smem_u32(bars + s), Q4K_TILE_BYTES);
                 tma_load_2d(smem_u32(tiles + s * Q4K_TILE_BYTES), &wmap, nx * 144, row0 + rg * 16,
@@ -313,11 +324,12 @@ gemv_q4k_tma_kernel(const __grid_constant__ CUtensorMap wmap, int row0, const vo
         red[warp * 16 + g + 8] = accB;
     }
     __syncthreads();
-    if (tid < 16) {  // fixed order over the warps: run-to-run bit-stable
+    if (tid < 16 * RG) {  // fixed order over the warps of a row group: run-to-run bit-stable
+        const int rgo = tid >> 4, r = tid & 15;
         float sum = 0.f;
 #pragma unroll
-        for (int w = 0; w < WARPS; w++) sum += red[w * 16 + tid];
-        int row = rg * 16 + tid;
+        for (int w = 0; w < WPR; w++) sum += red[(rgo * WPR + w) * 16 + r];
+        const int row = (blockIdx.x * RG + rgo) * 16 + r;
         if (row < nrows) Y[(size_t)tok * nrows + row] = sum;
     }
 }
@@ -343,7 +355,7 @@ int jl_gemv_choice(jl_ctx *ctx, uint32_t type, int nrows, int k, int ntok, jl_ch
     jl_choice c = {};
     int pin = ctx ? ctx->opts.pin_kernel : JL_K_AUTO;
     int warps = ctx && ctx->opts.pin_warps > 0 ? ctx->opts.pin_warps : 0;
-    if (warps != 2 && warps != 4 && warps != 8 && warps != 16 && warps != 108 && warps != 116 && (warps < 200 || warps > 299)) warps = 0;
+    if (warps != 2 && warps != 4 && warps != 8 && warps != 16 && warps != 108 && warps != 116 && (warps < 200 || warps > 499)) warps = 0;
     // the activation operand of the whole row must fit one CTA's shared memory
     bool mma_ok = type == JL_TYPE_Q4_K && k % 256 == 0 && q4k_tma_smem(8, 4, k / 256) <= 200 * 1024;
     if (type == JL_TYPE_MXFP4 && k % 64 == 0 && pin != JL_K_SIMT) {
@@ -421,12 +433,21 @@ int jl_launch_gemv(jl_ctx *ctx, float *out_dev, const jl_weight *w, int expert, 
         if (ctx->opts.flags & JL_FLAG_DECODE_SPLIT) fused = false;
         const bool prepared = x_dev == nullptr;   // the caller's kernels wrote the operand into the scratch already
         if (!warps && (ctx->opts.flags & JL_FLAG_DECODE_CONCURRENT) && !(ctx->opts.flags & JL_FLAG_DECODE_FUSED)) {
-            // many short-lived CTAs pay for their launch: two warps x eight-plus super-blocks each once a
-            // launch has enough row groups to fill the GPU by itself, four warps otherwise
-            warps = (nrows + 15) / 16 >= 512 ? 223 : 243;
+            // Overlapped matvecs run into the kernel-launch rate before HBM: ONE launch per matvec, the CTA (64
+            // rows, 8 warps, weight tiles three deep) converting the activation row itself (measured at 4096x4096,
+            // 8 overlapped chains: 1.62 us against 1.87 us for prep + decode). With the operand already prepared,
+            // or a row too long for shared memory, the small-CTA split variants.
+            if (x_dev != nullptr && nsb <= 64) warps = 446;
+            else warps = (nrows + 15) / 16 >= 512 ? 223 : 243;
+        } else if (!warps && x_dev != nullptr && !(ctx->opts.flags & (JL_FLAG_DECODE_FUSED | JL_FLAG_DECODE_SPLIT)) &&
+                   nsb <= 16 && nrows >= 1024) {
+            // A lone matvec of a short row: the single-launch wide form also has the shortest chain (4096x4096:
+            // 5.1 us against 5.9 us); one CTA per SM while the launch fits one wave, two above.
+            warps = ((nrows + 63) / 64 <= ctx->sm_count) ? 444 : 442;
         }
         if (prepared || warps >= 200) fused = false;
-        if (!fused && !prepared) {
+        const bool wide = warps >= 400 && warps < 500 && !prepared;   // one launch: the CTA converts the row itself
+        if (!fused && !prepared && !wide) {
             cudaLaunchConfig_t cfg = {};
             cfg.gridDim = dim3((nsb + 3) / 4, ntok); cfg.blockDim = dim3(128); cfg.stream = s;
             cfg.attrs = at; cfg.numAttrs = nattr;
@@ -448,6 +469,31 @@ int jl_launch_gemv(jl_ctx *ctx, float *out_dev, const jl_weight *w, int expert, 
                                         expert * nrows, xsrc, out_dev, nrows, nsb, ntok,                \
                                         ctx->dev_status));                                              \
     } while (0)
+#define LAUNCH_Q4K_WIDE(WP, ST, MB, RGN)                                                                 \
+    do {                                                                                                \
+        size_t smem = q4k_tma_smem(WP, ST, nsb, false, false);                                          \
+        if (smem > 48 * 1024)                                                                           \
+            JL_CUDA(ctx, cudaFuncSetAttribute(gemv_q4k_tma_kernel<WP, ST, MB, false, false, RGN, true>, \
+                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        cudaLaunchConfig_t cfg = {};                                                                    \
+        cfg.gridDim = dim3(((nrows + 15) / 16 + RGN - 1) / RGN, ntok); cfg.blockDim = dim3(WP * 32);    \
+        cfg.dynamicSmemBytes = smem; cfg.stream = s; cfg.attrs = at; cfg.numAttrs = nattr;              \
+        JL_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemv_q4k_tma_kernel<WP, ST, MB, false, false, RGN, true>, \
+                                        w->map_sb16, expert * nrows, (const void *)x_dev, out_dev,      \
+                                        nrows, nsb, ntok, ctx->dev_status));                            \
+    } while (0)
+        if (wide) {
+            if (warps == 442) LAUNCH_Q4K_WIDE(16, 2, 2, 4);
+            else if (warps == 444) LAUNCH_Q4K_WIDE(16, 2, 1, 4);
+            else if (warps == 443) LAUNCH_Q4K_WIDE(16, 3, 1, 4);
+            else if (warps == 446) LAUNCH_Q4K_WIDE(8, 3, 3, 4);
+            else if (warps == 482) LAUNCH_Q4K_WIDE(16, 2, 2, 8);
+            else LAUNCH_Q4K_WIDE(8, 3, 3, 2);
+            ctx->st.launches++;
+            JL_CUDA(ctx, cudaGetLastError());
+            return JL_OK;
+        }
+#undef LAUNCH_Q4K_WIDE
         // (warps per CTA, ring stages per warp, CTAs per SM the registers are held to, fused)
         if (fused) {
             if (warps == 4) LAUNCH_Q4K_TMA(4, 4, 4, true, false);

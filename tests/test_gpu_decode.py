@@ -283,3 +283,16 @@ def test_mxfp4_decode_half_codes_and_wide_scales(orc):
         assert d.MatMul(out, MXFP4, w, x, nrows, k, 2), d.Err()
     ref = orc.matmul_f64(MXFP4, w, x, nrows, k, 2)
     assert parity_err(out, ref) <= BAR
+
+
+@pytest.mark.parametrize("code", [442, 444, 446, 423, 243, 223])
+@pytest.mark.parametrize("nrows,k", [(16, 256), (100, 1024), (4096, 4096), (1030, 2048)])
+def test_q4k_decode_variants_by_code(orc, code, nrows, k):
+    """The single-launch wide forms (4xx: a CTA of 32..128 rows converts the activation row itself) and the
+    small-CTA split forms (2xx), each pinned by its code."""
+    with Device(0, pin_kernel=K_MMA, pin_warps=code) as d:
+        out, ref, w, x = _check(d, orc, Q4_K, nrows, k, 0xB2D0 + code + nrows)
+        assert nmse(out, ref) < 1e-8
+        out2 = np.empty_like(out)
+        assert d.MatVec(out2, Q4_K, w, x, nrows, k)
+        assert np.array_equal(out.view(np.uint32), out2.view(np.uint32))
