@@ -43,7 +43,7 @@ FALLBACK_HBM_GBS = 6650.0
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu
 # capture summarised under profiles/ (None until a capture exists for that workload).
-NCU_TRAFFIC_BYTES = {"q4k_gemv_4096": 9472768}
+NCU_TRAFFIC_BYTES = {"q4k_gemv_4096": 9471232}
 
 WORKLOADS = {
     # name: (type, nrows, k, ntok)
