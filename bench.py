@@ -16,8 +16,8 @@ call); `roofline` relates the dominant kernel's achieved GB/s to the measured
 HBM peak; `cpu_baseline` is the CPU restatement of the reference's int8 JIT
 arithmetic timed on this box's host cores.
 
-`--impl reference` times that CPU path alone (the reference is Go and cannot be
-built here) on the same workload and prints the same line shape.
+`--impl reference` times that CPU path alone (the reference is Go and no Go toolchain
+is available to build it) on the same workload and prints the same line shape.
 """
 from __future__ import annotations
 

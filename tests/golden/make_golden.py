@@ -24,7 +24,9 @@ import numpy as np
 
 
 def main() -> None:
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py <path of the jitllm checkout>")
+    ref = sys.argv[1]
     out = {}
     dq = os.path.join(ref, "testdata", "golden", "dequant")
     for name in ("q4_k_tiny", "q8_0_gemma", "q8_0_minilm", "q8_0_stories"):
