@@ -170,6 +170,8 @@ __device__ __forceinline__ void tc5_fma2(float &d0, float &d1, float a0, float a
 
 __device__ __forceinline__ uint4 ldg_nc16(const void *p) {
     uint4 v;
+    // allocating in L1 on purpose: the neighbouring 16 bytes of the sector are the next load of the same thread
+    // (measured: L1::no_allocate costs the prefill GEMM 24 %)
     asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
     return v;
 }
