@@ -196,11 +196,85 @@ def run_q8_batch(args):
 MOE = dict(E=32, topk=4, hidden=2880, ffn=2880, ntok=256, layers=2)   # 2 distinct layers: 846 MB of experts > L2
 
 
+def run_moe_ep(args):
+    """The same layer expert-parallel under torchrun: 32 / world experts per rank, the 256 tokens data-parallel,
+    NCCL all-to-all dispatch and return, combine in ascending expert id on the token's home rank."""
+    import torch
+    import torch.distributed as dist
+    from jitllm_b200 import Device, parallel, synth
+    from jitllm_b200._lib import MXFP4, MoeDesc
+    world, rank, local = _env()
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    E, topk, hidden, ffn, ntok_all = MOE["E"], MOE["topk"], MOE["hidden"], MOE["ffn"], MOE["ntok"]
+    epr, ntok = E // world, ntok_all // world
+    rng = synth.rng_for(0xB203 + rank)
+    dev = Device(local)
+    stream = torch.cuda.current_stream().cuda_stream
+    hs = [dev.Upload(MXFP4, synth.mxfp4_matrix(rng, epr * r, kk), r, kk, epr) for r, kk in ((ffn, hidden), (ffn, hidden), (hidden, ffn))]
+    dev.MoeReserve(ntok_all * topk, max(E, epr), topk, hidden, ffn)
+    d_route = MoeDesc(struct_size=C.sizeof(MoeDesc), type=MXFP4, n_expert=E, top_k=topk, hidden=hidden, ffn=ffn, act=0, norm=1, scale=1.0)
+    d_local = MoeDesc(struct_size=C.sizeof(MoeDesc), type=MXFP4, n_expert=epr, top_k=1, hidden=hidden, ffn=ffn, act=0, norm=1,
+                      scale=1.0, gate=hs[0].handle, up=hs[1].handle, down=hs[2].handle)
+
+    def route(lg):
+        sel = torch.empty(lg.shape[0], topk, dtype=torch.int32, device="cuda")
+        wt = torch.empty(lg.shape[0], topk, dtype=torch.float32, device="cuda")
+        dev.MoeRouteDev(lg, lg.shape[0], d_route, sel, wt, stream)
+        return sel, wt
+
+    def experts(rows, ids):
+        y = torch.empty(rows.shape[0], hidden, dtype=torch.float32, device="cuda")
+        dev.MoeExpertsDev(y, rows.contiguous(), ids.contiguous(), rows.shape[0], d_local, stream)
+        return y
+    moe = parallel.ExpertParallelMoE(route, experts, E, topk, hidden)
+    g = torch.Generator(device="cuda").manual_seed(11 + rank)
+    h = torch.randn(ntok, hidden, device="cuda", generator=g).to(torch.bfloat16)
+    logits = torch.randn(ntok, E, device="cuda", generator=g)
+    out = torch.zeros(ntok, hidden, device="cuda")
+    n0 = dev.Stats().launches
+    for _ in range(max(args.warmup, 3)):
+        moe.forward(out, h, logits)
+    per_step = (dev.Stats().launches - n0) // max(args.warmup, 3)
+    dist.barrier()
+    torch.cuda.synchronize()
+    import bench
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with bench.ClockSampler(local) as clk:
+        e0.record()
+        for _ in range(args.steps):
+            moe.forward(out, h, logits)
+        e1.record()
+        torch.cuda.synchronize()
+    tt = torch.tensor([e0.elapsed_time(e1)], device="cuda", dtype=torch.float64)
+    dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+    ms = float(tt)
+    us = ms * 1e3 / args.steps
+    hbm, burst, sustained, which = _peaks()
+    wbytes_rank = epr * 3 * hidden * (ffn // 32) * 17
+    if rank == 0:
+        print(json.dumps({
+            "metric": "mxfp4_moe_layers_per_s", "value": 1e6 / us, "unit": "layers/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "MXFP4 -> f16, bf16->f16 activations, f32 accumulate (tcgen05 kind::f16)", "data": "synthetic",
+            "config": {"workload": "mxfp4_moe_gptoss", **MOE, "parallelism": f"ep{world}: {epr} experts and {ntok} tokens per rank",
+                       "us_per_layer": us, "launch": "eager (the all-to-all sizes cross the host every layer)",
+                       "l2": "one layer of experts per rank, re-read every step: the per-rank working set is below L2 at 8 ranks"},
+            "roofline": {"bound": "hbm", "achieved": wbytes_rank / us / 1e3, "peak": hbm, "unit": "GB/s",
+                         "frac": wbytes_rank / us / 1e3 / hbm, "of": which, "kernel": "whole layer incl. NCCL all-to-all, weight bytes per rank", "traffic": None},
+            "e2e": None, "gpu_launches": int(per_step * args.steps), "clocks": clk.summary()}), flush=True)
+    dev.Close()
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def run_moe(args):
     import torch
     from jitllm_b200 import Device, synth
     from jitllm_b200._lib import MXFP4, MoeDesc
     world, rank, local = _env()
+    if world > 1:
+        return run_moe_ep(args)
     if rank != 0:
         return
     torch.cuda.set_device(local)
