@@ -100,6 +100,8 @@ typedef struct jl_opts {
  * single-launch latency. The arithmetic is the same; only the order in which the warps' f32 partial sums
  * meet can differ (each variant is run-to-run bit-stable). */
 #define JL_FLAG_DECODE_CONCURRENT 16u
+/* Bits 16..21 of `flags` switch off parts of the tcgen05 GEMM kernel (dequant math, MMAs, stores, TMA, raw loads)
+ * for timing experiments; with any of them set the results are meaningless. Leave them zero. */
 
 typedef struct jl_ctx jl_ctx;
 typedef struct jl_weight jl_weight;
