@@ -209,3 +209,17 @@ def test_moe_layer_matches_a_numpy_restatement_and_sums_ascending(orc):
             y = (D[e] @ a.astype(np.float64)).astype(np.float32)
             want[i] = (want[i] + wt[i, j] * y).astype(np.float32)
     assert nmse(got, want) < 1e-12
+
+
+def test_router_floors_the_divisor(orc):
+    """Mirror of the reference's TestMoERouterFloorsTheDivisor (engine/nn/moev3_test.go:341): an all-zero selection
+    gives finite, exactly-zero weights (divisor = sum + 1e-20), and an ordinary one still renormalises to 1."""
+    n_exp, k = 8, 4
+    dead = np.zeros(n_exp, np.float32)
+    sel, _, wt, _, sm = orc.moe_router(dead, k)
+    assert len(wt) == k and np.isfinite(wt).all() and not wt.any()
+    assert sorted(sel.tolist()) == [0, 1, 2, 3]                # ties go to the lowest ids
+    rng = np.random.default_rng(7)
+    ordinary = (1.0 / (1.0 + np.exp(-rng.standard_normal(n_exp)))).astype(np.float32)
+    _, _, wt, _, _ = orc.moe_router(ordinary, k)
+    assert abs(float(np.sum(wt, dtype=np.float32)) - 1.0) <= 1e-6
