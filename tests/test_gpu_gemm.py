@@ -180,3 +180,33 @@ def test_reserve_covers_smaller_row_counts(orc):
             ref = orc.matmul_f64_blas(T, w, x.cpu().numpy(), nrows, 1024, 600)
             assert parity_err(out.cpu().numpy(), ref) <= BAR, (nrows, parity_err(out.cpu().numpy(), ref))
             h.free()
+
+
+@pytest.mark.parametrize("t_name", ["Q4_K", "Q8_0"])
+def test_matmul_matches_matvec(orc, t_name):
+    """Mirror of the reference's TestMatMulMatchesMatVec (engine/nn/matmul_test.go:23-110), at its super-block shapes:
+    the batched call equals one matvec per token -- bit for bit while the decode kernels serve the batch (up to 8
+    tokens), inside the output bar once the tcgen05 GEMM takes over -- and both sit inside the bar of the f64 oracle."""
+    import jitllm_b200
+    t = getattr(jitllm_b200, t_name)
+    rng = synth.rng_for(0xB2AA)
+    shapes = [(64, 256, 5), (256, 512, 8), (2048, 2048, 5), (2048, 2048, 24), (257, 2048, 33), (5632, 2048, 7),
+              (2048, 5632, 5), (256, 2048, 48)]
+    with Device(0) as d:
+        for rows, k, ntok in shapes:
+            if t == jitllm_b200.Q8_0 and k % 256:
+                continue
+            w = synth.matrix(rng, t, rows, k)
+            x = synth.activations(rng, ntok, k)
+            batched = np.full((ntok, rows), np.nan, np.float32)
+            assert d.MatMul(batched, t, w, x, rows, k, ntok), d.Err()
+            single = np.empty_like(batched)
+            for i in range(ntok):
+                assert d.MatVec(single[i], t, w, x[i], rows, k), d.Err()
+            ref = orc.matmul_f64_blas(t, w, x, rows, k, ntok)
+            assert parity_err(batched, ref) <= BAR and parity_err(single, ref) <= BAR, (rows, k, ntok)
+            if ntok <= 8:
+                assert np.array_equal(batched.view(np.uint32), single.view(np.uint32)), (rows, k, ntok)
+            else:
+                assert parity_err(batched, single.astype(np.float64)) <= BAR, (rows, k, ntok)
+            d.Forget(w)
