@@ -3,9 +3,9 @@
 // Q8_0 weights ARE int8, so they feed mma.sync.m16n8k32.s32.s8.s8 unconverted: one MMA covers 16 rows
 // x one 32-element block, whose f16 scale d is applied to the integer sum afterwards. Activations are
 // prepared once per matvec as two int8 digits per value (x * s ~ 256 q1 + q2 with s = 32512 / amax of the
-// 256-element group, error <= 1.5e-5 of that amax); the 8 MMA columns are (token j, digit) pairs, so one
+// value's 32-element block, error <= 1.5e-5 of that amax); the 8 MMA columns are (token j, digit) pairs, so one
 // instruction serves up to four tokens and a lane ends up holding exactly the two digit sums of "its"
-// token: y[row][tok] += d[row][blk] * (1/s)[tok][group] * (256 * C1 + C2).
+// token: y[row][tok] += d[row][blk] * (1/s)[tok][blk] * (256 * C1 + C2).
 //
 // The resident code plane is stored in 64-element spans whose 16-byte piece t holds what lane t of a quad
 // feeds to the two MMAs of the span (formats.cu: q8_span_pos), so a lane's A fragments for two blocks are
@@ -14,8 +14,8 @@
 // 16 rows and meet in shared memory in fixed order (bit-stable).
 #include "jl_internal.cuh"
 
-// Prepared activation operand of one token: k/64 spans x [digit 2][t 4] x 16 B, then k/256 f32 (1/s).
-static inline size_t q8_xp_token_bytes(int k) { return (size_t)k * 2 + (size_t)(k / 256) * 4; }
+// Prepared activation operand of one token: k/64 spans x [digit 2][t 4] x 16 B, then k/32 f32 (1/s of each block).
+static inline size_t q8_xp_token_bytes(int k) { return (size_t)k * 2 + (size_t)(k / 32) * 4; }
 size_t jl_gemv_q8_scratch_bytes(int k, int ntok) { return ((q8_xp_token_bytes(k) + 255) & ~(size_t)255) * ntok; }
 
 // One warp per (256-element group, token).
@@ -32,8 +32,10 @@ __global__ void __launch_bounds__(128) q8_xprep_kernel(const float *__restrict__
     const float4 v1 = __ldg(reinterpret_cast<const float4 *>(x + 16 + 4 * t));
     float amax = fmaxf(fmaxf(fmaxf(fabsf(v0.x), fabsf(v0.y)), fmaxf(fabsf(v0.z), fabsf(v0.w))),
                        fmaxf(fmaxf(fabsf(v1.x), fabsf(v1.y)), fmaxf(fabsf(v1.z), fabsf(v1.w))));
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    // the scale is per 32-element BLOCK (the four lanes that differ in t): the weights' own block structure costs
+    // nothing extra in the kernel, and an outlier only coarsens its own block
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
     const bool live = amax > 0.f && amax < __int_as_float(0x7f800000);
     const float scale = live ? 32512.f / amax : 0.f;
     const float xs[8] = {v0.x * scale, v0.y * scale, v0.z * scale, v0.w * scale,
@@ -52,7 +54,7 @@ __global__ void __launch_bounds__(128) q8_xprep_kernel(const float *__restrict__
     uint8_t *span = base + ((size_t)grp * 4 + s) * 128;
     *reinterpret_cast<uint2 *>(span + t * 16 + hb * 8) = make_uint2(d1[0], d1[1]);        // digit 1
     *reinterpret_cast<uint2 *>(span + 64 + t * 16 + hb * 8) = make_uint2(d2[0], d2[1]);   // digit 2
-    if (lane == 0) reinterpret_cast<float *>(base + (size_t)k * 2)[grp] = live ? amax / 32512.f : 0.f;
+    if (t == 0) reinterpret_cast<float *>(base + (size_t)k * 2)[(grp * 4 + s) * 2 + hb] = live ? amax / 32512.f : 0.f;
 }
 
 __device__ __forceinline__ void q8_mma(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
@@ -134,20 +136,25 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_q8_mma_kernel(const uint8_t *
 #pragma unroll
             for (int s = 0; s < 4; s++)
                 xv[s] = blive ? *reinterpret_cast<const uint4 *>(xb + ((size_t)grp * 4 + s) * 128) : make_uint4(0, 0, 0, 0);
-            const float is = mytok < ntok ? reinterpret_cast<const float *>(xop + (size_t)mytok * tok_stride + (size_t)k * 2)[grp] : 0.f;
+            float4 isA = make_float4(0.f, 0.f, 0.f, 0.f), isB = isA;           // 1/s of the group's eight blocks
+            if (mytok < ntok) {
+                const float4 *ip = reinterpret_cast<const float4 *>(xop + (size_t)mytok * tok_stride + (size_t)k * 2) + grp * 2;
+                isA = ip[0]; isB = ip[1];
+            }
+            const float isb[8] = {isA.x, isA.y, isA.z, isA.w, isB.x, isB.y, isB.z, isB.w};
             float ga = 0.f, gb = 0.f;
 #pragma unroll
             for (int s = 0; s < 4; s++) {
                 int c0[4], c1[4];
                 q8_mma(c0, ua[s].x, ub[s].x, ua[s].y, ub[s].y, xv[s].x, xv[s].y);     // block 2s
                 q8_mma(c1, ua[s].z, ub[s].z, ua[s].w, ub[s].w, xv[s].z, xv[s].w);     // block 2s + 1
-                ga = fmaf(fa[s].x, (float)(256 * c0[0] + c0[1]), ga);
-                gb = fmaf(fb[s].x, (float)(256 * c0[2] + c0[3]), gb);
-                ga = fmaf(fa[s].y, (float)(256 * c1[0] + c1[1]), ga);
-                gb = fmaf(fb[s].y, (float)(256 * c1[2] + c1[3]), gb);
+                ga = fmaf(fa[s].x * isb[2 * s], (float)(256 * c0[0] + c0[1]), ga);
+                gb = fmaf(fb[s].x * isb[2 * s], (float)(256 * c0[2] + c0[3]), gb);
+                ga = fmaf(fa[s].y * isb[2 * s + 1], (float)(256 * c1[0] + c1[1]), ga);
+                gb = fmaf(fb[s].y * isb[2 * s + 1], (float)(256 * c1[2] + c1[3]), gb);
             }
-            acc_a[tg] = fmaf(ga, is, acc_a[tg]);
-            acc_b[tg] = fmaf(gb, is, acc_b[tg]);
+            acc_a[tg] += ga;
+            acc_b[tg] += gb;
         }
     }
 #pragma unroll

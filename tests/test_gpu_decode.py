@@ -296,3 +296,30 @@ def test_q4k_decode_variants_by_code(orc, code, nrows, k):
         out2 = np.empty_like(out)
         assert d.MatVec(out2, Q4_K, w, x, nrows, k)
         assert np.array_equal(out.view(np.uint32), out2.view(np.uint32))
+
+
+@pytest.mark.parametrize("t", [Q4_K, Q8_0, MXFP4])
+@pytest.mark.parametrize("dist", ["uniform", "student_t", "one_huge_per_block", "saturating"])
+def test_decode_reference_distributions_and_shapes(orc, t, dist):
+    """The reference's kernel gate (jit/cpu/matvec_test.go:46-143): its four activation distributions -- uniform,
+    heavy-tailed, one huge value per 32-block, alternating +-1 -- at its five shapes, for every decode kernel."""
+    shapes = [(1, 256), (4, 512), (8, 1024), (32, 2048), (3, 768)]
+    with Device(0) as d:
+        for nrows, k in shapes:
+            rng = synth.rng_for(nrows * 1000 + k)
+            w = synth.matrix(rng, t, nrows, k)
+            if dist == "uniform":
+                x = rng.uniform(-1, 1, k)
+            elif dist == "student_t":
+                x = rng.standard_normal(k) / (0.1 + np.abs(rng.standard_normal(k)))
+            elif dist == "one_huge_per_block":
+                x = rng.uniform(0, 0.01, k); x[7::32] = 1000.0
+            else:
+                x = np.where(np.arange(k) % 2 == 0, 1.0, -1.0)
+            x = x.astype(np.float32)
+            out = np.full(nrows, np.nan, np.float32)
+            assert d.MatVec(out, t, w, x, nrows, k), d.Err()
+            ref = orc.matmul_f64(t, w, x, nrows, k, 1)[0]
+            assert np.isfinite(out).all()
+            assert parity_err(out, ref) <= BAR, (nrows, k, parity_err(out, ref))
+            d.Forget(w)
