@@ -270,7 +270,9 @@ int jl_aux_attn_decode(float *out /* or NULL when operand_out is given */, void 
  * `w` expects its prepared activation operand, or NULL when that weight / token count has no such form;
  * the jl_aux_* kernels write it when given as `operand_out` (n must equal ntok, the row length w's k, a
  * multiple of 256; attention needs an even number of query heads per kv head); jl_matvec_dev_prepared then
- * runs the matvec on it. One operand per context at a time: produce, consume, then produce the next. */
+ * runs the matvec on it. One operand per context at a time: produce, consume, then produce the next. The
+ * pointer is valid until the context's scratch next grows (a weight upload, jl_reserve, jl_moe_reserve or a
+ * host-pointer call): size the context first, then ask. */
 void *jl_decode_operand(jl_ctx *ctx, const jl_weight *w, int ntok);
 int jl_matvec_dev_prepared(jl_ctx *ctx, float *out_dev, const jl_weight *w, int ntok, void *stream);
 
