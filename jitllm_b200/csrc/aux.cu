@@ -404,9 +404,13 @@ __global__ void __launch_bounds__(1024) aux_argmax_kernel(long long *out, const 
 static size_t aux_attn_ticket_bytes(int n, int hkv) { return (((size_t)n * hkv * 4) + 255) & ~(size_t)255; }
 
 // ------------------------------------------------------------------ C ABI
+// The kernels use 16-byte vector accesses: a pointer that is not 16-byte aligned is refused here, on the host.
+static inline bool aux_misaligned(const void *p) { return p && ((uintptr_t)p & 15u); }
 JL_EXPORT int jl_aux_add_rmsnorm(float *x_io, const float *delta, const float *w, float eps, float *out, void *operand_out,
                                  int n, int h, void *stream) {
     if (!x_io || (!out && !operand_out) || n < 1 || h < 4 || h % 4) return JL_EINVAL;
+    if (aux_misaligned(x_io) || aux_misaligned(delta) || aux_misaligned(w) || aux_misaligned(out) || aux_misaligned(operand_out))
+        return JL_EINVAL;
     if (h % 256 == 0)
         return aux_launch(aux_add_rmsnorm_sb_kernel, dim3(n), dim3(256), (cudaStream_t)stream, x_io, delta, w, eps, out,
                           (uint8_t *)operand_out, h);
@@ -416,6 +420,7 @@ JL_EXPORT int jl_aux_add_rmsnorm(float *x_io, const float *delta, const float *w
 
 JL_EXPORT int jl_aux_silu_mul(float *out, void *operand_out, const float *gu, int n, int ffn, void *stream) {
     if ((!out && !operand_out) || !gu || n < 1 || ffn < 4 || ffn % 4) return JL_EINVAL;
+    if (aux_misaligned(out) || aux_misaligned(gu) || aux_misaligned(operand_out)) return JL_EINVAL;
     if (ffn % 256 == 0)
         return aux_launch(aux_silu_mul_sb_kernel, dim3((ffn / 256 + 3) / 4, n), dim3(128), (cudaStream_t)stream, out,
                           (uint8_t *)operand_out, gu, ffn);
@@ -451,6 +456,9 @@ JL_EXPORT int jl_aux_attn_decode(float *out, void *operand_out, const void *q_bf
                                  int hkv, int d, int max_len, void *stream) {
     if ((!out && !operand_out) || !q_bf16 || !k_cache_bf16 || !v_cache_bf16 || !pos_dev || !scratch_zeroed_once) return JL_EINVAL;
     if (n < 1 || hkv < 1 || hq % hkv || d != ATT_D || max_len < 1) return JL_EINVAL;
+    if (aux_misaligned(out) || aux_misaligned(operand_out) || aux_misaligned(q_bf16) || aux_misaligned(k_cache_bf16) ||
+        aux_misaligned(v_cache_bf16) || aux_misaligned(scratch_zeroed_once))
+        return JL_EINVAL;
     const int g = hq / hkv, nsplit = (max_len + ATT_CHUNK - 1) / ATT_CHUNK;
     if (operand_out && (g & 1)) return JL_EINVAL;      // a super-block of the operand is two heads
     unsigned *tickets = (unsigned *)scratch_zeroed_once;

@@ -71,3 +71,19 @@ def test_unpack_rejects_unknown_types():
     o = np.zeros(64, np.uint8)
     assert lib.jl_unpack(2, b.ctypes.data, 1, o.ctypes.data, o.ctypes.data, o.ctypes.data, o.ctypes.data,
                          o.ctypes.data) == _lib.ENOTSUP
+
+
+def test_aux_entry_points_refuse_misaligned_pointers_on_the_host():
+    """The decode-step neighbour kernels use 16-byte accesses; a misaligned pointer is refused before any launch
+    (so this needs no GPU)."""
+    from jitllm_b200 import _lib
+    L = _lib.load()
+    good, bad = 0x10000, 0x10004
+    assert L.jl_aux_add_rmsnorm(bad, None, None, 1e-5, good, None, 1, 256, None) == -1
+    assert L.jl_aux_add_rmsnorm(good, bad, None, 1e-5, good, None, 1, 256, None) == -1
+    assert L.jl_aux_add_rmsnorm(good, None, None, 1e-5, None, None, 1, 256, None) == -1      # neither out nor operand
+    assert L.jl_aux_add_rmsnorm(good, None, None, 1e-5, good, None, 1, 250, None) == -1      # h % 4
+    assert L.jl_aux_silu_mul(good, None, bad, 1, 256, None) == -1
+    assert L.jl_aux_attn_decode(good, None, good, bad, good, good, good, 1, 4, 1, 128, 64, None) == -1
+    assert L.jl_aux_attn_decode(good, None, good, good, good, good, good, 1, 4, 1, 64, 64, None) == -1   # head_dim != 128
+    assert L.jl_aux_attn_scratch_bytes(1, 4, 3, 64) == 0                                       # hq % hkv
