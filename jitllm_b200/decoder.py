@@ -15,7 +15,7 @@ from __future__ import annotations
 
 import numpy as np
 
-from . import synth
+from . import parallel, synth
 from ._lib import Q4_K
 
 
@@ -59,19 +59,8 @@ class Decoder:
             share_full: every rank draws the same unsharded matrix and keeps its slice (parity tests);
             otherwise each rank draws only its own slice."""
             if share_full:
-                full = random_q4k(rng, sum(segments), k_full).reshape(sum(segments), k_full // 256, 144)
-                parts, r0 = [], 0
-                for n in segments:
-                    part = full[r0:r0 + n]
-                    r0 += n
-                    if k_split:
-                        nb = k_full // 256 // w_
-                        parts.append(part[:, rank * nb:(rank + 1) * nb])
-                    else:
-                        parts.append(part[rank * (n // w_):(rank + 1) * (n // w_)])
-                raw = np.ascontiguousarray(np.concatenate(parts, axis=0))
-                nrows, k = raw.shape[0], raw.shape[1] * 256
-                raw = raw.reshape(nrows, -1)
+                raw, nrows, k = parallel.shard_segments(random_q4k(rng, sum(segments), k_full), Q4_K, segments, k_full,
+                                                        rank, w_, k_split)
             else:
                 nrows = sum(segments) if k_split else sum(n // w_ for n in segments)
                 k = k_full // w_ if k_split else k_full

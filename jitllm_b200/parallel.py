@@ -59,6 +59,31 @@ def shard_experts(bank: np.ndarray, t: int, n_expert: int, rows: int, k: int, ra
     return flat[rank * per * eb:(rank + 1) * per * eb].copy(), per
 
 
+def shard_segments(full: np.ndarray, t: int, segments, k: int, rank: int, world: int, k_split: bool = False):
+    """Shard of a row-concatenated matrix (q|k|v, gate|up): `segments` are the row counts of its parts. Column
+    parallel (default): rows [rank/world) of EVERY part, concatenated in part order, so a rank holds matching
+    slices of all parts. Row parallel (k_split): the k-range [rank/world) of every row, cut at block boundaries.
+    Returns (bytes [rows_local][row_bytes_local], rows_local, k_local)."""
+    be, bb = BLOCK[t]
+    nrows = sum(segments)
+    m = np.ascontiguousarray(full).reshape(-1).view(np.uint8).reshape(nrows, k // be, bb)
+    if k_split:
+        if k % world or (k // world) % be:
+            raise ValueError(f"k={k} does not split over {world} ranks at {be}-element block boundaries")
+        nb = k // be // world
+        out = m[:, rank * nb:(rank + 1) * nb]
+        return np.ascontiguousarray(out).reshape(nrows, nb * bb), nrows, k // world
+    parts, r0 = [], 0
+    for n in segments:
+        if n % world:
+            raise ValueError(f"a part of {n} rows does not split over {world} ranks")
+        per = n // world
+        parts.append(m[r0 + rank * per:r0 + (rank + 1) * per])
+        r0 += n
+    out = np.ascontiguousarray(np.concatenate(parts, axis=0))
+    return out.reshape(out.shape[0], -1), out.shape[0], k
+
+
 # -------------------------------------------------------------- dense layers
 
 class ColumnParallel:

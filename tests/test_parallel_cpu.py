@@ -109,3 +109,46 @@ def test_dispatch_plan_and_ascending_combine():
     out = parallel.combine_ascending(torch.zeros(3, 4), y, sel, wt)
     want0 = 0.75 * y[0, 1] + 0.25 * y[0, 0]                           # expert 0 (slot 1) first, then expert 3
     assert torch.equal(out[0], (torch.zeros(4) + 0.75 * y[0, 1]) + 0.25 * y[0, 0]) and torch.allclose(out[0], want0)
+
+
+def test_shard_segments_reassembles_and_matches_the_dense_product(orc):
+    """q|k|v-style row-concatenated matrices: every rank holds matching slices of all parts (column parallel) or a
+    k-range of every row (row parallel); the shards reassemble to the full matrix and their products to the full
+    product."""
+    import numpy as np
+    from jitllm_b200 import parallel, synth
+    from jitllm_b200._lib import Q4_K, Q8_0
+    rng = synth.rng_for(8)
+    for t, k in ((Q4_K, 1024), (Q8_0, 256)):
+        segments = [64, 16, 16]
+        nrows = sum(segments)
+        full = synth.matrix(rng, t, nrows, k)
+        x = synth.activations(rng, 2, k)
+        ref = orc.matmul_f64(t, full, x, nrows, k, 2)
+        for world in (1, 2, 4):
+            # column parallel: outputs of rank r are the r-th slice of every part
+            outs = []
+            for rank in range(world):
+                raw, rows_l, k_l = parallel.shard_segments(full, t, segments, k, rank, world)
+                assert k_l == k and rows_l == nrows // world
+                outs.append(orc.matmul_f64(t, raw, x, rows_l, k, 2))
+            got = np.empty_like(ref)
+            r0 = 0
+            for si, n in enumerate(segments):
+                per = n // world
+                o0 = sum(s // world for s in segments[:si])
+                for rank in range(world):
+                    got[:, r0 + rank * per:r0 + (rank + 1) * per] = outs[rank][:, o0:o0 + per]
+                r0 += n
+            assert np.array_equal(got, ref)
+            # row parallel: partial products over the k-ranges add up (f64: exact enough to compare tightly)
+            acc = np.zeros_like(ref)
+            for rank in range(world):
+                raw, rows_l, k_l = parallel.shard_segments(full, t, segments, k, rank, world, k_split=True)
+                assert rows_l == nrows and k_l == k // world
+                acc += orc.matmul_f64(t, raw, x[:, rank * k_l:(rank + 1) * k_l], nrows, k_l, 2)
+            assert np.allclose(acc, ref, rtol=1e-12, atol=1e-9)
+    with pytest.raises(ValueError):
+        parallel.shard_segments(synth.q4k_matrix(rng, 6, 256), Q4_K, [6], 256, 0, 4)          # 6 rows over 4 ranks
+    with pytest.raises(ValueError):
+        parallel.shard_segments(synth.q4k_matrix(rng, 8, 256), Q4_K, [8], 256, 0, 2, k_split=True)   # 128 is not a block multiple
