@@ -6,7 +6,7 @@
  * Device.MatVec (engine/nn/device.go:23-31), the JIT.MatMul call site
  * (engine/nn/matmul.go:27) and the mixture-of-experts call sites
  * (engine/model/moe.go:502-760). Plain pointers and sizes only; a Go caller
- * reaches it through cgo or a dlopen FFI (see INTEGRATION.md).
+ * reaches it through cgo or a dlopen FFI.
  *
  * Conventions
  *   - Every function returns a jl_status: 0 = served, 1 = DECLINED (a supported
@@ -32,7 +32,7 @@
 extern "C" {
 #endif
 
-#define JL_ABI_VERSION 1
+#define JL_ABI_VERSION 2
 
 /* ggml type ids, format/quant/types.go:12-55. */
 #define JL_TYPE_F32 0u
@@ -63,7 +63,9 @@ typedef enum jl_dtype { JL_DT_F32 = 0, JL_DT_F16 = 1, JL_DT_BF16 = 2 } jl_dtype;
 typedef enum jl_kernel {
     JL_K_AUTO = 0,
     JL_K_SIMT = 1,   /* one warp per row, f32 FMA: every shape, the check kernel     */
-    JL_K_MMA = 2,    /* register dequant -> mma.sync f16, f32 accumulate: decode      */
+    JL_K_MMA = 2,    /* decode on mma.sync: Q4_K/Q8_0 codes as u8/s8 against two int8 digits
+                        of each activation (m16n8k32, s32), MXFP4 codes placed bit-wise into
+                        f16 fragments (m16n8k16); scales folded in f32                    */
     JL_K_TC5 = 3     /* TMA -> smem dequant -> tcgen05.mma, TMEM accumulators: prefill */
 } jl_kernel;
 
@@ -73,6 +75,18 @@ typedef enum jl_act { JL_ACT_SILU = 0, JL_ACT_SWIGLU_OAI = 1 } jl_act;
 /* Options: the reference's libraries read no environment, every knob is a
  * With...() option (engine/nn/options.go:7-13). Zero-initialise, set
  * struct_size = sizeof(jl_opts), then override. */
+/* Forms of the Q4_K tensor-core decode (JL_K_MMA). All share one arithmetic; they differ in who
+ * converts the activation row into the kernel's operand (two int8 digits per value, in MMA
+ * fragment order) and in how many rows a CTA covers. jl_select reports the form that runs. */
+typedef enum jl_decode_form {
+    JL_FORM_AUTO = 0,
+    JL_FORM_SPLIT = 1, /* a prep launch converts x once; 16-row CTAs stage the operand in shared memory */
+    JL_FORM_FUSED = 2, /* one launch; every 16-row CTA converts the super-blocks it consumes          */
+    JL_FORM_WIDE = 3,  /* one launch; a CTA of 16 x row_groups rows converts the whole row once      */
+    JL_FORM_L1 = 4     /* a prep launch; small CTAs hold weight tiles only and read the operand
+                          through L1 (most weight bytes in flight: for overlapped matvecs)           */
+} jl_decode_form;
+
 typedef struct jl_opts {
     uint32_t struct_size;
     int32_t pin_kernel;        /* jl_kernel; JL_K_AUTO = per-shape selection          */
@@ -83,6 +97,12 @@ typedef struct jl_opts {
     uint64_t max_resident_bytes; /* cap on device copies kept for host-pointer calls;
                                   0 = no cap                                          */
     uint32_t flags;            /* JL_FLAG_* */
+    int32_t decode_form;       /* jl_decode_form; pins the Q4_K decode form (the reference pins
+                                  its choices with WithSplit etc., jit/gpu/tier/split.go:18-31) */
+    int32_t pin_stages;        /* TMA ring depth per warp; 0 = the form's default     */
+    int32_t pin_row_groups;    /* JL_FORM_WIDE: 16-row groups per CTA; 0 = default    */
+    uint32_t wait_limit_us;    /* bound of every device-side wait, microseconds of the GPU's
+                                  global timer; 0 = 2,000,000 (2 s)                   */
 } jl_opts;
 
 /* Launch decode kernels without programmatic dependent launch (by default a decode kernel
@@ -90,18 +110,12 @@ typedef struct jl_opts {
 #define JL_FLAG_NO_PDL 1u
 /* Stream decode weights with per-lane 128-bit loads instead of TMA tile copies. */
 #define JL_FLAG_NO_TMA 2u
-/* Pin the form of the tensor-core decode: activations converted inside the decode kernel
- * (one launch, shortest dependency chain) or by a separate prep kernel (least work). */
-#define JL_FLAG_DECODE_FUSED 4u
-#define JL_FLAG_DECODE_SPLIT 8u
 /* The caller keeps several independent matvecs in flight on this GPU (streams, graph branches, experts): the
  * Q4_K decode then takes the variant with the most weight bytes in flight per SM (small CTAs, weight tiles
  * only in shared memory, the prepared activations read through L1) instead of the one with the shortest
  * single-launch latency. The arithmetic is the same; only the order in which the warps' f32 partial sums
  * meet can differ (each variant is run-to-run bit-stable). */
 #define JL_FLAG_DECODE_CONCURRENT 16u
-/* Bits 16..21 of `flags` switch off parts of the tcgen05 GEMM kernel (dequant math, MMAs, stores, TMA, raw loads)
- * for timing experiments; with any of them set the results are meaningless. Leave them zero. */
 
 typedef struct jl_ctx jl_ctx;
 typedef struct jl_weight jl_weight;
@@ -113,7 +127,10 @@ typedef struct jl_choice {
     int32_t rows_per_cta;
     int32_t split_k;  /* how many partial sums meet per output row */
     int32_t tile_m, tile_n, tile_k; /* tensor-core tile (rows, tokens, k) or 0 */
-    int32_t grid;     /* CTAs launched */
+    int32_t grid;     /* CTAs of the main kernel */
+    int32_t form;     /* jl_decode_form of a Q4_K JL_K_MMA choice, else 0 */
+    int32_t stages;   /* TMA ring depth per warp, or 0 */
+    int32_t launches; /* kernels one call launches (jl_stats.launches grows by this) */
 } jl_choice;
 
 /* Counters, the tier's Stats (jit/gpu/tier/tier.go:1246,2330). */
@@ -156,8 +173,13 @@ int jl_matmul(jl_ctx *ctx, void *out, int out_dtype, uint32_t type, const void *
               const void *x, int x_dtype, int nrows, int k, int ntok);
 
 /* ---- the mixture layer: State.moeBatch (engine/model/moe.go:502-760) ----- */
-/* Banks are [n_expert][rows][k/32*17] raw blocks (MXFP4; Q4_K/Q8_0 accepted):
- * gate, up: rows = ffn, k = hidden; down: rows = hidden, k = ffn. */
+/* Banks are [n_expert][rows][k/32*17] raw MXFP4 blocks (banks of any other type are DECLINED):
+ * gate, up: rows = ffn, k = hidden; down: rows = hidden, k = ffn.
+ * Gate: softmax over all experts (internal/oracle/moe.go:204-262). Served: logit_bias (added to
+ * the logits BEFORE the softmax, so it changes the weights too: gpt-oss), sel_bias (added to the
+ * gated scores for the SELECTION only, the weights come from the unbiased scores: the
+ * reference's MoEGate.Bias), norm, scale. Not served (no field; such a layer keeps its host
+ * path): the sigmoid gate, per-expert ExpScale, grouped top-k. */
 typedef struct jl_moe_desc {
     uint32_t struct_size;
     uint32_t type;                 /* bank block type */
@@ -168,7 +190,8 @@ typedef struct jl_moe_desc {
     const void *gate, *up, *down;  /* host banks (jl_moe) or jl_weight handles (jl_moe_dev) */
     size_t gate_bytes, up_bytes, down_bytes;
     const float *gate_bias, *up_bias, *down_bias; /* [n_expert][rows] f32 or NULL */
-    const float *router_bias;      /* added to the logits before the gate (gpt-oss) or NULL */
+    const float *router_bias;      /* logit bias [n_expert]: added to the logits before the softmax, or NULL */
+    const float *sel_bias;         /* selection-only bias [n_expert] on the gated scores, or NULL */
 } jl_moe_desc;
 /* out[ntok][hidden] f32 += sum over each row's top_k experts, ascending expert
  * id, of w_e * down_e(act(gate_e h, up_e h)). logits [ntok][n_expert] f32 are
@@ -275,6 +298,24 @@ int jl_aux_attn_decode(float *out /* or NULL when operand_out is given */, void 
  * host-pointer call): size the context first, then ask. */
 void *jl_decode_operand(jl_ctx *ctx, const jl_weight *w, int ntok);
 int jl_matvec_dev_prepared(jl_ctx *ctx, float *out_dev, const jl_weight *w, int ntok, void *stream);
+
+/* ---- bounded device waits ---------------------------------------------------
+ * Every wait inside a kernel of this library (an mbarrier a copy completes, a ring slot, a grid
+ * barrier, a peer's flag) gives up after jl_opts.wait_limit_us of the GPU's global timer, records a
+ * code in a status word of the context and lets the kernel return; the output of that launch is
+ * then incomplete. The host-pointer calls read the word themselves and return JL_ETIMEDOUT. After
+ * device-pointer calls the caller polls it: jl_status_poll enqueues a copy of the word on
+ * `stream`, waits for that stream, clears the word when it was set and returns JL_OK or
+ * JL_ETIMEDOUT (jl_last_error names the code). Not to be called during a stream capture. This
+ * mirrors the reference's rule that a failed device call is a decline the caller sees
+ * (engine/nn/device.go:1592-1593), never a wedged stream. */
+int jl_status_poll(jl_ctx *ctx, void *stream);
+/* The same for jl_matvec_q4k_noalloc's status word on the current device (allocates nothing). */
+int jl_noalloc_status(void *stream);
+/* Test-only: a one-thread kernel waits on an mbarrier that nothing ever completes, with
+ * `limit_us` as its bound, and records the timeout; jl_status_poll then reports it. The GPU is
+ * not faulted and the context stays usable. */
+int jl_test_wait_timeout(jl_ctx *ctx, uint32_t limit_us, void *stream);
 
 /* ---- host-side fault injection: JITLLM_DEVICE_FAIL_AT (jit/gpu/tier/fault.go:12-58)
  * The n-th, ... serving calls on ctx (1-based ordinals, counted from this call)

@@ -17,7 +17,9 @@ DT_F32, DT_F16, DT_BF16 = 0, 1, 2
 K_AUTO, K_SIMT, K_MMA, K_TC5 = 0, 1, 2, 3
 ACT_SILU, ACT_SWIGLU_OAI = 0, 1
 # jl_opts.flags
-FLAG_NO_PDL, FLAG_NO_TMA, FLAG_DECODE_FUSED, FLAG_DECODE_SPLIT, FLAG_DECODE_CONCURRENT = 1, 2, 4, 8, 16
+FLAG_NO_PDL, FLAG_NO_TMA, FLAG_DECODE_CONCURRENT = 1, 2, 16
+# jl_decode_form
+FORM_AUTO, FORM_SPLIT, FORM_FUSED, FORM_WIDE, FORM_L1 = 0, 1, 2, 3, 4
 OK, DECLINED = 0, 1
 EINVAL, ECUDA, ENOMEM, EDEVICE, ETIMEDOUT, ENOTSUP, ECOMM = -1, -2, -3, -4, -5, -6, -7
 
@@ -31,13 +33,15 @@ def row_bytes(t: int, k: int) -> int:
 
 class Opts(C.Structure):
     _fields_ = [("struct_size", C.c_uint32), ("pin_kernel", C.c_int32), ("pin_warps", C.c_int32),
-                ("min_weight_bytes", C.c_uint64), ("max_resident_bytes", C.c_uint64), ("flags", C.c_uint32)]
+                ("min_weight_bytes", C.c_uint64), ("max_resident_bytes", C.c_uint64), ("flags", C.c_uint32),
+                ("decode_form", C.c_int32), ("pin_stages", C.c_int32), ("pin_row_groups", C.c_int32),
+                ("wait_limit_us", C.c_uint32)]
 
 
 class Choice(C.Structure):
     _fields_ = [("kernel", C.c_int32), ("warps", C.c_int32), ("rows_per_cta", C.c_int32),
                 ("split_k", C.c_int32), ("tile_m", C.c_int32), ("tile_n", C.c_int32), ("tile_k", C.c_int32),
-                ("grid", C.c_int32)]
+                ("grid", C.c_int32), ("form", C.c_int32), ("stages", C.c_int32), ("launches", C.c_int32)]
 
 
 class Stats(C.Structure):
@@ -52,7 +56,7 @@ class MoeDesc(C.Structure):
                 ("gate", C.c_void_p), ("up", C.c_void_p), ("down", C.c_void_p),
                 ("gate_bytes", C.c_size_t), ("up_bytes", C.c_size_t), ("down_bytes", C.c_size_t),
                 ("gate_bias", C.c_void_p), ("up_bias", C.c_void_p), ("down_bias", C.c_void_p),
-                ("router_bias", C.c_void_p)]
+                ("router_bias", C.c_void_p), ("sel_bias", C.c_void_p)]
 
 
 # Every symbol include/jitllm_b200.h declares: (restype, argtypes).
@@ -82,6 +86,9 @@ SYMBOLS = {
     "jl_matmul_dev": (_I, [_VP, _VP, _I, _VP, _VP, _I, _I, _VP]),
     "jl_moe_dev": (_I, [_VP, _VP, _VP, _I, _VP, _I, C.POINTER(MoeDesc), _VP, _VP, _VP]),
     "jl_test_fail_at": (_I, [_VP, C.POINTER(C.c_int), _I]),
+    "jl_status_poll": (_I, [_VP, _VP]),
+    "jl_noalloc_status": (_I, [_VP]),
+    "jl_test_wait_timeout": (_I, [_VP, _U32, _VP]),
     "jl_noalloc_max_k": (_I, []),
     "jl_matvec_q4k_noalloc": (_I, [_VP, _VP, _VP, _I, _I, _VP]),
     "jl_aux_add_rmsnorm": (_I, [_VP, _VP, _VP, C.c_float, _VP, _VP, _I, _I, _VP]),

@@ -1,6 +1,7 @@
 // The C ABI: contexts, residency keyed on host addresses, the host-pointer and
 // device-pointer entry points, selection, statistics, host-side fault injection.
 #include "jl_internal.cuh"
+#include "tma.cuh"
 
 #include <stdarg.h>
 #include <stdio.h>
@@ -52,7 +53,14 @@ JL_EXPORT int jl_open(int device, const jl_opts *opts, jl_ctx **out) {
         return JL_ECUDA;
     }
     c->dev_status = nullptr;
-    if (cudaMalloc(&c->dev_status, sizeof(int)) != cudaSuccess || cudaMemset(c->dev_status, 0, sizeof(int)) != cudaSuccess) {
+    c->stat_pin = nullptr;
+    c->moe_stage = nullptr; c->moe_stage_cap = 0;
+    const int words[2] = {0, (int)c->opts.wait_limit_us};
+    if (cudaMalloc(&c->dev_status, sizeof words) != cudaSuccess ||
+        cudaMemcpy(c->dev_status, words, sizeof words, cudaMemcpyHostToDevice) != cudaSuccess ||
+        cudaMallocHost(&c->stat_pin, sizeof(int)) != cudaSuccess) {
+        cudaGetLastError();
+        if (c->dev_status) cudaFree(c->dev_status);
         cudaStreamDestroy(c->stream);
         delete c;
         return JL_ECUDA;
@@ -67,6 +75,10 @@ JL_EXPORT void jl_close(jl_ctx *ctx) {
     cudaStreamSynchronize(ctx->stream);
     for (auto &kv : ctx->cache) jl_weight_release(kv.second);
     ctx->cache.clear();
+    for (jl_weight *w : ctx->graveyard) jl_weight_release(w);
+    ctx->graveyard.clear();
+    if (ctx->moe_stage) cudaFree(ctx->moe_stage);
+    if (ctx->stat_pin) cudaFreeHost(ctx->stat_pin);
     if (ctx->x_dev) cudaFree(ctx->x_dev);
     if (ctx->o_dev) cudaFree(ctx->o_dev);
     if (ctx->scratch) cudaFree(ctx->scratch);
@@ -82,6 +94,7 @@ JL_EXPORT const char *jl_last_error(jl_ctx *ctx) { return ctx ? ctx->err.c_str()
 JL_EXPORT int jl_stats_get(jl_ctx *ctx, jl_stats *out) {
     if (!ctx || !out) return JL_EINVAL;
     std::lock_guard<std::mutex> lk(ctx->mu);
+    std::lock_guard<std::mutex> lk2(ctx->cache_mu);
     *out = ctx->st;
     return JL_OK;
 }
@@ -153,6 +166,7 @@ JL_EXPORT int jl_reserve(jl_ctx *ctx, int max_rows, int max_k, int max_tok) {
 // Serving calls share this prologue: health, fault injection.
 static int serving_prologue(jl_ctx *ctx) {
     if (ctx->unhealthy) return jl_set_err(ctx, JL_ECUDA, "context is unhealthy after an earlier CUDA error");
+    jl_drain_graveyard(ctx);
     ctx->call_ordinal++;
     for (int o : ctx->fail_at)
         if (o == ctx->call_ordinal) {
@@ -171,19 +185,38 @@ JL_EXPORT int jl_test_fail_at(jl_ctx *ctx, const int *ordinals, int n) {
 }
 
 // ---------------------------------------------------------------- residency
+// The map, the LRU list, the pins and the graveyard are guarded by cache_mu, which is never held
+// across device work; serving calls additionally hold ctx->mu.
 
-static void evict_for(jl_ctx *ctx, size_t incoming) {
-    uint64_t cap = ctx->opts.max_resident_bytes;
-    if (!cap) return;
-    while (!ctx->lru.empty() && ctx->st.resident_bytes + incoming > cap) {
-        uintptr_t key = ctx->lru.front();
-        ctx->lru.erase(ctx->lru.begin());
+// Frees what jl_forget dropped. Runs at the start of a serving call (which holds ctx->mu, so no
+// launch of this context is being issued); the copies were unlinked from the map when they were
+// forgotten, so nothing can pick them up any more. cudaFree waits for the device by itself.
+void jl_drain_graveyard(jl_ctx *ctx) {
+    std::vector<jl_weight *> dead;
+    {
+        std::lock_guard<std::mutex> lk(ctx->cache_mu);
+        dead.swap(ctx->graveyard);
+    }
+    for (jl_weight *w : dead) jl_weight_release(w);
+}
+
+// Makes room for `incoming` bytes under the cap by releasing least-recently-used copies that the
+// running call does not use. False when the pinned copies alone leave no room. cache_mu held.
+static bool evict_for(jl_ctx *ctx, size_t incoming, std::vector<jl_weight *> &dead) {
+    const uint64_t cap = ctx->opts.max_resident_bytes;
+    if (!cap) return true;
+    size_t i = 0;
+    while (ctx->st.resident_bytes + incoming > cap && i < ctx->lru.size()) {
+        const uintptr_t key = ctx->lru[i];
+        if (std::find(ctx->pins.begin(), ctx->pins.end(), key) != ctx->pins.end()) { i++; continue; }
+        ctx->lru.erase(ctx->lru.begin() + i);
         auto it = ctx->cache.find(key);
         if (it == ctx->cache.end()) continue;
         ctx->st.resident_bytes -= it->second->raw_bytes;
-        jl_weight_release(it->second);
+        dead.push_back(it->second);      // freed by the caller once cache_mu is released
         ctx->cache.erase(it);
     }
+    return ctx->st.resident_bytes + incoming <= cap;
 }
 
 static void touch(jl_ctx *ctx, uintptr_t key) {
@@ -195,29 +228,44 @@ static void touch(jl_ctx *ctx, uintptr_t key) {
 // The device copy of a host tensor, keyed on its address (Device.MatVec's
 // contract, engine/nn/device.go:25-30). A different shape or type at a known
 // address means the caller reused the memory without telling us: re-upload.
+// The copy stays pinned (safe from eviction) until jl_resident_unpin.
 static int resident(jl_ctx *ctx, uint32_t type, const void *w, size_t w_bytes, int n_expert, int nrows,
                     int k, jl_weight **out) {
-    uintptr_t key = (uintptr_t)w;
-    auto it = ctx->cache.find(key);
-    if (it != ctx->cache.end()) {
-        jl_weight *c = it->second;
-        if (c->type == type && c->nrows == nrows && c->k == k && c->n_expert == n_expert) {
-            touch(ctx, key);
-            *out = c;
-            return JL_OK;
+    const uintptr_t key = (uintptr_t)w;
+    const size_t need = (size_t)n_expert * nrows * jl_row_bytes(type, k);
+    std::vector<jl_weight *> dead;
+    bool fits = true;
+    {
+        std::lock_guard<std::mutex> lk(ctx->cache_mu);
+        auto it = ctx->cache.find(key);
+        if (it != ctx->cache.end()) {
+            jl_weight *c = it->second;
+            if (c->type == type && c->nrows == nrows && c->k == k && c->n_expert == n_expert) {
+                touch(ctx, key);
+                ctx->pins.push_back(key);
+                *out = c;
+                return JL_OK;
+            }
+            ctx->st.resident_bytes -= c->raw_bytes;
+            auto l = std::find(ctx->lru.begin(), ctx->lru.end(), key);
+            if (l != ctx->lru.end()) ctx->lru.erase(l);
+            dead.push_back(c);
+            ctx->cache.erase(it);
         }
-        ctx->st.resident_bytes -= c->raw_bytes;
-        jl_weight_release(c);
-        ctx->cache.erase(it);
+        fits = evict_for(ctx, need, dead);
     }
-    size_t need = (size_t)n_expert * nrows * jl_row_bytes(type, k);
-    evict_for(ctx, need);
+    for (jl_weight *d : dead) jl_weight_release(d);   // the caller holds ctx->mu: no launch of this context is in flight
+    if (!fits)
+        return jl_set_err(ctx, JL_ENOMEM, "%zu weight bytes do not fit under max_resident_bytes = %llu beside the "
+                          "copies this call already uses", need, (unsigned long long)ctx->opts.max_resident_bytes);
     jl_weight *nw = nullptr;
-    int rc = jl_repack_upload(ctx, type, w, w_bytes, n_expert, nrows, k, &nw);
+    int rc = jl_repack_upload(ctx, type, w, w_bytes, n_expert, nrows, k, &nw);   // device work: cache_mu released
     if (rc) return rc;
     nw->host_key = w;
+    std::lock_guard<std::mutex> lk(ctx->cache_mu);
     ctx->cache[key] = nw;
     touch(ctx, key);
+    ctx->pins.push_back(key);
     ctx->st.resident_bytes += nw->raw_bytes;
     *out = nw;
     return JL_OK;
@@ -227,11 +275,18 @@ int jl_resident_bank(jl_ctx *ctx, uint32_t type, const void *w, size_t w_bytes, 
                      jl_weight **out) {
     return resident(ctx, type, w, w_bytes, n_expert, nrows, k, out);
 }
+void jl_resident_unpin(jl_ctx *ctx) {
+    std::lock_guard<std::mutex> lk(ctx->cache_mu);
+    ctx->pins.clear();
+}
 
+// Forget never waits for the device (engine/nn/device.go:1575-1578): it takes only the small cache
+// mutex, unlinks the copies so that no later call can find them, and leaves the cudaFree to the next
+// serving call on this context (or jl_close). A call that is using one of them right now holds a pin:
+// its copy is unlinked too, and freed after that call has finished.
 JL_EXPORT int jl_forget(jl_ctx *ctx, const void *p, size_t n) {
     if (!ctx) return JL_EINVAL;
-    std::lock_guard<std::mutex> lk(ctx->mu);
-    cudaSetDevice(ctx->device);
+    std::lock_guard<std::mutex> lk(ctx->cache_mu);
     uintptr_t lo = (uintptr_t)p, hi = lo + n;
     // Every copy whose host range intersects [p, p+n).
     for (auto it = ctx->cache.begin(); it != ctx->cache.end();) {
@@ -240,7 +295,7 @@ JL_EXPORT int jl_forget(jl_ctx *ctx, const void *p, size_t n) {
             ctx->st.resident_bytes -= it->second->raw_bytes;
             auto l = std::find(ctx->lru.begin(), ctx->lru.end(), a);
             if (l != ctx->lru.end()) ctx->lru.erase(l);
-            jl_weight_release(it->second);
+            ctx->graveyard.push_back(it->second);
             it = ctx->cache.erase(it);
             ctx->st.forgets++;
         } else {
@@ -258,7 +313,10 @@ JL_EXPORT int jl_weight_upload_bank(jl_ctx *ctx, uint32_t type, const void *w_ho
     int rc = jl_grow_scratch(ctx, jl_gemv_scratch_bytes(type, k, type == JL_TYPE_Q8_0 ? 32 : 8));
     if (rc) return rc;
     rc = jl_repack_upload(ctx, type, w_host, w_bytes, n_expert, nrows, k, out);
-    if (rc == JL_OK) ctx->st.resident_bytes += (*out)->raw_bytes;
+    if (rc == JL_OK) {
+        std::lock_guard<std::mutex> lk2(ctx->cache_mu);
+        ctx->st.resident_bytes += (*out)->raw_bytes;
+    }
     return rc;
 }
 
@@ -272,7 +330,10 @@ JL_EXPORT void jl_weight_free(jl_ctx *ctx, jl_weight *w) {
     std::lock_guard<std::mutex> lk(ctx->mu);
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
-    ctx->st.resident_bytes -= w->raw_bytes;
+    {
+        std::lock_guard<std::mutex> lk2(ctx->cache_mu);
+        ctx->st.resident_bytes -= w->raw_bytes;
+    }
     jl_weight_release(w);
 }
 
@@ -314,8 +375,7 @@ static int matmul_dev_locked(jl_ctx *ctx, void *out_dev, int out_dtype, const jl
             return jl_launch_gemm_tc5(ctx, out_dev, out_dtype, w, expert, x_dev, x_dtype, ntok, s);
         return jl_set_err(ctx, JL_DECLINED, "the decode kernels take f32 activations and outputs");
     }
-    int warps = ctx->opts.pin_warps > 0 ? ctx->opts.pin_warps : 0;
-    return jl_launch_gemv(ctx, (float *)out_dev, w, expert, (const float *)x_dev, ntok, ch.kernel, warps, s);
+    return jl_launch_gemv(ctx, (float *)out_dev, w, expert, (const float *)x_dev, ntok, ch.kernel, s);
 }
 
 JL_EXPORT int jl_matvec_dev(jl_ctx *ctx, float *out_dev, const jl_weight *w, const float *x_dev, int ntok,
@@ -353,8 +413,7 @@ JL_EXPORT int jl_matvec_dev_prepared(jl_ctx *ctx, float *out_dev, const jl_weigh
     if (w->type != JL_TYPE_Q4_K || !w->has_map_sb16 || (ctx->opts.flags & JL_FLAG_NO_TMA) ||
         choose(ctx, w->type, w->nrows, w->k, ntok, &ch) != JL_OK || ch.kernel != JL_K_MMA)
         return jl_set_err(ctx, JL_DECLINED, "no prepared-operand form for this weight (jl_decode_operand returned NULL)");
-    int warps = ctx->opts.pin_warps > 0 ? ctx->opts.pin_warps : 0;
-    rc = jl_launch_gemv(ctx, out_dev, w, 0, nullptr, ntok, JL_K_MMA, warps, (cudaStream_t)stream);
+    rc = jl_launch_gemv(ctx, out_dev, w, 0, nullptr, ntok, JL_K_MMA, (cudaStream_t)stream);
     if (rc == JL_OK) ctx->st.served++;
     return rc;
 }
@@ -392,7 +451,9 @@ static int matmul_host(jl_ctx *ctx, void *out, int out_dtype, uint32_t type, con
     if (rc) return rc;
     JL_CUDA(ctx, cudaSetDevice(ctx->device));
     jl_weight *dw = nullptr;
-    if ((rc = resident(ctx, type, w, w_bytes, 1, nrows, k, &dw))) return rc;
+    rc = resident(ctx, type, w, w_bytes, 1, nrows, k, &dw);
+    jl_resident_unpin(ctx);   // ctx->mu is held to the end of this call: nothing else can evict dw meanwhile
+    if (rc) return rc;
     size_t xb = (size_t)ntok * k * dtype_bytes(x_dtype), ob = (size_t)ntok * nrows * dtype_bytes(out_dtype);
     if ((rc = reserve_locked(ctx, xb, ob))) return rc;
     {
@@ -406,18 +467,7 @@ static int matmul_host(jl_ctx *ctx, void *out, int out_dtype, uint32_t type, con
     rc = matmul_dev_locked(ctx, ctx->o_dev, out_dtype, dw, 0, ctx->x_dev, x_dtype, ntok, ctx->stream);
     if (rc) return rc;
     JL_CUDA(ctx, cudaMemcpyAsync(ctx->o_pin, ctx->o_dev, ob, cudaMemcpyDeviceToHost, ctx->stream));
-    // the status word rides along (the pinned x buffer is free again: reuse its first word)
-    JL_CUDA(ctx, cudaMemcpyAsync(ctx->x_pin, ctx->dev_status, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
-    cudaError_t e = cudaStreamSynchronize(ctx->stream);
-    if (e != cudaSuccess) {
-        ctx->unhealthy = true;
-        return jl_set_err(ctx, JL_ECUDA, "kernel or copy failed: %s", cudaGetErrorString(e));
-    }
-    const int dstat = *(const int *)ctx->x_pin;
-    if (dstat) {
-        cudaMemset(ctx->dev_status, 0, sizeof(int));
-        return jl_set_err(ctx, JL_ETIMEDOUT, "a bounded device-side wait ran out (code %d)", dstat);
-    }
+    if ((rc = jl_read_status(ctx, ctx->stream))) return rc;   // the status word rides along; synchronises
     memcpy(out, ctx->o_pin, ob);
     ctx->st.served++;
     return JL_OK;
@@ -436,4 +486,54 @@ JL_EXPORT int jl_matmul(jl_ctx *ctx, void *out, int out_dtype, uint32_t type, co
     if (out_dtype < 0 || out_dtype > 2 || x_dtype < 0 || x_dtype > 2) return JL_EINVAL;
     std::lock_guard<std::mutex> lk(ctx->mu);
     return matmul_host(ctx, out, out_dtype, type, w, w_bytes, x, x_dtype, nrows, k, ntok);
+}
+
+// ------------------------------------------------------------ device status
+
+// Copies the status word home on `s`, waits for `s`, clears the word when it was set.
+int jl_read_status(jl_ctx *ctx, cudaStream_t s) {
+    *ctx->stat_pin = 0;
+    cudaError_t e = cudaMemcpyAsync(ctx->stat_pin, ctx->dev_status, sizeof(int), cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    if (e != cudaSuccess) {
+        ctx->unhealthy = true;
+        return jl_set_err(ctx, JL_ECUDA, "kernel or copy failed: %s", cudaGetErrorString(e));
+    }
+    const int code = *ctx->stat_pin;
+    if (!code) return JL_OK;
+    e = cudaMemsetAsync(ctx->dev_status, 0, sizeof(int), s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    if (e != cudaSuccess) return jl_set_err(ctx, JL_ECUDA, "clearing the status word: %s", cudaGetErrorString(e));
+    static const char *const what[] = {"", "a weight tile of the decode kernel never landed", "a ring slot of the prefill GEMM",
+                                       "a ring slot of the grouped expert GEMM", "a grid barrier of the block kernel",
+                                       "a peer's partial sums (tensor-parallel exchange)", "the test wait"};
+    return jl_set_err(ctx, JL_ETIMEDOUT, "a bounded device-side wait ran out (code %d: %s)", code,
+                      code > 0 && code < 7 ? what[code] : "unknown");
+}
+
+JL_EXPORT int jl_status_poll(jl_ctx *ctx, void *stream) {
+    if (!ctx) return JL_EINVAL;
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    JL_CUDA(ctx, cudaSetDevice(ctx->device));
+    return jl_read_status(ctx, (cudaStream_t)stream);
+}
+
+// One thread waits on an mbarrier that expects bytes nobody sends; the wait is bounded like every
+// other wait in the library, runs out after `limit_ns`, and the kernel reports it and returns.
+__global__ void jl_test_wait_kernel(int *status, uint64_t limit_ns) {
+    __shared__ uint64_t bar;
+    mbar_init(smem_u32(&bar), 1);
+    mbar_init_fence();
+    mbar_arrive_expect_tx(smem_u32(&bar), 16);          // 16 bytes that never arrive
+    if (!mbar_wait_ns(smem_u32(&bar), 0, limit_ns)) atomicExch(status, 6);
+}
+
+JL_EXPORT int jl_test_wait_timeout(jl_ctx *ctx, uint32_t limit_us, void *stream) {
+    if (!ctx || limit_us < 1 || limit_us > 1000000u) return JL_EINVAL;
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    JL_CUDA(ctx, cudaSetDevice(ctx->device));
+    jl_test_wait_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(ctx->dev_status, (uint64_t)limit_us * 1000ull);
+    ctx->st.launches++;
+    JL_CUDA(ctx, cudaGetLastError());
+    return JL_OK;
 }

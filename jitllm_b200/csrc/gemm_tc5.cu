@@ -48,8 +48,7 @@ struct tc5_params {
     const uint8_t *w;             // Q4_K: raw rows of this weight (expert); Q8_0: its resident code plane [row][k]
     const uint16_t *w_d;          // Q8_0: f16 block scales [row][w_d_stride]
     int w_d_stride;
-    int *status;
-    int debug;                    // timing experiments: 1 = skip the dequant math, 2 = skip the MMAs
+    int *status;                  // [0] timeout code, [1] wait limit in microseconds
 };
 
 template <int NT, int SA, int SB>
@@ -96,7 +95,7 @@ __device__ __forceinline__ void tc5_epilogue(const tc5_params &p, int u, uint32_
                 const float sc = __shfl_sync(0xffffffffu, myscale, j);
                 const float raw = p.split ? __uint_as_float(v[(2 * j) & 31]) + __uint_as_float(v[(2 * j + 1) & 31])
                                           : __uint_as_float(v[j]);
-                if (row < p.nrows && tok < p.ntok && !(p.debug & 8)) {
+                if (row < p.nrows && tok < p.ntok) {
                     const float acc = raw * sc;
                     const size_t o = (size_t)tok * p.nrows + row;
                     if (partial) partial[o] = acc;
@@ -150,7 +149,8 @@ gemm_q4k_tc5_kernel(const __grid_constant__ CUtensorMap xmap, const tc5_params p
             mbar_init(smem_u32(acc_full + i), 1);
             mbar_init(smem_u32(acc_empty + i), 4);                  // one arrival per epilogue warp
         }
-        *abort_flag = 0;
+        abort_flag[0] = 0;
+        abort_flag[1] = p.status[1];                                // the wait limit, read once
         mbar_init_fence();
     }
     if (warp == 5) tc5_alloc(smem_u32(const_cast<uint32_t *>(tmem_slot)), L::ACC_COLS * L::ACC_BUFS);
@@ -178,7 +178,6 @@ gemm_q4k_tc5_kernel(const __grid_constant__ CUtensorMap xmap, const tc5_params p
                         const uint32_t s = kb_it % SB, ph = (kb_it / SB) & 1;
                         if (kb_it >= (uint32_t)SB) ok = tc5_wait(smem_u32(b_empty + s), ph ^ 1, abort_flag);
                         if (!ok) break;
-                        if (p.debug & 16) { mbar_arrive(smem_u32(b_full + s)); continue; }
                         mbar_arrive_expect_tx(smem_u32(b_full + s), L::B_BYTES);
                         tma_load_2d(sbase + L::B_OFS + s * L::B_BYTES, &xmap, sb * 256 + j * TC5_KB, tt * NT,
                                     smem_u32(b_full + s));
@@ -211,8 +210,7 @@ gemm_q4k_tc5_kernel(const __grid_constant__ CUtensorMap xmap, const tc5_params p
                         const uint64_t adesc = tc5_smem_desc(sbase + L::A_OFS + (sa * TC5_MS + ms) * TC5_A_BYTES);
 #pragma unroll
                         for (int j = 0; j < TC5_KB / 16; j++)  // 32 bytes of K per instruction: +2 in 16-byte units
-                            if (!(p.debug & 2))
-                                tc5_mma_f16(d_tmem + ms * NT, adesc + 2 * j, bdesc + 2 * j, idesc, (kb | j) != 0);
+                            tc5_mma_f16(d_tmem + ms * NT, adesc + 2 * j, bdesc + 2 * j, idesc, (kb | j) != 0);
                     }
                     tc5_commit(smem_u32(a_empty + sa));   // stages reusable once these MMAs have read them
                     tc5_commit(smem_u32(b_empty + s));
@@ -319,7 +317,7 @@ gemm_q4k_tc5_kernel(const __grid_constant__ CUtensorMap xmap, const tc5_params p
                     for (int j = 0; j < 4; j++, kb_it++) {   // k-block j = sub-blocks 2j (low nibbles), 2j+1 (high)
                         const uint32_t s = kb_it % SA, ph = (kb_it / SA) & 1;
                         const uint4 q0 = qcur[2 * j], q1 = qcur[2 * j + 1];
-                        if (more && !(p.debug & 32)) {       // next super-block: group j (and its header with j = 0)
+                        if (more) {       // next super-block: group j (and its header with j = 0)
                             if (j == 0) hnxt = ldg_nc16(nb);
                             qnxt[2 * j] = ldg_nc16(nb + 16 + 32 * j);
                             qnxt[2 * j + 1] = ldg_nc16(nb + 32 + 32 * j);
@@ -336,29 +334,27 @@ gemm_q4k_tc5_kernel(const __grid_constant__ CUtensorMap xmap, const tc5_params p
                         if (!ok) break;
                         uint8_t *arow = smem + L::A_OFS + s * TC5_MS * TC5_A_BYTES + a_row_ofs;
                         const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
-                        if (!(p.debug & 1)) {
     #pragma unroll
-                            for (int c = 0; c < 8; c++) {    // 16-byte chunk c = k 8c..8c+7 of the k-block
-                                const int nib = c >> 2, cq = c & 3;
-                                const float ds = nib ? ds_o : ds_e, cc = nib ? c_o : c_e;
-                                // four codes of a word -> bytes 0x80 | q: byte 2 of a float whose byte 3 is 0x3F,
-                                // i.e. 1 + q/128, picked out by one PRMT per weight
-                                const uint32_t ua = ((nib ? w[2 * cq] >> 4 : w[2 * cq]) & 0x0F0F0F0Fu) | 0x80808080u;
-                                const uint32_t ub = ((nib ? w[2 * cq + 1] >> 4 : w[2 * cq + 1]) & 0x0F0F0F0Fu) | 0x80808080u;
-                                float v[8];
-                                tc5_fma2(v[0], v[1], tc5_code_float(ua, 0), tc5_code_float(ua, 1), ds, cc);
-                                tc5_fma2(v[2], v[3], tc5_code_float(ua, 2), tc5_code_float(ua, 3), ds, cc);
-                                tc5_fma2(v[4], v[5], tc5_code_float(ub, 0), tc5_code_float(ub, 1), ds, cc);
-                                tc5_fma2(v[6], v[7], tc5_code_float(ub, 2), tc5_code_float(ub, 3), ds, cc);
-                                uint4 o;
-                                __half2 h0 = __floats2half2_rn(v[0], v[1]), h1 = __floats2half2_rn(v[2], v[3]);
-                                __half2 h2 = __floats2half2_rn(v[4], v[5]), h3 = __floats2half2_rn(v[6], v[7]);
-                                o.x = *reinterpret_cast<uint32_t *>(&h0); o.y = *reinterpret_cast<uint32_t *>(&h1);
-                                o.z = *reinterpret_cast<uint32_t *>(&h2); o.w = *reinterpret_cast<uint32_t *>(&h3);
-                                *reinterpret_cast<uint4 *>(arow + (((uint32_t)c ^ swz) << 4)) = o;
-                            }
+                        for (int c = 0; c < 8; c++) {    // 16-byte chunk c = k 8c..8c+7 of the k-block
+                            const int nib = c >> 2, cq = c & 3;
+                            const float ds = nib ? ds_o : ds_e, cc = nib ? c_o : c_e;
+                            // four codes of a word -> bytes 0x80 | q: byte 2 of a float whose byte 3 is 0x3F,
+                            // i.e. 1 + q/128, picked out by one PRMT per weight
+                            const uint32_t ua = ((nib ? w[2 * cq] >> 4 : w[2 * cq]) & 0x0F0F0F0Fu) | 0x80808080u;
+                            const uint32_t ub = ((nib ? w[2 * cq + 1] >> 4 : w[2 * cq + 1]) & 0x0F0F0F0Fu) | 0x80808080u;
+                            float v[8];
+                            tc5_fma2(v[0], v[1], tc5_code_float(ua, 0), tc5_code_float(ua, 1), ds, cc);
+                            tc5_fma2(v[2], v[3], tc5_code_float(ua, 2), tc5_code_float(ua, 3), ds, cc);
+                            tc5_fma2(v[4], v[5], tc5_code_float(ub, 0), tc5_code_float(ub, 1), ds, cc);
+                            tc5_fma2(v[6], v[7], tc5_code_float(ub, 2), tc5_code_float(ub, 3), ds, cc);
+                            uint4 o;
+                            __half2 h0 = __floats2half2_rn(v[0], v[1]), h1 = __floats2half2_rn(v[2], v[3]);
+                            __half2 h2 = __floats2half2_rn(v[4], v[5]), h3 = __floats2half2_rn(v[6], v[7]);
+                            o.x = *reinterpret_cast<uint32_t *>(&h0); o.y = *reinterpret_cast<uint32_t *>(&h1);
+                            o.z = *reinterpret_cast<uint32_t *>(&h2); o.w = *reinterpret_cast<uint32_t *>(&h3);
+                            *reinterpret_cast<uint4 *>(arow + (((uint32_t)c ^ swz) << 4)) = o;
                         }
-                        if (!(p.debug & 4)) fence_async_smem();   // generic writes -> visible to tcgen05.mma
+                        fence_async_smem();   // generic writes -> visible to tcgen05.mma
                         __syncwarp();
                         if (lane == 0) mbar_arrive(smem_u32(a_full + s));
                     }
@@ -507,7 +503,7 @@ int jl_launch_gemm_tc5(jl_ctx *ctx, void *out_dev, int out_dtype, const jl_weigh
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(ntok); cfg.blockDim = dim3(256); cfg.stream = s;
         cfg.attrs = at; cfg.numAttrs = nattr;
-        JL_CUDA(ctx, cudaLaunchKernelEx(&cfg, act_to_f16_kernel, x_dev, x_dtype, xh, inv_scale, k, split, (const int *)nullptr));
+        JL_CUDA(ctx, cudaLaunchKernelEx(&cfg, act_to_f16_kernel, x_dev, x_dtype, xh, inv_scale, k, split, (const int *)nullptr, 0));
         ctx->st.launches++;
     }
 
@@ -526,7 +522,6 @@ int jl_launch_gemm_tc5(jl_ctx *ctx, void *out_dev, int out_dtype, const jl_weigh
     p.out_dtype = out_dtype; p.out = out_dev; p.partial = partial; p.inv_scale = inv_scale; p.w = wbase; p.status = ctx->dev_status;
     p.w_d = q8 ? reinterpret_cast<const uint16_t *>(w->scales) + (size_t)expert * nrows * w->scale_stride : nullptr;
     p.w_d_stride = w->scale_stride;
-    p.debug = (int)((ctx->opts.flags >> 16) & 63);
     const int units = p.row_tiles * p.tok_tiles * p.ksplit;
     const int grid = units < ctx->sm_count ? units : ctx->sm_count;
     int rc;

@@ -8,19 +8,17 @@
 //              second against ~36e12 lane-instructions, so a SIMT decode
 //              (>= 3 instructions a weight) cannot keep up with HBM3e; the
 //              multiply-accumulate goes to the tensor cores instead:
-//                - a warp owns 16 rows x one 256-element super-block; each lane
-//                  pulls whole 16-byte chunks of the raw 144-byte block with
-//                  128-bit loads (the header chunk + two code chunks per row);
-//                - nibbles become exact f16 integers sc*q with one LOP3 (OR into
-//                  the mantissa of 1024.0) and one HFMA2 per two weights;
-//                - activations are split x = hi + lo into two f16 (22 bits) and
-//                  pre-arranged in shared memory in mma.sync B-fragment order;
-//                - mma.sync.m16n8k16 accumulates sum(sc*q*x) over the super-block
-//                  in f32; d, dmin and the sub-block minimums (a second tiny MMA
-//                  against per-sub-block activation sums) are applied in f32;
-//                - warps of a CTA cover different super-blocks of the same 16
-//                  rows and meet through shared memory in fixed order, so the
-//                  result is run-to-run bit-stable.
+//                - a warp-task is 16 rows x one 256-element super-block, fetched by
+//                  ONE TMA copy (box 144 B x 16 rows) into a per-warp ring;
+//                - the 4-bit codes become unsigned bytes with three ALU ops per
+//                  eight weights; activations are prepared once per matvec as two
+//                  int8 digits per value (x*s ~ 256 q1 + q2) in MMA fragment order;
+//                - mma.sync.m16n8k32.s32.u8.s8 against a block-diagonal B operand
+//                  collects four per-sub-block integer sums at once; sc and m fold
+//                  in as integers, d, dmin and 1/s in f32;
+//                - warps of a CTA cover different super-blocks of the same rows
+//                  and meet through shared memory in fixed order, so the result
+//                  is run-to-run bit-stable.
 #include "jl_internal.cuh"
 #include "tma.cuh"
 
@@ -232,7 +230,7 @@ gemv_q4k_tma_kernel(const __grid_constant__ CUtensorMap wmap, int row0, const vo
             bulk_load_1d(smem_u32(xop), static_cast<const uint8_t *>(xsrc) + (size_t)tok * xop_bytes, xop_bytes,
                          smem_u32(xbar));
         }
-        lost = !__all_sync(0xffffffffu, mbar_wait(smem_u32(xbar), 0));
+        lost = !__all_sync(0xffffffffu, mbar_wait(smem_u32(xbar), 0, status));
     }
 
     const bool bsel = ((g >> 1) == t);  // lanes that feed a non-zero B column: digit (g & 1) of group t
@@ -262,7 +260,7 @@ gemv_q4k_tma_kernel(const __grid_constant__ CUtensorMap wmap, int row0, const vo
                 xfo[cp] = bsel ? __ldg(reinterpret_cast<const uint2 *>(xf + 64 + cp * 16)) : make_uint2(0u, 0u);
             }
         }
-        if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(bars + s), parity))) { lost = true; break; }
+        if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(bars + s), parity, status))) { lost = true; break; }
         const uint8_t *tile = tiles + s * Q4K_TILE_BYTES;
         const uint4 hA = *reinterpret_cast<const uint4 *>(tile + g * 144);
         const uint4 qA0 = *reinterpret_cast<const uint4 *>(tile + g * 144 + 16 + 32 * t);
@@ -347,17 +345,113 @@ size_t jl_gemv_scratch_bytes(uint32_t type, int k, int ntok) {
 
 // ------------------------------------------------------------------ dispatch
 
-// Which decode kernel serves a shape. The reference decides per (quant, rows, k,
-// ntok) (jit/gpu/tier/layer.go:10953-11016); here the tensor-core kernel takes
-// every Q4_K shape whose activation fragments fit shared memory, the SIMT
-// kernel takes the rest.
+// The instantiations of the Q4_K tensor-core decode kernel, one row each: its form (jl_decode_form), warps per
+// CTA, TMA ring depth per warp, CTAs per SM the registers are held to, 16-row groups per CTA. Selection returns
+// an index into this table and BOTH jl_select and the launch read the same row, so what is reported is what runs.
+typedef void (*q4k_kernel_fn)(const CUtensorMap, int, const void *, float *, int, int, int, int *);
+struct q4k_variant {
+    int form, warps, stages, minb, rg;
+    q4k_kernel_fn fn;
+};
+#define Q4K_V(FORM, WP, ST, MB, FU, XG, RG, CP) \
+    {FORM, WP, ST, MB, RG, (q4k_kernel_fn)gemv_q4k_tma_kernel<WP, ST, MB, FU, XG, RG, CP>}
+static const q4k_variant q4k_variants[] = {
+    // the first row of a form is the form's default
+    Q4K_V(JL_FORM_SPLIT, 4, 4, 4, false, false, 1, false),
+    Q4K_V(JL_FORM_SPLIT, 8, 2, 2, false, false, 1, false),
+    Q4K_V(JL_FORM_SPLIT, 8, 4, 2, false, false, 1, false),
+    Q4K_V(JL_FORM_SPLIT, 2, 8, 8, false, false, 1, false),
+    Q4K_V(JL_FORM_FUSED, 16, 1, 1, true, false, 1, false),
+    Q4K_V(JL_FORM_FUSED, 16, 2, 1, true, false, 1, false),
+    Q4K_V(JL_FORM_FUSED, 8, 2, 2, true, false, 1, false),
+    Q4K_V(JL_FORM_FUSED, 4, 4, 4, true, false, 1, false),
+    Q4K_V(JL_FORM_WIDE, 16, 2, 1, false, false, 4, true),
+    Q4K_V(JL_FORM_WIDE, 16, 2, 2, false, false, 4, true),
+    Q4K_V(JL_FORM_WIDE, 16, 3, 1, false, false, 4, true),
+    Q4K_V(JL_FORM_WIDE, 8, 3, 3, false, false, 4, true),
+    Q4K_V(JL_FORM_WIDE, 8, 3, 3, false, false, 2, true),
+    Q4K_V(JL_FORM_WIDE, 16, 2, 2, false, false, 8, true),
+    Q4K_V(JL_FORM_L1, 4, 3, 8, false, true, 1, false),
+    Q4K_V(JL_FORM_L1, 2, 3, 16, false, true, 1, false),
+    Q4K_V(JL_FORM_L1, 4, 4, 5, false, true, 1, false),
+    Q4K_V(JL_FORM_L1, 2, 8, 5, false, true, 1, false),
+};
+#undef Q4K_V
+static const int Q4K_NVARIANTS = (int)(sizeof q4k_variants / sizeof q4k_variants[0]);
+
+static size_t q4k_variant_smem(const q4k_variant &v, int nsb) {
+    return q4k_tma_smem(v.warps, v.stages, nsb, v.form == JL_FORM_FUSED, v.form == JL_FORM_L1);
+}
+
+// First row of `form` that matches the pinned warps / stages / row groups (0 = any) and fits shared memory.
+static int q4k_find(int form, int warps, int stages, int rg, int minb, int nsb) {
+    for (int i = 0; i < Q4K_NVARIANTS; i++) {
+        const q4k_variant &v = q4k_variants[i];
+        if (v.form != form || (warps && v.warps != warps) || (stages && v.stages != stages) || (rg && v.rg != rg) ||
+            (minb && v.minb != minb))
+            continue;
+        if (q4k_variant_smem(v, nsb) > 200 * 1024) continue;
+        return i;
+    }
+    return -1;
+}
+
+// Which variant serves (nrows x nsb super-blocks, ntok tokens). have_x: the caller hands f32 activations (false:
+// the operand was already prepared by a producer kernel, so only the forms that read a prepared operand apply).
+// The reference decides per (quant, rows, k, ntok) (jit/gpu/tier/layer.go:10953-11016, tier.go:124-137).
+static int q4k_pick(const jl_ctx *ctx, int nrows, int nsb, int ntok, bool have_x) {
+    const jl_opts &o = ctx->opts;
+    const int nrg = (nrows + 15) / 16;
+    int form = o.decode_form;
+    if (form < JL_FORM_AUTO || form > JL_FORM_L1) form = JL_FORM_AUTO;
+    if (!have_x && (form == JL_FORM_FUSED || form == JL_FORM_WIDE)) form = JL_FORM_AUTO;   // those convert x themselves
+    int idx = -1;
+    if (form != JL_FORM_AUTO) {
+        idx = q4k_find(form, o.pin_warps, o.pin_stages, o.pin_row_groups, 0, nsb);
+        if (idx < 0) idx = q4k_find(form, 0, 0, 0, 0, nsb);
+        if (idx >= 0) return idx;
+    }
+    if (o.flags & JL_FLAG_DECODE_CONCURRENT) {
+        // Overlapped matvecs run into the kernel-launch rate before HBM: ONE launch per matvec, the CTA (64 rows,
+        // 8 warps, weight tiles three deep) converting the activation row itself (measured at 4096x4096, 8
+        // overlapped chains: 1.62 us against 1.87 us for prep + decode). With the operand already prepared, or a
+        // row too long for shared memory, the small-CTA variants that read the operand through L1.
+        if (have_x && nsb <= 64) idx = q4k_find(JL_FORM_WIDE, 8, 3, 4, 3, nsb);
+        if (idx < 0) idx = nrg >= 512 ? q4k_find(JL_FORM_L1, 2, 3, 1, 0, nsb) : q4k_find(JL_FORM_L1, 4, 3, 1, 0, nsb);
+        if (idx >= 0) return idx;
+    }
+    if (have_x && nsb <= 16 && nrows >= 1024) {
+        // A lone matvec of a short row: the single-launch wide form also has the shortest chain (4096x4096: 5.1 us
+        // against 5.9 us); one CTA per SM while the launch fits one wave, two above.
+        idx = q4k_find(JL_FORM_WIDE, 16, 2, 4, (nrows + 63) / 64 <= ctx->sm_count ? 1 : 2, nsb);
+        if (idx >= 0 && (!o.pin_warps || o.pin_warps == 16)) return idx;
+    }
+    // Latency-bound shapes (about one wave of warp-tasks or less) take the fused form, the rest the split form.
+    const long tasks = (long)nrg * nsb * ntok;
+    form = (have_x && tasks <= (long)ctx->sm_count * 16) ? JL_FORM_FUSED : JL_FORM_SPLIT;
+    idx = q4k_find(form, o.pin_warps, o.pin_stages, 0, 0, nsb);
+    if (idx < 0) idx = q4k_find(form, 0, 0, 0, 0, nsb);
+    if (idx < 0) idx = q4k_find(JL_FORM_SPLIT, 0, 0, 0, 0, nsb);
+    return idx;
+}
+
+static bool q4k_mma_ok(uint32_t type, int k) {
+    // the activation operand of the whole row must fit one CTA's shared memory beside the default ring
+    return type == JL_TYPE_Q4_K && k % 256 == 0 && q4k_find(JL_FORM_SPLIT, 0, 0, 0, 0, k / 256) >= 0;
+}
+
+static void q4k_fill_choice(const q4k_variant &v, int nrows, int nsb, int ntok, jl_choice *c) {
+    const int wpr = v.warps / v.rg;
+    c->kernel = JL_K_MMA; c->form = v.form; c->warps = v.warps; c->stages = v.stages; c->rows_per_cta = 16 * v.rg;
+    c->split_k = wpr < nsb ? wpr : nsb;
+    c->tile_m = 16; c->tile_n = 8; c->tile_k = 32;
+    c->grid = (((nrows + 15) / 16 + v.rg - 1) / v.rg) * ntok;
+    c->launches = (v.form == JL_FORM_SPLIT || v.form == JL_FORM_L1) ? 2 : 1;   // the prep launch in front
+}
+
 int jl_gemv_choice(jl_ctx *ctx, uint32_t type, int nrows, int k, int ntok, jl_choice *out) {
     jl_choice c = {};
-    int pin = ctx ? ctx->opts.pin_kernel : JL_K_AUTO;
-    int warps = ctx && ctx->opts.pin_warps > 0 ? ctx->opts.pin_warps : 0;
-    if (warps != 2 && warps != 4 && warps != 8 && warps != 16 && warps != 108 && warps != 116 && (warps < 200 || warps > 499)) warps = 0;
-    // the activation operand of the whole row must fit one CTA's shared memory
-    bool mma_ok = type == JL_TYPE_Q4_K && k % 256 == 0 && q4k_tma_smem(8, 4, k / 256) <= 200 * 1024;
+    const int pin = ctx->opts.pin_kernel;
     if (type == JL_TYPE_MXFP4 && k % 64 == 0 && pin != JL_K_SIMT) {
         // e2m1 codes become f16 A fragments by bit placement; mma.sync.m16n8k16, four tokens per launch row
         if (pin == JL_K_TC5) return JL_DECLINED;
@@ -365,6 +459,7 @@ int jl_gemv_choice(jl_ctx *ctx, uint32_t type, int nrows, int k, int ntok, jl_ch
         c.kernel = JL_K_MMA; c.warps = nspan >= 32 ? 8 : (nspan >= 16 ? 4 : (nspan >= 8 ? 2 : 1)); c.rows_per_cta = 16;
         c.split_k = c.warps; c.tile_m = 16; c.tile_n = 8; c.tile_k = 16;
         c.grid = (nrows + 15) / 16 * ((ntok + 3) / 4);
+        c.launches = 2;
         *out = c;
         return JL_OK;
     }
@@ -376,28 +471,26 @@ int jl_gemv_choice(jl_ctx *ctx, uint32_t type, int nrows, int k, int ntok, jl_ch
         c.split_k = c.warps; c.tile_m = 16; c.tile_n = 8; c.tile_k = 32;
         const int tgroups = (ntok + 3) / 4, ntg = tgroups >= 4 ? 4 : (tgroups >= 2 ? 2 : 1);
         c.grid = (nrows + 15) / 16 * ((tgroups + ntg - 1) / ntg);
+        c.launches = 2;
         *out = c;
         return JL_OK;
     }
-    if (pin == JL_K_SIMT || !mma_ok) {
+    if (pin == JL_K_SIMT || !q4k_mma_ok(type, k) || (ctx->opts.flags & JL_FLAG_NO_TMA)) {
         if (pin == JL_K_MMA || pin == JL_K_TC5) return JL_DECLINED;
         c.kernel = JL_K_SIMT; c.warps = 8; c.rows_per_cta = 8; c.split_k = 1;
         c.grid = (nrows + 7) / 8 * ntok;
+        c.launches = 1;
     } else {
-        const long tasks = (long)((nrows + 15) / 16) * (k / 256) * ntok;
-        const bool fused = ctx && tasks <= (long)ctx->sm_count * 16;
-        if (!warps) warps = fused ? 16 : 4;
-        c.kernel = JL_K_MMA; c.warps = warps % 100; c.rows_per_cta = 16;
-        c.split_k = c.warps < k / 256 ? c.warps : k / 256;
-        c.tile_m = 16; c.tile_n = 8; c.tile_k = 16;
-        c.grid = (nrows + 15) / 16 * ntok;
+        const int idx = q4k_pick(ctx, nrows, k / 256, ntok, true);
+        if (idx < 0) return JL_DECLINED;
+        q4k_fill_choice(q4k_variants[idx], nrows, k / 256, ntok, &c);
     }
     *out = c;
     return JL_OK;
 }
 
 int jl_launch_gemv(jl_ctx *ctx, float *out_dev, const jl_weight *w, int expert, const float *x_dev,
-                   int ntok, int kernel, int warps, cudaStream_t s) {
+                   int ntok, int kernel, cudaStream_t s) {
     const int nrows = w->nrows, k = w->k;
     size_t rows_off = (size_t)expert * nrows;
     const uint8_t *data = w->data;
@@ -410,113 +503,43 @@ int jl_launch_gemv(jl_ctx *ctx, float *out_dev, const jl_weight *w, int expert, 
         return jl_launch_gemv_mxfp4(ctx, out_dev, data, scales, w->scale_stride, x_dev, nrows, k, ntok, s);
     if (kernel == JL_K_MMA && w->type == JL_TYPE_Q8_0)
         return jl_launch_gemv_q8(ctx, out_dev, data, scales, w->scale_stride, x_dev, nrows, k, ntok, s);
-    if (kernel == JL_K_MMA && (!w->has_map_sb16 || (ctx->opts.flags & JL_FLAG_NO_TMA))) {
+    if (kernel == JL_K_MMA && !w->has_map_sb16) {
         if (ctx->opts.pin_kernel == JL_K_MMA)
             return jl_set_err(ctx, JL_DECLINED, "the tensor-core decode kernel needs the weight's tensor map");
         kernel = JL_K_SIMT;
     }
     if (kernel == JL_K_MMA && w->type == JL_TYPE_Q4_K) {
-        int nsb = k / 256;
-        size_t need = q4k_xprep_bytes(nsb, ntok);
+        const int nsb = k / 256;
+        const size_t need = q4k_xprep_bytes(nsb, ntok);
         if (ctx->scratch_cap < need)
             return jl_set_err(ctx, JL_ENOMEM, "decode scratch holds %zu bytes, %d x %d token(s) need %zu "
                               "(jl_reserve sizes it)", ctx->scratch_cap, k, ntok, need);
         uint8_t *scratch = (uint8_t *)ctx->scratch;
+        const bool prepared = x_dev == nullptr;   // the caller's kernels wrote the operand into the scratch already
+        const int idx = q4k_pick(ctx, nrows, nsb, ntok, !prepared);
+        if (idx < 0) return jl_set_err(ctx, JL_DECLINED, "no decode variant fits %d x %d", nrows, k);
+        const q4k_variant &v = q4k_variants[idx];
         cudaLaunchAttribute at[1];
         at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         at[0].val.programmaticStreamSerializationAllowed = 1;
         const int nattr = (ctx->opts.flags & JL_FLAG_NO_PDL) ? 0 : 1;
-        // Latency-bound shapes (about one wave of warp-tasks or less) take the fused form.
-        const long tasks = (long)((nrows + 15) / 16) * nsb * ntok;
-        bool fused = tasks <= (long)ctx->sm_count * 16;
-        if (ctx->opts.flags & JL_FLAG_DECODE_FUSED) fused = true;
-        if (ctx->opts.flags & JL_FLAG_DECODE_SPLIT) fused = false;
-        const bool prepared = x_dev == nullptr;   // the caller's kernels wrote the operand into the scratch already
-        if (!warps && (ctx->opts.flags & JL_FLAG_DECODE_CONCURRENT) && !(ctx->opts.flags & JL_FLAG_DECODE_FUSED)) {
-            // Overlapped matvecs run into the kernel-launch rate before HBM: ONE launch per matvec, the CTA (64
-            // rows, 8 warps, weight tiles three deep) converting the activation row itself (measured at 4096x4096,
-            // 8 overlapped chains: 1.62 us against 1.87 us for prep + decode). With the operand already prepared,
-            // or a row too long for shared memory, the small-CTA split variants.
-            if (x_dev != nullptr && nsb <= 64) warps = 446;
-            else warps = (nrows + 15) / 16 >= 512 ? 223 : 243;
-        } else if (!warps && x_dev != nullptr && !(ctx->opts.flags & (JL_FLAG_DECODE_FUSED | JL_FLAG_DECODE_SPLIT)) &&
-                   nsb <= 16 && nrows >= 1024) {
-            // A lone matvec of a short row: the single-launch wide form also has the shortest chain (4096x4096:
-            // 5.1 us against 5.9 us); one CTA per SM while the launch fits one wave, two above.
-            warps = ((nrows + 63) / 64 <= ctx->sm_count) ? 444 : 442;
-        }
-        if (prepared || warps >= 200) fused = false;
-        const bool wide = warps >= 400 && warps < 500 && !prepared;   // one launch: the CTA converts the row itself
-        if (!fused && !prepared && !wide) {
+        const bool converts = v.form == JL_FORM_FUSED || v.form == JL_FORM_WIDE;   // the kernel reads x itself
+        if (!converts && !prepared) {
             cudaLaunchConfig_t cfg = {};
             cfg.gridDim = dim3((nsb + 3) / 4, ntok); cfg.blockDim = dim3(128); cfg.stream = s;
             cfg.attrs = at; cfg.numAttrs = nattr;
             JL_CUDA(ctx, cudaLaunchKernelEx(&cfg, q4k_xprep_kernel, x_dev, scratch, nsb, ntok));
             ctx->st.launches++;
         }
-        const void *xsrc = fused ? (const void *)x_dev : (const void *)scratch;
-        dim3 grid((nrows + 15) / 16, ntok);
-#define LAUNCH_Q4K_TMA(WP, ST, MB, FU, XG)                                                               \
-    do {                                                                                                \
-        size_t smem = q4k_tma_smem(WP, ST, nsb, FU, XG);                                                    \
-        if (smem > 48 * 1024)                                                                           \
-            JL_CUDA(ctx, cudaFuncSetAttribute(gemv_q4k_tma_kernel<WP, ST, MB, FU, XG>,                      \
-                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-        cudaLaunchConfig_t cfg = {};                                                                    \
-        cfg.gridDim = grid; cfg.blockDim = dim3(WP * 32); cfg.dynamicSmemBytes = smem; cfg.stream = s;  \
-        cfg.attrs = at; cfg.numAttrs = nattr;                                                           \
-        JL_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemv_q4k_tma_kernel<WP, ST, MB, FU, XG>, w->map_sb16,         \
-                                        expert * nrows, xsrc, out_dev, nrows, nsb, ntok,                \
-                                        ctx->dev_status));                                              \
-    } while (0)
-#define LAUNCH_Q4K_WIDE(WP, ST, MB, RGN)                                                                 \
-    do {                                                                                                \
-        size_t smem = q4k_tma_smem(WP, ST, nsb, false, false);                                          \
-        if (smem > 48 * 1024)                                                                           \
-            JL_CUDA(ctx, cudaFuncSetAttribute(gemv_q4k_tma_kernel<WP, ST, MB, false, false, RGN, true>, \
-                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-        cudaLaunchConfig_t cfg = {};                                                                    \
-        cfg.gridDim = dim3(((nrows + 15) / 16 + RGN - 1) / RGN, ntok); cfg.blockDim = dim3(WP * 32);    \
-        cfg.dynamicSmemBytes = smem; cfg.stream = s; cfg.attrs = at; cfg.numAttrs = nattr;              \
-        JL_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemv_q4k_tma_kernel<WP, ST, MB, false, false, RGN, true>, \
-                                        w->map_sb16, expert * nrows, (const void *)x_dev, out_dev,      \
-                                        nrows, nsb, ntok, ctx->dev_status));                            \
-    } while (0)
-        if (wide) {
-            if (warps == 442) LAUNCH_Q4K_WIDE(16, 2, 2, 4);
-            else if (warps == 444) LAUNCH_Q4K_WIDE(16, 2, 1, 4);
-            else if (warps == 443) LAUNCH_Q4K_WIDE(16, 3, 1, 4);
-            else if (warps == 446) LAUNCH_Q4K_WIDE(8, 3, 3, 4);
-            else if (warps == 482) LAUNCH_Q4K_WIDE(16, 2, 2, 8);
-            else LAUNCH_Q4K_WIDE(8, 3, 3, 2);
-            ctx->st.launches++;
-            JL_CUDA(ctx, cudaGetLastError());
-            return JL_OK;
-        }
-#undef LAUNCH_Q4K_WIDE
-        // (warps per CTA, ring stages per warp, CTAs per SM the registers are held to, fused)
-        if (fused) {
-            if (warps == 4) LAUNCH_Q4K_TMA(4, 4, 4, true, false);
-            else if (warps == 116) LAUNCH_Q4K_TMA(16, 2, 1, true, false);
-            else if (warps == 8) LAUNCH_Q4K_TMA(8, 2, 2, true, false);
-            else LAUNCH_Q4K_TMA(16, 1, 1, true, false);
-        } else {
-            if (warps == 243) LAUNCH_Q4K_TMA(4, 3, 8, false, true);
-            else if (warps == 244) LAUNCH_Q4K_TMA(4, 4, 5, false, true);
-            else if (warps == 282) LAUNCH_Q4K_TMA(8, 2, 5, false, true);
-            else if (warps == 228) LAUNCH_Q4K_TMA(2, 8, 5, false, true);
-            else if (warps == 224) LAUNCH_Q4K_TMA(2, 4, 12, false, true);
-            else if (warps == 242) LAUNCH_Q4K_TMA(4, 2, 12, false, true);
-            else if (warps == 226) LAUNCH_Q4K_TMA(2, 6, 8, false, true);
-            else if (warps == 223) LAUNCH_Q4K_TMA(2, 3, 16, false, true);
-            else if (warps == 218) LAUNCH_Q4K_TMA(1, 8, 12, false, true);
-            else if (warps == 216) LAUNCH_Q4K_TMA(1, 16, 6, false, true);
-            else if (warps == 2) LAUNCH_Q4K_TMA(2, 8, 8, false, false);
-            else if (warps == 8) LAUNCH_Q4K_TMA(8, 2, 2, false, false);
-            else if (warps == 108) LAUNCH_Q4K_TMA(8, 4, 2, false, false);
-            else LAUNCH_Q4K_TMA(4, 4, 4, false, false);
-        }
-#undef LAUNCH_Q4K_TMA
+        const void *xsrc = converts ? (const void *)x_dev : (const void *)scratch;
+        const size_t smem = q4k_variant_smem(v, nsb);
+        if (smem > 48 * 1024)
+            JL_CUDA(ctx, cudaFuncSetAttribute((const void *)v.fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(((nrows + 15) / 16 + v.rg - 1) / v.rg, ntok); cfg.blockDim = dim3(v.warps * 32);
+        cfg.dynamicSmemBytes = smem; cfg.stream = s; cfg.attrs = at; cfg.numAttrs = nattr;
+        JL_CUDA(ctx, cudaLaunchKernelEx(&cfg, v.fn, w->map_sb16, expert * nrows, xsrc, out_dev, nrows, nsb, ntok,
+                                        ctx->dev_status));
     } else {
         dim3 grid((nrows + 7) / 8, ntok);
         if (w->type == JL_TYPE_Q4_K)
@@ -544,12 +567,12 @@ int jl_launch_gemv(jl_ctx *ctx, float *out_dev, const jl_weight *w, int expert, 
 // JL_NOALLOC_SCRATCH_BYTES until the process exits, every call on a device shares it (calls
 // whose kernels can overlap on the GPU race on it: keep them on one stream), and a call
 // finds the previous call's contents there -- the prep kernel rewrites every byte the
-// decode kernel reads, so nothing has to start at zero except the status word, which the
-// kernels only ever set.
+// decode kernel reads, so nothing has to start at zero except the status words, which the
+// kernels only ever set and jl_noalloc_status clears.
 #define JL_NOALLOC_MAX_K 16384
 #define JL_NOALLOC_SCRATCH_BYTES ((JL_NOALLOC_MAX_K / 256) * Q4K_XP_SB_BYTES + Q4K_XP_ZERO_BYTES)
 static __device__ __align__(256) uint8_t jl_noalloc_scratch[JL_NOALLOC_SCRATCH_BYTES];
-static __device__ int jl_noalloc_status;
+static __device__ int jl_noalloc_status_words[2];   // [0] timeout code, [1] wait limit (0 = default)
 
 // In host code the names above are only handles of the symbols; the device addresses are
 // asked for once per device, with that device current.
@@ -557,29 +580,55 @@ static std::mutex jl_noalloc_mu;
 static uint8_t *jl_noalloc_scratch_addr[64];
 static int *jl_noalloc_status_addr[64];
 
+static int jl_noalloc_setup(int *dev_out) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return JL_ECUDA;
+    std::lock_guard<std::mutex> lk(jl_noalloc_mu);
+    if (!jl_noalloc_scratch_addr[dev]) {   // first call on this device: before any stream capture
+        void *p = nullptr, *q = nullptr;
+        if (cudaGetSymbolAddress(&p, jl_noalloc_scratch) != cudaSuccess) { cudaGetLastError(); return JL_ECUDA; }
+        if (cudaGetSymbolAddress(&q, jl_noalloc_status_words) != cudaSuccess) { cudaGetLastError(); return JL_ECUDA; }
+        jl_noalloc_scratch_addr[dev] = (uint8_t *)p;
+        jl_noalloc_status_addr[dev] = (int *)q;
+    }
+    *dev_out = dev;
+    return JL_OK;
+}
+
 JL_EXPORT int jl_noalloc_max_k(void) { return JL_NOALLOC_MAX_K; }
+
+// Reads and clears the entry point's status word on the current device: JL_ETIMEDOUT when a
+// bounded wait of an earlier call ran out (that call's output is then incomplete). Copies
+// through the caller's stack; allocates nothing.
+JL_EXPORT int jl_noalloc_status(void *stream) {
+    int dev;
+    int rc = jl_noalloc_setup(&dev);
+    if (rc) return rc;
+    int word = 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (cudaMemcpyAsync(&word, jl_noalloc_status_addr[dev], sizeof word, cudaMemcpyDeviceToHost, s) != cudaSuccess ||
+        cudaStreamSynchronize(s) != cudaSuccess) {
+        cudaGetLastError();
+        return JL_ECUDA;
+    }
+    if (!word) return JL_OK;
+    if (cudaMemsetAsync(jl_noalloc_status_addr[dev], 0, sizeof(int), s) != cudaSuccess || cudaStreamSynchronize(s) != cudaSuccess) {
+        cudaGetLastError();
+        return JL_ECUDA;
+    }
+    return JL_ETIMEDOUT;
+}
 
 JL_EXPORT int jl_matvec_q4k_noalloc(float *out_dev, const void *w_dev, const float *x_dev, int nrows, int k,
                                     void *stream) {
     if (!out_dev || !w_dev || !x_dev || nrows < 1 || k < 256 || k % 256) return JL_EINVAL;
     if (k > JL_NOALLOC_MAX_K) return JL_ENOMEM;   // beyond the fixed scratch: refuse, never grow
     if (((uintptr_t)w_dev & 15) || ((uintptr_t)x_dev & 15)) return JL_EINVAL;
-    int dev = -1;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return JL_ECUDA;
-    uint8_t *scratch;
-    int *status;
-    {
-        std::lock_guard<std::mutex> lk(jl_noalloc_mu);
-        if (!jl_noalloc_scratch_addr[dev]) {   // first call on this device: before any stream capture
-            void *p = nullptr, *q = nullptr;
-            if (cudaGetSymbolAddress(&p, jl_noalloc_scratch) != cudaSuccess) { cudaGetLastError(); return JL_ECUDA; }
-            if (cudaGetSymbolAddress(&q, jl_noalloc_status) != cudaSuccess) { cudaGetLastError(); return JL_ECUDA; }
-            jl_noalloc_scratch_addr[dev] = (uint8_t *)p;
-            jl_noalloc_status_addr[dev] = (int *)q;
-        }
-        scratch = jl_noalloc_scratch_addr[dev];
-        status = jl_noalloc_status_addr[dev];
-    }
+    int dev;
+    int rc = jl_noalloc_setup(&dev);
+    if (rc) return rc;
+    uint8_t *scratch = jl_noalloc_scratch_addr[dev];
+    int *status = jl_noalloc_status_addr[dev];
     const int nsb = k / 256;
     const size_t row_bytes = (size_t)nsb * 144;
     CUtensorMap map;   // encoded on the host into this stack object: no device memory involved

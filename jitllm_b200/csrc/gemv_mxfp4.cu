@@ -179,5 +179,6 @@ int jl_launch_gemv_mxfp4(jl_ctx *ctx, float *out_dev, const uint8_t *codes, cons
     else if (warps == 4) JL_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemv_mxfp4_mma_kernel<4>, codes, eplane, e_stride, xhc, isc, out_dev, nrows, k, ntok));
     else if (warps == 2) JL_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemv_mxfp4_mma_kernel<2>, codes, eplane, e_stride, xhc, isc, out_dev, nrows, k, ntok));
     else JL_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemv_mxfp4_mma_kernel<1>, codes, eplane, e_stride, xhc, isc, out_dev, nrows, k, ntok));
+    ctx->st.launches++;
     return JL_OK;
 }

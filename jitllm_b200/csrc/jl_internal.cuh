@@ -72,7 +72,8 @@ struct jl_ctx {
     int device;
     jl_opts opts;
     cudaStream_t stream;
-    std::mutex mu;
+    std::mutex mu;          // serving calls: held across launches and, on the host-pointer calls, a stream sync
+    std::mutex cache_mu;    // the residency map, the LRU list and the graveyard only: never held across device work
     std::string err;
     bool unhealthy;
     jl_stats st;
@@ -80,13 +81,17 @@ struct jl_ctx {
     // host-pointer residency: keyed on the host address (Device.MatVec's contract).
     std::map<uintptr_t, jl_weight *> cache;
     std::vector<uintptr_t> lru;
+    std::vector<uintptr_t> pins;        // keys the running call is using: never evicted
+    std::vector<jl_weight *> graveyard; // copies jl_forget dropped; freed by the next serving call
+    void *moe_stage; size_t moe_stage_cap;   // jl_moe's device staging (h, logits, out, sel, wt, biases)
+    int *stat_pin;          // pinned word the status rides home in
     // staging for the host entry points (grown by jl_reserve or on demand).
     void *x_dev; size_t x_cap;
     void *o_dev; size_t o_cap;
     void *scratch; size_t scratch_cap;
     void *x_pin; size_t x_pin_cap;
     void *o_pin; size_t o_pin_cap;
-    int *dev_status;        // device word a kernel sets when a bounded wait ran out
+    int *dev_status;        // device words: [0] code a kernel sets when a bounded wait ran out, [1] the limit (us)
     // fault injection
     std::vector<int> fail_at;
     int call_ordinal;
@@ -117,13 +122,16 @@ int jl_launch_gemv_mxfp4(jl_ctx *ctx, float *out_dev, const uint8_t *codes, cons
 int jl_launch_gemv_q8(jl_ctx *ctx, float *out_dev, const uint8_t *codes, const uint8_t *scales, int d_stride,
                       const float *x_dev, int nrows, int k, int ntok, cudaStream_t s);
 int jl_launch_gemv(jl_ctx *ctx, float *out_dev, const jl_weight *w, int expert, const float *x_dev,
-                   int ntok, int kernel, int warps, cudaStream_t s);
+                   int ntok, int kernel, cudaStream_t s);
 int jl_gemv_choice(jl_ctx *ctx, uint32_t type, int nrows, int k, int ntok, jl_choice *out);
 size_t jl_gemv_scratch_bytes(uint32_t type, int k, int ntok);
 int jl_grow_scratch(jl_ctx *ctx, size_t need);
 // ctx.cu: device copy of a host bank keyed on its address (as jl_matvec does for one matrix)
 int jl_resident_bank(jl_ctx *ctx, uint32_t type, const void *w, size_t w_bytes, int n_expert, int nrows, int k,
                      jl_weight **out);
+void jl_resident_unpin(jl_ctx *ctx);
+void jl_drain_graveyard(jl_ctx *ctx);
+int jl_read_status(jl_ctx *ctx, cudaStream_t s);
 
 // gemm_tc5.cu -- prefill kernels (tcgen05).
 int jl_launch_gemm_tc5(jl_ctx *ctx, void *out_dev, int out_dtype, const jl_weight *w, int expert,

@@ -20,13 +20,15 @@
 #include "tc5.cuh"
 
 #include <math.h>
+#include <string.h>
 
 // ------------------------------------------------------------------ route
 
 // One warp per token. n_expert <= 256.
 __global__ void __launch_bounds__(128)
-moe_route_kernel(const float *__restrict__ logits, const float *__restrict__ router_bias, int ntok, int n_expert,
-                 int top_k, int norm, float scale, int32_t *__restrict__ sel, float *__restrict__ wt) {
+moe_route_kernel(const float *__restrict__ logits, const float *__restrict__ router_bias,
+                 const float *__restrict__ sel_bias, int ntok, int n_expert, int top_k, int norm, float scale,
+                 int32_t *__restrict__ sel, float *__restrict__ wt) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int tok = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
@@ -51,6 +53,14 @@ moe_route_kernel(const float *__restrict__ logits, const float *__restrict__ rou
     for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
 #pragma unroll
     for (int i = 0; i < 8; i++) pr[i] = (float)(ex[i] / sum);   // a NaN logit stays a NaN score
+    // the scores the SELECTION ranks: the gated scores plus the selection-only bias; the weights below
+    // come from the unbiased scores (internal/oracle/moe.go:204-262)
+    float rk[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const int e = lane + 32 * i;
+        rk[i] = (sel_bias && e < n_expert) ? pr[i] + sel_bias[e] : pr[i];
+    }
 
     // k rounds of "largest score, lowest index"; picked entries are retired
     bool taken[8] = {false, false, false, false, false, false, false, false};
@@ -58,24 +68,25 @@ moe_route_kernel(const float *__restrict__ logits, const float *__restrict__ rou
     float mywt = 0.f;     // lane j keeps the j-th selected weight
     int mysel = -1;
     for (int j = 0; j < top_k; j++) {
-        float best = -INFINITY;
+        float best = -INFINITY, bw = 0.f;            // ranking score and the unbiased score that goes with it
         int bi = 0x7fffffff;
 #pragma unroll
         for (int i = 0; i < 8; i++) {
             const int e = lane + 32 * i;
-            if (e < n_expert && !taken[i] && pr[i] == pr[i] && (bi == 0x7fffffff || pr[i] > best)) { best = pr[i]; bi = e; }
+            if (e < n_expert && !taken[i] && rk[i] == rk[i] && (bi == 0x7fffffff || rk[i] > best)) { best = rk[i]; bw = pr[i]; bi = e; }
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
             const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const float ow = __shfl_xor_sync(0xffffffffu, bw, o);
             const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (oi != 0x7fffffff && (bi == 0x7fffffff || ob > best || (ob == best && oi < bi))) { best = ob; bi = oi; }
+            if (oi != 0x7fffffff && (bi == 0x7fffffff || ob > best || (ob == best && oi < bi))) { best = ob; bw = ow; bi = oi; }
         }
         if (bi == 0x7fffffff) break;                 // nothing eligible is left
 #pragma unroll
         for (int i = 0; i < 8; i++) if (lane + 32 * i == bi) taken[i] = true;
-        wsum += best;                                // selection order, one addition at a time
-        if (lane == j) { mywt = best; mysel = bi; }
+        wsum += bw;                                  // selection order, one addition at a time
+        if (lane == j) { mywt = bw; mysel = bi; }
     }
     const float div = norm ? wsum + 1e-20f : 1.f;
     if (lane < top_k) {
@@ -116,7 +127,7 @@ moe_sort_kernel(const int32_t *__restrict__ sel, int npairs, int top_k, int n_ex
     __syncthreads();
     if (tid <= n_expert) off[tid] = s_base[tid];
     if (tid < n_expert) cnt[tid] = s_cnt[tid];
-    __syncthreads();
+    __syncthreads();                                   // off[] is read back below by every thread
     if (tid < 32) {
         for (int c = 0; c < npairs; c += 32) {
             const int i = c + tid;
@@ -134,6 +145,10 @@ moe_sort_kernel(const int32_t *__restrict__ sel, int npairs, int top_k, int n_ex
             __syncwarp();
         }
     }
+    // Pairs without an expert (a row of NaN logits fills fewer than top_k slots; an id out of range) leave the last
+    // positions of the list unused: name token 0 there, so that the gather that walks all npairs positions reads a
+    // real row (nothing consumes those positions).
+    for (int i = off[n_expert] + tid; i < npairs; i += blockDim.x) perm_tok[i] = 0;
 }
 
 // ---------------------------------------------------------------- combine
@@ -176,9 +191,7 @@ moe_combine_kernel(float *__restrict__ out, const float *__restrict__ y, const i
 
 // ------------------------------------------------------------ grouped GEMM
 
-#ifndef MOE_PF
-#define MOE_PF 4
-#endif
+#define MOE_PF 4   // k-blocks of raw codes a dequant thread keeps in flight
 struct moe_gemm_params {
     int mode;                    // 0: gate|up -> act(g, u);  1: down
     int n_expert, rows, k;       // rows, k of ONE expert matrix (mode 0: ffn x hidden; mode 1: hidden x ffn)
@@ -258,7 +271,8 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap xmap, const moe_gemm_params 
         for (int s = 0; s < SA; s++) { mbar_init(smem_u32(a_full + s), TC5_DQ_THREADS / 32); mbar_init(smem_u32(a_empty + s), 1); }
         for (int s = 0; s < SB; s++) { mbar_init(smem_u32(b_full + s), 1); mbar_init(smem_u32(b_empty + s), 1); }
         for (int i = 0; i < 2; i++) { mbar_init(smem_u32(acc_full + i), 1); mbar_init(smem_u32(acc_empty + i), 4); }
-        *abort_flag = 0;
+        abort_flag[0] = 0;
+        abort_flag[1] = p.status[1];                                // the wait limit, read once
         mbar_init_fence();
     }
     if (warp == 5) tc5_alloc(smem_u32(const_cast<uint32_t *>(tmem_slot)), L::ACC_COLS * L::ACC_BUFS);
@@ -581,7 +595,7 @@ static int moe_dev_locked(jl_ctx *ctx, float *out_dev, const void *h_dev, int h_
     {
         cudaLaunchConfig_t c = cfg_of(dim3((ntok + 3) / 4), dim3(128));
         if (!given_ids) {
-            JL_CUDA(ctx, cudaLaunchKernelEx(&c, moe_route_kernel, logits_dev, d->router_bias, ntok, E, K, d->norm, d->scale, sel, wt));
+            JL_CUDA(ctx, cudaLaunchKernelEx(&c, moe_route_kernel, logits_dev, d->router_bias, d->sel_bias, ntok, E, K, d->norm, d->scale, sel, wt));
             ctx->st.launches++;
         }
         c = cfg_of(dim3(1), dim3(256));
@@ -591,7 +605,7 @@ static int moe_dev_locked(jl_ctx *ctx, float *out_dev, const void *h_dev, int h_
     const int hsplit = h_dtype == JL_DT_F32 ? 1 : 0;
     {
         cudaLaunchConfig_t c = cfg_of(dim3(np), dim3(256));
-        JL_CUDA(ctx, cudaLaunchKernelEx(&c, act_to_f16_kernel, h_dev, h_dtype, xs, xs_scale, H, hsplit, (const int *)perm));
+        JL_CUDA(ctx, cudaLaunchKernelEx(&c, act_to_f16_kernel, h_dev, h_dtype, xs, xs_scale, H, hsplit, (const int *)perm, ntok));
         ctx->st.launches++;
     }
     moe_gemm_params p = {};
@@ -605,7 +619,7 @@ static int moe_dev_locked(jl_ctx *ctx, float *out_dev, const void *h_dev, int h_
     if (rc) return rc;
     {
         cudaLaunchConfig_t c = cfg_of(dim3(np), dim3(256));
-        JL_CUDA(ctx, cudaLaunchKernelEx(&c, act_to_f16_kernel, (const void *)act, (int)JL_DT_F32, as, as_scale, F, 1, (const int *)nullptr));
+        JL_CUDA(ctx, cudaLaunchKernelEx(&c, act_to_f16_kernel, (const void *)act, (int)JL_DT_F32, as, as_scale, F, 1, (const int *)nullptr, 0));
         ctx->st.launches++;
     }
     // down
@@ -625,10 +639,39 @@ static int moe_dev_locked(jl_ctx *ctx, float *out_dev, const void *h_dev, int h_
     return JL_OK;
 }
 
+// jl_moe_desc grew by a field (sel_bias): a caller built against the shorter struct says so in struct_size.
+static size_t desc_size(const jl_moe_desc *d) {
+    return d->struct_size >= 64 && d->struct_size < sizeof(jl_moe_desc) ? d->struct_size : sizeof(jl_moe_desc);
+}
+// The caller's descriptor as the current struct (fields it does not know are zero).
+static jl_moe_desc desc_local(const jl_moe_desc *d) {
+    jl_moe_desc out = {};
+    memcpy(&out, d, desc_size(d));
+    return out;
+}
+
+// The host-pointer call's device staging: grows only, and only here.
+static int moe_grow_stage(jl_ctx *ctx, size_t need) {
+    if (ctx->moe_stage_cap >= need) return JL_OK;
+    cudaStreamSynchronize(ctx->stream);
+    if (ctx->moe_stage) { cudaFree(ctx->moe_stage); ctx->moe_stage = nullptr; ctx->moe_stage_cap = 0; }
+    cudaError_t e = cudaMalloc(&ctx->moe_stage, need);
+    if (e != cudaSuccess) { cudaGetLastError(); return jl_set_err(ctx, JL_ENOMEM, "cudaMalloc(%zu): %s", need, cudaGetErrorString(e)); }
+    ctx->moe_stage_cap = need;
+    return JL_OK;
+}
+
 JL_EXPORT int jl_moe_reserve(jl_ctx *ctx, int ntok, int n_expert, int top_k, int hidden, int ffn) {
     if (!ctx || ntok < 1 || n_expert < 1 || top_k < 1 || hidden < 1 || ffn < 1) return JL_EINVAL;
     std::lock_guard<std::mutex> lk(ctx->mu);
     JL_CUDA(ctx, cudaSetDevice(ctx->device));
+    // the host-pointer call's staging with every optional operand present
+    const size_t np = (size_t)ntok * top_k;
+    const size_t stage = al256((size_t)ntok * hidden * 4) * 2 + al256((size_t)ntok * n_expert * 4) + al256(np * 4) * 2 +
+                         al256((size_t)n_expert * ffn * 4) * 2 + al256((size_t)n_expert * hidden * 4) +
+                         al256((size_t)n_expert * 4) * 2;
+    int rc = moe_grow_stage(ctx, stage);
+    if (rc) return rc;
     return jl_grow_scratch(ctx, jl_moe_scratch_bytes(ntok, n_expert, top_k, hidden, ffn));
 }
 
@@ -638,7 +681,8 @@ JL_EXPORT int jl_moe_dev(jl_ctx *ctx, float *out_dev, const void *h_dev, int h_d
     std::lock_guard<std::mutex> lk(ctx->mu);
     if (ctx->unhealthy) return jl_set_err(ctx, JL_ECUDA, "context is unhealthy after an earlier CUDA error");
     JL_CUDA(ctx, cudaSetDevice(ctx->device));
-    int rc = moe_dev_locked(ctx, out_dev, h_dev, h_dtype, logits_dev, ntok, desc, sel_out_dev, wt_out_dev, (cudaStream_t)stream);
+    const jl_moe_desc dl = desc_local(desc);
+    int rc = moe_dev_locked(ctx, out_dev, h_dev, h_dtype, logits_dev, ntok, &dl, sel_out_dev, wt_out_dev, (cudaStream_t)stream);
     if (rc == JL_OK) ctx->st.served++;
     return rc;
 }
@@ -650,9 +694,10 @@ JL_EXPORT int jl_moe_route_dev(jl_ctx *ctx, const float *logits_dev, int ntok, c
         return JL_EINVAL;
     std::lock_guard<std::mutex> lk(ctx->mu);
     JL_CUDA(ctx, cudaSetDevice(ctx->device));
-    moe_route_kernel<<<(ntok + 3) / 4, 128, 0, (cudaStream_t)stream>>>(logits_dev, desc->router_bias, ntok, desc->n_expert,
-                                                                     desc->top_k, desc->norm, desc->scale, sel_out_dev,
-                                                                     wt_out_dev);
+    const jl_moe_desc dl = desc_local(desc);
+    moe_route_kernel<<<(ntok + 3) / 4, 128, 0, (cudaStream_t)stream>>>(logits_dev, dl.router_bias, dl.sel_bias, ntok,
+                                                                     dl.n_expert, dl.top_k, dl.norm, dl.scale,
+                                                                     sel_out_dev, wt_out_dev);
     ctx->st.launches++;
     JL_CUDA(ctx, cudaGetLastError());
     return JL_OK;
@@ -665,7 +710,8 @@ JL_EXPORT int jl_moe_experts_dev(jl_ctx *ctx, float *y_dev, const void *h_dev, i
     std::lock_guard<std::mutex> lk(ctx->mu);
     if (ctx->unhealthy) return jl_set_err(ctx, JL_ECUDA, "context is unhealthy after an earlier CUDA error");
     JL_CUDA(ctx, cudaSetDevice(ctx->device));
-    int rc = moe_dev_locked(ctx, y_dev, h_dev, h_dtype, nullptr, nrows, desc, nullptr, nullptr, (cudaStream_t)stream,
+    const jl_moe_desc dl = desc_local(desc);
+    int rc = moe_dev_locked(ctx, y_dev, h_dev, h_dtype, nullptr, nrows, &dl, nullptr, nullptr, (cudaStream_t)stream,
                             expert_ids_dev);
     if (rc == JL_OK) ctx->st.served++;
     return rc;
@@ -678,64 +724,67 @@ JL_EXPORT int jl_moe(jl_ctx *ctx, float *out, const void *h, int h_dtype, const 
     std::lock_guard<std::mutex> lk(ctx->mu);
     if (ctx->unhealthy) return jl_set_err(ctx, JL_ECUDA, "context is unhealthy after an earlier CUDA error");
     JL_CUDA(ctx, cudaSetDevice(ctx->device));
+    const jl_moe_desc dcopy = desc_local(desc);
+    desc = &dcopy;
     const int E = desc->n_expert, K = desc->top_k, H = desc->hidden, F = desc->ffn;
     if (desc->type != JL_TYPE_MXFP4 || E < 1 || K < 1 || H < 64 || F < 64 || H % 64 || F % 64 || ntok < 1)
         return jl_set_err(ctx, JL_DECLINED, "the mixture layer serves MXFP4 banks with hidden and ffn multiples of 64");
+    jl_drain_graveyard(ctx);
     jl_weight *wg = nullptr, *wu = nullptr, *wd = nullptr;
-    int rc;
-    if ((rc = jl_resident_bank(ctx, desc->type, desc->gate, desc->gate_bytes, E, F, H, &wg))) return rc;
-    if ((rc = jl_resident_bank(ctx, desc->type, desc->up, desc->up_bytes, E, F, H, &wu))) return rc;
-    if ((rc = jl_resident_bank(ctx, desc->type, desc->down, desc->down_bytes, E, H, F, &wd))) return rc;
+    // the three banks stay pinned while they are fetched: fetching one never evicts another
+    int rc = jl_resident_bank(ctx, desc->type, desc->gate, desc->gate_bytes, E, F, H, &wg);
+    if (!rc) rc = jl_resident_bank(ctx, desc->type, desc->up, desc->up_bytes, E, F, H, &wu);
+    if (!rc) rc = jl_resident_bank(ctx, desc->type, desc->down, desc->down_bytes, E, H, F, &wd);
+    jl_resident_unpin(ctx);   // ctx->mu is held to the end of this call
+    if (rc) return rc;
     if ((rc = jl_grow_scratch(ctx, jl_moe_scratch_bytes(ntok, E, K, H, F)))) return rc;
 
     const size_t hb = (size_t)ntok * H * (h_dtype == JL_DT_F32 ? 4 : 2), ob = (size_t)ntok * H * 4;
     const size_t np = (size_t)ntok * K;
-    uint8_t *buf = nullptr;   // one temporary block: h | logits | out | sel | wt | biases
+    // one staging block of the context: h | logits | out | sel | wt | biases. It only grows (jl_moe_reserve
+    // pre-sizes it), so a steady-state call allocates nothing.
     const size_t nb_g = desc->gate_bias ? (size_t)E * F * 4 : 0, nb_u = desc->up_bias ? (size_t)E * F * 4 : 0;
     const size_t nb_d = desc->down_bias ? (size_t)E * H * 4 : 0, nb_r = desc->router_bias ? (size_t)E * 4 : 0;
+    const size_t nb_s = desc->sel_bias ? (size_t)E * 4 : 0;
     const size_t total = al256(hb) + al256((size_t)ntok * E * 4) + al256(ob) + al256(np * 4) * 2 + al256(nb_g) +
-                         al256(nb_u) + al256(nb_d) + al256(nb_r);
-    cudaError_t ce = cudaMalloc(&buf, total);
-    if (ce != cudaSuccess) { cudaGetLastError(); return jl_set_err(ctx, JL_ENOMEM, "cudaMalloc(%zu): %s", total, cudaGetErrorString(ce)); }
-    uint8_t *sp = buf;
+                         al256(nb_u) + al256(nb_d) + al256(nb_r) + al256(nb_s);
+    if ((rc = moe_grow_stage(ctx, total))) return rc;
+    uint8_t *sp = (uint8_t *)ctx->moe_stage;
     auto take = [&](size_t n) { uint8_t *r = sp; sp += al256(n); return r; };
     void *h_d = take(hb);
     float *lg_d = (float *)take((size_t)ntok * E * 4), *out_d = (float *)take(ob);
     int32_t *sel_d = (int32_t *)take(np * 4);
     float *wt_d = (float *)take(np * 4);
     float *bg = (float *)take(nb_g), *bu = (float *)take(nb_u), *bd = (float *)take(nb_d), *br = (float *)take(nb_r);
+    float *bs = (float *)take(nb_s);
     cudaStream_t s = ctx->stream;
-    ce = cudaMemcpyAsync(h_d, h, hb, cudaMemcpyHostToDevice, s);
+    cudaError_t ce = cudaMemcpyAsync(h_d, h, hb, cudaMemcpyHostToDevice, s);
     if (ce == cudaSuccess) ce = cudaMemcpyAsync(lg_d, logits, (size_t)ntok * E * 4, cudaMemcpyHostToDevice, s);
     if (ce == cudaSuccess) ce = cudaMemcpyAsync(out_d, out, ob, cudaMemcpyHostToDevice, s);   // the layer ADDS into out
     if (ce == cudaSuccess && nb_g) ce = cudaMemcpyAsync(bg, desc->gate_bias, nb_g, cudaMemcpyHostToDevice, s);
     if (ce == cudaSuccess && nb_u) ce = cudaMemcpyAsync(bu, desc->up_bias, nb_u, cudaMemcpyHostToDevice, s);
     if (ce == cudaSuccess && nb_d) ce = cudaMemcpyAsync(bd, desc->down_bias, nb_d, cudaMemcpyHostToDevice, s);
     if (ce == cudaSuccess && nb_r) ce = cudaMemcpyAsync(br, desc->router_bias, nb_r, cudaMemcpyHostToDevice, s);
+    if (ce == cudaSuccess && nb_s) ce = cudaMemcpyAsync(bs, desc->sel_bias, nb_s, cudaMemcpyHostToDevice, s);
     rc = JL_OK;
     if (ce == cudaSuccess) {
         jl_moe_desc dd = *desc;
         dd.gate = wg; dd.up = wu; dd.down = wd;
         dd.gate_bias = nb_g ? bg : nullptr; dd.up_bias = nb_u ? bu : nullptr; dd.down_bias = nb_d ? bd : nullptr;
-        dd.router_bias = nb_r ? br : nullptr;
+        dd.router_bias = nb_r ? br : nullptr; dd.sel_bias = nb_s ? bs : nullptr;
         rc = moe_dev_locked(ctx, out_d, h_d, h_dtype, lg_d, ntok, &dd, sel_d, wt_d, s);
     }
     if (ce == cudaSuccess && rc == JL_OK) ce = cudaMemcpyAsync(out, out_d, ob, cudaMemcpyDeviceToHost, s);
     if (ce == cudaSuccess && rc == JL_OK && sel_out) ce = cudaMemcpyAsync(sel_out, sel_d, np * 4, cudaMemcpyDeviceToHost, s);
     if (ce == cudaSuccess && rc == JL_OK && wt_out) ce = cudaMemcpyAsync(wt_out, wt_d, np * 4, cudaMemcpyDeviceToHost, s);
-    int dstat = 0;
-    if (ce == cudaSuccess) ce = cudaMemcpyAsync(&dstat, ctx->dev_status, sizeof(int), cudaMemcpyDeviceToHost, s);
-    if (ce == cudaSuccess) ce = cudaStreamSynchronize(s);
-    cudaFree(buf);
     if (ce != cudaSuccess) {
+        cudaStreamSynchronize(s);
         ctx->unhealthy = true;
         return jl_set_err(ctx, JL_ECUDA, "mixture layer: %s", cudaGetErrorString(ce));
     }
+    const int rs = jl_read_status(ctx, s);   // synchronises the stream
     if (rc) return rc;
-    if (dstat) {
-        cudaMemset(ctx->dev_status, 0, sizeof(int));
-        return jl_set_err(ctx, JL_ETIMEDOUT, "a bounded device-side wait ran out (code %d)", dstat);
-    }
+    if (rs) return rs;
     ctx->st.served++;
     return JL_OK;
 }

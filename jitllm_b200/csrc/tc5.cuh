@@ -39,15 +39,21 @@ __device__ __forceinline__ void act_load8(const void *x, int x_dtype, size_t idx
 
 // One CTA per destination row `tok`. dst rows: `split` ? (2 tok: hi, 2 tok + 1: lo) : tok. The
 // source row is rowmap[tok] when a map is given (the mixture layer gathers token rows into
-// expert order this way), else tok.
+// expert order this way), else tok. A map entry outside [0, nsrc) reads row 0 instead (its destination row
+// belongs to no expert's list and is never consumed): a stale or hostile map cannot send the load out of bounds.
 static __global__ void __launch_bounds__(256)
 act_to_f16_kernel(const void *__restrict__ x, int x_dtype, __half *__restrict__ dst, float *__restrict__ inv_scale,
-                  int k, int split, const int *__restrict__ rowmap) {
+                  int k, int split, const int *__restrict__ rowmap, int nsrc) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     __shared__ float wmax[8];
     const int tok = blockIdx.x, tid = threadIdx.x;
-    const size_t base = (size_t)(rowmap ? rowmap[tok] : tok) * k;
+    int src = tok;
+    if (rowmap) {
+        src = rowmap[tok];
+        if ((unsigned)src >= (unsigned)nsrc) src = 0;
+    }
+    const size_t base = (size_t)src * k;
     float amax = 0.f;
     for (int c = tid; c < k / 8; c += 256) {
         float v[8];
@@ -188,11 +194,23 @@ __device__ __forceinline__ uint32_t hsub2u(uint32_t a, uint32_t b) {
     return d;
 }
 
-// Bounded wait that also gives up when another role of the CTA has aborted.
+// Bounded wait that also gives up when another role of the CTA has aborted. abort_flag[0] is the CTA's abort
+// word in shared memory, abort_flag[1] the wait limit in microseconds (0 = default), copied there at start-up.
+__device__ __forceinline__ uint64_t tc5_limit_ns(volatile int *abort_flag) {
+    const uint32_t us = (uint32_t)abort_flag[1];
+    return (uint64_t)(us ? us : JL_WAIT_DEFAULT_US) * 1000ull;
+}
 __device__ __forceinline__ bool tc5_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
-    for (uint32_t i = 0; i < JL_SPIN_LIMIT; i++) {
+#pragma unroll 1
+    for (int i = 0; i < 64; i++)
         if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 255u) == 255u && *abort_flag) return false;
+    const uint64_t limit = tc5_limit_ns(abort_flag), t0 = jl_gtime_ns();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 64; i++)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (jl_gtime_ns() - t0 > limit) break;
     }
     *abort_flag = 1;
     return false;
@@ -201,12 +219,16 @@ __device__ __forceinline__ bool tc5_wait(uint32_t bar, uint32_t parity, volatile
 // The same, for a role that is not on the critical path: backs off between polls so that it
 // does not take issue slots from the dequant warps it shares a scheduler with.
 __device__ __forceinline__ bool tc5_wait_relaxed(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
-    for (uint32_t i = 0; i < (JL_SPIN_LIMIT >> 4); i++) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t limit = tc5_limit_ns(abort_flag), t0 = jl_gtime_ns();
+    for (uint32_t i = 0;; i++) {
         if (mbar_try_wait(bar, parity)) return true;
         __nanosleep(256);
-        if ((i & 63u) == 63u && *abort_flag) return false;
+        if ((i & 63u) == 63u) {
+            if (*abort_flag) return false;
+            if (jl_gtime_ns() - t0 > limit) break;
+        }
     }
     *abort_flag = 1;
     return false;
 }
-

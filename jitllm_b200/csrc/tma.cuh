@@ -24,27 +24,47 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-#ifndef JL_MBAR_WAIT_OP
-#define JL_MBAR_WAIT_OP "mbarrier.try_wait.parity.shared::cta.b64"
-#endif
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        JL_MBAR_WAIT_OP " p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
         : "r"(bar), "r"(parity)
         : "memory");
     return ok != 0;
 }
-// Bounded wait: every spin in this library gives up after a limit and reports it, so a
-// lost copy can never wedge the GPU. Returns false when the limit ran out.
-#define JL_SPIN_LIMIT (1u << 24)
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    for (uint32_t i = 0; i < JL_SPIN_LIMIT; i++)
+// Bounded waits: every spin in this library gives up after a limit measured on the GPU's global
+// timer and reports it, so a lost copy, a missing peer or a barrier that never fills can never
+// wedge the GPU. The limit travels beside the status word the kernel reports into:
+//   status[0]  code a kernel sets when a wait ran out (0 = none)
+//   status[1]  the limit in microseconds (0 = JL_WAIT_DEFAULT_US)
+#define JL_WAIT_DEFAULT_US 2000000u
+__device__ __forceinline__ uint64_t jl_gtime_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ uint64_t jl_wait_limit_ns(const int *status) {
+    const uint32_t us = status ? reinterpret_cast<const volatile uint32_t *>(status)[1] : 0u;
+    return (uint64_t)(us ? us : JL_WAIT_DEFAULT_US) * 1000ull;
+}
+// Returns false when the limit ran out.
+__device__ __forceinline__ bool mbar_wait_ns(uint32_t bar, uint32_t parity, uint64_t limit_ns) {
+    const uint64_t t0 = jl_gtime_ns();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 32; i++)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (jl_gtime_ns() - t0 > limit_ns) return false;
+    }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const int *status) {
+#pragma unroll 1
+    for (int i = 0; i < 16; i++)
         if (mbar_try_wait(bar, parity)) return true;
-    return false;
+    return mbar_wait_ns(bar, parity, jl_wait_limit_ns(status));
 }
 
 // One 2-D tile, global -> shared, completion counted in bytes on `bar`.

@@ -87,11 +87,15 @@ class Device:
     """One B200, behind the reference's `nn.Device` surface."""
 
     def __init__(self, device: int = 0, pin_kernel: int = _lib.K_AUTO, pin_warps: int = 0,
-                 min_weight_bytes: int = 0, max_resident_bytes: int = 0, flags: int = 0):
+                 min_weight_bytes: int = 0, max_resident_bytes: int = 0, flags: int = 0,
+                 decode_form: int = _lib.FORM_AUTO, pin_stages: int = 0, pin_row_groups: int = 0,
+                 wait_limit_us: int = 0):
         self.lib = _lib.load()
         self.ctx = C.c_void_p()
         o = Opts(struct_size=C.sizeof(Opts), pin_kernel=pin_kernel, pin_warps=pin_warps,
-                 min_weight_bytes=min_weight_bytes, max_resident_bytes=max_resident_bytes, flags=flags)
+                 min_weight_bytes=min_weight_bytes, max_resident_bytes=max_resident_bytes, flags=flags,
+                 decode_form=decode_form, pin_stages=pin_stages, pin_row_groups=pin_row_groups,
+                 wait_limit_us=wait_limit_us)
         rc = self.lib.jl_open(device, C.byref(o), C.byref(self.ctx))
         if rc != _lib.OK:
             self.ctx = None
@@ -156,6 +160,14 @@ class Device:
         self._check(self.lib.jl_stats_get(self.ctx, C.byref(s)))
         return s
 
+    def StatusPoll(self, stream: int = 0) -> bool:
+        """True when no bounded device-side wait ran out since the last poll; False = JL_ETIMEDOUT (Err() says
+        which wait). Synchronises `stream`."""
+        self.last_status = self.lib.jl_status_poll(self.ctx, stream)
+        if self.last_status not in (_lib.OK, _lib.ETIMEDOUT):
+            raise DeviceError(self.last_status, self.Err())
+        return self.last_status == _lib.OK
+
     def FailAt(self, ordinals) -> None:
         arr = (C.c_int * len(ordinals))(*ordinals)
         self._check(self.lib.jl_test_fail_at(self.ctx, arr, len(ordinals)))
@@ -184,14 +196,15 @@ class Device:
 
     def MoeHost(self, out, h, logits, gate, up, down, n_expert: int, top_k: int, hidden: int, ffn: int,
                 act: int = _lib.ACT_SILU, norm: bool = True, scale: float = 1.0, t: int = _lib.MXFP4,
-                gate_bias=None, up_bias=None, down_bias=None, router_bias=None, sel_out=None, wt_out=None) -> bool:
+                gate_bias=None, up_bias=None, down_bias=None, router_bias=None, sel_out=None, wt_out=None,
+                sel_bias=None) -> bool:
         """State.moeBatch with every operand in host memory (numpy). out is ADDED to. False = declined."""
         ntok = logits.shape[0]
         d = MoeDesc(struct_size=C.sizeof(MoeDesc), type=t, n_expert=n_expert, top_k=top_k, hidden=hidden, ffn=ffn,
                     act=act, norm=int(norm), scale=scale, gate=_ptr(gate), up=_ptr(up), down=_ptr(down),
                     gate_bytes=_nbytes(gate), up_bytes=_nbytes(up), down_bytes=_nbytes(down),
                     gate_bias=_ptr(gate_bias), up_bias=_ptr(up_bias), down_bias=_ptr(down_bias),
-                    router_bias=_ptr(router_bias))
+                    router_bias=_ptr(router_bias), sel_bias=_ptr(sel_bias))
         return self.Moe(out, h, logits, ntok, d, sel_out, wt_out)
 
     def MoeRouteDev(self, logits, ntok: int, desc: MoeDesc, sel_out, wt_out, stream: int = 0) -> None:

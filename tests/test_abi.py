@@ -27,16 +27,16 @@ def test_library_exports_every_declared_symbol():
     lib = _lib.load()
     for name in _declared():
         assert hasattr(lib, name), name
-    assert lib.jl_abi_version() == 1
+    assert lib.jl_abi_version() == 2
     assert b"sm_100a" in lib.jl_version()
 
 
 def test_struct_sizes_match_the_header_layout():
     # natural C layout of the structs in include/jitllm_b200.h
-    assert C.sizeof(_lib.Opts) == 40
-    assert C.sizeof(_lib.Choice) == 32
+    assert C.sizeof(_lib.Opts) == 56
+    assert C.sizeof(_lib.Choice) == 44
     assert C.sizeof(_lib.Stats) == 72
-    assert C.sizeof(_lib.MoeDesc) == 120
+    assert C.sizeof(_lib.MoeDesc) == 128
 
 
 @pytest.mark.skipif(os.path.exists("/dev/nvidiactl"), reason="a GPU is present")

@@ -4,6 +4,7 @@ import pytest
 
 from conftest import nmse, parity_err
 from jitllm_b200 import DECLINED, K_MMA, K_SIMT, MXFP4, Q4_K, Q8_0, Device, synth
+from jitllm_b200._lib import FORM_FUSED, FORM_L1, FORM_SPLIT, FORM_WIDE
 
 pytestmark = pytest.mark.gpu
 
@@ -285,17 +286,117 @@ def test_mxfp4_decode_half_codes_and_wide_scales(orc):
     assert parity_err(out, ref) <= BAR
 
 
-@pytest.mark.parametrize("code", [442, 444, 446, 423, 243, 223])
+# (form, warps, ring stages, 16-row groups per CTA) of pinned Q4_K decode variants
+VARIANTS = [(FORM_WIDE, 16, 2, 4), (FORM_WIDE, 8, 3, 4), (FORM_WIDE, 8, 3, 2), (FORM_WIDE, 16, 2, 8),
+            (FORM_L1, 4, 3, 0), (FORM_L1, 2, 3, 0), (FORM_SPLIT, 8, 4, 0), (FORM_SPLIT, 2, 8, 0), (FORM_FUSED, 16, 2, 0)]
+
+
+@pytest.mark.parametrize("variant", VARIANTS)
 @pytest.mark.parametrize("nrows,k", [(16, 256), (100, 1024), (4096, 4096), (1030, 2048)])
-def test_q4k_decode_variants_by_code(orc, code, nrows, k):
-    """The single-launch wide forms (4xx: a CTA of 32..128 rows converts the activation row itself) and the
-    small-CTA split forms (2xx), each pinned by its code."""
-    with Device(0, pin_kernel=K_MMA, pin_warps=code) as d:
-        out, ref, w, x = _check(d, orc, Q4_K, nrows, k, 0xB2D0 + code + nrows)
+def test_q4k_decode_variants_pinned_by_form(orc, variant, nrows, k):
+    """Every form of the Q4_K tensor-core decode, pinned through jl_opts (decode_form, pin_warps, pin_stages,
+    pin_row_groups): the single-launch wide forms (a CTA of 32..128 rows converts the activation row itself),
+    the small-CTA forms that read the operand through L1, split and fused. jl_select reports the pinned
+    variant, the result meets the oracle and repeats bit for bit."""
+    form, warps, stages, rg = variant
+    with Device(0, pin_kernel=K_MMA, decode_form=form, pin_warps=warps, pin_stages=stages, pin_row_groups=rg) as d:
+        ch = d.Select(Q4_K, nrows, k, 1)
+        assert (ch.kernel, ch.form, ch.warps, ch.stages) == (K_MMA, form, warps, stages)
+        assert ch.rows_per_cta == 16 * max(rg, 1) and ch.grid == -(-(-(-nrows // 16)) // max(rg, 1))
+        out, ref, w, x = _check(d, orc, Q4_K, nrows, k, 0xB2D0 + form * 100 + warps + nrows)
         assert nmse(out, ref) < 1e-8
         out2 = np.empty_like(out)
         assert d.MatVec(out2, Q4_K, w, x, nrows, k)
         assert np.array_equal(out.view(np.uint32), out2.view(np.uint32))
+
+
+@pytest.mark.parametrize("t,nrows,k,ntok", [(Q4_K, 4096, 4096, 1), (Q4_K, 14336, 4096, 1), (Q4_K, 4096, 14336, 1),
+                                             (Q4_K, 64, 512, 1), (Q4_K, 4096, 4096, 4), (Q8_0, 4096, 4096, 1),
+                                             (Q8_0, 1024, 4096, 8), (MXFP4, 2880, 2880, 1), (MXFP4, 96, 576, 1),
+                                             (Q4_K, 4096, 4096, 32), (Q8_0, 4096, 4096, 32)])
+@pytest.mark.parametrize("flags", [0, 16])
+def test_select_reports_what_launches(t, nrows, k, ntok, flags):
+    """jl_select's answer and the launch share one selection: the number of kernels a device-pointer call adds
+    to jl_stats.launches equals jl_choice.launches, and the default 4096x4096 decode reports the wide form
+    that actually runs (64-row CTAs, one per row group of four), not a 16-row grid."""
+    import torch
+    rng = synth.rng_for(77)
+    with Device(0, flags=flags) as d:
+        d.Reserve(nrows, k, ntok)
+        h = d.Upload(t, synth.matrix(rng, t, nrows, k), nrows, k)
+        ch = d.Select(t, nrows, k, ntok)
+        assert ch is not None and ch.launches >= 1 and ch.grid >= 1
+        x = torch.randn(ntok, k, device="cuda")
+        out = torch.empty(ntok, nrows, device="cuda")
+        n0 = d.Stats().launches
+        d.MatMulDev(out, h, x, ntok, torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+        assert d.Stats().launches - n0 == ch.launches
+        if t == Q4_K and ch.kernel == K_MMA:
+            assert ch.tile_k == 32 and ch.form in (FORM_SPLIT, FORM_FUSED, FORM_WIDE, FORM_L1)
+            assert ch.launches == (2 if ch.form in (FORM_SPLIT, FORM_L1) else 1)
+        if (t, nrows, k, ntok, flags) == (Q4_K, 4096, 4096, 1, 0):
+            assert (ch.form, ch.warps, ch.rows_per_cta, ch.grid, ch.stages) == (FORM_WIDE, 16, 64, 64, 2)
+        h.free()
+
+
+def test_a_wait_that_runs_out_surfaces_as_etimedout_and_the_context_stays_usable(orc):
+    """Every device-side wait is bounded by the GPU's global timer. A test kernel waits (limit 1 ms) on an
+    mbarrier that expects bytes nobody sends; it records the timeout and returns. jl_status_poll reports
+    JL_ETIMEDOUT once, then JL_OK, and the same context still serves a matvec. No GPU fault is involved."""
+    import time
+    from jitllm_b200 import _lib
+    with Device(0) as d:
+        assert d.StatusPoll()
+        t0 = time.perf_counter()
+        assert d.lib.jl_test_wait_timeout(d.ctx, 1000, None) == _lib.OK
+        assert not d.StatusPoll()
+        assert time.perf_counter() - t0 < 1.0                      # the wait gave up after about a millisecond
+        assert d.last_status == _lib.ETIMEDOUT and "test wait" in d.Err()
+        assert d.StatusPoll()                                      # cleared on read
+        out, ref, _, _ = _check(d, orc, Q4_K, 256, 1024, 3)
+        assert parity_err(out, ref) <= BAR
+        assert d.lib.jl_noalloc_status(None) == _lib.OK
+
+
+def test_eviction_under_a_cap_re_uploads_with_correct_results(orc):
+    """max_resident_bytes: the least recently used copy makes room, a later call on the evicted tensor uploads
+    it again and still matches the oracle."""
+    rng = synth.rng_for(31)
+    nrows, k = 512, 1024
+    ws = [synth.q4k_matrix(rng, nrows, k) for _ in range(3)]
+    x = synth.activations(rng, 1, k)[0]
+    one = ws[0].nbytes
+    with Device(0, max_resident_bytes=2 * one + 16) as d:
+        out = np.empty(nrows, np.float32)
+        for w in ws:
+            assert d.MatVec(out, Q4_K, w, x, nrows, k), d.Err()
+        st = d.Stats()
+        assert st.uploads == 3 and st.resident_bytes == 2 * one
+        assert d.MatVec(out, Q4_K, ws[0], x, nrows, k), d.Err()    # evicted above: uploaded again
+        assert d.Stats().uploads == 4 and d.Stats().resident_bytes == 2 * one
+        assert parity_err(out, orc.matmul_f64(Q4_K, ws[0], x, nrows, k, 1)[0]) <= BAR
+        assert d.MatVec(out, Q4_K, ws[2], x, nrows, k) and d.Stats().uploads == 4   # still resident
+    with Device(0, max_resident_bytes=one // 2) as d:              # a cap below one tensor: refused, not served wrongly
+        assert not d.MatVec(out, Q4_K, ws[0], x, nrows, k)
+        assert d.last_status == -3
+
+
+def test_forget_unlinks_at_once_and_frees_on_the_next_serving_call(orc):
+    rng = synth.rng_for(32)
+    nrows, k = 256, 1024
+    w, w2 = synth.q4k_matrix(rng, nrows, k), synth.q4k_matrix(rng, nrows, k)
+    x = synth.activations(rng, 1, k)[0]
+    out = np.empty(nrows, np.float32)
+    with Device(0) as d:
+        assert d.MatVec(out, Q4_K, w, x, nrows, k)
+        d.Forget(w)
+        st = d.Stats()
+        assert st.forgets == 1 and st.resident_bytes == 0
+        w[:] = w2                                                   # the caller may reuse the memory after Forget
+        assert d.MatVec(out, Q4_K, w, x, nrows, k)
+        assert d.Stats().uploads == 2
+        assert parity_err(out, orc.matmul_f64(Q4_K, w2, x, nrows, k, 1)[0]) <= BAR
 
 
 @pytest.mark.parametrize("t", [Q4_K, Q8_0, MXFP4])

@@ -128,3 +128,76 @@ def test_moe_scale_ranges_cover_both_dequant_forms(dev, orc, e_lo, e_hi):
     assert parity_err(out, ref) <= BAR, (parity_err(out, ref), nmse(out, ref))
     for w in (gate, up, down):
         dev.Forget(w)
+
+
+def test_selection_only_bias_changes_the_choice_not_the_weights(dev, orc):
+    """MoEGate.Bias (internal/oracle/moe.go:204-262): added to the gated scores for the selection only; the
+    weights come from the unbiased scores. Compared with the oracle's bias path."""
+    rng = synth.rng_for(41)
+    E, topk, hidden, ffn, ntok = 16, 4, 128, 128, 33
+    gate, up, down = _layer(rng, E, hidden, ffn)
+    h = synth.activations(rng, ntok, hidden) * np.float32(0.25)
+    logits = synth.activations(rng, ntok, E)
+    sel_bias = (rng.standard_normal(E) * 0.2).astype(np.float32)
+    rsel = np.zeros((ntok, topk), np.int32)
+    rwt = np.zeros((ntok, topk), np.float32)
+    plain = np.zeros((ntok, topk), np.int32)
+    for i in range(ntok):
+        sc = orc.softmax(logits[i])
+        rsel[i], _, rwt[i], _, _ = orc.moe_router(sc, topk, bias=sel_bias)
+        plain[i] = orc.moe_router(sc, topk)[0]
+    assert not np.array_equal(rsel, plain), "the bias must change at least one selection for this test to mean anything"
+    ref = orc.moe_layer(h, MXFP4, gate, up, down, rsel, rwt, E, hidden, ffn)
+    out = np.zeros((ntok, hidden), np.float32)
+    sel = np.full((ntok, topk), -7, np.int32)
+    wt = np.full((ntok, topk), np.nan, np.float32)
+    assert dev.MoeHost(out, h, logits, gate, up, down, E, topk, hidden, ffn, sel_bias=sel_bias, sel_out=sel, wt_out=wt), dev.Err()
+    assert np.array_equal(sel, rsel)
+    assert np.allclose(wt, rwt, rtol=2e-6, atol=0)
+    assert parity_err(out, ref) <= BAR
+    for w in (gate, up, down):
+        dev.Forget(w)
+
+
+def test_a_row_of_nan_logits_gets_no_contribution_and_the_rest_still_match(dev, orc):
+    """A row whose logits are all NaN selects nothing (sel = -1 in every slot): its output row is left as it was,
+    every other row matches the oracle, and nothing reads outside the activation rows (the unused tail of the
+    per-expert token lists names row 0)."""
+    rng = synth.rng_for(43)
+    E, topk, hidden, ffn, ntok = 8, 2, 128, 128, 12
+    gate, up, down = _layer(rng, E, hidden, ffn)
+    h = synth.activations(rng, ntok, hidden) * np.float32(0.25)
+    logits = synth.activations(rng, ntok, E)
+    bad = [3, 11]
+    logits[bad] = np.nan
+    good = [i for i in range(ntok) if i not in bad]
+    before = synth.activations(rng, ntok, hidden)
+    out = before.copy()
+    sel = np.full((ntok, topk), -7, np.int32)
+    wt = np.full((ntok, topk), np.nan, np.float32)
+    assert dev.MoeHost(out, h, logits, gate, up, down, E, topk, hidden, ffn, sel_out=sel, wt_out=wt), dev.Err()
+    assert (sel[bad] == -1).all()
+    assert np.array_equal(out[bad], before[bad])
+    ref, rsel, _ = _oracle(orc, h[good], logits[good], gate, up, down, E, topk, hidden, ffn)
+    assert np.array_equal(sel[good], rsel)
+    assert parity_err(out[good] - before[good], ref) <= BAR
+    for w in (gate, up, down):
+        dev.Forget(w)
+
+
+def test_banks_stay_pinned_while_a_capped_context_fetches_all_three(orc):
+    """With max_resident_bytes below the three banks' total the call is refused (JL_ENOMEM) instead of running on a
+    bank that fetching the next one evicted; with room for exactly three it is served."""
+    rng = synth.rng_for(44)
+    E, topk, hidden, ffn, ntok = 4, 2, 64, 64, 6
+    gate, up, down = _layer(rng, E, hidden, ffn)
+    h = synth.activations(rng, ntok, hidden) * np.float32(0.25)
+    logits = synth.activations(rng, ntok, E)
+    out = np.zeros((ntok, hidden), np.float32)
+    with Device(0, max_resident_bytes=gate.nbytes * 2 + 8) as d:
+        assert not d.MoeHost(out, h, logits, gate, up, down, E, topk, hidden, ffn)
+        assert d.last_status == -3
+    with Device(0, max_resident_bytes=gate.nbytes * 3) as d:
+        assert d.MoeHost(out, h, logits, gate, up, down, E, topk, hidden, ffn), d.Err()
+        ref, _, _ = _oracle(orc, h, logits, gate, up, down, E, topk, hidden, ffn)
+        assert parity_err(out, ref) <= BAR
