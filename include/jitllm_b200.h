@@ -217,7 +217,11 @@ int jl_moe_experts_dev(jl_ctx *ctx, float *y_dev, const void *h_dev, int h_dtype
  * jl_moe_dev never needs more than it finds. */
 int jl_moe_reserve(jl_ctx *ctx, int ntok, int n_expert, int top_k, int hidden, int ffn);
 
-/* ---- per-shape selection: batchMV / chooseSplit -------------------------- */
+/* ---- per-shape selection: batchMV / chooseSplit --------------------------
+ * What a call with f32 activations of this shape launches (jl_matvec, jl_matvec_dev, jl_matmul* with
+ * JL_DT_F32): selection and launch read the same table, and jl_stats.launches grows by
+ * jl_choice.launches per served call. 16-bit activations take one MMA column per token instead
+ * of two in the tcgen05 GEMM (tile_n / split_k may then differ). */
 int jl_select(jl_ctx *ctx, uint32_t type, int nrows, int k, int ntok, jl_choice *out);
 
 /* ---- integer view of the blocks: kernels.extract (jit/gpu/kernels/pack.go:252-386)
@@ -298,6 +302,59 @@ int jl_aux_attn_decode(float *out /* or NULL when operand_out is given */, void 
  * host-pointer call): size the context first, then ask. */
 void *jl_decode_operand(jl_ctx *ctx, const jl_weight *w, int ntok);
 int jl_matvec_dev_prepared(jl_ctx *ctx, float *out_dev, const jl_weight *w, int ntok, void *stream);
+
+/* ---- whole blocks in one submission: nn.LayerDevice (engine/nn/device.go:1096-1176) ------------
+ * PrepLayer hands a block's weights to the device, Layers runs blocks [lo, hi) for the positions of one
+ * step without the residual stream leaving the device, an optional Head continues the same submission
+ * with the output norm and the vocabulary projection (device.go:1104-1118), and EmbedDevice fills the
+ * residual row from the token id on the card (device.go:1178-1191). Here: ONE persistent kernel per decode
+ * step of ONE sequence runs every block (fused: residual add + RMSNorm, q|k|v, RoPE + KV append,
+ * attention over the cache, o, gate|up with SiLU(gate)*up, down), the head and the greedy argmax. The
+ * weights are Q4_K jl_weight handles of this context (q|k|v and gate|up row-concatenated, as the
+ * reference's MatVecSegments / Gate2 fuse them, jit/gpu/kernels/matvec.go:283-290); everything else is a
+ * device pointer. Shapes the block kernel does not serve are DECLINED at prep and the caller keeps its
+ * per-matvec path: head_dim must be 128, 1, 2 or 4 query heads per kv head, rows of at most 16384.
+ * Tensor parallel (world > 1): q|k|v, gate|up and the head hold this rank's rows, o and down this rank's
+ * k-range; the ranks exchange the row-parallel partial sums inside the kernel through peer-mapped slot
+ * buffers (jl_tp_*), one process per GPU. */
+typedef struct jl_layers jl_layers;
+typedef struct jl_layers_block {
+    const jl_weight *qkv, *o, *gate_up, *down;
+    const float *attn_norm, *ffn_norm;   /* [hidden] f32, or NULL for all ones */
+    void *k_cache, *v_cache;             /* bf16 [n_kv][max_len][128] of the one sequence */
+} jl_layers_block;
+typedef struct jl_layers_desc {
+    uint32_t struct_size;
+    int32_t n_layer, hidden, n_head, n_kv, head_dim, ffn, vocab, max_len; /* n_head, n_kv, ffn, vocab: THIS rank's share */
+    float eps;
+    const jl_layers_block *blocks;       /* host array [n_layer] */
+    const jl_weight *head;               /* [vocab][hidden] or NULL: no head, no argmax */
+    const float *final_norm;             /* [hidden] f32 or NULL */
+    const void *emb_bf16;                /* [all token ids][hidden] bf16: the residual row of *tok */
+    const float *cos_t, *sin_t;          /* f32 [max_len][64], adjacent-pair rotation */
+    int32_t rank, world;                 /* tensor parallel; world <= 1: none */
+} jl_layers_desc;
+int jl_layers_prep(jl_ctx *ctx, const jl_layers_desc *desc, jl_layers **out);
+void jl_layers_free(jl_ctx *ctx, jl_layers *layers);
+/* One decode step. *tok_dev (token id) and *pos_dev (its position) are read ON THE DEVICE, so a captured
+ * graph can be replayed; with advance != 0 the kernel stores the next token into *tok_dev and increments
+ * *pos_dev itself. logits_out_dev ([vocab] f32) and next_tok_dev may be NULL. Asynchronous on `stream`;
+ * a wait that ran out inside the kernel is reported by jl_status_poll. */
+int jl_layers_run(jl_ctx *ctx, jl_layers *layers, long long *tok_dev, long long *pos_dev, float *logits_out_dev,
+                  long long *next_tok_dev, int advance, void *stream);
+
+/* ---- tensor-parallel exchange without a collective library (no counterpart in the reference, which has
+ * no tensor parallelism: docs/perf/current.md:582) ------------------------------------------------
+ * Each rank owns a slot buffer (jl_tp_slot) that the other ranks' kernels store their partial sums and a
+ * sequence flag into with plain peer stores over NVLink. One process per GPU: export the slot as a 64-byte
+ * CUDA IPC handle, exchange the handles by any host channel, open the peers' handles, hand all world
+ * pointers (own slot at [rank]) to jl_tp_attach, then meet once on the host before the first step. In
+ * one process with peer access enabled the raw pointers can be attached directly. */
+int jl_tp_slot(jl_ctx *ctx, jl_layers *layers, void **slot_dev, size_t *bytes);
+int jl_tp_ipc_export(const void *dev_ptr, void *handle64);
+int jl_tp_ipc_open(const void *handle64, void **dev_ptr);
+int jl_tp_ipc_close(void *dev_ptr);
+int jl_tp_attach(jl_ctx *ctx, jl_layers *layers, void *const *peer_slots, int n);
 
 /* ---- bounded device waits ---------------------------------------------------
  * Every wait inside a kernel of this library (an mbarrier a copy completes, a ring slot, a grid

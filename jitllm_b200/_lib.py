@@ -59,6 +59,19 @@ class MoeDesc(C.Structure):
                 ("router_bias", C.c_void_p), ("sel_bias", C.c_void_p)]
 
 
+class LayersBlock(C.Structure):
+    _fields_ = [("qkv", C.c_void_p), ("o", C.c_void_p), ("gate_up", C.c_void_p), ("down", C.c_void_p),
+                ("attn_norm", C.c_void_p), ("ffn_norm", C.c_void_p), ("k_cache", C.c_void_p), ("v_cache", C.c_void_p)]
+
+
+class LayersDesc(C.Structure):
+    _fields_ = [("struct_size", C.c_uint32), ("n_layer", C.c_int32), ("hidden", C.c_int32), ("n_head", C.c_int32),
+                ("n_kv", C.c_int32), ("head_dim", C.c_int32), ("ffn", C.c_int32), ("vocab", C.c_int32),
+                ("max_len", C.c_int32), ("eps", C.c_float), ("blocks", C.POINTER(LayersBlock)), ("head", C.c_void_p),
+                ("final_norm", C.c_void_p), ("emb_bf16", C.c_void_p), ("cos_t", C.c_void_p), ("sin_t", C.c_void_p),
+                ("rank", C.c_int32), ("world", C.c_int32)]
+
+
 # Every symbol include/jitllm_b200.h declares: (restype, argtypes).
 _VP, _I, _SZ, _U32 = C.c_void_p, C.c_int, C.c_size_t, C.c_uint32
 SYMBOLS = {
@@ -86,6 +99,14 @@ SYMBOLS = {
     "jl_matmul_dev": (_I, [_VP, _VP, _I, _VP, _VP, _I, _I, _VP]),
     "jl_moe_dev": (_I, [_VP, _VP, _VP, _I, _VP, _I, C.POINTER(MoeDesc), _VP, _VP, _VP]),
     "jl_test_fail_at": (_I, [_VP, C.POINTER(C.c_int), _I]),
+    "jl_layers_prep": (_I, [_VP, C.POINTER(LayersDesc), C.POINTER(_VP)]),
+    "jl_layers_free": (None, [_VP, _VP]),
+    "jl_layers_run": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _I, _VP]),
+    "jl_tp_slot": (_I, [_VP, _VP, C.POINTER(_VP), C.POINTER(C.c_size_t)]),
+    "jl_tp_ipc_export": (_I, [_VP, _VP]),
+    "jl_tp_ipc_open": (_I, [_VP, C.POINTER(_VP)]),
+    "jl_tp_ipc_close": (_I, [_VP]),
+    "jl_tp_attach": (_I, [_VP, _VP, C.POINTER(_VP), _I]),
     "jl_status_poll": (_I, [_VP, _VP]),
     "jl_noalloc_status": (_I, [_VP]),
     "jl_test_wait_timeout": (_I, [_VP, _U32, _VP]),

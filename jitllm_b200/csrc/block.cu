@@ -1,0 +1,936 @@
+// Whole decoder blocks as ONE persistent kernel per token: the reference's LayerDevice seam
+// (engine/nn/device.go:1096-1176: PrepLayer uploads a block's weights, Layers runs blocks [lo, hi)
+// as one submission without the residual stream leaving the device, an optional Head continues the
+// same submission with the output norm and the vocabulary projection; EmbedDevice fills the
+// residual row from a token id on the card, :1178-1191).
+//
+// A decode step at batch 1 is a chain of small dependent matvecs (Llama-3-8B: 9.4 .. 66 MB of
+// Q4_K weights each). Launched one by one each pays a launch, a ramp and a tail, and HBM idles
+// between them. Here one cooperative launch of one CTA per SM walks a list of PHASES,
+//     qkv -> attention -> o -> gate|up -> down      (per block),   head,   argmax
+// separated by grid barriers. What makes it fast:
+//   * every warp owns a TMA ring of weight tiles (16 rows x one 144-byte super-block per copy) that
+//     runs ACROSS phases: weights do not depend on activations, so while a CTA waits at a barrier
+//     its warps' rings are already filling with the next phase's tiles and HBM never idles;
+//   * the glue between matvecs lives in the phases' prologues and epilogues: residual add +
+//     RMSNorm + conversion of the activation row into the decode operand (every CTA redoes the
+//     16 KB row: cheaper than a phase of its own), SiLU(gate)*up in the gate|up epilogue (a tile
+//     is 8 gate rows + 8 matching up rows: the reference's Gate2, jit/gpu/kernels/matvec.go:283-290),
+//     RoPE and the KV-cache append inside the attention phase, argmax after the head;
+//   * tensor parallel ranks exchange the row-parallel partial sums themselves: the o and down
+//     epilogues store their [hidden] partial row into every rank's slot buffer over NVLink with
+//     plain peer stores, a flag per rank carries a sequence number, and the next prologue sums the
+//     slots in rank order (bit-stable). No collective library call sits inside a token.
+// Every wait (ring slot, grid barrier, peer flag) is bounded by the GPU's global timer; when one
+// runs out the kernel records a code, raises an abort word that every other wait polls, waits
+// (bounded) for its own copies in flight and returns.
+#include "jl_internal.cuh"
+#include "tma.cuh"
+#include "q4k_dot.cuh"
+
+#include <string.h>
+
+#define BK_WARPS 16
+#define BK_THREADS (BK_WARPS * 32)
+#define BK_STAGES 3
+#define BK_TILE 2304                 // 16 rows x 144 B
+#define BK_MAX_NSB 64                // longest activation row: 64 super-blocks = 16384 elements
+#define BK_ROUND_TASKS 256           // warp-tasks whose partial sums one round keeps in shared memory
+#define BK_ATT_CHUNK 32              // cache positions per attention task
+#define BK_ATT_ROW 272               // bytes of a staged K/V row: 256 + 16 of padding (bank spread)
+#define BK_ATT_D 128
+#define BK_MAX_G 4                   // query heads per kv head
+#define BK_MAX_WORLD 8
+#define BK_ATT_SUB_BYTES 20480       // shared memory of one 128-thread attention group
+
+enum { BK_MATVEC = 0, BK_ATTN = 1, BK_FINAL = 2 };
+enum { BK_PRO_NORM = 0, BK_PRO_PLAIN = 1 };
+enum { BK_EPI_STORE = 0, BK_EPI_GATE2 = 1, BK_EPI_ARGMAX = 2 };
+
+struct bk_phase {
+    int kind;
+    // ---- matvec
+    int map;            // index of the weight's tensor map: box 144 B x 16 rows (GATE2: x 8 rows)
+    int nrows;          // output values (GATE2: ffn = the rows of the gate half)
+    int nsb;            // super-blocks per row
+    int prologue, epilogue;
+    int up_row0;        // GATE2: first row of the up half inside the map
+    int exchange;       // outputs go to every rank's slot buffer, then the ranks meet
+    int nplanes;        // NORM: partial planes added to the residual row (0 = none)
+    int from_emb;       // NORM: the residual row is the embedding of *tok
+    const float *xsrc;  // NORM: residual row in
+    float *xdst;        // NORM: residual row out (written by CTA 0)
+    const float *planes;   // NORM: [nplanes][hidden]
+    const float *norm_w;   // NORM: [hidden]
+    const float *vsrc;     // PLAIN: the activation row
+    float *out;            // STORE / GATE2 / ARGMAX: output vector
+    float *peer_out[BK_MAX_WORLD];   // exchange: this rank's plane inside every rank's slot buffer
+    // ---- attention
+    const float *qkv;      // [(hq + 2 hkv) * 128] f32
+    float *att;            // [hq * 128] f32
+    void *k_cache, *v_cache;   // bf16 [hkv][max_len][128]
+};
+
+struct bk_params {
+    const bk_phase *phases;
+    int nphases;
+    const CUtensorMap *maps;
+    int hidden, hq, hkv, max_len;
+    float eps;
+    const float *cos_t, *sin_t;          // [max_len][64]
+    const __nv_bfloat16 *emb;            // [vocab_total][hidden]
+    long long *tok, *pos;
+    int advance;                         // FINAL: *tok = argmax, *pos += 1
+    long long *next_tok;                 // FINAL: argmax goes here too (may be NULL)
+    float *part;                         // attention partials
+    unsigned *tickets;                   // [hkv]
+    float *cand_val; int *cand_idx;      // [grid] per-CTA argmax candidates
+    unsigned *bar;                       // grid barrier counter, zero at launch
+    int *abort_word;                     // zero at launch
+    int *status;                         // [0] code, [1] limit in microseconds
+    int rank, world;
+    unsigned *flags;                     // local [world]: sequence number of the last exchange rank r finished
+    unsigned *peer_flags[BK_MAX_WORLD];  // the same array on every rank
+    unsigned *seq;                       // local: exchanges completed by earlier launches
+    int nexchange;                       // exchanges per launch
+};
+
+// ------------------------------------------------------------------ small helpers
+
+__device__ __forceinline__ unsigned bk_ld_acquire_gpu(const unsigned *p) {
+    unsigned v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ unsigned bk_ld_acquire_sys(const unsigned *p) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void bk_st_release_sys(unsigned *p, unsigned v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int bk_ld_volatile(const int *p) {
+    int v;
+    asm volatile("ld.volatile.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void bk_subbar(int id) {   // the 128 threads of one attention group
+    asm volatile("bar.sync %0, 128;" ::"r"(id) : "memory");
+}
+__device__ __forceinline__ void bk_bf16x8(const uint4 &v, float *f) {
+    const __nv_bfloat162 *p = reinterpret_cast<const __nv_bfloat162 *>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 t = __bfloat1622float2(p[i]);
+        f[2 * i] = t.x; f[2 * i + 1] = t.y;
+    }
+}
+
+__device__ __forceinline__ bool bk_mbar_wait(uint32_t bar, uint32_t parity, uint64_t limit_ns) {
+#pragma unroll 1
+    for (int i = 0; i < 16; i++)
+        if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_ns(bar, parity, limit_ns);
+}
+
+// Spins until *p >= target (p: a counter other CTAs or other GPUs advance). False on abort or timeout.
+template <bool SYS>
+__device__ __forceinline__ bool bk_wait_ge(const unsigned *p, unsigned target, const bk_params &P, uint64_t limit_ns, int code) {
+    const uint64_t t0 = jl_gtime_ns();
+    for (uint32_t i = 0;; i++) {
+        const unsigned v = SYS ? bk_ld_acquire_sys(p) : bk_ld_acquire_gpu(p);
+        if (v >= target) return true;
+        if ((i & 15u) == 15u) {
+            if (bk_ld_volatile(P.abort_word)) return false;
+            if (jl_gtime_ns() - t0 > limit_ns) {
+                atomicExch(P.status, code);
+                atomicExch(P.abort_word, 1);
+                return false;
+            }
+        }
+    }
+}
+
+// All CTAs of the grid meet. `done` counts the barriers this launch has passed. Writes made before the barrier by
+// any CTA are visible (through L2: read them with ld.cg / ld.volatile, never through L1) after it.
+__device__ __forceinline__ bool bk_grid_sync(const bk_params &P, int &done, uint64_t limit_ns, bool sys_fence) {
+    __shared__ int s_ok;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        if (sys_fence) __threadfence_system(); else __threadfence();
+        atomicAdd(P.bar, 1u);
+        s_ok = bk_wait_ge<false>(P.bar, (unsigned)(done + 1) * gridDim.x, P, limit_ns, 4) ? 1 : 0;
+        __threadfence();
+    }
+    __syncthreads();
+    done++;
+    return s_ok != 0;
+}
+
+// ------------------------------------------------------------------ the warp's stream of weight tiles
+//
+// A CTA owns a contiguous range of a matvec phase's 16-row groups; it walks them in rounds of as many row groups
+// as BK_ROUND_TASKS warp-tasks cover; inside a round warp w takes tasks w, w + 16, ... (task = row group x
+// super-block, super-block fastest). The fetch side (TMA requests) and the consume side walk the same sequence;
+// the fetch side runs BK_STAGES tasks ahead and simply continues into the following matvec phases.
+struct bk_cursor {
+    int p;        // phase index (nphases = exhausted)
+    int rg1;      // end of the CTA's row groups in this phase
+    int rbase;    // first row group of the current round
+    int nr;       // row groups in the current round
+    int t;        // this warp's task inside the round
+    int nsb;
+};
+
+__device__ __forceinline__ int bk_phase_nrg(const bk_phase &ph) {
+    return ph.epilogue == BK_EPI_GATE2 ? (ph.nrows + 7) / 8 : (ph.nrows + 15) / 16;
+}
+__device__ __forceinline__ int bk_rounds_rgs(int nsb) {
+    const int r = BK_ROUND_TASKS / nsb;
+    return r < 1 ? 1 : r;
+}
+// Positions the cursor on the warp's first task of the first matvec phase >= p that has one.
+__device__ __forceinline__ void bk_cursor_seek(bk_cursor &c, const bk_params &P, int p, int warp) {
+    for (; p < P.nphases; p++) {
+        const bk_phase &ph = P.phases[p];
+        if (ph.kind != BK_MATVEC) continue;
+        const int nrg = bk_phase_nrg(ph);
+        const int rg0 = (int)((long long)blockIdx.x * nrg / gridDim.x);
+        c.rg1 = (int)((long long)(blockIdx.x + 1) * nrg / gridDim.x);
+        c.nsb = ph.nsb;
+        const int rpr = bk_rounds_rgs(c.nsb);
+        for (c.rbase = rg0; c.rbase < c.rg1; c.rbase += rpr) {
+            c.nr = min(rpr, c.rg1 - c.rbase);
+            if (warp < c.nr * c.nsb) { c.p = p; c.t = warp; return; }
+        }
+    }
+    c.p = P.nphases;
+}
+__device__ __forceinline__ void bk_cursor_next(bk_cursor &c, const bk_params &P, int warp) {
+    c.t += BK_WARPS;
+    if (c.t < c.nr * c.nsb) return;
+    const int rpr = bk_rounds_rgs(c.nsb);
+    for (c.rbase += rpr; c.rbase < c.rg1; c.rbase += rpr) {
+        c.nr = min(rpr, c.rg1 - c.rbase);
+        if (warp < c.nr * c.nsb) { c.t = warp; return; }
+    }
+    bk_cursor_seek(c, P, c.p + 1, warp);
+}
+// Requests the cursor's tile into ring stage `stage` (one elected lane calls this).
+__device__ __forceinline__ void bk_fetch(const bk_cursor &c, const bk_params &P, uint32_t tile_smem, uint32_t bar) {
+    const bk_phase &ph = P.phases[c.p];
+    const int rg = c.rbase + c.t / c.nsb, sb = c.t % c.nsb;
+    const CUtensorMap *map = P.maps + ph.map;
+    mbar_arrive_expect_tx(bar, BK_TILE);
+    if (ph.epilogue == BK_EPI_GATE2) {
+        tma_load_2d(tile_smem, map, sb * 144, rg * 8, bar);                            // 8 gate rows
+        tma_load_2d(tile_smem + 8 * 144, map, sb * 144, ph.up_row0 + rg * 8, bar);     // the matching 8 up rows
+    } else {
+        tma_load_2d(tile_smem, map, sb * 144, rg * 16, bar);
+    }
+}
+
+// ------------------------------------------------------------------ prologues
+
+// The activation row of a NORM prologue: x + planes (rank order), or the embedding row of *tok.
+__device__ __forceinline__ float4 bk_resid4(const bk_params &P, const bk_phase &ph, int i4) {
+    float4 v;
+    if (ph.from_emb) {
+        const long long tok = *P.tok;
+        const uint2 u = __ldg(reinterpret_cast<const uint2 *>(P.emb + (size_t)tok * P.hidden) + i4);
+        const __nv_bfloat162 *b = reinterpret_cast<const __nv_bfloat162 *>(&u);
+        const float2 lo = __bfloat1622float2(b[0]), hi = __bfloat1622float2(b[1]);
+        v = make_float4(lo.x, lo.y, hi.x, hi.y);
+    } else {
+        v = __ldcg(reinterpret_cast<const float4 *>(ph.xsrc) + i4);
+    }
+    for (int r = 0; r < ph.nplanes; r++) {
+        const float4 d = __ldcg(reinterpret_cast<const float4 *>(ph.planes + (size_t)r * P.hidden) + i4);
+        v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+    }
+    return v;
+}
+
+// Builds the decode operand of the phase's activation row in shared memory (every CTA, the whole row).
+__device__ __forceinline__ void bk_prologue(const bk_params &P, const bk_phase &ph, uint8_t *xop, float *ssq) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nsb = ph.nsb;
+    if (ph.prologue == BK_PRO_NORM) {
+        float ss = 0.f;
+        for (int sb = warp; sb < nsb; sb += BK_WARPS)
+#pragma unroll
+            for (int hf = 0; hf < 2; ++hf) {
+                const int i4 = sb * 64 + hf * 32 + lane;
+                const float4 v = bk_resid4(P, ph, i4);
+                if (blockIdx.x == 0 && ph.xdst) reinterpret_cast<float4 *>(ph.xdst)[i4] = v;   // the new residual row
+                ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+            }
+#pragma unroll
+        for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (lane == 0) ssq[warp] = ss;
+        __syncthreads();
+        float tot = 0.f;
+#pragma unroll
+        for (int i = 0; i < BK_WARPS; i++) tot += ssq[i];      // fixed order: every CTA gets the same bits
+        const float r = rsqrtf(tot / (float)P.hidden + P.eps);
+        for (int sb = warp; sb < nsb; sb += BK_WARPS) {
+            float4 v[2];
+#pragma unroll
+            for (int hf = 0; hf < 2; ++hf) {
+                const int i4 = sb * 64 + hf * 32 + lane;
+                const float4 a = bk_resid4(P, ph, i4);
+                const float4 gw = ph.norm_w ? __ldg(reinterpret_cast<const float4 *>(ph.norm_w) + i4) : make_float4(1.f, 1.f, 1.f, 1.f);
+                v[hf] = make_float4(a.x * r * gw.x, a.y * r * gw.y, a.z * r * gw.z, a.w * r * gw.w);
+            }
+            q4k_prep_sb_vals(v[0], v[1], xop + (size_t)sb * Q4K_XP_SB_BYTES, lane);
+        }
+    } else {
+        for (int sb = warp; sb < nsb; sb += BK_WARPS) {
+            const float4 *s4 = reinterpret_cast<const float4 *>(ph.vsrc) + sb * 64;
+            q4k_prep_sb_vals(__ldcg(s4 + lane), __ldcg(s4 + 32 + lane), xop + (size_t)sb * Q4K_XP_SB_BYTES, lane);
+        }
+    }
+    __syncthreads();
+}
+
+// ------------------------------------------------------------------ attention phase
+//
+// One 128-thread group = one (kv head, chunk of BK_ATT_CHUNK cache positions) task, all G query heads of the kv
+// head at once. q and the new k are rotated here (adjacent-pair RoPE), rounded to bf16 as the cache stores them;
+// the group whose chunk holds the new position appends k and v to the cache. Partial (max, sum, weighted V)
+// records go to `part`; the group that takes the last ticket of its kv head merges them in chunk order.
+template <int G>
+__device__ void bk_attention(const bk_params &P, const bk_phase &ph, uint8_t *sm, int sub, int t) {
+    constexpr int HDR = (2 * G + 3) & ~3;
+    constexpr int STRIDE = HDR + G * BK_ATT_D;
+    uint8_t *tiles = sm;                                                   // K rows 0..31, V rows 32..63
+    float(*qs)[BK_ATT_D] = reinterpret_cast<float(*)[BK_ATT_D]>(sm + 2 * BK_ATT_CHUNK * BK_ATT_ROW);
+    float(*sc)[BK_ATT_CHUNK] = reinterpret_cast<float(*)[BK_ATT_CHUNK]>(qs + G);
+    float(*mred)[G] = reinterpret_cast<float(*)[G]>(sc + G);
+    float(*lred)[G] = mred + 4;
+    volatile unsigned *last = reinterpret_cast<volatile unsigned *>(lred + 4);
+    static_assert(2 * BK_ATT_CHUNK * BK_ATT_ROW + G * BK_ATT_D * 4 + G * BK_ATT_CHUNK * 4 + 8 * G * 4 + 16 <= BK_ATT_SUB_BYTES, "attention group smem");
+    static_assert(8 * G * BK_ATT_D * 4 <= 2 * BK_ATT_CHUNK * BK_ATT_ROW, "reduction buffer must fit in the tiles");
+    const int bid = 1 + sub;
+    const long long pos = *P.pos;
+    if (pos < 0 || pos >= P.max_len) return;
+    const int len = (int)pos + 1;
+    const int nchunk = (len + BK_ATT_CHUNK - 1) / BK_ATT_CHUNK;
+    const int nchunk_max = (P.max_len + BK_ATT_CHUNK - 1) / BK_ATT_CHUNK;
+    const int ntask = P.hkv * nchunk;
+    const int warp = t >> 5, lane = t & 31;
+    __nv_bfloat16 *kc = static_cast<__nv_bfloat16 *>(ph.k_cache), *vc = static_cast<__nv_bfloat16 *>(ph.v_cache);
+    for (int task = blockIdx.x * 4 + sub; task < ntask; task += gridDim.x * 4) {
+        const int kv = task / nchunk, chunk = task % nchunk;
+        const int s0 = chunk * BK_ATT_CHUNK;
+        const int cnt = min(BK_ATT_CHUNK, len - s0);
+        const int frow = (int)pos - s0;                                   // the new position's row, if inside this chunk
+        const bool fresh = frow >= 0 && frow < BK_ATT_CHUNK;
+        const size_t base_row = (size_t)kv * P.max_len + s0;
+        const uint4 *kg = reinterpret_cast<const uint4 *>(kc + base_row * BK_ATT_D);
+        const uint4 *vg = reinterpret_cast<const uint4 *>(vc + base_row * BK_ATT_D);
+        uint4 kreg[4], vreg[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {                                     // 512 16-byte pieces per tile, 4 per thread
+            const int piece = i * 128 + t;
+            const bool ok = s0 + (piece >> 4) < (int)pos;                 // rows before the new position come from the cache
+            kreg[i] = ok ? kg[piece] : make_uint4(0, 0, 0, 0);
+            vreg[i] = ok ? vg[piece] : make_uint4(0, 0, 0, 0);
+        }
+        const float *cs = P.cos_t + (size_t)pos * (BK_ATT_D / 2), *sn = P.sin_t + (size_t)pos * (BK_ATT_D / 2);
+        for (int pi = t; pi < G * (BK_ATT_D / 2); pi += 128) {            // q: rotate, round to bf16, scale
+            const int h = pi >> 6, j = pi & 63;
+            const float2 ab = __ldcg(reinterpret_cast<const float2 *>(ph.qkv + (size_t)(kv * G + h) * BK_ATT_D) + j);
+            const float c = cs[j], s = sn[j];
+            const __nv_bfloat162 o = __floats2bfloat162_rn(ab.x * c - ab.y * s, ab.x * s + ab.y * c);
+            const float2 f = __bfloat1622float2(o);
+            qs[h][2 * j] = f.x * 0.08838834764831845f;
+            qs[h][2 * j + 1] = f.y * 0.08838834764831845f;
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int piece = i * 128 + t, row = piece >> 4;
+            if (fresh && row == frow) continue;                           // written below from the new k, v
+            *reinterpret_cast<uint4 *>(tiles + row * BK_ATT_ROW + (piece & 15) * 16) = kreg[i];
+            *reinterpret_cast<uint4 *>(tiles + (BK_ATT_CHUNK + row) * BK_ATT_ROW + (piece & 15) * 16) = vreg[i];
+        }
+        if (fresh) {
+            const int j = t & 63;
+            __nv_bfloat162 o;
+            if (t < 64) {
+                const float2 ab = __ldcg(reinterpret_cast<const float2 *>(ph.qkv + (size_t)(P.hq + kv) * BK_ATT_D) + j);
+                const float c = cs[j], s = sn[j];
+                o = __floats2bfloat162_rn(ab.x * c - ab.y * s, ab.x * s + ab.y * c);
+                reinterpret_cast<__nv_bfloat162 *>(tiles + frow * BK_ATT_ROW)[j] = o;
+                reinterpret_cast<__nv_bfloat162 *>(kc + ((size_t)kv * P.max_len + pos) * BK_ATT_D)[j] = o;
+            } else {
+                const float2 ab = __ldcg(reinterpret_cast<const float2 *>(ph.qkv + (size_t)(P.hq + P.hkv + kv) * BK_ATT_D) + j);
+                o = __floats2bfloat162_rn(ab.x, ab.y);
+                reinterpret_cast<__nv_bfloat162 *>(tiles + (BK_ATT_CHUNK + frow) * BK_ATT_ROW)[j] = o;
+                reinterpret_cast<__nv_bfloat162 *>(vc + ((size_t)kv * P.max_len + pos) * BK_ATT_D)[j] = o;
+            }
+        }
+        bk_subbar(bid);
+        // scores: four threads per position, 32 dims each
+        const int p1 = t >> 2, qd = t & 3;
+        float s[G];
+#pragma unroll
+        for (int h = 0; h < G; ++h) s[h] = 0.f;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            float f[8];
+            bk_bf16x8(*reinterpret_cast<const uint4 *>(tiles + p1 * BK_ATT_ROW + (qd * 4 + c) * 16), f);
+#pragma unroll
+            for (int h = 0; h < G; ++h)
+#pragma unroll
+                for (int e = 0; e < 8; ++e) s[h] = fmaf(f[e], qs[h][(qd * 4 + c) * 8 + e], s[h]);
+        }
+#pragma unroll
+        for (int h = 0; h < G; ++h) {
+            s[h] += __shfl_xor_sync(0xffffffffu, s[h], 1);
+            s[h] += __shfl_xor_sync(0xffffffffu, s[h], 2);
+            if (p1 >= cnt) s[h] = -INFINITY;
+            float m = s[h];
+            for (int o = 16; o >= 4; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+            if (lane == 0) mred[warp][h] = m;
+        }
+        bk_subbar(bid);
+        float *my = P.part + ((size_t)kv * nchunk_max + chunk) * STRIDE;
+#pragma unroll
+        for (int h = 0; h < G; ++h) {
+            const float M = fmaxf(fmaxf(mred[0][h], mred[1][h]), fmaxf(mred[2][h], mred[3][h]));
+            float p = (p1 < cnt && qd == 0) ? __expf(s[h] - M) : 0.f;
+            if (qd == 0) sc[h][p1] = p;
+            for (int o = 16; o; o >>= 1) p += __shfl_xor_sync(0xffffffffu, p, o);
+            if (lane == 0) lred[warp][h] = p;
+        }
+        bk_subbar(bid);
+        if (t < G) {
+            my[t] = fmaxf(fmaxf(mred[0][t], mred[1][t]), fmaxf(mred[2][t], mred[3][t]));
+            my[G + t] = lred[0][t] + lred[1][t] + lred[2][t] + lred[3][t];
+        }
+        // weighted V: 16 threads per row (8 dims each), 8 position groups, 4 positions each
+        const int dg = t & 15, pg = t >> 4;
+        float acc[G][8];
+#pragma unroll
+        for (int h = 0; h < G; ++h)
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[h][e] = 0.f;
+#pragma unroll
+        for (int i = 0; i < BK_ATT_CHUNK / 8; ++i) {
+            const int p = pg + 8 * i;                                     // rows past cnt hold zeros and weight 0
+            float f[8];
+            bk_bf16x8(*reinterpret_cast<const uint4 *>(tiles + (BK_ATT_CHUNK + p) * BK_ATT_ROW + dg * 16), f);
+#pragma unroll
+            for (int h = 0; h < G; ++h) {
+                const float w = sc[h][p];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) acc[h][e] = fmaf(w, f[e], acc[h][e]);
+            }
+        }
+        bk_subbar(bid);                                                   // tiles consumed: reuse them
+        float(*red)[G][BK_ATT_D] = reinterpret_cast<float(*)[G][BK_ATT_D]>(tiles);
+#pragma unroll
+        for (int h = 0; h < G; ++h)
+#pragma unroll
+            for (int e = 0; e < 8; ++e) red[pg][h][dg * 8 + e] = acc[h][e];
+        bk_subbar(bid);
+#pragma unroll
+        for (int h = 0; h < G; ++h) {
+            float o = 0.f;
+#pragma unroll
+            for (int g8 = 0; g8 < 8; ++g8) o += red[g8][h][t];
+            my[HDR + h * BK_ATT_D + t] = o;
+        }
+        __threadfence();
+        bk_subbar(bid);
+        if (t == 0) *last = atomicAdd(&P.tickets[kv], 1u) == (unsigned)(nchunk - 1) ? 1u : 0u;
+        bk_subbar(bid);
+        if (*last) {
+            __threadfence();
+            // merge: warp w takes heads w, w+4, ...; chunks ascending (bit-stable), 16 loads in flight
+            const float *base = P.part + (size_t)kv * nchunk_max * STRIDE;
+            for (int h = warp; h < G; h += 4) {
+                constexpr int MAXR = 4;                                   // 128 chunks held in registers per pass
+                float mr[MAXR], lr[MAXR];
+#pragma unroll
+                for (int r = 0; r < MAXR; ++r) {
+                    const int s_ = lane + 32 * r;
+                    mr[r] = s_ < nchunk ? __ldcg(base + (size_t)s_ * STRIDE + h) : -INFINITY;
+                    lr[r] = s_ < nchunk ? __ldcg(base + (size_t)s_ * STRIDE + G + h) : 0.f;
+                }
+                float M = fmaxf(fmaxf(mr[0], mr[1]), fmaxf(mr[2], mr[3]));
+                for (int s_ = lane + 32 * MAXR; s_ < nchunk; s_ += 32) M = fmaxf(M, __ldcg(base + (size_t)s_ * STRIDE + h));
+                for (int o = 16; o; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+                float L = 0.f;
+#pragma unroll
+                for (int r = 0; r < MAXR; ++r) {
+                    mr[r] = __expf(mr[r] - M);                            // now the chunk's weight
+                    L = fmaf(lr[r], mr[r], L);
+                }
+                for (int s_ = lane + 32 * MAXR; s_ < nchunk; s_ += 32)
+                    L += __ldcg(base + (size_t)s_ * STRIDE + G + h) * __expf(__ldcg(base + (size_t)s_ * STRIDE + h) - M);
+                for (int o = 16; o; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
+                float4 a4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                const float *ob = base + HDR + h * BK_ATT_D + 4 * lane;
+                const int nreg = nchunk < 32 * MAXR ? nchunk : 32 * MAXR;
+#pragma unroll
+                for (int r = 0; r < MAXR; ++r) {
+                    for (int s0b = 32 * r; s0b < nreg && s0b < 32 * (r + 1); s0b += 16) {
+                        float4 v[16];
+#pragma unroll
+                        for (int u = 0; u < 16; ++u)
+                            v[u] = s0b + u < nreg ? __ldcg(reinterpret_cast<const float4 *>(ob + (size_t)(s0b + u) * STRIDE))
+                                                  : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                        for (int u = 0; u < 16; ++u) {
+                            const float w = __shfl_sync(0xffffffffu, mr[r], (s0b + u) & 31);
+                            a4.x = fmaf(v[u].x, w, a4.x); a4.y = fmaf(v[u].y, w, a4.y);
+                            a4.z = fmaf(v[u].z, w, a4.z); a4.w = fmaf(v[u].w, w, a4.w);
+                        }
+                    }
+                }
+                for (int s_ = nreg; s_ < nchunk; ++s_) {                  // very long sequences: the plain walk
+                    const float4 v = __ldcg(reinterpret_cast<const float4 *>(ob + (size_t)s_ * STRIDE));
+                    const float w = __expf(__ldcg(base + (size_t)s_ * STRIDE + h) - M);
+                    a4.x = fmaf(v.x, w, a4.x); a4.y = fmaf(v.y, w, a4.y);
+                    a4.z = fmaf(v.z, w, a4.z); a4.w = fmaf(v.w, w, a4.w);
+                }
+                const float inv = L > 0.f ? 1.f / L : 0.f;
+                *reinterpret_cast<float4 *>(ph.att + (size_t)(kv * G + h) * BK_ATT_D + 4 * lane) =
+                    make_float4(a4.x * inv, a4.y * inv, a4.z * inv, a4.w * inv);
+            }
+            if (t == 0) P.tickets[kv] = 0;                                // ready for the next attention phase
+        }
+        bk_subbar(bid);                                                   // the group's shared memory is free again
+    }
+}
+
+// ------------------------------------------------------------------ the kernel
+
+#define BK_RING_BYTES (BK_WARPS * BK_STAGES * BK_TILE)
+#define BK_XOP_BYTES (BK_MAX_NSB * Q4K_XP_SB_BYTES)
+#define BK_RED_BYTES (BK_ROUND_TASKS * 16 * 4)
+#define BK_WORK_BYTES (4 * BK_ATT_SUB_BYTES > BK_XOP_BYTES + BK_RED_BYTES ? 4 * BK_ATT_SUB_BYTES : BK_XOP_BYTES + BK_RED_BYTES)
+#define BK_SMEM_BYTES (BK_RING_BYTES + BK_WORK_BYTES + Q4K_XP_ZERO_BYTES + BK_WARPS * BK_STAGES * 8 + 64 * 4 + 128)
+
+__global__ void __launch_bounds__(BK_THREADS, 1) jl_block_kernel(const __grid_constant__ bk_params P) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    // [rings | work: operand + round partials, or the four attention groups | zero fragment | barriers | misc]
+    uint8_t *tiles = smem + (size_t)warp * BK_STAGES * BK_TILE;
+    uint8_t *work = smem + BK_RING_BYTES;
+    uint8_t *xop = work;
+    float *red = reinterpret_cast<float *>(work + BK_XOP_BYTES);
+    uint8_t *zero = work + BK_WORK_BYTES;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(zero + Q4K_XP_ZERO_BYTES) + warp * BK_STAGES;
+    float *misc = reinterpret_cast<float *>(zero + Q4K_XP_ZERO_BYTES + BK_WARPS * BK_STAGES * 8);   // 64 floats
+    const uint64_t limit_ns = jl_wait_limit_ns(P.status);
+
+    if (lane == 0) {
+#pragma unroll
+        for (int s = 0; s < BK_STAGES; s++) mbar_init(smem_u32(bars + s), 1);
+        mbar_init_fence();
+    }
+    if (tid < Q4K_XP_ZERO_BYTES / 4) reinterpret_cast<uint32_t *>(zero)[tid] = 0u;
+    __syncwarp();
+    // The ring runs ahead of everything else: the first BK_STAGES tiles of this warp are requested now.
+    bk_cursor fc;                       // fetch side
+    uint32_t fetched = 0, consumed = 0;
+    bk_cursor_seek(fc, P, 0, warp);
+    for (int s = 0; s < BK_STAGES && fc.p < P.nphases; s++) {
+        if (lane == 0) bk_fetch(fc, P, smem_u32(tiles + s * BK_TILE), smem_u32(bars + s));
+        bk_cursor_next(fc, P, warp);
+        fetched++;
+    }
+    __syncthreads();
+
+    int barriers_done = 0;
+    const unsigned seq_start = P.world > 1 ? bk_ld_acquire_gpu(P.seq) : 0u;     // exchanges finished by earlier launches
+    unsigned seq = seq_start;
+    bool alive = true;
+    float best_val = -INFINITY;
+    int best_idx = 0x7fffffff;
+
+    for (int p = 0; p < P.nphases && alive; p++) {
+        const bk_phase &ph = P.phases[p];
+        if (ph.kind == BK_MATVEC) {
+            bk_prologue(P, ph, xop, misc);
+            const int nrg = bk_phase_nrg(ph), nsb = ph.nsb;
+            const int rg0 = (int)((long long)blockIdx.x * nrg / gridDim.x), rg1 = (int)((long long)(blockIdx.x + 1) * nrg / gridDim.x);
+            const int rpr = bk_rounds_rgs(nsb);
+            for (int rbase = rg0; rbase < rg1 && alive; rbase += rpr) {
+                const int nr = min(rpr, rg1 - rbase), ntask = nr * nsb;
+                for (int tk = warp; tk < ntask; tk += BK_WARPS) {
+                    const int sb = tk % nsb;
+                    const uint32_t s = consumed % BK_STAGES, parity = (consumed / BK_STAGES) & 1u;
+                    if (!__all_sync(0xffffffffu, bk_mbar_wait(smem_u32(bars + s), parity, limit_ns))) {
+                        if (lane == 0) { atomicExch(P.status, 1); atomicExch(P.abort_word, 1); }
+                        alive = false;
+                        break;
+                    }
+                    const q4k_lane_tile w = q4k_lane_load(tiles + s * BK_TILE, g, t);
+                    consumed++;
+                    __syncwarp();        // every lane holds its share: the stage may be refilled
+                    if (fc.p < P.nphases) {
+                        if (lane == 0) bk_fetch(fc, P, smem_u32(tiles + s * BK_TILE), smem_u32(bars + s));
+                        bk_cursor_next(fc, P, warp);
+                        fetched++;
+                    }
+                    float accA = 0.f, accB = 0.f;
+                    q4k_dot_task(w, xop + (size_t)sb * Q4K_XP_SB_BYTES, zero, g, t, accA, accB);
+                    accA += __shfl_xor_sync(0xffffffffu, accA, 1);
+                    accA += __shfl_xor_sync(0xffffffffu, accA, 2);
+                    accB += __shfl_xor_sync(0xffffffffu, accB, 1);
+                    accB += __shfl_xor_sync(0xffffffffu, accB, 2);
+                    if (t == 0) {
+                        red[tk * 16 + g] = accA;
+                        red[tk * 16 + g + 8] = accB;
+                    }
+                }
+                alive = __syncthreads_and(alive ? 1 : 0) != 0;
+                if (!alive) break;
+                // the round's row groups: super-blocks in ascending order (run-to-run bit-stable)
+                if (ph.epilogue == BK_EPI_GATE2) {
+                    if (tid < nr * 8) {
+                        const int rgl = tid >> 3, r = tid & 7;
+                        float sg = 0.f, su = 0.f;
+                        for (int sb = 0; sb < nsb; sb++) {
+                            sg += red[(rgl * nsb + sb) * 16 + r];
+                            su += red[(rgl * nsb + sb) * 16 + r + 8];
+                        }
+                        const int o = (rbase + rgl) * 8 + r;
+                        if (o < ph.nrows) ph.out[o] = sg / (1.f + __expf(-sg)) * su;     // SiLU(gate) * up
+                    }
+                } else if (tid < nr * 16) {
+                    const int rgl = tid >> 4, r = tid & 15;
+                    float sum = 0.f;
+                    for (int sb = 0; sb < nsb; sb++) sum += red[(rgl * nsb + sb) * 16 + r];
+                    const int row = (rbase + rgl) * 16 + r;
+                    if (row < ph.nrows) {
+                        if (ph.exchange) {
+#pragma unroll 1
+                            for (int pr = 0; pr < P.world; pr++) ph.peer_out[pr][row] = sum;
+                        } else {
+                            ph.out[row] = sum;
+                        }
+                        if (ph.epilogue == BK_EPI_ARGMAX && (sum > best_val || (sum == best_val && row < best_idx))) {
+                            best_val = sum; best_idx = row;
+                        }
+                    }
+                }
+                __syncthreads();         // the round's partials are consumed
+            }
+            if (alive && ph.epilogue == BK_EPI_ARGMAX) {
+                // the CTA's candidate: largest value, lowest row on a tie
+                for (int o = 16; o; o >>= 1) {
+                    const float ov = __shfl_xor_sync(0xffffffffu, best_val, o);
+                    const int oi = __shfl_xor_sync(0xffffffffu, best_idx, o);
+                    if (ov > best_val || (ov == best_val && oi < best_idx)) { best_val = ov; best_idx = oi; }
+                }
+                int *misc_i = reinterpret_cast<int *>(misc + 32);
+                if (lane == 0) { misc[warp] = best_val; misc_i[warp] = best_idx; }
+                __syncthreads();
+                if (tid == 0) {
+                    float bv = misc[0]; int bi = misc_i[0];
+                    for (int i = 1; i < BK_WARPS; i++)
+                        if (misc[i] > bv || (misc[i] == bv && misc_i[i] < bi)) { bv = misc[i]; bi = misc_i[i]; }
+                    P.cand_val[blockIdx.x] = bv; P.cand_idx[blockIdx.x] = bi;
+                }
+            }
+        } else if (ph.kind == BK_ATTN) {
+            const int G = P.hq / P.hkv, sub = tid >> 7, t128 = tid & 127;
+            uint8_t *asm_ = work + (size_t)sub * BK_ATT_SUB_BYTES;
+            if (G == 4) bk_attention<4>(P, ph, asm_, sub, t128);
+            else if (G == 2) bk_attention<2>(P, ph, asm_, sub, t128);
+            else bk_attention<1>(P, ph, asm_, sub, t128);
+        } else {   // BK_FINAL: CTA 0 picks the winner among the CTAs' candidates
+            if (blockIdx.x == 0 && warp == 0) {
+                float bv = -INFINITY; int bi = 0x7fffffff;
+                for (int i = lane; i < (int)gridDim.x; i += 32) {
+                    const float v = __ldcg(P.cand_val + i); const int ix = __ldcg(P.cand_idx + i);
+                    if (v > bv || (v == bv && ix < bi)) { bv = v; bi = ix; }
+                }
+                for (int o = 16; o; o >>= 1) {
+                    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+                    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                    if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+                }
+                if (lane == 0) {
+                    const long long nxt = bi == 0x7fffffff ? 0 : bi;
+                    if (P.next_tok) *P.next_tok = nxt;
+                    if (P.advance) { *P.tok = nxt; *P.pos = *P.pos + 1; }
+                }
+            }
+        }
+        if (!alive || p + 1 >= P.nphases) break;
+        const bool ex = ph.kind == BK_MATVEC && ph.exchange && P.world > 1;
+        alive = bk_grid_sync(P, barriers_done, limit_ns, ex);
+        if (alive && ex) {
+            // every CTA of this rank has stored its rows into every rank's slot buffer: tell the ranks, then wait for theirs
+            seq++;
+            if (blockIdx.x == 0 && tid < P.world) bk_st_release_sys(P.peer_flags[tid] + P.rank, seq);
+            __shared__ int s_ok2;
+            if (tid == 0) s_ok2 = 1;
+            __syncthreads();
+            if (tid < P.world && !bk_wait_ge<true>(P.flags + tid, seq, P, limit_ns, 5)) s_ok2 = 0;
+            __syncthreads();
+            alive = s_ok2 != 0;
+        }
+    }
+    // The launch's exchanges are accounted for (also after an abort, so that the ranks' counters stay in step).
+    if (P.world > 1 && blockIdx.x == 0 && tid == 0) *P.seq = seq_start + (unsigned)P.nexchange;
+    // Copies still in flight into this CTA's shared memory must land before the CTA may exit.
+    for (; consumed < fetched; consumed++) {
+        const uint32_t s = consumed % BK_STAGES, parity = (consumed / BK_STAGES) & 1u;
+        mbar_wait_ns(smem_u32(bars + s), parity, limit_ns);
+    }
+}
+
+// ------------------------------------------------------------------ host
+
+struct jl_layers {
+    jl_ctx *ctx;
+    int n_layer, hidden, hq, hkv, ffn, vocab, max_len, rank, world, grid;
+    uint8_t *buf;          // phases, tensor maps and every scratch vector of the step: one allocation
+    uint8_t *slot;         // partial-sum planes of o and down for every rank + the exchange flags (peers write here)
+    size_t slot_bytes;
+    bk_phase *phases_dev;
+    std::vector<bk_phase> phases;
+    float *logits;
+    bk_params P;
+    bool attached;
+};
+
+static size_t bk_al(size_t n) { return (n + 255) & ~(size_t)255; }
+static size_t bk_slot_bytes(int world, int hidden) { return 2 * bk_al((size_t)world * hidden * 4) + 256; }
+
+// PrepLayer for every block plus the head (engine/nn/device.go:1099-1102): checks that each weight has a
+// kernel here, builds the phase list and sizes all scratch. Declines (JL_DECLINED) instead of running a
+// shape the block kernel does not serve; the caller then keeps its per-matvec path.
+JL_EXPORT int jl_layers_prep(jl_ctx *ctx, const jl_layers_desc *d, jl_layers **out) {
+    if (!ctx || !d || !out || !d->blocks) return JL_EINVAL;
+    *out = nullptr;
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    JL_CUDA(ctx, cudaSetDevice(ctx->device));
+    const int L = d->n_layer, H = d->hidden, hq = d->n_head, hkv = d->n_kv, F = d->ffn, V = d->vocab;
+    const int world = d->world < 1 ? 1 : d->world, rank = d->rank;
+    if (L < 1 || H < 256 || H % 256 || d->head_dim != BK_ATT_D || hq < 1 || hkv < 1 || hq % hkv || F < 256 || F % 256 ||
+        (hq * BK_ATT_D) % 256 || d->max_len < 1 || world > BK_MAX_WORLD || rank < 0 || rank >= world)
+        return jl_set_err(ctx, JL_DECLINED, "block kernel: shape not served (hidden %d, heads %d/%d x %d, ffn %d, world %d)", H, hq,
+                          hkv, d->head_dim, F, world);
+    const int G = hq / hkv;
+    if (G != 1 && G != 2 && G != 4)
+        return jl_set_err(ctx, JL_DECLINED, "block kernel: %d query heads per kv head (1, 2 or 4 are served)", G);
+    if (H / 256 > BK_MAX_NSB || F / 256 > BK_MAX_NSB || hq * BK_ATT_D / 256 > BK_MAX_NSB)
+        return jl_set_err(ctx, JL_DECLINED, "block kernel: a row longer than %d elements", BK_MAX_NSB * 256);
+    if (!d->cos_t || !d->sin_t) return JL_EINVAL;
+    auto okw = [&](const jl_weight *w, int rows, int k) {
+        return w && w->type == JL_TYPE_Q4_K && w->n_expert == 1 && w->nrows == rows && w->k == k && w->has_map_sb16;
+    };
+    for (int l = 0; l < L; l++) {
+        const jl_layers_block &b = d->blocks[l];
+        if (!okw(b.qkv, (hq + 2 * hkv) * BK_ATT_D, H) || !okw(b.o, H, hq * BK_ATT_D) || !okw(b.gate_up, 2 * F, H) ||
+            !okw(b.down, H, F) || !b.k_cache || !b.v_cache)
+            return jl_set_err(ctx, JL_DECLINED, "block %d: every projection must be a resident Q4_K matrix of the block's shape", l);
+    }
+    if (d->head && !okw(d->head, V, H)) return jl_set_err(ctx, JL_DECLINED, "head: not a resident Q4_K matrix %d x %d", V, H);
+
+    int occ = 0;
+    JL_CUDA(ctx, cudaFuncSetAttribute(jl_block_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BK_SMEM_BYTES));
+    JL_CUDA(ctx, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, jl_block_kernel, BK_THREADS, BK_SMEM_BYTES));
+    if (occ < 1) return jl_set_err(ctx, JL_DECLINED, "block kernel does not fit an SM");
+
+    jl_layers *S = new jl_layers();
+    S->ctx = ctx; S->n_layer = L; S->hidden = H; S->hq = hq; S->hkv = hkv; S->ffn = F; S->vocab = V; S->max_len = d->max_len;
+    S->rank = rank; S->world = world; S->grid = ctx->sm_count; S->attached = world == 1; S->buf = nullptr; S->slot = nullptr;
+    const int nmaps = 4 * L + (d->head ? 1 : 0);
+    const int nph = 5 * L + (d->head ? 2 : 0);
+    const int nchunk_max = (d->max_len + BK_ATT_CHUNK - 1) / BK_ATT_CHUNK;
+    const size_t stride = (size_t)(((2 * G + 3) & ~3) + G * BK_ATT_D);
+    size_t off = 0;
+    auto take = [&](size_t n) { size_t o = off; off += bk_al(n); return o; };
+    const size_t o_ph = take((size_t)nph * sizeof(bk_phase)), o_maps = take((size_t)nmaps * sizeof(CUtensorMap));
+    const size_t o_xa = take((size_t)H * 4), o_xb = take((size_t)H * 4), o_qkv = take((size_t)(hq + 2 * hkv) * BK_ATT_D * 4);
+    const size_t o_att = take((size_t)hq * BK_ATT_D * 4), o_a = take((size_t)F * 4), o_logits = take((size_t)(V > 0 ? V : 1) * 4);
+    const size_t o_part = take((size_t)hkv * nchunk_max * stride * 4), o_tick = take((size_t)hkv * 4);
+    const size_t o_cv = take((size_t)S->grid * 4), o_ci = take((size_t)S->grid * 4), o_bar = take(16), o_seq = take(16);
+    S->slot_bytes = bk_slot_bytes(world, H);
+    cudaError_t e = cudaMalloc(&S->buf, off);
+    if (e == cudaSuccess) e = cudaMalloc(&S->slot, S->slot_bytes);
+    if (e == cudaSuccess) e = cudaMemset(S->buf, 0, off);
+    if (e == cudaSuccess) e = cudaMemset(S->slot, 0, S->slot_bytes);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        if (S->buf) cudaFree(S->buf);
+        if (S->slot) cudaFree(S->slot);
+        delete S;
+        return jl_set_err(ctx, JL_ENOMEM, "block kernel scratch (%zu bytes): %s", off, cudaGetErrorString(e));
+    }
+    uint8_t *B = S->buf;
+    float *xa = (float *)(B + o_xa), *xb = (float *)(B + o_xb), *qkv = (float *)(B + o_qkv), *att = (float *)(B + o_att);
+    float *abuf = (float *)(B + o_a);
+    float *planesO = (float *)S->slot, *planesD = (float *)(S->slot + bk_al((size_t)world * H * 4));
+    unsigned *flags = (unsigned *)(S->slot + 2 * bk_al((size_t)world * H * 4));
+    S->logits = (float *)(B + o_logits);
+    S->phases_dev = (bk_phase *)(B + o_ph);
+
+    std::vector<CUtensorMap> maps(nmaps);
+    bool maps_ok = true;
+    auto map16 = [&](const jl_weight *w) { return w->map_sb16; };
+    auto map8 = [&](const jl_weight *w, CUtensorMap *m) {
+        const size_t rb = jl_row_bytes(w->type, w->k);
+        return jl_make_tmap_2d(m, w->data, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, rb, (uint64_t)w->nrows, rb, 144, 8,
+                               CU_TENSOR_MAP_SWIZZLE_NONE);
+    };
+    S->phases.assign(nph, bk_phase());
+    int pi = 0;
+    for (int l = 0; l < L; l++) {
+        const jl_layers_block &b = d->blocks[l];
+        maps[4 * l + 0] = map16(b.qkv); maps[4 * l + 1] = map16(b.o);
+        maps_ok = maps_ok && map8(b.gate_up, &maps[4 * l + 2]);
+        maps[4 * l + 3] = map16(b.down);
+        bk_phase q = {};
+        q.kind = BK_MATVEC; q.map = 4 * l; q.nrows = (hq + 2 * hkv) * BK_ATT_D; q.nsb = H / 256; q.prologue = BK_PRO_NORM;
+        q.epilogue = BK_EPI_STORE; q.from_emb = l == 0; q.xsrc = xb; q.xdst = xa; q.planes = planesD; q.nplanes = l == 0 ? 0 : world;
+        q.norm_w = b.attn_norm; q.out = qkv;
+        S->phases[pi++] = q;
+        bk_phase a = {};
+        a.kind = BK_ATTN; a.qkv = qkv; a.att = att; a.k_cache = b.k_cache; a.v_cache = b.v_cache;
+        S->phases[pi++] = a;
+        bk_phase o = {};
+        o.kind = BK_MATVEC; o.map = 4 * l + 1; o.nrows = H; o.nsb = hq * BK_ATT_D / 256; o.prologue = BK_PRO_PLAIN; o.epilogue = BK_EPI_STORE;
+        o.vsrc = att; o.out = planesO + (size_t)rank * H; o.exchange = world > 1;
+        S->phases[pi++] = o;
+        bk_phase gu = {};
+        gu.kind = BK_MATVEC; gu.map = 4 * l + 2; gu.nrows = F; gu.nsb = H / 256; gu.prologue = BK_PRO_NORM; gu.epilogue = BK_EPI_GATE2;
+        gu.up_row0 = F; gu.xsrc = xa; gu.xdst = xb; gu.planes = planesO; gu.nplanes = world; gu.norm_w = b.ffn_norm; gu.out = abuf;
+        S->phases[pi++] = gu;
+        bk_phase dn = {};
+        dn.kind = BK_MATVEC; dn.map = 4 * l + 3; dn.nrows = H; dn.nsb = F / 256; dn.prologue = BK_PRO_PLAIN; dn.epilogue = BK_EPI_STORE;
+        dn.vsrc = abuf; dn.out = planesD + (size_t)rank * H; dn.exchange = world > 1;
+        S->phases[pi++] = dn;
+    }
+    if (d->head) {
+        maps[4 * L] = map16(d->head);
+        bk_phase h = {};
+        h.kind = BK_MATVEC; h.map = 4 * L; h.nrows = V; h.nsb = H / 256; h.prologue = BK_PRO_NORM; h.epilogue = BK_EPI_ARGMAX;
+        h.xsrc = xb; h.xdst = xa; h.planes = planesD; h.nplanes = world; h.norm_w = d->final_norm; h.out = S->logits;
+        S->phases[pi++] = h;
+        bk_phase f = {};
+        f.kind = BK_FINAL;
+        S->phases[pi++] = f;
+    }
+    e = cudaSuccess;
+    if (maps_ok) e = cudaMemcpy(B + o_maps, maps.data(), (size_t)nmaps * sizeof(CUtensorMap), cudaMemcpyHostToDevice);
+    if (maps_ok && e == cudaSuccess) e = cudaMemcpy(S->phases_dev, S->phases.data(), (size_t)nph * sizeof(bk_phase), cudaMemcpyHostToDevice);
+    if (!maps_ok || e != cudaSuccess) {
+        cudaGetLastError();
+        cudaFree(S->buf); cudaFree(S->slot);
+        delete S;
+        return maps_ok ? jl_set_err(ctx, JL_ECUDA, "block kernel set-up: %s", cudaGetErrorString(e))
+                       : jl_set_err(ctx, JL_DECLINED, "the driver refused a tensor map for a gate|up matrix");
+    }
+    bk_params &P = S->P;
+    memset(&P, 0, sizeof P);
+    P.phases = S->phases_dev; P.nphases = nph; P.maps = (const CUtensorMap *)(B + o_maps);
+    P.hidden = H; P.hq = hq; P.hkv = hkv; P.max_len = d->max_len; P.eps = d->eps; P.cos_t = d->cos_t; P.sin_t = d->sin_t;
+    P.emb = (const __nv_bfloat16 *)d->emb_bf16;
+    P.part = (float *)(B + o_part); P.tickets = (unsigned *)(B + o_tick); P.cand_val = (float *)(B + o_cv); P.cand_idx = (int *)(B + o_ci);
+    P.bar = (unsigned *)(B + o_bar); P.abort_word = (int *)(B + o_bar) + 1; P.status = ctx->dev_status;
+    P.rank = rank; P.world = world; P.flags = flags; P.seq = (unsigned *)(B + o_seq); P.nexchange = world > 1 ? 2 * L : 0;
+    *out = S;
+    return JL_OK;
+}
+
+JL_EXPORT void jl_layers_free(jl_ctx *ctx, jl_layers *S) {
+    if (!ctx || !S) return;
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    cudaSetDevice(ctx->device);
+    cudaDeviceSynchronize();
+    if (S->buf) cudaFree(S->buf);
+    if (S->slot) cudaFree(S->slot);
+    delete S;
+}
+
+// Where the other ranks store their partial sums and flags for this rank (device memory of this GPU).
+JL_EXPORT int jl_tp_slot(jl_ctx *ctx, jl_layers *S, void **slot_dev, size_t *bytes) {
+    if (!ctx || !S || !slot_dev || !bytes) return JL_EINVAL;
+    *slot_dev = S->slot; *bytes = S->slot_bytes;
+    return JL_OK;
+}
+// Handles for handing a slot to the other ranks' processes (CUDA IPC; 64 bytes each).
+JL_EXPORT int jl_tp_ipc_export(const void *dev_ptr, void *handle64) {
+    if (!dev_ptr || !handle64) return JL_EINVAL;
+    cudaIpcMemHandle_t h;
+    if (cudaIpcGetMemHandle(&h, const_cast<void *>(dev_ptr)) != cudaSuccess) { cudaGetLastError(); return JL_ECOMM; }
+    static_assert(sizeof h == 64, "IPC handle size");
+    memcpy(handle64, &h, 64);
+    return JL_OK;
+}
+JL_EXPORT int jl_tp_ipc_open(const void *handle64, void **dev_ptr) {
+    if (!handle64 || !dev_ptr) return JL_EINVAL;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, 64);
+    if (cudaIpcOpenMemHandle(dev_ptr, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) { cudaGetLastError(); return JL_ECOMM; }
+    return JL_OK;
+}
+JL_EXPORT int jl_tp_ipc_close(void *dev_ptr) {
+    if (!dev_ptr) return JL_EINVAL;
+    if (cudaIpcCloseMemHandle(dev_ptr) != cudaSuccess) { cudaGetLastError(); return JL_ECOMM; }
+    return JL_OK;
+}
+// peer_slots[r] = rank r's slot as THIS process can address it (own slot at [rank]). After every rank has attached,
+// the ranks meet once on the host (a barrier) before the first jl_layers_run.
+JL_EXPORT int jl_tp_attach(jl_ctx *ctx, jl_layers *S, void *const *peer_slots, int n) {
+    if (!ctx || !S || !peer_slots || n != S->world) return JL_EINVAL;
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    JL_CUDA(ctx, cudaSetDevice(ctx->device));
+    if (peer_slots[S->rank] != S->slot) return jl_set_err(ctx, JL_EINVAL, "peer_slots[rank] must be this rank's own slot");
+    const size_t plane = bk_al((size_t)S->world * S->hidden * 4);
+    for (int r = 0; r < S->world; r++) {
+        if (!peer_slots[r]) return JL_EINVAL;
+        S->P.peer_flags[r] = (unsigned *)((uint8_t *)peer_slots[r] + 2 * plane);
+    }
+    for (bk_phase &ph : S->phases) {
+        if (ph.kind != BK_MATVEC || !ph.exchange) continue;
+        const bool is_down = ph.prologue == BK_PRO_PLAIN && ph.nsb == S->ffn / 256 && ph.vsrc != nullptr &&
+                             ph.out == (float *)(S->slot + plane) + (size_t)S->rank * S->hidden;
+        for (int r = 0; r < S->world; r++)
+            ph.peer_out[r] = (float *)((uint8_t *)peer_slots[r] + (is_down ? plane : 0)) + (size_t)S->rank * S->hidden;
+    }
+    JL_CUDA(ctx, cudaMemcpy(S->phases_dev, S->phases.data(), S->phases.size() * sizeof(bk_phase), cudaMemcpyHostToDevice));
+    S->attached = true;
+    return JL_OK;
+}
+
+// Layers(0, n_layer, pos, 1, x, head) (engine/nn/device.go:1104-1118) with the residual row filled from the token
+// id on the device (EmbedDevice, :1178-1191): one launch runs every block and, when a head was given, the output
+// norm, the vocabulary projection and the greedy argmax. *tok_dev, *pos_dev are read on the device, so a captured
+// graph can be replayed; with `advance` the kernel itself stores the next token into *tok_dev and increments
+// *pos_dev. logits_out_dev / next_tok_dev may be NULL. Asynchronous on `stream`; poll jl_status_poll afterwards.
+JL_EXPORT int jl_layers_run(jl_ctx *ctx, jl_layers *S, long long *tok_dev, long long *pos_dev, float *logits_out_dev,
+                            long long *next_tok_dev, int advance, void *stream) {
+    if (!ctx || !S || !tok_dev || !pos_dev) return JL_EINVAL;
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    if (ctx->unhealthy) return jl_set_err(ctx, JL_ECUDA, "context is unhealthy after an earlier CUDA error");
+    if (!S->attached) return jl_set_err(ctx, JL_ECOMM, "tensor-parallel blocks: jl_tp_attach has not been called");
+    if (!S->P.emb) return jl_set_err(ctx, JL_EINVAL, "jl_layers_run needs the embedding table given at jl_layers_prep");
+    JL_CUDA(ctx, cudaSetDevice(ctx->device));
+    cudaStream_t s = (cudaStream_t)stream;
+    bk_params P = S->P;
+    P.tok = tok_dev; P.pos = pos_dev; P.advance = advance; P.next_tok = next_tok_dev;
+    JL_CUDA(ctx, cudaMemsetAsync(P.bar, 0, 8, s));           // barrier counter and abort word
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeCooperative;
+    at[0].val.cooperative = 1;                               // all CTAs co-resident: the grid barriers rely on it
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(S->grid); cfg.blockDim = dim3(BK_THREADS); cfg.dynamicSmemBytes = BK_SMEM_BYTES; cfg.stream = s;
+    cfg.attrs = at; cfg.numAttrs = 1;
+    JL_CUDA(ctx, cudaLaunchKernelEx(&cfg, jl_block_kernel, P));
+    ctx->st.launches++;
+    if (logits_out_dev && S->vocab > 0)
+        JL_CUDA(ctx, cudaMemcpyAsync(logits_out_dev, S->logits, (size_t)S->vocab * 4, cudaMemcpyDeviceToDevice, s));
+    ctx->st.served++;
+    return JL_OK;
+}

@@ -438,16 +438,20 @@ static int tc5_ksplit(int nrows, int ntok_eff, int k, int sms) {
     return ks < 2 ? 1 : ks;
 }
 
+// Answers for f32 activations (what jl_select is asked about: the decode-side entry points take f32), which
+// occupy two MMA columns per token (hi + lo); 16-bit activations occupy one.
 int jl_gemm_tc5_choice(jl_ctx *ctx, uint32_t type, int nrows, int k, int ntok, jl_choice *out) {
     if (!jl_gemm_tc5_supported(type, nrows, k, ntok)) return JL_DECLINED;
     jl_choice c = {};
     const int sms = ctx ? ctx->sm_count : 148;
-    const int nt = tc5_pick_nt(ntok);
+    const int ntok_eff = 2 * ntok;
+    const int nt = tc5_pick_nt(ntok_eff);
     c.kernel = JL_K_TC5; c.warps = TC5_THREADS / 32; c.rows_per_cta = TC5_ROWS;
-    c.split_k = tc5_ksplit(nrows, ntok, k, sms);
+    c.split_k = tc5_ksplit(nrows, ntok_eff, k, sms);
     c.tile_m = TC5_M; c.tile_n = nt; c.tile_k = TC5_KB;
-    const int units = ((nrows + TC5_ROWS - 1) / TC5_ROWS) * ((ntok + nt - 1) / nt) * c.split_k;
+    const int units = ((nrows + TC5_ROWS - 1) / TC5_ROWS) * ((ntok_eff + nt - 1) / nt) * c.split_k;
     c.grid = units < sms ? units : sms;
+    c.launches = 2 + (c.split_k > 1 ? 1 : 0);   // activation conversion, GEMM, and the split-K sum when K is split
     *out = c;
     return JL_OK;
 }

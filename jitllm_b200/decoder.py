@@ -2,8 +2,10 @@
 
 Every matmul (q|k|v, o, gate|up, down, lm_head) goes through libjitllm_b200.so on Q4_K weights;
 the steps around them -- RMSNorm, RoPE, the KV cache, attention, SiLU*up, the residual adds and
-the greedy argmax -- are plain PyTorch ops, because they are neighbours of the path, not the
-path. Weights are random-init Q4_K blocks of the right shapes (no checkpoint can be fetched);
+the greedy argmax -- are neighbours of the path: the prefill runs them as PyTorch ops, a decode
+step runs the library's own short kernels between the matvecs (`decode_step`), and a decode step
+of ONE sequence runs everything as one persistent kernel (`decode_step_block`: the reference's
+LayerDevice seam). Weights are random-init Q4_K blocks of the right shapes (no checkpoint can be fetched);
 q|k|v and gate|up are stored as one row-concatenated matrix each, as the reference's
 `MatVecSegments` fuses them (docs/kernel-inventory.md:83).
 
@@ -221,6 +223,43 @@ class Decoder:
             logits = torch.cat(parts, dim=-1)
         nxt = torch.empty(B, device="cuda", dtype=torch.int64)
         ok(lib.jl_aux_argmax(nxt.data_ptr(), logits.data_ptr(), B, logits.shape[1], st))
+        return nxt
+
+    # -- whole step as one kernel (nn.LayerDevice) -----------------------------------
+    def prep_block_kernel(self):
+        """PrepLayer for every block + the head. Returns False when the library declines the shape (the per-matvec
+        decode_step keeps working). Under tensor parallelism the ranks exchange their slot handles here."""
+        c = self.cfg
+        blocks = [dict(qkv=l["qkv"], o=l["o"], gate_up=l["gu"], down=l["down"], attn_norm=self.norm_w, ffn_norm=self.norm_w,
+                       k_cache=self.k_cache[li, 0], v_cache=self.v_cache[li, 0]) for li, l in enumerate(self.layers)]
+        self.block = self.dev.PrepLayers(blocks, c.hidden, self.hq, self.hkv, c.head_dim, self.ffn_l, self.max_len, c.eps,
+                                         self.cos, self.sin, self.emb, head=self.head, final_norm=self.norm_w,
+                                         rank=self.rank, world=self.world)
+        if self.block is None:
+            return False
+        if self.world > 1:
+            parallel.tp_attach(self.block, self.group)
+        return True
+
+    def decode_step_block(self, tok_dev, pos_dev, advance=False):
+        """One decode step of ONE sequence as ONE kernel launch (plus, under tensor parallelism, the gather of the
+        vocabulary shards and the argmax). tok_dev, pos_dev: 1-element int64 device tensors. Returns the next token
+        [1]; with advance (single GPU) the kernel also stores it into tok_dev and increments pos_dev."""
+        torch = self.torch
+        st = torch.cuda.current_stream().cuda_stream
+        nxt = torch.empty(1, device="cuda", dtype=torch.int64)
+        logits = self.last_logits = torch.empty(1, self.vocab_l, device="cuda", dtype=torch.float32)
+        if self.world == 1:
+            self.block.Run(tok_dev, pos_dev, logits, nxt, advance, st)
+            return nxt
+        import torch.distributed as dist
+        self.block.Run(tok_dev, pos_dev, logits, None, False, st)
+        parts = [torch.empty_like(logits) for _ in range(self.world)]
+        dist.all_gather(parts, logits, group=self.group)
+        full = torch.cat(parts, dim=-1)
+        rc = self.dev.lib.jl_aux_argmax(nxt.data_ptr(), full.data_ptr(), 1, full.shape[1], st)
+        if rc != 0:
+            raise RuntimeError(f"jl_aux_argmax failed with status {rc}")
         return nxt
 
     def decode_step_torch(self, tokens, pos_dev):

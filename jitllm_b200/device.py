@@ -14,7 +14,7 @@ import ctypes as C
 import numpy as np
 
 from . import _lib
-from ._lib import Choice, MoeDesc, Opts, Stats
+from ._lib import Choice, LayersBlock, LayersDesc, MoeDesc, Opts, Stats
 
 
 class DeviceError(RuntimeError):
@@ -81,6 +81,56 @@ class Weight:
         self.dev._check(self.dev.lib.jl_unpack_resident(self.dev.ctx, self.handle, _ptr(q), _ptr(d), _ptr(dm),
                                                         _ptr(sc), _ptr(m)))
         return q, d, dm, sc, m
+
+
+class Layers:
+    """Blocks prepared for whole-step submissions: the reference's nn.LayerDevice (PrepLayer / Layers / Head,
+    engine/nn/device.go:1096-1176) over jl_layers_*. One decode step of one sequence is one kernel."""
+
+    def __init__(self, dev: "Device", handle: int, rank: int, world: int, keep):
+        self.dev, self.handle, self.rank, self.world, self._keep, self._peers = dev, handle, rank, world, keep, []
+
+    def Run(self, tok, pos, logits=None, next_tok=None, advance: bool = False, stream: int = 0) -> None:
+        """Layers(0, n_layer, pos, 1, ...) with the head: tok, pos are 1-element int64 DEVICE tensors."""
+        self.dev._check(self.dev.lib.jl_layers_run(self.dev.ctx, self.handle, _ptr(tok), _ptr(pos), _ptr(logits),
+                                                   _ptr(next_tok), int(advance), stream))
+
+    def Slot(self):
+        """(device pointer, bytes) of this rank's tensor-parallel slot buffer."""
+        p, n = C.c_void_p(), C.c_size_t()
+        self.dev._check(self.dev.lib.jl_tp_slot(self.dev.ctx, self.handle, C.byref(p), C.byref(n)))
+        return p.value, n.value
+
+    def ExportHandle(self) -> bytes:
+        buf = C.create_string_buffer(64)
+        rc = self.dev.lib.jl_tp_ipc_export(self.Slot()[0], buf)
+        if rc != _lib.OK:
+            raise DeviceError(rc, "jl_tp_ipc_export")
+        return buf.raw
+
+    def Attach(self, handles) -> None:
+        """handles[r]: rank r's 64-byte IPC handle (own entry ignored), or an int device pointer."""
+        ptrs = (C.c_void_p * self.world)()
+        for r, h in enumerate(handles):
+            if r == self.rank:
+                ptrs[r] = self.Slot()[0]
+            elif isinstance(h, int):
+                ptrs[r] = h
+            else:
+                p = C.c_void_p()
+                rc = self.dev.lib.jl_tp_ipc_open(C.create_string_buffer(bytes(h), 64), C.byref(p))
+                if rc != _lib.OK:
+                    raise DeviceError(rc, "jl_tp_ipc_open")
+                self._peers.append(p.value)
+                ptrs[r] = p.value
+        self.dev._check(self.dev.lib.jl_tp_attach(self.dev.ctx, self.handle, ptrs, self.world))
+
+    def free(self) -> None:
+        if self.handle and self.dev.ctx:
+            self.dev.lib.jl_layers_free(self.dev.ctx, self.handle)
+            for p in self._peers:
+                self.dev.lib.jl_tp_ipc_close(p)
+        self.handle, self._peers = 0, []
 
 
 class Device:
@@ -178,6 +228,28 @@ class Device:
         self._check(self.lib.jl_weight_upload_bank(self.ctx, t, _ptr(w), _nbytes(w), n_expert, nrows, k,
                                                    C.byref(h)))
         return Weight(self, h.value, t, nrows, k, n_expert)
+
+    def PrepLayers(self, blocks, hidden: int, n_head: int, n_kv: int, head_dim: int, ffn: int, max_len: int, eps: float,
+                   cos, sin, emb, head: Weight | None = None, final_norm=None, rank: int = 0, world: int = 1):
+        """nn.LayerDevice.PrepLayer for every block plus the head. blocks: dicts with qkv, o, gate_up, down (Weight),
+        attn_norm, ffn_norm (device f32 or None), k_cache, v_cache (device bf16 [n_kv][max_len][head_dim]).
+        n_head / n_kv / ffn and the head's rows are THIS rank's share. Returns None when the shape is declined."""
+        arr = (LayersBlock * len(blocks))()
+        for i, b in enumerate(blocks):
+            arr[i] = LayersBlock(qkv=b["qkv"].handle, o=b["o"].handle, gate_up=b["gate_up"].handle, down=b["down"].handle,
+                                 attn_norm=_ptr(b.get("attn_norm")), ffn_norm=_ptr(b.get("ffn_norm")),
+                                 k_cache=_ptr(b["k_cache"]), v_cache=_ptr(b["v_cache"]))
+        d = LayersDesc(struct_size=C.sizeof(LayersDesc), n_layer=len(blocks), hidden=hidden, n_head=n_head, n_kv=n_kv,
+                       head_dim=head_dim, ffn=ffn, vocab=head.nrows if head else 0, max_len=max_len, eps=eps, blocks=arr,
+                       head=head.handle if head else None, final_norm=_ptr(final_norm), emb_bf16=_ptr(emb),
+                       cos_t=_ptr(cos), sin_t=_ptr(sin), rank=rank, world=world)
+        h = C.c_void_p()
+        rc = self.lib.jl_layers_prep(self.ctx, C.byref(d), C.byref(h))
+        self.last_status = rc
+        if rc == _lib.DECLINED:
+            return None
+        self._check(rc)
+        return Layers(self, h.value, rank, world, keep=(arr, blocks, cos, sin, emb, final_norm))
 
     def MatVecDev(self, out, weight: Weight, x, ntok: int = 1, stream: int = 0) -> None:
         """Device tensors: x [ntok][k] f32 -> out [ntok][nrows] f32, on `stream`."""

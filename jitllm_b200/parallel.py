@@ -185,3 +185,17 @@ class ExpertParallelMoE:
         y_pairs = torch.empty((ntok * self.top_k, self.hidden), dtype=torch.float32, device=h.device)
         y_pairs[order] = y_back                                            # back to (token, slot) order
         return combine_ascending(out, y_pairs.view(ntok, self.top_k, self.hidden), sel, wt)
+
+
+# ------------------------------------------------------ tensor-parallel slot exchange
+
+def tp_attach(block, group=None):
+    """Every rank exports its slot buffer as a CUDA IPC handle, the handles travel over the process group (any
+    backend: they are 64 host bytes), every rank opens its peers' slots and attaches them, then the ranks meet once
+    so that no kernel stores into a slot that is not mapped yet. `block` is a device.Layers."""
+    import torch.distributed as dist
+    world = dist.get_world_size(group)
+    handles = [None] * world
+    dist.all_gather_object(handles, block.ExportHandle(), group=group)
+    block.Attach(handles)
+    dist.barrier(group=group)

@@ -69,3 +69,83 @@ def test_decoder_matches_float_restatement(dev, orc, T):
         # the PyTorch-glue form of the same step agrees with the fused-neighbour form
         dec.decode_step_torch(tokens[T:T + 1].expand(3).contiguous(), pos)
         assert float((dec.last_logits.double() - got_dec).abs().max() / scale) < 1e-2
+
+
+def _ref_decode_step(torch, orc, dec, cfg, tokens, pos, kc0, vc0):
+    """float64 restatement of ONE decode step at position `pos` over caches kc0 / vc0 ([layer][B][hkv][len][d],
+    positions < pos filled). It keeps the harness's storage formats -- q, k, v rounded to bf16 where the step
+    stores them as bf16 -- so that what is compared is the arithmetic, not a storage choice."""
+    from jitllm_b200._lib import Q4_K
+    F = torch.nn.functional
+    it = iter(dec.host)
+    B, d, g = tokens.shape[0], cfg.head_dim, cfg.n_head // cfg.n_kv
+
+    def W(nrows, k):
+        return torch.from_numpy(orc.dequant32(Q4_K, next(it), nrows * k).reshape(nrows, k)).cuda().double()
+
+    def rms(x):
+        return x * torch.rsqrt((x * x).mean(-1, keepdim=True) + cfg.eps)
+
+    def rope(t):
+        cos, sin = dec.cos[pos].double(), dec.sin[pos].double()
+        a, b = t[..., 0::2], t[..., 1::2]
+        return torch.stack((a * cos - b * sin, a * sin + b * cos), dim=-1).flatten(-2)
+
+    def bf(t):
+        return t.float().to(torch.bfloat16).double()
+
+    x = dec.emb[tokens].double()
+    for li in range(cfg.n_layer):
+        wqkv, wo = W((cfg.n_head + 2 * cfg.n_kv) * d, cfg.hidden), W(cfg.hidden, cfg.n_head * d)
+        qkv = (rms(x).float().double() @ wqkv.T).float().double()          # the kernel reads f32 rows, writes f32
+        del wqkv
+        q = bf(rope(qkv[:, :cfg.n_head * d].view(B, cfg.n_head, d)))
+        k = bf(rope(qkv[:, cfg.n_head * d:(cfg.n_head + cfg.n_kv) * d].view(B, cfg.n_kv, d)))
+        v = bf(qkv[:, (cfg.n_head + cfg.n_kv) * d:].view(B, cfg.n_kv, d))
+        kk = torch.cat([kc0[li][:, :, :pos].double(), k[:, :, None, :]], dim=2)   # [B][hkv][pos+1][d]
+        vv = torch.cat([vc0[li][:, :, :pos].double(), v[:, :, None, :]], dim=2)
+        sc = torch.einsum("bkgd,bksd->bkgs", q.view(B, cfg.n_kv, g, d), kk) / d ** 0.5
+        att = torch.einsum("bkgs,bksd->bkgd", sc.softmax(-1), vv).reshape(B, -1)
+        x = x + att.float().double() @ wo.T
+        del wo
+        wgu = W(2 * cfg.ffn, cfg.hidden)
+        gu = rms(x).float().double() @ wgu.T
+        del wgu
+        wdn = W(cfg.hidden, cfg.ffn)
+        x = x + (F.silu(gu[:, :cfg.ffn]) * gu[:, cfg.ffn:]).float().double() @ wdn.T
+        del wdn
+    return rms(x).float().double() @ W(cfg.vocab, cfg.hidden).T
+
+
+@pytest.mark.parametrize("B,bar", [(1, 2e-3), (64, 5e-3)])
+def test_one_full_width_llama8b_layer_at_2049_positions(orc, B, bar):
+    """One layer at the real width (hidden 4096, 32 query / 8 kv heads of 128, ffn 14336) with 2048 cached
+    positions, batch 1 (decode kernels, producers writing the matvec operands) and batch 64 (tcgen05 GEMMs):
+    the logits of a 4096-row head against the float64 restatement. Batch 1: 2e-3, the bar of every single
+    kernel. Batch 64: five GEMMs in a chain each round the weights to f16 once (each within 2e-3 by itself),
+    so the chain is given 5e-3."""
+    import torch
+    from conftest import parity_err
+    from jitllm_b200 import Device
+    from jitllm_b200.decoder import Config, Decoder
+    cfg = Config(n_layer=1, vocab=4096)
+    T = 2048
+    with Device(0) as dev:
+        dec = Decoder(dev, cfg, max_batch=B, max_len=T + 16, max_prefill=64, keep_host=True, seed=23)
+        g = torch.Generator(device="cuda").manual_seed(B)
+        dec.k_cache[:, :, :, :T] = torch.randn(1, B, cfg.n_kv, T, cfg.head_dim, device="cuda", generator=g).to(torch.bfloat16)
+        dec.v_cache[:, :, :, :T] = torch.randn(1, B, cfg.n_kv, T, cfg.head_dim, device="cuda", generator=g).to(torch.bfloat16)
+        kc0, vc0 = dec.k_cache.clone(), dec.v_cache.clone()
+        tokens = torch.randint(0, cfg.vocab, (B,), device="cuda", generator=g)
+        pos = torch.tensor([T], device="cuda")
+        with torch.no_grad():
+            nxt = dec.decode_step(tokens, pos)
+            torch.cuda.synchronize()
+            assert dev.StatusPoll()
+            got = dec.last_logits.double()
+            ref = _ref_decode_step(torch, orc, dec, cfg, tokens, T, kc0, vc0)
+        assert torch.isfinite(got).all()
+        assert torch.equal(nxt, dec.last_logits.argmax(-1))
+        err = parity_err(got.cpu().numpy(), ref.cpu().numpy())
+        assert err <= bar, err
+        del dec
