@@ -37,12 +37,12 @@ from jitllm_b200 import synth  # noqa: E402
 from jitllm_b200._lib import FLAG_DECODE_CONCURRENT, Q4_K, Q8_0, row_bytes  # noqa: E402
 
 RING = 64
-PASSES = 16  # ring passes per step
+PASSES = 256  # ring passes per step: 16384 matvecs, ~26 ms, so that 20 timed steps run for about half a second
 BRANCHES = 8  # parallel branches of the CUDA graph: the ring's matvecs are independent of one another
 FALLBACK_HBM_GBS = 6650.0
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu
-# capture summarised under profiles/ (None until a capture exists for that workload).
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from one ncu capture of
+# this workload's kernel (None until a capture exists for that workload).
 NCU_TRAFFIC_BYTES = {"q4k_gemv_4096": 9471232}
 
 WORKLOADS = {
@@ -129,24 +129,36 @@ def make_ring(t, nrows, k, ntok, seed, ring):
     return ws, x
 
 
-def cpu_time_ring(ws, x, t, nrows, k, ntok, seconds, window):
-    """The CPU twin over the ring, all host threads; returns (GB/s, cores, sample description)."""
+def gemv_config(name, world):
+    """The `config` object of the headline workload: the same for this library's arm and the reference arm."""
+    t, nrows, k, ntok = WORKLOADS[name]
+    return {"workload": name, "type": "Q4_K", "nrows": nrows, "k": k, "ntok": ntok, "ring": RING,
+            "matvecs_per_step": RING * PASSES,
+            "l2": f"inputs larger than L2: ring of {RING} distinct weight copies = {RING * nrows * row_bytes(t, k) / 1e6:.0f} MB",
+            "algorithmic_bytes_per_matvec": algorithmic_bytes(t, nrows, k, ntok), "parallelism": f"independent rings x{world}"}
+
+
+def cpu_ring_rate(ws, x, t, nrows, k, ntok, window, warmup, steps=None, seconds=None):
+    """The CPU twin over the ring, all host threads. One CPU step = one pass over the ring of distinct weight
+    copies (beyond the host's caches); the rate is bytes over the MEAN step time -- the same statistic in the
+    `cpu_baseline` leg and in the reference arm. Runs `steps` steps, or as many as fit `seconds`.
+    Returns (GB/s, cores, seconds per step, steps)."""
     import oracle
     oracle.build()
     cores = os.cpu_count() or 1
     per = algorithmic_bytes(t, nrows, k, ntok)
-    oracle.matmul_int8(t, ws[0], x, nrows, k, ntok, window=window, nthreads=cores)  # soak
-    times = []
-    t_end = time.perf_counter() + seconds
-    i = 0
-    while time.perf_counter() < t_end or len(times) < 15:
-        w = ws[i % len(ws)]
-        t0 = time.perf_counter()
-        oracle.matmul_int8(t, w, x, nrows, k, ntok, window=window, nthreads=cores)
-        times.append(time.perf_counter() - t0)
-        i += 1
-    med = float(np.median(times))
-    return per / med / 1e9, cores, f"{len(times)} matvecs of {nrows}x{k} over a {len(ws)}-copy ring, median"
+
+    def step():
+        for w in ws:
+            oracle.matmul_int8(t, w, x, nrows, k, ntok, window=window, nthreads=cores)
+    for _ in range(warmup):
+        step()
+    n, t0 = 0, time.perf_counter()
+    while (steps is not None and n < steps) or (steps is None and (time.perf_counter() - t0 < seconds or n < 3)):
+        step()
+        n += 1
+    dt = (time.perf_counter() - t0) / n
+    return per * len(ws) / dt / 1e9, cores, dt, n
 
 
 def run_reference(args, name):
@@ -155,32 +167,16 @@ def run_reference(args, name):
     if rank != 0:
         return
     t, nrows, k, ntok = WORKLOADS[name]
-    ring = RING  # a step is one pass over the same ring of distinct copies (604 MB: beyond the host's caches)
-    ws, x = make_ring(t, nrows, k, ntok, 0xB200, ring)
-    import oracle
-    oracle.build()
-    cores = os.cpu_count() or 1
-    window = 256 if t == Q4_K else 32
-    per = algorithmic_bytes(t, nrows, k, ntok)
-
-    def step():
-        for w in ws:
-            oracle.matmul_int8(t, w, x, nrows, k, ntok, window=window, nthreads=cores)
-    for _ in range(args.warmup):
-        step()
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        step()
-    dt = time.perf_counter() - t0
-    val = per * ring * args.steps / dt / 1e9
-    sample = f"step = {ring} matvecs of {nrows}x{k} (distinct weight copies), {cores} threads"
+    ws, x = make_ring(t, nrows, k, ntok, 0xB200, RING)   # a CPU step is one pass over the same ring of distinct copies
+    val, cores, dt, n = cpu_ring_rate(ws, x, t, nrows, k, ntok, 256 if t == Q4_K else 32, args.warmup, steps=args.steps)
+    sample = (f"CPU step = one pass over the ring ({RING} matvecs of {nrows}x{k}, distinct weight copies), {cores} threads, "
+              f"mean of {n} steps; the reference is Go and cannot be built here: CPU restatement of its int8-activation "
+              "JIT arithmetic (oracle/jl_oracle.c)")
     print(json.dumps({
         "impl": "reference", "metric": "q4k_gemv_gbs", "value": val, "unit": "GB/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8 x u4 -> f32",
-        "data": "synthetic", "config": {"workload": name, "ring": ring,
-                                        "note": "reference is Go and cannot be built here; CPU restatement "
-                                                "of its int8-activation JIT arithmetic (oracle/jl_oracle.c)"},
+        "data": "synthetic", "config": gemv_config(name, args.gpus),
         "cpu_baseline": {"value": val, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -197,7 +193,8 @@ def run_ours(args, name):
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        import bench_workloads as bw
+        bw._pg(local)
     t, nrows, k, ntok = WORKLOADS[name]
     per = algorithmic_bytes(t, nrows, k, ntok)
     ws, x = make_ring(t, nrows, k, ntok, 0xB200 + rank, RING)
@@ -286,6 +283,7 @@ def run_ours(args, name):
     ev1.record(stream)
     torch.cuda.synchronize()
     chain_us = ev0.elapsed_time(ev1) * 1e3 / (launches_per_step * max(2, args.steps // 5))
+    del graph, chain
 
     # correctness guard: the timed outputs are real (first ring entry against a second run).
     chk = torch.empty_like(outs[0])
@@ -319,16 +317,15 @@ def run_ours(args, name):
         "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "u4 x 2xint8 digits -> s32 (mma.sync u8.s8), f32 fold",
         "data": "synthetic",
-        "config": {"workload": name, "type": "Q4_K", "nrows": nrows, "k": k, "ntok": ntok, "ring": RING,
-                   "matvecs_per_step": RING * PASSES, "launch": f"CUDA graph replay, launches back to back in {BRANCHES} parallel branches "
-                             "(the ring's matvecs are independent; programmatic dependent launch inside a branch)",
-                   "single_chain_us_per_matvec": chain_us, "single_chain_gbs": per / chain_us / 1e3,
-                   "l2": f"inputs larger than L2: ring of {RING} distinct weight copies = "
-                         f"{RING * nrows * row_bytes(t, k) / 1e6:.0f} MB",
-                   "algorithmic_bytes_per_matvec": per, "parallelism": f"independent rings x{world}"},
+        "config": gemv_config(name, world),
+        "launch": {"how": f"CUDA graph replay, launches back to back in {BRANCHES} parallel branches (the ring's matvecs are "
+                          "independent; programmatic dependent launch inside a branch)",
+                   "timed_region_ms": ms,
+                   "single_chain_us_per_matvec": chain_us, "single_chain_gbs": per / chain_us / 1e3},
         "roofline": {"bound": "hbm", "achieved": per / (kernel_us * 1e-6) / 1e9, "peak": peak,
                      "unit": "GB/s", "frac": per / (kernel_us * 1e-6) / 1e9 / peak, "of": which,
                      "kernel": "gemv_q4k_tma_kernel", "us_per_launch": kernel_us,
+                     "us_per_launch_is": "timed region / launches, with 8 launches overlapped on the GPU (not one kernel's duration)",
                      "traffic": NCU_TRAFFIC_BYTES.get(name)},
         "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": ntok * k * 4 * RING * PASSES,
                 "d2h_bytes_per_step": ntok * nrows * 4 * RING * PASSES,
@@ -337,17 +334,63 @@ def run_ours(args, name):
         "clocks": clk.summary(),
     }
     if rank == 0 and world == 1:
-        gbs, cores, sample = cpu_time_ring(ws, x, t, nrows, k, ntok, seconds=10.0,
-                                           window=256 if t == Q4_K else 32)
-        line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample}
-    if rank == 0:
-        print(json.dumps(line), flush=True)
+        gbs, cores, dt, n = cpu_ring_rate(ws, x, t, nrows, k, ntok, 256 if t == Q4_K else 32, 2, seconds=10.0)
+        line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port",
+                                "sample": f"CPU step = one pass over the ring ({RING} matvecs of {nrows}x{k}), mean of {n} steps"}
     for h in handles:
         h.free()
     for d in branch_devs + [dev]:
         d.Close()
+    del outs, x_dev
+    torch.cuda.empty_cache()
+    if not args.no_also:
+        line.update(also_block(args, world, rank, local))
+    if rank == 0:
+        print(json.dumps(line), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        dist.barrier()
+        sys.stdout.flush()
+        os._exit(0)      # a process group whose collectives were captured in a graph can stall in its destructor
+
+
+def _brief(line):
+    """What the `also` block keeps of a workload's line."""
+    if line is None:
+        return None
+    keep = ("metric", "value", "unit", "ms_per_step", "steps", "scaling", "config", "roofline", "e2e", "gpu_launches", "clocks")
+    return {k: line[k] for k in keep if k in line}
+
+
+def also_block(args, world, rank, local):
+    """The other quantities the metric names, timed in the same run: the prefill GEMM (TFLOP/s against the tensor
+    roofline), Q8_0 batch 32, the MXFP4 mixture layer and Llama-3-8B-shaped decode tok/s at batch 1 and 64, each with
+    its roofline. Under torchrun they are the SHARDED forms (column-sharded Q8_0, expert-parallel mixture layer,
+    tensor-parallel decode: strong scaling), preceded by a parity check of the sharded forms against the unsharded
+    ones on the live process group; the run fails when that check is above 2e-3."""
+    import bench_workloads as bw
+    import copy
+    out = {}
+    if world > 1:
+        par = bw.sharded_parity(local)
+        out["sharded_parity"] = par
+        if not (par["tp_err"] <= par["bar"] and par["ep_err"] <= par["bar"]):
+            if rank == 0:
+                print(json.dumps({"error": "sharded parity above the bar", **par}), flush=True)
+            sys.stdout.flush()
+            os._exit(3)
+    a = copy.copy(args)
+    a.steps, a.warmup = max(args.steps, 20), max(args.warmup, 3)
+    also = {}
+    if world == 1:
+        also["q4k_gemm_prefill"] = _brief(bw.run_gemm(a, emit=False))
+    also["q8_0_batch32"] = _brief(bw.run_q8_batch(a, emit=False))
+    also["mxfp4_moe_gptoss"] = _brief(bw.run_moe(a, emit=False))
+    a.prompt, a.batch = 2048, 1
+    lines = bw.run_decode(a, emit=False, batches=[1, 64], steps=256)
+    for b, l in zip((1, 64), lines or []):
+        also[f"llama8b_q4k_decode_b{b}"] = _brief(l)
+    out["also"] = also
+    return out
 
 
 def main():
@@ -360,6 +403,7 @@ def main():
                     choices=sorted(WORKLOADS) + ["q4k_gemm_prefill", "q8_0_batch32", "mxfp4_moe_gptoss", "llama8b_q4k_decode"])
     ap.add_argument("--batch", type=int, default=1, help="llama8b_q4k_decode: sequences decoded together")
     ap.add_argument("--prompt", type=int, default=2048, help="llama8b_q4k_decode: prompt length")
+    ap.add_argument("--no-also", action="store_true", help="headline workload only (skip the `also` block)")
     args = ap.parse_args()
     if args.workload not in WORKLOADS:
         import bench_workloads as bw
@@ -367,6 +411,9 @@ def main():
             bw.run_reference(args)
         else:
             {"q4k_gemm_prefill": bw.run_gemm, "q8_0_batch32": bw.run_q8_batch, "mxfp4_moe_gptoss": bw.run_moe, "llama8b_q4k_decode": bw.run_decode}[args.workload](args)
+            if int(os.environ.get("WORLD_SIZE", "1")) > 1:
+                sys.stdout.flush()
+                os._exit(0)
         return
     if args.impl == "reference":
         run_reference(args, args.workload)

@@ -24,6 +24,21 @@ def _env():
     return world, int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
 
 
+def _pg(local):
+    """The process group of a torchrun launch, created once per process (NCCL, one rank per GPU)."""
+    import torch
+    import torch.distributed as dist
+    if not dist.is_initialized():
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    return dist
+
+
+def _emit(line, emit):
+    if emit and line is not None:
+        print(json.dumps(line), flush=True)
+    return line
+
+
 def _peaks():
     import bench
     p = os.path.join(bench.ROOT, "MEASURED_PEAKS.json")
@@ -52,13 +67,13 @@ GEMM_SHAPES = [(14336, 4096), (4096, 14336)]
 GEMM_NTOK, GEMM_COPIES = 512, 6          # 6 distinct weight copies per shape: 198 MB > L2
 
 
-def run_gemm(args):
+def run_gemm(args, emit=True):
     import torch
     from jitllm_b200 import Device, synth
     from jitllm_b200._lib import Q4_K
     world, rank, local = _env()
     if rank != 0:
-        return          # single-GPU workload: replicas would only repeat it
+        return None     # single-GPU workload: replicas would only repeat it
     torch.cuda.set_device(local)
     dev = Device(local)
     rng = synth.rng_for(0xB201)
@@ -97,7 +112,7 @@ def run_gemm(args):
     e2e_tf = 2.0 * GEMM_NTOK * nrows * k * n_e2e / (time.perf_counter() - t0) / 1e12
     hbm, burst, sustained, which = _peaks()
     ngemm = len(GEMM_SHAPES) * GEMM_COPIES
-    print(json.dumps({
+    line = ({
         "metric": "q4k_gemm_tflops", "value": tf, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "Q4_K -> f16 weights x bf16->f16 activations, f32 accumulate (tcgen05 kind::f16), bf16 out",
@@ -109,8 +124,12 @@ def run_gemm(args):
                      "frac_of_sustained": tf / sustained, "kernel": "gemm_q4k_tc5_kernel", "traffic": None},
         "e2e": {"value": e2e_tf, "unit": "TFLOP/s", "h2d_bytes_per_step": GEMM_NTOK * k * 2,
                 "d2h_bytes_per_step": GEMM_NTOK * nrows * 2, "note": "jl_matmul host-pointer call, 14336x4096, wall clock"},
-        "gpu_launches": int(per_replay * args.steps), "clocks": clocks}), flush=True)
+        "gpu_launches": int(per_replay * args.steps), "clocks": clocks})
+    for hs, _, _ in sets:
+        for h in hs:
+            h.free()
     dev.Close()
+    return _emit(line, emit)
 
 
 # ------------------------------------------------------------------ Q8_0 batched decode
@@ -118,7 +137,7 @@ Q8_SHAPES = [(4096, 4096), (1024, 4096), (14336, 4096)]
 Q8_NTOK = 32
 
 
-def run_q8_batch(args):
+def run_q8_batch(args, emit=True):
     """Q8_0 batch-32 decode matmuls (f32 activations), the three shapes back to back over rings of distinct
     weight copies. Under torchrun the rows are column-sharded over the ranks (strong scaling, no collective)."""
     import torch
@@ -127,8 +146,7 @@ def run_q8_batch(args):
     world, rank, local = _env()
     torch.cuda.set_device(local)
     if world > 1:
-        import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        dist = _pg(local)
     dev = Device(local)
     rng = synth.rng_for(0xB202 + rank)
     sh = torch.cuda.current_stream().cuda_stream
@@ -172,8 +190,9 @@ def run_q8_batch(args):
         dev.MatMul(out_host, Q8_0, w_host, x_host, nrows, k, Q8_NTOK)
     e2e = 50 * (nrows * k * 34 // 32 + Q8_NTOK * (k + nrows) * 4) / (time.perf_counter() - t0) / 1e9
     hbm, burst, sustained, which = _peaks()
+    line = None
     if rank == 0:
-        print(json.dumps({
+        line = ({
             "metric": "q8_0_batch32_gbs", "value": gbs * world, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "Q8_0 -> f16 weights (one rounding), f32 activations as f16 hi+lo, f32 accumulate (tcgen05)",
@@ -185,18 +204,21 @@ def run_q8_batch(args):
                          "kernel": "gemm_q4k_tc5_kernel<1,...> (Q8_0 dequant)", "traffic": None},
             "e2e": {"value": e2e * world, "unit": "GB/s", "h2d_bytes_per_step": Q8_NTOK * k * 4, "d2h_bytes_per_step": Q8_NTOK * nrows * 4,
                     "note": "jl_matmul host-pointer call on the 4096x4096 shard, wall clock"},
-            "gpu_launches": int(per_replay * args.steps), "clocks": clocks}), flush=True)
+            "gpu_launches": int(per_replay * args.steps), "clocks": clocks})
+    for hs, _, _ in sets:
+        for h in hs:
+            h.free()
     dev.Close()
     if world > 1:
         dist.barrier()
-        dist.destroy_process_group()
+    return _emit(line, emit)
 
 
 # ------------------------------------------------------------------ mixture layer
 MOE = dict(E=32, topk=4, hidden=2880, ffn=2880, ntok=256, layers=2)   # 2 distinct layers: 846 MB of experts > L2
 
 
-def run_moe_ep(args):
+def run_moe_ep(args, emit=True):
     """The same layer expert-parallel under torchrun: 32 / world experts per rank, the 256 tokens data-parallel,
     NCCL all-to-all dispatch and return, combine in ascending expert id on the token's home rank."""
     import torch
@@ -205,7 +227,7 @@ def run_moe_ep(args):
     from jitllm_b200._lib import MXFP4, MoeDesc
     world, rank, local = _env()
     torch.cuda.set_device(local)
-    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    _pg(local)
     E, topk, hidden, ffn, ntok_all = MOE["E"], MOE["topk"], MOE["hidden"], MOE["ffn"], MOE["ntok"]
     epr, ntok = E // world, ntok_all // world
     rng = synth.rng_for(0xB203 + rank)
@@ -252,8 +274,9 @@ def run_moe_ep(args):
     us = ms * 1e3 / args.steps
     hbm, burst, sustained, which = _peaks()
     wbytes_rank = epr * 3 * hidden * (ffn // 32) * 17
+    line = None
     if rank == 0:
-        print(json.dumps({
+        line = ({
             "metric": "mxfp4_moe_layers_per_s", "value": 1e6 / us, "unit": "layers/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "MXFP4 -> f16, bf16->f16 activations, f32 accumulate (tcgen05 kind::f16)", "data": "synthetic",
@@ -262,21 +285,23 @@ def run_moe_ep(args):
                        "l2": "one layer of experts per rank, re-read every step: the per-rank working set is below L2 at 8 ranks"},
             "roofline": {"bound": "hbm", "achieved": wbytes_rank / us / 1e3, "peak": hbm, "unit": "GB/s",
                          "frac": wbytes_rank / us / 1e3 / hbm, "of": which, "kernel": "whole layer incl. NCCL all-to-all, weight bytes per rank", "traffic": None},
-            "e2e": None, "gpu_launches": int(per_step * args.steps), "clocks": clk.summary()}), flush=True)
+            "e2e": None, "gpu_launches": int(per_step * args.steps), "clocks": clk.summary()})
+    for h_ in hs:
+        h_.free()
     dev.Close()
     dist.barrier()
-    dist.destroy_process_group()
+    return _emit(line, emit)
 
 
-def run_moe(args):
+def run_moe(args, emit=True):
     import torch
     from jitllm_b200 import Device, synth
     from jitllm_b200._lib import MXFP4, MoeDesc
     world, rank, local = _env()
     if world > 1:
-        return run_moe_ep(args)
+        return run_moe_ep(args, emit)
     if rank != 0:
-        return
+        return None
     torch.cuda.set_device(local)
     E, topk, hidden, ffn, ntok = MOE["E"], MOE["topk"], MOE["hidden"], MOE["ffn"], MOE["ntok"]
     rng = synth.rng_for(0xB203)
@@ -320,7 +345,7 @@ def run_moe(args):
         dev.MoeHost(out_host, h_host, lg_host, hg, hu, hd, E, topk, hidden, ffn)
     e2e_layers = n_e2e / (time.perf_counter() - t0)
     hbm, burst, sustained, which = _peaks()
-    print(json.dumps({
+    line = ({
         "metric": "mxfp4_moe_layers_per_s", "value": 1e6 / us, "unit": "layers/s", "n_gpus": 1, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "MXFP4 -> f16 (cvt e2m1x2), bf16->f16 activations, f32 accumulate (tcgen05 kind::f16)",
@@ -332,103 +357,237 @@ def run_moe(args):
                      "algorithmic_bytes_per_layer": abytes},
         "e2e": {"value": e2e_layers, "unit": "layers/s", "h2d_bytes_per_step": ntok * hidden * 2 + ntok * E * 4,
                 "d2h_bytes_per_step": ntok * hidden * 4, "note": "jl_moe host-pointer call, wall clock"},
-        "gpu_launches": int(per_replay * args.steps), "clocks": clocks}), flush=True)
+        "gpu_launches": int(per_replay * args.steps), "clocks": clocks})
+    for hs in keep:
+        for h_ in hs:
+            h_.free()
     dev.Close()
+    return _emit(line, emit)
 
 
 # ------------------------------------------------------------------ decoder
-def run_decode(args):
+def run_decode(args, emit=True, batches=None, steps=None):
     """Llama-3-8B-shaped Q4_K decoder: prompt prefill (GEMM path), then greedy decode steps replayed from a CUDA
-    graph. Under torchrun the model is tensor-parallel over the ranks (strong scaling: one model, N GPUs)."""
+    graph. Batch 1 runs the block kernel (one persistent launch per token); larger batches the per-matmul chain.
+    Under torchrun the model is tensor-parallel over the ranks (strong scaling: one model, N GPUs): at batch 1 the
+    ranks exchange partial sums inside the kernel over peer slots, above it through NCCL all-reduce.
+    Returns one line per batch size."""
     import torch
+    import bench
     from jitllm_b200 import Device
     from jitllm_b200.decoder import Config, Decoder
     world, rank, local = _env()
     torch.cuda.set_device(local)
-    if world > 1:
-        import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    B, T = args.batch, args.prompt
-    steps = args.steps
+    dist = _pg(local) if world > 1 else None
+    batches = batches or [args.batch]
+    T = args.prompt
+    steps = steps or args.steps
+    warm = max(args.warmup, 3)
     dev = Device(local)
-    dec = Decoder(dev, Config(), max_batch=B, max_len=T + (max(args.warmup, 3) + steps) + 16, rank=rank, world=world,
-                  max_prefill=T)
+    dec = Decoder(dev, Config(), max_batch=max(batches), max_len=T + len(batches) * (warm + steps + 24) + 16, rank=rank,
+                  world=world, max_prefill=T, group=dist.group.WORLD if world > 1 else None)
     prompt = torch.randint(0, 128256, (T,), device="cuda", generator=torch.Generator(device="cuda").manual_seed(7))
+    hbm, burst, sustained, which = _peaks()
+    wb = dec.weight_bytes                                       # per rank
+    lines = []
     with torch.no_grad():
         torch.cuda.synchronize()
         t0 = time.perf_counter()
         nxt = dec.prefill(prompt)
         torch.cuda.synchronize()
         prefill_s = time.perf_counter() - t0
-        tok = nxt.expand(B).contiguous()
-        pos = torch.tensor([T], device="cuda")
-        for _ in range(2):
-            dec.decode_step(tok, pos)                      # eager warm-up (sizes the attention scratch)
-        torch.cuda.synchronize()
-        n0 = dev.Stats().launches
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
-            out = dec.decode_step(tok, pos)
-            tok.copy_(out)
-            pos.add_(1)
-        matmul_launches = dev.Stats().launches - n0
-        aux_launches = 1 + 6 * dec.cfg.n_layer + 1            # norms, rope, attention, silu per layer; first norm; argmax
-        import bench
-        for _ in range(max(args.warmup, 3)):
-            g.replay()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        with bench.ClockSampler(local) as clk:
-            e0.record()
-            for _ in range(steps):
+        use_block = 1 in batches and dec.prep_block_kernel()
+        start = T
+        for B in batches:
+            block = use_block and B == 1
+            tok = nxt.expand(B).contiguous()
+            pos = torch.tensor([start], device="cuda")
+
+            def one_step():
+                if block:
+                    out = dec.decode_step_block(tok, pos, advance=world == 1)
+                    if world > 1:
+                        tok.copy_(out)
+                        pos.add_(1)
+                else:
+                    out = dec.decode_step(tok, pos)
+                    tok.copy_(out)
+                    pos.add_(1)
+            for _ in range(2):
+                one_step()                                     # eager warm-up (sizes the attention scratch)
+            torch.cuda.synchronize()
+            n0 = dev.Stats().launches
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                one_step()
+            lib_launches = dev.Stats().launches - n0
+            aux_launches = 0 if block else 1 + 6 * dec.cfg.n_layer + 1   # norms, rope, attention, silu per layer; first norm; argmax
+            if block and world > 1:
+                aux_launches = 1                                # argmax over the gathered vocabulary shards
+            for _ in range(warm):
                 g.replay()
-            e1.record()
+            if world > 1:
+                dist.barrier()
             torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1)
-        # end to end: the token ids cross the host boundary every step (ids in from pinned memory, next ids out)
-        tok_pin = torch.empty(B, dtype=torch.int64).pin_memory()
-        tok_pin.copy_(tok)
-        n_e2e = min(steps, 16)
-        pos.fill_(T)
-        torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        for _ in range(n_e2e):
-            tok.copy_(tok_pin, non_blocking=True)
-            g.replay()
-            tok_pin.copy_(tok, non_blocking=True)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            with bench.ClockSampler(local) as clk:
+                e0.record()
+                for _ in range(steps):
+                    g.replay()
+                e1.record()
+                torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1)
+            ok = dev.StatusPoll()
+            # end to end: the token ids cross the host boundary every step (ids in from pinned memory, next ids out)
+            tok_pin = torch.empty(B, dtype=torch.int64).pin_memory()
+            tok_pin.copy_(tok)
+            n_e2e = min(steps, 16)
             torch.cuda.synchronize()
-        e2e_s = time.perf_counter() - t0
-    if world > 1:
-        tt = torch.tensor([ms, e2e_s], device="cuda", dtype=torch.float64)
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        ms, e2e_s = float(tt[0]), float(tt[1])
-    ms_step = ms / steps
-    hbm, burst, sustained, which = _peaks()
-    wb = dec.weight_bytes                                       # per rank
-    if rank == 0:
-        print(json.dumps({
-            "metric": "decode_tok_s", "value": B * 1e3 / ms_step, "unit": "tok/s", "n_gpus": world, "steps": steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "Q4_K weights, f32 activations (int8-digit MMA decode / f16 tcgen05 GEMM), bf16 KV",
-            "data": "synthetic (random-init Q4_K weights, random prompt ids)",
-            "config": {"workload": "llama8b_q4k_decode", "batch": B, "prompt": T, "layers": 32, "hidden": 4096, "heads": "32q/8kv x128",
-                       "ffn": 14336, "vocab": 128256, "parallelism": f"tp{world}", "prefill_tok_s": T / prefill_s,
-                       "l2": f"weights per rank {wb / 1e9:.2f} GB stream every step: larger than L2",
-                       "weight_roofline_tok_s": B * hbm * 1e9 / (wb * world) * world},
-            "roofline": {"bound": "hbm", "achieved": wb / ms_step / 1e6, "peak": hbm, "unit": "GB/s",
-                         "frac": wb / ms_step / 1e6 / hbm, "of": which, "kernel": "whole decode step, weight bytes per rank only",
-                         "traffic": None},
-            "e2e": {"value": B * n_e2e / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": B * 8, "d2h_bytes_per_step": B * 8,
-                    "note": "token ids in from pinned host memory and next ids back to the host every step, wall clock"},
-            "gpu_launches": int((matmul_launches + aux_launches) * steps), "clocks": clk.summary()}), flush=True)
-    del g
-    torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            for _ in range(n_e2e):
+                tok.copy_(tok_pin, non_blocking=True)
+                g.replay()
+                tok_pin.copy_(tok, non_blocking=True)
+                torch.cuda.synchronize()
+            e2e_s = time.perf_counter() - t0
+            start = int(pos.item()) + 1
+            if world > 1:
+                tt = torch.tensor([ms, e2e_s, 0.0 if ok else 1.0], device="cuda", dtype=torch.float64)
+                dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+                ms, e2e_s, ok = float(tt[0]), float(tt[1]), float(tt[2]) == 0.0
+            if not ok:
+                raise RuntimeError("a bounded device-side wait ran out during the timed decode steps: " + dev.Err())
+            ms_step = ms / steps
+            kv_bytes = B * 2 * (start - 1) * dec.hkv * dec.cfg.head_dim * 2 * dec.cfg.n_layer   # K and V rows read per step, per rank
+            line = {
+                "metric": "decode_tok_s", "value": B * 1e3 / ms_step, "unit": "tok/s", "n_gpus": world, "steps": steps,
+                "warmup": warm, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+                "vs_baseline": None, "dtype": "Q4_K weights, f32 activations (int8-digit MMA decode / f16 tcgen05 GEMM), bf16 KV",
+                "data": "synthetic (random-init Q4_K weights, random prompt ids)",
+                "config": {"workload": "llama8b_q4k_decode", "batch": B, "prompt": T, "layers": 32, "hidden": 4096, "heads": "32q/8kv x128",
+                           "ffn": 14336, "vocab": 128256, "parallelism": f"tp{world}", "prefill_tok_s": T / prefill_s,
+                           "form": ("block kernel: one persistent launch per token" + (", partial sums exchanged in-kernel over peer slots" if world > 1 else ""))
+                                   if block else ("per-matmul chain" + (", NCCL all-reduce" if world > 1 else "")),
+                           "l2": f"weights per rank {wb / 1e9:.2f} GB stream every step: larger than L2",
+                           "weight_roofline_tok_s": B * hbm * 1e9 / wb},
+                "roofline": {"bound": "hbm", "achieved": (wb + kv_bytes) / ms_step / 1e6, "peak": hbm, "unit": "GB/s",
+                             "frac": (wb + kv_bytes) / ms_step / 1e6 / hbm, "of": which,
+                             "kernel": "jl_block_kernel" if block else "whole decode step",
+                             "algorithmic_bytes_per_step": wb + kv_bytes, "traffic": None},
+                "e2e": {"value": B * n_e2e / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": B * 8, "d2h_bytes_per_step": B * 8,
+                        "note": "token ids in from pinned host memory and next ids back to the host every step, wall clock"},
+                "gpu_launches": int((lib_launches + aux_launches) * steps), "clocks": clk.summary()}
+            del g
+            torch.cuda.synchronize()
+            if rank == 0:
+                lines.append(_emit(line, emit))
+    if use_block:
+        dec.block.free()
+    del dec
+    dev.Close()
     if world > 1:
         dist.barrier()
-        os._exit(0)      # a process group whose collectives were captured in a graph can stall in its destructor
+    return lines
 
+
+# ------------------------------------------------------------------ sharded forms against the unsharded ones
+def _perr(got, ref):
+    """max_i |got - ref| / max(|ref_i|, rms(ref)): the output-parity measure (bar 2e-3)."""
+    got, ref = got.double().reshape(-1), ref.double().reshape(-1)
+    rms = ref.pow(2).mean().sqrt().clamp_min(1e-30)
+    return float(((got - ref).abs() / ref.abs().clamp_min(rms)).max())
+
+
+def sharded_parity(local):
+    """Run on the live process group before anything is timed: (1) one full-width Llama-3-8B-shaped block + head,
+    tensor-parallel over the ranks, against the same block unsharded on this rank's own GPU -- batch 1 through the
+    block kernel (partial sums exchanged in-kernel over peer slots) and batch 2 through the per-matmul chain (NCCL
+    all-reduce); (2) a mixture layer expert-parallel over the ranks against the whole layer on one GPU. The
+    unsharded forms are what the single-GPU parity tests hold against the CPU oracle. Returns the two errors."""
+    import torch
+    import torch.distributed as dist
+    from jitllm_b200 import Device, parallel, synth
+    from jitllm_b200._lib import MXFP4, MoeDesc
+    from jitllm_b200.decoder import Config, Decoder
+    world, rank, _ = _env()
+    dev = Device(local)
+    T = 200
+    tp_err = 0.0
+    with torch.no_grad():
+        cfg = Config(n_layer=1, vocab=8192)
+        one = Decoder(dev, cfg, max_batch=2, max_len=T + 8, max_prefill=16, share_full=True, seed=5)
+        tp = Decoder(dev, cfg, max_batch=2, max_len=T + 8, max_prefill=16, share_full=True, seed=5, rank=rank, world=world)
+        g = torch.Generator(device="cuda").manual_seed(3)                  # the same cache contents on every rank
+        kfull = torch.randn(1, 2, cfg.n_kv, T, cfg.head_dim, device="cuda", generator=g).to(torch.bfloat16)
+        vfull = torch.randn(1, 2, cfg.n_kv, T, cfg.head_dim, device="cuda", generator=g).to(torch.bfloat16)
+        one.k_cache[:, :, :, :T], one.v_cache[:, :, :, :T] = kfull, vfull
+        tp.k_cache[:, :, :, :T] = kfull[:, :, rank * tp.hkv:(rank + 1) * tp.hkv]
+        tp.v_cache[:, :, :, :T] = vfull[:, :, rank * tp.hkv:(rank + 1) * tp.hkv]
+        ok = one.prep_block_kernel() and tp.prep_block_kernel()
+        if not ok:
+            raise RuntimeError("the block kernel declined the Llama-3-8B-shaped block: " + dev.Err())
+        pos = torch.tensor([T], device="cuda")
+        for B in (1, 2):
+            tok = torch.tensor([17, 4099][:B], device="cuda")
+            if B == 1:
+                one.decode_step_block(tok.clone(), pos)
+            else:
+                one.decode_step(tok, pos)
+            ref = one.last_logits.clone()
+            if B == 1:
+                tp.decode_step_block(tok.clone(), pos)
+            else:
+                tp.decode_step(tok, pos)
+            parts = [torch.empty_like(tp.last_logits) for _ in range(world)]
+            dist.all_gather(parts, tp.last_logits.contiguous())
+            torch.cuda.synchronize()
+            if not dev.StatusPoll():
+                raise RuntimeError("tensor-parallel step: " + dev.Err())
+            tp_err = max(tp_err, _perr(torch.cat(parts, dim=-1), ref))
+        one.block.free()
+        tp.block.free()
+        del one, tp
+        # ---- expert parallel
+        E, topk, hidden, ffn, ntok = 32, 4, 576, 576, 64
+        rng = synth.rng_for(0xE9)                                          # the same banks on every rank
+        banks = [synth.mxfp4_matrix(rng, E * r, kk) for r, kk in ((ffn, hidden), (ffn, hidden), (hidden, ffn))]
+        epr = E // world
+        stream = torch.cuda.current_stream().cuda_stream
+        full = [dev.Upload(MXFP4, b, r, kk, E) for b, (r, kk) in zip(banks, ((ffn, hidden), (ffn, hidden), (hidden, ffn)))]
+        mine = [dev.Upload(MXFP4, parallel.shard_experts(b, MXFP4, E, r, kk, rank, world)[0], r, kk, epr)
+                for b, (r, kk) in zip(banks, ((ffn, hidden), (ffn, hidden), (hidden, ffn)))]
+        dev.MoeReserve(ntok * topk, E, topk, hidden, ffn)
+        d_full = MoeDesc(struct_size=C.sizeof(MoeDesc), type=MXFP4, n_expert=E, top_k=topk, hidden=hidden, ffn=ffn, act=0, norm=1,
+                         scale=1.0, gate=full[0].handle, up=full[1].handle, down=full[2].handle)
+        d_local = MoeDesc(struct_size=C.sizeof(MoeDesc), type=MXFP4, n_expert=epr, top_k=1, hidden=hidden, ffn=ffn, act=0, norm=1,
+                          scale=1.0, gate=mine[0].handle, up=mine[1].handle, down=mine[2].handle)
+        g = torch.Generator(device="cuda").manual_seed(100 + rank)          # every rank routes its own tokens
+        h = (torch.randn(ntok, hidden, device="cuda", generator=g) * 0.25).to(torch.bfloat16)
+        logits = torch.randn(ntok, E, device="cuda", generator=g)
+        ref = torch.zeros(ntok, hidden, device="cuda")
+        dev.MoeDev(ref, h, logits, ntok, d_full, None, None, stream)
+
+        def route(lg):
+            sel = torch.empty(lg.shape[0], topk, dtype=torch.int32, device="cuda")
+            wt = torch.empty(lg.shape[0], topk, dtype=torch.float32, device="cuda")
+            dev.MoeRouteDev(lg, lg.shape[0], d_full, sel, wt, stream)
+            return sel, wt
+
+        def experts(rows, ids):
+            y = torch.empty(rows.shape[0], hidden, dtype=torch.float32, device="cuda")
+            dev.MoeExpertsDev(y, rows.contiguous(), ids.contiguous(), rows.shape[0], d_local, stream)
+            return y
+        out = torch.zeros(ntok, hidden, device="cuda")
+        parallel.ExpertParallelMoE(route, experts, E, topk, hidden).forward(out, h, logits)
+        torch.cuda.synchronize()
+        ep_err = _perr(out, ref)
+        for w in full + mine:
+            w.free()
+    dev.Close()
+    tt = torch.tensor([tp_err, ep_err], device="cuda", dtype=torch.float64)
+    dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+    return {"tp_err": float(tt[0]), "ep_err": float(tt[1]), "bar": 2e-3,
+            "against": "the unsharded forms on one GPU (which the single-GPU tests hold against the CPU oracle)"}
 
 
 # ------------------------------------------------------------------ reference arm (CPU restatement, host cores)

@@ -78,6 +78,28 @@ def _worker(rank, world, port, tmp):
             tp.decode_step(a.expand(2).contiguous(), pos)
             lb = torch.cat([t_ for t_ in _gather(dist, tp.last_logits)], dim=-1).double()
             assert float((la - lb).abs().max() / la.abs().max()) < 1e-2
+            # ---- the same step as ONE kernel per rank: partial sums cross NVLink inside the kernel (peer slots and
+            # flags, no collective call), summed in rank order; against the unsharded block kernel, several steps
+            assert one.prep_block_kernel() and tp.prep_block_kernel(), dev.Err()
+            ka, va, kb, vb = one.k_cache.clone(), one.v_cache.clone(), tp.k_cache.clone(), tp.v_cache.clone()
+            runs = []
+            for _ in range(2):                                       # twice from the same state: the same bits
+                one.k_cache.copy_(ka); one.v_cache.copy_(va); tp.k_cache.copy_(kb); tp.v_cache.copy_(vb)
+                ta, tb, pa, pb = a.clone(), a.clone(), torch.tensor([7], device="cuda"), torch.tensor([7], device="cuda")
+                seen = []
+                for _ in range(5):
+                    na = one.decode_step_block(ta, pa)
+                    la = one.last_logits.double()
+                    nb = tp.decode_step_block(tb, pb)
+                    lb = torch.cat([t_ for t_ in _gather(dist, tp.last_logits)], dim=-1).double()
+                    torch.cuda.synchronize()
+                    assert dev.StatusPoll(), dev.Err()
+                    assert parity_err(lb.cpu().numpy(), la.cpu().numpy()) <= BAR
+                    seen.append(lb.clone())
+                    ta.copy_(na); tb.copy_(na); pa += 1; pb += 1     # both continue from the unsharded run's token
+                runs.append(torch.stack(seen))
+            assert torch.equal(runs[0], runs[1])
+            one.block.free(); tp.block.free()
         # ---- expert parallel mixture layer, tokens data-parallel
         E, topk, hidden, ffn, ntok_all = 8, 2, 128, 192, 24
         gate = synth.mxfp4_matrix(rng, E * ffn, hidden)
