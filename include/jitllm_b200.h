@@ -343,6 +343,15 @@ void jl_layers_free(jl_ctx *ctx, jl_layers *layers);
 int jl_layers_run(jl_ctx *ctx, jl_layers *layers, long long *tok_dev, long long *pos_dev, float *logits_out_dev,
                   long long *next_tok_dev, int advance, void *stream);
 
+/* Per-phase timing of one step, the reference's per-op nanosecond counters (model.OpProfile,
+ * engine/model/forward.go:22-75): runs one step (no advance), waits for it and returns, for every phase,
+ * four GPU global-timer stamps (ns) of the grid's first and last CTA -- phase start, prologue done, work
+ * done, barrier passed: stamps_out[2][jl_layers_phases()][4] in host memory. Phases per block: q|k|v,
+ * attention, o, gate|up, down; then the head and the argmax. */
+int jl_layers_phases(jl_layers *layers);
+int jl_layers_profile(jl_ctx *ctx, jl_layers *layers, long long *tok_dev, long long *pos_dev, void *stream,
+                      unsigned long long *stamps_out, int n_phases);
+
 /* ---- tensor-parallel exchange without a collective library (no counterpart in the reference, which has
  * no tensor parallelism: docs/perf/current.md:582) ------------------------------------------------
  * Each rank owns a slot buffer (jl_tp_slot) that the other ranks' kernels store their partial sums and a

@@ -102,6 +102,8 @@ SYMBOLS = {
     "jl_layers_prep": (_I, [_VP, C.POINTER(LayersDesc), C.POINTER(_VP)]),
     "jl_layers_free": (None, [_VP, _VP]),
     "jl_layers_run": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _I, _VP]),
+    "jl_layers_phases": (_I, [_VP]),
+    "jl_layers_profile": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _I]),
     "jl_tp_slot": (_I, [_VP, _VP, C.POINTER(_VP), C.POINTER(C.c_size_t)]),
     "jl_tp_ipc_export": (_I, [_VP, _VP]),
     "jl_tp_ipc_open": (_I, [_VP, C.POINTER(_VP)]),

@@ -32,22 +32,21 @@
 
 #define BK_WARPS 16
 #define BK_THREADS (BK_WARPS * 32)
-#define BK_STAGES 3
+#define BK_STAGES 4
 #define BK_TILE 2304                 // 16 rows x 144 B
 #define BK_MAX_NSB 64                // longest activation row: 64 super-blocks = 16384 elements
 #define BK_ROUND_TASKS 256           // warp-tasks whose partial sums one round keeps in shared memory
 #define BK_ATT_CHUNK 32              // cache positions per attention task
-#define BK_ATT_ROW 272               // bytes of a staged K/V row: 256 + 16 of padding (bank spread)
 #define BK_ATT_D 128
 #define BK_MAX_G 4                   // query heads per kv head
 #define BK_MAX_WORLD 8
-#define BK_ATT_SUB_BYTES 20480       // shared memory of one 128-thread attention group
+#define BK_ATT_SUB_BYTES 13312       // shared memory of one 128-thread attention group
 
 enum { BK_MATVEC = 0, BK_ATTN = 1, BK_FINAL = 2 };
 enum { BK_PRO_NORM = 0, BK_PRO_PLAIN = 1 };
 enum { BK_EPI_STORE = 0, BK_EPI_GATE2 = 1, BK_EPI_ARGMAX = 2 };
 
-struct bk_phase {
+struct alignas(16) bk_phase {
     int kind;
     // ---- matvec
     int map;            // index of the weight's tensor map: box 144 B x 16 rows (GATE2: x 8 rows)
@@ -93,6 +92,7 @@ struct bk_params {
     unsigned *peer_flags[BK_MAX_WORLD];  // the same array on every rank
     unsigned *seq;                       // local: exchanges completed by earlier launches
     int nexchange;                       // exchanges per launch
+    unsigned long long *trace;           // optional [2][nphases][4] global-timer stamps of the first and the last CTA
 };
 
 // ------------------------------------------------------------------ small helpers
@@ -158,10 +158,10 @@ __device__ __forceinline__ bool bk_grid_sync(const bk_params &P, int &done, uint
     __shared__ int s_ok;
     __syncthreads();
     if (threadIdx.x == 0) {
-        if (sys_fence) __threadfence_system(); else __threadfence();
-        atomicAdd(P.bar, 1u);
-        s_ok = bk_wait_ge<false>(P.bar, (unsigned)(done + 1) * gridDim.x, P, limit_ns, 4) ? 1 : 0;
-        __threadfence();
+        // release: the CTA's writes (ordered before this thread by the barrier above) become visible before the count
+        if (sys_fence) __threadfence_system();
+        asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(P.bar) : "memory");
+        s_ok = bk_wait_ge<false>(P.bar, (unsigned)(done + 1) * gridDim.x, P, limit_ns, 4) ? 1 : 0;   // acquire loads
     }
     __syncthreads();
     done++;
@@ -174,13 +174,21 @@ __device__ __forceinline__ bool bk_grid_sync(const bk_params &P, int &done, uint
 // as BK_ROUND_TASKS warp-tasks cover; inside a round warp w takes tasks w, w + 16, ... (task = row group x
 // super-block, super-block fastest). The fetch side (TMA requests) and the consume side walk the same sequence;
 // the fetch side runs BK_STAGES tasks ahead and simply continues into the following matvec phases.
+// What the hot loop needs to know about a phase, staged in shared memory once per launch (the phase list itself
+// lives in global memory: reading it from the fetch path cost more than the fetch).
+struct bk_pinfo {
+    int kind, map, nsb, epi;
+    int rg0, rg1, up_row0, rpr;   // this CTA's row groups [rg0, rg1); row groups per round
+};
+#define BK_MAX_PHASES 512
+
 struct bk_cursor {
     int p;        // phase index (nphases = exhausted)
     int rg1;      // end of the CTA's row groups in this phase
     int rbase;    // first row group of the current round
     int nr;       // row groups in the current round
-    int t;        // this warp's task inside the round
-    int nsb;
+    int rgl, sb;  // this warp's task inside the round: row group (relative to rbase) and super-block
+    int nsb, rpr;
 };
 
 __device__ __forceinline__ int bk_phase_nrg(const bk_phase &ph) {
@@ -190,42 +198,45 @@ __device__ __forceinline__ int bk_rounds_rgs(int nsb) {
     const int r = BK_ROUND_TASKS / nsb;
     return r < 1 ? 1 : r;
 }
+// The warp's first task of a round: task index `warp`, if the round has that many.
+__device__ __forceinline__ bool bk_cursor_round(bk_cursor &c, int warp) {
+    if (warp >= c.nr * c.nsb) return false;
+    c.rgl = warp / c.nsb; c.sb = warp % c.nsb;
+    return true;
+}
 // Positions the cursor on the warp's first task of the first matvec phase >= p that has one.
-__device__ __forceinline__ void bk_cursor_seek(bk_cursor &c, const bk_params &P, int p, int warp) {
-    for (; p < P.nphases; p++) {
-        const bk_phase &ph = P.phases[p];
-        if (ph.kind != BK_MATVEC) continue;
-        const int nrg = bk_phase_nrg(ph);
-        const int rg0 = (int)((long long)blockIdx.x * nrg / gridDim.x);
-        c.rg1 = (int)((long long)(blockIdx.x + 1) * nrg / gridDim.x);
-        c.nsb = ph.nsb;
-        const int rpr = bk_rounds_rgs(c.nsb);
-        for (c.rbase = rg0; c.rbase < c.rg1; c.rbase += rpr) {
-            c.nr = min(rpr, c.rg1 - c.rbase);
-            if (warp < c.nr * c.nsb) { c.p = p; c.t = warp; return; }
+__device__ __forceinline__ void bk_cursor_seek(bk_cursor &c, const bk_pinfo *pi, int nphases, int p, int warp) {
+    for (; p < nphases; p++) {
+        const bk_pinfo f = pi[p];
+        if (f.kind != BK_MATVEC) continue;
+        c.rg1 = f.rg1; c.nsb = f.nsb; c.rpr = f.rpr;
+        for (c.rbase = f.rg0; c.rbase < c.rg1; c.rbase += c.rpr) {
+            c.nr = min(c.rpr, c.rg1 - c.rbase);
+            if (bk_cursor_round(c, warp)) { c.p = p; return; }
         }
     }
-    c.p = P.nphases;
+    c.p = nphases;
 }
-__device__ __forceinline__ void bk_cursor_next(bk_cursor &c, const bk_params &P, int warp) {
-    c.t += BK_WARPS;
-    if (c.t < c.nr * c.nsb) return;
-    const int rpr = bk_rounds_rgs(c.nsb);
-    for (c.rbase += rpr; c.rbase < c.rg1; c.rbase += rpr) {
-        c.nr = min(rpr, c.rg1 - c.rbase);
-        if (warp < c.nr * c.nsb) { c.t = warp; return; }
+__device__ __forceinline__ void bk_cursor_next(bk_cursor &c, const bk_pinfo *pi, int nphases, int warp) {
+    c.sb += BK_WARPS;                       // task index + 16, super-block fastest
+    while (c.sb >= c.nsb) { c.sb -= c.nsb; c.rgl++; }
+    if (c.rgl < c.nr) return;
+    for (c.rbase += c.rpr; c.rbase < c.rg1; c.rbase += c.rpr) {
+        c.nr = min(c.rpr, c.rg1 - c.rbase);
+        if (bk_cursor_round(c, warp)) return;
     }
-    bk_cursor_seek(c, P, c.p + 1, warp);
+    bk_cursor_seek(c, pi, nphases, c.p + 1, warp);
 }
-// Requests the cursor's tile into ring stage `stage` (one elected lane calls this).
-__device__ __forceinline__ void bk_fetch(const bk_cursor &c, const bk_params &P, uint32_t tile_smem, uint32_t bar) {
-    const bk_phase &ph = P.phases[c.p];
-    const int rg = c.rbase + c.t / c.nsb, sb = c.t % c.nsb;
-    const CUtensorMap *map = P.maps + ph.map;
+// Requests the cursor's tile into a ring stage (one elected lane calls this).
+__device__ __forceinline__ void bk_fetch(const bk_cursor &c, const bk_pinfo *pi, const CUtensorMap *maps, uint32_t tile_smem,
+                                         uint32_t bar) {
+    const bk_pinfo f = pi[c.p];
+    const int rg = c.rbase + c.rgl, sb = c.sb;
+    const CUtensorMap *map = maps + f.map;
     mbar_arrive_expect_tx(bar, BK_TILE);
-    if (ph.epilogue == BK_EPI_GATE2) {
+    if (f.epi == BK_EPI_GATE2) {
         tma_load_2d(tile_smem, map, sb * 144, rg * 8, bar);                            // 8 gate rows
-        tma_load_2d(tile_smem + 8 * 144, map, sb * 144, ph.up_row0 + rg * 8, bar);     // the matching 8 up rows
+        tma_load_2d(tile_smem + 8 * 144, map, sb * 144, f.up_row0 + rg * 8, bar);      // the matching 8 up rows
     } else {
         tma_load_2d(tile_smem, map, sb * 144, rg * 16, bar);
     }
@@ -252,138 +263,262 @@ __device__ __forceinline__ float4 bk_resid4(const bk_params &P, const bk_phase &
     return v;
 }
 
-// Builds the decode operand of the phase's activation row in shared memory (every CTA, the whole row).
-__device__ __forceinline__ void bk_prologue(const bk_params &P, const bk_phase &ph, uint8_t *xop, float *ssq) {
+// Builds the decode operand of the phase's activation row in shared memory (every CTA, the whole row). Warp w owns
+// super-blocks w, w + 16, ... (at most BK_MAX_NSB / BK_WARPS of them); all their loads are issued before the first
+// is used, and the values stay in registers between the sum of squares and the normalisation.
+#define BK_PRO_IT (BK_MAX_NSB / BK_WARPS)
+#ifdef BK_FINE_TRACE
+#define BK_PT(i) do { ft[i] = clock64(); } while (0)
+#define BK_PT_ARG , long long *ft
+#else
+#define BK_PT(i) do { } while (0)
+#define BK_PT_ARG
+#endif
+__device__ __forceinline__ void bk_prologue(const bk_params &P, const bk_phase &ph, uint8_t *xop, float *ssq BK_PT_ARG) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nsb = ph.nsb;
+    BK_PT(0);
     if (ph.prologue == BK_PRO_NORM) {
-        float ss = 0.f;
-        for (int sb = warp; sb < nsb; sb += BK_WARPS)
+        if (nsb <= BK_WARPS) {
+            // one super-block per warp: its eight values and weights stay in registers between the two passes
+            float4 v[2], gw[2];
+            const bool mine = warp < nsb;
+            if (mine) {
 #pragma unroll
-            for (int hf = 0; hf < 2; ++hf) {
-                const int i4 = sb * 64 + hf * 32 + lane;
-                const float4 v = bk_resid4(P, ph, i4);
-                if (blockIdx.x == 0 && ph.xdst) reinterpret_cast<float4 *>(ph.xdst)[i4] = v;   // the new residual row
-                ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+                for (int hf = 0; hf < 2; ++hf) {
+                    const int i4 = warp * 64 + hf * 32 + lane;
+                    v[hf] = bk_resid4(P, ph, i4);
+                    gw[hf] = ph.norm_w ? __ldg(reinterpret_cast<const float4 *>(ph.norm_w) + i4) : make_float4(1.f, 1.f, 1.f, 1.f);
+                }
+            }
+            float ss = 0.f;
+            if (mine) {
+#pragma unroll
+                for (int hf = 0; hf < 2; ++hf) {
+                    const float4 a = v[hf];
+                    if (blockIdx.x == 0 && ph.xdst) reinterpret_cast<float4 *>(ph.xdst)[warp * 64 + hf * 32 + lane] = a;   // the new residual row
+                    ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+                }
             }
 #pragma unroll
-        for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-        if (lane == 0) ssq[warp] = ss;
-        __syncthreads();
-        float tot = 0.f;
+            for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            BK_PT(1);
+            if (lane == 0) ssq[warp] = ss;
+            __syncthreads();
+            BK_PT(2);
+            float tot = 0.f;
 #pragma unroll
-        for (int i = 0; i < BK_WARPS; i++) tot += ssq[i];      // fixed order: every CTA gets the same bits
-        const float r = rsqrtf(tot / (float)P.hidden + P.eps);
-        for (int sb = warp; sb < nsb; sb += BK_WARPS) {
-            float4 v[2];
+            for (int i = 0; i < BK_WARPS; i++) tot += ssq[i];      // fixed order: every CTA gets the same bits
+            const float r = rsqrtf(tot / (float)P.hidden + P.eps);
+            if (mine) {
 #pragma unroll
-            for (int hf = 0; hf < 2; ++hf) {
-                const int i4 = sb * 64 + hf * 32 + lane;
-                const float4 a = bk_resid4(P, ph, i4);
-                const float4 gw = ph.norm_w ? __ldg(reinterpret_cast<const float4 *>(ph.norm_w) + i4) : make_float4(1.f, 1.f, 1.f, 1.f);
-                v[hf] = make_float4(a.x * r * gw.x, a.y * r * gw.y, a.z * r * gw.z, a.w * r * gw.w);
+                for (int hf = 0; hf < 2; ++hf) {
+                    const float4 a = v[hf], g4 = gw[hf];
+                    v[hf] = make_float4(a.x * r * g4.x, a.y * r * g4.y, a.z * r * g4.z, a.w * r * g4.w);
+                }
+                q4k_prep_sb_vals(v[0], v[1], xop + (size_t)warp * Q4K_XP_SB_BYTES, lane);
             }
-            q4k_prep_sb_vals(v[0], v[1], xop + (size_t)sb * Q4K_XP_SB_BYTES, lane);
+        } else {
+            // longer rows: two passes over the row (the second one hits L2)
+            float ss = 0.f;
+            for (int sb = warp; sb < nsb; sb += BK_WARPS)
+#pragma unroll
+                for (int hf = 0; hf < 2; ++hf) {
+                    const int i4 = sb * 64 + hf * 32 + lane;
+                    const float4 a = bk_resid4(P, ph, i4);
+                    if (blockIdx.x == 0 && ph.xdst) reinterpret_cast<float4 *>(ph.xdst)[i4] = a;
+                    ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+                }
+#pragma unroll
+            for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            if (lane == 0) ssq[warp] = ss;
+            __syncthreads();
+            float tot = 0.f;
+#pragma unroll
+            for (int i = 0; i < BK_WARPS; i++) tot += ssq[i];
+            const float r = rsqrtf(tot / (float)P.hidden + P.eps);
+            for (int sb = warp; sb < nsb; sb += BK_WARPS) {
+                float4 w2[2];
+#pragma unroll
+                for (int hf = 0; hf < 2; ++hf) {
+                    const int i4 = sb * 64 + hf * 32 + lane;
+                    const float4 a = bk_resid4(P, ph, i4);
+                    const float4 g4 = ph.norm_w ? __ldg(reinterpret_cast<const float4 *>(ph.norm_w) + i4) : make_float4(1.f, 1.f, 1.f, 1.f);
+                    w2[hf] = make_float4(a.x * r * g4.x, a.y * r * g4.y, a.z * r * g4.z, a.w * r * g4.w);
+                }
+                q4k_prep_sb_vals(w2[0], w2[1], xop + (size_t)sb * Q4K_XP_SB_BYTES, lane);
+            }
         }
     } else {
-        for (int sb = warp; sb < nsb; sb += BK_WARPS) {
-            const float4 *s4 = reinterpret_cast<const float4 *>(ph.vsrc) + sb * 64;
-            q4k_prep_sb_vals(__ldcg(s4 + lane), __ldcg(s4 + 32 + lane), xop + (size_t)sb * Q4K_XP_SB_BYTES, lane);
+        float4 v[BK_PRO_IT][2];
+#pragma unroll
+        for (int it = 0; it < BK_PRO_IT; it++) {
+            const int sb = warp + it * BK_WARPS;
+            if (sb < nsb) {
+                const float4 *s4 = reinterpret_cast<const float4 *>(ph.vsrc) + sb * 64;
+                v[it][0] = __ldcg(s4 + lane);
+                v[it][1] = __ldcg(s4 + 32 + lane);
+            }
+        }
+        BK_PT(1);
+        BK_PT(2);
+#pragma unroll
+        for (int it = 0; it < BK_PRO_IT; it++) {
+            const int sb = warp + it * BK_WARPS;
+            if (sb < nsb) q4k_prep_sb_vals(v[it][0], v[it][1], xop + (size_t)sb * Q4K_XP_SB_BYTES, lane);
         }
     }
+    BK_PT(3);
     __syncthreads();
+    BK_PT(4);
+}
+
+// Pulls the next matvec phase's norm weights (and, for the first phase, nothing else) towards L2 while the current phase
+// streams: the weights of a step are far larger than L2, so without this every prologue would wait on HBM for 16 KB.
+__device__ __forceinline__ void bk_prefetch_norm(const bk_params &P, int p_from) {
+    for (int q = p_from; q < P.nphases; q++) {
+        const bk_phase &n = P.phases[q];
+        if (n.kind != BK_MATVEC || n.prologue != BK_PRO_NORM) continue;
+        if (n.norm_w) {
+            const int lines = P.hidden * 4 / 128;
+            for (int i = threadIdx.x; i < lines; i += BK_THREADS)
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const uint8_t *>(n.norm_w) + (size_t)i * 128));
+        }
+        return;
+    }
 }
 
 // ------------------------------------------------------------------ attention phase
 //
-// One 128-thread group = one (kv head, chunk of BK_ATT_CHUNK cache positions) task, all G query heads of the kv
-// head at once. q and the new k are rotated here (adjacent-pair RoPE), rounded to bf16 as the cache stores them;
-// the group whose chunk holds the new position appends k and v to the cache. Partial (max, sum, weighted V)
-// records go to `part`; the group that takes the last ticket of its kv head merges them in chunk order.
+// A CTA-task is (kv head, block of four chunks of BK_ATT_CHUNK cache positions); each of the CTA's four 128-thread
+// groups takes one chunk, all G query heads of the kv head at once. K and V rows go from global memory straight
+// into registers (a thread owns 64 bytes of one K row and 16 bytes of four V rows; the lines were pulled into L2
+// before the preceding grid barrier). q and the new k are rotated here (adjacent-pair RoPE) and rounded to bf16 as
+// the cache stores them; the thread that owns the new position builds its k / v piece from the q|k|v row instead of
+// loading it, and appends it to the cache. The four groups' partial (max, sum, weighted V) meet in shared memory;
+// one record per CTA goes to `part`, and the CTA that takes the last ticket of its kv head merges the records in
+// block order (bit-stable).
+#define BK_QS_STRIDE 36     // floats between the four 32-dim quarters of a q row: keeps the quarter reads off one bank
+
+struct bk_att_smem {        // one group's shared memory
+    float qs[BK_MAX_G][4 * BK_QS_STRIDE];
+    float sc[BK_MAX_G][BK_ATT_CHUNK];
+    float mred[4][BK_MAX_G], lred[4][BK_MAX_G];
+    float red4[4][BK_MAX_G][BK_ATT_D];
+    float gp_o[BK_MAX_G][BK_ATT_D];
+    float gp_m[BK_MAX_G], gp_l[BK_MAX_G];
+};
+static_assert(sizeof(bk_att_smem) <= BK_ATT_SUB_BYTES, "attention group smem");
+
+__device__ __forceinline__ int bk_att_nblk(int len) { return (len + 4 * BK_ATT_CHUNK - 1) / (4 * BK_ATT_CHUNK); }
+
+// Before the grid barrier in front of an attention phase: the CTA's first task's K and V lines, towards L2.
+__device__ __forceinline__ void bk_attention_prefetch(const bk_params &P, const bk_phase &ph) {
+    const long long pos = *P.pos;
+    if (pos < 0 || pos >= P.max_len) return;
+    const int nblk = bk_att_nblk((int)pos + 1);
+    const int ct = blockIdx.x;
+    if (ct >= P.hkv * nblk) return;
+    const int kv = ct / nblk, j = ct % nblk, sub = threadIdx.x >> 7, t = threadIdx.x & 127;
+    const int s0 = (4 * j + sub) * BK_ATT_CHUNK;
+    const int row = s0 + (t & 63) / 2;                           // two 128-byte lines per 256-byte row
+    if (row >= (int)pos) return;
+    const uint8_t *base = static_cast<const uint8_t *>(t < 64 ? ph.k_cache : ph.v_cache);
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(base + ((size_t)kv * P.max_len + row) * 256 + (t & 1) * 128));
+}
+
 template <int G>
-__device__ void bk_attention(const bk_params &P, const bk_phase &ph, uint8_t *sm, int sub, int t) {
+__device__ void bk_attention(const bk_params &P, const bk_phase &ph, uint8_t *work) {
     constexpr int HDR = (2 * G + 3) & ~3;
     constexpr int STRIDE = HDR + G * BK_ATT_D;
-    uint8_t *tiles = sm;                                                   // K rows 0..31, V rows 32..63
-    float(*qs)[BK_ATT_D] = reinterpret_cast<float(*)[BK_ATT_D]>(sm + 2 * BK_ATT_CHUNK * BK_ATT_ROW);
-    float(*sc)[BK_ATT_CHUNK] = reinterpret_cast<float(*)[BK_ATT_CHUNK]>(qs + G);
-    float(*mred)[G] = reinterpret_cast<float(*)[G]>(sc + G);
-    float(*lred)[G] = mred + 4;
-    volatile unsigned *last = reinterpret_cast<volatile unsigned *>(lred + 4);
-    static_assert(2 * BK_ATT_CHUNK * BK_ATT_ROW + G * BK_ATT_D * 4 + G * BK_ATT_CHUNK * 4 + 8 * G * 4 + 16 <= BK_ATT_SUB_BYTES, "attention group smem");
-    static_assert(8 * G * BK_ATT_D * 4 <= 2 * BK_ATT_CHUNK * BK_ATT_ROW, "reduction buffer must fit in the tiles");
+    const int tid = threadIdx.x, sub = tid >> 7, t = tid & 127, warp = t >> 5, lane = t & 31;
+    bk_att_smem *S = reinterpret_cast<bk_att_smem *>(work + (size_t)sub * BK_ATT_SUB_BYTES);
+    auto group = [&](int g4) { return reinterpret_cast<const bk_att_smem *>(work + (size_t)g4 * BK_ATT_SUB_BYTES); };
+    __shared__ unsigned s_last;
     const int bid = 1 + sub;
     const long long pos = *P.pos;
     if (pos < 0 || pos >= P.max_len) return;
     const int len = (int)pos + 1;
     const int nchunk = (len + BK_ATT_CHUNK - 1) / BK_ATT_CHUNK;
-    const int nchunk_max = (P.max_len + BK_ATT_CHUNK - 1) / BK_ATT_CHUNK;
-    const int ntask = P.hkv * nchunk;
-    const int warp = t >> 5, lane = t & 31;
+    const int nblk = bk_att_nblk(len), nblk_max = bk_att_nblk(P.max_len);
     __nv_bfloat16 *kc = static_cast<__nv_bfloat16 *>(ph.k_cache), *vc = static_cast<__nv_bfloat16 *>(ph.v_cache);
-    for (int task = blockIdx.x * 4 + sub; task < ntask; task += gridDim.x * 4) {
-        const int kv = task / nchunk, chunk = task % nchunk;
+    const float *cs = P.cos_t + (size_t)pos * (BK_ATT_D / 2), *sn = P.sin_t + (size_t)pos * (BK_ATT_D / 2);
+    const int p1 = t >> 2, qd = t & 3;          // scores: four threads per position, 32 dims each
+    const int dg = t & 15, pg = t >> 4;         // weighted V: 16 threads per row (8 dims each), 8 position groups
+    for (int ct = blockIdx.x; ct < P.hkv * nblk; ct += gridDim.x) {
+        const int kv = ct / nblk, j = ct % nblk;
+        const int chunk = 4 * j + sub;
         const int s0 = chunk * BK_ATT_CHUNK;
-        const int cnt = min(BK_ATT_CHUNK, len - s0);
-        const int frow = (int)pos - s0;                                   // the new position's row, if inside this chunk
-        const bool fresh = frow >= 0 && frow < BK_ATT_CHUNK;
-        const size_t base_row = (size_t)kv * P.max_len + s0;
-        const uint4 *kg = reinterpret_cast<const uint4 *>(kc + base_row * BK_ATT_D);
-        const uint4 *vg = reinterpret_cast<const uint4 *>(vc + base_row * BK_ATT_D);
+        const int cnt = chunk < nchunk ? min(BK_ATT_CHUNK, len - s0) : 0;
         uint4 kreg[4], vreg[4];
+        {   // K: this thread's 64 bytes of row p1; V: 16 bytes of rows pg, pg + 8, pg + 16, pg + 24
+            const int krow = s0 + p1;
+            const uint4 *kg = reinterpret_cast<const uint4 *>(kc + ((size_t)kv * P.max_len + krow) * BK_ATT_D) + qd * 4;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {                                     // 512 16-byte pieces per tile, 4 per thread
-            const int piece = i * 128 + t;
-            const bool ok = s0 + (piece >> 4) < (int)pos;                 // rows before the new position come from the cache
-            kreg[i] = ok ? kg[piece] : make_uint4(0, 0, 0, 0);
-            vreg[i] = ok ? vg[piece] : make_uint4(0, 0, 0, 0);
-        }
-        const float *cs = P.cos_t + (size_t)pos * (BK_ATT_D / 2), *sn = P.sin_t + (size_t)pos * (BK_ATT_D / 2);
-        for (int pi = t; pi < G * (BK_ATT_D / 2); pi += 128) {            // q: rotate, round to bf16, scale
-            const int h = pi >> 6, j = pi & 63;
-            const float2 ab = __ldcg(reinterpret_cast<const float2 *>(ph.qkv + (size_t)(kv * G + h) * BK_ATT_D) + j);
-            const float c = cs[j], s = sn[j];
-            const __nv_bfloat162 o = __floats2bfloat162_rn(ab.x * c - ab.y * s, ab.x * s + ab.y * c);
-            const float2 f = __bfloat1622float2(o);
-            qs[h][2 * j] = f.x * 0.08838834764831845f;
-            qs[h][2 * j + 1] = f.y * 0.08838834764831845f;
-        }
+            for (int c = 0; c < 4; ++c) kreg[c] = krow < (int)pos ? kg[c] : make_uint4(0, 0, 0, 0);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int piece = i * 128 + t, row = piece >> 4;
-            if (fresh && row == frow) continue;                           // written below from the new k, v
-            *reinterpret_cast<uint4 *>(tiles + row * BK_ATT_ROW + (piece & 15) * 16) = kreg[i];
-            *reinterpret_cast<uint4 *>(tiles + (BK_ATT_CHUNK + row) * BK_ATT_ROW + (piece & 15) * 16) = vreg[i];
-        }
-        if (fresh) {
-            const int j = t & 63;
-            __nv_bfloat162 o;
-            if (t < 64) {
-                const float2 ab = __ldcg(reinterpret_cast<const float2 *>(ph.qkv + (size_t)(P.hq + kv) * BK_ATT_D) + j);
-                const float c = cs[j], s = sn[j];
-                o = __floats2bfloat162_rn(ab.x * c - ab.y * s, ab.x * s + ab.y * c);
-                reinterpret_cast<__nv_bfloat162 *>(tiles + frow * BK_ATT_ROW)[j] = o;
-                reinterpret_cast<__nv_bfloat162 *>(kc + ((size_t)kv * P.max_len + pos) * BK_ATT_D)[j] = o;
-            } else {
-                const float2 ab = __ldcg(reinterpret_cast<const float2 *>(ph.qkv + (size_t)(P.hq + P.hkv + kv) * BK_ATT_D) + j);
-                o = __floats2bfloat162_rn(ab.x, ab.y);
-                reinterpret_cast<__nv_bfloat162 *>(tiles + (BK_ATT_CHUNK + frow) * BK_ATT_ROW)[j] = o;
-                reinterpret_cast<__nv_bfloat162 *>(vc + ((size_t)kv * P.max_len + pos) * BK_ATT_D)[j] = o;
+            for (int i = 0; i < 4; ++i) {
+                const int vrow = s0 + pg + 8 * i;
+                vreg[i] = vrow < (int)pos ? reinterpret_cast<const uint4 *>(vc + ((size_t)kv * P.max_len + vrow) * BK_ATT_D)[dg]
+                                          : make_uint4(0, 0, 0, 0);
+            }
+            if (krow == (int)pos) {             // the new key: rotate, round, keep, append
+                const float *src = ph.qkv + (size_t)(P.hq + kv) * BK_ATT_D;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int jp = qd * 16 + c * 4 + i;
+                        const float2 ab = __ldcg(reinterpret_cast<const float2 *>(src) + jp);
+                        const float cc = cs[jp], ss = sn[jp];
+                        const __nv_bfloat162 o = __floats2bfloat162_rn(ab.x * cc - ab.y * ss, ab.x * ss + ab.y * cc);
+                        w[i] = *reinterpret_cast<const uint32_t *>(&o);
+                    }
+                    kreg[c] = make_uint4(w[0], w[1], w[2], w[3]);
+                    reinterpret_cast<uint4 *>(kc + ((size_t)kv * P.max_len + pos) * BK_ATT_D)[qd * 4 + c] = kreg[c];
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                if (s0 + pg + 8 * i == (int)pos) {   // the new value: round, keep, append
+                    const float *src = ph.qkv + (size_t)(P.hq + P.hkv + kv) * BK_ATT_D + dg * 8;
+                    uint32_t w[4];
+#pragma unroll
+                    for (int q2 = 0; q2 < 4; ++q2) {
+                        const float2 ab = __ldcg(reinterpret_cast<const float2 *>(src) + q2);
+                        const __nv_bfloat162 o = __floats2bfloat162_rn(ab.x, ab.y);
+                        w[q2] = *reinterpret_cast<const uint32_t *>(&o);
+                    }
+                    vreg[i] = make_uint4(w[0], w[1], w[2], w[3]);
+                    reinterpret_cast<uint4 *>(vc + ((size_t)kv * P.max_len + pos) * BK_ATT_D)[dg] = vreg[i];
+                }
             }
         }
+        for (int pi = t; pi < G * (BK_ATT_D / 2); pi += 128) {            // q: rotate, round to bf16, scale
+            const int h = pi >> 6, jp = pi & 63;
+            const float2 ab = __ldcg(reinterpret_cast<const float2 *>(ph.qkv + (size_t)(kv * G + h) * BK_ATT_D) + jp);
+            const float c = cs[jp], s_ = sn[jp];
+            const __nv_bfloat162 o = __floats2bfloat162_rn(ab.x * c - ab.y * s_, ab.x * s_ + ab.y * c);
+            const float2 f = __bfloat1622float2(o);
+            const int d0 = 2 * jp;                                        // dims d0, d0 + 1: quarter d0 / 32
+            S->qs[h][(d0 >> 5) * BK_QS_STRIDE + (d0 & 31)] = f.x * 0.08838834764831845f;
+            S->qs[h][(d0 >> 5) * BK_QS_STRIDE + (d0 & 31) + 1] = f.y * 0.08838834764831845f;
+        }
         bk_subbar(bid);
-        // scores: four threads per position, 32 dims each
-        const int p1 = t >> 2, qd = t & 3;
         float s[G];
 #pragma unroll
         for (int h = 0; h < G; ++h) s[h] = 0.f;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
             float f[8];
-            bk_bf16x8(*reinterpret_cast<const uint4 *>(tiles + p1 * BK_ATT_ROW + (qd * 4 + c) * 16), f);
+            bk_bf16x8(kreg[c], f);
 #pragma unroll
-            for (int h = 0; h < G; ++h)
-#pragma unroll
-                for (int e = 0; e < 8; ++e) s[h] = fmaf(f[e], qs[h][(qd * 4 + c) * 8 + e], s[h]);
+            for (int h = 0; h < G; ++h) {
+                const float4 q0 = *reinterpret_cast<const float4 *>(&S->qs[h][qd * BK_QS_STRIDE + c * 8]);
+                const float4 q1 = *reinterpret_cast<const float4 *>(&S->qs[h][qd * BK_QS_STRIDE + c * 8 + 4]);
+                s[h] = fmaf(f[0], q0.x, s[h]); s[h] = fmaf(f[1], q0.y, s[h]); s[h] = fmaf(f[2], q0.z, s[h]); s[h] = fmaf(f[3], q0.w, s[h]);
+                s[h] = fmaf(f[4], q1.x, s[h]); s[h] = fmaf(f[5], q1.y, s[h]); s[h] = fmaf(f[6], q1.z, s[h]); s[h] = fmaf(f[7], q1.w, s[h]);
+            }
         }
 #pragma unroll
         for (int h = 0; h < G; ++h) {
@@ -392,117 +527,99 @@ __device__ void bk_attention(const bk_params &P, const bk_phase &ph, uint8_t *sm
             if (p1 >= cnt) s[h] = -INFINITY;
             float m = s[h];
             for (int o = 16; o >= 4; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-            if (lane == 0) mred[warp][h] = m;
+            if (lane == 0) S->mred[warp][h] = m;
         }
         bk_subbar(bid);
-        float *my = P.part + ((size_t)kv * nchunk_max + chunk) * STRIDE;
+        float Mh[G];
 #pragma unroll
         for (int h = 0; h < G; ++h) {
-            const float M = fmaxf(fmaxf(mred[0][h], mred[1][h]), fmaxf(mred[2][h], mred[3][h]));
-            float p = (p1 < cnt && qd == 0) ? __expf(s[h] - M) : 0.f;
-            if (qd == 0) sc[h][p1] = p;
+            Mh[h] = fmaxf(fmaxf(S->mred[0][h], S->mred[1][h]), fmaxf(S->mred[2][h], S->mred[3][h]));
+            float p = (p1 < cnt && qd == 0) ? __expf(s[h] - Mh[h]) : 0.f;
+            if (qd == 0) S->sc[h][p1] = p;
             for (int o = 16; o; o >>= 1) p += __shfl_xor_sync(0xffffffffu, p, o);
-            if (lane == 0) lred[warp][h] = p;
+            if (lane == 0) S->lred[warp][h] = p;
         }
         bk_subbar(bid);
-        if (t < G) {
-            my[t] = fmaxf(fmaxf(mred[0][t], mred[1][t]), fmaxf(mred[2][t], mred[3][t]));
-            my[G + t] = lred[0][t] + lred[1][t] + lred[2][t] + lred[3][t];
-        }
-        // weighted V: 16 threads per row (8 dims each), 8 position groups, 4 positions each
-        const int dg = t & 15, pg = t >> 4;
         float acc[G][8];
 #pragma unroll
         for (int h = 0; h < G; ++h)
 #pragma unroll
             for (int e = 0; e < 8; ++e) acc[h][e] = 0.f;
 #pragma unroll
-        for (int i = 0; i < BK_ATT_CHUNK / 8; ++i) {
+        for (int i = 0; i < 4; ++i) {
             const int p = pg + 8 * i;                                     // rows past cnt hold zeros and weight 0
             float f[8];
-            bk_bf16x8(*reinterpret_cast<const uint4 *>(tiles + (BK_ATT_CHUNK + p) * BK_ATT_ROW + dg * 16), f);
+            bk_bf16x8(vreg[i], f);
 #pragma unroll
             for (int h = 0; h < G; ++h) {
-                const float w = sc[h][p];
+                const float w = S->sc[h][p];
 #pragma unroll
                 for (int e = 0; e < 8; ++e) acc[h][e] = fmaf(w, f[e], acc[h][e]);
             }
         }
-        bk_subbar(bid);                                                   // tiles consumed: reuse them
-        float(*red)[G][BK_ATT_D] = reinterpret_cast<float(*)[G][BK_ATT_D]>(tiles);
 #pragma unroll
         for (int h = 0; h < G; ++h)
 #pragma unroll
-            for (int e = 0; e < 8; ++e) red[pg][h][dg * 8 + e] = acc[h][e];
+            for (int e = 0; e < 8; ++e) acc[h][e] += __shfl_xor_sync(0xffffffffu, acc[h][e], 16);   // the warp's two position groups
+        if (lane < 16) {
+#pragma unroll
+            for (int h = 0; h < G; ++h) {
+                *reinterpret_cast<float4 *>(&S->red4[warp][h][dg * 8]) = make_float4(acc[h][0], acc[h][1], acc[h][2], acc[h][3]);
+                *reinterpret_cast<float4 *>(&S->red4[warp][h][dg * 8 + 4]) = make_float4(acc[h][4], acc[h][5], acc[h][6], acc[h][7]);
+            }
+        }
         bk_subbar(bid);
 #pragma unroll
-        for (int h = 0; h < G; ++h) {
-            float o = 0.f;
+        for (int h = 0; h < G; ++h) S->gp_o[h][t] = (S->red4[0][h][t] + S->red4[1][h][t]) + (S->red4[2][h][t] + S->red4[3][h][t]);
+        if (t < G) {
+            S->gp_m[t] = fmaxf(fmaxf(S->mred[0][t], S->mred[1][t]), fmaxf(S->mred[2][t], S->mred[3][t]));
+            S->gp_l[t] = (S->lred[0][t] + S->lred[1][t]) + (S->lred[2][t] + S->lred[3][t]);
+        }
+        __syncthreads();
+        // the CTA's record: the four groups in chunk order
+        float *my = P.part + ((size_t)kv * nblk_max + j) * STRIDE;
+        {
+            const int h = tid >> 7, d = tid & 127;
+            if (h < G) {
+                float M = -INFINITY;
 #pragma unroll
-            for (int g8 = 0; g8 < 8; ++g8) o += red[g8][h][t];
-            my[HDR + h * BK_ATT_D + t] = o;
+                for (int g4 = 0; g4 < 4; ++g4) M = fmaxf(M, group(g4)->gp_m[h]);
+                float o = 0.f, l = 0.f;
+#pragma unroll
+                for (int g4 = 0; g4 < 4; ++g4) {
+                    const float mg = group(g4)->gp_m[h];
+                    const float w = mg == -INFINITY ? 0.f : __expf(mg - M);
+                    o = fmaf(w, group(g4)->gp_o[h][d], o);
+                    l = fmaf(w, group(g4)->gp_l[h], l);
+                }
+                my[HDR + h * BK_ATT_D + d] = o;
+                if (d == 0) { my[h] = M; my[G + h] = l; }
+            }
         }
         __threadfence();
-        bk_subbar(bid);
-        if (t == 0) *last = atomicAdd(&P.tickets[kv], 1u) == (unsigned)(nchunk - 1) ? 1u : 0u;
-        bk_subbar(bid);
-        if (*last) {
+        __syncthreads();
+        if (tid == 0) s_last = atomicAdd(&P.tickets[kv], 1u) == (unsigned)(nblk - 1) ? 1u : 0u;
+        __syncthreads();
+        if (s_last) {
             __threadfence();
-            // merge: warp w takes heads w, w+4, ...; chunks ascending (bit-stable), 16 loads in flight
-            const float *base = P.part + (size_t)kv * nchunk_max * STRIDE;
-            for (int h = warp; h < G; h += 4) {
-                constexpr int MAXR = 4;                                   // 128 chunks held in registers per pass
-                float mr[MAXR], lr[MAXR];
-#pragma unroll
-                for (int r = 0; r < MAXR; ++r) {
-                    const int s_ = lane + 32 * r;
-                    mr[r] = s_ < nchunk ? __ldcg(base + (size_t)s_ * STRIDE + h) : -INFINITY;
-                    lr[r] = s_ < nchunk ? __ldcg(base + (size_t)s_ * STRIDE + G + h) : 0.f;
+            const float *base = P.part + (size_t)kv * nblk_max * STRIDE;
+            const int h = tid >> 7, d = tid & 127;
+            if (h < G) {
+                float M = -INFINITY;
+                for (int b2 = 0; b2 < nblk; ++b2) M = fmaxf(M, __ldcg(base + (size_t)b2 * STRIDE + h));
+                float o = 0.f, l = 0.f;
+#pragma unroll 4
+                for (int b2 = 0; b2 < nblk; ++b2) {                       // ascending block order: bit-stable
+                    const float mb = __ldcg(base + (size_t)b2 * STRIDE + h);
+                    const float w = mb == -INFINITY ? 0.f : __expf(mb - M);
+                    o = fmaf(w, __ldcg(base + (size_t)b2 * STRIDE + HDR + h * BK_ATT_D + d), o);
+                    l = fmaf(w, __ldcg(base + (size_t)b2 * STRIDE + G + h), l);
                 }
-                float M = fmaxf(fmaxf(mr[0], mr[1]), fmaxf(mr[2], mr[3]));
-                for (int s_ = lane + 32 * MAXR; s_ < nchunk; s_ += 32) M = fmaxf(M, __ldcg(base + (size_t)s_ * STRIDE + h));
-                for (int o = 16; o; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
-                float L = 0.f;
-#pragma unroll
-                for (int r = 0; r < MAXR; ++r) {
-                    mr[r] = __expf(mr[r] - M);                            // now the chunk's weight
-                    L = fmaf(lr[r], mr[r], L);
-                }
-                for (int s_ = lane + 32 * MAXR; s_ < nchunk; s_ += 32)
-                    L += __ldcg(base + (size_t)s_ * STRIDE + G + h) * __expf(__ldcg(base + (size_t)s_ * STRIDE + h) - M);
-                for (int o = 16; o; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
-                float4 a4 = make_float4(0.f, 0.f, 0.f, 0.f);
-                const float *ob = base + HDR + h * BK_ATT_D + 4 * lane;
-                const int nreg = nchunk < 32 * MAXR ? nchunk : 32 * MAXR;
-#pragma unroll
-                for (int r = 0; r < MAXR; ++r) {
-                    for (int s0b = 32 * r; s0b < nreg && s0b < 32 * (r + 1); s0b += 16) {
-                        float4 v[16];
-#pragma unroll
-                        for (int u = 0; u < 16; ++u)
-                            v[u] = s0b + u < nreg ? __ldcg(reinterpret_cast<const float4 *>(ob + (size_t)(s0b + u) * STRIDE))
-                                                  : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-                        for (int u = 0; u < 16; ++u) {
-                            const float w = __shfl_sync(0xffffffffu, mr[r], (s0b + u) & 31);
-                            a4.x = fmaf(v[u].x, w, a4.x); a4.y = fmaf(v[u].y, w, a4.y);
-                            a4.z = fmaf(v[u].z, w, a4.z); a4.w = fmaf(v[u].w, w, a4.w);
-                        }
-                    }
-                }
-                for (int s_ = nreg; s_ < nchunk; ++s_) {                  // very long sequences: the plain walk
-                    const float4 v = __ldcg(reinterpret_cast<const float4 *>(ob + (size_t)s_ * STRIDE));
-                    const float w = __expf(__ldcg(base + (size_t)s_ * STRIDE + h) - M);
-                    a4.x = fmaf(v.x, w, a4.x); a4.y = fmaf(v.y, w, a4.y);
-                    a4.z = fmaf(v.z, w, a4.z); a4.w = fmaf(v.w, w, a4.w);
-                }
-                const float inv = L > 0.f ? 1.f / L : 0.f;
-                *reinterpret_cast<float4 *>(ph.att + (size_t)(kv * G + h) * BK_ATT_D + 4 * lane) =
-                    make_float4(a4.x * inv, a4.y * inv, a4.z * inv, a4.w * inv);
+                ph.att[(size_t)(kv * G + h) * BK_ATT_D + d] = l > 0.f ? o / l : 0.f;
             }
-            if (t == 0) P.tickets[kv] = 0;                                // ready for the next attention phase
+            if (tid == 0) P.tickets[kv] = 0;                              // ready for the next attention phase
         }
-        bk_subbar(bid);                                                   // the group's shared memory is free again
+        __syncthreads();                                                  // the groups' shared memory is free again
     }
 }
 
@@ -512,7 +629,8 @@ __device__ void bk_attention(const bk_params &P, const bk_phase &ph, uint8_t *sm
 #define BK_XOP_BYTES (BK_MAX_NSB * Q4K_XP_SB_BYTES)
 #define BK_RED_BYTES (BK_ROUND_TASKS * 16 * 4)
 #define BK_WORK_BYTES (4 * BK_ATT_SUB_BYTES > BK_XOP_BYTES + BK_RED_BYTES ? 4 * BK_ATT_SUB_BYTES : BK_XOP_BYTES + BK_RED_BYTES)
-#define BK_SMEM_BYTES (BK_RING_BYTES + BK_WORK_BYTES + Q4K_XP_ZERO_BYTES + BK_WARPS * BK_STAGES * 8 + 64 * 4 + 128)
+#define BK_PHASE_BYTES ((sizeof(bk_phase) + 15) / 16 * 16)
+#define BK_SMEM_BYTES (BK_RING_BYTES + BK_WORK_BYTES + Q4K_XP_ZERO_BYTES + BK_WARPS * BK_STAGES * 8 + 64 * 4 + BK_MAX_PHASES * 32 + 2 * BK_PHASE_BYTES + 128)
 
 __global__ void __launch_bounds__(BK_THREADS, 1) jl_block_kernel(const __grid_constant__ bk_params P) {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -525,7 +643,31 @@ __global__ void __launch_bounds__(BK_THREADS, 1) jl_block_kernel(const __grid_co
     uint8_t *zero = work + BK_WORK_BYTES;
     uint64_t *bars = reinterpret_cast<uint64_t *>(zero + Q4K_XP_ZERO_BYTES) + warp * BK_STAGES;
     float *misc = reinterpret_cast<float *>(zero + Q4K_XP_ZERO_BYTES + BK_WARPS * BK_STAGES * 8);   // 64 floats
+    bk_pinfo *pinfo = reinterpret_cast<bk_pinfo *>(misc + 64);
+    // the current and the next phase's full descriptors, copied from global memory one phase ahead of their use
+    uint8_t *phase_sm = reinterpret_cast<uint8_t *>(pinfo + BK_MAX_PHASES);
+    auto stage_phase = [&](int q) {
+        if (q < P.nphases && tid < (int)(BK_PHASE_BYTES / 16))
+            reinterpret_cast<uint4 *>(phase_sm + (size_t)(q & 1) * BK_PHASE_BYTES)[tid] = __ldg(reinterpret_cast<const uint4 *>(P.phases + q) + tid);
+    };
+    stage_phase(0);
     const uint64_t limit_ns = jl_wait_limit_ns(P.status);
+    const int nphases = P.nphases;
+    const CUtensorMap *maps = P.maps;
+
+    for (int i = tid; i < nphases; i += BK_THREADS) {
+        const bk_phase &q = P.phases[i];
+        bk_pinfo f;
+        f.kind = q.kind; f.map = q.map; f.nsb = q.nsb; f.epi = q.epilogue; f.up_row0 = q.up_row0;
+        f.rg0 = f.rg1 = 0; f.rpr = 1;
+        if (q.kind == BK_MATVEC) {
+            const int nrg = bk_phase_nrg(q);
+            f.rg0 = (int)((long long)blockIdx.x * nrg / gridDim.x);
+            f.rg1 = (int)((long long)(blockIdx.x + 1) * nrg / gridDim.x);
+            f.rpr = bk_rounds_rgs(q.nsb);
+        }
+        pinfo[i] = f;
+    }
 
     if (lane == 0) {
 #pragma unroll
@@ -533,17 +675,16 @@ __global__ void __launch_bounds__(BK_THREADS, 1) jl_block_kernel(const __grid_co
         mbar_init_fence();
     }
     if (tid < Q4K_XP_ZERO_BYTES / 4) reinterpret_cast<uint32_t *>(zero)[tid] = 0u;
-    __syncwarp();
+    __syncthreads();                    // the phase table is complete
     // The ring runs ahead of everything else: the first BK_STAGES tiles of this warp are requested now.
     bk_cursor fc;                       // fetch side
     uint32_t fetched = 0, consumed = 0;
-    bk_cursor_seek(fc, P, 0, warp);
-    for (int s = 0; s < BK_STAGES && fc.p < P.nphases; s++) {
-        if (lane == 0) bk_fetch(fc, P, smem_u32(tiles + s * BK_TILE), smem_u32(bars + s));
-        bk_cursor_next(fc, P, warp);
+    bk_cursor_seek(fc, pinfo, nphases, 0, warp);
+    for (int s = 0; s < BK_STAGES && fc.p < nphases; s++) {
+        if (lane == 0) bk_fetch(fc, pinfo, maps, smem_u32(tiles + s * BK_TILE), smem_u32(bars + s));
+        bk_cursor_next(fc, pinfo, nphases, warp);
         fetched++;
     }
-    __syncthreads();
 
     int barriers_done = 0;
     const unsigned seq_start = P.world > 1 ? bk_ld_acquire_gpu(P.seq) : 0u;     // exchanges finished by earlier launches
@@ -552,31 +693,60 @@ __global__ void __launch_bounds__(BK_THREADS, 1) jl_block_kernel(const __grid_co
     float best_val = -INFINITY;
     int best_idx = 0x7fffffff;
 
+    // per-phase time stamps (phase start, prologue done, work done, barrier passed) of the first and last CTA
+    const int tr_cta = blockIdx.x == 0 ? 0 : (blockIdx.x == gridDim.x - 1 ? 1 : -1);
+#define BK_TRACE(slot)                                                                      \
+    do {                                                                                    \
+        if (P.trace && tr_cta >= 0 && tid == 0) P.trace[((size_t)tr_cta * P.nphases + p) * 4 + (slot)] = jl_gtime_ns(); \
+    } while (0)
+
+#ifdef BK_FINE_TRACE
+    // experimental builds only: clock64 spent between marks 0..6 of the consume loop, first CTA's first warp, per phase
+    long long ft_acc[7], ft_last = 0;
+#define BK_FT(i) do { const long long c_ = clock64(); if ((i) > 0) ft_acc[i] += c_ - ft_last; ft_last = c_; } while (0)
+#else
+#define BK_FT(i) do { } while (0)
+#endif
     for (int p = 0; p < P.nphases && alive; p++) {
-        const bk_phase &ph = P.phases[p];
+        const bk_phase &ph = *reinterpret_cast<const bk_phase *>(phase_sm + (size_t)(p & 1) * BK_PHASE_BYTES);
+        stage_phase(p + 1);       // lands long before the next phase starts (at least one __syncthreads away)
+#ifdef BK_FINE_TRACE
+        for (int i = 0; i < 7; i++) ft_acc[i] = 0;
+#endif
+        BK_TRACE(0);
+        if ((int)blockIdx.x == (p + 1) % (int)gridDim.x) bk_prefetch_norm(P, p + 1);
         if (ph.kind == BK_MATVEC) {
+#ifdef BK_FINE_TRACE
+            long long pt[5] = {0, 0, 0, 0, 0};
+            bk_prologue(P, ph, xop, misc, pt);
+            if (P.trace && blockIdx.x == 0 && tid == 0)
+                for (int i = 1; i < 5; i++) P.trace[(size_t)2 * P.nphases * 4 + (size_t)P.nphases * 8 + (size_t)p * 4 + i - 1] = (unsigned long long)(pt[i] - pt[i - 1]);
+#else
             bk_prologue(P, ph, xop, misc);
-            const int nrg = bk_phase_nrg(ph), nsb = ph.nsb;
-            const int rg0 = (int)((long long)blockIdx.x * nrg / gridDim.x), rg1 = (int)((long long)(blockIdx.x + 1) * nrg / gridDim.x);
-            const int rpr = bk_rounds_rgs(nsb);
+#endif
+            BK_TRACE(1);
+            const int nsb = pinfo[p].nsb, rg0 = pinfo[p].rg0, rg1 = pinfo[p].rg1, rpr = pinfo[p].rpr;
             for (int rbase = rg0; rbase < rg1 && alive; rbase += rpr) {
                 const int nr = min(rpr, rg1 - rbase), ntask = nr * nsb;
                 for (int tk = warp; tk < ntask; tk += BK_WARPS) {
                     const int sb = tk % nsb;
                     const uint32_t s = consumed % BK_STAGES, parity = (consumed / BK_STAGES) & 1u;
+                    BK_FT(0);
                     if (!__all_sync(0xffffffffu, bk_mbar_wait(smem_u32(bars + s), parity, limit_ns))) {
                         if (lane == 0) { atomicExch(P.status, 1); atomicExch(P.abort_word, 1); }
                         alive = false;
                         break;
                     }
+                    BK_FT(1);
                     const q4k_lane_tile w = q4k_lane_load(tiles + s * BK_TILE, g, t);
                     consumed++;
                     __syncwarp();        // every lane holds its share: the stage may be refilled
-                    if (fc.p < P.nphases) {
-                        if (lane == 0) bk_fetch(fc, P, smem_u32(tiles + s * BK_TILE), smem_u32(bars + s));
-                        bk_cursor_next(fc, P, warp);
+                    if (fc.p < nphases) {
+                        if (lane == 0) bk_fetch(fc, pinfo, maps, smem_u32(tiles + s * BK_TILE), smem_u32(bars + s));
+                        bk_cursor_next(fc, pinfo, nphases, warp);
                         fetched++;
                     }
+                    BK_FT(2);
                     float accA = 0.f, accB = 0.f;
                     q4k_dot_task(w, xop + (size_t)sb * Q4K_XP_SB_BYTES, zero, g, t, accA, accB);
                     accA += __shfl_xor_sync(0xffffffffu, accA, 1);
@@ -587,8 +757,11 @@ __global__ void __launch_bounds__(BK_THREADS, 1) jl_block_kernel(const __grid_co
                         red[tk * 16 + g] = accA;
                         red[tk * 16 + g + 8] = accB;
                     }
+                    BK_FT(3);
                 }
+                BK_FT(4);
                 alive = __syncthreads_and(alive ? 1 : 0) != 0;
+                BK_FT(5);
                 if (!alive) break;
                 // the round's row groups: super-blocks in ascending order (run-to-run bit-stable)
                 if (ph.epilogue == BK_EPI_GATE2) {
@@ -620,6 +793,7 @@ __global__ void __launch_bounds__(BK_THREADS, 1) jl_block_kernel(const __grid_co
                     }
                 }
                 __syncthreads();         // the round's partials are consumed
+                BK_FT(6);
             }
             if (alive && ph.epilogue == BK_EPI_ARGMAX) {
                 // the CTA's candidate: largest value, lowest row on a tie
@@ -639,11 +813,10 @@ __global__ void __launch_bounds__(BK_THREADS, 1) jl_block_kernel(const __grid_co
                 }
             }
         } else if (ph.kind == BK_ATTN) {
-            const int G = P.hq / P.hkv, sub = tid >> 7, t128 = tid & 127;
-            uint8_t *asm_ = work + (size_t)sub * BK_ATT_SUB_BYTES;
-            if (G == 4) bk_attention<4>(P, ph, asm_, sub, t128);
-            else if (G == 2) bk_attention<2>(P, ph, asm_, sub, t128);
-            else bk_attention<1>(P, ph, asm_, sub, t128);
+            const int G = P.hq / P.hkv;
+            if (G == 4) bk_attention<4>(P, ph, work);
+            else if (G == 2) bk_attention<2>(P, ph, work);
+            else bk_attention<1>(P, ph, work);
         } else {   // BK_FINAL: CTA 0 picks the winner among the CTAs' candidates
             if (blockIdx.x == 0 && warp == 0) {
                 float bv = -INFINITY; int bi = 0x7fffffff;
@@ -663,7 +836,14 @@ __global__ void __launch_bounds__(BK_THREADS, 1) jl_block_kernel(const __grid_co
                 }
             }
         }
+        BK_TRACE(2);
+#ifdef BK_FINE_TRACE
+        if (P.trace && blockIdx.x == 0 && tid == 0)
+            for (int i = 1; i < 7; i++) P.trace[(size_t)2 * P.nphases * 4 + (size_t)p * 8 + i] = (unsigned long long)ft_acc[i];
+#endif
         if (!alive || p + 1 >= P.nphases) break;
+        if (pinfo[p + 1].kind == BK_ATTN)
+            bk_attention_prefetch(P, *reinterpret_cast<const bk_phase *>(phase_sm + (size_t)((p + 1) & 1) * BK_PHASE_BYTES));
         const bool ex = ph.kind == BK_MATVEC && ph.exchange && P.world > 1;
         alive = bk_grid_sync(P, barriers_done, limit_ns, ex);
         if (alive && ex) {
@@ -677,7 +857,10 @@ __global__ void __launch_bounds__(BK_THREADS, 1) jl_block_kernel(const __grid_co
             __syncthreads();
             alive = s_ok2 != 0;
         }
+        BK_TRACE(3);
     }
+#undef BK_TRACE
+#undef BK_FT
     // The launch's exchanges are accounted for (also after an abort, so that the ranks' counters stay in step).
     if (P.world > 1 && blockIdx.x == 0 && tid == 0) *P.seq = seq_start + (unsigned)P.nexchange;
     // Copies still in flight into this CTA's shared memory must land before the CTA may exit.
@@ -698,6 +881,7 @@ struct jl_layers {
     bk_phase *phases_dev;
     std::vector<bk_phase> phases;
     float *logits;
+    unsigned long long *trace;   // [2][nphases][4]
     bk_params P;
     bool attached;
 };
@@ -735,6 +919,7 @@ JL_EXPORT int jl_layers_prep(jl_ctx *ctx, const jl_layers_desc *d, jl_layers **o
             return jl_set_err(ctx, JL_DECLINED, "block %d: every projection must be a resident Q4_K matrix of the block's shape", l);
     }
     if (d->head && !okw(d->head, V, H)) return jl_set_err(ctx, JL_DECLINED, "head: not a resident Q4_K matrix %d x %d", V, H);
+    if (5 * L + 2 > BK_MAX_PHASES) return jl_set_err(ctx, JL_DECLINED, "block kernel: more than %d blocks", (BK_MAX_PHASES - 2) / 5);
 
     int occ = 0;
     JL_CUDA(ctx, cudaFuncSetAttribute(jl_block_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BK_SMEM_BYTES));
@@ -746,7 +931,7 @@ JL_EXPORT int jl_layers_prep(jl_ctx *ctx, const jl_layers_desc *d, jl_layers **o
     S->rank = rank; S->world = world; S->grid = ctx->sm_count; S->attached = world == 1; S->buf = nullptr; S->slot = nullptr;
     const int nmaps = 4 * L + (d->head ? 1 : 0);
     const int nph = 5 * L + (d->head ? 2 : 0);
-    const int nchunk_max = (d->max_len + BK_ATT_CHUNK - 1) / BK_ATT_CHUNK;
+    const int nchunk_max = (d->max_len + 4 * BK_ATT_CHUNK - 1) / (4 * BK_ATT_CHUNK);   // records: one per block of four chunks
     const size_t stride = (size_t)(((2 * G + 3) & ~3) + G * BK_ATT_D);
     size_t off = 0;
     auto take = [&](size_t n) { size_t o = off; off += bk_al(n); return o; };
@@ -755,6 +940,7 @@ JL_EXPORT int jl_layers_prep(jl_ctx *ctx, const jl_layers_desc *d, jl_layers **o
     const size_t o_att = take((size_t)hq * BK_ATT_D * 4), o_a = take((size_t)F * 4), o_logits = take((size_t)(V > 0 ? V : 1) * 4);
     const size_t o_part = take((size_t)hkv * nchunk_max * stride * 4), o_tick = take((size_t)hkv * 4);
     const size_t o_cv = take((size_t)S->grid * 4), o_ci = take((size_t)S->grid * 4), o_bar = take(16), o_seq = take(16);
+    const size_t o_trace = take((size_t)2 * nph * 4 * 8 + (size_t)nph * 12 * 8);
     S->slot_bytes = bk_slot_bytes(world, H);
     cudaError_t e = cudaMalloc(&S->buf, off);
     if (e == cudaSuccess) e = cudaMalloc(&S->slot, S->slot_bytes);
@@ -773,6 +959,7 @@ JL_EXPORT int jl_layers_prep(jl_ctx *ctx, const jl_layers_desc *d, jl_layers **o
     float *planesO = (float *)S->slot, *planesD = (float *)(S->slot + bk_al((size_t)world * H * 4));
     unsigned *flags = (unsigned *)(S->slot + 2 * bk_al((size_t)world * H * 4));
     S->logits = (float *)(B + o_logits);
+    S->trace = (unsigned long long *)(B + o_trace);
     S->phases_dev = (bk_phase *)(B + o_ph);
 
     std::vector<CUtensorMap> maps(nmaps);
@@ -909,10 +1096,8 @@ JL_EXPORT int jl_tp_attach(jl_ctx *ctx, jl_layers *S, void *const *peer_slots, i
 // norm, the vocabulary projection and the greedy argmax. *tok_dev, *pos_dev are read on the device, so a captured
 // graph can be replayed; with `advance` the kernel itself stores the next token into *tok_dev and increments
 // *pos_dev. logits_out_dev / next_tok_dev may be NULL. Asynchronous on `stream`; poll jl_status_poll afterwards.
-JL_EXPORT int jl_layers_run(jl_ctx *ctx, jl_layers *S, long long *tok_dev, long long *pos_dev, float *logits_out_dev,
-                            long long *next_tok_dev, int advance, void *stream) {
-    if (!ctx || !S || !tok_dev || !pos_dev) return JL_EINVAL;
-    std::lock_guard<std::mutex> lk(ctx->mu);
+static int layers_run_locked(jl_ctx *ctx, jl_layers *S, long long *tok_dev, long long *pos_dev, float *logits_out_dev,
+                             long long *next_tok_dev, int advance, void *stream, bool trace) {
     if (ctx->unhealthy) return jl_set_err(ctx, JL_ECUDA, "context is unhealthy after an earlier CUDA error");
     if (!S->attached) return jl_set_err(ctx, JL_ECOMM, "tensor-parallel blocks: jl_tp_attach has not been called");
     if (!S->P.emb) return jl_set_err(ctx, JL_EINVAL, "jl_layers_run needs the embedding table given at jl_layers_prep");
@@ -920,6 +1105,7 @@ JL_EXPORT int jl_layers_run(jl_ctx *ctx, jl_layers *S, long long *tok_dev, long 
     cudaStream_t s = (cudaStream_t)stream;
     bk_params P = S->P;
     P.tok = tok_dev; P.pos = pos_dev; P.advance = advance; P.next_tok = next_tok_dev;
+    P.trace = trace ? S->trace : nullptr;
     JL_CUDA(ctx, cudaMemsetAsync(P.bar, 0, 8, s));           // barrier counter and abort word
     cudaLaunchAttribute at[1];
     at[0].id = cudaLaunchAttributeCooperative;
@@ -934,3 +1120,33 @@ JL_EXPORT int jl_layers_run(jl_ctx *ctx, jl_layers *S, long long *tok_dev, long 
     ctx->st.served++;
     return JL_OK;
 }
+
+JL_EXPORT int jl_layers_run(jl_ctx *ctx, jl_layers *S, long long *tok_dev, long long *pos_dev, float *logits_out_dev,
+                            long long *next_tok_dev, int advance, void *stream) {
+    if (!ctx || !S || !tok_dev || !pos_dev) return JL_EINVAL;
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    return layers_run_locked(ctx, S, tok_dev, pos_dev, logits_out_dev, next_tok_dev, advance, stream, false);
+}
+
+// Per-phase nanoseconds of one step (the reference keeps per-op ns counters, model.OpProfile,
+// engine/model/forward.go:22-75): runs ONE step like jl_layers_run (no advance), waits for it, and returns for every
+// phase four global-timer stamps of the grid's first CTA and of its last: phase start, prologue done, work done,
+// barrier passed -- stamps_out[2][n_phases][4]. Phases: per block qkv, attention, o, gate|up, down; then head, argmax.
+JL_EXPORT int jl_layers_profile(jl_ctx *ctx, jl_layers *S, long long *tok_dev, long long *pos_dev, void *stream,
+                                unsigned long long *stamps_out, int n_phases) {
+    if (!ctx || !S || !tok_dev || !pos_dev || !stamps_out) return JL_EINVAL;
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    if (n_phases != S->P.nphases) return jl_set_err(ctx, JL_EINVAL, "this stack has %d phases", S->P.nphases);
+    size_t bytes = (size_t)2 * n_phases * 4 * 8;
+#ifdef BK_FINE_TRACE
+    bytes += (size_t)n_phases * 12 * 8;   // experimental builds: the consume loop's and the prologue's clock counts follow the stamps
+#endif
+    JL_CUDA(ctx, cudaSetDevice(ctx->device));
+    JL_CUDA(ctx, cudaMemsetAsync(S->trace, 0, bytes, (cudaStream_t)stream));
+    int rc = layers_run_locked(ctx, S, tok_dev, pos_dev, nullptr, nullptr, 0, stream, true);
+    if (rc) return rc;
+    JL_CUDA(ctx, cudaMemcpyAsync(stamps_out, S->trace, bytes, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    JL_CUDA(ctx, cudaStreamSynchronize((cudaStream_t)stream));
+    return JL_OK;
+}
+JL_EXPORT int jl_layers_phases(jl_layers *S) { return S ? S->P.nphases : 0; }

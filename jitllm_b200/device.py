@@ -95,6 +95,14 @@ class Layers:
         self.dev._check(self.dev.lib.jl_layers_run(self.dev.ctx, self.handle, _ptr(tok), _ptr(pos), _ptr(logits),
                                                    _ptr(next_tok), int(advance), stream))
 
+    def Profile(self, tok, pos, stream: int = 0):
+        """One step with per-phase time stamps: uint64 array [2 (first / last CTA)][phases][4 (start, prologue done,
+        work done, barrier passed)] in nanoseconds of the GPU's global timer."""
+        n = self.dev.lib.jl_layers_phases(self.handle)
+        out = np.zeros((2, n, 4), np.uint64)
+        self.dev._check(self.dev.lib.jl_layers_profile(self.dev.ctx, self.handle, _ptr(tok), _ptr(pos), stream, _ptr(out), n))
+        return out
+
     def Slot(self):
         """(device pointer, bytes) of this rank's tensor-parallel slot buffer."""
         p, n = C.c_void_p(), C.c_size_t()
