@@ -8,7 +8,7 @@
 // Q4_K weights each). Launched one by one each pays a launch, a ramp and a tail, and HBM idles
 // between them. Here one cooperative launch of one CTA per SM walks a list of PHASES,
 //     qkv -> attention -> o -> gate|up -> down      (per block),   head,   argmax
-// separated by grid barriers. What makes it fast:
+// handing each phase's output vector to the next through memory. What makes it fast:
 //   * every warp owns a TMA ring of weight tiles (16 rows x one 144-byte super-block per copy) that
 //     runs ACROSS phases: weights do not depend on activations, so while a CTA waits at a barrier
 //     its warps' rings are already filling with the next phase's tiles and HBM never idles;
@@ -17,11 +17,17 @@
 //     16 KB row: cheaper than a phase of its own), SiLU(gate)*up in the gate|up epilogue (a tile
 //     is 8 gate rows + 8 matching up rows: the reference's Gate2, jit/gpu/kernels/matvec.go:283-290),
 //     RoPE and the KV-cache append inside the attention phase, argmax after the head;
-//   * tensor parallel ranks exchange the row-parallel partial sums themselves: the o and down
-//     epilogues store their [hidden] partial row into every rank's slot buffer over NVLink with
-//     plain peer stores, a flag per rank carries a sequence number, and the next prologue sums the
-//     slots in rank order (bit-stable). No collective library call sits inside a token.
-// Every wait (ring slot, grid barrier, peer flag) is bounded by the GPU's global timer; when one
+//   * no grid barrier between phases: every vector that crosses a phase boundary (q|k|v, the attention output,
+//     the o and down partial sums, SiLU*up) is stored as (value, sequence number) pairs in single 8-byte
+//     stores, and a consumer simply re-reads a pair until it carries the sequence number of the producing
+//     phase. The handoff costs one trip through L2 instead of a fence, an atomic and a poll, and a CTA waits
+//     only for the data it reads. (A phase's prologue reads the WHOLE vector, so it still orders a CTA after
+//     every producer, which is what makes the single-buffered reuse of the vectors safe.)
+//   * tensor parallel ranks exchange the row-parallel partial sums the same way: the o and down epilogues
+//     store their pairs into every rank's slot buffer over NVLink with plain peer stores, and the next
+//     prologue sums the ranks' planes in rank order (bit-stable). No collective call, no system-wide fence.
+// Every wait (ring slot, data pair, the one grid barrier in front of the argmax) is bounded by the GPU's
+// global timer; when one
 // runs out the kernel records a code, raises an abort word that every other wait polls, waits
 // (bounded) for its own copies in flight and returns.
 #include "jl_internal.cuh"
@@ -40,11 +46,13 @@
 #define BK_ATT_D 128
 #define BK_MAX_G 4                   // query heads per kv head
 #define BK_MAX_WORLD 8
-#define BK_ATT_SUB_BYTES 13312       // shared memory of one 128-thread attention group
+#define BK_ATT_SUB_BYTES 13824       // shared memory of one 128-thread attention group
 
 enum { BK_MATVEC = 0, BK_ATTN = 1, BK_FINAL = 2 };
 enum { BK_PRO_NORM = 0, BK_PRO_PLAIN = 1 };
 enum { BK_EPI_STORE = 0, BK_EPI_GATE2 = 1, BK_EPI_ARGMAX = 2 };
+
+typedef uint2 bk_ll;    // {float bits, sequence number of the phase that produced it}: one 8-byte store, atomic
 
 struct alignas(16) bk_phase {
     int kind;
@@ -54,20 +62,20 @@ struct alignas(16) bk_phase {
     int nsb;            // super-blocks per row
     int prologue, epilogue;
     int up_row0;        // GATE2: first row of the up half inside the map
-    int exchange;       // outputs go to every rank's slot buffer, then the ranks meet
+    int exchange;       // outputs go to every rank's slot buffer
     int nplanes;        // NORM: partial planes added to the residual row (0 = none)
-    int from_emb;       // NORM: the residual row is the embedding of *tok
-    const float *xsrc;  // NORM: residual row in
-    float *xdst;        // NORM: residual row out (written by CTA 0)
-    const float *planes;   // NORM: [nplanes][hidden]
+    int from_emb;       // NORM: the residual row starts as the embedding of *tok
+    const bk_ll *planes;   // NORM: [nplanes][hidden]
     const float *norm_w;   // NORM: [hidden]
-    const float *vsrc;     // PLAIN: the activation row
-    float *out;            // STORE / GATE2 / ARGMAX: output vector
-    float *peer_out[BK_MAX_WORLD];   // exchange: this rank's plane inside every rank's slot buffer
+    const bk_ll *vsrc;     // PLAIN: the activation row
+    bk_ll *out;            // STORE / GATE2: output vector
+    float *out_f32;        // ARGMAX: the logits, plain f32
+    bk_ll *peer_out[BK_MAX_WORLD];   // exchange: this rank's plane inside every rank's slot buffer
     // ---- attention
-    const float *qkv;      // [(hq + 2 hkv) * 128] f32
-    float *att;            // [hq * 128] f32
+    const bk_ll *qkv;      // [(hq + 2 hkv) * 128]
+    bk_ll *att;            // [hq * 128]
     void *k_cache, *v_cache;   // bf16 [hkv][max_len][128]
+    unsigned *tickets;     // [hkv], zero at launch
 };
 
 struct bk_params {
@@ -82,16 +90,12 @@ struct bk_params {
     int advance;                         // FINAL: *tok = argmax, *pos += 1
     long long *next_tok;                 // FINAL: argmax goes here too (may be NULL)
     float *part;                         // attention partials
-    unsigned *tickets;                   // [hkv]
     float *cand_val; int *cand_idx;      // [grid] per-CTA argmax candidates
     unsigned *bar;                       // grid barrier counter, zero at launch
     int *abort_word;                     // zero at launch
     int *status;                         // [0] code, [1] limit in microseconds
     int rank, world;
-    unsigned *flags;                     // local [world]: sequence number of the last exchange rank r finished
-    unsigned *peer_flags[BK_MAX_WORLD];  // the same array on every rank
-    unsigned *seq;                       // local: exchanges completed by earlier launches
-    int nexchange;                       // exchanges per launch
+    unsigned *seq;                       // sequence numbers used up by earlier launches (nphases per launch)
     unsigned long long *trace;           // optional [2][nphases][4] global-timer stamps of the first and the last CTA
 };
 
@@ -101,14 +105,6 @@ __device__ __forceinline__ unsigned bk_ld_acquire_gpu(const unsigned *p) {
     unsigned v;
     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
-}
-__device__ __forceinline__ unsigned bk_ld_acquire_sys(const unsigned *p) {
-    unsigned v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ void bk_st_release_sys(unsigned *p, unsigned v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 __device__ __forceinline__ int bk_ld_volatile(const int *p) {
     int v;
@@ -127,6 +123,82 @@ __device__ __forceinline__ void bk_bf16x8(const uint4 &v, float *f) {
     }
 }
 
+__device__ __forceinline__ uint4 bk_ld_vol16(const void *p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void bk_ll_store(bk_ll *p, float v, unsigned seq) {
+    asm volatile("st.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(seq) : "memory");
+}
+struct bk_params;
+__device__ __forceinline__ bool bk_ll_giveup(const bk_params &P, uint64_t t0, uint64_t limit_ns, int code);
+// Two / four consecutive values of a vector another CTA (or another GPU) produces in phase `seq`: re-read until
+// every pair carries `seq`. p is 16- / 32-byte aligned. False when the wait was given up (abort or timeout).
+__device__ __forceinline__ bool bk_ll_read2(const bk_ll *p, unsigned seq, float2 &out, const bk_params &P, uint64_t limit_ns, int code) {
+    uint4 a = bk_ld_vol16(p);
+    if (a.y != seq || a.w != seq) {
+        const uint64_t t0 = jl_gtime_ns();
+        for (uint32_t i = 0;; i++) {
+            a = bk_ld_vol16(p);
+            if (a.y == seq && a.w == seq) break;
+            if ((i & 7u) == 7u && bk_ll_giveup(P, t0, limit_ns, code)) return false;
+        }
+    }
+    out = make_float2(__uint_as_float(a.x), __uint_as_float(a.z));
+    return true;
+}
+__device__ __forceinline__ bool bk_ll_read4(const bk_ll *p, unsigned seq, float4 &out, const bk_params &P, uint64_t limit_ns, int code) {
+    uint4 a = bk_ld_vol16(p), b = bk_ld_vol16(p + 2);
+    if (a.y != seq || a.w != seq || b.y != seq || b.w != seq) {
+        const uint64_t t0 = jl_gtime_ns();
+        for (uint32_t i = 0;; i++) {
+            a = bk_ld_vol16(p); b = bk_ld_vol16(p + 2);
+            if (a.y == seq && a.w == seq && b.y == seq && b.w == seq) break;
+            if ((i & 7u) == 7u && bk_ll_giveup(P, t0, limit_ns, code)) return false;
+        }
+    }
+    out = make_float4(__uint_as_float(a.x), __uint_as_float(a.z), __uint_as_float(b.x), __uint_as_float(b.z));
+    return true;
+}
+
+// N reads at once: every load is issued before the first flag is looked at, so a batch costs one trip to L2 instead of
+// N. A null pointer skips its slot (the output is zero).
+template <int N>
+__device__ __forceinline__ bool bk_ll_read4_n(const bk_ll *const (&p)[N], unsigned seq, float4 (&out)[N], const bk_params &P,
+                                              uint64_t limit_ns, int code) {
+    uint4 a[N], b[N];
+#pragma unroll
+    for (int i = 0; i < N; i++) {
+        a[i] = b[i] = make_uint4(0u, seq, 0u, seq);
+        if (p[i]) { a[i] = bk_ld_vol16(p[i]); b[i] = bk_ld_vol16(p[i] + 2); }
+    }
+    bool ok = true;
+#pragma unroll
+    for (int i = 0; i < N; i++) {
+        if (a[i].y != seq || a[i].w != seq || b[i].y != seq || b[i].w != seq) ok = bk_ll_read4(p[i], seq, out[i], P, limit_ns, code) && ok;
+        else out[i] = make_float4(__uint_as_float(a[i].x), __uint_as_float(a[i].z), __uint_as_float(b[i].x), __uint_as_float(b[i].z));
+    }
+    return ok;
+}
+template <int N>
+__device__ __forceinline__ bool bk_ll_read2_n(const bk_ll *const (&p)[N], unsigned seq, float2 (&out)[N], const bk_params &P,
+                                              uint64_t limit_ns, int code) {
+    uint4 a[N];
+#pragma unroll
+    for (int i = 0; i < N; i++) {
+        a[i] = make_uint4(0u, seq, 0u, seq);
+        if (p[i]) a[i] = bk_ld_vol16(p[i]);
+    }
+    bool ok = true;
+#pragma unroll
+    for (int i = 0; i < N; i++) {
+        if (a[i].y != seq || a[i].w != seq) ok = bk_ll_read2(p[i], seq, out[i], P, limit_ns, code) && ok;
+        else out[i] = make_float2(__uint_as_float(a[i].x), __uint_as_float(a[i].z));
+    }
+    return ok;
+}
+
 __device__ __forceinline__ bool bk_mbar_wait(uint32_t bar, uint32_t parity, uint64_t limit_ns) {
 #pragma unroll 1
     for (int i = 0; i < 16; i++)
@@ -134,12 +206,22 @@ __device__ __forceinline__ bool bk_mbar_wait(uint32_t bar, uint32_t parity, uint
     return mbar_wait_ns(bar, parity, limit_ns);
 }
 
+__device__ __forceinline__ bool bk_ll_giveup(const bk_params &P, uint64_t t0, uint64_t limit_ns, int code) {
+    if (bk_ld_volatile(P.abort_word)) return true;
+    if (jl_gtime_ns() - t0 > limit_ns) {
+        atomicExch(P.status, code);
+        atomicExch(P.abort_word, 1);
+        return true;
+    }
+    return false;
+}
+
 // Spins until *p >= target (p: a counter other CTAs or other GPUs advance). False on abort or timeout.
 template <bool SYS>
 __device__ __forceinline__ bool bk_wait_ge(const unsigned *p, unsigned target, const bk_params &P, uint64_t limit_ns, int code) {
     const uint64_t t0 = jl_gtime_ns();
     for (uint32_t i = 0;; i++) {
-        const unsigned v = SYS ? bk_ld_acquire_sys(p) : bk_ld_acquire_gpu(p);
+        const unsigned v = bk_ld_acquire_gpu(p);
         if (v >= target) return true;
         if ((i & 15u) == 15u) {
             if (bk_ld_volatile(P.abort_word)) return false;
@@ -154,12 +236,11 @@ __device__ __forceinline__ bool bk_wait_ge(const unsigned *p, unsigned target, c
 
 // All CTAs of the grid meet. `done` counts the barriers this launch has passed. Writes made before the barrier by
 // any CTA are visible (through L2: read them with ld.cg / ld.volatile, never through L1) after it.
-__device__ __forceinline__ bool bk_grid_sync(const bk_params &P, int &done, uint64_t limit_ns, bool sys_fence) {
+__device__ __forceinline__ bool bk_grid_sync(const bk_params &P, int &done, uint64_t limit_ns) {
     __shared__ int s_ok;
     __syncthreads();
     if (threadIdx.x == 0) {
         // release: the CTA's writes (ordered before this thread by the barrier above) become visible before the count
-        if (sys_fence) __threadfence_system();
         asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(P.bar) : "memory");
         s_ok = bk_wait_ge<false>(P.bar, (unsigned)(done + 1) * gridDim.x, P, limit_ns, 4) ? 1 : 0;   // acquire loads
     }
@@ -244,28 +325,13 @@ __device__ __forceinline__ void bk_fetch(const bk_cursor &c, const bk_pinfo *pi,
 
 // ------------------------------------------------------------------ prologues
 
-// The activation row of a NORM prologue: x + planes (rank order), or the embedding row of *tok.
-__device__ __forceinline__ float4 bk_resid4(const bk_params &P, const bk_phase &ph, int i4) {
-    float4 v;
-    if (ph.from_emb) {
-        const long long tok = *P.tok;
-        const uint2 u = __ldg(reinterpret_cast<const uint2 *>(P.emb + (size_t)tok * P.hidden) + i4);
-        const __nv_bfloat162 *b = reinterpret_cast<const __nv_bfloat162 *>(&u);
-        const float2 lo = __bfloat1622float2(b[0]), hi = __bfloat1622float2(b[1]);
-        v = make_float4(lo.x, lo.y, hi.x, hi.y);
-    } else {
-        v = __ldcg(reinterpret_cast<const float4 *>(ph.xsrc) + i4);
-    }
-    for (int r = 0; r < ph.nplanes; r++) {
-        const float4 d = __ldcg(reinterpret_cast<const float4 *>(ph.planes + (size_t)r * P.hidden) + i4);
-        v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
-    }
-    return v;
-}
-
 // Builds the decode operand of the phase's activation row in shared memory (every CTA, the whole row). Warp w owns
-// super-blocks w, w + 16, ... (at most BK_MAX_NSB / BK_WARPS of them); all their loads are issued before the first
-// is used, and the values stay in registers between the sum of squares and the normalisation.
+// super-block w (NORM: rows of at most BK_WARPS super-blocks) or super-blocks w, w + 16, ... (PLAIN).
+//   NORM   the residual row lives in registers for the whole launch (xres: warp w's lanes hold the eight values of
+//          super-block w each): xres (+)= the planes of the previous o / down phase in rank order, then
+//          RMSNorm(xres) * norm_w becomes the operand. Every CTA keeps its own copy and gets the same bits.
+//   PLAIN  the operand of the previous phase's output vector as it is (attention output, SiLU*up).
+// seq: the sequence number the producing phase stamped on its values. False when a wait was given up.
 #define BK_PRO_IT (BK_MAX_NSB / BK_WARPS)
 #ifdef BK_FINE_TRACE
 #define BK_PT(i) do { ft[i] = clock64(); } while (0)
@@ -274,90 +340,82 @@ __device__ __forceinline__ float4 bk_resid4(const bk_params &P, const bk_phase &
 #define BK_PT(i) do { } while (0)
 #define BK_PT_ARG
 #endif
-__device__ __forceinline__ void bk_prologue(const bk_params &P, const bk_phase &ph, uint8_t *xop, float *ssq BK_PT_ARG) {
+__device__ __forceinline__ bool bk_prologue(const bk_params &P, const bk_phase &ph, uint8_t *xop, float *ssq, float4 (&xres)[2],
+                                            unsigned seq, uint64_t limit_ns BK_PT_ARG) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nsb = ph.nsb;
+    bool ok = true;
     BK_PT(0);
     if (ph.prologue == BK_PRO_NORM) {
-        if (nsb <= BK_WARPS) {
-            // one super-block per warp: its eight values and weights stay in registers between the two passes
-            float4 v[2], gw[2];
-            const bool mine = warp < nsb;
-            if (mine) {
+        const bool mine = warp < nsb;
+        float4 gw[2];
+        if (mine) {
 #pragma unroll
-                for (int hf = 0; hf < 2; ++hf) {
-                    const int i4 = warp * 64 + hf * 32 + lane;
-                    v[hf] = bk_resid4(P, ph, i4);
-                    gw[hf] = ph.norm_w ? __ldg(reinterpret_cast<const float4 *>(ph.norm_w) + i4) : make_float4(1.f, 1.f, 1.f, 1.f);
+            for (int hf = 0; hf < 2; ++hf) {
+                const int i4 = warp * 64 + hf * 32 + lane;
+                gw[hf] = ph.norm_w ? __ldg(reinterpret_cast<const float4 *>(ph.norm_w) + i4) : make_float4(1.f, 1.f, 1.f, 1.f);
+                if (ph.from_emb) {
+                    const long long tok = *P.tok;
+                    const uint2 u = __ldg(reinterpret_cast<const uint2 *>(P.emb + (size_t)tok * P.hidden) + i4);
+                    const __nv_bfloat162 *b2 = reinterpret_cast<const __nv_bfloat162 *>(&u);
+                    const float2 lo = __bfloat1622float2(b2[0]), hi = __bfloat1622float2(b2[1]);
+                    xres[hf] = make_float4(lo.x, lo.y, hi.x, hi.y);
                 }
             }
-            float ss = 0.f;
-            if (mine) {
+            for (int r = 0; r < ph.nplanes; r += 2) {                 // two planes per batch of loads
+                const bk_ll *pp[4];
+                float4 d[4];
 #pragma unroll
-                for (int hf = 0; hf < 2; ++hf) {
-                    const float4 a = v[hf];
-                    if (blockIdx.x == 0 && ph.xdst) reinterpret_cast<float4 *>(ph.xdst)[warp * 64 + hf * 32 + lane] = a;   // the new residual row
-                    ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+                for (int q = 0; q < 4; q++)
+                    pp[q] = r + (q >> 1) < ph.nplanes
+                                ? ph.planes + (size_t)(r + (q >> 1)) * P.hidden + (size_t)(warp * 64 + (q & 1) * 32 + lane) * 4 : nullptr;
+                ok = bk_ll_read4_n<4>(pp, seq, d, P, limit_ns, 5) && ok;
+#pragma unroll
+                for (int q = 0; q < 4; q++) {                           // rank order: the same sum on every CTA and every rank
+                    float4 &x = xres[q & 1];
+                    x.x += d[q].x; x.y += d[q].y; x.z += d[q].z; x.w += d[q].w;
                 }
             }
+        }
+        float ss = 0.f;
+        if (mine) {
 #pragma unroll
-            for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-            BK_PT(1);
-            if (lane == 0) ssq[warp] = ss;
-            __syncthreads();
-            BK_PT(2);
-            float tot = 0.f;
-#pragma unroll
-            for (int i = 0; i < BK_WARPS; i++) tot += ssq[i];      // fixed order: every CTA gets the same bits
-            const float r = rsqrtf(tot / (float)P.hidden + P.eps);
-            if (mine) {
-#pragma unroll
-                for (int hf = 0; hf < 2; ++hf) {
-                    const float4 a = v[hf], g4 = gw[hf];
-                    v[hf] = make_float4(a.x * r * g4.x, a.y * r * g4.y, a.z * r * g4.z, a.w * r * g4.w);
-                }
-                q4k_prep_sb_vals(v[0], v[1], xop + (size_t)warp * Q4K_XP_SB_BYTES, lane);
+            for (int hf = 0; hf < 2; ++hf) {
+                const float4 a = xres[hf];
+                ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
             }
-        } else {
-            // longer rows: two passes over the row (the second one hits L2)
-            float ss = 0.f;
-            for (int sb = warp; sb < nsb; sb += BK_WARPS)
+        }
 #pragma unroll
-                for (int hf = 0; hf < 2; ++hf) {
-                    const int i4 = sb * 64 + hf * 32 + lane;
-                    const float4 a = bk_resid4(P, ph, i4);
-                    if (blockIdx.x == 0 && ph.xdst) reinterpret_cast<float4 *>(ph.xdst)[i4] = a;
-                    ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
-                }
+        for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        BK_PT(1);
+        if (lane == 0) ssq[warp] = ss;
+        __syncthreads();
+        BK_PT(2);
+        float tot = 0.f;
 #pragma unroll
-            for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-            if (lane == 0) ssq[warp] = ss;
-            __syncthreads();
-            float tot = 0.f;
+        for (int i = 0; i < BK_WARPS; i++) tot += ssq[i];      // fixed order: every CTA gets the same bits
+        const float r = rsqrtf(tot / (float)P.hidden + P.eps);
+        if (mine) {
+            float4 v[2];
 #pragma unroll
-            for (int i = 0; i < BK_WARPS; i++) tot += ssq[i];
-            const float r = rsqrtf(tot / (float)P.hidden + P.eps);
-            for (int sb = warp; sb < nsb; sb += BK_WARPS) {
-                float4 w2[2];
-#pragma unroll
-                for (int hf = 0; hf < 2; ++hf) {
-                    const int i4 = sb * 64 + hf * 32 + lane;
-                    const float4 a = bk_resid4(P, ph, i4);
-                    const float4 g4 = ph.norm_w ? __ldg(reinterpret_cast<const float4 *>(ph.norm_w) + i4) : make_float4(1.f, 1.f, 1.f, 1.f);
-                    w2[hf] = make_float4(a.x * r * g4.x, a.y * r * g4.y, a.z * r * g4.z, a.w * r * g4.w);
-                }
-                q4k_prep_sb_vals(w2[0], w2[1], xop + (size_t)sb * Q4K_XP_SB_BYTES, lane);
+            for (int hf = 0; hf < 2; ++hf) {
+                const float4 a = xres[hf], g4 = gw[hf];
+                v[hf] = make_float4(a.x * r * g4.x, a.y * r * g4.y, a.z * r * g4.z, a.w * r * g4.w);
             }
+            q4k_prep_sb_vals(v[0], v[1], xop + (size_t)warp * Q4K_XP_SB_BYTES, lane);
         }
     } else {
         float4 v[BK_PRO_IT][2];
 #pragma unroll
-        for (int it = 0; it < BK_PRO_IT; it++) {
-            const int sb = warp + it * BK_WARPS;
-            if (sb < nsb) {
-                const float4 *s4 = reinterpret_cast<const float4 *>(ph.vsrc) + sb * 64;
-                v[it][0] = __ldcg(s4 + lane);
-                v[it][1] = __ldcg(s4 + 32 + lane);
+        for (int it = 0; it < BK_PRO_IT; it += 2) {
+            const bk_ll *pp[4];
+            float4 d[4];
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                const int sb = warp + (it + (q >> 1)) * BK_WARPS;
+                pp[q] = sb < nsb ? ph.vsrc + (size_t)sb * 256 + (q & 1) * 128 + lane * 4 : nullptr;
             }
+            ok = bk_ll_read4_n<4>(pp, seq, d, P, limit_ns, 4) && ok;
+            v[it][0] = d[0]; v[it][1] = d[1]; v[it + 1][0] = d[2]; v[it + 1][1] = d[3];
         }
         BK_PT(1);
         BK_PT(2);
@@ -368,8 +426,9 @@ __device__ __forceinline__ void bk_prologue(const bk_params &P, const bk_phase &
         }
     }
     BK_PT(3);
-    __syncthreads();
+    ok = __syncthreads_and(ok ? 1 : 0) != 0;
     BK_PT(4);
+    return ok;
 }
 
 // Pulls the next matvec phase's norm weights (and, for the first phase, nothing else) towards L2 while the current phase
@@ -406,13 +465,14 @@ struct bk_att_smem {        // one group's shared memory
     float red4[4][BK_MAX_G][BK_ATT_D];
     float gp_o[BK_MAX_G][BK_ATT_D];
     float gp_m[BK_MAX_G], gp_l[BK_MAX_G];
+    uint32_t kf[BK_ATT_D / 2], vf[BK_ATT_D / 2];   // the new position's key (rotated) and value as bf16 pairs
 };
 static_assert(sizeof(bk_att_smem) <= BK_ATT_SUB_BYTES, "attention group smem");
 
 __device__ __forceinline__ int bk_att_nblk(int len) { return (len + 4 * BK_ATT_CHUNK - 1) / (4 * BK_ATT_CHUNK); }
 
 // Before the grid barrier in front of an attention phase: the CTA's first task's K and V lines, towards L2.
-__device__ __forceinline__ void bk_attention_prefetch(const bk_params &P, const bk_phase &ph) {
+__device__ __forceinline__ void bk_attention_prefetch(const bk_params &P, const void *k_cache, const void *v_cache) {
     const long long pos = *P.pos;
     if (pos < 0 || pos >= P.max_len) return;
     const int nblk = bk_att_nblk((int)pos + 1);
@@ -422,12 +482,20 @@ __device__ __forceinline__ void bk_attention_prefetch(const bk_params &P, const 
     const int s0 = (4 * j + sub) * BK_ATT_CHUNK;
     const int row = s0 + (t & 63) / 2;                           // two 128-byte lines per 256-byte row
     if (row >= (int)pos) return;
-    const uint8_t *base = static_cast<const uint8_t *>(t < 64 ? ph.k_cache : ph.v_cache);
+    const uint8_t *base = static_cast<const uint8_t *>(t < 64 ? k_cache : v_cache);
     asm volatile("prefetch.global.L2 [%0];" ::"l"(base + ((size_t)kv * P.max_len + row) * 256 + (t & 1) * 128));
 }
 
+#ifdef BK_FINE_TRACE
+#define BK_AT(i) do { if (at && threadIdx.x == 0) at[i] = jl_gtime_ns(); } while (0)
+#define BK_AT_ARG , unsigned long long *at
+#else
+#define BK_AT(i) do { } while (0)
+#define BK_AT_ARG
+#endif
 template <int G>
-__device__ void bk_attention(const bk_params &P, const bk_phase &ph, uint8_t *work) {
+__device__ bool bk_attention(const bk_params &P, const bk_phase &ph, uint8_t *work, unsigned seq_r, unsigned seq_w,
+                             uint64_t limit_ns BK_AT_ARG) {
     constexpr int HDR = (2 * G + 3) & ~3;
     constexpr int STRIDE = HDR + G * BK_ATT_D;
     const int tid = threadIdx.x, sub = tid >> 7, t = tid & 127, warp = t >> 5, lane = t & 31;
@@ -436,7 +504,8 @@ __device__ void bk_attention(const bk_params &P, const bk_phase &ph, uint8_t *wo
     __shared__ unsigned s_last;
     const int bid = 1 + sub;
     const long long pos = *P.pos;
-    if (pos < 0 || pos >= P.max_len) return;
+    if (pos < 0 || pos >= P.max_len) return true;
+    bool ok = true;
     const int len = (int)pos + 1;
     const int nchunk = (len + BK_ATT_CHUNK - 1) / BK_ATT_CHUNK;
     const int nblk = bk_att_nblk(len), nblk_max = bk_att_nblk(P.max_len);
@@ -444,6 +513,7 @@ __device__ void bk_attention(const bk_params &P, const bk_phase &ph, uint8_t *wo
     const float *cs = P.cos_t + (size_t)pos * (BK_ATT_D / 2), *sn = P.sin_t + (size_t)pos * (BK_ATT_D / 2);
     const int p1 = t >> 2, qd = t & 3;          // scores: four threads per position, 32 dims each
     const int dg = t & 15, pg = t >> 4;         // weighted V: 16 threads per row (8 dims each), 8 position groups
+    BK_AT(0);
     for (int ct = blockIdx.x; ct < P.hkv * nblk; ct += gridDim.x) {
         const int kv = ct / nblk, j = ct % nblk;
         const int chunk = 4 * j + sub;
@@ -461,50 +531,62 @@ __device__ void bk_attention(const bk_params &P, const bk_phase &ph, uint8_t *wo
                 vreg[i] = vrow < (int)pos ? reinterpret_cast<const uint4 *>(vc + ((size_t)kv * P.max_len + vrow) * BK_ATT_D)[dg]
                                           : make_uint4(0, 0, 0, 0);
             }
-            if (krow == (int)pos) {             // the new key: rotate, round, keep, append
-                const float *src = ph.qkv + (size_t)(P.hq + kv) * BK_ATT_D;
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    uint32_t w[4];
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const int jp = qd * 16 + c * 4 + i;
-                        const float2 ab = __ldcg(reinterpret_cast<const float2 *>(src) + jp);
-                        const float cc = cs[jp], ss = sn[jp];
-                        const __nv_bfloat162 o = __floats2bfloat162_rn(ab.x * cc - ab.y * ss, ab.x * ss + ab.y * cc);
-                        w[i] = *reinterpret_cast<const uint32_t *>(&o);
-                    }
-                    kreg[c] = make_uint4(w[0], w[1], w[2], w[3]);
-                    reinterpret_cast<uint4 *>(kc + ((size_t)kv * P.max_len + pos) * BK_ATT_D)[qd * 4 + c] = kreg[c];
-                }
-            }
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                if (s0 + pg + 8 * i == (int)pos) {   // the new value: round, keep, append
-                    const float *src = ph.qkv + (size_t)(P.hq + P.hkv + kv) * BK_ATT_D + dg * 8;
-                    uint32_t w[4];
-#pragma unroll
-                    for (int q2 = 0; q2 < 4; ++q2) {
-                        const float2 ab = __ldcg(reinterpret_cast<const float2 *>(src) + q2);
-                        const __nv_bfloat162 o = __floats2bfloat162_rn(ab.x, ab.y);
-                        w[q2] = *reinterpret_cast<const uint32_t *>(&o);
-                    }
-                    vreg[i] = make_uint4(w[0], w[1], w[2], w[3]);
-                    reinterpret_cast<uint4 *>(vc + ((size_t)kv * P.max_len + pos) * BK_ATT_D)[dg] = vreg[i];
-                }
+        }
+        const bool fresh = (int)pos >= s0 && (int)pos < s0 + BK_ATT_CHUNK;
+        if (fresh) {
+            // the new position's key (rotated) and value: one pair per thread, rounded to bf16, appended to the cache and
+            // handed through shared memory to the threads that own that row's pieces
+            const int jp = t & 63;
+            const bk_ll *src[1] = {ph.qkv + (size_t)(t < 64 ? P.hq + kv : P.hq + P.hkv + kv) * BK_ATT_D + 2 * jp};
+            float2 ab[1];
+            ok = bk_ll_read2_n<1>(src, seq_r, ab, P, limit_ns, 4) && ok;
+            __nv_bfloat162 o;
+            if (t < 64) {
+                const float cc = cs[jp], ss = sn[jp];
+                o = __floats2bfloat162_rn(ab[0].x * cc - ab[0].y * ss, ab[0].x * ss + ab[0].y * cc);
+                S->kf[jp] = *reinterpret_cast<const uint32_t *>(&o);
+                reinterpret_cast<__nv_bfloat162 *>(kc + ((size_t)kv * P.max_len + pos) * BK_ATT_D)[jp] = o;
+            } else {
+                o = __floats2bfloat162_rn(ab[0].x, ab[0].y);
+                S->vf[jp] = *reinterpret_cast<const uint32_t *>(&o);
+                reinterpret_cast<__nv_bfloat162 *>(vc + ((size_t)kv * P.max_len + pos) * BK_ATT_D)[jp] = o;
             }
         }
-        for (int pi = t; pi < G * (BK_ATT_D / 2); pi += 128) {            // q: rotate, round to bf16, scale
-            const int h = pi >> 6, jp = pi & 63;
-            const float2 ab = __ldcg(reinterpret_cast<const float2 *>(ph.qkv + (size_t)(kv * G + h) * BK_ATT_D) + jp);
-            const float c = cs[jp], s_ = sn[jp];
-            const __nv_bfloat162 o = __floats2bfloat162_rn(ab.x * c - ab.y * s_, ab.x * s_ + ab.y * c);
-            const float2 f = __bfloat1622float2(o);
-            const int d0 = 2 * jp;                                        // dims d0, d0 + 1: quarter d0 / 32
-            S->qs[h][(d0 >> 5) * BK_QS_STRIDE + (d0 & 31)] = f.x * 0.08838834764831845f;
-            S->qs[h][(d0 >> 5) * BK_QS_STRIDE + (d0 & 31) + 1] = f.y * 0.08838834764831845f;
+        {
+            const int nq = G * (BK_ATT_D / 2);                            // q: rotate, round to bf16, scale; <= 2 pairs per thread
+            const bk_ll *src[2];
+            float2 ab[2];
+#pragma unroll
+            for (int u = 0; u < 2; u++) {
+                const int pi = t + 128 * u;
+                src[u] = pi < nq ? ph.qkv + (size_t)(kv * G + (pi >> 6)) * BK_ATT_D + 2 * (pi & 63) : nullptr;
+            }
+            ok = bk_ll_read2_n<2>(src, seq_r, ab, P, limit_ns, 4) && ok;
+#pragma unroll
+            for (int u = 0; u < 2; u++) {
+                const int pi = t + 128 * u;
+                if (pi < nq) {
+                    const int h = pi >> 6, jp = pi & 63;
+                    const float c = cs[jp], s_ = sn[jp];
+                    const __nv_bfloat162 o = __floats2bfloat162_rn(ab[u].x * c - ab[u].y * s_, ab[u].x * s_ + ab[u].y * c);
+                    const float2 f = __bfloat1622float2(o);
+                    const int d0 = 2 * jp;                                // dims d0, d0 + 1: quarter d0 / 32
+                    S->qs[h][(d0 >> 5) * BK_QS_STRIDE + (d0 & 31)] = f.x * 0.08838834764831845f;
+                    S->qs[h][(d0 >> 5) * BK_QS_STRIDE + (d0 & 31) + 1] = f.y * 0.08838834764831845f;
+                }
+            }
         }
         bk_subbar(bid);
+        BK_AT(1);
+        if (fresh) {                            // the owners of the new row's pieces take them from shared memory
+            if (s0 + p1 == (int)pos) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) kreg[c] = reinterpret_cast<const uint4 *>(S->kf)[qd * 4 + c];
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                if (s0 + pg + 8 * i == (int)pos) vreg[i] = reinterpret_cast<const uint4 *>(S->vf)[dg];
+        }
         float s[G];
 #pragma unroll
         for (int h = 0; h < G; ++h) s[h] = 0.f;
@@ -596,31 +678,43 @@ __device__ void bk_attention(const bk_params &P, const bk_phase &ph, uint8_t *wo
                 if (d == 0) { my[h] = M; my[G + h] = l; }
             }
         }
+        BK_AT(2);
         __threadfence();
-        __syncthreads();
-        if (tid == 0) s_last = atomicAdd(&P.tickets[kv], 1u) == (unsigned)(nblk - 1) ? 1u : 0u;
+        if (!__syncthreads_and(ok ? 1 : 0)) return false;
+        BK_AT(3);
+        if (tid == 0) s_last = atomicAdd(&ph.tickets[kv], 1u) == (unsigned)(nblk - 1) ? 1u : 0u;
         __syncthreads();
         if (s_last) {
             __threadfence();
             const float *base = P.part + (size_t)kv * nblk_max * STRIDE;
             const int h = tid >> 7, d = tid & 127;
+            // ONE trip to L2 for the whole merge: the kv head's records are contiguous, so the CTA copies them (as many
+            // as fit: 26 at G = 4, i.e. 3328 positions) into the groups' now free shared memory with every load in
+            // flight at once, and merges from there. Dependent loads in a loop would cost a trip each.
+            float *rs = reinterpret_cast<float *>(work);
+            const int nrec = min(nblk, (int)(4 * BK_ATT_SUB_BYTES / 4) / STRIDE);
+#pragma unroll 8
+            for (int i = tid; i < nrec * STRIDE; i += BK_THREADS) rs[i] = __ldcg(base + i);
+            __syncthreads();
             if (h < G) {
                 float M = -INFINITY;
-                for (int b2 = 0; b2 < nblk; ++b2) M = fmaxf(M, __ldcg(base + (size_t)b2 * STRIDE + h));
+                for (int b2 = 0; b2 < nblk; ++b2) M = fmaxf(M, b2 < nrec ? rs[b2 * STRIDE + h] : __ldcg(base + (size_t)b2 * STRIDE + h));
                 float o = 0.f, l = 0.f;
-#pragma unroll 4
                 for (int b2 = 0; b2 < nblk; ++b2) {                       // ascending block order: bit-stable
-                    const float mb = __ldcg(base + (size_t)b2 * STRIDE + h);
+                    const float *rec = b2 < nrec ? rs + b2 * STRIDE : base + (size_t)b2 * STRIDE;
+                    const float mb = b2 < nrec ? rec[h] : __ldcg(rec + h);
                     const float w = mb == -INFINITY ? 0.f : __expf(mb - M);
-                    o = fmaf(w, __ldcg(base + (size_t)b2 * STRIDE + HDR + h * BK_ATT_D + d), o);
-                    l = fmaf(w, __ldcg(base + (size_t)b2 * STRIDE + G + h), l);
+                    o = fmaf(w, b2 < nrec ? rec[HDR + h * BK_ATT_D + d] : __ldcg(rec + HDR + h * BK_ATT_D + d), o);
+                    l = fmaf(w, b2 < nrec ? rec[G + h] : __ldcg(rec + G + h), l);
                 }
-                ph.att[(size_t)(kv * G + h) * BK_ATT_D + d] = l > 0.f ? o / l : 0.f;
+                bk_ll_store(ph.att + (size_t)(kv * G + h) * BK_ATT_D + d, l > 0.f ? o / l : 0.f, seq_w);
             }
-            if (tid == 0) P.tickets[kv] = 0;                              // ready for the next attention phase
         }
         __syncthreads();                                                  // the groups' shared memory is free again
+        BK_AT(4);
     }
+    BK_AT(5);
+    return true;
 }
 
 // ------------------------------------------------------------------ the kernel
@@ -630,7 +724,7 @@ __device__ void bk_attention(const bk_params &P, const bk_phase &ph, uint8_t *wo
 #define BK_RED_BYTES (BK_ROUND_TASKS * 16 * 4)
 #define BK_WORK_BYTES (4 * BK_ATT_SUB_BYTES > BK_XOP_BYTES + BK_RED_BYTES ? 4 * BK_ATT_SUB_BYTES : BK_XOP_BYTES + BK_RED_BYTES)
 #define BK_PHASE_BYTES ((sizeof(bk_phase) + 15) / 16 * 16)
-#define BK_SMEM_BYTES (BK_RING_BYTES + BK_WORK_BYTES + Q4K_XP_ZERO_BYTES + BK_WARPS * BK_STAGES * 8 + 64 * 4 + BK_MAX_PHASES * 32 + 2 * BK_PHASE_BYTES + 128)
+#define BK_SMEM_BYTES (BK_RING_BYTES + BK_WORK_BYTES + Q4K_XP_ZERO_BYTES + BK_WARPS * BK_STAGES * 8 + 64 * 4 + BK_MAX_PHASES * 32 + 3 * BK_PHASE_BYTES + 128)
 
 __global__ void __launch_bounds__(BK_THREADS, 1) jl_block_kernel(const __grid_constant__ bk_params P) {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -644,11 +738,14 @@ __global__ void __launch_bounds__(BK_THREADS, 1) jl_block_kernel(const __grid_co
     uint64_t *bars = reinterpret_cast<uint64_t *>(zero + Q4K_XP_ZERO_BYTES) + warp * BK_STAGES;
     float *misc = reinterpret_cast<float *>(zero + Q4K_XP_ZERO_BYTES + BK_WARPS * BK_STAGES * 8);   // 64 floats
     bk_pinfo *pinfo = reinterpret_cast<bk_pinfo *>(misc + 64);
-    // the current and the next phase's full descriptors, copied from global memory one phase ahead of their use
+    // Full phase descriptors, copied from global memory one phase ahead of their use into a ring of THREE: when phase
+    // p + 1 is staged (at the start of phase p) it overwrites phase p - 2's copy, and every thread left phase p - 2
+    // before the first __syncthreads of phase p - 1, which every thread has passed by now. (Two copies would not do:
+    // nothing separates a slow warp's last look at phase p - 1 from the start of phase p.)
     uint8_t *phase_sm = reinterpret_cast<uint8_t *>(pinfo + BK_MAX_PHASES);
     auto stage_phase = [&](int q) {
         if (q < P.nphases && tid < (int)(BK_PHASE_BYTES / 16))
-            reinterpret_cast<uint4 *>(phase_sm + (size_t)(q & 1) * BK_PHASE_BYTES)[tid] = __ldg(reinterpret_cast<const uint4 *>(P.phases + q) + tid);
+            reinterpret_cast<uint4 *>(phase_sm + (size_t)(q % 3) * BK_PHASE_BYTES)[tid] = __ldg(reinterpret_cast<const uint4 *>(P.phases + q) + tid);
     };
     stage_phase(0);
     const uint64_t limit_ns = jl_wait_limit_ns(P.status);
@@ -687,8 +784,10 @@ __global__ void __launch_bounds__(BK_THREADS, 1) jl_block_kernel(const __grid_co
     }
 
     int barriers_done = 0;
-    const unsigned seq_start = P.world > 1 ? bk_ld_acquire_gpu(P.seq) : 0u;     // exchanges finished by earlier launches
-    unsigned seq = seq_start;
+    // Phase p stamps its outputs with seq_base + p + 1; its inputs carry the previous phase's number, seq_base + p.
+    const unsigned seq_base = bk_ld_acquire_gpu(P.seq);
+    float4 xres[2];                     // the residual row: warp w's lanes hold super-block w's values
+    xres[0] = xres[1] = make_float4(0.f, 0.f, 0.f, 0.f);
     bool alive = true;
     float best_val = -INFINITY;
     int best_idx = 0x7fffffff;
@@ -708,23 +807,28 @@ __global__ void __launch_bounds__(BK_THREADS, 1) jl_block_kernel(const __grid_co
 #define BK_FT(i) do { } while (0)
 #endif
     for (int p = 0; p < P.nphases && alive; p++) {
-        const bk_phase &ph = *reinterpret_cast<const bk_phase *>(phase_sm + (size_t)(p & 1) * BK_PHASE_BYTES);
+        const bk_phase &ph = *reinterpret_cast<const bk_phase *>(phase_sm + (size_t)(p % 3) * BK_PHASE_BYTES);
+        const int p_kind = pinfo[p].kind, p_epi = pinfo[p].epi;   // from the immutable table, not from the ring
         stage_phase(p + 1);       // lands long before the next phase starts (at least one __syncthreads away)
 #ifdef BK_FINE_TRACE
         for (int i = 0; i < 7; i++) ft_acc[i] = 0;
 #endif
         BK_TRACE(0);
+        const unsigned seq_r = seq_base + (unsigned)p, seq_w = seq_r + 1u;
         if ((int)blockIdx.x == (p + 1) % (int)gridDim.x) bk_prefetch_norm(P, p + 1);
-        if (ph.kind == BK_MATVEC) {
+        if (p + 1 < nphases && pinfo[p + 1].kind == BK_ATTN)          // the next phase's K and V lines, towards L2
+            bk_attention_prefetch(P, P.phases[p + 1].k_cache, P.phases[p + 1].v_cache);
+        if (p_kind == BK_MATVEC) {
 #ifdef BK_FINE_TRACE
             long long pt[5] = {0, 0, 0, 0, 0};
-            bk_prologue(P, ph, xop, misc, pt);
+            alive = bk_prologue(P, ph, xop, misc, xres, seq_r, limit_ns, pt);
             if (P.trace && blockIdx.x == 0 && tid == 0)
                 for (int i = 1; i < 5; i++) P.trace[(size_t)2 * P.nphases * 4 + (size_t)P.nphases * 8 + (size_t)p * 4 + i - 1] = (unsigned long long)(pt[i] - pt[i - 1]);
 #else
-            bk_prologue(P, ph, xop, misc);
+            alive = bk_prologue(P, ph, xop, misc, xres, seq_r, limit_ns);
 #endif
             BK_TRACE(1);
+            if (!alive) break;
             const int nsb = pinfo[p].nsb, rg0 = pinfo[p].rg0, rg1 = pinfo[p].rg1, rpr = pinfo[p].rpr;
             for (int rbase = rg0; rbase < rg1 && alive; rbase += rpr) {
                 const int nr = min(rpr, rg1 - rbase), ntask = nr * nsb;
@@ -764,7 +868,7 @@ __global__ void __launch_bounds__(BK_THREADS, 1) jl_block_kernel(const __grid_co
                 BK_FT(5);
                 if (!alive) break;
                 // the round's row groups: super-blocks in ascending order (run-to-run bit-stable)
-                if (ph.epilogue == BK_EPI_GATE2) {
+                if (p_epi == BK_EPI_GATE2) {
                     if (tid < nr * 8) {
                         const int rgl = tid >> 3, r = tid & 7;
                         float sg = 0.f, su = 0.f;
@@ -773,7 +877,7 @@ __global__ void __launch_bounds__(BK_THREADS, 1) jl_block_kernel(const __grid_co
                             su += red[(rgl * nsb + sb) * 16 + r + 8];
                         }
                         const int o = (rbase + rgl) * 8 + r;
-                        if (o < ph.nrows) ph.out[o] = sg / (1.f + __expf(-sg)) * su;     // SiLU(gate) * up
+                        if (o < ph.nrows) bk_ll_store(ph.out + o, sg / (1.f + __expf(-sg)) * su, seq_w);     // SiLU(gate) * up
                     }
                 } else if (tid < nr * 16) {
                     const int rgl = tid >> 4, r = tid & 15;
@@ -781,21 +885,21 @@ __global__ void __launch_bounds__(BK_THREADS, 1) jl_block_kernel(const __grid_co
                     for (int sb = 0; sb < nsb; sb++) sum += red[(rgl * nsb + sb) * 16 + r];
                     const int row = (rbase + rgl) * 16 + r;
                     if (row < ph.nrows) {
-                        if (ph.exchange) {
+                        if (p_epi == BK_EPI_ARGMAX) {
+                            ph.out_f32[row] = sum;
+                            if (sum > best_val || (sum == best_val && row < best_idx)) { best_val = sum; best_idx = row; }
+                        } else if (ph.exchange) {
 #pragma unroll 1
-                            for (int pr = 0; pr < P.world; pr++) ph.peer_out[pr][row] = sum;
+                            for (int pr = 0; pr < P.world; pr++) bk_ll_store(ph.peer_out[pr] + row, sum, seq_w);   // over NVLink for pr != rank
                         } else {
-                            ph.out[row] = sum;
-                        }
-                        if (ph.epilogue == BK_EPI_ARGMAX && (sum > best_val || (sum == best_val && row < best_idx))) {
-                            best_val = sum; best_idx = row;
+                            bk_ll_store(ph.out + row, sum, seq_w);
                         }
                     }
                 }
                 __syncthreads();         // the round's partials are consumed
                 BK_FT(6);
             }
-            if (alive && ph.epilogue == BK_EPI_ARGMAX) {
+            if (alive && p_epi == BK_EPI_ARGMAX) {
                 // the CTA's candidate: largest value, lowest row on a tie
                 for (int o = 16; o; o >>= 1) {
                     const float ov = __shfl_xor_sync(0xffffffffu, best_val, o);
@@ -812,11 +916,18 @@ __global__ void __launch_bounds__(BK_THREADS, 1) jl_block_kernel(const __grid_co
                     P.cand_val[blockIdx.x] = bv; P.cand_idx[blockIdx.x] = bi;
                 }
             }
-        } else if (ph.kind == BK_ATTN) {
+        } else if (p_kind == BK_ATTN) {
             const int G = P.hq / P.hkv;
-            if (G == 4) bk_attention<4>(P, ph, work);
-            else if (G == 2) bk_attention<2>(P, ph, work);
-            else bk_attention<1>(P, ph, work);
+#ifdef BK_FINE_TRACE
+            unsigned long long *at = (P.trace && p == 6) ? P.trace + (size_t)2 * P.nphases * 4 + (size_t)P.nphases * 12 + (size_t)blockIdx.x * 8 : nullptr;
+            if (G == 4) alive = bk_attention<4>(P, ph, work, seq_r, seq_w, limit_ns, at);
+            else if (G == 2) alive = bk_attention<2>(P, ph, work, seq_r, seq_w, limit_ns, at);
+            else alive = bk_attention<1>(P, ph, work, seq_r, seq_w, limit_ns, at);
+#else
+            if (G == 4) alive = bk_attention<4>(P, ph, work, seq_r, seq_w, limit_ns);
+            else if (G == 2) alive = bk_attention<2>(P, ph, work, seq_r, seq_w, limit_ns);
+            else alive = bk_attention<1>(P, ph, work, seq_r, seq_w, limit_ns);
+#endif
         } else {   // BK_FINAL: CTA 0 picks the winner among the CTAs' candidates
             if (blockIdx.x == 0 && warp == 0) {
                 float bv = -INFINITY; int bi = 0x7fffffff;
@@ -842,27 +953,15 @@ __global__ void __launch_bounds__(BK_THREADS, 1) jl_block_kernel(const __grid_co
             for (int i = 1; i < 7; i++) P.trace[(size_t)2 * P.nphases * 4 + (size_t)p * 8 + i] = (unsigned long long)ft_acc[i];
 #endif
         if (!alive || p + 1 >= P.nphases) break;
-        if (pinfo[p + 1].kind == BK_ATTN)
-            bk_attention_prefetch(P, *reinterpret_cast<const bk_phase *>(phase_sm + (size_t)((p + 1) & 1) * BK_PHASE_BYTES));
-        const bool ex = ph.kind == BK_MATVEC && ph.exchange && P.world > 1;
-        alive = bk_grid_sync(P, barriers_done, limit_ns, ex);
-        if (alive && ex) {
-            // every CTA of this rank has stored its rows into every rank's slot buffer: tell the ranks, then wait for theirs
-            seq++;
-            if (blockIdx.x == 0 && tid < P.world) bk_st_release_sys(P.peer_flags[tid] + P.rank, seq);
-            __shared__ int s_ok2;
-            if (tid == 0) s_ok2 = 1;
-            __syncthreads();
-            if (tid < P.world && !bk_wait_ge<true>(P.flags + tid, seq, P, limit_ns, 5)) s_ok2 = 0;
-            __syncthreads();
-            alive = s_ok2 != 0;
-        }
+        // The only grid-wide meeting of a launch: the argmax reads every CTA's candidate.
+        if (pinfo[p + 1].kind == BK_FINAL) alive = bk_grid_sync(P, barriers_done, limit_ns);
         BK_TRACE(3);
     }
 #undef BK_TRACE
 #undef BK_FT
-    // The launch's exchanges are accounted for (also after an abort, so that the ranks' counters stay in step).
-    if (P.world > 1 && blockIdx.x == 0 && tid == 0) *P.seq = seq_start + (unsigned)P.nexchange;
+    // The launch's sequence numbers are used up (also after an abort, so that the ranks' counters stay in step). Every
+    // CTA read the counter before it produced anything CTA 0's last phases depend on.
+    if (blockIdx.x == 0 && tid == 0) *P.seq = seq_base + (unsigned)P.nphases;
     // Copies still in flight into this CTA's shared memory must land before the CTA may exit.
     for (; consumed < fetched; consumed++) {
         const uint32_t s = consumed % BK_STAGES, parity = (consumed / BK_STAGES) & 1u;
@@ -881,13 +980,14 @@ struct jl_layers {
     bk_phase *phases_dev;
     std::vector<bk_phase> phases;
     float *logits;
+    size_t zero_bytes;           // barrier counter, abort word and attention tickets: cleared in front of every launch
     unsigned long long *trace;   // [2][nphases][4]
     bk_params P;
     bool attached;
 };
 
 static size_t bk_al(size_t n) { return (n + 255) & ~(size_t)255; }
-static size_t bk_slot_bytes(int world, int hidden) { return 2 * bk_al((size_t)world * hidden * 4) + 256; }
+static size_t bk_slot_bytes(int world, int hidden) { return 2 * bk_al((size_t)world * hidden * sizeof(bk_ll)); }
 
 // PrepLayer for every block plus the head (engine/nn/device.go:1099-1102): checks that each weight has a
 // kernel here, builds the phase list and sizes all scratch. Declines (JL_DECLINED) instead of running a
@@ -906,8 +1006,9 @@ JL_EXPORT int jl_layers_prep(jl_ctx *ctx, const jl_layers_desc *d, jl_layers **o
     const int G = hq / hkv;
     if (G != 1 && G != 2 && G != 4)
         return jl_set_err(ctx, JL_DECLINED, "block kernel: %d query heads per kv head (1, 2 or 4 are served)", G);
-    if (H / 256 > BK_MAX_NSB || F / 256 > BK_MAX_NSB || hq * BK_ATT_D / 256 > BK_MAX_NSB)
-        return jl_set_err(ctx, JL_DECLINED, "block kernel: a row longer than %d elements", BK_MAX_NSB * 256);
+    if (H / 256 > BK_WARPS || F / 256 > BK_MAX_NSB || hq * BK_ATT_D / 256 > BK_MAX_NSB)
+        return jl_set_err(ctx, JL_DECLINED, "block kernel: hidden above %d or a row longer than %d elements", BK_WARPS * 256,
+                          BK_MAX_NSB * 256);
     if (!d->cos_t || !d->sin_t) return JL_EINVAL;
     auto okw = [&](const jl_weight *w, int rows, int k) {
         return w && w->type == JL_TYPE_Q4_K && w->n_expert == 1 && w->nrows == rows && w->k == k && w->has_map_sb16;
@@ -936,11 +1037,15 @@ JL_EXPORT int jl_layers_prep(jl_ctx *ctx, const jl_layers_desc *d, jl_layers **o
     size_t off = 0;
     auto take = [&](size_t n) { size_t o = off; off += bk_al(n); return o; };
     const size_t o_ph = take((size_t)nph * sizeof(bk_phase)), o_maps = take((size_t)nmaps * sizeof(CUtensorMap));
-    const size_t o_xa = take((size_t)H * 4), o_xb = take((size_t)H * 4), o_qkv = take((size_t)(hq + 2 * hkv) * BK_ATT_D * 4);
-    const size_t o_att = take((size_t)hq * BK_ATT_D * 4), o_a = take((size_t)F * 4), o_logits = take((size_t)(V > 0 ? V : 1) * 4);
-    const size_t o_part = take((size_t)hkv * nchunk_max * stride * 4), o_tick = take((size_t)hkv * 4);
-    const size_t o_cv = take((size_t)S->grid * 4), o_ci = take((size_t)S->grid * 4), o_bar = take(16), o_seq = take(16);
-    const size_t o_trace = take((size_t)2 * nph * 4 * 8 + (size_t)nph * 12 * 8);
+    const size_t o_qkv = take((size_t)(hq + 2 * hkv) * BK_ATT_D * sizeof(bk_ll));
+    const size_t o_att = take((size_t)hq * BK_ATT_D * sizeof(bk_ll)), o_a = take((size_t)F * sizeof(bk_ll));
+    const size_t o_logits = take((size_t)(V > 0 ? V : 1) * 4);
+    const size_t o_part = take((size_t)hkv * nchunk_max * stride * 4);
+    const size_t o_cv = take((size_t)S->grid * 4), o_ci = take((size_t)S->grid * 4), o_seq = take(16);
+    // zeroed in front of every launch: the grid barrier's counter, the abort word, every attention phase's tickets
+    S->zero_bytes = 16 + (size_t)L * hkv * 4;
+    const size_t o_bar = take(S->zero_bytes);
+    const size_t o_trace = take((size_t)2 * nph * 4 * 8 + (size_t)nph * 12 * 8 + (size_t)S->grid * 8 * 8);
     S->slot_bytes = bk_slot_bytes(world, H);
     cudaError_t e = cudaMalloc(&S->buf, off);
     if (e == cudaSuccess) e = cudaMalloc(&S->slot, S->slot_bytes);
@@ -954,10 +1059,9 @@ JL_EXPORT int jl_layers_prep(jl_ctx *ctx, const jl_layers_desc *d, jl_layers **o
         return jl_set_err(ctx, JL_ENOMEM, "block kernel scratch (%zu bytes): %s", off, cudaGetErrorString(e));
     }
     uint8_t *B = S->buf;
-    float *xa = (float *)(B + o_xa), *xb = (float *)(B + o_xb), *qkv = (float *)(B + o_qkv), *att = (float *)(B + o_att);
-    float *abuf = (float *)(B + o_a);
-    float *planesO = (float *)S->slot, *planesD = (float *)(S->slot + bk_al((size_t)world * H * 4));
-    unsigned *flags = (unsigned *)(S->slot + 2 * bk_al((size_t)world * H * 4));
+    bk_ll *qkv = (bk_ll *)(B + o_qkv), *att = (bk_ll *)(B + o_att), *abuf = (bk_ll *)(B + o_a);
+    bk_ll *planesO = (bk_ll *)S->slot, *planesD = (bk_ll *)(S->slot + bk_al((size_t)world * H * sizeof(bk_ll)));
+    unsigned *tickets = (unsigned *)(B + o_bar + 16);
     S->logits = (float *)(B + o_logits);
     S->trace = (unsigned long long *)(B + o_trace);
     S->phases_dev = (bk_phase *)(B + o_ph);
@@ -979,30 +1083,32 @@ JL_EXPORT int jl_layers_prep(jl_ctx *ctx, const jl_layers_desc *d, jl_layers **o
         maps[4 * l + 3] = map16(b.down);
         bk_phase q = {};
         q.kind = BK_MATVEC; q.map = 4 * l; q.nrows = (hq + 2 * hkv) * BK_ATT_D; q.nsb = H / 256; q.prologue = BK_PRO_NORM;
-        q.epilogue = BK_EPI_STORE; q.from_emb = l == 0; q.xsrc = xb; q.xdst = xa; q.planes = planesD; q.nplanes = l == 0 ? 0 : world;
+        q.epilogue = BK_EPI_STORE; q.from_emb = l == 0; q.planes = planesD; q.nplanes = l == 0 ? 0 : world;
         q.norm_w = b.attn_norm; q.out = qkv;
         S->phases[pi++] = q;
         bk_phase a = {};
-        a.kind = BK_ATTN; a.qkv = qkv; a.att = att; a.k_cache = b.k_cache; a.v_cache = b.v_cache;
+        a.kind = BK_ATTN; a.qkv = qkv; a.att = att; a.k_cache = b.k_cache; a.v_cache = b.v_cache; a.tickets = tickets + (size_t)l * hkv;
         S->phases[pi++] = a;
         bk_phase o = {};
         o.kind = BK_MATVEC; o.map = 4 * l + 1; o.nrows = H; o.nsb = hq * BK_ATT_D / 256; o.prologue = BK_PRO_PLAIN; o.epilogue = BK_EPI_STORE;
         o.vsrc = att; o.out = planesO + (size_t)rank * H; o.exchange = world > 1;
+        o.peer_out[rank] = o.out;
         S->phases[pi++] = o;
         bk_phase gu = {};
         gu.kind = BK_MATVEC; gu.map = 4 * l + 2; gu.nrows = F; gu.nsb = H / 256; gu.prologue = BK_PRO_NORM; gu.epilogue = BK_EPI_GATE2;
-        gu.up_row0 = F; gu.xsrc = xa; gu.xdst = xb; gu.planes = planesO; gu.nplanes = world; gu.norm_w = b.ffn_norm; gu.out = abuf;
+        gu.up_row0 = F; gu.planes = planesO; gu.nplanes = world; gu.norm_w = b.ffn_norm; gu.out = abuf;
         S->phases[pi++] = gu;
         bk_phase dn = {};
         dn.kind = BK_MATVEC; dn.map = 4 * l + 3; dn.nrows = H; dn.nsb = F / 256; dn.prologue = BK_PRO_PLAIN; dn.epilogue = BK_EPI_STORE;
         dn.vsrc = abuf; dn.out = planesD + (size_t)rank * H; dn.exchange = world > 1;
+        dn.peer_out[rank] = dn.out;
         S->phases[pi++] = dn;
     }
     if (d->head) {
         maps[4 * L] = map16(d->head);
         bk_phase h = {};
         h.kind = BK_MATVEC; h.map = 4 * L; h.nrows = V; h.nsb = H / 256; h.prologue = BK_PRO_NORM; h.epilogue = BK_EPI_ARGMAX;
-        h.xsrc = xb; h.xdst = xa; h.planes = planesD; h.nplanes = world; h.norm_w = d->final_norm; h.out = S->logits;
+        h.planes = planesD; h.nplanes = world; h.norm_w = d->final_norm; h.out_f32 = S->logits;
         S->phases[pi++] = h;
         bk_phase f = {};
         f.kind = BK_FINAL;
@@ -1023,9 +1129,9 @@ JL_EXPORT int jl_layers_prep(jl_ctx *ctx, const jl_layers_desc *d, jl_layers **o
     P.phases = S->phases_dev; P.nphases = nph; P.maps = (const CUtensorMap *)(B + o_maps);
     P.hidden = H; P.hq = hq; P.hkv = hkv; P.max_len = d->max_len; P.eps = d->eps; P.cos_t = d->cos_t; P.sin_t = d->sin_t;
     P.emb = (const __nv_bfloat16 *)d->emb_bf16;
-    P.part = (float *)(B + o_part); P.tickets = (unsigned *)(B + o_tick); P.cand_val = (float *)(B + o_cv); P.cand_idx = (int *)(B + o_ci);
+    P.part = (float *)(B + o_part); P.cand_val = (float *)(B + o_cv); P.cand_idx = (int *)(B + o_ci);
     P.bar = (unsigned *)(B + o_bar); P.abort_word = (int *)(B + o_bar) + 1; P.status = ctx->dev_status;
-    P.rank = rank; P.world = world; P.flags = flags; P.seq = (unsigned *)(B + o_seq); P.nexchange = world > 1 ? 2 * L : 0;
+    P.rank = rank; P.world = world; P.seq = (unsigned *)(B + o_seq);
     *out = S;
     return JL_OK;
 }
@@ -1074,17 +1180,15 @@ JL_EXPORT int jl_tp_attach(jl_ctx *ctx, jl_layers *S, void *const *peer_slots, i
     std::lock_guard<std::mutex> lk(ctx->mu);
     JL_CUDA(ctx, cudaSetDevice(ctx->device));
     if (peer_slots[S->rank] != S->slot) return jl_set_err(ctx, JL_EINVAL, "peer_slots[rank] must be this rank's own slot");
-    const size_t plane = bk_al((size_t)S->world * S->hidden * 4);
-    for (int r = 0; r < S->world; r++) {
+    const size_t plane = bk_al((size_t)S->world * S->hidden * sizeof(bk_ll));
+    for (int r = 0; r < S->world; r++)
         if (!peer_slots[r]) return JL_EINVAL;
-        S->P.peer_flags[r] = (unsigned *)((uint8_t *)peer_slots[r] + 2 * plane);
-    }
-    for (bk_phase &ph : S->phases) {
-        if (ph.kind != BK_MATVEC || !ph.exchange) continue;
-        const bool is_down = ph.prologue == BK_PRO_PLAIN && ph.nsb == S->ffn / 256 && ph.vsrc != nullptr &&
-                             ph.out == (float *)(S->slot + plane) + (size_t)S->rank * S->hidden;
-        for (int r = 0; r < S->world; r++)
-            ph.peer_out[r] = (float *)((uint8_t *)peer_slots[r] + (is_down ? plane : 0)) + (size_t)S->rank * S->hidden;
+    for (int l = 0; l < S->n_layer; l++) {
+        bk_phase &o = S->phases[5 * l + 2], &dn = S->phases[5 * l + 4];   // a block's phases: q|k|v, attention, o, gate|up, down
+        for (int r = 0; r < S->world; r++) {
+            o.peer_out[r] = (bk_ll *)peer_slots[r] + (size_t)S->rank * S->hidden;
+            dn.peer_out[r] = (bk_ll *)((uint8_t *)peer_slots[r] + plane) + (size_t)S->rank * S->hidden;
+        }
     }
     JL_CUDA(ctx, cudaMemcpy(S->phases_dev, S->phases.data(), S->phases.size() * sizeof(bk_phase), cudaMemcpyHostToDevice));
     S->attached = true;
@@ -1106,7 +1210,7 @@ static int layers_run_locked(jl_ctx *ctx, jl_layers *S, long long *tok_dev, long
     bk_params P = S->P;
     P.tok = tok_dev; P.pos = pos_dev; P.advance = advance; P.next_tok = next_tok_dev;
     P.trace = trace ? S->trace : nullptr;
-    JL_CUDA(ctx, cudaMemsetAsync(P.bar, 0, 8, s));           // barrier counter and abort word
+    JL_CUDA(ctx, cudaMemsetAsync(P.bar, 0, S->zero_bytes, s));   // barrier counter, abort word, attention tickets
     cudaLaunchAttribute at[1];
     at[0].id = cudaLaunchAttributeCooperative;
     at[0].val.cooperative = 1;                               // all CTAs co-resident: the grid barriers rely on it
@@ -1139,7 +1243,7 @@ JL_EXPORT int jl_layers_profile(jl_ctx *ctx, jl_layers *S, long long *tok_dev, l
     if (n_phases != S->P.nphases) return jl_set_err(ctx, JL_EINVAL, "this stack has %d phases", S->P.nphases);
     size_t bytes = (size_t)2 * n_phases * 4 * 8;
 #ifdef BK_FINE_TRACE
-    bytes += (size_t)n_phases * 12 * 8;   // experimental builds: the consume loop's and the prologue's clock counts follow the stamps
+    bytes += (size_t)n_phases * 12 * 8 + (size_t)S->grid * 8 * 8;   // experimental builds: clock counts of the consume loop and the prologue, per-CTA attention stamps
 #endif
     JL_CUDA(ctx, cudaSetDevice(ctx->device));
     JL_CUDA(ctx, cudaMemsetAsync(S->trace, 0, bytes, (cudaStream_t)stream));

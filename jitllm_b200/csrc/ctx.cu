@@ -505,7 +505,7 @@ int jl_read_status(jl_ctx *ctx, cudaStream_t s) {
     if (e == cudaSuccess) e = cudaStreamSynchronize(s);
     if (e != cudaSuccess) return jl_set_err(ctx, JL_ECUDA, "clearing the status word: %s", cudaGetErrorString(e));
     static const char *const what[] = {"", "a weight tile of the decode kernel never landed", "a ring slot of the prefill GEMM",
-                                       "a ring slot of the grouped expert GEMM", "a grid barrier of the block kernel",
+                                       "a ring slot of the grouped expert GEMM", "a phase's input or the grid barrier inside the block kernel",
                                        "a peer's partial sums (tensor-parallel exchange)", "the test wait"};
     return jl_set_err(ctx, JL_ETIMEDOUT, "a bounded device-side wait ran out (code %d: %s)", code,
                       code > 0 && code < 7 ? what[code] : "unknown");
