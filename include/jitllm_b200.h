@@ -37,8 +37,13 @@ extern "C" {
 /* ggml type ids, format/quant/types.go:12-55. */
 #define JL_TYPE_F32 0u
 #define JL_TYPE_F16 1u
+#define JL_TYPE_Q4_0 2u   /* 32 elements in 18 bytes  {f16 d; u8 qs[16]}               */
+#define JL_TYPE_Q5_0 6u   /* 32 elements in 22 bytes  {f16 d; u32 qh; u8 qs[16]}       */
+#define JL_TYPE_Q5_1 7u   /* 32 elements in 24 bytes  {f16 d, m; u32 qh; u8 qs[16]}    */
 #define JL_TYPE_Q8_0 8u   /* 32 elements in 34 bytes  {f16 d; i8 qs[32]}              */
 #define JL_TYPE_Q4_K 12u  /* 256 elements in 144 bytes {f16 d,dmin; u8 sc[12]; u8 qs[128]} */
+#define JL_TYPE_Q5_K 13u  /* 256 elements in 176 bytes {f16 d,dmin; u8 sc[12]; u8 qh[32]; u8 qs[128]} */
+#define JL_TYPE_Q6_K 14u  /* 256 elements in 210 bytes {u8 ql[128]; u8 qh[64]; i8 sc[16]; f16 d} */
 #define JL_TYPE_BF16 30u
 #define JL_TYPE_MXFP4 39u /* 32 elements in 17 bytes  {u8 e; u8 qs[16]}               */
 
@@ -158,7 +163,10 @@ int jl_stats_get(jl_ctx *ctx, jl_stats *out);
 /* out[0:nrows] = W x. w: raw ggml blocks on the HOST; x, out: host f32. The
  * device copy of w is keyed on (w, w_bytes): the first call uploads (and may
  * repack, bit-exactly), later calls reuse it. The caller guarantees the bytes
- * at w stay unchanged until jl_forget covers them. Types: Q4_K, Q8_0, MXFP4. */
+ * at w stay unchanged until jl_forget covers them. Types: Q4_K, Q8_0, MXFP4 on the tensor-core
+ * decode kernels; Q4_0, Q5_0, Q5_1, Q5_K, Q6_K (what real Q4_K_M files mix in,
+ * format/quant/dequant.go:85-146,399-470) on the one-warp-per-row kernel, which decodes each weight
+ * exactly as quant.Dequant32 does. Any other type is DECLINED. */
 int jl_matvec(jl_ctx *ctx, float *out, uint32_t type, const void *w, size_t w_bytes,
               const float *x, int nrows, int k);
 /* CopyForgetter.Forget (engine/nn/device.go:1570-1581): drop every device copy
@@ -226,8 +234,11 @@ int jl_select(jl_ctx *ctx, uint32_t type, int nrows, int k, int ntok, jl_choice 
 
 /* ---- integer view of the blocks: kernels.extract (jit/gpu/kernels/pack.go:252-386)
  * One record per 32-element sub-block: q[32] codes (Q4_K 0..15, Q8_0 -128..127,
- * MXFP4 raw e2m1 code 0..15), raw f16 bits of d (MXFP4: the stored byte e-1,
- * pack.go:388-395) and dmin, the 6-bit sc and m. n_blocks counts format blocks.
+ * MXFP4 raw e2m1 code 0..15, Q4_0 0..15, Q5_0 / Q5_1 / Q5_K 0..31), raw f16 bits of d
+ * (MXFP4: the stored byte e-1, pack.go:388-395) and dmin (Q5_1: its m with the sign bit
+ * flipped, pack.go:275-290), the 6-bit sc and m. Q6_K: one record per SIXTEEN elements,
+ * q[16] in 0..63 and sc = the int8 scale biased by 128 (pack.go:367-384). n_blocks counts
+ * format blocks; q holds one code per element in every case.
  * jl_unpack runs on the host; jl_unpack_resident reads the DEVICE-RESIDENT
  * (possibly repacked) copy back through a kernel, which is how a repack is
  * shown to be bit-exact. Host output buffers in both. */

@@ -13,6 +13,7 @@ LIB_PATH = os.environ.get("JITLLM_B200_LIB") or os.path.join(HERE, "libjitllm_b2
 
 # ggml type ids (include/jitllm_b200.h)
 F32, F16, Q8_0, Q4_K, BF16, MXFP4 = 0, 1, 8, 12, 30, 39
+Q4_0, Q5_0, Q5_1, Q5_K, Q6_K = 2, 6, 7, 13, 14
 DT_F32, DT_F16, DT_BF16 = 0, 1, 2
 K_AUTO, K_SIMT, K_MMA, K_TC5 = 0, 1, 2, 3
 ACT_SILU, ACT_SWIGLU_OAI = 0, 1
@@ -23,7 +24,8 @@ FORM_AUTO, FORM_SPLIT, FORM_FUSED, FORM_WIDE, FORM_L1 = 0, 1, 2, 3, 4
 OK, DECLINED = 0, 1
 EINVAL, ECUDA, ENOMEM, EDEVICE, ETIMEDOUT, ENOTSUP, ECOMM = -1, -2, -3, -4, -5, -6, -7
 
-BLOCK = {Q8_0: (32, 34), Q4_K: (256, 144), MXFP4: (32, 17), F32: (1, 4), F16: (1, 2), BF16: (1, 2)}
+BLOCK = {Q8_0: (32, 34), Q4_K: (256, 144), MXFP4: (32, 17), F32: (1, 4), F16: (1, 2), BF16: (1, 2),
+         Q4_0: (32, 18), Q5_0: (32, 22), Q5_1: (32, 24), Q5_K: (256, 176), Q6_K: (256, 210)}
 
 
 def row_bytes(t: int, k: int) -> int:

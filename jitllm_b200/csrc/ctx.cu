@@ -55,6 +55,7 @@ JL_EXPORT int jl_open(int device, const jl_opts *opts, jl_ctx **out) {
     c->dev_status = nullptr;
     c->stat_pin = nullptr;
     c->moe_stage = nullptr; c->moe_stage_cap = 0;
+    c->x_map = c->o_map = nullptr; c->x_map_cap = c->o_map_cap = 0; c->done_map = nullptr; c->done_seq = 0;
     const int words[2] = {0, (int)c->opts.wait_limit_us};
     if (cudaMalloc(&c->dev_status, sizeof words) != cudaSuccess ||
         cudaMemcpy(c->dev_status, words, sizeof words, cudaMemcpyHostToDevice) != cudaSuccess ||
@@ -79,6 +80,9 @@ JL_EXPORT void jl_close(jl_ctx *ctx) {
     ctx->graveyard.clear();
     if (ctx->moe_stage) cudaFree(ctx->moe_stage);
     if (ctx->stat_pin) cudaFreeHost(ctx->stat_pin);
+    if (ctx->x_map) cudaFreeHost(ctx->x_map);
+    if (ctx->o_map) cudaFreeHost(ctx->o_map);
+    if (ctx->done_map) cudaFreeHost((void *)ctx->done_map);
     if (ctx->x_dev) cudaFree(ctx->x_dev);
     if (ctx->o_dev) cudaFree(ctx->o_dev);
     if (ctx->scratch) cudaFree(ctx->scratch);
@@ -126,8 +130,26 @@ int jl_grow_scratch(jl_ctx *ctx, size_t need) {
     return grow_dev(ctx, &ctx->scratch, &ctx->scratch_cap, need);
 }
 
+static int grow_map(jl_ctx *ctx, void **p, size_t *cap, size_t need) {
+    if (*cap >= need) return JL_OK;
+    if (*p) { cudaStreamSynchronize(ctx->stream); cudaFreeHost(*p); *p = nullptr; *cap = 0; }
+    cudaError_t e = cudaHostAlloc(p, need, cudaHostAllocMapped);
+    if (e != cudaSuccess) { cudaGetLastError(); return jl_set_err(ctx, JL_ENOMEM, "cudaHostAlloc(%zu): %s", need, cudaGetErrorString(e)); }
+    *cap = need;
+    return JL_OK;
+}
+
 static int reserve_locked(jl_ctx *ctx, size_t x_bytes, size_t o_bytes) {
     int rc;
+    // the decode call's zero-copy staging (a few tokens at most)
+    if ((rc = grow_map(ctx, &ctx->x_map, &ctx->x_map_cap, x_bytes < (1u << 20) ? x_bytes : (1u << 20)))) return rc;
+    if ((rc = grow_map(ctx, &ctx->o_map, &ctx->o_map_cap, o_bytes < (1u << 22) ? o_bytes : (1u << 22)))) return rc;
+    if (!ctx->done_map) {
+        void *p = nullptr;
+        if (cudaHostAlloc(&p, 64, cudaHostAllocMapped) != cudaSuccess) { cudaGetLastError(); return jl_set_err(ctx, JL_ENOMEM, "cudaHostAlloc(64)"); }
+        memset(p, 0, 64);
+        ctx->done_map = (volatile int *)p;
+    }
     if ((rc = grow_dev(ctx, &ctx->x_dev, &ctx->x_cap, x_bytes))) return rc;
     if ((rc = grow_dev(ctx, &ctx->o_dev, &ctx->o_cap, o_bytes))) return rc;
     if ((rc = grow_pin(ctx, &ctx->x_pin, &ctx->x_pin_cap, x_bytes))) return rc;
@@ -354,8 +376,7 @@ JL_EXPORT int jl_select(jl_ctx *ctx, uint32_t type, int nrows, int k, int ntok, 
     if (!ctx || !out) return JL_EINVAL;
     std::lock_guard<std::mutex> lk(ctx->mu);
     int be = jl_block_elems(type);
-    if ((type != JL_TYPE_Q4_K && type != JL_TYPE_Q8_0 && type != JL_TYPE_MXFP4) || nrows < 1 || k < be ||
-        k % be || ntok < 1)
+    if (!jl_type_served(type) || nrows < 1 || k < be || k % be || ntok < 1)
         return jl_set_err(ctx, JL_DECLINED, "no kernel for type %u, %d x %d, %d token(s)", type, nrows, k, ntok);
     return choose(ctx, type, nrows, k, ntok, out);
 }
@@ -435,10 +456,41 @@ JL_EXPORT int jl_matmul_dev(jl_ctx *ctx, void *out_dev, int out_dtype, const jl_
 
 static size_t dtype_bytes(int dt) { return dt == JL_DT_F32 ? 4 : 2; }
 
+// Last kernel of a zero-copy decode call: the status word and then the call's sequence number, into pinned host memory.
+__global__ void jl_done_kernel(int *status, volatile int *done, int seq) {
+    const int code = *status;
+    if (code) *status = 0;
+    done[1] = code;
+    __threadfence_system();
+    done[0] = seq;
+}
+
+// Waits for the call's sequence number to arrive in pinned memory: polls the word; now and then asks the stream
+// whether it failed, so that a kernel fault ends the wait with the error instead of an endless poll.
+static int jl_wait_done(jl_ctx *ctx) {
+    const int seq = ++ctx->done_seq;
+    jl_done_kernel<<<1, 1, 0, ctx->stream>>>(ctx->dev_status, ctx->done_map, seq);
+    ctx->st.launches++;
+    JL_CUDA(ctx, cudaGetLastError());
+    for (unsigned spins = 0;; spins++) {
+        if (ctx->done_map[0] == seq) break;
+        if ((spins & 0xFFFu) == 0xFFFu) {
+            const cudaError_t q = cudaStreamQuery(ctx->stream);
+            if (q != cudaSuccess && q != cudaErrorNotReady) {
+                ctx->unhealthy = true;
+                return jl_set_err(ctx, JL_ECUDA, "kernel failed: %s", cudaGetErrorString(q));
+            }
+        }
+    }
+    const int code = ctx->done_map[1];
+    if (code) return jl_set_err(ctx, JL_ETIMEDOUT, "a bounded device-side wait ran out (code %d)", code);
+    return JL_OK;
+}
+
 static int matmul_host(jl_ctx *ctx, void *out, int out_dtype, uint32_t type, const void *w, size_t w_bytes,
                        const void *x, int x_dtype, int nrows, int k, int ntok) {
     int be = jl_block_elems(type);
-    if (type != JL_TYPE_Q4_K && type != JL_TYPE_Q8_0 && type != JL_TYPE_MXFP4)
+    if (!jl_type_served(type))
         return jl_set_err(ctx, JL_DECLINED, "type %u is not served", type);
     if (nrows < 1 || k < be || k % be || ntok < 1)
         return jl_set_err(ctx, JL_DECLINED, "shape %d x %d x %d tokens does not tile %d-element blocks", nrows, k, ntok, be);
@@ -461,6 +513,28 @@ static int matmul_host(jl_ctx *ctx, void *out, int out_dtype, uint32_t type, con
         const size_t need_gemm = jl_gemm_tc5_scratch_bytes(nrows, k, ntok, x_dtype, ctx->sm_count);
         if (need_gemm > need) need = need_gemm;
         if ((rc = jl_grow_scratch(ctx, need))) return rc;
+    }
+    {
+        // Decode calls (a few tokens, f32 in and out): no copy engine and no stream synchronisation on the path. The
+        // kernels read x from and write y to pinned host memory directly (16 KB each way at 4096 x 4096), a last
+        // one-warp kernel posts the status word and a sequence number there, and the host polls that word. The
+        // activation row is converted by the prep launch (read across the bus ONCE), so the forms in which every
+        // CTA converts the row itself are not used here.
+        jl_choice ch;
+        if (x_dtype == JL_DT_F32 && out_dtype == JL_DT_F32 && xb <= ctx->x_map_cap && ob <= ctx->o_map_cap && ctx->done_map &&
+            choose(ctx, type, nrows, k, ntok, &ch) == JL_OK && ch.kernel == JL_K_MMA) {
+            const int saved_form = ctx->opts.decode_form;
+            if (ch.kernel == JL_K_MMA && type == JL_TYPE_Q4_K && (ch.form == JL_FORM_WIDE || ch.form == JL_FORM_FUSED))
+                ctx->opts.decode_form = JL_FORM_SPLIT;
+            memcpy(ctx->x_map, x, xb);
+            rc = matmul_dev_locked(ctx, ctx->o_map, out_dtype, dw, 0, ctx->x_map, x_dtype, ntok, ctx->stream);
+            ctx->opts.decode_form = saved_form;
+            if (rc) return rc;
+            if ((rc = jl_wait_done(ctx))) return rc;
+            memcpy(out, ctx->o_map, ob);
+            ctx->st.served++;
+            return JL_OK;
+        }
     }
     memcpy(ctx->x_pin, x, xb);
     JL_CUDA(ctx, cudaMemcpyAsync(ctx->x_dev, ctx->x_pin, xb, cudaMemcpyHostToDevice, ctx->stream));

@@ -24,6 +24,8 @@ __host__ __device__ static inline void q4k_scale_min(int j, const uint8_t *q, ui
     }
 }
 
+#include "raw_formats.cuh"
+
 JL_EXPORT int jl_unpack(uint32_t type, const void *blocks, size_t n_blocks, int8_t *q, uint16_t *d_bits,
                         uint16_t *dmin_bits, uint8_t *sc, uint8_t *m) {
     if (!blocks || !q || !d_bits || !dmin_bits || !sc || !m) return JL_EINVAL;
@@ -59,6 +61,18 @@ JL_EXPORT int jl_unpack(uint32_t type, const void *blocks, size_t n_blocks, int8
             }
         }
         return JL_OK;
+    case JL_TYPE_Q4_0: case JL_TYPE_Q5_0: case JL_TYPE_Q5_1: case JL_TYPE_Q5_K: case JL_TYPE_Q6_K: {
+        // element by element through the same accessors the kernels use (raw_formats.cuh)
+        const int be = jl_block_elems(type), bb = jl_block_bytes(type), sub = type == JL_TYPE_Q6_K ? 16 : 32;
+        for (size_t b = 0; b < n_blocks; b++) {
+            const uint8_t *blk = src + b * bb;
+            for (int s = 0; s < be / sub; s++, r++) {
+                for (int l = 0; l < sub; l++) q[r * sub + l] = (int8_t)jl_raw_code(type, blk, s * sub + l);
+                jl_raw_record(type, blk, s, &d_bits[r], &dmin_bits[r], &sc[r], &m[r]);
+            }
+        }
+        return JL_OK;
+    }
     }
     return JL_ENOTSUP;
 }
@@ -116,7 +130,7 @@ void jl_weight_release(jl_weight *w) {
 int jl_repack_upload(jl_ctx *ctx, uint32_t type, const void *w_host, size_t w_bytes, int n_expert,
                      int nrows, int k, jl_weight **out) {
     int be = jl_block_elems(type);
-    if (type != JL_TYPE_Q4_K && type != JL_TYPE_Q8_0 && type != JL_TYPE_MXFP4)
+    if (!jl_type_served(type))
         return jl_set_err(ctx, JL_DECLINED, "type %u has no resident layout", type);
     if (nrows < 1 || k < be || k % be || n_expert < 1)
         return jl_set_err(ctx, JL_DECLINED, "shape %d x %d does not tile %d-element blocks", nrows, k, be);
@@ -143,12 +157,12 @@ int jl_repack_upload(jl_ctx *ctx, uint32_t type, const void *w_host, size_t w_by
         if (w->emin > w->emax) { w->emin = 127; w->emax = 127; }
     }
     cudaError_t e;
-    if (type == JL_TYPE_Q4_K) {
+    if (type == JL_TYPE_Q4_K || jl_type_raw_simt(type)) {
         // +16 so a kernel may over-read one aligned chunk past the end.
         w->data_bytes = need;
         if ((e = cudaMalloc(&w->data, need + 16)) != cudaSuccess) goto oom;
         if ((e = cudaMemcpyAsync(w->data, w_host, need, cudaMemcpyHostToDevice, ctx->stream)) != cudaSuccess) goto fail;
-        w->has_map_sb16 = jl_make_tmap_2d(&w->map_sb16, w->data, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1,
+        if (type == JL_TYPE_Q4_K) w->has_map_sb16 = jl_make_tmap_2d(&w->map_sb16, w->data, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1,
                                           jl_row_bytes(type, k), rows, jl_row_bytes(type, k), 144, 16,
                                           CU_TENSOR_MAP_SWIZZLE_NONE);
     } else {
@@ -219,6 +233,18 @@ __global__ void unpack_resident_kernel(uint32_t type, const uint8_t *__restrict_
             dmin_bits[r] = (uint16_t)(blk[2] | (blk[3] << 8));
             const uint8_t *grp = blk + 16 + (s / 2) * 32;
             for (int l = 0; l < 32; l++) q[r * 32 + l] = (int8_t)((s & 1) ? (grp[l] >> 4) : (grp[l] & 0xF));
+        } else if (jl_type_raw_simt(type)) {
+            // raw blocks: sub-block si of the row (Q6_K: two 16-element records)
+            const int be = jl_block_elems(type), bb = jl_block_bytes(type);
+            const uint8_t *blk = data + (row * (size_t)(k / be) + (size_t)(si * 32 / be)) * bb;
+            const int e0 = (si * 32) % be;
+            for (int l = 0; l < 32; l++) q[r * 32 + l] = (int8_t)jl_raw_code(type, blk, e0 + l);
+            if (type == JL_TYPE_Q6_K) {
+                jl_raw_record(type, blk, e0 / 16, &d_bits[2 * r], &dmin_bits[2 * r], &sc[2 * r], &m[2 * r]);
+                jl_raw_record(type, blk, e0 / 16 + 1, &d_bits[2 * r + 1], &dmin_bits[2 * r + 1], &sc[2 * r + 1], &m[2 * r + 1]);
+            } else {
+                jl_raw_record(type, blk, e0 / 32, &d_bits[r], &dmin_bits[r], &sc[r], &m[r]);
+            }
         } else if (type == JL_TYPE_Q8_0) {
             const uint8_t *span = data + row * (size_t)k + (size_t)(si >> 1) * 64;
             for (int l = 0; l < 32; l++) q[r * 32 + l] = (int8_t)span[q8_span_pos((si & 1) * 32 + l)];
@@ -243,12 +269,13 @@ JL_EXPORT int jl_unpack_resident(jl_ctx *ctx, const jl_weight *w, int8_t *q, uin
     JL_CUDA(ctx, cudaSetDevice(ctx->device));
     size_t rows = (size_t)w->n_expert * (size_t)w->nrows;
     size_t nsub = rows * (size_t)(w->k / 32);
+    const size_t nrec = w->type == JL_TYPE_Q6_K ? 2 * nsub : nsub;   // Q6_K: a record per 16 elements
     int8_t *dq = nullptr; uint16_t *dd = nullptr, *ddm = nullptr; uint8_t *dsc = nullptr, *dm = nullptr;
     cudaError_t e = cudaMalloc(&dq, nsub * 32);
-    if (e == cudaSuccess) e = cudaMalloc(&dd, nsub * 2);
-    if (e == cudaSuccess) e = cudaMalloc(&ddm, nsub * 2);
-    if (e == cudaSuccess) e = cudaMalloc(&dsc, nsub);
-    if (e == cudaSuccess) e = cudaMalloc(&dm, nsub);
+    if (e == cudaSuccess) e = cudaMalloc(&dd, nrec * 2);
+    if (e == cudaSuccess) e = cudaMalloc(&ddm, nrec * 2);
+    if (e == cudaSuccess) e = cudaMalloc(&dsc, nrec);
+    if (e == cudaSuccess) e = cudaMalloc(&dm, nrec);
     if (e == cudaSuccess) {
         int grid = (int)((nsub + 127) / 128 < 148 * 8 ? (nsub + 127) / 128 : 148 * 8);
         unpack_resident_kernel<<<grid, 128, 0, ctx->stream>>>(w->type, w->data, w->scales, w->scale_stride,
@@ -257,10 +284,10 @@ JL_EXPORT int jl_unpack_resident(jl_ctx *ctx, const jl_weight *w, int8_t *q, uin
         e = cudaGetLastError();
     }
     if (e == cudaSuccess) e = cudaMemcpyAsync(q, dq, nsub * 32, cudaMemcpyDeviceToHost, ctx->stream);
-    if (e == cudaSuccess) e = cudaMemcpyAsync(d_bits, dd, nsub * 2, cudaMemcpyDeviceToHost, ctx->stream);
-    if (e == cudaSuccess) e = cudaMemcpyAsync(dmin_bits, ddm, nsub * 2, cudaMemcpyDeviceToHost, ctx->stream);
-    if (e == cudaSuccess) e = cudaMemcpyAsync(sc, dsc, nsub, cudaMemcpyDeviceToHost, ctx->stream);
-    if (e == cudaSuccess) e = cudaMemcpyAsync(m, dm, nsub, cudaMemcpyDeviceToHost, ctx->stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(d_bits, dd, nrec * 2, cudaMemcpyDeviceToHost, ctx->stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(dmin_bits, ddm, nrec * 2, cudaMemcpyDeviceToHost, ctx->stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(sc, dsc, nrec, cudaMemcpyDeviceToHost, ctx->stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(m, dm, nrec, cudaMemcpyDeviceToHost, ctx->stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
     cudaFree(dq); cudaFree(dd); cudaFree(ddm); cudaFree(dsc); cudaFree(dm);
     if (e != cudaSuccess) {

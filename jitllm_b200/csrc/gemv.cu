@@ -21,6 +21,7 @@
 //                  is run-to-run bit-stable.
 #include "jl_internal.cuh"
 #include "tma.cuh"
+#include "raw_formats.cuh"
 
 #include <stdio.h>
 
@@ -96,6 +97,13 @@ __global__ void __launch_bounds__(256) gemv_simt_kernel(const uint8_t *__restric
                 float w = __fmul_rn(d, (float)(int8_t)span[q8_span_pos((si & 1) * 32 + l)]);
                 acc = fmaf(w, xs[l], acc);
             }
+        } else if (jl_type_raw_simt(TYPE)) {
+            // raw ggml blocks; each weight exactly as quant.Dequant32 forms it
+            constexpr int BE = TYPE == JL_TYPE_Q5_K || TYPE == JL_TYPE_Q6_K ? 256 : 32;
+            constexpr int BB = TYPE == JL_TYPE_Q4_0 ? 18 : TYPE == JL_TYPE_Q5_0 ? 22 : TYPE == JL_TYPE_Q5_1 ? 24 : TYPE == JL_TYPE_Q5_K ? 176 : 210;
+            const uint8_t *blk = data + ((size_t)row * (k / BE) + (size_t)(si * 32 / BE)) * BB;
+            const int e0 = (si * 32) % BE;
+            for (int l = 0; l < 32; l++) acc = fmaf(jl_raw_weight(TYPE, blk, e0 + l), xs[l], acc);
         } else {  // MXFP4
             const uint8_t *c = data + ((size_t)row * nsub + si) * 16;
             int e = scales[(size_t)row * scale_stride + si];
@@ -495,7 +503,7 @@ int jl_launch_gemv(jl_ctx *ctx, float *out_dev, const jl_weight *w, int expert, 
     size_t rows_off = (size_t)expert * nrows;
     const uint8_t *data = w->data;
     const uint8_t *scales = w->scales;
-    if (w->type == JL_TYPE_Q4_K) data += rows_off * jl_row_bytes(w->type, k);
+    if (w->type == JL_TYPE_Q4_K || jl_type_raw_simt(w->type)) data += rows_off * jl_row_bytes(w->type, k);
     else if (w->type == JL_TYPE_Q8_0) { data += rows_off * (size_t)k; scales += rows_off * (size_t)w->scale_stride * 2; }
     else { data += rows_off * (size_t)(k / 32) * 16; scales += rows_off * (size_t)w->scale_stride; }
 
@@ -546,8 +554,12 @@ int jl_launch_gemv(jl_ctx *ctx, float *out_dev, const jl_weight *w, int expert, 
             gemv_simt_kernel<JL_TYPE_Q4_K><<<grid, 256, 0, s>>>(data, scales, w->scale_stride, x_dev, out_dev, nrows, k, ntok);
         else if (w->type == JL_TYPE_Q8_0)
             gemv_simt_kernel<JL_TYPE_Q8_0><<<grid, 256, 0, s>>>(data, scales, w->scale_stride, x_dev, out_dev, nrows, k, ntok);
-        else
+        else if (w->type == JL_TYPE_MXFP4)
             gemv_simt_kernel<JL_TYPE_MXFP4><<<grid, 256, 0, s>>>(data, scales, w->scale_stride, x_dev, out_dev, nrows, k, ntok);
+#define JL_SIMT_RAW(T) else if (w->type == T) gemv_simt_kernel<T><<<grid, 256, 0, s>>>(data, scales, w->scale_stride, x_dev, out_dev, nrows, k, ntok);
+        JL_SIMT_RAW(JL_TYPE_Q4_0) JL_SIMT_RAW(JL_TYPE_Q5_0) JL_SIMT_RAW(JL_TYPE_Q5_1) JL_SIMT_RAW(JL_TYPE_Q5_K) JL_SIMT_RAW(JL_TYPE_Q6_K)
+#undef JL_SIMT_RAW
+        else return jl_set_err(ctx, JL_DECLINED, "type %u has no decode kernel", w->type);
     }
     ctx->st.launches++;
     JL_CUDA(ctx, cudaGetLastError());

@@ -17,24 +17,36 @@
 #define JL_EXPORT extern "C" __attribute__((visibility("default")))
 
 // Block geometry, format/quant/types.go:61-85.
-static inline int jl_block_elems(uint32_t t) {
+__host__ __device__ static inline int jl_block_elems(uint32_t t) {
     switch (t) {
-    case JL_TYPE_Q8_0: return 32;
-    case JL_TYPE_Q4_K: return 256;
+    case JL_TYPE_Q8_0: case JL_TYPE_Q4_0: case JL_TYPE_Q5_0: case JL_TYPE_Q5_1: return 32;
+    case JL_TYPE_Q4_K: case JL_TYPE_Q5_K: case JL_TYPE_Q6_K: return 256;
     case JL_TYPE_MXFP4: return 32;
     case JL_TYPE_F32: case JL_TYPE_F16: case JL_TYPE_BF16: return 1;
     }
     return 0;
 }
-static inline int jl_block_bytes(uint32_t t) {
+__host__ __device__ static inline int jl_block_bytes(uint32_t t) {
     switch (t) {
     case JL_TYPE_Q8_0: return 34;
+    case JL_TYPE_Q4_0: return 18;
+    case JL_TYPE_Q5_0: return 22;
+    case JL_TYPE_Q5_1: return 24;
     case JL_TYPE_Q4_K: return 144;
+    case JL_TYPE_Q5_K: return 176;
+    case JL_TYPE_Q6_K: return 210;
     case JL_TYPE_MXFP4: return 17;
     case JL_TYPE_F32: return 4;
     case JL_TYPE_F16: case JL_TYPE_BF16: return 2;
     }
     return 0;
+}
+// Formats that stay as raw ggml blocks on the device and run on the one-warp-per-row kernel only.
+__host__ __device__ static inline bool jl_type_raw_simt(uint32_t t) {
+    return t == JL_TYPE_Q4_0 || t == JL_TYPE_Q5_0 || t == JL_TYPE_Q5_1 || t == JL_TYPE_Q5_K || t == JL_TYPE_Q6_K;
+}
+static inline bool jl_type_served(uint32_t t) {
+    return t == JL_TYPE_Q4_K || t == JL_TYPE_Q8_0 || t == JL_TYPE_MXFP4 || jl_type_raw_simt(t);
 }
 static inline size_t jl_row_bytes(uint32_t t, int k) {
     return (size_t)(k / jl_block_elems(t)) * (size_t)jl_block_bytes(t);
@@ -52,6 +64,7 @@ static inline size_t jl_row_bytes(uint32_t t, int k) {
 //          which one mma.sync lane consumes them. scales = f16 d, [row][k/32].
 //   MXFP4  data = the 16 code bytes of each block, [row][k/32][16];
 //          scales = the e8m0 byte of each block, [row][scale_stride].
+//   Q4_0, Q5_0, Q5_1, Q5_K, Q6_K   data = the raw blocks, untouched.
 struct jl_weight {
     uint32_t type;
     int n_expert, nrows, k;
@@ -85,6 +98,11 @@ struct jl_ctx {
     std::vector<jl_weight *> graveyard; // copies jl_forget dropped; freed by the next serving call
     void *moe_stage; size_t moe_stage_cap;   // jl_moe's device staging (h, logits, out, sel, wt, biases)
     int *stat_pin;          // pinned word the status rides home in
+    // the decode call's zero-copy staging: pinned host memory the kernels read x from and write y to directly
+    void *x_map; size_t x_map_cap;
+    void *o_map; size_t o_map_cap;
+    volatile int *done_map; // pinned {sequence number, status}: written by the call's last kernel, polled by the host
+    int done_seq;
     // staging for the host entry points (grown by jl_reserve or on demand).
     void *x_dev; size_t x_cap;
     void *o_dev; size_t o_cap;

@@ -71,9 +71,10 @@ class Weight:
         self.handle = 0
 
     def unpack(self):
-        """Integer view of the RESIDENT copy: (q, d_bits, dmin_bits, sc, m) per 32-sub-block."""
-        nsub = self.n_expert * self.nrows * (self.k // 32)
-        q = np.empty(nsub * 32, np.int8)
+        """Integer view of the RESIDENT copy: (q, d_bits, dmin_bits, sc, m), a record per 32 elements (Q6_K: per 16)."""
+        sub = 16 if self.type == _lib.Q6_K else 32
+        nsub = self.n_expert * self.nrows * (self.k // sub)
+        q = np.empty(nsub * sub, np.int8)
         d = np.empty(nsub, np.uint16)
         dm = np.empty(nsub, np.uint16)
         sc = np.empty(nsub, np.uint8)
@@ -313,8 +314,9 @@ class Device:
 def unpack_host(t: int, blocks, n_blocks: int):
     """jl_unpack: the host implementation of kernels.extract over raw blocks."""
     lib = _lib.load()
-    nsub = n_blocks * (_lib.BLOCK[t][0] // 32)
-    q = np.empty(nsub * 32, np.int8)
+    sub = 16 if t == _lib.Q6_K else 32
+    nsub = n_blocks * (_lib.BLOCK[t][0] // sub)
+    q = np.empty(nsub * sub, np.int8)
     d = np.empty(nsub, np.uint16)
     dm = np.empty(nsub, np.uint16)
     sc = np.empty(nsub, np.uint8)

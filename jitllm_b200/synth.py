@@ -13,7 +13,7 @@ from __future__ import annotations
 
 import numpy as np
 
-from ._lib import MXFP4, Q4_K, Q8_0
+from ._lib import BLOCK, MXFP4, Q4_0, Q4_K, Q5_0, Q5_1, Q5_K, Q6_K, Q8_0
 
 
 def rng_for(seed: int) -> np.random.Generator:
@@ -97,7 +97,23 @@ def mxfp4_matrix(rng: np.random.Generator, nrows: int, k: int, e_lo: int = -8, e
     return mxfp4_from_parts(e, codes).reshape(nrows, (k // 32) * 17)
 
 
+def random_blocks(rng: np.random.Generator, t: int, nrows: int, k: int, d_sigma: float = 0.02) -> np.ndarray:
+    """Random tensor of a format whose every payload bit pattern is a valid code (Q4_0, Q5_0, Q5_1, Q5_K, Q6_K):
+    uniform random payload bytes, and every f16 scale field = f16(|N(0, d_sigma)|) so that no value is Inf or NaN."""
+    be, bb = BLOCK[t]
+    nb = nrows * (k // be)
+    blk = rng.integers(0, 256, (nb, bb), dtype=np.uint8)
+    halves = {Q4_0: (0,), Q5_0: (0,), Q5_1: (0, 2), Q5_K: (0, 2), Q6_K: (208,)}[t]
+    for off in halves:
+        h = np.abs(rng.normal(0.0, d_sigma, nb)).astype(np.float16).view(np.uint16)
+        blk[:, off] = h & 0xFF
+        blk[:, off + 1] = h >> 8
+    return blk.reshape(nrows, (k // be) * bb)
+
+
 def matrix(rng: np.random.Generator, t: int, nrows: int, k: int) -> np.ndarray:
+    if t in (Q4_0, Q5_0, Q5_1, Q5_K, Q6_K):
+        return random_blocks(rng, t, nrows, k)
     if t == Q4_K:
         return q4k_matrix(rng, nrows, k)
     if t == Q8_0:

@@ -17,6 +17,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _SO = os.path.join(_HERE, "libjl_oracle.so")
 
 F32, F16, Q8_0, Q4_K, BF16, MXFP4 = 0, 1, 8, 12, 30, 39
+Q4_0, Q5_0, Q5_1, Q5_K, Q6_K = 2, 6, 7, 13, 14
 
 
 def build(force: bool = False) -> str:
@@ -97,10 +98,12 @@ def dequant64(t: int, src, n: int) -> np.ndarray:
 
 
 def unpack(t: int, src, nblocks: int):
-    """Integer view of the blocks: (q[int8, nsub*32], d_bits, dmin_bits, sc, m) per 32-sub-block."""
+    """Integer view of the blocks: (q[int8, one per element], d_bits, dmin_bits, sc, m), one record per 32-element
+    sub-block (Q6_K: per 16 elements, as the reference's extract has it)."""
     s = _bytes(src)
-    nsub = nblocks * (block_elems(t) // 32)
-    q = np.empty(nsub * 32, dtype=np.int8)
+    sub = 16 if t == Q6_K else 32
+    nsub = nblocks * (block_elems(t) // sub)
+    q = np.empty(nsub * sub, dtype=np.int8)
     d = np.empty(nsub, dtype=np.uint16)
     dmin = np.empty(nsub, dtype=np.uint16)
     sc = np.empty(nsub, dtype=np.uint8)

@@ -31,14 +31,15 @@
 #define ORC_API __attribute__((visibility("default")))
 
 /* ggml type ids -- format/quant/types.go:12-55 */
-enum { ORC_F32 = 0, ORC_F16 = 1, ORC_Q8_0 = 8, ORC_Q4_K = 12, ORC_BF16 = 30, ORC_MXFP4 = 39 };
+enum { ORC_F32 = 0, ORC_F16 = 1, ORC_Q4_0 = 2, ORC_Q5_0 = 6, ORC_Q5_1 = 7, ORC_Q8_0 = 8, ORC_Q4_K = 12, ORC_Q5_K = 13,
+       ORC_Q6_K = 14, ORC_BF16 = 30, ORC_MXFP4 = 39 };
 
 /* format/quant/types.go:61-85 (blockInfo): elements and bytes per block. */
 ORC_API int orc_block_elems(uint32_t t) {
     switch (t) {
     case ORC_F32: case ORC_F16: case ORC_BF16: return 1;
-    case ORC_Q8_0: return 32;
-    case ORC_Q4_K: return 256;
+    case ORC_Q8_0: case ORC_Q4_0: case ORC_Q5_0: case ORC_Q5_1: return 32;
+    case ORC_Q4_K: case ORC_Q5_K: case ORC_Q6_K: return 256;
     case ORC_MXFP4: return 32;
     }
     return 0;
@@ -48,7 +49,12 @@ ORC_API int orc_block_bytes(uint32_t t) {
     case ORC_F32: return 4;
     case ORC_F16: case ORC_BF16: return 2;
     case ORC_Q8_0: return 34;
+    case ORC_Q4_0: return 18;
+    case ORC_Q5_0: return 22;
+    case ORC_Q5_1: return 24;
     case ORC_Q4_K: return 144;
+    case ORC_Q5_K: return 176;
+    case ORC_Q6_K: return 210;
     case ORC_MXFP4: return 17;
     }
     return 0;
@@ -185,6 +191,85 @@ static const int8_t k_mxfp4[16] = {0, 1, 2, 3, 4, 6, 8, 12, 0, -1, -2, -3, -4, -
             }                                                                               \
         }                                                                                   \
         break;                                                                              \
+    case ORC_Q4_0: /* dequant.go:85-101: {f16 d; u8 qs[16]}, lo = j, hi = j + 16, (q - 8) d in f64 */ \
+        for (size_t b = 0; b < blocks; b++) {                                               \
+            const uint8_t *blk = src + b * 18;                                              \
+            double d = orc_half_decode(le16(blk));                                          \
+            for (int j = 0; j < 16; j++) {                                                  \
+                dst[b * 32 + j]      = (T)((double)((int)(blk[2 + j] & 0xF) - 8) * d);      \
+                dst[b * 32 + j + 16] = (T)((double)((int)(blk[2 + j] >> 4) - 8) * d);       \
+            }                                                                               \
+        }                                                                                   \
+        break;                                                                              \
+    case ORC_Q5_0: /* dequant.go:103-125: {f16 d; u32 qh; u8 qs[16]}, element l takes bit l of qh */ \
+    case ORC_Q5_1: /* dequant.go:127-146: {f16 d; f16 m; u32 qh; u8 qs[16]}, d q + m */     \
+        for (size_t b = 0; b < blocks; b++) {                                               \
+            const int one = t == ORC_Q5_1;                                                  \
+            const uint8_t *blk = src + b * (one ? 24 : 22);                                 \
+            double d = orc_half_decode(le16(blk));                                          \
+            double m = one ? orc_half_decode(le16(blk + 2)) : 0;                            \
+            const uint8_t *hp = blk + (one ? 4 : 2), *qs = hp + 4;                          \
+            uint32_t qh = (uint32_t)hp[0] | (uint32_t)hp[1] << 8 | (uint32_t)hp[2] << 16 | (uint32_t)hp[3] << 24; \
+            for (int j = 0; j < 16; j++) {                                                  \
+                int lo = qs[j] & 0xF, hi = qs[j] >> 4;                                      \
+                if (qh & (1u << j)) lo += 16;                                               \
+                if (qh & (1u << (j + 16))) hi += 16;                                        \
+                dst[b * 32 + j]      = one ? (T)((double)lo * d + m) : (T)((double)(lo - 16) * d); \
+                dst[b * 32 + j + 16] = one ? (T)((double)hi * d + m) : (T)((double)(hi - 16) * d); \
+            }                                                                               \
+        }                                                                                   \
+        break;                                                                              \
+    case ORC_Q5_K: /* dequant.go:399-441: {f16 d, dmin; u8 scales[12]; u8 qh[32]; u8 qs[128]} */ \
+        for (size_t b = 0; b < blocks; b++) {                                               \
+            const uint8_t *blk = src + b * 176;                                             \
+            float d = (float)orc_half_decode(le16(blk));                                    \
+            float dmin = (float)orc_half_decode(le16(blk + 2));                             \
+            const uint8_t *scales = blk + 4, *qh = blk + 16, *qs = blk + 48;                \
+            size_t o = b * 256; int is = 0; uint8_t u1 = 1, u2 = 2;                         \
+            for (int j = 0; j < 256; j += 64) {                                             \
+                const uint8_t *q = qs + j / 2;                                              \
+                uint8_t sc1, m1, sc2, m2;                                                   \
+                scale_min_k4(is, scales, &sc1, &m1);                                        \
+                scale_min_k4(is + 1, scales, &sc2, &m2);                                    \
+                volatile float d1 = d * (float)sc1, min1 = dmin * (float)m1;                \
+                volatile float d2 = d * (float)sc2, min2 = dmin * (float)m2;                \
+                for (int l = 0; l < 32; l++) {                                              \
+                    int v = (q[l] & 0xF) + ((qh[l] & u1) ? 16 : 0);                         \
+                    volatile float p = d1 * (float)v;                                       \
+                    volatile float w = p - min1; dst[o++] = (T)(double)w;                   \
+                }                                                                           \
+                for (int l = 0; l < 32; l++) {                                              \
+                    int v = (q[l] >> 4) + ((qh[l] & u2) ? 16 : 0);                          \
+                    volatile float p = d2 * (float)v;                                       \
+                    volatile float w = p - min2; dst[o++] = (T)(double)w;                   \
+                }                                                                           \
+                is += 2; u1 = (uint8_t)(u1 << 2); u2 = (uint8_t)(u2 << 2);                  \
+            }                                                                               \
+        }                                                                                   \
+        break;                                                                              \
+    case ORC_Q6_K: /* dequant.go:443-470: {u8 ql[128]; u8 qh[64]; i8 scales[16]; f16 d}, (d sc) q in f32 */ \
+        for (size_t b = 0; b < blocks; b++) {                                               \
+            const uint8_t *blk = src + b * 210;                                             \
+            float d = (float)orc_half_decode(le16(blk + 208));                              \
+            for (int n = 0; n < 256; n += 128) {                                            \
+                const uint8_t *ql = blk + n / 2, *qh = blk + 128 + n / 4;                   \
+                const int8_t *sc = (const int8_t *)(blk + 192 + n / 16);                    \
+                for (int l = 0; l < 32; l++) {                                              \
+                    int is = l / 16;                                                        \
+                    int q[4];                                                               \
+                    q[0] = (int)(int8_t)((ql[l] & 0xF) | (((qh[l] >> 0) & 3) << 4)) - 32;   \
+                    q[1] = (int)(int8_t)((ql[l + 32] & 0xF) | (((qh[l] >> 2) & 3) << 4)) - 32; \
+                    q[2] = (int)(int8_t)((ql[l] >> 4) | (((qh[l] >> 4) & 3) << 4)) - 32;    \
+                    q[3] = (int)(int8_t)((ql[l + 32] >> 4) | (((qh[l] >> 6) & 3) << 4)) - 32; \
+                    for (int j = 0; j < 4; j++) {                                           \
+                        volatile float ds = d * (float)sc[is + 2 * j];                      \
+                        volatile float w = ds * (float)q[j];                                \
+                        dst[b * 256 + n + 32 * j + l] = (T)(double)w;                       \
+                    }                                                                       \
+                }                                                                           \
+            }                                                                               \
+        }                                                                                   \
+        break;                                                                              \
     default: return -1;                                                                     \
     }                                                                                       \
     (void)bb;                                                                               \
@@ -234,6 +319,64 @@ ORC_API int orc_unpack(uint32_t t, const uint8_t *src, size_t nblocks, int8_t *q
                 for (int l = 0; l < 32; l++)
                     q[r * 32 + l] = (int8_t)((s % 2 == 0) ? (grp[l] & 0xF) : (grp[l] >> 4));
                 d[r] = le16(blk); dmin[r] = le16(blk + 2);
+            }
+        }
+        return 0;
+    case ORC_Q4_0:   /* pack.go:254-259 */
+        for (size_t b = 0; b < nblocks; b++, r++) {
+            const uint8_t *blk = src + b * 18;
+            for (int l = 0; l < 16; l++) {
+                q[r * 32 + l] = (int8_t)(blk[2 + l] & 0xF);
+                q[r * 32 + l + 16] = (int8_t)(blk[2 + l] >> 4);
+            }
+            d[r] = le16(blk); dmin[r] = 0; sc[r] = 0; m[r] = 0;
+        }
+        return 0;
+    case ORC_Q5_0:   /* pack.go:261-273 */
+    case ORC_Q5_1:   /* pack.go:275-290: the minimum goes out with its sign bit flipped */
+        for (size_t b = 0; b < nblocks; b++, r++) {
+            const int one = t == ORC_Q5_1;
+            const uint8_t *blk = src + b * (one ? 24 : 22);
+            const uint8_t *hp = blk + (one ? 4 : 2), *qs = hp + 4;
+            uint32_t qh = (uint32_t)hp[0] | (uint32_t)hp[1] << 8 | (uint32_t)hp[2] << 16 | (uint32_t)hp[3] << 24;
+            for (int l = 0; l < 16; l++) {
+                q[r * 32 + l] = (int8_t)(qs[l] & 0xF);
+                q[r * 32 + l + 16] = (int8_t)(qs[l] >> 4);
+            }
+            for (int l = 0; l < 32; l++)
+                if (qh & (1u << l)) q[r * 32 + l] = (int8_t)(q[r * 32 + l] + 16);
+            d[r] = le16(blk); dmin[r] = one ? (uint16_t)(le16(blk + 2) ^ 0x8000) : 0; sc[r] = 0; m[r] = 0;
+        }
+        return 0;
+    case ORC_Q5_K:   /* pack.go:332-348 */
+        for (size_t b = 0; b < nblocks; b++) {
+            const uint8_t *blk = src + b * 176;
+            for (int s = 0; s < 8; s++, r++) {
+                scale_min_k4(s, blk + 4, &sc[r], &m[r]);
+                const uint8_t *qh = blk + 16, *ql = blk + 48 + (s / 2) * 32;
+                for (int l = 0; l < 32; l++) {
+                    int v = (s % 2 == 1) ? (ql[l] >> 4) : (ql[l] & 0xF);
+                    if (qh[l] & (1u << s)) v += 16;
+                    q[r * 32 + l] = (int8_t)v;
+                }
+                d[r] = le16(blk); dmin[r] = le16(blk + 2);
+            }
+        }
+        return 0;
+    case ORC_Q6_K:   /* pack.go:367-384: one record per SIXTEEN elements; the scale stored biased by 128 */
+        for (size_t b = 0; b < nblocks; b++) {
+            const uint8_t *blk = src + b * 210;
+            for (int s = 0; s < 16; s++, r++) {
+                int g = s / 8, e0 = (s % 8) * 16;
+                const uint8_t *ql = blk + g * 64, *qh = blk + 128 + g * 32;
+                for (int l = 0; l < 16; l++) {
+                    int e = e0 + l, lo = e % 32, sh = 2 * (e / 32);
+                    uint8_t nib = ql[lo + (e / 32) % 2 * 32];
+                    nib = (e / 32 >= 2) ? (uint8_t)(nib >> 4) : (uint8_t)(nib & 0xF);
+                    q[r * 16 + l] = (int8_t)(nib | (((qh[lo] >> sh) & 3) << 4));
+                }
+                d[r] = le16(blk + 208); dmin[r] = 0;
+                sc[r] = (uint8_t)((int)(int8_t)blk[192 + s] + 128); m[r] = 0;
             }
         }
         return 0;

@@ -10,6 +10,7 @@ bit-exactness against:
 
   testdata/golden/dequant/q4_k_tiny.{in,f32}      llama.cpp dequantize_row_q4_K
   testdata/golden/dequant/q8_0_{gemma,minilm,stories}.{in,f32}
+  testdata/golden/dequant/{q4_0_gemma,q4_0_stories,q5_k_tiny,q6_k_tiny}.{in,f32}
   format/quant/testdata/mxfp4.json                gguf-py MXFP4.dequantize_blocks
 
 and writes tests/golden/ref_decoder_vectors.npz (raw block bytes + expected f32
@@ -29,7 +30,8 @@ def main() -> None:
     ref = sys.argv[1]
     out = {}
     dq = os.path.join(ref, "testdata", "golden", "dequant")
-    for name in ("q4_k_tiny", "q8_0_gemma", "q8_0_minilm", "q8_0_stories"):
+    for name in ("q4_k_tiny", "q8_0_gemma", "q8_0_minilm", "q8_0_stories", "q4_0_gemma", "q4_0_stories", "q5_k_tiny",
+                 "q6_k_tiny"):
         out[name + "_blocks"] = np.fromfile(os.path.join(dq, name + ".in"), dtype=np.uint8)
         out[name + "_bits"] = np.fromfile(os.path.join(dq, name + ".f32"), dtype="<u4")
     with open(os.path.join(ref, "format", "quant", "testdata", "mxfp4.json")) as f:

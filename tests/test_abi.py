@@ -46,10 +46,10 @@ def test_open_fails_loudly_without_a_gpu():
         Device(0)
 
 
-@pytest.mark.parametrize("t", [_lib.Q4_K, _lib.Q8_0, _lib.MXFP4])
+@pytest.mark.parametrize("t", [_lib.Q4_K, _lib.Q8_0, _lib.MXFP4, _lib.Q4_0, _lib.Q5_0, _lib.Q5_1, _lib.Q5_K, _lib.Q6_K])
 def test_host_unpack_equals_the_oracle(orc, t):
     rng = synth.rng_for(100 + t)
-    w = synth.matrix(rng, t, 5, 768 if t != _lib.Q4_K else 1024)
+    w = synth.matrix(rng, t, 5, 768 if _lib.BLOCK[t][0] == 32 else 1024)
     nb = w.size // _lib.BLOCK[t][1]
     got = unpack_host(t, w, nb)
     want = orc.unpack(t, w, nb)
@@ -58,7 +58,7 @@ def test_host_unpack_equals_the_oracle(orc, t):
 
 
 def test_host_unpack_on_reference_goldens(orc, golden):
-    for name, t in [("q4_k_tiny", 12), ("q8_0_gemma", 8), ("mxfp4", 39)]:
+    for name, t in [("q4_k_tiny", 12), ("q8_0_gemma", 8), ("mxfp4", 39), ("q4_0_gemma", 2), ("q5_k_tiny", 13), ("q6_k_tiny", 14)]:
         blocks = golden[name + "_blocks"]
         nb = blocks.size // _lib.BLOCK[t][1]
         for g, x in zip(unpack_host(t, blocks, nb), orc.unpack(t, blocks, nb)):
@@ -69,7 +69,7 @@ def test_unpack_rejects_unknown_types():
     lib = _lib.load()
     b = np.zeros(64, np.uint8)
     o = np.zeros(64, np.uint8)
-    assert lib.jl_unpack(2, b.ctypes.data, 1, o.ctypes.data, o.ctypes.data, o.ctypes.data, o.ctypes.data,
+    assert lib.jl_unpack(3, b.ctypes.data, 1, o.ctypes.data, o.ctypes.data, o.ctypes.data, o.ctypes.data,
                          o.ctypes.data) == _lib.ENOTSUP
 
 

@@ -34,6 +34,26 @@ def test_matvec_check_kernel_matches_oracle(orc, t, nrows, k):
         assert nmse(out, ref) < 1e-10
 
 
+@pytest.mark.parametrize("t", [2, 6, 7, 13, 14])
+@pytest.mark.parametrize("nrows,k,ntok", [(16, 256, 1), (1, 256, 1), (37, 512, 3), (256, 2048, 1), (4096, 4096, 1), (128256 // 64, 4096, 2)])
+def test_more_formats_on_the_row_kernel_match_dequant32(orc, t, nrows, k, ntok):
+    """Q4_0, Q5_0, Q5_1, Q5_K, Q6_K (what real Q4_K_M files carry beside Q4_K: Q6_K in the head and in half of the
+    v / down projections) stay as raw blocks on the device and run on the one-warp-per-row kernel, every weight formed
+    exactly as quant.Dequant32 forms it: f32 accumulation is the only difference from the f64 oracle."""
+    rng = synth.rng_for(0xB400 + t + nrows + k)
+    w = synth.matrix(rng, t, nrows, k)
+    x = synth.activations(rng, ntok, k)
+    with Device(0) as d:
+        ch = d.Select(t, nrows, k, ntok)
+        assert ch is not None and ch.kernel == K_SIMT
+        out = np.full((ntok, nrows), np.nan, np.float32)
+        assert d.MatMul(out, t, w, x, nrows, k, ntok), d.Err()
+        ref = orc.matmul_f64(t, w, x, nrows, k, ntok)
+        assert np.isfinite(out).all()
+        assert parity_err(out, ref) <= BAR
+        assert nmse(out, ref) < 1e-10
+
+
 @pytest.mark.parametrize("warps", [4, 8, 16])
 @pytest.mark.parametrize("nrows,k", [(16, 256), (16, 512), (5, 256), (100, 1024), (4096, 4096), (1024, 4096),
                                       (4096, 14336), (14336, 4096)])
@@ -122,15 +142,16 @@ def test_small_batch_matmul_matches_oracle(dev, orc):
         dev.Forget(w)
 
 
-@pytest.mark.parametrize("t", [Q4_K, Q8_0, MXFP4])
+@pytest.mark.parametrize("t", [Q4_K, Q8_0, MXFP4, 2, 6, 7, 13, 14])
 def test_resident_copy_unpacks_bit_exact(dev, orc, t):
     # the repack at upload is a permutation: codes, scales and raw d bits survive it exactly
+    from jitllm_b200._lib import BLOCK
     rng = synth.rng_for(200 + t)
-    nrows, k = 24, 1024 if t == Q4_K else 640
+    nrows, k = 24, 1024 if BLOCK[t][0] == 256 else 640
     w = synth.matrix(rng, t, nrows, k)
     h = dev.Upload(t, w, nrows, k)
     got = h.unpack()
-    want = orc.unpack(t, w, w.size // {Q4_K: 144, Q8_0: 34, MXFP4: 17}[t])
+    want = orc.unpack(t, w, w.size // BLOCK[t][1])
     for g, x in zip(got, want):
         assert np.array_equal(g, x)
     h.free()

@@ -6,7 +6,8 @@ import pytest
 from conftest import nmse
 from jitllm_b200 import synth
 
-CASES = [("q4_k_tiny", 12), ("q8_0_gemma", 8), ("q8_0_minilm", 8), ("q8_0_stories", 8), ("mxfp4", 39)]
+CASES = [("q4_k_tiny", 12), ("q8_0_gemma", 8), ("q8_0_minilm", 8), ("q8_0_stories", 8), ("mxfp4", 39),
+         ("q4_0_gemma", 2), ("q4_0_stories", 2), ("q5_k_tiny", 13), ("q6_k_tiny", 14)]
 
 
 @pytest.mark.parametrize("name,t", CASES)
@@ -65,6 +66,37 @@ def test_unpack_reassembles_to_the_decoder(orc, t):
         table = np.array([0, 1, 2, 3, 4, 6, 8, 12, 0, -1, -2, -3, -4, -6, -8, -12], np.float32)
         scale = ((d.astype(np.uint32) & 0xFF) << 23).view(np.float32)  # stored byte e-1 -> 2^(e-128)
         val = table[q.astype(np.int64)] * scale[:, None]
+    assert np.array_equal(val.reshape(-1).view(np.uint32), ref.view(np.uint32))
+
+
+@pytest.mark.parametrize("t", [2, 6, 7, 13, 14])
+def test_unpack_reassembles_to_the_decoder_more_formats(orc, t):
+    """The integer view of Q4_0, Q5_0, Q5_1, Q5_K and Q6_K (extract, jit/gpu/kernels/pack.go:252-386) put back
+    together as value = scale * q - bias equals Dequant32 bit for bit. The reference commits no golden for Q5_0 /
+    Q5_1; for those this identity against the decoder restated from dequant.go:103-146 is the pin."""
+    rng = synth.rng_for(0xB300 + t)
+    k = 512
+    w = synth.matrix(rng, t, 6, k)
+    nb = 6 * k // orc.block_elems(t)
+    q, d, dmin, sc, m = orc.unpack(t, w, nb)
+    ref = orc.dequant32(t, w, 6 * k)
+    sub = 16 if t == 14 else 32
+    q = q.reshape(-1, sub).astype(np.float32)
+    df = d.view(np.float16).astype(np.float32)
+    if t == 2:
+        val = df[:, None] * (q - 8)
+    elif t == 6:
+        val = df[:, None] * (q - 16)
+    elif t == 7:   # dmin carries m with its sign flipped: value = d q - (-m)
+        mf = (dmin ^ 0x8000).view(np.float16).astype(np.float64)
+        val = (df.astype(np.float64)[:, None] * q.astype(np.float64) + mf[:, None]).astype(np.float32)
+    elif t == 13:
+        mf = dmin.view(np.float16).astype(np.float32)
+        val = (df * sc.astype(np.float32))[:, None] * q - (mf * m.astype(np.float32))[:, None]
+        assert q.max() <= 31 and sc.max() <= 63
+    else:
+        val = (df * (sc.astype(np.float32) - 128))[:, None] * (q - 32)
+        assert q.min() >= 0 and q.max() <= 63
     assert np.array_equal(val.reshape(-1).view(np.uint32), ref.view(np.uint32))
 
 
