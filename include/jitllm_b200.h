@@ -180,6 +180,27 @@ int jl_forget(jl_ctx *ctx, const void *p, size_t n);
 int jl_matmul(jl_ctx *ctx, void *out, int out_dtype, uint32_t type, const void *w, size_t w_bytes,
               const void *x, int x_dtype, int nrows, int k, int ntok);
 
+/* ---- container-packed weights: nn.Packed{QS, D, SC, Row, Stride} (engine/nn/device.go:62-80) ----
+ * What the reference's .jlm containers store and JIT.MatVecPacked / MatMulPacked read
+ * (engine/nn/packed.go:24, engine/nn/packedmm.go:23): the blocks' fields as three planes laid out
+ * [sub-block][word][row] by kernels.PackWeights (jit/gpu/kernels/pack.go:27-239). stride is the row
+ * count of the whole buffer, row where this weight starts in it (both 0: the whole buffer). Served for
+ * Q4_K, Q8_0 and MXFP4: the planes are re-interleaved once, at upload, into the raw blocks the kernels
+ * stream (the exact inverse of PackWeights: jl_packed_to_blocks), so results are those of the raw
+ * entry points bit for bit. Residency of the host calls is keyed on the payload plane (plus row);
+ * jl_forget over the payload plane's bytes drops it. sc is NULL / 0 for formats without a
+ * sub-block scale table (Q8_0, MXFP4). */
+typedef struct jl_packed {
+    const void *qs, *d, *sc;
+    size_t qs_bytes, d_bytes, sc_bytes;
+    int32_t row, stride;
+} jl_packed;
+int jl_packed_to_blocks(uint32_t type, const jl_packed *p, int nrows, int k, void *raw_out, size_t raw_bytes);
+int jl_weight_upload_packed(jl_ctx *ctx, uint32_t type, const jl_packed *p, int nrows, int k, jl_weight **out);
+int jl_matvec_packed(jl_ctx *ctx, float *out, uint32_t type, const jl_packed *p, const float *x, int nrows, int k);
+int jl_matmul_packed(jl_ctx *ctx, void *out, int out_dtype, uint32_t type, const jl_packed *p, const void *x, int x_dtype,
+                     int nrows, int k, int ntok);
+
 /* ---- the mixture layer: State.moeBatch (engine/model/moe.go:502-760) ----- */
 /* Banks are [n_expert][rows][k/32*17] raw MXFP4 blocks (banks of any other type are DECLINED):
  * gate, up: rows = ffn, k = hidden; down: rows = hidden, k = ffn.

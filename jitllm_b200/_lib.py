@@ -61,6 +61,11 @@ class MoeDesc(C.Structure):
                 ("router_bias", C.c_void_p), ("sel_bias", C.c_void_p)]
 
 
+class Packed(C.Structure):
+    _fields_ = [("qs", C.c_void_p), ("d", C.c_void_p), ("sc", C.c_void_p), ("qs_bytes", C.c_size_t), ("d_bytes", C.c_size_t),
+                ("sc_bytes", C.c_size_t), ("row", C.c_int32), ("stride", C.c_int32)]
+
+
 class LayersBlock(C.Structure):
     _fields_ = [("qkv", C.c_void_p), ("o", C.c_void_p), ("gate_up", C.c_void_p), ("down", C.c_void_p),
                 ("attn_norm", C.c_void_p), ("ffn_norm", C.c_void_p), ("k_cache", C.c_void_p), ("v_cache", C.c_void_p)]
@@ -87,6 +92,10 @@ SYMBOLS = {
     "jl_matvec": (_I, [_VP, _VP, _U32, _VP, _SZ, _VP, _I, _I]),
     "jl_forget": (_I, [_VP, _VP, _SZ]),
     "jl_matmul": (_I, [_VP, _VP, _I, _U32, _VP, _SZ, _VP, _I, _I, _I, _I]),
+    "jl_packed_to_blocks": (_I, [_U32, C.POINTER(Packed), _I, _I, _VP, _SZ]),
+    "jl_weight_upload_packed": (_I, [_VP, _U32, C.POINTER(Packed), _I, _I, C.POINTER(_VP)]),
+    "jl_matvec_packed": (_I, [_VP, _VP, _U32, C.POINTER(Packed), _VP, _I, _I]),
+    "jl_matmul_packed": (_I, [_VP, _VP, _I, _U32, C.POINTER(Packed), _VP, _I, _I, _I, _I]),
     "jl_moe": (_I, [_VP, _VP, _VP, _I, _VP, _I, C.POINTER(MoeDesc), _VP, _VP]),
     "jl_moe_route_dev": (_I, [_VP, _VP, _I, C.POINTER(MoeDesc), _VP, _VP, _VP]),
     "jl_moe_experts_dev": (_I, [_VP, _VP, _VP, _I, _VP, _I, C.POINTER(MoeDesc), _VP]),

@@ -16,7 +16,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libjitllm_b200.so")
-SOURCES = ["ctx.cu", "formats.cu", "gemv.cu", "gemv_q8.cu", "gemv_mxfp4.cu", "gemm_tc5.cu", "moe.cu", "aux.cu", "block.cu"]
+SOURCES = ["ctx.cu", "formats.cu", "gemv.cu", "gemv_q8.cu", "gemv_mxfp4.cu", "gemm_tc5.cu", "moe.cu", "aux.cu", "block.cu", "packed.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC,-fvisibility=hidden", "-DJL_BUILD",

@@ -252,8 +252,10 @@ static void touch(jl_ctx *ctx, uintptr_t key) {
 // address means the caller reused the memory without telling us: re-upload.
 // The copy stays pinned (safe from eviction) until jl_resident_unpin.
 static int resident(jl_ctx *ctx, uint32_t type, const void *w, size_t w_bytes, int n_expert, int nrows,
-                    int k, jl_weight **out) {
-    const uintptr_t key = (uintptr_t)w;
+                    int k, jl_weight **out, const void *key_ptr = nullptr) {
+    // key_ptr: the address residency is keyed on when it is not the source bytes' own (a packed weight is keyed on
+    // its payload plane while the bytes uploaded are the re-interleaved blocks); w may then be NULL for a lookup.
+    const uintptr_t key = (uintptr_t)(key_ptr ? key_ptr : w);
     const size_t need = (size_t)n_expert * nrows * jl_row_bytes(type, k);
     std::vector<jl_weight *> dead;
     bool fits = true;
@@ -280,10 +282,11 @@ static int resident(jl_ctx *ctx, uint32_t type, const void *w, size_t w_bytes, i
     if (!fits)
         return jl_set_err(ctx, JL_ENOMEM, "%zu weight bytes do not fit under max_resident_bytes = %llu beside the "
                           "copies this call already uses", need, (unsigned long long)ctx->opts.max_resident_bytes);
+    if (!w) return jl_set_err(ctx, JL_EINVAL, "no resident copy under this key and no bytes to upload");
     jl_weight *nw = nullptr;
     int rc = jl_repack_upload(ctx, type, w, w_bytes, n_expert, nrows, k, &nw);   // device work: cache_mu released
     if (rc) return rc;
-    nw->host_key = w;
+    nw->host_key = (const void *)key;
     std::lock_guard<std::mutex> lk(ctx->cache_mu);
     ctx->cache[key] = nw;
     touch(ctx, key);
@@ -458,6 +461,7 @@ static size_t dtype_bytes(int dt) { return dt == JL_DT_F32 ? 4 : 2; }
 
 // Last kernel of a zero-copy decode call: the status word and then the call's sequence number, into pinned host memory.
 __global__ void jl_done_kernel(int *status, volatile int *done, int seq) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");   // launched early; runs once the matvec has completed
     const int code = *status;
     if (code) *status = 0;
     done[1] = code;
@@ -469,9 +473,16 @@ __global__ void jl_done_kernel(int *status, volatile int *done, int seq) {
 // whether it failed, so that a kernel fault ends the wait with the error instead of an endless poll.
 static int jl_wait_done(jl_ctx *ctx) {
     const int seq = ++ctx->done_seq;
-    jl_done_kernel<<<1, 1, 0, ctx->stream>>>(ctx->dev_status, ctx->done_map, seq);
+    {
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[0].val.programmaticStreamSerializationAllowed = 1;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(1); cfg.blockDim = dim3(1); cfg.stream = ctx->stream; cfg.attrs = at;
+        cfg.numAttrs = (ctx->opts.flags & JL_FLAG_NO_PDL) ? 0 : 1;
+        JL_CUDA(ctx, cudaLaunchKernelEx(&cfg, jl_done_kernel, ctx->dev_status, ctx->done_map, seq));
+    }
     ctx->st.launches++;
-    JL_CUDA(ctx, cudaGetLastError());
     for (unsigned spins = 0;; spins++) {
         if (ctx->done_map[0] == seq) break;
         if ((spins & 0xFFFu) == 0xFFFu) {
@@ -488,14 +499,14 @@ static int jl_wait_done(jl_ctx *ctx) {
 }
 
 static int matmul_host(jl_ctx *ctx, void *out, int out_dtype, uint32_t type, const void *w, size_t w_bytes,
-                       const void *x, int x_dtype, int nrows, int k, int ntok) {
+                       const void *x, int x_dtype, int nrows, int k, int ntok, const void *key = nullptr) {
     int be = jl_block_elems(type);
     if (!jl_type_served(type))
         return jl_set_err(ctx, JL_DECLINED, "type %u is not served", type);
     if (nrows < 1 || k < be || k % be || ntok < 1)
         return jl_set_err(ctx, JL_DECLINED, "shape %d x %d x %d tokens does not tile %d-element blocks", nrows, k, ntok, be);
     size_t need = (size_t)nrows * jl_row_bytes(type, k);
-    if (w_bytes < need) return jl_set_err(ctx, JL_EINVAL, "weight has %zu bytes, shape needs %zu", w_bytes, need);
+    if (w && w_bytes < need) return jl_set_err(ctx, JL_EINVAL, "weight has %zu bytes, shape needs %zu", w_bytes, need);
     if (ctx->opts.min_weight_bytes && need < ctx->opts.min_weight_bytes)
         return jl_set_err(ctx, JL_DECLINED, "%zu weight bytes is below the %llu-byte break-even", need,
                           (unsigned long long)ctx->opts.min_weight_bytes);
@@ -503,7 +514,7 @@ static int matmul_host(jl_ctx *ctx, void *out, int out_dtype, uint32_t type, con
     if (rc) return rc;
     JL_CUDA(ctx, cudaSetDevice(ctx->device));
     jl_weight *dw = nullptr;
-    rc = resident(ctx, type, w, w_bytes, 1, nrows, k, &dw);
+    rc = resident(ctx, type, w, w_bytes, 1, nrows, k, &dw, key);
     jl_resident_unpin(ctx);   // ctx->mu is held to the end of this call: nothing else can evict dw meanwhile
     if (rc) return rc;
     size_t xb = (size_t)ntok * k * dtype_bytes(x_dtype), ob = (size_t)ntok * nrows * dtype_bytes(out_dtype);
@@ -545,6 +556,21 @@ static int matmul_host(jl_ctx *ctx, void *out, int out_dtype, uint32_t type, con
     memcpy(out, ctx->o_pin, ob);
     ctx->st.served++;
     return JL_OK;
+}
+
+// packed.cu: is there a resident copy of this shape under `key`?
+bool jl_resident_known(jl_ctx *ctx, const void *key, uint32_t type, int nrows, int k) {
+    std::lock_guard<std::mutex> lk(ctx->cache_mu);
+    auto it = ctx->cache.find((uintptr_t)key);
+    return it != ctx->cache.end() && it->second->type == type && it->second->nrows == nrows && it->second->k == k &&
+           it->second->n_expert == 1;
+}
+// packed.cu: the host-pointer matmul with residency keyed on `key`; raw (may be NULL when the copy is resident) are the
+// re-interleaved blocks to upload.
+int jl_matmul_keyed(jl_ctx *ctx, void *out, int out_dtype, uint32_t type, const void *key, const void *raw, size_t raw_bytes,
+                    const void *x, int x_dtype, int nrows, int k, int ntok) {
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    return matmul_host(ctx, out, out_dtype, type, raw, raw_bytes, x, x_dtype, nrows, k, ntok, key);
 }
 
 JL_EXPORT int jl_matvec(jl_ctx *ctx, float *out, uint32_t type, const void *w, size_t w_bytes, const float *x,

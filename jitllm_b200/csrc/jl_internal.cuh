@@ -148,6 +148,9 @@ int jl_grow_scratch(jl_ctx *ctx, size_t need);
 int jl_resident_bank(jl_ctx *ctx, uint32_t type, const void *w, size_t w_bytes, int n_expert, int nrows, int k,
                      jl_weight **out);
 void jl_resident_unpin(jl_ctx *ctx);
+bool jl_resident_known(jl_ctx *ctx, const void *key, uint32_t type, int nrows, int k);
+int jl_matmul_keyed(jl_ctx *ctx, void *out, int out_dtype, uint32_t type, const void *key, const void *raw, size_t raw_bytes,
+                    const void *x, int x_dtype, int nrows, int k, int ntok);
 void jl_drain_graveyard(jl_ctx *ctx);
 int jl_read_status(jl_ctx *ctx, cudaStream_t s);
 

@@ -14,7 +14,7 @@ import ctypes as C
 import numpy as np
 
 from . import _lib
-from ._lib import Choice, LayersBlock, LayersDesc, MoeDesc, Opts, Stats
+from ._lib import Choice, LayersBlock, LayersDesc, MoeDesc, Opts, Packed, Stats
 
 
 class DeviceError(RuntimeError):
@@ -82,6 +82,21 @@ class Weight:
         self.dev._check(self.dev.lib.jl_unpack_resident(self.dev.ctx, self.handle, _ptr(q), _ptr(d), _ptr(dm),
                                                         _ptr(sc), _ptr(m)))
         return q, d, dm, sc, m
+
+
+def packed_desc(qs, d, sc=None, row: int = 0, stride: int = 0) -> Packed:
+    """nn.Packed over three numpy uint32 planes (sc None for formats without a sub-block scale table)."""
+    return Packed(qs=_ptr(qs), d=_ptr(d), sc=_ptr(sc) if sc is not None and sc.size else None, qs_bytes=qs.nbytes, d_bytes=d.nbytes,
+                  sc_bytes=sc.nbytes if sc is not None else 0, row=row, stride=stride)
+
+
+def packed_to_blocks(t: int, p: Packed, nrows: int, k: int) -> np.ndarray:
+    """The raw ggml blocks a packed weight was made from (the inverse of kernels.PackWeights)."""
+    out = np.empty(nrows * _lib.row_bytes(t, k), np.uint8)
+    rc = _lib.load().jl_packed_to_blocks(t, C.byref(p), nrows, k, _ptr(out), out.nbytes)
+    if rc != _lib.OK:
+        raise DeviceError(rc, "jl_packed_to_blocks")
+    return out
 
 
 class Layers:
@@ -195,6 +210,22 @@ class Device:
         self.last_status = self.lib.jl_matmul(self.ctx, _ptr(out), out_dtype, t, _ptr(w), _nbytes(w), _ptr(x),
                                               x_dtype, nrows, k, ntok)
         return self.last_status == _lib.OK
+
+    def MatVecPacked(self, out, t: int, p: Packed, x, nrows: int, k: int) -> bool:
+        """JIT.MatVecPacked: the matvec on a weight in the container's planar layout. False = declined."""
+        self.last_status = self.lib.jl_matvec_packed(self.ctx, _ptr(out), t, C.byref(p), _ptr(x), nrows, k)
+        return self.last_status == _lib.OK
+
+    def MatMulPacked(self, out, t: int, p: Packed, x, nrows: int, k: int, ntok: int) -> bool:
+        """JIT.MatMulPacked: x [ntok][k] -> out [ntok][nrows] on a packed weight."""
+        self.last_status = self.lib.jl_matmul_packed(self.ctx, _ptr(out), _dtype_code(out), t, C.byref(p), _ptr(x),
+                                                     _dtype_code(x), nrows, k, ntok)
+        return self.last_status == _lib.OK
+
+    def UploadPacked(self, t: int, p: Packed, nrows: int, k: int) -> Weight:
+        h = C.c_void_p()
+        self._check(self.lib.jl_weight_upload_packed(self.ctx, t, C.byref(p), nrows, k, C.byref(h)))
+        return Weight(self, h.value, t, nrows, k, 1)
 
     def Forget(self, p, n: int | None = None) -> None:
         """CopyForgetter.Forget: drop device copies of host bytes [p, p+n)."""

@@ -114,6 +114,22 @@ def unpack(t: int, src, nblocks: int):
     return q, d, dmin, sc, m
 
 
+def pack_weights(t: int, src, nrows: int, k: int, row0: int = 0, stride: int | None = None, into=None):
+    """kernels.PackWeights: the container / device planes (qs, d, sc as uint32 arrays) of a raw tensor. With `into` =
+    (qs, d, sc) the rows are ORed into an existing buffer of `stride` rows starting at `row0` (a bank's experts)."""
+    s = _bytes(src)
+    stride = stride or nrows
+    nq, nd, ns = C.c_size_t(), C.c_size_t(), C.c_size_t()
+    if lib().orc_packed_words(C.c_uint32(t), stride, k, C.byref(nq), C.byref(nd), C.byref(ns)):
+        raise ValueError("orc_packed_words: type or k not packable")
+    qs, d, sc = into if into is not None else (np.zeros(nq.value, np.uint32), np.zeros(nd.value, np.uint32),
+                                                np.zeros(ns.value, np.uint32))
+    rc = lib().orc_pack_weights(C.c_uint32(t), _p(s), nrows, k, row0, stride, _p(qs), _p(d), _p(sc) if sc.size else None)
+    if rc:
+        raise ValueError(f"orc_pack_weights rc={rc}")
+    return qs, d, sc
+
+
 def matvec(t: int, w, x: np.ndarray, nrows: int, k: int) -> np.ndarray:
     """oracle.MatVec: compensated f32 dot of Dequant32 rows."""
     s = _bytes(w)

@@ -851,3 +851,69 @@ ORC_API int orc_moe_layer(float *out, const float *h, uint32_t t, const uint8_t 
     free(rows); free(w); free(A);
     return 0;
 }
+
+/* ------------------------------------------------ container-packed planes */
+
+/* kernels.PackWeights (jit/gpu/kernels/pack.go:27-239) for the formats of this path: the device / container
+ * layout [sub-block][word][row]. qs, d, sc are caller-zeroed u32 arrays of orc_packed_words() lengths; `stride` is
+ * the row count of the whole buffer and `row0` where this weight starts in it (engine/nn/device.go:62-80).
+ *   payload   packSub (pack.go:186-224): sub-block si of row r is words (si*pw + w)*stride + r, pw = 4 (4-bit: byte j
+ *             holds element j in its low and j + 16 in its high nibble) or 8 (Q8_0: the signed bytes in order)
+ *   d plane   DIndex / DSlots (pack.go:545-575): Q4_K one word per (super-block, row) = d | dmin << 16; Q8_0 two
+ *             rows a word (f16 each); MXFP4 four rows a word (the stored exponent byte e - 1 each)
+ *   sc plane  Q4_K only: the 96-bit stream of sixteen 6-bit fields, scale then minimum per sub-block
+ *             (scstream.go:26-62), three words per (super-block, row) */
+static int orc_dslots(uint32_t t) { return t == ORC_MXFP4 ? 4 : (t == ORC_Q8_0 ? 2 : 1); }
+ORC_API int orc_packed_words(uint32_t t, int stride, int k, size_t *nqs, size_t *nd, size_t *nsc) {
+    if (t != ORC_Q4_K && t != ORC_Q8_0 && t != ORC_MXFP4) return -1;
+    if (k <= 0 || k % orc_block_elems(t)) return -2;
+    const int nsub = k / 32, pw = t == ORC_Q8_0 ? 8 : 4, ds = orc_dslots(t);
+    const int nsuper = t == ORC_Q4_K ? k / 256 : nsub;
+    *nqs = (size_t)stride * nsub * pw;
+    *nd = (size_t)nsuper * ((stride + ds - 1) / ds);
+    *nsc = t == ORC_Q4_K ? (size_t)nsuper * 3 * stride : 0;
+    return 0;
+}
+static void sc_put(uint32_t *w3, int sub, int min, uint8_t v) {
+    const int f = 2 * sub + (min ? 1 : 0), w = f * 6 / 32, b = f * 6 % 32, hi = b > 26 ? b - 26 : 0;
+    w3[w] |= (uint32_t)(v & 63) << b;
+    if (hi > 0) w3[w + 1] |= (uint32_t)(v & 63) >> (6 - hi);
+}
+ORC_API int orc_pack_weights(uint32_t t, const uint8_t *src, int nrows, int k, int row0, int stride,
+                             uint32_t *qs, uint32_t *d, uint32_t *sc) {
+    size_t nq, nd, ns;
+    if (orc_packed_words(t, stride, k, &nq, &nd, &ns)) return -1;
+    if (row0 < 0 || row0 + nrows > stride) return -2;
+    const int be = orc_block_elems(t), bb = orc_block_bytes(t), per = be / 32, nblk = k / be;
+    const int pw = t == ORC_Q8_0 ? 8 : 4, ds = orc_dslots(t);
+    const size_t nsub_blocks = (size_t)nrows * nblk;
+    int8_t *q = malloc(nsub_blocks * be);
+    uint16_t *db = malloc(nsub_blocks * per * 2), *dm = malloc(nsub_blocks * per * 2);
+    uint8_t *scv = malloc(nsub_blocks * per), *mv = malloc(nsub_blocks * per);
+    orc_unpack(t, src, nsub_blocks, q, db, dm, scv, mv);         /* extract, one record per 32 elements */
+    for (int r = 0; r < nrows; r++) {
+        const int R = row0 + r;
+        for (int si = 0; si < k / 32; si++) {
+            const size_t rec = (size_t)r * (k / 32) + si;
+            const int8_t *qq = q + rec * 32;
+            uint8_t out[32] = {0};
+            if (pw == 4) for (int l = 0; l < 32; l++) out[l % 16] |= (uint8_t)((qq[l] & 15) << (4 * (l / 16)));
+            else for (int l = 0; l < 32; l++) out[l] = (uint8_t)qq[l];
+            for (int w = 0; w < pw; w++)
+                qs[((size_t)si * pw + w) * stride + R] = (uint32_t)out[4 * w] | (uint32_t)out[4 * w + 1] << 8 |
+                                                         (uint32_t)out[4 * w + 2] << 16 | (uint32_t)out[4 * w + 3] << 24;
+            const int sup = t == ORC_Q4_K ? si / 8 : si;
+            if (ds == 1) d[(size_t)sup * stride + R] |= (uint32_t)db[rec] | (uint32_t)dm[rec] << 16;
+            else if (ds == 2) d[(size_t)sup * ((stride + 1) / 2) + R / 2] |= (uint32_t)db[rec] << (16 * (R % 2));
+            else d[(size_t)sup * ((stride + 3) / 4) + R / 4] |= (uint32_t)(db[rec] & 0xFF) << (8 * (R % 4));
+            if (t == ORC_Q4_K) {
+                uint32_t w3[3] = {0, 0, 0};
+                sc_put(w3, si % 8, 0, scv[rec]);
+                sc_put(w3, si % 8, 1, mv[rec]);
+                for (int w = 0; w < 3; w++) sc[((size_t)sup * 3 + w) * stride + R] |= w3[w];
+            }
+        }
+    }
+    free(q); free(db); free(dm); free(scv); free(mv);
+    return 0;
+}

@@ -161,7 +161,7 @@ def test_declines_and_errors_follow_the_reference_contract(dev):
     out = np.zeros(8, np.float32)
     x = np.zeros(100, np.float32)
     w = np.zeros(4096, np.uint8)
-    assert not dev.MatVec(out, 2, w, x, 8, 64)          # Q4_0: unsupported type declines
+    assert not dev.MatVec(out, 3, w, x, 8, 64)          # Q4_1: unsupported type declines
     assert dev.last_status == DECLINED and "not served" in dev.Err()
     assert not dev.MatVec(out, Q4_K, w, x, 8, 100)      # ragged k declines
     assert dev.last_status == DECLINED
