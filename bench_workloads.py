@@ -242,12 +242,12 @@ def run_moe_ep(args, emit=True):
     def route(lg):
         sel = torch.empty(lg.shape[0], topk, dtype=torch.int32, device="cuda")
         wt = torch.empty(lg.shape[0], topk, dtype=torch.float32, device="cuda")
-        dev.MoeRouteDev(lg, lg.shape[0], d_route, sel, wt, stream)
+        dev.MoeRouteDev(lg, lg.shape[0], d_route, sel, wt, torch.cuda.current_stream().cuda_stream)
         return sel, wt
 
     def experts(rows, ids):
         y = torch.empty(rows.shape[0], hidden, dtype=torch.float32, device="cuda")
-        dev.MoeExpertsDev(y, rows.contiguous(), ids.contiguous(), rows.shape[0], d_local, stream)
+        dev.MoeExpertsDev(y, rows.contiguous(), ids.contiguous(), rows.shape[0], d_local, torch.cuda.current_stream().cuda_stream)
         return y
     moe = parallel.ExpertParallelMoE(route, experts, E, topk, hidden)
     g = torch.Generator(device="cuda").manual_seed(11 + rank)
@@ -260,12 +260,36 @@ def run_moe_ep(args, emit=True):
     per_step = (dev.Stats().launches - n0) // max(args.warmup, 3)
     dist.barrier()
     torch.cuda.synchronize()
+    # the layer is a fixed sequence of device operations (no size crosses the host): hold it in a CUDA graph
+    graph, launch = None, "eager"
+    if os.environ.get("JITLLM_B200_EP_GRAPH", "1") != "0":
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        try:
+            with torch.cuda.stream(side):
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
+                    moe.forward(out, h, logits)
+            launch = "one CUDA graph per layer (router, exchange, experts, exchange, combine)"
+        except Exception as e:  # noqa: BLE001 -- a capture the libraries refuse falls back to eager launches
+            graph, launch = None, f"eager (graph capture refused: {type(e).__name__})"
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+    ok = torch.tensor([1 if graph is not None else 0], device="cuda")
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    if not int(ok):
+        graph = None
+    step = graph.replay if graph is not None else (lambda: moe.forward(out, h, logits))
+    for _ in range(3):
+        step()
+    dist.barrier()
+    torch.cuda.synchronize()
     import bench
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with bench.ClockSampler(local) as clk:
         e0.record()
         for _ in range(args.steps):
-            moe.forward(out, h, logits)
+            step()
         e1.record()
         torch.cuda.synchronize()
     tt = torch.tensor([e0.elapsed_time(e1)], device="cuda", dtype=torch.float64)
@@ -281,7 +305,7 @@ def run_moe_ep(args, emit=True):
             "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "MXFP4 -> f16, bf16->f16 activations, f32 accumulate (tcgen05 kind::f16)", "data": "synthetic",
             "config": {"workload": "mxfp4_moe_gptoss", **MOE, "parallelism": f"ep{world}: {epr} experts and {ntok} tokens per rank",
-                       "us_per_layer": us, "launch": "eager (the all-to-all sizes cross the host every layer)",
+                       "us_per_layer": us, "launch": launch, "exchange": "fixed capacity (tokens x top_k slots per destination, unused slots skipped by the experts)",
                        "l2": "one layer of experts per rank, re-read every step: the per-rank working set is below L2 at 8 ranks"},
             "roofline": {"bound": "hbm", "achieved": wbytes_rank / us / 1e3, "peak": hbm, "unit": "GB/s",
                          "frac": wbytes_rank / us / 1e3 / hbm, "of": which, "kernel": "whole layer incl. NCCL all-to-all, weight bytes per rank", "traffic": None},
@@ -556,7 +580,7 @@ def sharded_parity(local):
         full = [dev.Upload(MXFP4, b, r, kk, E) for b, (r, kk) in zip(banks, ((ffn, hidden), (ffn, hidden), (hidden, ffn)))]
         mine = [dev.Upload(MXFP4, parallel.shard_experts(b, MXFP4, E, r, kk, rank, world)[0], r, kk, epr)
                 for b, (r, kk) in zip(banks, ((ffn, hidden), (ffn, hidden), (hidden, ffn)))]
-        dev.MoeReserve(ntok * topk, E, topk, hidden, ffn)
+        dev.MoeReserve(world * ntok * topk, E, topk, hidden, ffn)
         d_full = MoeDesc(struct_size=C.sizeof(MoeDesc), type=MXFP4, n_expert=E, top_k=topk, hidden=hidden, ffn=ffn, act=0, norm=1,
                          scale=1.0, gate=full[0].handle, up=full[1].handle, down=full[2].handle)
         d_local = MoeDesc(struct_size=C.sizeof(MoeDesc), type=MXFP4, n_expert=epr, top_k=1, hidden=hidden, ffn=ffn, act=0, norm=1,
@@ -570,12 +594,12 @@ def sharded_parity(local):
         def route(lg):
             sel = torch.empty(lg.shape[0], topk, dtype=torch.int32, device="cuda")
             wt = torch.empty(lg.shape[0], topk, dtype=torch.float32, device="cuda")
-            dev.MoeRouteDev(lg, lg.shape[0], d_full, sel, wt, stream)
+            dev.MoeRouteDev(lg, lg.shape[0], d_full, sel, wt, torch.cuda.current_stream().cuda_stream)
             return sel, wt
 
         def experts(rows, ids):
             y = torch.empty(rows.shape[0], hidden, dtype=torch.float32, device="cuda")
-            dev.MoeExpertsDev(y, rows.contiguous(), ids.contiguous(), rows.shape[0], d_local, stream)
+            dev.MoeExpertsDev(y, rows.contiguous(), ids.contiguous(), rows.shape[0], d_local, torch.cuda.current_stream().cuda_stream)
             return y
         out = torch.zeros(ntok, hidden, device="cuda")
         parallel.ExpertParallelMoE(route, experts, E, topk, hidden).forward(out, h, logits)

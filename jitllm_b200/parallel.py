@@ -163,28 +163,45 @@ class ExpertParallelMoE:
             raise ValueError(f"{n_expert} experts do not split over {self.world} ranks")
         self.epr, self.top_k, self.hidden, self.group = n_expert // self.world, top_k, hidden, group
 
-    def forward(self, out, h, logits):
-        """out [ntok][hidden] f32 += layer(h); h [ntok][hidden] (f32 or bf16), logits [ntok][E] f32."""
+    def forward(self, out, h, logits, capacity: int | None = None):
+        """out [ntok][hidden] f32 += layer(h); h [ntok][hidden] (f32 or bf16), logits [ntok][E] f32.
+
+        Fixed-capacity exchange: every rank sends every other rank the same number of row slots (`capacity`,
+        default ntok * top_k: the worst case, so nothing can overflow; every rank must pass the same value), unused
+        slots carrying expert id -1, which the experts' token lists skip. No size crosses the host, so the whole
+        layer is a fixed sequence of device operations (a CUDA graph can hold it); the price is padding on the wire.
+        The reference's grouped launches read one word home per chunk instead (jit/gpu/tier/moegroup.go:10-19)."""
         import torch
         import torch.distributed as dist
-        ntok = h.shape[0]
+        ntok, K, W = h.shape[0], self.top_k, self.world
+        npairs = ntok * K
+        cap = capacity or npairs
         sel, wt = self.route(logits)
-        order, send_counts, local_ids = dispatch_plan(sel, self.epr, self.world)
-        recv_counts = torch.empty_like(send_counts)
-        dist.all_to_all_single(recv_counts, send_counts, group=self.group)
-        sc, rc = send_counts.tolist(), recv_counts.tolist()               # sizes of the exchange (host)
-        tok_of_pair = torch.div(order, self.top_k, rounding_mode="floor")
-        send_rows = h.index_select(0, tok_of_pair).contiguous()
-        recv_rows = torch.empty((sum(rc), self.hidden), dtype=h.dtype, device=h.device)
-        recv_ids = torch.empty(sum(rc), dtype=torch.int32, device=h.device)
-        dist.all_to_all_single(recv_rows, send_rows, rc, sc, group=self.group)
-        dist.all_to_all_single(recv_ids, local_ids.contiguous(), rc, sc, group=self.group)
-        y_recv = self.experts(recv_rows, recv_ids) if sum(rc) else torch.empty((0, self.hidden), dtype=torch.float32, device=h.device)
-        y_back = torch.empty((sum(sc), self.hidden), dtype=torch.float32, device=h.device)
-        dist.all_to_all_single(y_back, y_recv.contiguous(), sc, rc, group=self.group)
-        y_pairs = torch.empty((ntok * self.top_k, self.hidden), dtype=torch.float32, device=h.device)
-        y_pairs[order] = y_back                                            # back to (token, slot) order
-        return combine_ascending(out, y_pairs.view(ntok, self.top_k, self.hidden), sel, wt)
+        flat = sel.reshape(-1).to(torch.int64)
+        valid = flat >= 0
+        dest = torch.where(valid, torch.div(flat, self.epr, rounding_mode="floor"), torch.zeros_like(flat))
+        # slot of each pair inside its destination's bucket: pairs keep their order (a stable rank by one-hot cumsum)
+        onehot = torch.nn.functional.one_hot(dest, W) * valid[:, None]
+        rank_in = (onehot.cumsum(0) - onehot).gather(1, dest[:, None])[:, 0]
+        ok = valid & (rank_in < cap)
+        send_idx = torch.where(ok, dest * cap + rank_in, torch.full_like(dest, W * cap))     # W*cap: a scratch slot for the unsent
+        tok_of_pair = torch.arange(npairs, device=h.device) // K
+        send_rows = torch.zeros((W * cap + 1, self.hidden), dtype=h.dtype, device=h.device)
+        send_ids = torch.full((W * cap + 1,), -1, dtype=torch.int32, device=h.device)
+        send_rows[send_idx] = h[tok_of_pair]
+        send_ids[send_idx] = torch.where(ok, flat - dest * self.epr, torch.full_like(flat, -1)).to(torch.int32)
+        recv_rows = torch.empty((W * cap, self.hidden), dtype=h.dtype, device=h.device)
+        recv_ids = torch.empty(W * cap, dtype=torch.int32, device=h.device)
+        dist.all_to_all_single(recv_rows, send_rows[:W * cap].contiguous(), group=self.group)
+        dist.all_to_all_single(recv_ids, send_ids[:W * cap].contiguous(), group=self.group)
+        y_recv = self.experts(recv_rows, recv_ids)                         # rows whose id is -1 are not computed
+        y_back = torch.empty((W * cap + 1, self.hidden), dtype=torch.float32, device=h.device)
+        dist.all_to_all_single(y_back[:W * cap], y_recv.contiguous(), group=self.group)
+        y_back[W * cap] = 0
+        y_pairs = y_back[send_idx]                                         # back to (token, slot) order
+        y_pairs = torch.where(ok[:, None], y_pairs, torch.zeros_like(y_pairs))
+        wt_eff = torch.where(ok.view(ntok, K), wt, torch.zeros_like(wt))
+        return combine_ascending(out, y_pairs.view(ntok, K, self.hidden), sel, wt_eff)
 
 
 # ------------------------------------------------------ tensor-parallel slot exchange

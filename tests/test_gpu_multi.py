@@ -128,12 +128,12 @@ def _worker(rank, world, port, tmp):
         def route(lg):
             sel = torch.empty(lg.shape[0], topk, dtype=torch.int32, device="cuda")
             wt = torch.empty(lg.shape[0], topk, dtype=torch.float32, device="cuda")
-            dev.MoeRouteDev(lg, lg.shape[0], d_route, sel, wt, stream)
+            dev.MoeRouteDev(lg, lg.shape[0], d_route, sel, wt, torch.cuda.current_stream().cuda_stream)
             return sel, wt
 
         def experts(rows, ids):
             y = torch.empty(rows.shape[0], hidden, dtype=torch.float32, device="cuda")
-            dev.MoeExpertsDev(y, rows.contiguous(), ids.contiguous(), rows.shape[0], d_local, stream)
+            dev.MoeExpertsDev(y, rows.contiguous(), ids.contiguous(), rows.shape[0], d_local, torch.cuda.current_stream().cuda_stream)
             return y
         moe = parallel.ExpertParallelMoE(route, experts, E, topk, hidden)
         got = moe.forward(torch.zeros(hi - lo, hidden, device="cuda"), torch.from_numpy(h[lo:hi]).cuda(),
