@@ -404,7 +404,15 @@ def main():
     ap.add_argument("--batch", type=int, default=1, help="llama8b_q4k_decode: sequences decoded together")
     ap.add_argument("--prompt", type=int, default=2048, help="llama8b_q4k_decode: prompt length")
     ap.add_argument("--no-also", action="store_true", help="headline workload only (skip the `also` block)")
+    ap.add_argument("--profile", default=None, choices=["gemv", "q8", "gemm", "moe", "block", "attn"],
+                    help="run one small fixed case of the named kernel for a profiler to capture (no timing) and exit")
+    ap.add_argument("--form", default="auto", choices=["auto", "split", "fused", "wide", "l1", "concurrent"],
+                    help="--profile gemv: decode form (concurrent = what the bench's independent branches run)")
     args = ap.parse_args()
+    if args.profile:
+        import bench_workloads as bw
+        bw.profile_case(args)
+        return
     if args.workload not in WORKLOADS:
         import bench_workloads as bw
         if args.impl == "reference":

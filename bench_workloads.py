@@ -515,6 +515,86 @@ def run_decode(args, emit=True, batches=None, steps=None):
 
 
 # ------------------------------------------------------------------ sharded forms against the unsharded ones
+def profile_case(args):
+    """Small fixed cases for a profiler to capture: no timing, few launches, a few hundred MB on the device (but
+    above the 126 MB L2, so DRAM counters mean something). Prints the kernels' launch count."""
+    import torch
+    from jitllm_b200 import Q4_K, Q8_0, Device, synth
+    from jitllm_b200 import _lib
+    torch.cuda.set_device(0)
+    case = args.profile
+    stream = torch.cuda.current_stream().cuda_stream
+    rng = synth.rng_for(0x9F0)
+    forms = {"auto": 0, "split": _lib.FORM_SPLIT, "fused": _lib.FORM_FUSED, "wide": _lib.FORM_WIDE, "l1": _lib.FORM_L1}
+    if case in ("gemv", "q8"):
+        t, ntok = (Q4_K, 1) if case == "gemv" else (Q8_0, 32)
+        n = k = 4096
+        ring = 32 if case == "gemv" else 16
+        flags = _lib.FLAG_DECODE_CONCURRENT if args.form == "concurrent" else 0
+        with Device(0, decode_form=forms.get(args.form, 0), flags=flags) as dev:
+            dev.Reserve(n, k, ntok)
+            ws = [dev.Upload(t, synth.matrix(rng, t, n, k), n, k) for _ in range(ring)]
+            x = torch.randn(ntok, k, device="cuda")
+            y = torch.empty(ntok, n, device="cuda")
+            for i in range(ring + 8):
+                dev.MatMulDev(y, ws[i % ring], x, ntok, stream)
+            torch.cuda.synchronize()
+            assert dev.StatusPoll(), dev.Err()
+            print(json.dumps({"profile": case, "form": args.form, "launches": dev.Stats().launches}))
+            for w in ws:
+                w.free()
+    elif case == "gemm":
+        n, k, ntok = 14336, 4096, 512
+        with Device(0) as dev:
+            dev.Reserve(n, k, ntok)
+            ws = [dev.Upload(Q4_K, synth.q4k_matrix(rng, n, k), n, k) for _ in range(4)]
+            x = torch.randn(ntok, k, device="cuda").to(torch.bfloat16)
+            y = torch.empty(ntok, n, device="cuda", dtype=torch.bfloat16)
+            for i in range(6):
+                dev.MatMulDev(y, ws[i % 4], x, ntok, stream)
+            torch.cuda.synchronize()
+            assert dev.StatusPoll(), dev.Err()
+            print(json.dumps({"profile": case, "launches": dev.Stats().launches}))
+    elif case == "moe":
+        a2 = type(args)(**{**vars(args), "steps": 2, "warmup": 1})
+        run_moe(a2, emit=True)
+    elif case == "block":
+        from jitllm_b200.decoder import Config, Decoder
+        T = 2048
+        with Device(0) as dev:
+            dec = Decoder(dev, Config(n_layer=4, vocab=32768), max_batch=1, max_len=T + 32, max_prefill=64, seed=5)
+            assert dec.prep_block_kernel(), dev.Err()
+            g = torch.Generator(device="cuda").manual_seed(1)
+            dec.k_cache[:, :, :, :T] = torch.randn(dec.k_cache[:, :, :, :T].shape, device="cuda", generator=g).to(torch.bfloat16)
+            dec.v_cache[:, :, :, :T] = torch.randn(dec.v_cache[:, :, :, :T].shape, device="cuda", generator=g).to(torch.bfloat16)
+            tok, pos = torch.tensor([17], device="cuda"), torch.tensor([T], device="cuda")
+            with torch.no_grad():
+                for _ in range(6):
+                    dec.decode_step_block(tok, pos, advance=True)
+            torch.cuda.synchronize()
+            assert dev.StatusPoll(), dev.Err()
+            print(json.dumps({"profile": case, "layers": 4, "cached": T, "steps": 6, "last_token": int(tok)}))
+            dec.block.free()
+    elif case == "attn":
+        L = _lib.load()
+        n, hq, hkv, d, pos = 1, 32, 8, 128, 2048
+        max_len = pos + 16
+        g = torch.Generator(device="cuda").manual_seed(3)
+        q = torch.randn(n, hq, d, device="cuda", generator=g).to(torch.bfloat16)
+        caches = [(torch.randn(n, hkv, max_len, d, device="cuda", generator=g).to(torch.bfloat16),
+                   torch.randn(n, hkv, max_len, d, device="cuda", generator=g).to(torch.bfloat16)) for _ in range(24)]   # 24 x 8.4 MB > L2
+        scr = torch.zeros(L.jl_aux_attn_scratch_bytes(n, hq, hkv, max_len), device="cuda", dtype=torch.uint8)
+        pd = torch.tensor([pos], device="cuda")
+        out = torch.empty(n, hq * d, device="cuda")
+        for kc, vc in caches:
+            assert L.jl_aux_attn_decode(out.data_ptr(), None, q.data_ptr(), kc.data_ptr(), vc.data_ptr(), pd.data_ptr(), scr.data_ptr(),
+                                        n, hq, hkv, d, max_len, stream) == 0
+        torch.cuda.synchronize()
+        print(json.dumps({"profile": case, "launches": len(caches)}))
+    else:
+        raise SystemExit(f"unknown profile case {case}")
+
+
 def _perr(got, ref):
     """max_i |got - ref| / max(|ref_i|, rms(ref)): the output-parity measure (bar 2e-3)."""
     got, ref = got.double().reshape(-1), ref.double().reshape(-1)
