@@ -195,13 +195,13 @@ def run_q8_batch(args, emit=True):
         line = ({
             "metric": "q8_0_batch32_gbs", "value": gbs * world, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "Q8_0 -> f16 weights (one rounding), f32 activations as f16 hi+lo, f32 accumulate (tcgen05)",
+            "vs_baseline": None, "dtype": "s8 codes x two int8 digits per activation (mma.sync m16n8k32), d and 1/s folded in f32",
             "data": "synthetic",
             "config": {"workload": "q8_0_batch32", "ntok": Q8_NTOK, "shapes": Q8_SHAPES, "parallelism": f"column-parallel x{world}",
                        "l2": "a ring of distinct weight copies per shape, each ring > 200 MB: larger than L2",
                        "tflops": flops * args.steps / (ms * 1e-3) / 1e12 * world},
             "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm, "unit": "GB/s", "frac": gbs / hbm, "of": which,
-                         "kernel": "gemm_q4k_tc5_kernel<1,...> (Q8_0 dequant)", "traffic": None},
+                         "kernel": "q8_xprep_kernel + gemv_q8_batch_kernel (k-slices summed inside a cluster)", "traffic": None},
             "e2e": {"value": e2e * world, "unit": "GB/s", "h2d_bytes_per_step": Q8_NTOK * k * 4, "d2h_bytes_per_step": Q8_NTOK * nrows * 4,
                     "note": "jl_matmul host-pointer call on the 4096x4096 shard, wall clock"},
             "gpu_launches": int(per_replay * args.steps), "clocks": clocks})

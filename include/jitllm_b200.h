@@ -253,6 +253,35 @@ int jl_moe_reserve(jl_ctx *ctx, int ntok, int n_expert, int top_k, int hidden, i
  * of two in the tcgen05 GEMM (tile_n / split_k may then differ). */
 int jl_select(jl_ctx *ctx, uint32_t type, int nrows, int k, int ntok, jl_choice *out);
 
+/* ---- measured selection: tuneSplit (jit/gpu/tier/split.go:18-75), the tune cache
+ * (jit/gpu/tier/choose.go:196-216), WithTune / WithTuneCache ----------------------------------
+ * With tuning on, the first upload of a (type, rows, k) shape times the admissible variants of its
+ * decode kernel against the resident copy (one launch each, L2 flushed in front, 2 warm-up + 9 timed
+ * rounds, CUDA events): a candidate whose sample is dispersed (IQR / median > 0.10) is refused, a
+ * later candidate must beat the best so far by more than 1 %, and the table's pick is tried first,
+ * so it wins every tie. The verdict overrides the table for jl_select and for the launch alike. It
+ * persists in <cache_dir>/jl_select1 keyed by GPU UUID + driver version + build of this library;
+ * an entry that does not parse or names a variant the shape cannot take is measured again and
+ * overwritten. Contexts that pin a kernel or form, or set JL_FLAG_DECODE_CONCURRENT, do not tune.
+ * Served today: the Q4_K decode kernel (1..8 tokens). */
+typedef enum jl_tune_mode { JL_TUNE_OFF = 0, JL_TUNE_ON = 1, JL_TUNE_FORCE = 2 /* ignore persisted verdicts */ } jl_tune_mode;
+int jl_tune_configure(jl_ctx *ctx, int mode, const char *cache_dir /* NULL: do not persist */);
+/* Measure (or load) the verdict for w's shape at ntok tokens now; *out (may be NULL) = the choice. */
+int jl_tune(jl_ctx *ctx, const jl_weight *w, int ntok, jl_choice *out);
+/* out[0] timed launches, [1] shapes measured, [2] shapes answered from the file, [3] candidates refused. */
+int jl_tune_stats(jl_ctx *ctx, int64_t out[4]);
+/* The duel itself, host code: timer(user, candidate, round) returns a rate (higher is better; <= 0 =
+ * the run failed). refused[c] / medians[c] may be NULL. Returns the winner or -1 when no candidate
+ * gave a usable sample. */
+int jl_tune_duel(int ncand, int nrounds, double (*timer)(void *user, int cand, int round), void *user,
+                 double iqr_gate, double margin, int *refused, double *medians);
+/* The verdict file: 1 = found / saved, 0 = not. */
+int jl_tune_cache_lookup(const char *dir, const char *key, char *value, size_t cap);
+int jl_tune_cache_save(const char *dir, const char *key, const char *value);
+/* 16 hex digits identifying (GPU UUID, driver version, library build). */
+void jl_tune_device_key(const void *uuid16, int driver_version, const char *build_id, char out[17]);
+const char *jl_build_id(void);
+
 /* ---- integer view of the blocks: kernels.extract (jit/gpu/kernels/pack.go:252-386)
  * One record per 32-element sub-block: q[32] codes (Q4_K 0..15, Q8_0 -128..127,
  * MXFP4 raw e2m1 code 0..15, Q4_0 0..15, Q5_0 / Q5_1 / Q5_K 0..31), raw f16 bits of d

@@ -81,6 +81,9 @@ class LayersDesc(C.Structure):
 
 # Every symbol include/jitllm_b200.h declares: (restype, argtypes).
 _VP, _I, _SZ, _U32 = C.c_void_p, C.c_int, C.c_size_t, C.c_uint32
+TUNE_OFF, TUNE_ON, TUNE_FORCE = 0, 1, 2
+TUNE_TIMER = C.CFUNCTYPE(C.c_double, C.c_void_p, C.c_int, C.c_int)
+
 SYMBOLS = {
     "jl_version": (C.c_char_p, []),
     "jl_abi_version": (_I, []),
@@ -101,6 +104,14 @@ SYMBOLS = {
     "jl_moe_experts_dev": (_I, [_VP, _VP, _VP, _I, _VP, _I, C.POINTER(MoeDesc), _VP]),
     "jl_moe_reserve": (_I, [_VP, _I, _I, _I, _I, _I]),
     "jl_select": (_I, [_VP, _U32, _I, _I, _I, C.POINTER(Choice)]),
+    "jl_tune_configure": (_I, [_VP, _I, C.c_char_p]),
+    "jl_tune": (_I, [_VP, _VP, _I, C.POINTER(Choice)]),
+    "jl_tune_stats": (_I, [_VP, C.POINTER(C.c_int64 * 4)]),
+    "jl_tune_duel": (_I, [_I, _I, TUNE_TIMER, _VP, C.c_double, C.c_double, C.POINTER(_I), C.POINTER(C.c_double)]),
+    "jl_tune_cache_lookup": (_I, [C.c_char_p, C.c_char_p, C.c_char_p, _SZ]),
+    "jl_tune_cache_save": (_I, [C.c_char_p, C.c_char_p, C.c_char_p]),
+    "jl_tune_device_key": (None, [_VP, _I, C.c_char_p, C.c_char_p]),
+    "jl_build_id": (C.c_char_p, []),
     "jl_unpack": (_I, [_U32, _VP, _SZ, _VP, _VP, _VP, _VP, _VP]),
     "jl_unpack_resident": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _VP]),
     "jl_weight_upload": (_I, [_VP, _U32, _VP, _SZ, _I, _I, C.POINTER(_VP)]),

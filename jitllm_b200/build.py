@@ -7,6 +7,7 @@ header) is newer; the shared library lands beside this file.
 """
 from __future__ import annotations
 
+import hashlib
 import os
 import shutil
 import subprocess
@@ -16,7 +17,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libjitllm_b200.so")
-SOURCES = ["ctx.cu", "formats.cu", "gemv.cu", "gemv_q8.cu", "gemv_mxfp4.cu", "gemm_tc5.cu", "moe.cu", "aux.cu", "block.cu", "packed.cu"]
+SOURCES = ["ctx.cu", "formats.cu", "gemv.cu", "gemv_q8.cu", "gemv_mxfp4.cu", "gemm_tc5.cu", "moe.cu", "aux.cu", "block.cu", "packed.cu", "tune.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC,-fvisibility=hidden", "-DJL_BUILD",
@@ -42,14 +43,25 @@ def build(force: bool = False, verbose: bool = False) -> str:
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
     headers.append(os.path.join(HERE, "..", "include", "jitllm_b200.h"))
     nvcc = _nvcc()
+    # the build's identity: persisted selection verdicts are keyed on it (a changed kernel is measured again)
+    h = hashlib.sha1()
+    for f in sorted(headers + [os.path.join(CSRC, s) for s in SOURCES]):
+        h.update(open(f, "rb").read())
+    build_id = h.hexdigest()[:16]
+    stamp = os.path.join(OBJ, "build_id.txt")
+    if not os.path.exists(stamp) or open(stamp).read() != build_id:
+        open(stamp, "w").write(build_id)
     objs = []
     procs = []
     for s in SOURCES:
         src = os.path.join(CSRC, s)
         obj = os.path.join(OBJ, s.replace(".cu", ".o"))
         objs.append(obj)
-        if force or _newer(obj, [src] + headers):
+        extra = [stamp] if s == "tune.cu" else []
+        if force or _newer(obj, [src] + headers + extra):
             cmd = [nvcc, *NVCC_FLAGS, "-c", src, "-o", obj]
+            if s == "tune.cu":
+                cmd.insert(-4, f'-DJL_BUILD_ID="{build_id}"')
             if verbose:
                 cmd.insert(1, "-Xptxas=-v")
                 print(" ".join(cmd), flush=True)

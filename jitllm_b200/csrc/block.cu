@@ -794,10 +794,22 @@ __global__ void __launch_bounds__(BK_THREADS, 1) jl_block_kernel(const __grid_co
 
     // per-phase time stamps (phase start, prologue done, work done, barrier passed) of the first and last CTA
     const int tr_cta = blockIdx.x == 0 ? 0 : (blockIdx.x == gridDim.x - 1 ? 1 : -1);
+#ifdef BK_FINE_TRACE
+    // experimental builds only: every CTA's stamps, after the other regions
+#define BK_TRACE(slot)                                                                      \
+    do {                                                                                    \
+        if (P.trace && tid == 0) {                                                          \
+            const unsigned long long now_ = jl_gtime_ns();                                  \
+            if (tr_cta >= 0) P.trace[((size_t)tr_cta * P.nphases + p) * 4 + (slot)] = now_; \
+            P.trace[(size_t)2 * P.nphases * 4 + (size_t)P.nphases * 12 + (size_t)gridDim.x * 8 + ((size_t)blockIdx.x * P.nphases + p) * 4 + (slot)] = now_; \
+        }                                                                                   \
+    } while (0)
+#else
 #define BK_TRACE(slot)                                                                      \
     do {                                                                                    \
         if (P.trace && tr_cta >= 0 && tid == 0) P.trace[((size_t)tr_cta * P.nphases + p) * 4 + (slot)] = jl_gtime_ns(); \
     } while (0)
+#endif
 
 #ifdef BK_FINE_TRACE
     // experimental builds only: clock64 spent between marks 0..6 of the consume loop, first CTA's first warp, per phase
@@ -1045,7 +1057,11 @@ JL_EXPORT int jl_layers_prep(jl_ctx *ctx, const jl_layers_desc *d, jl_layers **o
     // zeroed in front of every launch: the grid barrier's counter, the abort word, every attention phase's tickets
     S->zero_bytes = 16 + (size_t)L * hkv * 4;
     const size_t o_bar = take(S->zero_bytes);
+#ifdef BK_FINE_TRACE
+    const size_t o_trace = take((size_t)2 * nph * 4 * 8 + (size_t)nph * 12 * 8 + (size_t)S->grid * 8 * 8 + (size_t)S->grid * nph * 4 * 8);
+#else
     const size_t o_trace = take((size_t)2 * nph * 4 * 8 + (size_t)nph * 12 * 8 + (size_t)S->grid * 8 * 8);
+#endif
     S->slot_bytes = bk_slot_bytes(world, H);
     cudaError_t e = cudaMalloc(&S->buf, off);
     if (e == cudaSuccess) e = cudaMalloc(&S->slot, S->slot_bytes);
@@ -1243,7 +1259,8 @@ JL_EXPORT int jl_layers_profile(jl_ctx *ctx, jl_layers *S, long long *tok_dev, l
     if (n_phases != S->P.nphases) return jl_set_err(ctx, JL_EINVAL, "this stack has %d phases", S->P.nphases);
     size_t bytes = (size_t)2 * n_phases * 4 * 8;
 #ifdef BK_FINE_TRACE
-    bytes += (size_t)n_phases * 12 * 8 + (size_t)S->grid * 8 * 8;   // experimental builds: clock counts of the consume loop and the prologue, per-CTA attention stamps
+    // experimental builds: clock counts of the consume loop and the prologue, per-CTA attention stamps, every CTA's phase stamps
+    bytes += (size_t)n_phases * 12 * 8 + (size_t)S->grid * 8 * 8 + (size_t)S->grid * n_phases * 4 * 8;
 #endif
     JL_CUDA(ctx, cudaSetDevice(ctx->device));
     JL_CUDA(ctx, cudaMemsetAsync(S->trace, 0, bytes, (cudaStream_t)stream));

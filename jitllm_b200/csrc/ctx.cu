@@ -48,6 +48,8 @@ JL_EXPORT int jl_open(int device, const jl_opts *opts, jl_ctx **out) {
     c->x_dev = c->o_dev = c->scratch = c->x_pin = c->o_pin = nullptr;
     c->x_cap = c->o_cap = c->scratch_cap = c->x_pin_cap = c->o_pin_cap = 0;
     c->call_ordinal = 0;
+    c->tune_mode = JL_TUNE_OFF; c->tune_devkey[0] = 0; c->force_variant = -1;
+    c->tune_trials = c->tune_measured = c->tune_cached = c->tune_refused = 0;
     if (cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) != cudaSuccess) {
         delete c;
         return JL_ECUDA;
@@ -342,6 +344,8 @@ JL_EXPORT int jl_weight_upload_bank(jl_ctx *ctx, uint32_t type, const void *w_ho
         std::lock_guard<std::mutex> lk2(ctx->cache_mu);
         ctx->st.resident_bytes += (*out)->raw_bytes;
     }
+    // measured selection: the decode variant of a new shape is timed here, against the copy that will be read
+    if (rc == JL_OK && ctx->tune_mode != JL_TUNE_OFF) jl_tune_shape_locked(ctx, *out, 1);
     return rc;
 }
 
@@ -366,9 +370,9 @@ JL_EXPORT void jl_weight_free(jl_ctx *ctx, jl_weight *w) {
 
 static int choose(jl_ctx *ctx, uint32_t type, int nrows, int k, int ntok, jl_choice *out) {
     int pin = ctx->opts.pin_kernel;
-    // the decode kernels serve up to 8 tokens; measured at 16 and 32 tokens the Q8_0 one (which loops over
-    // token groups with the weights in registers) only ties with or loses to the GEMM
-    const int decode_max = 8;
+    // the decode kernels serve up to 8 tokens; Q8_0 has a batch kernel for up to 32 (one pass over the weights,
+    // no conversion of the codes: at 32 tokens the GEMM's fixed cost is several times that kernel's whole run)
+    const int decode_max = (type == JL_TYPE_Q8_0 && k % 256 == 0) ? 32 : 8;
     if ((pin == JL_K_TC5 || (pin == JL_K_AUTO && ntok > decode_max)) && jl_gemm_tc5_supported(type, nrows, k, ntok))
         return jl_gemm_tc5_choice(ctx, type, nrows, k, ntok, out);
     if (pin == JL_K_TC5) return JL_DECLINED;

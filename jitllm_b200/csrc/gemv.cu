@@ -410,6 +410,12 @@ static int q4k_find(int form, int warps, int stages, int rg, int minb, int nsb) 
 static int q4k_pick(const jl_ctx *ctx, int nrows, int nsb, int ntok, bool have_x) {
     const jl_opts &o = ctx->opts;
     const int nrg = (nrows + 15) / 16;
+    if (ctx->force_variant >= 0) return ctx->force_variant;       // a tuning trial is timing this variant
+    if (have_x && o.decode_form == JL_FORM_AUTO && !o.pin_warps && !(o.flags & JL_FLAG_DECODE_CONCURRENT)) {
+        // a measured verdict for this shape (tune.cu) overrides the table below
+        auto it = ctx->tuned.find(jl_tune_shape_key(JL_TYPE_Q4_K, nrows, nsb * 256, ntok));
+        if (it != ctx->tuned.end()) return it->second;
+    }
     int form = o.decode_form;
     if (form < JL_FORM_AUTO || form > JL_FORM_L1) form = JL_FORM_AUTO;
     if (!have_x && (form == JL_FORM_FUSED || form == JL_FORM_WIDE)) form = JL_FORM_AUTO;   // those convert x themselves
@@ -441,6 +447,32 @@ static int q4k_pick(const jl_ctx *ctx, int nrows, int nsb, int ntok, bool have_x
     if (idx < 0) idx = q4k_find(form, 0, 0, 0, 0, nsb);
     if (idx < 0) idx = q4k_find(JL_FORM_SPLIT, 0, 0, 0, 0, nsb);
     return idx;
+}
+
+// tune.cu: the variants a shape may run, the table's pick first.
+int jl_gemv_tune_candidates(jl_ctx *ctx, int nrows, int k, int ntok, int *out, int cap) {
+    const int nsb = k / 256;
+    if (k % 256 || ntok < 1 || ntok > 8 || cap < 1) return 0;
+    const uint64_t key = jl_tune_shape_key(JL_TYPE_Q4_K, nrows, k, ntok);
+    int held = -1;
+    auto it = ctx->tuned.find(key);
+    if (it != ctx->tuned.end()) { held = it->second; ctx->tuned.erase(it); }
+    const int first = q4k_pick(ctx, nrows, nsb, ntok, true);
+    if (held >= 0) ctx->tuned[key] = held;
+    if (first < 0) return 0;
+    int n = 0;
+    out[n++] = first;
+    for (int i = 0; i < Q4K_NVARIANTS && n < cap; i++)
+        if (i != first && q4k_variant_smem(q4k_variants[i], nsb) <= 200 * 1024) out[n++] = i;
+    return n;
+}
+int jl_gemv_variant_index(int form, int warps, int stages, int minb, int rg, int nsb) {
+    if (warps < 1 || stages < 1 || minb < 1 || rg < 1) return -1;
+    return q4k_find(form, warps, stages, rg, minb, nsb);
+}
+void jl_gemv_variant_describe(int idx, int *form, int *warps, int *stages, int *minb, int *rg) {
+    const q4k_variant &v = q4k_variants[idx];
+    *form = v.form; *warps = v.warps; *stages = v.stages; *minb = v.minb; *rg = v.rg;
 }
 
 static bool q4k_mma_ok(uint32_t type, int k) {
@@ -479,6 +511,12 @@ int jl_gemv_choice(jl_ctx *ctx, uint32_t type, int nrows, int k, int ntok, jl_ch
         c.split_k = c.warps; c.tile_m = 16; c.tile_n = 8; c.tile_k = 32;
         const int tgroups = (ntok + 3) / 4, ntg = tgroups >= 4 ? 4 : (tgroups >= 2 ? 2 : 1);
         c.grid = (nrows + 15) / 16 * ((tgroups + ntg - 1) / ntg);
+        if (ntok > 8 && ntok <= 32) {   // the batch kernel: a row tile per CTA, k-slices as one cluster
+            int bw, ks;
+            jl_gemv_q8_batch_plan(nrows, k, &bw, &ks);
+            c.warps = bw; c.rows_per_cta = 16 * bw; c.split_k = ks;
+            c.grid = (nrows + 16 * bw - 1) / (16 * bw) * ks;
+        }
         c.launches = 2;
         *out = c;
         return JL_OK;

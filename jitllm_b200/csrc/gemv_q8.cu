@@ -1,4 +1,4 @@
-// Q8_0 decode and small batches (1..32 tokens) on the int8 tensor-core path.
+// Q8_0 decode (1..8 tokens) and small batches (9..32 tokens) on the int8 tensor-core path.
 //
 // Q8_0 weights ARE int8, so they feed mma.sync.m16n8k32.s32.s8.s8 unconverted: one MMA covers 16 rows
 // x one 32-element block, whose f16 scale d is applied to the integer sum afterwards. Activations are
@@ -173,6 +173,185 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_q8_mma_kernel(const uint8_t *
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Batches of 9..32 tokens: one pass over the weights for all tokens.
+//
+// A CTA of WARPS warps covers 16 * WARPS rows (a row group of 16 per warp) and a slice of the row's 256-element
+// groups; all of its warps work on the same group at a time, so the group's prepared activations of all tokens
+// (32 x 544 bytes) are staged ONCE per CTA in shared memory (cp.async, two stages) and every warp takes its MMA B
+// fragments from there. The weights go straight from global memory into registers, one group ahead, and are used
+// by up to eight token groups of four. The k-slices of a row tile are the CTAs of one thread-block cluster: each
+// leaves its partial tile in its own shared memory, and after a cluster barrier CTA r sums slice r of the tile
+// over the ranks in rank order through distributed shared memory (bit-stable; no partial planes in global memory,
+// no second launch, no flag that one CTA would spin on).
+#include <cooperative_groups.h>
+namespace cg = cooperative_groups;
+
+#define Q8B_TOK 32
+#define Q8B_TOK_BYTES 544          // 4 spans x 128 B of digits + 8 x f32 (1/s of the group's blocks)
+
+__device__ __forceinline__ void q8b_cp16(void *smem, const void *g) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(g) : "memory");
+}
+
+template <int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, 2)
+gemv_q8_batch_kernel(const uint8_t *__restrict__ codes, const uint16_t *__restrict__ dplane, int d_stride,
+                     const uint8_t *__restrict__ xop, size_t tok_stride, float *__restrict__ Y, int nrows, int k, int ntok,
+                     int groups_per_cta) {
+    constexpr int ROWS = WARPS * 16, RED_STRIDE = ROWS + 4;
+    constexpr int STAGE = Q8B_TOK * Q8B_TOK_BYTES;
+    static_assert(Q8B_TOK * RED_STRIDE * 4 <= 2 * STAGE, "the partial tile reuses the activation stages");
+    __shared__ __align__(16) uint8_t smem[2 * STAGE];
+    cg::cluster_group cluster = cg::this_cluster();
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int row0 = blockIdx.x * ROWS + warp * 16;
+    const int row_a = min(row0 + g, nrows - 1), row_b = min(row0 + g + 8, nrows - 1);
+    const int grp0 = blockIdx.y * groups_per_cta;
+    const int ntg = (ntok + 3) >> 2;
+    const uint8_t *ca = codes + (size_t)row_a * k + t * 16, *cb = codes + (size_t)row_b * k + t * 16;
+    const uint8_t *da = reinterpret_cast<const uint8_t *>(dplane + (size_t)row_a * d_stride);
+    const uint8_t *db = reinterpret_cast<const uint8_t *>(dplane + (size_t)row_b * d_stride);
+
+    // weights of the first group: they do not depend on the kernel in front
+    uint4 wa[4], wb[4], dda, ddb;
+#pragma unroll
+    for (int s = 0; s < 4; s++) {
+        wa[s] = q8_ldg16(ca + (size_t)grp0 * 256 + s * 64);
+        wb[s] = q8_ldg16(cb + (size_t)grp0 * 256 + s * 64);
+    }
+    dda = q8_ldg16(da + (size_t)grp0 * 16);
+    ddb = q8_ldg16(db + (size_t)grp0 * 16);
+    // tokens beyond ntok multiply zeros
+    for (int i = tid; i < 2 * STAGE / 16; i += WARPS * 32) reinterpret_cast<uint4 *>(smem)[i] = make_uint4(0, 0, 0, 0);
+    __syncthreads();
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");   // the prepared activations come from the kernel in front
+
+    auto stage_in = [&](int st, int grp) {
+        uint8_t *dst = smem + st * STAGE;
+        for (int i = tid; i < ntok * 34; i += WARPS * 32) {
+            const int tok = i / 34, c = i - tok * 34;
+            const uint8_t *src = xop + (size_t)tok * tok_stride + (c < 32 ? (size_t)grp * 512 + c * 16 : (size_t)k * 2 + (size_t)grp * 32 + (c - 32) * 16);
+            q8b_cp16(dst + tok * Q8B_TOK_BYTES + c * 16, src);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    stage_in(0, grp0);
+
+    float acc_a[8], acc_b[8];
+#pragma unroll
+    for (int tg = 0; tg < 8; tg++) acc_a[tg] = acc_b[tg] = 0.f;
+    const int lane_xofs = (g >> 1) * Q8B_TOK_BYTES + (g & 1) * 64 + t * 16;   // B column: token 4 tg + (g >> 1), digit g & 1
+    const int lane_iofs = t * Q8B_TOK_BYTES + 512;                            // accumulators: token 4 tg + t
+
+    for (int i = 0; i < groups_per_cta; i++) {
+        const int grp = grp0 + i;
+        const uint4 ua[4] = {wa[0], wa[1], wa[2], wa[3]}, ub[4] = {wb[0], wb[1], wb[2], wb[3]};
+        const uint32_t dwa[4] = {dda.x, dda.y, dda.z, dda.w}, dwb[4] = {ddb.x, ddb.y, ddb.z, ddb.w};
+        if (i + 1 < groups_per_cta) {
+#pragma unroll
+            for (int s = 0; s < 4; s++) {
+                wa[s] = q8_ldg16(ca + (size_t)(grp + 1) * 256 + s * 64);
+                wb[s] = q8_ldg16(cb + (size_t)(grp + 1) * 256 + s * 64);
+            }
+            dda = q8_ldg16(da + (size_t)(grp + 1) * 16);
+            ddb = q8_ldg16(db + (size_t)(grp + 1) * 16);
+            stage_in((i + 1) & 1, grp + 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();
+        const uint8_t *xs = smem + (i & 1) * STAGE;
+        float2 fa[4], fb[4];
+#pragma unroll
+        for (int s = 0; s < 4; s++) {
+            fa[s] = __half22float2(*reinterpret_cast<const __half2 *>(&dwa[s]));
+            fb[s] = __half22float2(*reinterpret_cast<const __half2 *>(&dwb[s]));
+        }
+#pragma unroll
+        for (int tg = 0; tg < 8; tg++) {
+            if (tg < ntg) {
+                const uint8_t *xb = xs + tg * 4 * Q8B_TOK_BYTES;
+                uint4 xv[4];
+#pragma unroll
+                for (int s = 0; s < 4; s++) xv[s] = *reinterpret_cast<const uint4 *>(xb + lane_xofs + s * 128);
+                const float4 isA = *reinterpret_cast<const float4 *>(xb + lane_iofs);
+                const float4 isB = *reinterpret_cast<const float4 *>(xb + lane_iofs + 16);
+                const float isb[8] = {isA.x, isA.y, isA.z, isA.w, isB.x, isB.y, isB.z, isB.w};
+                float ga = 0.f, gb = 0.f;
+#pragma unroll
+                for (int s = 0; s < 4; s++) {
+                    int c0[4], c1[4];
+                    q8_mma(c0, ua[s].x, ub[s].x, ua[s].y, ub[s].y, xv[s].x, xv[s].y);     // block 2s
+                    q8_mma(c1, ua[s].z, ub[s].z, ua[s].w, ub[s].w, xv[s].z, xv[s].w);     // block 2s + 1
+                    ga = fmaf(fa[s].x * isb[2 * s], (float)(256 * c0[0] + c0[1]), ga);
+                    gb = fmaf(fb[s].x * isb[2 * s], (float)(256 * c0[2] + c0[3]), gb);
+                    ga = fmaf(fa[s].y * isb[2 * s + 1], (float)(256 * c1[0] + c1[1]), ga);
+                    gb = fmaf(fb[s].y * isb[2 * s + 1], (float)(256 * c1[2] + c1[3]), gb);
+                }
+                acc_a[tg] += ga;
+                acc_b[tg] += gb;
+            }
+        }
+        __syncthreads();   // the stage is refilled two iterations on
+    }
+
+    // partial tile [token][row] into this CTA's shared memory, then the cluster's ranks sum it slice by slice
+    float *red = reinterpret_cast<float *>(smem);
+#pragma unroll
+    for (int tg = 0; tg < 8; tg++) {
+        red[(4 * tg + t) * RED_STRIDE + warp * 16 + g] = acc_a[tg];
+        red[(4 * tg + t) * RED_STRIDE + warp * 16 + g + 8] = acc_b[tg];
+    }
+    cluster.sync();
+    const int ks = gridDim.y, rank = blockIdx.y;      // the cluster spans the whole y dimension
+    const int per = (ntok * ROWS + ks - 1) / ks;
+    const int e1 = min(ntok * ROWS, (rank + 1) * per);
+    for (int e = rank * per + tid; e < e1; e += WARPS * 32) {
+        const int tok = e / ROWS, r = e - tok * ROWS;
+        float sum = 0.f;
+        for (int q = 0; q < ks; q++) sum += cluster.map_shared_rank(red, q)[tok * RED_STRIDE + r];   // rank order
+        const int row = blockIdx.x * ROWS + r;
+        if (row < nrows) Y[(size_t)tok * nrows + row] = sum;
+    }
+    cluster.sync();    // nobody leaves while a peer still reads its tile
+}
+
+// Row tile (warps) and k-slices of the batch kernel for a shape: the fewest slices that give every SM a CTA.
+void jl_gemv_q8_batch_plan(int nrows, int k, int *warps, int *slices) {
+    const int ngrp = k / 256;
+    const int w = nrows >= 2048 ? 8 : 4;
+    const int tiles = (nrows + 16 * w - 1) / (16 * w);
+    int ks = 1;
+    while (ks < 8 && tiles * ks < 148 && ngrp % (ks * 2) == 0) ks *= 2;
+    *warps = w;
+    *slices = ks;
+}
+
+static int launch_q8_batch(jl_ctx *ctx, float *out_dev, const uint8_t *codes, const uint16_t *dpl, int d_stride,
+                           const uint8_t *xop, size_t tok_stride, int nrows, int k, int ntok, cudaStream_t s) {
+    int warps, ks;
+    jl_gemv_q8_batch_plan(nrows, k, &warps, &ks);
+    cudaLaunchAttribute at[2];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = 1; at[0].val.clusterDim.y = ks; at[0].val.clusterDim.z = 1;
+    at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[1].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((nrows + 16 * warps - 1) / (16 * warps), ks); cfg.blockDim = dim3(warps * 32); cfg.stream = s;
+    cfg.attrs = at; cfg.numAttrs = (ctx->opts.flags & JL_FLAG_NO_PDL) ? 1 : 2;
+    const int gpc = k / 256 / ks;
+    if (warps == 8)
+        JL_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemv_q8_batch_kernel<8>, codes, dpl, d_stride, xop, tok_stride, out_dev, nrows, k, ntok, gpc));
+    else
+        JL_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemv_q8_batch_kernel<4>, codes, dpl, d_stride, xop, tok_stride, out_dev, nrows, k, ntok, gpc));
+    ctx->st.launches++;
+    return JL_OK;
+}
+
 int jl_launch_gemv_q8(jl_ctx *ctx, float *out_dev, const uint8_t *codes, const uint8_t *scales, int d_stride,
                       const float *x_dev, int nrows, int k, int ntok, cudaStream_t s) {
     const size_t tok_stride = (q8_xp_token_bytes(k) + 255) & ~(size_t)255;
@@ -189,6 +368,8 @@ int jl_launch_gemv_q8(jl_ctx *ctx, float *out_dev, const uint8_t *codes, const u
     cfg.gridDim = dim3((k / 256 + 3) / 4, ntok); cfg.blockDim = dim3(128); cfg.stream = s; cfg.attrs = at; cfg.numAttrs = nattr;
     JL_CUDA(ctx, cudaLaunchKernelEx(&cfg, q8_xprep_kernel, x_dev, scratch, k, tok_stride));
     ctx->st.launches++;
+    if (ntok > 8 && ntok <= Q8B_TOK)
+        return launch_q8_batch(ctx, out_dev, codes, reinterpret_cast<const uint16_t *>(scales), d_stride, scratch, tok_stride, nrows, k, ntok, s);
     const int ngrp = k / 256;
     const int warps = ngrp >= 8 ? 8 : (ngrp >= 4 ? 4 : (ngrp >= 2 ? 2 : 1));
     const int tgroups = (ntok + 3) / 4;

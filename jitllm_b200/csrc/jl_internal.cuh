@@ -113,7 +113,23 @@ struct jl_ctx {
     // fault injection
     std::vector<int> fail_at;
     int call_ordinal;
+    // measured selection (tune.cu)
+    int tune_mode;                      // jl_tune_mode
+    std::string tune_dir;               // where verdicts persist ("" = nowhere)
+    char tune_devkey[17];               // GPU UUID + driver + build of this library, hashed
+    std::map<uint64_t, int> tuned;      // (type, rows, k, tokens) -> decode variant
+    int force_variant;                  // >= 0 while a trial times that variant
+    int64_t tune_trials, tune_measured, tune_cached, tune_refused;
 };
+
+static inline uint64_t jl_tune_shape_key(uint32_t type, int nrows, int k, int ntok) {
+    return ((uint64_t)type << 56) ^ ((uint64_t)ntok << 48) ^ ((uint64_t)(uint32_t)nrows << 24) ^ (uint64_t)(uint32_t)k;
+}
+// tune.cu / gemv.cu
+int jl_tune_shape_locked(jl_ctx *ctx, const jl_weight *w, int ntok);
+int jl_gemv_tune_candidates(jl_ctx *ctx, int nrows, int k, int ntok, int *out, int cap);
+int jl_gemv_variant_index(int form, int warps, int stages, int minb, int rg, int nsb);
+void jl_gemv_variant_describe(int idx, int *form, int *warps, int *stages, int *minb, int *rg);
 
 #define JL_CUDA(ctx, call)                                                           \
     do {                                                                             \
@@ -137,6 +153,7 @@ size_t jl_gemv_q8_scratch_bytes(int k, int ntok);
 size_t jl_gemv_mxfp4_scratch_bytes(int k, int ntok);
 int jl_launch_gemv_mxfp4(jl_ctx *ctx, float *out_dev, const uint8_t *codes, const uint8_t *eplane, int e_stride,
                          const float *x_dev, int nrows, int k, int ntok, cudaStream_t s);
+void jl_gemv_q8_batch_plan(int nrows, int k, int *warps, int *slices);
 int jl_launch_gemv_q8(jl_ctx *ctx, float *out_dev, const uint8_t *codes, const uint8_t *scales, int d_stride,
                       const float *x_dev, int nrows, int k, int ntok, cudaStream_t s);
 int jl_launch_gemv(jl_ctx *ctx, float *out_dev, const jl_weight *w, int expert, const float *x_dev,

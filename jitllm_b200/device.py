@@ -245,6 +245,23 @@ class Device:
         self.last_status = rc
         return ch if rc == _lib.OK else None
 
+    def WithTune(self, mode: int = _lib.TUNE_ON, cache_dir: str | None = None) -> None:
+        """Measured selection (the reference's WithTune / WithTuneCache, jit/gpu/tier/split.go:18-75): new shapes
+        are timed at upload; verdicts persist under cache_dir keyed by GPU UUID + driver + library build."""
+        self._check(self.lib.jl_tune_configure(self.ctx, mode, cache_dir.encode() if cache_dir else None))
+
+    def Tune(self, weight: "Weight", ntok: int = 1) -> Choice | None:
+        """Measure (or load) the verdict for this weight's shape now; returns what will run."""
+        ch = Choice()
+        rc = self.lib.jl_tune(self.ctx, weight.handle, ntok, C.byref(ch))
+        self.last_status = rc
+        return ch if rc == _lib.OK else None
+
+    def TuneStats(self) -> dict:
+        out = (C.c_int64 * 4)()
+        self._check(self.lib.jl_tune_stats(self.ctx, C.byref(out)))
+        return dict(trials=out[0], measured=out[1], cached=out[2], refused=out[3])
+
     def Stats(self) -> Stats:
         s = Stats()
         self._check(self.lib.jl_stats_get(self.ctx, C.byref(s)))

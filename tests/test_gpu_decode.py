@@ -445,3 +445,74 @@ def test_decode_reference_distributions_and_shapes(orc, t, dist):
             assert np.isfinite(out).all()
             assert parity_err(out, ref) <= BAR, (nrows, k, parity_err(out, ref))
             d.Forget(w)
+
+
+def test_measured_selection_times_the_variants_persists_and_is_what_launches(orc, tmp_path):
+    """With tuning on, the first upload of a shape runs the timed duel over the decode variants; the verdict is what
+    jl_select reports AND what launches; it persists, a second context answers from the file without a single trial,
+    a damaged entry is measured again and overwritten, and a context that pins its form does not tune."""
+    import torch
+    from jitllm_b200 import _lib
+    rng = synth.rng_for(0x7E)
+    nrows, k = 4096, 4096
+    w = synth.q4k_matrix(rng, nrows, k)
+    x = synth.activations(rng, 1, k)
+    ref = orc.matmul_f64(Q4_K, w, x, nrows, k, 1)
+    cache = str(tmp_path / "tune")
+
+    def serve(d, h):
+        ch = d.Select(Q4_K, nrows, k, 1)
+        xd, out = torch.from_numpy(x).cuda(), torch.empty(1, nrows, device="cuda")
+        n0 = d.Stats().launches
+        d.MatMulDev(out, h, xd, 1, torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+        assert d.Stats().launches - n0 == ch.launches
+        assert parity_err(out.cpu().numpy(), ref) <= 2e-3
+        return (ch.form, ch.warps, ch.stages, ch.rows_per_cta, ch.grid)
+
+    with Device(0) as d:
+        d.WithTune(_lib.TUNE_ON, cache)
+        n0 = d.Stats().launches
+        h = d.Upload(Q4_K, w, nrows, k)
+        ts = d.TuneStats()
+        assert ts["trials"] >= 2 * 11 and ts["measured"] + (1 if ts["refused"] else 0) >= 1
+        assert d.Stats().launches == n0                              # trials are not served work
+        first = serve(d, h)
+        h2 = d.Upload(Q4_K, w, nrows, k)                             # the same shape again: no new trials
+        assert d.TuneStats()["trials"] == ts["trials"]
+        h.free(); h2.free()
+    measured = ts["measured"] == 1
+    if measured:
+        line = open(cache + "/jl_select1").read()
+        assert f"/12-{nrows}x{k}x1 " in line and line.count("\n") == 1
+        with Device(0) as d:                                         # a later process: answered from the file
+            d.WithTune(_lib.TUNE_ON, cache)
+            h = d.Upload(Q4_K, w, nrows, k)
+            ts2 = d.TuneStats()
+            assert ts2["trials"] == 0 and ts2["cached"] == 1
+            assert serve(d, h) == first
+            h.free()
+        key = line.split(" ")[0]
+        open(cache + "/jl_select1", "w").write(f"{key} 9 9 9 9 9\n")  # names no variant: measured again, overwritten
+        with Device(0) as d:
+            d.WithTune(_lib.TUNE_ON, cache)
+            h = d.Upload(Q4_K, w, nrows, k)
+            ts3 = d.TuneStats()
+            assert ts3["trials"] > 0 and ts3["cached"] == 0
+            serve(d, h)
+            h.free()
+        if ts3["measured"]:
+            assert " 9 9 9 9 9" not in open(cache + "/jl_select1").read()
+    with Device(0, decode_form=FORM_SPLIT) as d:                     # the caller chose already
+        d.WithTune(_lib.TUNE_FORCE, cache)
+        h = d.Upload(Q4_K, w, nrows, k)
+        assert d.TuneStats()["trials"] == 0
+        assert d.Select(Q4_K, nrows, k, 1).form == FORM_SPLIT
+        h.free()
+    with Device(0) as d:                                             # explicit call on a context with tuning off
+        h = d.Upload(Q4_K, w, nrows, k)
+        assert d.TuneStats()["trials"] == 0
+        ch = d.Tune(h, 2)
+        assert ch is not None and d.TuneStats()["trials"] > 0
+        assert (ch.form, ch.warps, ch.stages) == (lambda c: (c.form, c.warps, c.stages))(d.Select(Q4_K, nrows, k, 2))
+        h.free()

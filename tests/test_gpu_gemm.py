@@ -127,17 +127,43 @@ def _run_q8(dev, orc, nrows, k, ntok, seed, x_dtype):
 
 @pytest.mark.parametrize("nrows,k,ntok,x_dtype", [(4096, 4096, 32, DT_F32), (1024, 4096, 32, DT_F32), (14336, 4096, 32, DT_F32),
                                                    (200, 512, 9, DT_F32), (256, 256, 64, DT_BF16), (520, 1024, 300, DT_BF16),
-                                                   (300, 512, 40, DT_F32), (128, 256, 17, DT_F32)])
+                                                   (300, 512, 40, DT_F32), (128, 256, 17, DT_F32), (4096, 14336, 32, DT_F32),
+                                                   (2049, 768, 31, DT_F32), (17, 256, 10, DT_F32), (512, 2048, 32, DT_BF16),
+                                                   (128, 160, 12, DT_F32)])
 def test_q8_0_batched_gemm_matches_oracle(orc, nrows, k, ntok, x_dtype):
+    """Batches above 8 tokens. f32 activations of up to 32 tokens and k a multiple of 256 run the int8 batch kernel
+    (one pass over the weights, k-slices summed inside a cluster); everything else the tcgen05 GEMM."""
     from jitllm_b200 import Q8_0
-    from jitllm_b200 import K_MMA
-    with Device(0) as d:                      # selection on its own: more than 8 tokens -> the tcgen05 GEMM
+    from jitllm_b200 import K_MMA, K_SIMT
+    with Device(0) as d:
         ch = d.Select(Q8_0, nrows, k, ntok)
-        assert ch is not None and ch.kernel == K_TC5
+        batch_kernel = ntok <= 32 and k % 256 == 0
+        assert ch is not None and ch.kernel == (K_MMA if batch_kernel else (K_TC5 if k % 256 == 0 else K_SIMT))
+        if batch_kernel:
+            assert ch.rows_per_cta in (64, 128) and ch.split_k in (1, 2, 4, 8) and (k // 256) % ch.split_k == 0
+            assert ch.grid == -(-nrows // ch.rows_per_cta) * ch.split_k and ch.launches == 2
         got, ref = _run_q8(d, orc, nrows, k, ntok, 0xB208 + nrows + ntok, x_dtype)
         assert np.isfinite(got).all()
         assert parity_err(got, ref) <= BAR, (parity_err(got, ref), nmse(got, ref))
         assert nmse(got, ref) <= 1e-6
+
+
+def test_q8_0_batch_kernel_same_bits_twice_and_ragged_token_counts(orc):
+    """The cluster's ranks sum the k-slices in rank order: two runs give the same bits; every token count of 9..32
+    (the last token group partly empty) is right."""
+    from jitllm_b200 import Q8_0
+    rng = synth.rng_for(0xB2AA)
+    nrows, k = 1000, 2048
+    w = synth.q8_0_matrix(rng, nrows, k)
+    with Device(0) as d:
+        for ntok in range(9, 33):
+            x = synth.activations(rng, ntok, k)
+            a, b = np.empty((ntok, nrows), np.float32), np.full((ntok, nrows), np.nan, np.float32)
+            assert d.MatMulRaw(a, DT_F32, Q8_0, w, x, DT_F32, nrows, k, ntok), d.Err()
+            assert d.MatMulRaw(b, DT_F32, Q8_0, w, x, DT_F32, nrows, k, ntok), d.Err()
+            assert np.array_equal(a, b)
+            ref = orc.matmul_f64(Q8_0, w, x, nrows, k, ntok)
+            assert parity_err(a, ref) <= BAR, ntok
 
 
 def test_q8_0_gemm_agrees_with_the_simt_check_kernel(orc):
