@@ -14,6 +14,8 @@
 // 16 rows and meet in shared memory in fixed order (bit-stable).
 #include "jl_internal.cuh"
 
+#include <stdlib.h>
+
 // Prepared activation operand of one token: k/64 spans x [digit 2][t 4] x 16 B, then k/32 f32 (1/s of each block).
 static inline size_t q8_xp_token_bytes(int k) { return (size_t)k * 2 + (size_t)(k / 32) * 4; }
 size_t jl_gemv_q8_scratch_bytes(int k, int ntok) { return ((q8_xp_token_bytes(k) + 255) & ~(size_t)255) * ntok; }
@@ -232,7 +234,7 @@ gemv_q8_batch_kernel(const uint8_t *__restrict__ codes, const uint16_t *__restri
     auto stage_in = [&](int st, int grp) {
         uint8_t *dst = smem + st * STAGE;
         for (int i = tid; i < ntok * 34; i += WARPS * 32) {
-            const int tok = i / 34, c = i - tok * 34;
+            const int tok = (int)(((unsigned)i * 1928u) >> 16), c = i - tok * 34;   // i / 34 for i < 32 * 34
             const uint8_t *src = xop + (size_t)tok * tok_stride + (c < 32 ? (size_t)grp * 512 + c * 16 : (size_t)k * 2 + (size_t)grp * 32 + (c - 32) * 16);
             q8b_cp16(dst + tok * Q8B_TOK_BYTES + c * 16, src);
         }
@@ -308,14 +310,33 @@ gemv_q8_batch_kernel(const uint8_t *__restrict__ codes, const uint16_t *__restri
     }
     cluster.sync();
     const int ks = gridDim.y, rank = blockIdx.y;      // the cluster spans the whole y dimension
-    const int per = (ntok * ROWS + ks - 1) / ks;
-    const int e1 = min(ntok * ROWS, (rank + 1) * per);
+    // four consecutive rows of one token per thread; the ranks' values are fetched together (independent loads over
+    // distributed shared memory: one after the other they cost a round trip each), then added in rank order
+    const float4 *peer[8];
+#pragma unroll
+    for (int q = 0; q < 8; q++) peer[q] = reinterpret_cast<const float4 *>(cluster.map_shared_rank(red, q < ks ? q : 0));
+    const int nvec = ntok * (ROWS / 4), per = (nvec + ks - 1) / ks;
+    const int e1 = min(nvec, (rank + 1) * per);
     for (int e = rank * per + tid; e < e1; e += WARPS * 32) {
-        const int tok = e / ROWS, r = e - tok * ROWS;
-        float sum = 0.f;
-        for (int q = 0; q < ks; q++) sum += cluster.map_shared_rank(red, q)[tok * RED_STRIDE + r];   // rank order
-        const int row = blockIdx.x * ROWS + r;
-        if (row < nrows) Y[(size_t)tok * nrows + row] = sum;
+        const int tok = e / (ROWS / 4), r4 = e - tok * (ROWS / 4);
+        float4 v[8];
+#pragma unroll
+        for (int q = 0; q < 8; q++)
+            if (q < ks) v[q] = peer[q][(tok * RED_STRIDE) / 4 + r4];
+        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int q = 0; q < 8; q++)
+            if (q < ks) { sum.x += v[q].x; sum.y += v[q].y; sum.z += v[q].z; sum.w += v[q].w; }
+        const int row = blockIdx.x * ROWS + 4 * r4;
+        float *y = Y + (size_t)tok * nrows + row;
+        if (row + 3 < nrows && (nrows & 3) == 0) {
+            *reinterpret_cast<float4 *>(y) = sum;
+        } else {
+            if (row < nrows) y[0] = sum.x;
+            if (row + 1 < nrows) y[1] = sum.y;
+            if (row + 2 < nrows) y[2] = sum.z;
+            if (row + 3 < nrows) y[3] = sum.w;
+        }
     }
     cluster.sync();    // nobody leaves while a peer still reads its tile
 }
@@ -327,6 +348,9 @@ void jl_gemv_q8_batch_plan(int nrows, int k, int *warps, int *slices) {
     const int tiles = (nrows + 16 * w - 1) / (16 * w);
     int ks = 1;
     while (ks < 8 && tiles * ks < 148 && ngrp % (ks * 2) == 0) ks *= 2;
+#ifdef JL_EXPERIMENT_ENV
+    if (const char *e = getenv("Q8B_KS")) { const int v = atoi(e); if (v >= 1 && v <= 8 && ngrp % v == 0) ks = v; }
+#endif
     *warps = w;
     *slices = ks;
 }
