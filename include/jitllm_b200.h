@@ -221,7 +221,17 @@ typedef struct jl_moe_desc {
     const float *gate_bias, *up_bias, *down_bias; /* [n_expert][rows] f32 or NULL */
     const float *router_bias;      /* logit bias [n_expert]: added to the logits before the softmax, or NULL */
     const float *sel_bias;         /* selection-only bias [n_expert] on the gated scores, or NULL */
+    int32_t arm;                   /* jl_moe_arm; 0 = the exact-weights arm (the parity arm) */
 } jl_moe_desc;
+/* Numerics arms of the expert GEMMs (jl_moe, jl_moe_dev and jl_moe_experts_dev).
+ * EXACT: MXFP4 weights dequantised exactly to f16, activations as f16 hi + lo, tcgen05 kind::f16: meets the
+ * 2e-3 parity bar against the reference's f32-activation arithmetic. BLOCK_SCALED: tcgen05
+ * kind::mxf8f6f4.block_scale on the e2m1 codes and e8m0 scales as they are, activations quantised per 32
+ * elements to e4m3 with a ue8m0 scale -- faster (no warp converts a weight), but the activation
+ * quantisation (3 mantissa bits) puts its error near 1e-2: it does NOT meet the parity bar and is never
+ * selected implicitly. No counterpart in the reference (its grouped expert GEMM is mma.sync,
+ * jit/gpu/kernels/gemm70.go:123-129). */
+typedef enum jl_moe_arm { JL_MOE_ARM_EXACT = 0, JL_MOE_ARM_BLOCK_SCALED = 1 } jl_moe_arm;
 /* out[ntok][hidden] f32 += sum over each row's top_k experts, ascending expert
  * id, of w_e * down_e(act(gate_e h, up_e h)). logits [ntok][n_expert] f32 are
  * the router's raw outputs: softmax, lexicographic top-k (ties to the lowest

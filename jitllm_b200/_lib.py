@@ -58,7 +58,7 @@ class MoeDesc(C.Structure):
                 ("gate", C.c_void_p), ("up", C.c_void_p), ("down", C.c_void_p),
                 ("gate_bytes", C.c_size_t), ("up_bytes", C.c_size_t), ("down_bytes", C.c_size_t),
                 ("gate_bias", C.c_void_p), ("up_bias", C.c_void_p), ("down_bias", C.c_void_p),
-                ("router_bias", C.c_void_p), ("sel_bias", C.c_void_p)]
+                ("router_bias", C.c_void_p), ("sel_bias", C.c_void_p), ("arm", C.c_int32)]
 
 
 class Packed(C.Structure):
@@ -82,6 +82,7 @@ class LayersDesc(C.Structure):
 # Every symbol include/jitllm_b200.h declares: (restype, argtypes).
 _VP, _I, _SZ, _U32 = C.c_void_p, C.c_int, C.c_size_t, C.c_uint32
 TUNE_OFF, TUNE_ON, TUNE_FORCE = 0, 1, 2
+MOE_ARM_EXACT, MOE_ARM_BLOCK_SCALED = 0, 1
 TUNE_TIMER = C.CFUNCTYPE(C.c_double, C.c_void_p, C.c_int, C.c_int)
 
 SYMBOLS = {

@@ -207,6 +207,8 @@ struct moe_gemm_params {
     int npairs;
     int bitdq;                   // every block scale byte is in [104, 128]: the conversion-free dequant applies
     int *status;
+    const uint8_t *sfb;          // block-scaled arm: ue8m0 scales of the activation rows, [npairs][sfb_stride]
+    int sfb_stride;              // a multiple of 4: one 32-bit word per 128-element stage
 };
 
 // Two e2m1 codes of one byte -> two f16 (low nibble first).
@@ -233,6 +235,8 @@ __device__ __forceinline__ float moe_act(int kind, float g, float u) {
     }
     return g / (1.f + expf(-g)) * u;   // SiLU gate
 }
+
+#include "moe_bs.cuh"
 
 template <int NT, int SA, int SB>
 struct moe_smem {
@@ -549,6 +553,28 @@ static int moe_grouped(jl_ctx *ctx, moe_gemm_params p, const __half *xs, int nto
     return p.split ? moe_launch<128, 2, 3>(ctx, xmap, p, s, nattr, at) : moe_launch<64, 2, 4>(ctx, xmap, p, s, nattr, at);
 }
 
+// The block-scaled arm's grouped GEMM over the sorted e4m3 activation rows `xq` ([npairs][k] bytes).
+static int moe_grouped_bs(jl_ctx *ctx, moe_gemm_params p, const uint8_t *xq, int ntok, cudaStream_t s, int nattr,
+                          cudaLaunchAttribute *at) {
+    constexpr int NT = 64, SA = 3, SB = 4;
+    using L = moe_bs_smem<NT, SA, SB>;
+    static_assert(L::TOTAL <= 227 * 1024, "shared memory budget");
+    p.max_tok_tiles = (ntok + NT - 1) / NT;
+    p.split = 0;
+    CUtensorMap xmap;
+    if (!jl_make_tmap_2d(&xmap, xq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)p.k, (uint64_t)p.npairs, (uint64_t)p.k, BS_KB, NT,
+                         CU_TENSOR_MAP_SWIZZLE_128B))
+        return jl_set_err(ctx, JL_DECLINED, "the driver refused a tensor map for the mixture's e4m3 activations");
+    JL_CUDA(ctx, cudaFuncSetAttribute(moe_gemm_bs_kernel<NT, SA, SB>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
+    const int units = p.n_expert * p.row_tiles * p.max_tok_tiles;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(units < ctx->sm_count ? units : ctx->sm_count); cfg.blockDim = dim3(TC5_THREADS);
+    cfg.dynamicSmemBytes = L::TOTAL; cfg.stream = s; cfg.attrs = at; cfg.numAttrs = nattr;
+    JL_CUDA(ctx, cudaLaunchKernelEx(&cfg, moe_gemm_bs_kernel<NT, SA, SB>, xmap, p));
+    ctx->st.launches++;
+    return JL_OK;
+}
+
 // given_ids != NULL: no router and no combine -- row i goes through expert given_ids[i] and
 // out_dev[i] = down(act(gate h_i, up h_i)) is WRITTEN in the caller's row order (the expert-parallel
 // path: rows arrive from other ranks already routed). Otherwise the whole layer, ADDED into out_dev.
@@ -565,7 +591,12 @@ static int moe_dev_locked(jl_ctx *ctx, float *out_dev, const void *h_dev, int h_
     if (wg->n_expert != E || wu->n_expert != E || wd->n_expert != E || wg->nrows != F || wg->k != H || wu->nrows != F ||
         wu->k != H || wd->nrows != H || wd->k != F)
         return jl_set_err(ctx, JL_EINVAL, "expert banks do not match the descriptor's shape");
-    if (wg->emin < 104 || wg->emax > 140 || wu->emin < 104 || wu->emax > 140 || wd->emin < 104 || wd->emax > 140)
+    if (d->arm != JL_MOE_ARM_EXACT && d->arm != JL_MOE_ARM_BLOCK_SCALED)
+        return jl_set_err(ctx, JL_EINVAL, "jl_moe_desc.arm %d is not a known arm", d->arm);
+    if (d->arm == JL_MOE_ARM_BLOCK_SCALED && (H % 32 || F % 32 || H % 16 || F % 16))
+        return jl_set_err(ctx, JL_DECLINED, "the block-scaled arm needs hidden and ffn in whole 32-element blocks");
+    if (d->arm == JL_MOE_ARM_EXACT &&
+        (wg->emin < 104 || wg->emax > 140 || wu->emin < 104 || wu->emax > 140 || wd->emin < 104 || wd->emax > 140))
         return jl_set_err(ctx, JL_DECLINED, "an MXFP4 block scale lies outside 2^-23..2^13, where f16 holds the weights exactly");
     const size_t need = jl_moe_scratch_bytes(ntok, E, K, H, F);
     if (ctx->scratch_cap < need)
@@ -601,6 +632,41 @@ static int moe_dev_locked(jl_ctx *ctx, float *out_dev, const void *h_dev, int h_
         c = cfg_of(dim3(1), dim3(256));
         JL_CUDA(ctx, cudaLaunchKernelEx(&c, moe_sort_kernel, (const int32_t *)sel, np, K, E, cnt, off, perm, pos_of));
         ctx->st.launches++;
+    }
+    if (d->arm == JL_MOE_ARM_BLOCK_SCALED) {
+        // The block-scaled arm: activations to e4m3 + ue8m0 per 32 (twice: the routed rows, then the gated
+        // intermediates), weights and their scales as they are. The e4m3 rows and scale rows live where the exact
+        // arm keeps its f16 rows.
+        const int sfs1 = (H + BS_KB - 1) / BS_KB * 4, sfs2 = (F + BS_KB - 1) / BS_KB * 4;
+        uint8_t *q1 = (uint8_t *)xs, *sf1 = q1 + (size_t)np * H;
+        uint8_t *q2 = (uint8_t *)as, *sf2 = q2 + (size_t)np * F;
+        const int src_rows = given_ids ? ntok : ntok;
+        cudaLaunchConfig_t c = cfg_of(dim3(np), dim3(256));
+        JL_CUDA(ctx, cudaLaunchKernelEx(&c, act_to_mx8_kernel, h_dev, h_dtype, q1, sf1, H, sfs1, (const int *)perm, src_rows));
+        ctx->st.launches++;
+        moe_gemm_params p = {};
+        p.n_expert = E; p.cnt = cnt; p.off = off; p.npairs = np; p.status = ctx->dev_status; p.act = d->act;
+        p.mode = 0; p.rows = F; p.k = H; p.row_tiles = (F + TC5_M - 1) / TC5_M;
+        p.c0 = wg->data; p.c1 = wu->data; p.e0 = wg->scales; p.e1 = wu->scales; p.e_stride = wg->scale_stride;
+        p.b0 = d->gate_bias; p.b1 = d->up_bias; p.outp = act; p.sfb = sf1; p.sfb_stride = sfs1;
+        int rc = moe_grouped_bs(ctx, p, q1, ntok, s, nattr, at);
+        if (rc) return rc;
+        c = cfg_of(dim3(np), dim3(256));
+        JL_CUDA(ctx, cudaLaunchKernelEx(&c, act_to_mx8_kernel, (const void *)act, (int)JL_DT_F32, q2, sf2, F, sfs2, (const int *)nullptr, 0));
+        ctx->st.launches++;
+        p.mode = 1; p.rows = H; p.k = F; p.row_tiles = (H + TC5_ROWS - 1) / TC5_ROWS;
+        p.c0 = wd->data; p.c1 = nullptr; p.e0 = wd->scales; p.e1 = nullptr; p.e_stride = wd->scale_stride;
+        p.b0 = d->down_bias; p.b1 = nullptr; p.outp = y; p.sfb = sf2; p.sfb_stride = sfs2;
+        if (given_ids) { p.outp = out_dev; p.out_rowmap = perm; }
+        if ((rc = moe_grouped_bs(ctx, p, q2, ntok, s, nattr, at))) return rc;
+        if (!given_ids) {
+            c = cfg_of(dim3(ntok), dim3(256));
+            JL_CUDA(ctx, cudaLaunchKernelEx(&c, moe_combine_kernel, out_dev, (const float *)y, (const int32_t *)sel, (const float *)wt,
+                                            (const int *)pos_of, ntok, K, H));
+            ctx->st.launches++;
+        }
+        JL_CUDA(ctx, cudaGetLastError());
+        return JL_OK;
     }
     const int hsplit = h_dtype == JL_DT_F32 ? 1 : 0;
     {

@@ -1,0 +1,347 @@
+// Block-scaled arm of the MXFP4 mixture layer: tcgen05.mma kind::mxf8f6f4.block_scale consumes the e2m1 codes and
+// their e8m0 block scales AS THEY ARE, so no warp converts a weight. The price is on the activation side: they are
+// quantised per 32 elements to e4m3 with a ue8m0 scale (the MX format the instruction takes), which the reference's
+// f32-activation arithmetic does not do: this arm is reported with its own measured error and is selected only by
+// jl_moe_desc.arm = JL_MOE_ARM_BLOCK_SCALED. (The reference has no counterpart: its grouped expert GEMM runs on
+// mma.sync, jit/gpu/kernels/gemm70.go:123-129.)
+//
+// Operand layout in shared memory, K-major, 128-byte swizzle, 128 elements of K per stage:
+//   A (weights)  the instruction reads 4-bit operands as 16 packed values in the low 8 bytes of every 16-byte unit.
+//                The resident code plane keeps a block's 32 codes in 16 bytes, byte j = element j | element j+16 << 4;
+//                the eight unpack warps copy bytes 0..7 and 8..15 of a block into two units. The K ORDER inside a
+//                block is therefore 0, 16, 1, 17, ...: the activation quantiser writes its bytes in the same order
+//                (a dot product does not care in which order both sides list k, and the scale blocks are untouched).
+//   B (activations)  one e4m3 byte per element, by TMA.
+//   scale factors  one 32-bit word per (row or token, stage) = the four block scales of the stage, in the 512-byte
+//                atom [(r % 32) * 16 + (r / 32) * 4] that tcgen05.cp.32x128b.warpx4 spreads over four TMEM columns; the
+//                instruction descriptor's a_sf_id / b_sf_id pick the byte (block) for each K = 32 MMA.
+#pragma once
+#include <cuda_fp8.h>
+
+#include "tc5.cuh"
+
+#define BS_KB 128                       // elements of K per stage: four MX blocks, four K = 32 MMAs
+#define BS_SF_ATOM 512                  // scale-factor atom: 128 rows x 4 blocks
+#define BS_SF_COLS 16                   // TMEM columns of one scale-factor set: A tile 0, A tile 1, B, spare
+
+// Instruction descriptor, kind::mxf8f6f4 block-scaled: A e2m1, B e4m3, scales ue8m0, both K-major, D f32.
+__host__ __device__ constexpr uint32_t bs_idesc(int m, int n, int a_sf, int b_sf) {
+    return ((uint32_t)b_sf << 4) | (5u << 7) | (0u << 10) | ((uint32_t)(n >> 3) << 17) | (1u << 23) | ((uint32_t)(m >> 4) << 24) |
+           ((uint32_t)a_sf << 29);
+}
+// Shared-memory descriptor of a scale-factor atom: 32 rows of 16 bytes, no swizzle, 8-row core matrices 128 bytes apart.
+__device__ __forceinline__ uint64_t bs_sf_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+    d |= (uint64_t)1 << 16;               // leading byte offset: a single 16-byte column, unused
+    d |= (uint64_t)(128 >> 4) << 32;      // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;               // version
+    return d;                             // swizzle field 0: none
+}
+__device__ __forceinline__ void bs_cp_sf(uint32_t taddr, uint64_t sdesc) {
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+__device__ __forceinline__ void bs_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate,
+                                       uint32_t tsfa, uint32_t tsfb) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(tsfa), "r"(tsfb)
+        : "memory");
+}
+
+// Position of element i of a 32-element block in the K order both operands use: 0, 16, 1, 17, ...
+__host__ __device__ constexpr int bs_kpos(int i) { return i < 16 ? 2 * i : 2 * (i - 16) + 1; }
+
+// One CTA per destination row: q[row][k] e4m3 bytes (block-permuted K order), sf[row][sf_stride] ue8m0 bytes. The
+// source row is rowmap[row] when a map is given (entries outside [0, nsrc) read row 0: their destination belongs to
+// no expert's list). The scale is the smallest power of two that brings the block's amax within e4m3's 448.
+static __global__ void __launch_bounds__(256)
+act_to_mx8_kernel(const void *__restrict__ x, int x_dtype, uint8_t *__restrict__ q, uint8_t *__restrict__ sf, int k, int sf_stride,
+                  const int *__restrict__ rowmap, int nsrc) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int row = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int src = row;
+    if (rowmap) {
+        src = rowmap[row];
+        if ((unsigned)src >= (unsigned)nsrc) src = 0;
+    }
+    const size_t base = (size_t)src * k;
+    const int nblk = k / 32;
+    for (int b = warp; b < sf_stride; b += 8) {
+        if (b >= nblk) {                                  // padding of the scale row: 2^0
+            if (lane == 0) sf[(size_t)row * sf_stride + b] = 127;
+            continue;
+        }
+        float v;
+        const size_t i = base + (size_t)b * 32 + lane;
+        if (x_dtype == JL_DT_F32) v = __ldg(static_cast<const float *>(x) + i);
+        else if (x_dtype == JL_DT_BF16) v = __bfloat162float(__ldg(static_cast<const __nv_bfloat16 *>(x) + i));
+        else v = __half2float(__ldg(static_cast<const __half *>(x) + i));
+        float amax = fabsf(v);
+#pragma unroll
+        for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        int se = 0;
+        if (amax > 0.f && amax < __int_as_float(0x7f800000)) {
+            int ex;
+            const float m = frexpf(amax * (1.f / 448.f), &ex);     // amax / 448 = m 2^ex, m in [0.5, 1)
+            se = m == 0.5f ? ex - 1 : ex;
+            se = max(-126, min(127, se));
+        }
+        const float scaled = v * __uint_as_float((uint32_t)(127 - se) << 23);
+        const uint8_t code = (uint8_t)__nv_cvt_float_to_fp8(scaled, __NV_SATFINITE, __NV_E4M3);
+        q[(size_t)row * k + (size_t)b * 32 + bs_kpos(lane)] = code;
+        if (lane == 0) sf[(size_t)row * sf_stride + b] = (uint8_t)(127 + se);
+    }
+}
+
+// ------------------------------------------------------------------------------------------- the grouped GEMM
+// (moe_gemm_params and moe_act come from moe.cu, which includes this file after defining them.)
+
+template <int NT, int SA, int SB>
+struct moe_bs_smem {
+    static constexpr int ACC_COLS = TC5_MS * NT;
+    static constexpr int ACC_BUFS = 2;
+    static constexpr int B_BYTES = NT * BS_KB;                 // e4m3: one byte per element
+    static constexpr int A_OFS = 0;
+    static constexpr int B_OFS = SA * TC5_MS * TC5_A_BYTES;    // an A tile is 128 rows x 128 bytes, as in the f16 arm
+    static constexpr int SFA_OFS = B_OFS + SB * B_BYTES;
+    static constexpr int SFB_OFS = SFA_OFS + SA * TC5_MS * BS_SF_ATOM;
+    static constexpr int BAR_OFS = SFB_OFS + SB * BS_SF_ATOM;
+    static constexpr int NBARS = 2 * SA + 2 * SB + 4;
+    static constexpr int MISC_OFS = BAR_OFS + NBARS * 8;
+    static constexpr int TOTAL = MISC_OFS + 16 + 1024;
+    static constexpr int TMEM_COLS = 512;                      // accumulators (ACC_COLS x 2) + two scale-factor sets
+    static_assert(ACC_COLS * ACC_BUFS + 2 * BS_SF_COLS <= TMEM_COLS, "TMEM budget");
+};
+
+// Roles as in moe_gemm_kernel: warps 0..3 epilogue, 4 producer (activation tiles by TMA + their scale words), 5 MMA
+// issuer (scale factors to TMEM, then four K = 32 MMAs per tile and stage), 6..13 unpack (thread r owns tile row r).
+template <int NT, int SA, int SB>
+__global__ void __launch_bounds__(TC5_THREADS, 1)
+moe_gemm_bs_kernel(const __grid_constant__ CUtensorMap xmap, const moe_gemm_params p) {
+    using L = moe_bs_smem<NT, SA, SB>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const uint32_t sbase = smem_u32(smem);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + L::BAR_OFS);
+    uint64_t *a_full = bars, *a_empty = bars + SA, *b_full = bars + 2 * SA, *b_empty = b_full + SB;
+    uint64_t *acc_full = b_empty + SB, *acc_empty = acc_full + 2;
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + L::MISC_OFS);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L::MISC_OFS + 4);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int nkb = (p.k + BS_KB - 1) / BS_KB;
+    const int nblk = p.k / 32;
+    const int nunits = p.n_expert * p.row_tiles * p.max_tok_tiles;
+
+    if (tid == 0) {
+        for (int s = 0; s < SA; s++) { mbar_init(smem_u32(a_full + s), TC5_DQ_THREADS / 32); mbar_init(smem_u32(a_empty + s), 1); }
+        for (int s = 0; s < SB; s++) { mbar_init(smem_u32(b_full + s), 1); mbar_init(smem_u32(b_empty + s), 1); }
+        for (int i = 0; i < 2; i++) { mbar_init(smem_u32(acc_full + i), 1); mbar_init(smem_u32(acc_empty + i), 4); }
+        abort_flag[0] = 0;
+        abort_flag[1] = p.status[1];
+        mbar_init_fence();
+    }
+    if (warp == 5) tc5_alloc(smem_u32(const_cast<uint32_t *>(tmem_slot)), L::TMEM_COLS);
+    tc5_fence_before();
+    __syncthreads();
+    tc5_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+
+#define BS_UNIT(u)                                                                    \
+    const int tt = (u) / (p.n_expert * p.row_tiles);                                  \
+    const int e = ((u) / p.row_tiles) % p.n_expert, rt = (u) % p.row_tiles;           \
+    const int m_eff = p.cnt[e], col0 = p.off[e] + tt * NT;                            \
+    const bool live = tt * NT < m_eff;                                                \
+    (void)rt; (void)col0; (void)m_eff
+
+    if (warp == 4) {
+        // every lane walks the loop: lane 0 waits and issues the TMA copy, all lanes move the tokens' scale words
+        uint32_t kb_it = 0;
+        bool ok = true;
+        for (int u = blockIdx.x; u < nunits && ok && !*abort_flag; u += gridDim.x) {
+            BS_UNIT(u);
+            if (!live) continue;
+            for (int kb = 0; kb < nkb && ok; kb++, kb_it++) {
+                const uint32_t s = kb_it % SB, ph = (kb_it / SB) & 1;
+                if (kb_it >= (uint32_t)SB) {
+                    int w = 1;
+                    if (lane == 0) w = tc5_wait(smem_u32(b_empty + s), ph ^ 1, abort_flag) ? 1 : 0;
+                    ok = __shfl_sync(0xffffffffu, w, 0) != 0;
+                }
+                if (!ok) break;
+                uint8_t *sfb = smem + L::SFB_OFS + s * BS_SF_ATOM;
+#pragma unroll
+                for (int i = 0; i < NT / 32; i++) {
+                    const int col = lane + 32 * i;
+                    const int pos = min(col0 + col, p.npairs - 1);                       // rows past the list are never stored
+                    const uint32_t w4 = __ldg(reinterpret_cast<const uint32_t *>(p.sfb + (size_t)pos * p.sfb_stride) + kb);
+                    *reinterpret_cast<uint32_t *>(sfb + (col & 31) * 16 + (col >> 5) * 4) = w4;
+                }
+                fence_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive_expect_tx(smem_u32(b_full + s), L::B_BYTES);
+                    tma_load_2d(sbase + L::B_OFS + s * L::B_BYTES, &xmap, kb * BS_KB, col0, smem_u32(b_full + s));
+                }
+            }
+        }
+    } else if (warp == 5) {
+        if (lane == 0) {
+            uint32_t kb_it = 0, unit_it = 0;
+            bool ok = true;
+            const uint32_t tsf0 = tmem_base + L::ACC_COLS * L::ACC_BUFS;
+            for (int u = blockIdx.x; u < nunits && ok && !*abort_flag; u += gridDim.x) {
+                BS_UNIT(u);
+                if (!live) continue;
+                const uint32_t ab = unit_it % L::ACC_BUFS, aph = (unit_it / L::ACC_BUFS) & 1;
+                if (unit_it >= (uint32_t)L::ACC_BUFS) ok = tc5_wait(smem_u32(acc_empty + ab), aph ^ 1, abort_flag);
+                if (!ok) break;
+                tc5_fence_after();
+                const uint32_t d_tmem = tmem_base + ab * L::ACC_COLS;
+                for (int kb = 0; kb < nkb && ok; kb++, kb_it++) {
+                    const uint32_t sa = kb_it % SA, pha = (kb_it / SA) & 1, s = kb_it % SB, ph = (kb_it / SB) & 1;
+                    ok = tc5_wait(smem_u32(a_full + sa), pha, abort_flag) && tc5_wait(smem_u32(b_full + s), ph, abort_flag);
+                    if (!ok) break;
+                    tc5_fence_after();
+                    const uint32_t tsf = tsf0 + (kb_it & 1) * BS_SF_COLS;         // two sets, alternating
+#pragma unroll
+                    for (int ms = 0; ms < TC5_MS; ms++)
+                        bs_cp_sf(tsf + ms * 4, bs_sf_desc(sbase + L::SFA_OFS + (sa * TC5_MS + ms) * BS_SF_ATOM));
+                    bs_cp_sf(tsf + 8, bs_sf_desc(sbase + L::SFB_OFS + s * BS_SF_ATOM));
+                    const uint64_t bdesc = tc5_smem_desc(sbase + L::B_OFS + s * L::B_BYTES);
+                    const int nj = min(BS_KB / 32, nblk - kb * (BS_KB / 32));     // the last stage of a row may be short
+#pragma unroll
+                    for (int ms = 0; ms < TC5_MS; ms++) {
+                        const uint64_t adesc = tc5_smem_desc(sbase + L::A_OFS + (sa * TC5_MS + ms) * TC5_A_BYTES);
+#pragma unroll
+                        for (int j = 0; j < BS_KB / 32; j++)
+                            if (j < nj)
+                                bs_mma(d_tmem + ms * NT, adesc + 2 * j, bdesc + 2 * j, bs_idesc(TC5_M, NT, j, j), (kb | j) != 0,
+                                       tsf + ms * 4, tsf + 8);
+                    }
+                    tc5_commit(smem_u32(a_empty + sa));
+                    tc5_commit(smem_u32(b_empty + s));
+                }
+                if (!ok) break;
+                tc5_commit(smem_u32(acc_full + ab));
+                unit_it++;
+            }
+        }
+    } else if (warp >= 6) {
+        // ---- unpack: thread r owns tile row r. mode 0: rows 0..127 gate, 128..255 up (same row index); mode 1: 256
+        //      consecutive rows of down. Per stage: four blocks of 16 code bytes -> eight 16-byte units (codes in the low
+        //      half), and the four block scales as one word of the scale-factor atom.
+        const int r = tid - 192;
+        const uint32_t swz = (uint32_t)(r & 7);
+        const int a_row_ofs = (r >> 7) * TC5_A_BYTES + (r & 127) * 128;
+        const int sf_ofs = (r >> 7) * BS_SF_ATOM + ((r & 127) & 31) * 16 + ((r & 127) >> 5) * 4;
+        uint32_t kb_it = 0;
+        bool ok = true;
+        for (int u = blockIdx.x; u < nunits && ok && !*abort_flag; u += gridDim.x) {
+            BS_UNIT(u);
+            if (!live) continue;
+            const bool second = p.mode == 0 && r >= 128;
+            const int row = p.mode == 0 ? min(rt * TC5_M + (r & 127), p.rows - 1) : min(rt * TC5_ROWS + r, p.rows - 1);
+            const size_t grow = (size_t)e * p.rows + row;
+            const uint8_t *codes = (second ? p.c1 : p.c0) + grow * nblk * 16;
+            const uint8_t *ebytes = (second ? p.e1 : p.e0) + grow * p.e_stride;
+            auto load_stage = [&](int kb, uint4 (&c)[4], uint32_t &sfw) {
+                sfw = 0x7F7F7F7Fu;
+#pragma unroll
+                for (int b = 0; b < 4; b++) {
+                    const int blk = kb * 4 + b;
+                    c[b] = make_uint4(0, 0, 0, 0);
+                    if (blk < nblk) {
+                        c[b] = ldg_nc16(codes + (size_t)blk * 16);
+                        sfw = (sfw & ~(0xFFu << (8 * b))) | ((uint32_t)ebytes[blk] << (8 * b));
+                    }
+                }
+            };
+            uint4 cur[4], nxt[4];
+            uint32_t sf_cur, sf_nxt = 0;
+            load_stage(0, cur, sf_cur);
+            for (int kb = 0; kb < nkb && ok; kb++, kb_it++) {
+                const uint32_t s = kb_it % SA, ph = (kb_it / SA) & 1;
+                if (kb + 1 < nkb) load_stage(kb + 1, nxt, sf_nxt);
+                if (kb_it >= (uint32_t)SA) ok = tc5_wait(smem_u32(a_empty + s), ph ^ 1, abort_flag);
+                if (!ok) break;
+                uint8_t *arow = smem + L::A_OFS + s * TC5_MS * TC5_A_BYTES + a_row_ofs;
+#pragma unroll
+                for (int b = 0; b < 4; b++) {
+                    *reinterpret_cast<uint4 *>(arow + (((uint32_t)(2 * b) ^ swz) << 4)) = make_uint4(cur[b].x, cur[b].y, 0u, 0u);
+                    *reinterpret_cast<uint4 *>(arow + (((uint32_t)(2 * b + 1) ^ swz) << 4)) = make_uint4(cur[b].z, cur[b].w, 0u, 0u);
+                }
+                *reinterpret_cast<uint32_t *>(smem + L::SFA_OFS + s * TC5_MS * BS_SF_ATOM + sf_ofs) = sf_cur;
+                fence_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(a_full + s));
+#pragma unroll
+                for (int b = 0; b < 4; b++) cur[b] = nxt[b];
+                sf_cur = sf_nxt;
+            }
+        }
+    } else {
+        // ---- epilogue: warp w reads TMEM lanes 32w..32w+31 (tile rows), 32 token columns at a time
+        uint32_t unit_it = 0;
+        for (int u = blockIdx.x; u < nunits && !*abort_flag; u += gridDim.x) {
+            BS_UNIT(u);
+            if (!live) continue;
+            const uint32_t ab = unit_it % L::ACC_BUFS, aph = (unit_it / L::ACC_BUFS) & 1;
+            if (!tc5_wait_relaxed(smem_u32(acc_full + ab), aph, abort_flag)) break;
+            tc5_fence_after();
+            const uint32_t tacc = tmem_base + ab * L::ACC_COLS + ((uint32_t)(warp * 32) << 16);
+            const int pos_end = p.off[e] + p.cnt[e];
+#pragma unroll 1
+            for (int c0 = 0; c0 < NT; c0 += 32) {
+                const int pos0 = col0 + c0;
+                if (p.mode == 0) {
+                    uint32_t vg[32], vu[32];
+                    tc5_ld32(tacc + c0, vg);
+                    tc5_ld32(tacc + NT + c0, vu);
+                    tc5_wait_ld();
+                    const int row = rt * TC5_M + warp * 32 + lane;
+                    const float bg = (p.b0 && row < p.rows) ? p.b0[(size_t)e * p.rows + row] : 0.f;
+                    const float bu = (p.b1 && row < p.rows) ? p.b1[(size_t)e * p.rows + row] : 0.f;
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        const int pos = pos0 + j;
+                        if (row < p.rows && pos < pos_end)
+                            p.outp[(size_t)pos * p.rows + row] = moe_act(p.act, __uint_as_float(vg[j]) + bg, __uint_as_float(vu[j]) + bu);
+                    }
+                } else {
+#pragma unroll 1
+                    for (int ms = 0; ms < TC5_MS; ms++) {
+                        uint32_t v[32];
+                        tc5_ld32(tacc + ms * NT + c0, v);
+                        tc5_wait_ld();
+                        const int row = rt * TC5_ROWS + ms * TC5_M + warp * 32 + lane;
+                        const float bd = (p.b0 && row < p.rows) ? p.b0[(size_t)e * p.rows + row] : 0.f;
+#pragma unroll
+                        for (int j = 0; j < 32; j++) {
+                            const int pos = pos0 + j;
+                            if (row < p.rows && pos < pos_end)
+                                p.outp[(size_t)(p.out_rowmap ? p.out_rowmap[pos] : pos) * p.rows + row] = __uint_as_float(v[j]) + bd;
+                        }
+                    }
+                }
+            }
+            tc5_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(acc_empty + ab));
+            unit_it++;
+        }
+    }
+#undef BS_UNIT
+    tc5_fence_before();
+    __syncthreads();
+    if (tid == 0 && *abort_flag) atomicExch(p.status, 3);
+    if (warp == 5) {
+        tc5_fence_after();
+        tc5_dealloc(tmem_base, L::TMEM_COLS);
+    }
+}

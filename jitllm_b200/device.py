@@ -326,14 +326,16 @@ class Device:
     def MoeHost(self, out, h, logits, gate, up, down, n_expert: int, top_k: int, hidden: int, ffn: int,
                 act: int = _lib.ACT_SILU, norm: bool = True, scale: float = 1.0, t: int = _lib.MXFP4,
                 gate_bias=None, up_bias=None, down_bias=None, router_bias=None, sel_out=None, wt_out=None,
-                sel_bias=None) -> bool:
-        """State.moeBatch with every operand in host memory (numpy). out is ADDED to. False = declined."""
+                sel_bias=None, arm: int = _lib.MOE_ARM_EXACT) -> bool:
+        """State.moeBatch with every operand in host memory (numpy). out is ADDED to. False = declined.
+        arm = MOE_ARM_BLOCK_SCALED runs the expert GEMMs on the block-scaled tensor-core path (activations
+        quantised to e4m3 per 32: faster, outside the parity bar)."""
         ntok = logits.shape[0]
         d = MoeDesc(struct_size=C.sizeof(MoeDesc), type=t, n_expert=n_expert, top_k=top_k, hidden=hidden, ffn=ffn,
                     act=act, norm=int(norm), scale=scale, gate=_ptr(gate), up=_ptr(up), down=_ptr(down),
                     gate_bytes=_nbytes(gate), up_bytes=_nbytes(up), down_bytes=_nbytes(down),
                     gate_bias=_ptr(gate_bias), up_bias=_ptr(up_bias), down_bias=_ptr(down_bias),
-                    router_bias=_ptr(router_bias), sel_bias=_ptr(sel_bias))
+                    router_bias=_ptr(router_bias), sel_bias=_ptr(sel_bias), arm=arm)
         return self.Moe(out, h, logits, ntok, d, sel_out, wt_out)
 
     def MoeRouteDev(self, logits, ntok: int, desc: MoeDesc, sel_out, wt_out, stream: int = 0) -> None:

@@ -36,7 +36,7 @@ def test_struct_sizes_match_the_header_layout():
     assert C.sizeof(_lib.Opts) == 56
     assert C.sizeof(_lib.Choice) == 44
     assert C.sizeof(_lib.Stats) == 72
-    assert C.sizeof(_lib.MoeDesc) == 128
+    assert C.sizeof(_lib.MoeDesc) == 136
 
 
 @pytest.mark.skipif(os.path.exists("/dev/nvidiactl"), reason="a GPU is present")

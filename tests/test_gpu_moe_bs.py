@@ -1,0 +1,86 @@
+"""The block-scaled arm of the MXFP4 mixture layer (tcgen05 kind::mxf8f6f4.block_scale: e2m1 codes and e8m0 scales
+as they are, activations quantised per 32 elements to e4m3 + ue8m0) on a B200 through the C ABI.
+
+Two references. (1) A float64 restatement of what the arm claims to compute -- the same router, the activations of
+both expert GEMMs quantised exactly as the kernel's quantiser does, exact weights: the kernel must match it closely
+(3e-3; the difference is f32 accumulation order and an occasional e4m3 rounding of an intermediate that the order
+flips). (2) The exact oracle of State.moeBatch: the arm's error against it is REPORTED (largest element by the parity
+metric, and rms) and only bounded loosely: it does not meet the 2e-3 parity bar, by construction -- e4m3 keeps 3
+mantissa bits of every activation, twice (the routed rows and the gated intermediates)."""
+import numpy as np
+import pytest
+
+from conftest import nmse, parity_err
+from jitllm_b200 import ACT_SILU, ACT_SWIGLU_OAI, MXFP4, Device, _lib, synth
+
+pytestmark = pytest.mark.gpu
+
+
+def _mx8(x):
+    """x [n][k] f32 -> the values the quantiser's e4m3 codes and ue8m0 scales stand for (float64)."""
+    import torch
+    n, k = x.shape
+    xb = x.astype(np.float32).reshape(n, k // 32, 32)
+    amax = np.abs(xb).max(-1)
+    m, ex = np.frexp((amax * np.float32(1.0 / 448.0)).astype(np.float32))
+    se = np.where(m == 0.5, ex - 1, ex)
+    se = np.where(amax > 0, np.clip(se, -126, 127), 0).astype(np.int32)
+    scaled = xb * np.exp2(-se.astype(np.float32))[..., None]
+    q = torch.from_numpy(np.ascontiguousarray(scaled)).to(torch.float8_e4m3fn).to(torch.float32).numpy()
+    return (q.astype(np.float64) * np.exp2(se.astype(np.float64))[..., None]).reshape(n, k)
+
+
+def _restatement(orc, h, gate, up, down, sel, wt, E, hidden, ffn, act):
+    ntok, topk = sel.shape
+    W = lambda b, r, k: orc.dequant64(MXFP4, b, E * r * k).reshape(E, r, k)
+    Wg, Wu, Wd = W(gate, ffn, hidden), W(up, ffn, hidden), W(down, hidden, ffn)
+    hq = _mx8(h)
+    out = np.zeros((ntok, hidden), np.float64)
+    for i in range(ntok):
+        for e, w in sorted(zip(sel[i], wt[i])):                       # ascending expert id
+            g, u = Wg[e] @ hq[i], Wu[e] @ hq[i]
+            if act == ACT_SWIGLU_OAI:
+                x, y = np.minimum(g, 7.0), np.clip(u, -7.0, 7.0)
+                a = x / (1 + np.exp(-1.702 * x)) * (y + 1)
+            else:
+                a = g / (1 + np.exp(-g)) * u
+            aq = _mx8(a.astype(np.float32)[None, :])[0]
+            out[i] += np.float64(w) * (Wd[e] @ aq)
+    return out
+
+
+@pytest.mark.parametrize("E,topk,hidden,ffn,ntok,act", [(4, 2, 256, 320, 40, ACT_SILU), (8, 4, 128, 128, 7, ACT_SILU),
+                                                         (8, 2, 576, 704, 150, ACT_SWIGLU_OAI), (2, 1, 128, 192, 65, ACT_SILU)])
+@pytest.mark.parametrize("h_bf16", [True, False])
+def test_block_scaled_arm_matches_its_restatement_and_reports_its_error(dev, orc, E, topk, hidden, ffn, ntok, act, h_bf16):
+    from test_gpu_moe import _layer, _oracle
+    rng = synth.rng_for(0xB5 + E + hidden + ntok)
+    gate, up, down = _layer(rng, E, hidden, ffn)
+    h = synth.activations(rng, ntok, hidden) * np.float32(0.25)
+    logits = synth.activations(rng, ntok, E)
+    if h_bf16:
+        hin = synth.to_bf16_bits(h)
+        h = synth.bf16_bits_to_f32(hin)
+    else:
+        hin = h
+    out = np.zeros((ntok, hidden), np.float32)
+    sel = np.full((ntok, topk), -7, np.int32)
+    wt = np.full((ntok, topk), np.nan, np.float32)
+    assert dev.MoeHost(out, hin, logits, gate, up, down, E, topk, hidden, ffn, act=act, sel_out=sel, wt_out=wt,
+                       arm=_lib.MOE_ARM_BLOCK_SCALED), dev.Err()
+    exact, rsel, rwt = _oracle(orc, h, logits, gate, up, down, E, topk, hidden, ffn, act=act)
+    assert np.array_equal(sel, rsel) and np.allclose(wt, rwt, rtol=2e-6, atol=0)     # the router is the same
+    assert np.isfinite(out).all()
+    want = _restatement(orc, h, gate, up, down, sel, wt, E, hidden, ffn, act)
+    err_claim, err_exact = parity_err(out, want), parity_err(out, exact)
+    rms_exact = float(np.sqrt(nmse(out, exact)))
+    print(f"block-scaled arm E={E} hidden={hidden} ffn={ffn} ntok={ntok}: vs its restatement {err_claim:.2e}; "
+          f"vs the exact oracle: largest {err_exact:.2e}, rms {rms_exact:.2e} of the output's rms")
+    assert err_claim <= 3e-3, (err_claim, err_exact)
+    assert rms_exact <= 8e-2, rms_exact                              # e4m3 keeps 3 mantissa bits: a few per cent
+    # the exact arm on the same inputs still meets the parity bar (the arm field selects, nothing leaks)
+    out2 = np.zeros((ntok, hidden), np.float32)
+    assert dev.MoeHost(out2, hin, logits, gate, up, down, E, topk, hidden, ffn, act=act), dev.Err()
+    assert parity_err(out2, exact) <= 2e-3
+    for w in (gate, up, down):
+        dev.Forget(w)
