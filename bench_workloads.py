@@ -353,6 +353,27 @@ def run_moe(args, emit=True):
     per_replay = dev.Stats().launches - n0
     ms, clocks = _timed_replays(torch, g, args.steps, args.warmup, local)
     us = ms * 1e3 / (args.steps * MOE["layers"])
+    # the block-scaled arm on the same layers and inputs: its time, and its error against the exact arm's output
+    from jitllm_b200._lib import MOE_ARM_BLOCK_SCALED
+    bs_descs = []
+    for d in descs:
+        b = MoeDesc.from_buffer_copy(d)
+        b.arm = MOE_ARM_BLOCK_SCALED
+        bs_descs.append(b)
+    st0 = torch.cuda.current_stream().cuda_stream
+    o_exact, o_bs = torch.zeros_like(out), torch.zeros_like(out)
+    dev.MoeDev(o_exact, h, logits, ntok, descs[0], None, None, st0)
+    dev.MoeDev(o_bs, h, logits, ntok, bs_descs[0], None, None, st0)
+    torch.cuda.synchronize()
+    diff = (o_bs - o_exact).double()
+    bs_rms = float(diff.pow(2).sum().sqrt() / o_exact.double().pow(2).sum().sqrt())
+    bs_max = float((diff.abs() / torch.maximum(o_exact.double().abs(), o_exact.double().pow(2).mean().sqrt())).max())
+    g2, cap2 = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+    with torch.cuda.graph(g2, stream=cap2):
+        for d in bs_descs:
+            dev.MoeDev(out, h, logits, ntok, d, None, None, torch.cuda.current_stream().cuda_stream)
+    ms_bs, clocks_bs = _timed_replays(torch, g2, args.steps, args.warmup, local)
+    us_bs = ms_bs * 1e3 / (args.steps * MOE["layers"])
     wbytes = E * 3 * hidden * (ffn // 32) * 17
     abytes = wbytes + ntok * hidden * 2 + ntok * E * 4 + ntok * hidden * 4
     fl = ntok * topk * 3 * 2.0 * hidden * ffn
@@ -379,6 +400,12 @@ def run_moe(args, emit=True):
         "roofline": {"bound": "hbm", "achieved": abytes / us / 1e3, "peak": hbm, "unit": "GB/s", "frac": abytes / us / 1e3 / hbm,
                      "of": which, "kernel": "moe_gemm_kernel (gate|up, down)", "traffic": None,
                      "algorithmic_bytes_per_layer": abytes},
+        "block_scaled_arm": {"us_per_layer": us_bs, "layers_per_s": 1e6 / us_bs, "hbm_gbs": abytes / us_bs / 1e3,
+                             "hbm_frac": abytes / us_bs / 1e3 / hbm, "useful_tflops": fl / us_bs / 1e6,
+                             "kernel": "moe_gemm_bs_kernel (tcgen05 kind::mxf8f6f4.block_scale; activations e4m3 + ue8m0 per 32)",
+                             "error_vs_exact_arm": {"rms_rel": bs_rms, "largest_rel": bs_max,
+                                                    "note": "outside the 2e-3 parity bar by construction; selected only by jl_moe_desc.arm"},
+                             "clocks": clocks_bs},
         "e2e": {"value": e2e_layers, "unit": "layers/s", "h2d_bytes_per_step": ntok * hidden * 2 + ntok * E * 4,
                 "d2h_bytes_per_step": ntok * hidden * 4, "note": "jl_moe host-pointer call, wall clock"},
         "gpu_launches": int(per_replay * args.steps), "clocks": clocks})

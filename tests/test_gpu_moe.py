@@ -71,6 +71,8 @@ def test_router_ties_go_to_the_lowest_id_and_out_is_added_to(dev, orc):
     out2 = base.copy()
     assert dev.MoeHost(out2, h, logits, gate, up, down, E, topk, hidden, ffn)
     assert np.array_equal(out.view(np.uint32), out2.view(np.uint32)), "fixed combine order: same bits twice"
+    for w in (gate, up, down):
+        dev.Forget(w)
 
 
 def test_swiglu_oai_with_biases(dev, orc):
@@ -85,6 +87,8 @@ def test_swiglu_oai_with_biases(dev, orc):
     assert dev.MoeHost(out, h, logits, gate, up, down, E, topk, hidden, ffn, act=ACT_SWIGLU_OAI, **b), dev.Err()
     ref, _, _ = _oracle(orc, h, logits, gate, up, down, E, topk, hidden, ffn, act=1, **b)
     assert parity_err(out, ref) <= BAR
+    for w in (gate, up, down):       # residency is keyed on the host address: forget before the arrays are freed
+        dev.Forget(w)
 
 
 def test_config3_gpt_oss_shape(dev, orc):
@@ -101,6 +105,8 @@ def test_config3_gpt_oss_shape(dev, orc):
     ref, rsel, _ = _oracle(orc, h, logits, gate, up, down, E, topk, hidden, ffn)
     assert np.array_equal(sel, rsel)
     assert parity_err(out, ref) <= BAR, (parity_err(out, ref), nmse(out, ref))
+    for w in (gate, up, down):
+        dev.Forget(w)
 
 
 def test_declines(dev):
