@@ -403,6 +403,7 @@ def run_moe(args, emit=True):
         "block_scaled_arm": {"us_per_layer": us_bs, "layers_per_s": 1e6 / us_bs, "hbm_gbs": abytes / us_bs / 1e3,
                              "hbm_frac": abytes / us_bs / 1e3 / hbm, "useful_tflops": fl / us_bs / 1e6,
                              "kernel": "moe_gemm_bs_kernel (tcgen05 kind::mxf8f6f4.block_scale; activations e4m3 + ue8m0 per 32)",
+                             "weights_by_tma": bool(dev.lib.jl_moe_bs_weights_by_tma(dev.ctx)),
                              "error_vs_exact_arm": {"rms_rel": bs_rms, "largest_rel": bs_max,
                                                     "note": "outside the 2e-3 parity bar by construction; selected only by jl_moe_desc.arm"},
                              "clocks": clocks_bs},

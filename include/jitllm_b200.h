@@ -232,6 +232,9 @@ typedef struct jl_moe_desc {
  * selected implicitly. No counterpart in the reference (its grouped expert GEMM is mma.sync,
  * jit/gpu/kernels/gemm70.go:123-129). */
 typedef enum jl_moe_arm { JL_MOE_ARM_EXACT = 0, JL_MOE_ARM_BLOCK_SCALED = 1 } jl_moe_arm;
+/* 1 when the last block-scaled launch of this context took its weight tiles by TMA (packed 4-bit tensor maps),
+ * 0 when the driver refused those maps and the codes went through registers. */
+int jl_moe_bs_weights_by_tma(jl_ctx *ctx);
 /* out[ntok][hidden] f32 += sum over each row's top_k experts, ascending expert
  * id, of w_e * down_e(act(gate_e h, up_e h)). logits [ntok][n_expert] f32 are
  * the router's raw outputs: softmax, lexicographic top-k (ties to the lowest

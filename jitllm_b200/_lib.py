@@ -104,6 +104,7 @@ SYMBOLS = {
     "jl_moe_route_dev": (_I, [_VP, _VP, _I, C.POINTER(MoeDesc), _VP, _VP, _VP]),
     "jl_moe_experts_dev": (_I, [_VP, _VP, _VP, _I, _VP, _I, C.POINTER(MoeDesc), _VP]),
     "jl_moe_reserve": (_I, [_VP, _I, _I, _I, _I, _I]),
+    "jl_moe_bs_weights_by_tma": (_I, [_VP]),
     "jl_select": (_I, [_VP, _U32, _I, _I, _I, C.POINTER(Choice)]),
     "jl_tune_configure": (_I, [_VP, _I, C.c_char_p]),
     "jl_tune": (_I, [_VP, _VP, _I, C.POINTER(Choice)]),

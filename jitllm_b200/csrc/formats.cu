@@ -184,7 +184,10 @@ int jl_repack_upload(jl_ctx *ctx, uint32_t type, const void *w_host, size_t w_by
             w->data_bytes = nblk * 16;
             w->scale_stride = ((k / 32) + 15) / 16 * 16;
             w->scales_bytes = rows * (size_t)w->scale_stride;
-            if ((e = cudaMalloc(&w->data, w->data_bytes + 16)) != cudaSuccess) { cudaFree(raw); goto oom; }
+            // slack behind the code plane: the block-scaled mixture arm's last TMA box of the last row reads up to 64
+            // bytes past the end (zero codes)
+            if ((e = cudaMalloc(&w->data, w->data_bytes + 128)) != cudaSuccess) { cudaFree(raw); goto oom; }
+            if ((e = cudaMemsetAsync(w->data + w->data_bytes, 0, 128, ctx->stream)) != cudaSuccess) { cudaFree(raw); goto fail; }
             if ((e = cudaMalloc(&w->scales, w->scales_bytes + 16)) != cudaSuccess) { cudaFree(raw); goto oom; }
             if ((e = cudaMemsetAsync(w->scales, 0, w->scales_bytes, ctx->stream)) != cudaSuccess) { cudaFree(raw); goto fail; }
             repack_mxfp4_kernel<<<grid, 256, 0, ctx->stream>>>(raw, w->data, w->scales, rows, k, w->scale_stride);

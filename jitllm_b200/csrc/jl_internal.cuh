@@ -120,6 +120,7 @@ struct jl_ctx {
     std::map<uint64_t, int> tuned;      // (type, rows, k, tokens) -> decode variant
     int force_variant;                  // >= 0 while a trial times that variant
     int64_t tune_trials, tune_measured, tune_cached, tune_refused;
+    int moe_bs_tma;                     // the last block-scaled mixture launch took its weights by TMA (1) or through registers (0)
 };
 
 static inline uint64_t jl_tune_shape_key(uint32_t type, int nrows, int k, int ntok) {

@@ -556,7 +556,7 @@ static int moe_grouped(jl_ctx *ctx, moe_gemm_params p, const __half *xs, int nto
 // The block-scaled arm's grouped GEMM over the sorted e4m3 activation rows `xq` ([npairs][k] bytes).
 static int moe_grouped_bs(jl_ctx *ctx, moe_gemm_params p, const uint8_t *xq, int ntok, cudaStream_t s, int nattr,
                           cudaLaunchAttribute *at) {
-    constexpr int NT = 64, SA = 3, SB = 4;
+    constexpr int NT = 64, SA = 4, SB = 4;
     using L = moe_bs_smem<NT, SA, SB>;
     static_assert(L::TOTAL <= 227 * 1024, "shared memory budget");
     p.max_tok_tiles = (ntok + NT - 1) / NT;
@@ -565,13 +565,31 @@ static int moe_grouped_bs(jl_ctx *ctx, moe_gemm_params p, const uint8_t *xq, int
     if (!jl_make_tmap_2d(&xmap, xq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)p.k, (uint64_t)p.npairs, (uint64_t)p.k, BS_KB, NT,
                          CU_TENSOR_MAP_SWIZZLE_128B))
         return jl_set_err(ctx, JL_DECLINED, "the driver refused a tensor map for the mixture's e4m3 activations");
-    JL_CUDA(ctx, cudaFuncSetAttribute(moe_gemm_bs_kernel<NT, SA, SB>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
+    // The weight planes as packed 4-bit tensors: 16 codes per 8 bytes in HBM, 16 bytes (8 of them a gap) in shared
+    // memory. The inner extent has to be a multiple of 128 codes: a row of k codes is declared ceil(k / 128) * 128
+    // long at its true pitch, so a row's last box runs into the first bytes of the next row (or the slack behind
+    // the plane): codes the activation side multiplies by its own zero fill, in stages whose MMAs are not issued.
+    const uint64_t kpad = (uint64_t)((p.k + BS_KB - 1) / BS_KB) * BS_KB, nrows_all = (uint64_t)p.n_expert * p.rows;
+    CUtensorMap amap0, amap1;
+    bool tma_a = p.k % 64 == 0 &&
+                 jl_make_tmap_2d(&amap0, p.c0, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 1, kpad, nrows_all, (uint64_t)p.k / 2, BS_KB, TC5_M,
+                                 CU_TENSOR_MAP_SWIZZLE_128B);
+    if (tma_a) tma_a = jl_make_tmap_2d(&amap1, p.c1 ? p.c1 : p.c0, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 1, kpad, nrows_all,
+                                       (uint64_t)p.k / 2, BS_KB, TC5_M, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (!tma_a) amap0 = amap1 = xmap;
     const int units = p.n_expert * p.row_tiles * p.max_tok_tiles;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(units < ctx->sm_count ? units : ctx->sm_count); cfg.blockDim = dim3(TC5_THREADS);
     cfg.dynamicSmemBytes = L::TOTAL; cfg.stream = s; cfg.attrs = at; cfg.numAttrs = nattr;
-    JL_CUDA(ctx, cudaLaunchKernelEx(&cfg, moe_gemm_bs_kernel<NT, SA, SB>, xmap, p));
+    if (tma_a) {
+        JL_CUDA(ctx, cudaFuncSetAttribute(moe_gemm_bs_kernel<NT, SA, SB, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
+        JL_CUDA(ctx, cudaLaunchKernelEx(&cfg, moe_gemm_bs_kernel<NT, SA, SB, true>, xmap, amap0, amap1, p));
+    } else {
+        JL_CUDA(ctx, cudaFuncSetAttribute(moe_gemm_bs_kernel<NT, SA, SB, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
+        JL_CUDA(ctx, cudaLaunchKernelEx(&cfg, moe_gemm_bs_kernel<NT, SA, SB, false>, xmap, amap0, amap1, p));
+    }
     ctx->st.launches++;
+    ctx->moe_bs_tma = tma_a ? 1 : 0;
     return JL_OK;
 }
 
@@ -726,6 +744,8 @@ static int moe_grow_stage(jl_ctx *ctx, size_t need) {
     ctx->moe_stage_cap = need;
     return JL_OK;
 }
+
+JL_EXPORT int jl_moe_bs_weights_by_tma(jl_ctx *ctx) { return ctx ? ctx->moe_bs_tma : 0; }
 
 JL_EXPORT int jl_moe_reserve(jl_ctx *ctx, int ntok, int n_expert, int top_k, int hidden, int ffn) {
     if (!ctx || ntok < 1 || n_expert < 1 || top_k < 1 || hidden < 1 || ffn < 1) return JL_EINVAL;

@@ -22,7 +22,8 @@
 
 #define BS_KB 128                       // elements of K per stage: four MX blocks, four K = 32 MMAs
 #define BS_SF_ATOM 512                  // scale-factor atom: 128 rows x 4 blocks
-#define BS_SF_COLS 16                   // TMEM columns of one scale-factor set: A tile 0, A tile 1, B, spare
+#define BS_SF_COLS 16
+#define BS_PF 4                         // stages of raw codes an unpack thread keeps in flight                   // TMEM columns of one scale-factor set: A tile 0, A tile 1, B, spare
 
 // Instruction descriptor, kind::mxf8f6f4 block-scaled: A e2m1, B e4m3, scales ue8m0, both K-major, D f32.
 __host__ __device__ constexpr uint32_t bs_idesc(int m, int n, int a_sf, int b_sf) {
@@ -119,9 +120,13 @@ struct moe_bs_smem {
 
 // Roles as in moe_gemm_kernel: warps 0..3 epilogue, 4 producer (activation tiles by TMA + their scale words), 5 MMA
 // issuer (scale factors to TMEM, then four K = 32 MMAs per tile and stage), 6..13 unpack (thread r owns tile row r).
-template <int NT, int SA, int SB>
+// TMAA: the weight tiles come by TMA as well (tensor maps of packed 4-bit type whose copies leave the 8-byte gaps the
+// instruction wants: nothing touches a code between HBM and the tensor core), and the eight warps only move the
+// scale words. Without it (the driver refused the maps) they also copy the codes through registers.
+template <int NT, int SA, int SB, bool TMAA>
 __global__ void __launch_bounds__(TC5_THREADS, 1)
-moe_gemm_bs_kernel(const __grid_constant__ CUtensorMap xmap, const moe_gemm_params p) {
+moe_gemm_bs_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap amap0,
+                   const __grid_constant__ CUtensorMap amap1, const moe_gemm_params p) {
     using L = moe_bs_smem<NT, SA, SB>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -137,7 +142,7 @@ moe_gemm_bs_kernel(const __grid_constant__ CUtensorMap xmap, const moe_gemm_para
     const int nunits = p.n_expert * p.row_tiles * p.max_tok_tiles;
 
     if (tid == 0) {
-        for (int s = 0; s < SA; s++) { mbar_init(smem_u32(a_full + s), TC5_DQ_THREADS / 32); mbar_init(smem_u32(a_empty + s), 1); }
+        for (int s = 0; s < SA; s++) { mbar_init(smem_u32(a_full + s), TC5_DQ_THREADS / 32 + (TMAA ? 1 : 0)); mbar_init(smem_u32(a_empty + s), 1); }
         for (int s = 0; s < SB; s++) { mbar_init(smem_u32(b_full + s), 1); mbar_init(smem_u32(b_empty + s), 1); }
         for (int i = 0; i < 2; i++) { mbar_init(smem_u32(acc_full + i), 1); mbar_init(smem_u32(acc_empty + i), 4); }
         abort_flag[0] = 0;
@@ -187,6 +192,25 @@ moe_gemm_bs_kernel(const __grid_constant__ CUtensorMap xmap, const moe_gemm_para
                 if (lane == 0) {
                     mbar_arrive_expect_tx(smem_u32(b_full + s), L::B_BYTES);
                     tma_load_2d(sbase + L::B_OFS + s * L::B_BYTES, &xmap, kb * BS_KB, col0, smem_u32(b_full + s));
+                }
+                if (TMAA) {
+                    const uint32_t sa = kb_it % SA, pha = (kb_it / SA) & 1;
+                    if (kb_it >= (uint32_t)SA) {
+                        int w = 1;
+                        if (lane == 0) w = tc5_wait(smem_u32(a_empty + sa), pha ^ 1, abort_flag) ? 1 : 0;
+                        ok = __shfl_sync(0xffffffffu, w, 0) != 0;
+                    }
+                    if (!ok) break;
+                    if (lane == 0) {
+                        // two boxes of 128 rows x 128 codes; in shared memory a code row takes 128 bytes (16 codes in the
+                        // low half of every 16-byte unit), but the barrier counts the 64 bytes per row that are copied
+                        const int y0 = e * p.rows + (p.mode == 0 ? rt * TC5_M : rt * TC5_ROWS);
+                        const uint32_t dst = sbase + L::A_OFS + sa * TC5_MS * TC5_A_BYTES;
+                        mbar_arrive_expect_tx(smem_u32(a_full + sa), TC5_MS * TC5_A_BYTES / 2);
+                        tma_load_2d(dst, &amap0, kb * BS_KB, y0, smem_u32(a_full + sa));
+                        tma_load_2d(dst + TC5_A_BYTES, p.mode == 0 ? &amap1 : &amap0, kb * BS_KB, p.mode == 0 ? y0 : y0 + TC5_M,
+                                    smem_u32(a_full + sa));
+                    }
                 }
             }
         }
@@ -257,32 +281,49 @@ moe_gemm_bs_kernel(const __grid_constant__ CUtensorMap xmap, const moe_gemm_para
                     const int blk = kb * 4 + b;
                     c[b] = make_uint4(0, 0, 0, 0);
                     if (blk < nblk) {
-                        c[b] = ldg_nc16(codes + (size_t)blk * 16);
+                        if (!TMAA) c[b] = ldg_nc16(codes + (size_t)blk * 16);
                         sfw = (sfw & ~(0xFFu << (8 * b))) | ((uint32_t)ebytes[blk] << (8 * b));
                     }
                 }
             };
-            uint4 cur[4], nxt[4];
-            uint32_t sf_cur, sf_nxt = 0;
-            load_stage(0, cur, sf_cur);
-            for (int kb = 0; kb < nkb && ok; kb++, kb_it++) {
-                const uint32_t s = kb_it % SA, ph = (kb_it / SA) & 1;
-                if (kb + 1 < nkb) load_stage(kb + 1, nxt, sf_nxt);
-                if (kb_it >= (uint32_t)SA) ok = tc5_wait(smem_u32(a_empty + s), ph ^ 1, abort_flag);
-                if (!ok) break;
-                uint8_t *arow = smem + L::A_OFS + s * TC5_MS * TC5_A_BYTES + a_row_ofs;
+            // raw codes run BS_PF stages (64 bytes of the row each) ahead of their use, in registers: slot j is refilled
+            // with stage kb + BS_PF the moment stage kb has been copied out of it
+            uint4 q[BS_PF][4];
+            uint32_t sfw[BS_PF];
 #pragma unroll
-                for (int b = 0; b < 4; b++) {
-                    *reinterpret_cast<uint4 *>(arow + (((uint32_t)(2 * b) ^ swz) << 4)) = make_uint4(cur[b].x, cur[b].y, 0u, 0u);
-                    *reinterpret_cast<uint4 *>(arow + (((uint32_t)(2 * b + 1) ^ swz) << 4)) = make_uint4(cur[b].z, cur[b].w, 0u, 0u);
+            for (int j = 0; j < BS_PF; j++) {
+                sfw[j] = 0x7F7F7F7Fu;
+#pragma unroll
+                for (int b = 0; b < 4; b++) q[j][b] = make_uint4(0, 0, 0, 0);
+                if (j < nkb) load_stage(j, q[j], sfw[j]);
+            }
+            for (int kb0 = 0; kb0 < nkb && ok; kb0 += BS_PF) {
+#pragma unroll
+                for (int j = 0; j < BS_PF; j++) {
+                    const int kb = kb0 + j;
+                    if (kb >= nkb) break;
+                    const uint32_t s = kb_it % SA, ph = (kb_it / SA) & 1;
+                    uint4 c[4];
+#pragma unroll
+                    for (int b = 0; b < 4; b++) c[b] = q[j][b];
+                    const uint32_t sf_cur = sfw[j];
+                    if (kb + BS_PF < nkb) load_stage(kb + BS_PF, q[j], sfw[j]);
+                    if (kb_it >= (uint32_t)SA) ok = tc5_wait(smem_u32(a_empty + s), ph ^ 1, abort_flag);
+                    if (!ok) break;
+                    if (!TMAA) {
+                        uint8_t *arow = smem + L::A_OFS + s * TC5_MS * TC5_A_BYTES + a_row_ofs;
+#pragma unroll
+                        for (int b = 0; b < 4; b++) {
+                            *reinterpret_cast<uint4 *>(arow + (((uint32_t)(2 * b) ^ swz) << 4)) = make_uint4(c[b].x, c[b].y, 0u, 0u);
+                            *reinterpret_cast<uint4 *>(arow + (((uint32_t)(2 * b + 1) ^ swz) << 4)) = make_uint4(c[b].z, c[b].w, 0u, 0u);
+                        }
+                    }
+                    *reinterpret_cast<uint32_t *>(smem + L::SFA_OFS + s * TC5_MS * BS_SF_ATOM + sf_ofs) = sf_cur;
+                    fence_async_smem();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(a_full + s));
+                    kb_it++;
                 }
-                *reinterpret_cast<uint32_t *>(smem + L::SFA_OFS + s * TC5_MS * BS_SF_ATOM + sf_ofs) = sf_cur;
-                fence_async_smem();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(a_full + s));
-#pragma unroll
-                for (int b = 0; b < 4; b++) cur[b] = nxt[b];
-                sf_cur = sf_nxt;
             }
         }
     } else {

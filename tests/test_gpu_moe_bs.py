@@ -74,6 +74,7 @@ def test_block_scaled_arm_matches_its_restatement_and_reports_its_error(dev, orc
     want = _restatement(orc, h, gate, up, down, sel, wt, E, hidden, ffn, act)
     err_claim, err_exact = parity_err(out, want), parity_err(out, exact)
     rms_exact = float(np.sqrt(nmse(out, exact)))
+    print("weights by TMA:", dev.lib.jl_moe_bs_weights_by_tma(dev.ctx))
     print(f"block-scaled arm E={E} hidden={hidden} ffn={ffn} ntok={ntok}: vs its restatement {err_claim:.2e}; "
           f"vs the exact oracle: largest {err_exact:.2e}, rms {rms_exact:.2e} of the output's rms")
     assert err_claim <= 3e-3, (err_claim, err_exact)
