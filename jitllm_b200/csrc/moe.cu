@@ -556,7 +556,7 @@ static int moe_grouped(jl_ctx *ctx, moe_gemm_params p, const __half *xs, int nto
 // The block-scaled arm's grouped GEMM over the sorted e4m3 activation rows `xq` ([npairs][k] bytes).
 static int moe_grouped_bs(jl_ctx *ctx, moe_gemm_params p, const uint8_t *xq, int ntok, cudaStream_t s, int nattr,
                           cudaLaunchAttribute *at) {
-    constexpr int NT = 64, SA = 4, SB = 4;
+    constexpr int NT = 64, SA = BS_SA, SB = BS_SB;
     using L = moe_bs_smem<NT, SA, SB>;
     static_assert(L::TOTAL <= 227 * 1024, "shared memory budget");
     p.max_tok_tiles = (ntok + NT - 1) / NT;
@@ -611,8 +611,8 @@ static int moe_dev_locked(jl_ctx *ctx, float *out_dev, const void *h_dev, int h_
         return jl_set_err(ctx, JL_EINVAL, "expert banks do not match the descriptor's shape");
     if (d->arm != JL_MOE_ARM_EXACT && d->arm != JL_MOE_ARM_BLOCK_SCALED)
         return jl_set_err(ctx, JL_EINVAL, "jl_moe_desc.arm %d is not a known arm", d->arm);
-    if (d->arm == JL_MOE_ARM_BLOCK_SCALED && (H % 32 || F % 32 || H % 16 || F % 16))
-        return jl_set_err(ctx, JL_DECLINED, "the block-scaled arm needs hidden and ffn in whole 32-element blocks");
+    if (d->arm == JL_MOE_ARM_BLOCK_SCALED && (H > BS_MAX_KB * BS_KB || F > BS_MAX_KB * BS_KB))
+        return jl_set_err(ctx, JL_DECLINED, "the block-scaled arm serves hidden and ffn up to %d", BS_MAX_KB * BS_KB);
     if (d->arm == JL_MOE_ARM_EXACT &&
         (wg->emin < 104 || wg->emax > 140 || wu->emin < 104 || wu->emax > 140 || wd->emin < 104 || wd->emax > 140))
         return jl_set_err(ctx, JL_DECLINED, "an MXFP4 block scale lies outside 2^-23..2^13, where f16 holds the weights exactly");

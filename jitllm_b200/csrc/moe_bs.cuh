@@ -23,6 +23,19 @@
 #define BS_KB 128                       // elements of K per stage: four MX blocks, four K = 32 MMAs
 #define BS_SF_ATOM 512                  // scale-factor atom: 128 rows x 4 blocks
 #define BS_SF_COLS 16
+#define BS_MAX_KB 64                    // stages of one row at most (k <= 8192)
+#ifndef BS_EXP_MOVERS
+#define BS_EXP_MOVERS 1                   // experiment builds set 0: the eight warps stay out of the stage handshake (timing only)
+#endif
+#ifndef BS_SA
+#define BS_SA 4                         // weight stages in flight (32 KB of shared memory each)
+#define BS_SB 4                         // activation stages (8 KB each)
+#endif
+#ifdef BS_EXP_NOMMA
+#define BS_EXP_MMA 0
+#else
+#define BS_EXP_MMA 1
+#endif
 #define BS_PF 4                         // stages of raw codes an unpack thread keeps in flight                   // TMEM columns of one scale-factor set: A tile 0, A tile 1, B, spare
 
 // Instruction descriptor, kind::mxf8f6f4 block-scaled: A e2m1, B e4m3, scales ue8m0, both K-major, D f32.
@@ -110,7 +123,7 @@ struct moe_bs_smem {
     static constexpr int B_OFS = SA * TC5_MS * TC5_A_BYTES;    // an A tile is 128 rows x 128 bytes, as in the f16 arm
     static constexpr int SFA_OFS = B_OFS + SB * B_BYTES;
     static constexpr int SFB_OFS = SFA_OFS + SA * TC5_MS * BS_SF_ATOM;
-    static constexpr int BAR_OFS = SFB_OFS + SB * BS_SF_ATOM;
+    static constexpr int BAR_OFS = SFB_OFS + SA * BS_SF_ATOM;   // the activation scale atoms ride the A ring
     static constexpr int NBARS = 2 * SA + 2 * SB + 4;
     static constexpr int MISC_OFS = BAR_OFS + NBARS * 8;
     static constexpr int TOTAL = MISC_OFS + 16 + 1024;
@@ -142,7 +155,7 @@ moe_gemm_bs_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
     const int nunits = p.n_expert * p.row_tiles * p.max_tok_tiles;
 
     if (tid == 0) {
-        for (int s = 0; s < SA; s++) { mbar_init(smem_u32(a_full + s), TC5_DQ_THREADS / 32 + (TMAA ? 1 : 0)); mbar_init(smem_u32(a_empty + s), 1); }
+        for (int s = 0; s < SA; s++) { mbar_init(smem_u32(a_full + s), BS_EXP_MOVERS * (TC5_DQ_THREADS / 32) + (TMAA ? 1 : 0)); mbar_init(smem_u32(a_empty + s), 1); }
         for (int s = 0; s < SB; s++) { mbar_init(smem_u32(b_full + s), 1); mbar_init(smem_u32(b_empty + s), 1); }
         for (int i = 0; i < 2; i++) { mbar_init(smem_u32(acc_full + i), 1); mbar_init(smem_u32(acc_empty + i), 4); }
         abort_flag[0] = 0;
@@ -165,51 +178,40 @@ moe_gemm_bs_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
     (void)rt; (void)col0; (void)m_eff
 
     if (warp == 4) {
-        // every lane walks the loop: lane 0 waits and issues the TMA copy, all lanes move the tokens' scale words
-        uint32_t kb_it = 0;
-        bool ok = true;
-        for (int u = blockIdx.x; u < nunits && ok && !*abort_flag; u += gridDim.x) {
-            BS_UNIT(u);
-            if (!live) continue;
-            for (int kb = 0; kb < nkb && ok; kb++, kb_it++) {
-                const uint32_t s = kb_it % SB, ph = (kb_it / SB) & 1;
-                if (kb_it >= (uint32_t)SB) {
-                    int w = 1;
-                    if (lane == 0) w = tc5_wait(smem_u32(b_empty + s), ph ^ 1, abort_flag) ? 1 : 0;
-                    ok = __shfl_sync(0xffffffffu, w, 0) != 0;
-                }
-                if (!ok) break;
-                uint8_t *sfb = smem + L::SFB_OFS + s * BS_SF_ATOM;
-#pragma unroll
-                for (int i = 0; i < NT / 32; i++) {
-                    const int col = lane + 32 * i;
-                    const int pos = min(col0 + col, p.npairs - 1);                       // rows past the list are never stored
-                    const uint32_t w4 = __ldg(reinterpret_cast<const uint32_t *>(p.sfb + (size_t)pos * p.sfb_stride) + kb);
-                    *reinterpret_cast<uint32_t *>(sfb + (col & 31) * 16 + (col >> 5) * 4) = w4;
-                }
-                fence_async_smem();
-                __syncwarp();
-                if (lane == 0) {
+        // TMA only, one lane: activation tile, then the two weight tiles. (Nothing in this warp writes shared memory:
+        // a proxy fence here would wait for the copies in flight and put their latency into every stage.)
+        if (lane == 0) {
+            uint32_t kb_it = 0;
+            bool ok = true;
+            for (int u = blockIdx.x; u < nunits && ok && !*abort_flag; u += gridDim.x) {
+                BS_UNIT(u);
+                if (!live) continue;
+                for (int kb = 0; kb < nkb && ok; kb++, kb_it++) {
+                    const uint32_t s = kb_it % SB, ph = (kb_it / SB) & 1;
+                    if (kb_it >= (uint32_t)SB) ok = tc5_wait(smem_u32(b_empty + s), ph ^ 1, abort_flag);
+                    if (!ok) break;
+#ifdef BS_EXP_NOB
+                    mbar_arrive(smem_u32(b_full + s));
+#else
                     mbar_arrive_expect_tx(smem_u32(b_full + s), L::B_BYTES);
                     tma_load_2d(sbase + L::B_OFS + s * L::B_BYTES, &xmap, kb * BS_KB, col0, smem_u32(b_full + s));
-                }
-                if (TMAA) {
-                    const uint32_t sa = kb_it % SA, pha = (kb_it / SA) & 1;
-                    if (kb_it >= (uint32_t)SA) {
-                        int w = 1;
-                        if (lane == 0) w = tc5_wait(smem_u32(a_empty + sa), pha ^ 1, abort_flag) ? 1 : 0;
-                        ok = __shfl_sync(0xffffffffu, w, 0) != 0;
-                    }
-                    if (!ok) break;
-                    if (lane == 0) {
+#endif
+                    if (TMAA) {
+                        const uint32_t sa = kb_it % SA, pha = (kb_it / SA) & 1;
+                        if (kb_it >= (uint32_t)SA) ok = tc5_wait(smem_u32(a_empty + sa), pha ^ 1, abort_flag);
+                        if (!ok) break;
                         // two boxes of 128 rows x 128 codes; in shared memory a code row takes 128 bytes (16 codes in the
                         // low half of every 16-byte unit), but the barrier counts the 64 bytes per row that are copied
                         const int y0 = e * p.rows + (p.mode == 0 ? rt * TC5_M : rt * TC5_ROWS);
                         const uint32_t dst = sbase + L::A_OFS + sa * TC5_MS * TC5_A_BYTES;
+#ifdef BS_EXP_NOA
+                        mbar_arrive(smem_u32(a_full + sa));
+#else
                         mbar_arrive_expect_tx(smem_u32(a_full + sa), TC5_MS * TC5_A_BYTES / 2);
                         tma_load_2d(dst, &amap0, kb * BS_KB, y0, smem_u32(a_full + sa));
                         tma_load_2d(dst + TC5_A_BYTES, p.mode == 0 ? &amap1 : &amap0, kb * BS_KB, p.mode == 0 ? y0 : y0 + TC5_M,
                                     smem_u32(a_full + sa));
+#endif
                     }
                 }
             }
@@ -233,10 +235,12 @@ moe_gemm_bs_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
                     if (!ok) break;
                     tc5_fence_after();
                     const uint32_t tsf = tsf0 + (kb_it & 1) * BS_SF_COLS;         // two sets, alternating
+#ifndef BS_EXP_NOMMA
 #pragma unroll
                     for (int ms = 0; ms < TC5_MS; ms++)
                         bs_cp_sf(tsf + ms * 4, bs_sf_desc(sbase + L::SFA_OFS + (sa * TC5_MS + ms) * BS_SF_ATOM));
-                    bs_cp_sf(tsf + 8, bs_sf_desc(sbase + L::SFB_OFS + s * BS_SF_ATOM));
+                    bs_cp_sf(tsf + 8, bs_sf_desc(sbase + L::SFB_OFS + sa * BS_SF_ATOM));
+#endif
                     const uint64_t bdesc = tc5_smem_desc(sbase + L::B_OFS + s * L::B_BYTES);
                     const int nj = min(BS_KB / 32, nblk - kb * (BS_KB / 32));     // the last stage of a row may be short
 #pragma unroll
@@ -244,7 +248,7 @@ moe_gemm_bs_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
                         const uint64_t adesc = tc5_smem_desc(sbase + L::A_OFS + (sa * TC5_MS + ms) * TC5_A_BYTES);
 #pragma unroll
                         for (int j = 0; j < BS_KB / 32; j++)
-                            if (j < nj)
+                            if (j < nj && BS_EXP_MMA)
                                 bs_mma(d_tmem + ms * NT, adesc + 2 * j, bdesc + 2 * j, bs_idesc(TC5_M, NT, j, j), (kb | j) != 0,
                                        tsf + ms * 4, tsf + 8);
                     }
@@ -256,7 +260,7 @@ moe_gemm_bs_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
                 unit_it++;
             }
         }
-    } else if (warp >= 6) {
+    } else if (warp >= 6 && BS_EXP_MOVERS) {
         // ---- unpack: thread r owns tile row r. mode 0: rows 0..127 gate, 128..255 up (same row index); mode 1: 256
         //      consecutive rows of down. Per stage: four blocks of 16 code bytes -> eight 16-byte units (codes in the low
         //      half), and the four block scales as one word of the scale-factor atom.
@@ -274,6 +278,10 @@ moe_gemm_bs_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
             const size_t grow = (size_t)e * p.rows + row;
             const uint8_t *codes = (second ? p.c1 : p.c0) + grow * nblk * 16;
             const uint8_t *ebytes = (second ? p.e1 : p.e0) + grow * p.e_stride;
+            const uint32_t *sfb_row = reinterpret_cast<const uint32_t *>(p.sfb + (size_t)min(col0 + (r & (NT - 1)), p.npairs - 1) * p.sfb_stride);
+            uint32_t sfbw[BS_PF];                          // threads r < NT: token col0 + r's scale words, BS_PF stages ahead
+#pragma unroll
+            for (int j = 0; j < BS_PF; j++) sfbw[j] = (r < NT && j < nkb) ? __ldg(sfb_row + j) : 0x7F7F7F7Fu;
             auto load_stage = [&](int kb, uint4 (&c)[4], uint32_t &sfw) {
                 sfw = 0x7F7F7F7Fu;
 #pragma unroll
@@ -306,8 +314,11 @@ moe_gemm_bs_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
                     uint4 c[4];
 #pragma unroll
                     for (int b = 0; b < 4; b++) c[b] = q[j][b];
-                    const uint32_t sf_cur = sfw[j];
-                    if (kb + BS_PF < nkb) load_stage(kb + BS_PF, q[j], sfw[j]);
+                    const uint32_t sf_cur = sfw[j], sfb_cur = sfbw[j];
+                    if (kb + BS_PF < nkb) {
+                        load_stage(kb + BS_PF, q[j], sfw[j]);
+                        if (r < NT) sfbw[j] = __ldg(sfb_row + kb + BS_PF);
+                    }
                     if (kb_it >= (uint32_t)SA) ok = tc5_wait(smem_u32(a_empty + s), ph ^ 1, abort_flag);
                     if (!ok) break;
                     if (!TMAA) {
@@ -319,6 +330,7 @@ moe_gemm_bs_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
                         }
                     }
                     *reinterpret_cast<uint32_t *>(smem + L::SFA_OFS + s * TC5_MS * BS_SF_ATOM + sf_ofs) = sf_cur;
+                    if (r < NT) *reinterpret_cast<uint32_t *>(smem + L::SFB_OFS + s * BS_SF_ATOM + (r & 31) * 16 + (r >> 5) * 4) = sfb_cur;
                     fence_async_smem();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(smem_u32(a_full + s));
@@ -326,7 +338,7 @@ moe_gemm_bs_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
                 }
             }
         }
-    } else {
+    } else if (warp < 4) {
         // ---- epilogue: warp w reads TMEM lanes 32w..32w+31 (tile rows), 32 token columns at a time
         uint32_t unit_it = 0;
         for (int u = blockIdx.x; u < nunits && !*abort_flag; u += gridDim.x) {
@@ -339,6 +351,9 @@ moe_gemm_bs_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
             const int pos_end = p.off[e] + p.cnt[e];
 #pragma unroll 1
             for (int c0 = 0; c0 < NT; c0 += 32) {
+#ifdef BS_EXP_NOEPI
+                break;
+#endif
                 const int pos0 = col0 + c0;
                 if (p.mode == 0) {
                     uint32_t vg[32], vu[32];
