@@ -71,6 +71,8 @@ __host__ __device__ constexpr int bs_kpos(int i) { return i < 16 ? 2 * i : 2 * (
 // One CTA per destination row: q[row][k] e4m3 bytes (block-permuted K order), sf[row][sf_stride] ue8m0 bytes. The
 // source row is rowmap[row] when a map is given (entries outside [0, nsrc) read row 0: their destination belongs to
 // no expert's list). The scale is the smallest power of two that brings the block's amax within e4m3's 448.
+// A warp takes four blocks at a time: lane l holds elements 4 (l % 8) .. + 3 of block l / 8; elements e and e + 16 are
+// neighbours in the permuted order, so lanes q and q + 4 of a block trade their codes and lane q < 4 stores 8 bytes.
 static __global__ void __launch_bounds__(256)
 act_to_mx8_kernel(const void *__restrict__ x, int x_dtype, uint8_t *__restrict__ q, uint8_t *__restrict__ sf, int k, int sf_stride,
                   const int *__restrict__ rowmap, int nsrc) {
@@ -83,20 +85,31 @@ act_to_mx8_kernel(const void *__restrict__ x, int x_dtype, uint8_t *__restrict__
         if ((unsigned)src >= (unsigned)nsrc) src = 0;
     }
     const size_t base = (size_t)src * k;
-    const int nblk = k / 32;
-    for (int b = warp; b < sf_stride; b += 8) {
-        if (b >= nblk) {                                  // padding of the scale row: 2^0
-            if (lane == 0) sf[(size_t)row * sf_stride + b] = 127;
-            continue;
+    const int nblk = k / 32, sub = lane >> 3, qd = lane & 7;
+    for (int b0 = warp * 4; b0 < sf_stride; b0 += 32) {
+        const int b = b0 + sub;
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
+        if (b < nblk) {
+            const size_t i = base + (size_t)b * 32 + 4 * qd;
+            if (x_dtype == JL_DT_F32) {
+                const float4 t = __ldg(reinterpret_cast<const float4 *>(static_cast<const float *>(x) + i));
+                v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+            } else {
+                const uint2 t = __ldg(reinterpret_cast<const uint2 *>(static_cast<const uint16_t *>(x) + i));
+                if (x_dtype == JL_DT_BF16) {
+                    const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&t.x));
+                    const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&t.y));
+                    v[0] = lo.x; v[1] = lo.y; v[2] = hi.x; v[3] = hi.y;
+                } else {
+                    const float2 lo = __half22float2(*reinterpret_cast<const __half2 *>(&t.x));
+                    const float2 hi = __half22float2(*reinterpret_cast<const __half2 *>(&t.y));
+                    v[0] = lo.x; v[1] = lo.y; v[2] = hi.x; v[3] = hi.y;
+                }
+            }
         }
-        float v;
-        const size_t i = base + (size_t)b * 32 + lane;
-        if (x_dtype == JL_DT_F32) v = __ldg(static_cast<const float *>(x) + i);
-        else if (x_dtype == JL_DT_BF16) v = __bfloat162float(__ldg(static_cast<const __nv_bfloat16 *>(x) + i));
-        else v = __half2float(__ldg(static_cast<const __half *>(x) + i));
-        float amax = fabsf(v);
+        float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
 #pragma unroll
-        for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        for (int o = 4; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));   // the block's eight lanes
         int se = 0;
         if (amax > 0.f && amax < __int_as_float(0x7f800000)) {
             int ex;
@@ -104,10 +117,22 @@ act_to_mx8_kernel(const void *__restrict__ x, int x_dtype, uint8_t *__restrict__
             se = m == 0.5f ? ex - 1 : ex;
             se = max(-126, min(127, se));
         }
-        const float scaled = v * __uint_as_float((uint32_t)(127 - se) << 23);
-        const uint8_t code = (uint8_t)__nv_cvt_float_to_fp8(scaled, __NV_SATFINITE, __NV_E4M3);
-        q[(size_t)row * k + (size_t)b * 32 + bs_kpos(lane)] = code;
-        if (lane == 0) sf[(size_t)row * sf_stride + b] = (uint8_t)(127 + se);
+        const float sc = __uint_as_float((uint32_t)(127 - se) << 23);
+        uint32_t mine = 0;
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+            mine |= (uint32_t)(uint8_t)__nv_cvt_float_to_fp8(v[j] * sc, __NV_SATFINITE, __NV_E4M3) << (8 * j);
+        const uint32_t other = __shfl_xor_sync(0xffffffffu, mine, 4);       // lanes qd and qd + 4: elements e and e + 16
+        if (b < nblk) {
+            if (qd < 4) {
+                // bytes 8 qd .. 8 qd + 7: elements 4 qd + j (even positions) and 16 + 4 qd + j (odd positions)
+                const uint32_t w0 = __byte_perm(mine, other, 0x5140), w1 = __byte_perm(mine, other, 0x7362);
+                *reinterpret_cast<uint2 *>(q + (size_t)row * k + (size_t)b * 32 + 8 * qd) = make_uint2(w0, w1);
+            }
+            if (qd == 0) sf[(size_t)row * sf_stride + b] = (uint8_t)(127 + se);
+        } else if (b < sf_stride && qd == 0) {
+            sf[(size_t)row * sf_stride + b] = 127;                         // padding of the scale row: 2^0
+        }
     }
 }
 
