@@ -260,7 +260,7 @@ moe_gemm_bs_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
                     if (!ok) break;
                     tc5_fence_after();
                     const uint32_t tsf = tsf0 + (kb_it & 1) * BS_SF_COLS;         // two sets, alternating
-#ifndef BS_EXP_NOMMA
+#if !defined(BS_EXP_NOMMA) && !defined(BS_EXP_NOCP)
 #pragma unroll
                     for (int ms = 0; ms < TC5_MS; ms++)
                         bs_cp_sf(tsf + ms * 4, bs_sf_desc(sbase + L::SFA_OFS + (sa * TC5_MS + ms) * BS_SF_ATOM));
