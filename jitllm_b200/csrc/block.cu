@@ -65,6 +65,9 @@ struct alignas(16) bk_phase {
     int exchange;       // outputs go to every rank's slot buffer
     int nplanes;        // NORM: partial planes added to the residual row (0 = none)
     int from_emb;       // NORM: the residual row starts as the embedding of *tok
+    int ksplit;         // STORE: the CTAs split the phase's (row group, super-block) tasks evenly, cutting row groups:
+                        // the part of a row group that starts at super-block 0 goes to plane 0 of `out`, the rest to
+                        // plane 1 (out + hidden), whole row groups write 0 to plane 1; the consumer adds both planes
     const bk_ll *planes;   // NORM: [nplanes][hidden]
     const float *norm_w;   // NORM: [hidden]
     const bk_ll *vsrc;     // PLAIN: the activation row
@@ -260,6 +263,8 @@ __device__ __forceinline__ bool bk_grid_sync(const bk_params &P, int &done, uint
 struct bk_pinfo {
     int kind, map, nsb, epi;
     int rg0, rg1, up_row0, rpr;   // this CTA's row groups [rg0, rg1); row groups per round
+    int off0, xend;               // ksplit phases (xend > 0): ONE round starting at row group rg0 whose tasks are the
+                                  // indices [off0, xend) of (row group - rg0) * nsb + super-block
 };
 #define BK_MAX_PHASES 512
 
@@ -270,6 +275,7 @@ struct bk_cursor {
     int nr;       // row groups in the current round
     int rgl, sb;  // this warp's task inside the round: row group (relative to rbase) and super-block
     int nsb, rpr;
+    int off0, xend;   // the round's tasks: indices [off0, xend) of rgl * nsb + sb (whole row groups: 0, nr * nsb)
 };
 
 __device__ __forceinline__ int bk_phase_nrg(const bk_phase &ph) {
@@ -281,8 +287,9 @@ __device__ __forceinline__ int bk_rounds_rgs(int nsb) {
 }
 // The warp's first task of a round: task index `warp`, if the round has that many.
 __device__ __forceinline__ bool bk_cursor_round(bk_cursor &c, int warp) {
-    if (warp >= c.nr * c.nsb) return false;
-    c.rgl = warp / c.nsb; c.sb = warp % c.nsb;
+    const int x = c.off0 + warp;
+    if (x >= c.xend) return false;
+    c.rgl = x / c.nsb; c.sb = x % c.nsb;
     return true;
 }
 // Positions the cursor on the warp's first task of the first matvec phase >= p that has one.
@@ -293,6 +300,7 @@ __device__ __forceinline__ void bk_cursor_seek(bk_cursor &c, const bk_pinfo *pi,
         c.rg1 = f.rg1; c.nsb = f.nsb; c.rpr = f.rpr;
         for (c.rbase = f.rg0; c.rbase < c.rg1; c.rbase += c.rpr) {
             c.nr = min(c.rpr, c.rg1 - c.rbase);
+            c.off0 = f.xend ? f.off0 : 0; c.xend = f.xend ? f.xend : c.nr * c.nsb;
             if (bk_cursor_round(c, warp)) { c.p = p; return; }
         }
     }
@@ -301,9 +309,10 @@ __device__ __forceinline__ void bk_cursor_seek(bk_cursor &c, const bk_pinfo *pi,
 __device__ __forceinline__ void bk_cursor_next(bk_cursor &c, const bk_pinfo *pi, int nphases, int warp) {
     c.sb += BK_WARPS;                       // task index + 16, super-block fastest
     while (c.sb >= c.nsb) { c.sb -= c.nsb; c.rgl++; }
-    if (c.rgl < c.nr) return;
+    if (c.rgl * c.nsb + c.sb < c.xend) return;
     for (c.rbase += c.rpr; c.rbase < c.rg1; c.rbase += c.rpr) {
         c.nr = min(c.rpr, c.rg1 - c.rbase);
+        c.off0 = 0; c.xend = c.nr * c.nsb;
         if (bk_cursor_round(c, warp)) return;
     }
     bk_cursor_seek(c, pi, nphases, c.p + 1, warp);
@@ -723,8 +732,9 @@ __device__ bool bk_attention(const bk_params &P, const bk_phase &ph, uint8_t *wo
 #define BK_XOP_BYTES (BK_MAX_NSB * Q4K_XP_SB_BYTES)
 #define BK_RED_BYTES (BK_ROUND_TASKS * 16 * 4)
 #define BK_WORK_BYTES (4 * BK_ATT_SUB_BYTES > BK_XOP_BYTES + BK_RED_BYTES ? 4 * BK_ATT_SUB_BYTES : BK_XOP_BYTES + BK_RED_BYTES)
+static_assert(sizeof(bk_pinfo) % 8 == 0, "the phase table is followed by 16-byte aligned descriptors");
 #define BK_PHASE_BYTES ((sizeof(bk_phase) + 15) / 16 * 16)
-#define BK_SMEM_BYTES (BK_RING_BYTES + BK_WORK_BYTES + Q4K_XP_ZERO_BYTES + BK_WARPS * BK_STAGES * 8 + 64 * 4 + BK_MAX_PHASES * 32 + 3 * BK_PHASE_BYTES + 128)
+#define BK_SMEM_BYTES (BK_RING_BYTES + BK_WORK_BYTES + Q4K_XP_ZERO_BYTES + BK_WARPS * BK_STAGES * 8 + 64 * 4 + BK_MAX_PHASES * sizeof(bk_pinfo) + 3 * BK_PHASE_BYTES + 128)
 
 __global__ void __launch_bounds__(BK_THREADS, 1) jl_block_kernel(const __grid_constant__ bk_params P) {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -756,12 +766,21 @@ __global__ void __launch_bounds__(BK_THREADS, 1) jl_block_kernel(const __grid_co
         const bk_phase &q = P.phases[i];
         bk_pinfo f;
         f.kind = q.kind; f.map = q.map; f.nsb = q.nsb; f.epi = q.epilogue; f.up_row0 = q.up_row0;
-        f.rg0 = f.rg1 = 0; f.rpr = 1;
+        f.rg0 = f.rg1 = 0; f.rpr = 1; f.off0 = f.xend = 0;
         if (q.kind == BK_MATVEC) {
             const int nrg = bk_phase_nrg(q);
             f.rg0 = (int)((long long)blockIdx.x * nrg / gridDim.x);
             f.rg1 = (int)((long long)(blockIdx.x + 1) * nrg / gridDim.x);
             f.rpr = bk_rounds_rgs(q.nsb);
+            if (q.ksplit) {
+                // an even share of the tasks, in row-group-major order; one round (the host checked that it fits)
+                const long long total = (long long)nrg * q.nsb;
+                const int t0 = (int)(blockIdx.x * total / gridDim.x), t1 = (int)((blockIdx.x + 1) * total / gridDim.x);
+                f.rg0 = t0 / q.nsb; f.rg1 = (t1 + q.nsb - 1) / q.nsb;
+                f.rpr = max(1, f.rg1 - f.rg0);
+                f.off0 = t0 - f.rg0 * q.nsb; f.xend = t1 - f.rg0 * q.nsb;
+                if (t1 <= t0) { f.rg1 = f.rg0; f.xend = 0; }
+            }
         }
         pinfo[i] = f;
     }
@@ -842,10 +861,12 @@ __global__ void __launch_bounds__(BK_THREADS, 1) jl_block_kernel(const __grid_co
             BK_TRACE(1);
             if (!alive) break;
             const int nsb = pinfo[p].nsb, rg0 = pinfo[p].rg0, rg1 = pinfo[p].rg1, rpr = pinfo[p].rpr;
+            const int ks_off0 = pinfo[p].off0, ks_xend = pinfo[p].xend;      // ksplit phases: one round, tasks [off0, xend)
             for (int rbase = rg0; rbase < rg1 && alive; rbase += rpr) {
-                const int nr = min(rpr, rg1 - rbase), ntask = nr * nsb;
-                for (int tk = warp; tk < ntask; tk += BK_WARPS) {
-                    const int sb = tk % nsb;
+                const int nr = min(rpr, rg1 - rbase);
+                const int x0 = ks_xend ? ks_off0 : 0, x1 = ks_xend ? ks_xend : nr * nsb;
+                for (int x = x0 + warp; x < x1; x += BK_WARPS) {
+                    const int sb = x % nsb, tk = x - x0;
                     const uint32_t s = consumed % BK_STAGES, parity = (consumed / BK_STAGES) & 1u;
                     BK_FT(0);
                     if (!__all_sync(0xffffffffu, bk_mbar_wait(smem_u32(bars + s), parity, limit_ns))) {
@@ -890,6 +911,21 @@ __global__ void __launch_bounds__(BK_THREADS, 1) jl_block_kernel(const __grid_co
                         }
                         const int o = (rbase + rgl) * 8 + r;
                         if (o < ph.nrows) bk_ll_store(ph.out + o, sg / (1.f + __expf(-sg)) * su, seq_w);     // SiLU(gate) * up
+                    }
+                } else if (ks_xend) {
+                    // the pieces of row groups this CTA computed: the piece that starts a row group goes to plane 0, the
+                    // piece that ends one (and does not start it) to plane 1; a whole row group writes 0 to plane 1
+                    if (tid < nr * 16) {
+                        const int rgl = tid >> 4, r = tid & 15;
+                        const int a = max(x0, rgl * nsb), b = min(x1, (rgl + 1) * nsb);
+                        float sum = 0.f;
+                        for (int x = a; x < b; x++) sum += red[(x - x0) * 16 + r];
+                        const int row = (rbase + rgl) * 16 + r;
+                        if (row < ph.nrows && a < b) {
+                            const bool head = a == rgl * nsb, whole = head && b == (rgl + 1) * nsb;
+                            bk_ll_store(ph.out + (head ? 0 : P.hidden) + row, sum, seq_w);
+                            if (whole) bk_ll_store(ph.out + P.hidden + row, 0.f, seq_w);
+                        }
                     }
                 } else if (tid < nr * 16) {
                     const int rgl = tid >> 4, r = tid & 15;
@@ -999,7 +1035,10 @@ struct jl_layers {
 };
 
 static size_t bk_al(size_t n) { return (n + 255) & ~(size_t)255; }
-static size_t bk_slot_bytes(int world, int hidden) { return 2 * bk_al((size_t)world * hidden * sizeof(bk_ll)); }
+// Two output vectors (o, down) of `world` planes each; a single-GPU stack uses two planes per vector for the
+// row-group split (bk_phase::ksplit).
+static size_t bk_slot_planes(int world) { return world > 1 ? world : 2; }
+static size_t bk_slot_bytes(int world, int hidden) { return 2 * bk_al(bk_slot_planes(world) * hidden * sizeof(bk_ll)); }
 
 // PrepLayer for every block plus the head (engine/nn/device.go:1099-1102): checks that each weight has a
 // kernel here, builds the phase list and sizes all scratch. Declines (JL_DECLINED) instead of running a
@@ -1076,7 +1115,16 @@ JL_EXPORT int jl_layers_prep(jl_ctx *ctx, const jl_layers_desc *d, jl_layers **o
     }
     uint8_t *B = S->buf;
     bk_ll *qkv = (bk_ll *)(B + o_qkv), *att = (bk_ll *)(B + o_att), *abuf = (bk_ll *)(B + o_a);
-    bk_ll *planesO = (bk_ll *)S->slot, *planesD = (bk_ll *)(S->slot + bk_al((size_t)world * H * sizeof(bk_ll)));
+    bk_ll *planesO = (bk_ll *)S->slot, *planesD = (bk_ll *)(S->slot + bk_al(bk_slot_planes(world) * H * sizeof(bk_ll)));
+    // Single GPU: o and down have H / 16 row groups for 148 CTAs (1 or 2 each): the CTAs take even shares of the
+    // (row group, super-block) tasks instead and the consumer adds two planes. Needs at least one row group's tasks
+    // per CTA (a row group is cut at most once) and a share that fits one round.
+    auto can_split = [&](int nrows, int nsb) {
+        const long long total = (long long)((nrows + 15) / 16) * nsb;
+        return world == 1 && total / S->grid >= nsb && (total + S->grid - 1) / S->grid + 1 <= BK_ROUND_TASKS && nrows == H;
+    };
+    const bool split_o = can_split(H, hq * BK_ATT_D / 256), split_d = can_split(H, F / 256);
+    const int planes_o = split_o ? 2 : world, planes_d = split_d ? 2 : world;
     unsigned *tickets = (unsigned *)(B + o_bar + 16);
     S->logits = (float *)(B + o_logits);
     S->trace = (unsigned long long *)(B + o_trace);
@@ -1099,7 +1147,7 @@ JL_EXPORT int jl_layers_prep(jl_ctx *ctx, const jl_layers_desc *d, jl_layers **o
         maps[4 * l + 3] = map16(b.down);
         bk_phase q = {};
         q.kind = BK_MATVEC; q.map = 4 * l; q.nrows = (hq + 2 * hkv) * BK_ATT_D; q.nsb = H / 256; q.prologue = BK_PRO_NORM;
-        q.epilogue = BK_EPI_STORE; q.from_emb = l == 0; q.planes = planesD; q.nplanes = l == 0 ? 0 : world;
+        q.epilogue = BK_EPI_STORE; q.from_emb = l == 0; q.planes = planesD; q.nplanes = l == 0 ? 0 : planes_d;
         q.norm_w = b.attn_norm; q.out = qkv;
         S->phases[pi++] = q;
         bk_phase a = {};
@@ -1107,16 +1155,16 @@ JL_EXPORT int jl_layers_prep(jl_ctx *ctx, const jl_layers_desc *d, jl_layers **o
         S->phases[pi++] = a;
         bk_phase o = {};
         o.kind = BK_MATVEC; o.map = 4 * l + 1; o.nrows = H; o.nsb = hq * BK_ATT_D / 256; o.prologue = BK_PRO_PLAIN; o.epilogue = BK_EPI_STORE;
-        o.vsrc = att; o.out = planesO + (size_t)rank * H; o.exchange = world > 1;
+        o.vsrc = att; o.out = planesO + (size_t)rank * H; o.exchange = world > 1; o.ksplit = split_o;
         o.peer_out[rank] = o.out;
         S->phases[pi++] = o;
         bk_phase gu = {};
         gu.kind = BK_MATVEC; gu.map = 4 * l + 2; gu.nrows = F; gu.nsb = H / 256; gu.prologue = BK_PRO_NORM; gu.epilogue = BK_EPI_GATE2;
-        gu.up_row0 = F; gu.planes = planesO; gu.nplanes = world; gu.norm_w = b.ffn_norm; gu.out = abuf;
+        gu.up_row0 = F; gu.planes = planesO; gu.nplanes = planes_o; gu.norm_w = b.ffn_norm; gu.out = abuf;
         S->phases[pi++] = gu;
         bk_phase dn = {};
         dn.kind = BK_MATVEC; dn.map = 4 * l + 3; dn.nrows = H; dn.nsb = F / 256; dn.prologue = BK_PRO_PLAIN; dn.epilogue = BK_EPI_STORE;
-        dn.vsrc = abuf; dn.out = planesD + (size_t)rank * H; dn.exchange = world > 1;
+        dn.vsrc = abuf; dn.out = planesD + (size_t)rank * H; dn.exchange = world > 1; dn.ksplit = split_d;
         dn.peer_out[rank] = dn.out;
         S->phases[pi++] = dn;
     }
@@ -1124,7 +1172,7 @@ JL_EXPORT int jl_layers_prep(jl_ctx *ctx, const jl_layers_desc *d, jl_layers **o
         maps[4 * L] = map16(d->head);
         bk_phase h = {};
         h.kind = BK_MATVEC; h.map = 4 * L; h.nrows = V; h.nsb = H / 256; h.prologue = BK_PRO_NORM; h.epilogue = BK_EPI_ARGMAX;
-        h.planes = planesD; h.nplanes = world; h.norm_w = d->final_norm; h.out_f32 = S->logits;
+        h.planes = planesD; h.nplanes = planes_d; h.norm_w = d->final_norm; h.out_f32 = S->logits;
         S->phases[pi++] = h;
         bk_phase f = {};
         f.kind = BK_FINAL;
