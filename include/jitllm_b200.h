@@ -456,6 +456,12 @@ int jl_noalloc_status(void *stream);
  * `limit_us` as its bound, and records the timeout; jl_status_poll then reports it. The GPU is
  * not faulted and the context stays usable. */
 int jl_test_wait_timeout(jl_ctx *ctx, uint32_t limit_us, void *stream);
+/* Measurement helper: `iters` passes over `nw` weights, one jl_matvec per weight (host pointers in and out,
+ * exactly the public call), issued from a loop inside the library so that the caller's language adds nothing
+ * to the time. *seconds = wall clock of the loop. Stops at the first call that is not served and returns its
+ * status. */
+int jl_test_matvec_loop(jl_ctx *ctx, float *out, uint32_t type, const void *const *ws, size_t w_bytes, const float *x,
+                        int nrows, int k, int nw, int iters, double *seconds);
 
 /* ---- host-side fault injection: JITLLM_DEVICE_FAIL_AT (jit/gpu/tier/fault.go:12-58)
  * The n-th, ... serving calls on ctx (1-based ordinals, counted from this call)

@@ -123,6 +123,7 @@ SYMBOLS = {
     "jl_matmul_dev": (_I, [_VP, _VP, _I, _VP, _VP, _I, _I, _VP]),
     "jl_moe_dev": (_I, [_VP, _VP, _VP, _I, _VP, _I, C.POINTER(MoeDesc), _VP, _VP, _VP]),
     "jl_test_fail_at": (_I, [_VP, C.POINTER(C.c_int), _I]),
+    "jl_test_matvec_loop": (_I, [_VP, _VP, _U32, C.POINTER(_VP), _SZ, _VP, _I, _I, _I, _I, C.POINTER(C.c_double)]),
     "jl_layers_prep": (_I, [_VP, C.POINTER(LayersDesc), C.POINTER(_VP)]),
     "jl_layers_free": (None, [_VP, _VP]),
     "jl_layers_run": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _I, _VP]),

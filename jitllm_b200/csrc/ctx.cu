@@ -1,6 +1,8 @@
 // The C ABI: contexts, residency keyed on host addresses, the host-pointer and
 // device-pointer entry points, selection, statistics, host-side fault injection.
 #include "jl_internal.cuh"
+
+#include <chrono>
 #include "tma.cuh"
 
 #include <stdarg.h>
@@ -639,5 +641,19 @@ JL_EXPORT int jl_test_wait_timeout(jl_ctx *ctx, uint32_t limit_us, void *stream)
     jl_test_wait_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(ctx->dev_status, (uint64_t)limit_us * 1000ull);
     ctx->st.launches++;
     JL_CUDA(ctx, cudaGetLastError());
+    return JL_OK;
+}
+
+// The public host-pointer call in a loop of the library's own (see the header).
+JL_EXPORT int jl_test_matvec_loop(jl_ctx *ctx, float *out, uint32_t type, const void *const *ws, size_t w_bytes, const float *x,
+                                  int nrows, int k, int nw, int iters, double *seconds) {
+    if (!ctx || !out || !ws || !x || nw < 1 || iters < 1 || !seconds) return JL_EINVAL;
+    const auto t0 = std::chrono::steady_clock::now();
+    for (int it = 0; it < iters; it++)
+        for (int i = 0; i < nw; i++) {
+            const int rc = jl_matvec(ctx, out, type, ws[i], w_bytes, x, nrows, k);
+            if (rc != JL_OK) return rc;
+        }
+    *seconds = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
     return JL_OK;
 }

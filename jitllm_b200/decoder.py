@@ -30,7 +30,7 @@ class Config:
 
 def random_q4k(rng: np.random.Generator, nrows: int, k: int) -> np.ndarray:
     """Fast random Q4_K tensor: uniform random payload bytes (codes U{0..15}, 6-bit fields uniform),
-    d and dmin = f16(|N(0, 0.02)|) -- the distribution BASELINE config 0 states."""
+    d and dmin = f16(|N(0, 0.02)|) -- the value distribution of the headline 4096x4096 workload."""
     nb = nrows * (k // 256)
     blk = rng.integers(0, 256, (nb, 144), dtype=np.uint8)
     dd = np.abs(rng.normal(0.0, 0.02, (nb, 2))).astype(np.float16).view(np.uint16)

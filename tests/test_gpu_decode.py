@@ -68,7 +68,7 @@ def test_q4k_tensor_core_decode_matches_oracle(orc, warps, nrows, k):
 
 
 def test_q4k_decode_equals_oracle_matvec_config0(dev, orc):
-    """BASELINE config 0 verbatim: 4096x4096 Q4_K, x ~ N(0,1) f32, one seed."""
+    """The headline workload verbatim: 4096x4096 Q4_K, x ~ N(0,1) f32, one seed."""
     rng = synth.rng_for(0xB200)
     w = synth.q4k_matrix(rng, 4096, 4096)
     x = synth.activations(rng, 1, 4096)[0]

@@ -98,7 +98,7 @@ def test_activation_ranges_do_not_overflow_f16(orc):
 
 @pytest.mark.parametrize("nrows,k", [(14336, 4096), (4096, 14336)])
 def test_config1_full_size_sampled_rows(orc, nrows, k):
-    """BASELINE config 1 at full size (512 tokens, bf16 in): three 128-row bands against the f64 oracle."""
+    """The prefill workload at full size (512 tokens, bf16 in): three 128-row bands against the f64 oracle."""
     with Device(0) as d:
         bands = [(0, 128), (nrows // 2 - 64, nrows // 2 + 64), (nrows - 128, nrows)]
         got, ref = _run(d, orc, nrows, k, 512, 0xB201, rows=bands)
@@ -107,7 +107,7 @@ def test_config1_full_size_sampled_rows(orc, nrows, k):
         assert nmse(got, ref) <= 1e-6
 
 
-# ---- Q8_0 through the same kernel (batched decode, BASELINE config 2: f32 activations, batch 32)
+# ---- Q8_0 through the same kernel (batched decode workload: f32 activations, batch 32)
 
 def _run_q8(dev, orc, nrows, k, ntok, seed, x_dtype):
     from jitllm_b200 import Q8_0

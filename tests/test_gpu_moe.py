@@ -92,7 +92,7 @@ def test_swiglu_oai_with_biases(dev, orc):
 
 
 def test_config3_gpt_oss_shape(dev, orc):
-    """BASELINE config 3: hidden = ffn = 2880, 32 experts, top-4, 256 tokens, bf16 activations."""
+    """The gpt-oss-shaped mixture workload: hidden = ffn = 2880, 32 experts, top-4, 256 tokens, bf16 activations."""
     rng = synth.rng_for(0xB203)
     E, topk, hidden, ffn, ntok = 32, 4, 2880, 2880, 256
     gate, up, down = _layer(rng, E, hidden, ffn)
