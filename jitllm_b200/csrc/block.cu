@@ -52,6 +52,18 @@ enum { BK_MATVEC = 0, BK_ATTN = 1, BK_FINAL = 2 };
 enum { BK_PRO_NORM = 0, BK_PRO_PLAIN = 1 };
 enum { BK_EPI_STORE = 0, BK_EPI_GATE2 = 1, BK_EPI_ARGMAX = 2 };
 
+// Status codes of the waits. Diagnostic builds (BK_DIAG) append the site and, through bk_diag_phase, the phase and CTA.
+#ifdef BK_DIAG
+#define BK_CODE(code, site) ((code) * 10 + (site))
+static __device__ int bk_diag_phase[256];   // the phase each CTA is in
+static __device__ unsigned bk_diag_iter[256];   // polls of the wait that gave up, in thousands
+#define BK_DIAG_WHERE(code) ((code) + 100 * bk_diag_phase[blockIdx.x] + 100000 * (int)min(bk_diag_iter[blockIdx.x] >> 10, 20000u))
+#define BK_DIAG_ITER(i) (bk_diag_iter[blockIdx.x] = (i))
+#else
+#define BK_DIAG_WHERE(code) (code)
+#define BK_DIAG_ITER(i) ((void)0)
+#define BK_CODE(code, site) (code)
+#endif
 typedef uint2 bk_ll;    // {float bits, sequence number of the phase that produced it}: one 8-byte store, atomic
 
 struct alignas(16) bk_phase {
@@ -65,9 +77,6 @@ struct alignas(16) bk_phase {
     int exchange;       // outputs go to every rank's slot buffer
     int nplanes;        // NORM: partial planes added to the residual row (0 = none)
     int from_emb;       // NORM: the residual row starts as the embedding of *tok
-    int ksplit;         // STORE: the CTAs split the phase's (row group, super-block) tasks evenly, cutting row groups:
-                        // the part of a row group that starts at super-block 0 goes to plane 0 of `out`, the rest to
-                        // plane 1 (out + hidden), whole row groups write 0 to plane 1; the consumer adds both planes
     const bk_ll *planes;   // NORM: [nplanes][hidden]
     const float *norm_w;   // NORM: [hidden]
     const bk_ll *vsrc;     // PLAIN: the activation row
@@ -145,7 +154,7 @@ __device__ __forceinline__ bool bk_ll_read2(const bk_ll *p, unsigned seq, float2
         for (uint32_t i = 0;; i++) {
             a = bk_ld_vol16(p);
             if (a.y == seq && a.w == seq) break;
-            if ((i & 7u) == 7u && bk_ll_giveup(P, t0, limit_ns, code)) return false;
+            if ((i & 7u) == 7u) { BK_DIAG_ITER(i); if (bk_ll_giveup(P, t0, limit_ns, code)) return false; }
         }
     }
     out = make_float2(__uint_as_float(a.x), __uint_as_float(a.z));
@@ -158,7 +167,7 @@ __device__ __forceinline__ bool bk_ll_read4(const bk_ll *p, unsigned seq, float4
         for (uint32_t i = 0;; i++) {
             a = bk_ld_vol16(p); b = bk_ld_vol16(p + 2);
             if (a.y == seq && a.w == seq && b.y == seq && b.w == seq) break;
-            if ((i & 7u) == 7u && bk_ll_giveup(P, t0, limit_ns, code)) return false;
+            if ((i & 7u) == 7u) { BK_DIAG_ITER(i); if (bk_ll_giveup(P, t0, limit_ns, code)) return false; }
         }
     }
     out = make_float4(__uint_as_float(a.x), __uint_as_float(a.z), __uint_as_float(b.x), __uint_as_float(b.z));
@@ -212,7 +221,7 @@ __device__ __forceinline__ bool bk_mbar_wait(uint32_t bar, uint32_t parity, uint
 __device__ __forceinline__ bool bk_ll_giveup(const bk_params &P, uint64_t t0, uint64_t limit_ns, int code) {
     if (bk_ld_volatile(P.abort_word)) return true;
     if (jl_gtime_ns() - t0 > limit_ns) {
-        atomicExch(P.status, code);
+        atomicCAS(P.status, 0, BK_DIAG_WHERE(code));       // the first wait that ran out names the cause; later ones are its consequences
         atomicExch(P.abort_word, 1);
         return true;
     }
@@ -229,7 +238,7 @@ __device__ __forceinline__ bool bk_wait_ge(const unsigned *p, unsigned target, c
         if ((i & 15u) == 15u) {
             if (bk_ld_volatile(P.abort_word)) return false;
             if (jl_gtime_ns() - t0 > limit_ns) {
-                atomicExch(P.status, code);
+                atomicCAS(P.status, 0, BK_DIAG_WHERE(code));       // the first wait that ran out names the cause; later ones are its consequences
                 atomicExch(P.abort_word, 1);
                 return false;
             }
@@ -245,7 +254,7 @@ __device__ __forceinline__ bool bk_grid_sync(const bk_params &P, int &done, uint
     if (threadIdx.x == 0) {
         // release: the CTA's writes (ordered before this thread by the barrier above) become visible before the count
         asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(P.bar) : "memory");
-        s_ok = bk_wait_ge<false>(P.bar, (unsigned)(done + 1) * gridDim.x, P, limit_ns, 4) ? 1 : 0;   // acquire loads
+        s_ok = bk_wait_ge<false>(P.bar, (unsigned)(done + 1) * gridDim.x, P, limit_ns, BK_CODE(4, 4)) ? 1 : 0;   // acquire loads
     }
     __syncthreads();
     done++;
@@ -263,8 +272,6 @@ __device__ __forceinline__ bool bk_grid_sync(const bk_params &P, int &done, uint
 struct bk_pinfo {
     int kind, map, nsb, epi;
     int rg0, rg1, up_row0, rpr;   // this CTA's row groups [rg0, rg1); row groups per round
-    int off0, xend;               // ksplit phases (xend > 0): ONE round starting at row group rg0 whose tasks are the
-                                  // indices [off0, xend) of (row group - rg0) * nsb + super-block
 };
 #define BK_MAX_PHASES 512
 
@@ -275,7 +282,6 @@ struct bk_cursor {
     int nr;       // row groups in the current round
     int rgl, sb;  // this warp's task inside the round: row group (relative to rbase) and super-block
     int nsb, rpr;
-    int off0, xend;   // the round's tasks: indices [off0, xend) of rgl * nsb + sb (whole row groups: 0, nr * nsb)
 };
 
 __device__ __forceinline__ int bk_phase_nrg(const bk_phase &ph) {
@@ -287,9 +293,8 @@ __device__ __forceinline__ int bk_rounds_rgs(int nsb) {
 }
 // The warp's first task of a round: task index `warp`, if the round has that many.
 __device__ __forceinline__ bool bk_cursor_round(bk_cursor &c, int warp) {
-    const int x = c.off0 + warp;
-    if (x >= c.xend) return false;
-    c.rgl = x / c.nsb; c.sb = x % c.nsb;
+    if (warp >= c.nr * c.nsb) return false;
+    c.rgl = warp / c.nsb; c.sb = warp % c.nsb;
     return true;
 }
 // Positions the cursor on the warp's first task of the first matvec phase >= p that has one.
@@ -300,7 +305,6 @@ __device__ __forceinline__ void bk_cursor_seek(bk_cursor &c, const bk_pinfo *pi,
         c.rg1 = f.rg1; c.nsb = f.nsb; c.rpr = f.rpr;
         for (c.rbase = f.rg0; c.rbase < c.rg1; c.rbase += c.rpr) {
             c.nr = min(c.rpr, c.rg1 - c.rbase);
-            c.off0 = f.xend ? f.off0 : 0; c.xend = f.xend ? f.xend : c.nr * c.nsb;
             if (bk_cursor_round(c, warp)) { c.p = p; return; }
         }
     }
@@ -309,10 +313,9 @@ __device__ __forceinline__ void bk_cursor_seek(bk_cursor &c, const bk_pinfo *pi,
 __device__ __forceinline__ void bk_cursor_next(bk_cursor &c, const bk_pinfo *pi, int nphases, int warp) {
     c.sb += BK_WARPS;                       // task index + 16, super-block fastest
     while (c.sb >= c.nsb) { c.sb -= c.nsb; c.rgl++; }
-    if (c.rgl * c.nsb + c.sb < c.xend) return;
+    if (c.rgl < c.nr) return;
     for (c.rbase += c.rpr; c.rbase < c.rg1; c.rbase += c.rpr) {
         c.nr = min(c.rpr, c.rg1 - c.rbase);
-        c.off0 = 0; c.xend = c.nr * c.nsb;
         if (bk_cursor_round(c, warp)) return;
     }
     bk_cursor_seek(c, pi, nphases, c.p + 1, warp);
@@ -377,7 +380,7 @@ __device__ __forceinline__ bool bk_prologue(const bk_params &P, const bk_phase &
                 for (int q = 0; q < 4; q++)
                     pp[q] = r + (q >> 1) < ph.nplanes
                                 ? ph.planes + (size_t)(r + (q >> 1)) * P.hidden + (size_t)(warp * 64 + (q & 1) * 32 + lane) * 4 : nullptr;
-                ok = bk_ll_read4_n<4>(pp, seq, d, P, limit_ns, 5) && ok;
+                ok = bk_ll_read4_n<4>(pp, seq, d, P, limit_ns, BK_CODE(5, 5)) && ok;
 #pragma unroll
                 for (int q = 0; q < 4; q++) {                           // rank order: the same sum on every CTA and every rank
                     float4 &x = xres[q & 1];
@@ -423,7 +426,7 @@ __device__ __forceinline__ bool bk_prologue(const bk_params &P, const bk_phase &
                 const int sb = warp + (it + (q >> 1)) * BK_WARPS;
                 pp[q] = sb < nsb ? ph.vsrc + (size_t)sb * 256 + (q & 1) * 128 + lane * 4 : nullptr;
             }
-            ok = bk_ll_read4_n<4>(pp, seq, d, P, limit_ns, 4) && ok;
+            ok = bk_ll_read4_n<4>(pp, seq, d, P, limit_ns, BK_CODE(4, 1)) && ok;
             v[it][0] = d[0]; v[it][1] = d[1]; v[it + 1][0] = d[2]; v[it + 1][1] = d[3];
         }
         BK_PT(1);
@@ -548,7 +551,7 @@ __device__ bool bk_attention(const bk_params &P, const bk_phase &ph, uint8_t *wo
             const int jp = t & 63;
             const bk_ll *src[1] = {ph.qkv + (size_t)(t < 64 ? P.hq + kv : P.hq + P.hkv + kv) * BK_ATT_D + 2 * jp};
             float2 ab[1];
-            ok = bk_ll_read2_n<1>(src, seq_r, ab, P, limit_ns, 4) && ok;
+            ok = bk_ll_read2_n<1>(src, seq_r, ab, P, limit_ns, BK_CODE(4, 2)) && ok;
             __nv_bfloat162 o;
             if (t < 64) {
                 const float cc = cs[jp], ss = sn[jp];
@@ -570,7 +573,7 @@ __device__ bool bk_attention(const bk_params &P, const bk_phase &ph, uint8_t *wo
                 const int pi = t + 128 * u;
                 src[u] = pi < nq ? ph.qkv + (size_t)(kv * G + (pi >> 6)) * BK_ATT_D + 2 * (pi & 63) : nullptr;
             }
-            ok = bk_ll_read2_n<2>(src, seq_r, ab, P, limit_ns, 4) && ok;
+            ok = bk_ll_read2_n<2>(src, seq_r, ab, P, limit_ns, BK_CODE(4, 3)) && ok;
 #pragma unroll
             for (int u = 0; u < 2; u++) {
                 const int pi = t + 128 * u;
@@ -732,7 +735,7 @@ __device__ bool bk_attention(const bk_params &P, const bk_phase &ph, uint8_t *wo
 #define BK_XOP_BYTES (BK_MAX_NSB * Q4K_XP_SB_BYTES)
 #define BK_RED_BYTES (BK_ROUND_TASKS * 16 * 4)
 #define BK_WORK_BYTES (4 * BK_ATT_SUB_BYTES > BK_XOP_BYTES + BK_RED_BYTES ? 4 * BK_ATT_SUB_BYTES : BK_XOP_BYTES + BK_RED_BYTES)
-static_assert(sizeof(bk_pinfo) % 8 == 0, "the phase table is followed by 16-byte aligned descriptors");
+static_assert(sizeof(bk_pinfo) % 16 == 0, "the phase table is followed by 16-byte aligned descriptors");
 #define BK_PHASE_BYTES ((sizeof(bk_phase) + 15) / 16 * 16)
 #define BK_SMEM_BYTES (BK_RING_BYTES + BK_WORK_BYTES + Q4K_XP_ZERO_BYTES + BK_WARPS * BK_STAGES * 8 + 64 * 4 + BK_MAX_PHASES * sizeof(bk_pinfo) + 3 * BK_PHASE_BYTES + 128)
 
@@ -748,10 +751,9 @@ __global__ void __launch_bounds__(BK_THREADS, 1) jl_block_kernel(const __grid_co
     uint64_t *bars = reinterpret_cast<uint64_t *>(zero + Q4K_XP_ZERO_BYTES) + warp * BK_STAGES;
     float *misc = reinterpret_cast<float *>(zero + Q4K_XP_ZERO_BYTES + BK_WARPS * BK_STAGES * 8);   // 64 floats
     bk_pinfo *pinfo = reinterpret_cast<bk_pinfo *>(misc + 64);
-    // Full phase descriptors, copied from global memory one phase ahead of their use into a ring of THREE: when phase
-    // p + 1 is staged (at the start of phase p) it overwrites phase p - 2's copy, and every thread left phase p - 2
-    // before the first __syncthreads of phase p - 1, which every thread has passed by now. (Two copies would not do:
-    // nothing separates a slow warp's last look at phase p - 1 from the start of phase p.)
+    // Full phase descriptors, copied from global memory one phase ahead of their use into a ring of three; a barrier
+    // at the top of every phase (right after the copy) orders the copy against both its readers and the readers
+    // of the copy it replaces.
     uint8_t *phase_sm = reinterpret_cast<uint8_t *>(pinfo + BK_MAX_PHASES);
     auto stage_phase = [&](int q) {
         if (q < P.nphases && tid < (int)(BK_PHASE_BYTES / 16))
@@ -766,21 +768,12 @@ __global__ void __launch_bounds__(BK_THREADS, 1) jl_block_kernel(const __grid_co
         const bk_phase &q = P.phases[i];
         bk_pinfo f;
         f.kind = q.kind; f.map = q.map; f.nsb = q.nsb; f.epi = q.epilogue; f.up_row0 = q.up_row0;
-        f.rg0 = f.rg1 = 0; f.rpr = 1; f.off0 = f.xend = 0;
+        f.rg0 = f.rg1 = 0; f.rpr = 1;
         if (q.kind == BK_MATVEC) {
             const int nrg = bk_phase_nrg(q);
             f.rg0 = (int)((long long)blockIdx.x * nrg / gridDim.x);
             f.rg1 = (int)((long long)(blockIdx.x + 1) * nrg / gridDim.x);
             f.rpr = bk_rounds_rgs(q.nsb);
-            if (q.ksplit) {
-                // an even share of the tasks, in row-group-major order; one round (the host checked that it fits)
-                const long long total = (long long)nrg * q.nsb;
-                const int t0 = (int)(blockIdx.x * total / gridDim.x), t1 = (int)((blockIdx.x + 1) * total / gridDim.x);
-                f.rg0 = t0 / q.nsb; f.rg1 = (t1 + q.nsb - 1) / q.nsb;
-                f.rpr = max(1, f.rg1 - f.rg0);
-                f.off0 = t0 - f.rg0 * q.nsb; f.xend = t1 - f.rg0 * q.nsb;
-                if (t1 <= t0) { f.rg1 = f.rg0; f.xend = 0; }
-            }
         }
         pinfo[i] = f;
     }
@@ -840,7 +833,16 @@ __global__ void __launch_bounds__(BK_THREADS, 1) jl_block_kernel(const __grid_co
     for (int p = 0; p < P.nphases && alive; p++) {
         const bk_phase &ph = *reinterpret_cast<const bk_phase *>(phase_sm + (size_t)(p % 3) * BK_PHASE_BYTES);
         const int p_kind = pinfo[p].kind, p_epi = pinfo[p].epi;   // from the immutable table, not from the ring
-        stage_phase(p + 1);       // lands long before the next phase starts (at least one __syncthreads away)
+#ifdef BK_DIAG
+        if (tid == 0) bk_diag_phase[blockIdx.x] = p;
+#endif
+        stage_phase(p + 1);
+        // Every thread passes this barrier between the staging of phase p + 1's descriptor and its first use, and
+        // between its last look at phase p - 2's copy and the overwrite above. Without it a CTA that has no work
+        // item in an attention phase crosses that phase without any barrier, and a warp could read the FOLLOWING
+        // phase's descriptor before warp 0 had stored it: it then waited for the inputs of the phase that had used
+        // the slot three phases earlier (seen as a bounded-wait timeout about once in 250,000 attention phases).
+        __syncthreads();
 #ifdef BK_FINE_TRACE
         for (int i = 0; i < 7; i++) ft_acc[i] = 0;
 #endif
@@ -861,16 +863,14 @@ __global__ void __launch_bounds__(BK_THREADS, 1) jl_block_kernel(const __grid_co
             BK_TRACE(1);
             if (!alive) break;
             const int nsb = pinfo[p].nsb, rg0 = pinfo[p].rg0, rg1 = pinfo[p].rg1, rpr = pinfo[p].rpr;
-            const int ks_off0 = pinfo[p].off0, ks_xend = pinfo[p].xend;      // ksplit phases: one round, tasks [off0, xend)
             for (int rbase = rg0; rbase < rg1 && alive; rbase += rpr) {
-                const int nr = min(rpr, rg1 - rbase);
-                const int x0 = ks_xend ? ks_off0 : 0, x1 = ks_xend ? ks_xend : nr * nsb;
-                for (int x = x0 + warp; x < x1; x += BK_WARPS) {
-                    const int sb = x % nsb, tk = x - x0;
+                const int nr = min(rpr, rg1 - rbase), ntask = nr * nsb;
+                for (int tk = warp; tk < ntask; tk += BK_WARPS) {
+                    const int sb = tk % nsb;
                     const uint32_t s = consumed % BK_STAGES, parity = (consumed / BK_STAGES) & 1u;
                     BK_FT(0);
                     if (!__all_sync(0xffffffffu, bk_mbar_wait(smem_u32(bars + s), parity, limit_ns))) {
-                        if (lane == 0) { atomicExch(P.status, 1); atomicExch(P.abort_word, 1); }
+                        if (lane == 0) { atomicCAS(P.status, 0, BK_DIAG_WHERE(BK_CODE(1, 6))); atomicExch(P.abort_word, 1); }
                         alive = false;
                         break;
                     }
@@ -911,21 +911,6 @@ __global__ void __launch_bounds__(BK_THREADS, 1) jl_block_kernel(const __grid_co
                         }
                         const int o = (rbase + rgl) * 8 + r;
                         if (o < ph.nrows) bk_ll_store(ph.out + o, sg / (1.f + __expf(-sg)) * su, seq_w);     // SiLU(gate) * up
-                    }
-                } else if (ks_xend) {
-                    // the pieces of row groups this CTA computed: the piece that starts a row group goes to plane 0, the
-                    // piece that ends one (and does not start it) to plane 1; a whole row group writes 0 to plane 1
-                    if (tid < nr * 16) {
-                        const int rgl = tid >> 4, r = tid & 15;
-                        const int a = max(x0, rgl * nsb), b = min(x1, (rgl + 1) * nsb);
-                        float sum = 0.f;
-                        for (int x = a; x < b; x++) sum += red[(x - x0) * 16 + r];
-                        const int row = (rbase + rgl) * 16 + r;
-                        if (row < ph.nrows && a < b) {
-                            const bool head = a == rgl * nsb, whole = head && b == (rgl + 1) * nsb;
-                            bk_ll_store(ph.out + (head ? 0 : P.hidden) + row, sum, seq_w);
-                            if (whole) bk_ll_store(ph.out + P.hidden + row, 0.f, seq_w);
-                        }
                     }
                 } else if (tid < nr * 16) {
                     const int rgl = tid >> 4, r = tid & 15;
@@ -1035,10 +1020,7 @@ struct jl_layers {
 };
 
 static size_t bk_al(size_t n) { return (n + 255) & ~(size_t)255; }
-// Two output vectors (o, down) of `world` planes each; a single-GPU stack uses two planes per vector for the
-// row-group split (bk_phase::ksplit).
-static size_t bk_slot_planes(int world) { return world > 1 ? world : 2; }
-static size_t bk_slot_bytes(int world, int hidden) { return 2 * bk_al(bk_slot_planes(world) * hidden * sizeof(bk_ll)); }
+static size_t bk_slot_bytes(int world, int hidden) { return 2 * bk_al((size_t)world * hidden * sizeof(bk_ll)); }
 
 // PrepLayer for every block plus the head (engine/nn/device.go:1099-1102): checks that each weight has a
 // kernel here, builds the phase list and sizes all scratch. Declines (JL_DECLINED) instead of running a
@@ -1115,16 +1097,7 @@ JL_EXPORT int jl_layers_prep(jl_ctx *ctx, const jl_layers_desc *d, jl_layers **o
     }
     uint8_t *B = S->buf;
     bk_ll *qkv = (bk_ll *)(B + o_qkv), *att = (bk_ll *)(B + o_att), *abuf = (bk_ll *)(B + o_a);
-    bk_ll *planesO = (bk_ll *)S->slot, *planesD = (bk_ll *)(S->slot + bk_al(bk_slot_planes(world) * H * sizeof(bk_ll)));
-    // Single GPU: o and down have H / 16 row groups for 148 CTAs (1 or 2 each): the CTAs take even shares of the
-    // (row group, super-block) tasks instead and the consumer adds two planes. Needs at least one row group's tasks
-    // per CTA (a row group is cut at most once) and a share that fits one round.
-    auto can_split = [&](int nrows, int nsb) {
-        const long long total = (long long)((nrows + 15) / 16) * nsb;
-        return world == 1 && total / S->grid >= nsb && (total + S->grid - 1) / S->grid + 1 <= BK_ROUND_TASKS && nrows == H;
-    };
-    const bool split_o = can_split(H, hq * BK_ATT_D / 256), split_d = can_split(H, F / 256);
-    const int planes_o = split_o ? 2 : world, planes_d = split_d ? 2 : world;
+    bk_ll *planesO = (bk_ll *)S->slot, *planesD = (bk_ll *)(S->slot + bk_al((size_t)world * H * sizeof(bk_ll)));
     unsigned *tickets = (unsigned *)(B + o_bar + 16);
     S->logits = (float *)(B + o_logits);
     S->trace = (unsigned long long *)(B + o_trace);
@@ -1147,7 +1120,7 @@ JL_EXPORT int jl_layers_prep(jl_ctx *ctx, const jl_layers_desc *d, jl_layers **o
         maps[4 * l + 3] = map16(b.down);
         bk_phase q = {};
         q.kind = BK_MATVEC; q.map = 4 * l; q.nrows = (hq + 2 * hkv) * BK_ATT_D; q.nsb = H / 256; q.prologue = BK_PRO_NORM;
-        q.epilogue = BK_EPI_STORE; q.from_emb = l == 0; q.planes = planesD; q.nplanes = l == 0 ? 0 : planes_d;
+        q.epilogue = BK_EPI_STORE; q.from_emb = l == 0; q.planes = planesD; q.nplanes = l == 0 ? 0 : world;
         q.norm_w = b.attn_norm; q.out = qkv;
         S->phases[pi++] = q;
         bk_phase a = {};
@@ -1155,16 +1128,16 @@ JL_EXPORT int jl_layers_prep(jl_ctx *ctx, const jl_layers_desc *d, jl_layers **o
         S->phases[pi++] = a;
         bk_phase o = {};
         o.kind = BK_MATVEC; o.map = 4 * l + 1; o.nrows = H; o.nsb = hq * BK_ATT_D / 256; o.prologue = BK_PRO_PLAIN; o.epilogue = BK_EPI_STORE;
-        o.vsrc = att; o.out = planesO + (size_t)rank * H; o.exchange = world > 1; o.ksplit = split_o;
+        o.vsrc = att; o.out = planesO + (size_t)rank * H; o.exchange = world > 1;
         o.peer_out[rank] = o.out;
         S->phases[pi++] = o;
         bk_phase gu = {};
         gu.kind = BK_MATVEC; gu.map = 4 * l + 2; gu.nrows = F; gu.nsb = H / 256; gu.prologue = BK_PRO_NORM; gu.epilogue = BK_EPI_GATE2;
-        gu.up_row0 = F; gu.planes = planesO; gu.nplanes = planes_o; gu.norm_w = b.ffn_norm; gu.out = abuf;
+        gu.up_row0 = F; gu.planes = planesO; gu.nplanes = world; gu.norm_w = b.ffn_norm; gu.out = abuf;
         S->phases[pi++] = gu;
         bk_phase dn = {};
         dn.kind = BK_MATVEC; dn.map = 4 * l + 3; dn.nrows = H; dn.nsb = F / 256; dn.prologue = BK_PRO_PLAIN; dn.epilogue = BK_EPI_STORE;
-        dn.vsrc = abuf; dn.out = planesD + (size_t)rank * H; dn.exchange = world > 1; dn.ksplit = split_d;
+        dn.vsrc = abuf; dn.out = planesD + (size_t)rank * H; dn.exchange = world > 1;
         dn.peer_out[rank] = dn.out;
         S->phases[pi++] = dn;
     }
@@ -1172,7 +1145,7 @@ JL_EXPORT int jl_layers_prep(jl_ctx *ctx, const jl_layers_desc *d, jl_layers **o
         maps[4 * L] = map16(d->head);
         bk_phase h = {};
         h.kind = BK_MATVEC; h.map = 4 * L; h.nrows = V; h.nsb = H / 256; h.prologue = BK_PRO_NORM; h.epilogue = BK_EPI_ARGMAX;
-        h.planes = planesD; h.nplanes = planes_d; h.norm_w = d->final_norm; h.out_f32 = S->logits;
+        h.planes = planesD; h.nplanes = world; h.norm_w = d->final_norm; h.out_f32 = S->logits;
         S->phases[pi++] = h;
         bk_phase f = {};
         f.kind = BK_FINAL;

@@ -130,8 +130,9 @@ __global__ void __launch_bounds__(256) gemv_simt_kernel(const uint8_t *__restric
 //                144 B x 16 rows) into a per-warp shared-memory ring; the first STAGES
 //                tasks of every warp are requested in the kernel's first instructions,
 //                before it waits for its predecessor in the stream.
-//   A operand    the 4-bit codes as unsigned bytes: (w & 0x0F0F0F0F) and
-//                ((w >> 4) & 0x0F0F0F0F), three ALU ops per eight weights.
+//   A operand    the 4-bit codes as unsigned bytes: (w & 0x0F0F0F0F) and, for the odd sub-block,
+//                (w & 0xF0F0F0F0) = 16 x the code, divided out of the integer sum afterwards (exact):
+//                two ALU ops per eight weights.
 //   activations  made once per matvec by q4k_xprep_kernel: per super-block a scale
 //                s = 32512 / amax and two int8 digits, x*s ~ 256 q1 + q2 (|err| <= 0.5,
 //                i.e. 1.5e-5 of the super-block's amax), already laid out as MMA B
@@ -289,14 +290,14 @@ gemv_q4k_tma_kernel(const __grid_constant__ CUtensorMap wmap, int row0, const vo
         const uint32_t wa[8] = {qA0.x, qA0.y, qA0.z, qA0.w, qA1.x, qA1.y, qA1.z, qA1.w};
         const uint32_t wb[8] = {qB0.x, qB0.y, qB0.z, qB0.w, qB1.x, qB1.y, qB1.z, qB1.w};
         int ce[4] = {0, 0, 0, 0}, co[4] = {0, 0, 0, 0};
-        const uint32_t m4 = 0x0F0F0F0Fu;
+        const uint32_t m4 = 0x0F0F0F0Fu, h4 = 0xF0F0F0F0u;
 #pragma unroll
         for (int cp = 0; cp < 4; cp++) {
             const uint2 fe = XG ? xfe[cp] : *reinterpret_cast<const uint2 *>(xf + cp * 16);
             const uint2 fo = XG ? xfo[cp] : *reinterpret_cast<const uint2 *>(xf + 64 + cp * 16);
             const uint32_t a0 = wa[2 * cp], a2 = wa[2 * cp + 1], a1 = wb[2 * cp], a3 = wb[2 * cp + 1];
             mma_u8s8(ce, a0 & m4, a1 & m4, a2 & m4, a3 & m4, fe.x, fe.y);
-            mma_u8s8(co, (a0 >> 4) & m4, (a1 >> 4) & m4, (a2 >> 4) & m4, (a3 >> 4) & m4, fo.x, fo.y);
+            mma_u8s8(co, a0 & h4, a1 & h4, a2 & h4, a3 & h4, fo.x, fo.y);   // the high nibbles in place: 16 x the code
         }
 
         // sub-blocks e = 2t and o = 2t+1 (format/quant/dequant.go:360-365):
@@ -311,7 +312,7 @@ gemv_q4k_tma_kernel(const __grid_constant__ CUtensorMap wmap, int row0, const vo
             if (t < 2) { scp = a & 0x3F3Fu; mp = b & 0x3F3Fu; }
             else { scp = (c & 0x0F0Fu) | ((a >> 2) & 0x3030u); mp = ((c >> 4) & 0x0F0Fu) | ((b >> 2) & 0x3030u); }
             const int pe = (ce[2 * r] << 8) + ce[2 * r + 1];   // sum q (256 q1 + q2), sub-block e
-            const int po = (co[2 * r] << 8) + co[2 * r + 1];
+            const int po = ((co[2 * r] << 8) + co[2 * r + 1]) >> 4;   // the odd sub-block's codes entered as 16 q: exact
             const int dotq = (int)(scp & 0xFF) * pe + (int)(scp >> 8) * po;      // < 2^31: 2 * 63 * 15 * 32 * 32639
             const int dotm = (int)(mp & 0xFF) * ax.x + (int)(mp >> 8) * ax.y;
             const float2 dd = __half22float2(*reinterpret_cast<const __half2 *>(&h.x));

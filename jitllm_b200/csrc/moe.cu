@@ -192,6 +192,7 @@ moe_combine_kernel(float *__restrict__ out, const float *__restrict__ y, const i
 // ------------------------------------------------------------ grouped GEMM
 
 #define MOE_PF 4   // k-blocks of raw codes a dequant thread keeps in flight
+#define MOE_KH 2   // 64-wide k-blocks per shared-memory stage
 struct moe_gemm_params {
     int mode;                    // 0: gate|up -> act(g, u);  1: down
     int n_expert, rows, k;       // rows, k of ONE expert matrix (mode 0: ffn x hidden; mode 1: hidden x ffn)
@@ -242,9 +243,13 @@ template <int NT, int SA, int SB>
 struct moe_smem {
     static constexpr int ACC_COLS = TC5_MS * NT;
     static constexpr int ACC_BUFS = ACC_COLS * 2 <= 512 ? 2 : 1;
-    static constexpr int B_BYTES = NT * TC5_KB * 2;
+    // A stage holds MOE_KH 64-wide halves of k (each a 128-byte swizzle atom wide): one barrier handshake per 128 k
+    static constexpr int BH_BYTES = NT * TC5_KB * 2;            // one half of an activation stage
+    static constexpr int B_BYTES = MOE_KH * BH_BYTES;
+    static constexpr int AH_BYTES = TC5_MS * TC5_A_BYTES;       // one half of a weight stage
+    static constexpr int A_BYTES = MOE_KH * AH_BYTES;
     static constexpr int A_OFS = 0;
-    static constexpr int B_OFS = SA * TC5_MS * TC5_A_BYTES;
+    static constexpr int B_OFS = SA * A_BYTES;
     static constexpr int BAR_OFS = B_OFS + SB * B_BYTES;
     static constexpr int NBARS = 2 * SA + 2 * SB + 4;
     static constexpr int MISC_OFS = BAR_OFS + NBARS * 8;
@@ -267,7 +272,8 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap xmap, const moe_gemm_params 
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + L::MISC_OFS);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L::MISC_OFS + 4);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int nkb = p.k / TC5_KB;
+    const int n64 = p.k / TC5_KB;                       // 64-wide k-blocks of a row
+    const int nkb = (n64 + MOE_KH - 1) / MOE_KH;        // stages (the last one may hold a single half)
     const int nunits = p.n_expert * p.row_tiles * p.max_tok_tiles;
     const int mult = p.split ? 2 : 1;
 
@@ -307,8 +313,11 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap xmap, const moe_gemm_params 
                     const uint32_t s = kb_it % SB, ph = (kb_it / SB) & 1;
                     if (kb_it >= (uint32_t)SB) ok = tc5_wait(smem_u32(b_empty + s), ph ^ 1, abort_flag);
                     if (!ok) break;
-                    mbar_arrive_expect_tx(smem_u32(b_full + s), L::B_BYTES);
-                    tma_load_2d(sbase + L::B_OFS + s * L::B_BYTES, &xmap, kb * TC5_KB, col0, smem_u32(b_full + s));
+                    mbar_arrive_expect_tx(smem_u32(b_full + s), L::B_BYTES);      // a half beyond k arrives as zeros
+#pragma unroll
+                    for (int h = 0; h < MOE_KH; h++)
+                        tma_load_2d(sbase + L::B_OFS + s * L::B_BYTES + h * L::BH_BYTES, &xmap, (kb * MOE_KH + h) * TC5_KB, col0,
+                                    smem_u32(b_full + s));
                 }
             }
         }
@@ -330,13 +339,17 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap xmap, const moe_gemm_params 
                     ok = tc5_wait(smem_u32(a_full + sa), pha, abort_flag) && tc5_wait(smem_u32(b_full + s), ph, abort_flag);
                     if (!ok) break;
                     tc5_fence_after();
-                    const uint64_t bdesc = tc5_smem_desc(sbase + L::B_OFS + s * L::B_BYTES);
 #pragma unroll
-                    for (int ms = 0; ms < TC5_MS; ms++) {
-                        const uint64_t adesc = tc5_smem_desc(sbase + L::A_OFS + (sa * TC5_MS + ms) * TC5_A_BYTES);
+                    for (int h = 0; h < MOE_KH; h++) {
+                        if (kb * MOE_KH + h >= n64) break;
+                        const uint64_t bdesc = tc5_smem_desc(sbase + L::B_OFS + s * L::B_BYTES + h * L::BH_BYTES);
 #pragma unroll
-                        for (int j = 0; j < TC5_KB / 16; j++)
-                            tc5_mma_f16(d_tmem + ms * NT, adesc + 2 * j, bdesc + 2 * j, idesc, (kb | j) != 0);
+                        for (int ms = 0; ms < TC5_MS; ms++) {
+                            const uint64_t adesc = tc5_smem_desc(sbase + L::A_OFS + sa * L::A_BYTES + h * L::AH_BYTES + ms * TC5_A_BYTES);
+#pragma unroll
+                            for (int j = 0; j < TC5_KB / 16; j++)
+                                tc5_mma_f16(d_tmem + ms * NT, adesc + 2 * j, bdesc + 2 * j, idesc, (kb | h | j) != 0);
+                        }
                     }
                     tc5_commit(smem_u32(a_empty + sa));
                     tc5_commit(smem_u32(b_empty + s));
@@ -370,28 +383,30 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap xmap, const moe_gemm_params 
 #pragma unroll
             for (int j = 0; j < MOE_PF; j++) {
                 q[2 * j] = q[2 * j + 1] = make_uint4(0, 0, 0, 0); ec[j] = 0x7F7F;
-                if (j < nkb) {
+                if (j < n64) {
                     q[2 * j] = ldg_nc16(codes + (size_t)j * 32);
                     q[2 * j + 1] = ldg_nc16(codes + (size_t)j * 32 + 16);
                     ec[j] = *reinterpret_cast<const uint16_t *>(ebytes + 2 * j);
                 }
             }
-            for (int kb0 = 0; kb0 < nkb && ok; kb0 += MOE_PF) {
+            static_assert(MOE_PF % MOE_KH == 0, "a stage's halves are consecutive slots of the prefetch ring");
+            for (int kb0 = 0; kb0 < n64 && ok; kb0 += MOE_PF) {
 #pragma unroll
               for (int j = 0; j < MOE_PF; j++) {
-                const int kb = kb0 + j;
-                if (kb >= nkb) break;
+                const int kb = kb0 + j;                 // 64-wide k-block; half j % MOE_KH of stage kb / MOE_KH
+                if (kb >= n64) break;
+                const int half = j % MOE_KH;
                 const uint32_t s = kb_it % SA, ph = (kb_it / SA) & 1;
                 const uint4 c0 = q[2 * j], c1 = q[2 * j + 1];
                 const uint32_t e_lo = ec[j] & 0xFF, e_hi = ec[j] >> 8;
-                if (kb + MOE_PF < nkb) {
+                if (kb + MOE_PF < n64) {
                     q[2 * j] = ldg_nc16(codes + (size_t)(kb + MOE_PF) * 32);
                     q[2 * j + 1] = ldg_nc16(codes + (size_t)(kb + MOE_PF) * 32 + 16);
                     ec[j] = *reinterpret_cast<const uint16_t *>(ebytes + 2 * (kb + MOE_PF));
                 }
-                if (kb_it >= (uint32_t)SA) ok = tc5_wait(smem_u32(a_empty + s), ph ^ 1, abort_flag);
+                if (half == 0 && kb_it >= (uint32_t)SA) ok = tc5_wait(smem_u32(a_empty + s), ph ^ 1, abort_flag);
                 if (!ok) break;
-                uint8_t *arow = smem + L::A_OFS + s * TC5_MS * TC5_A_BYTES + a_row_ofs;
+                uint8_t *arow = smem + L::A_OFS + s * L::A_BYTES + half * L::AH_BYTES + a_row_ofs;
 #pragma unroll
                 for (int b = 0; b < 2; b++) {           // block b of the k-block: k 32b..32b+31
                     const uint4 cw = b ? c1 : c0;
@@ -432,10 +447,12 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap xmap, const moe_gemm_params 
                     *reinterpret_cast<uint4 *>(arow + (((uint32_t)(4 * b + 2) ^ swz) << 4)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
                     *reinterpret_cast<uint4 *>(arow + (((uint32_t)(4 * b + 3) ^ swz) << 4)) = make_uint4(hi[4], hi[5], hi[6], hi[7]);
                 }
-                fence_async_smem();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(a_full + s));
-                kb_it++;
+                if (half == MOE_KH - 1 || kb == n64 - 1) {     // the stage is complete (the last one may be short)
+                    fence_async_smem();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(a_full + s));
+                    kb_it++;
+                }
               }
             }
         }
@@ -550,7 +567,7 @@ static int moe_grouped(jl_ctx *ctx, moe_gemm_params p, const __half *xs, int nto
         return jl_set_err(ctx, JL_DECLINED, "the driver refused a tensor map for the mixture's activations");
     // shallow rings: shared memory not taken is L1 for the dequant warps' raw-weight loads (5-deep A rings: 576 us
     // per layer against 348 us)
-    return p.split ? moe_launch<128, 2, 3>(ctx, xmap, p, s, nattr, at) : moe_launch<64, 2, 4>(ctx, xmap, p, s, nattr, at);
+    return p.split ? moe_launch<128, 2, 2>(ctx, xmap, p, s, nattr, at) : moe_launch<64, 2, 3>(ctx, xmap, p, s, nattr, at);
 }
 
 // The block-scaled arm's grouped GEMM over the sorted e4m3 activation rows `xq` ([npairs][k] bytes).

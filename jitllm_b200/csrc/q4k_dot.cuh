@@ -46,14 +46,14 @@ __device__ __forceinline__ void q4k_dot_task(const q4k_lane_tile &w, const uint8
     const uint32_t wa[8] = {w.qA0.x, w.qA0.y, w.qA0.z, w.qA0.w, w.qA1.x, w.qA1.y, w.qA1.z, w.qA1.w};
     const uint32_t wb[8] = {w.qB0.x, w.qB0.y, w.qB0.z, w.qB0.w, w.qB1.x, w.qB1.y, w.qB1.z, w.qB1.w};
     int ce[4] = {0, 0, 0, 0}, co[4] = {0, 0, 0, 0};
-    const uint32_t m4 = 0x0F0F0F0Fu;
+    const uint32_t m4 = 0x0F0F0F0Fu, h4 = 0xF0F0F0F0u;
 #pragma unroll
     for (int cp = 0; cp < 4; cp++) {
         const uint2 fe = *reinterpret_cast<const uint2 *>(xf + cp * 16);
         const uint2 fo = *reinterpret_cast<const uint2 *>(xf + 64 + cp * 16);
         const uint32_t a0 = wa[2 * cp], a2 = wa[2 * cp + 1], a1 = wb[2 * cp], a3 = wb[2 * cp + 1];
         q4k_dot_mma(ce, a0 & m4, a1 & m4, a2 & m4, a3 & m4, fe.x, fe.y);
-        q4k_dot_mma(co, (a0 >> 4) & m4, (a1 >> 4) & m4, (a2 >> 4) & m4, (a3 >> 4) & m4, fo.x, fo.y);
+        q4k_dot_mma(co, a0 & h4, a1 & h4, a2 & h4, a3 & h4, fo.x, fo.y);   // the high nibbles in place: 16 x the code
     }
     const float inv_scale = __int_as_float(ax.z);
 #pragma unroll
@@ -64,7 +64,7 @@ __device__ __forceinline__ void q4k_dot_task(const q4k_lane_tile &w, const uint8
         if (t < 2) { scp = a & 0x3F3Fu; mp = b & 0x3F3Fu; }
         else { scp = (c & 0x0F0Fu) | ((a >> 2) & 0x3030u); mp = ((c >> 4) & 0x0F0Fu) | ((b >> 2) & 0x3030u); }
         const int pe = (ce[2 * r] << 8) + ce[2 * r + 1];   // sum q (256 q1 + q2), sub-block 2t
-        const int po = (co[2 * r] << 8) + co[2 * r + 1];   // sub-block 2t + 1
+        const int po = ((co[2 * r] << 8) + co[2 * r + 1]) >> 4;   // sub-block 2t + 1, whose codes entered as 16 q: exact
         const int dotq = (int)(scp & 0xFF) * pe + (int)(scp >> 8) * po;
         const int dotm = (int)(mp & 0xFF) * ax.x + (int)(mp >> 8) * ax.y;
         const float2 dd = __half22float2(*reinterpret_cast<const __half2 *>(&h.x));
