@@ -399,11 +399,6 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap xmap, const moe_gemm_params 
                 const uint32_t s = kb_it % SA, ph = (kb_it / SA) & 1;
                 const uint4 c0 = q[2 * j], c1 = q[2 * j + 1];
                 const uint32_t e_lo = ec[j] & 0xFF, e_hi = ec[j] >> 8;
-                if (kb + MOE_PF < n64) {
-                    q[2 * j] = ldg_nc16(codes + (size_t)(kb + MOE_PF) * 32);
-                    q[2 * j + 1] = ldg_nc16(codes + (size_t)(kb + MOE_PF) * 32 + 16);
-                    ec[j] = *reinterpret_cast<const uint16_t *>(ebytes + 2 * (kb + MOE_PF));
-                }
                 if (half == 0 && kb_it >= (uint32_t)SA) ok = tc5_wait(smem_u32(a_empty + s), ph ^ 1, abort_flag);
                 if (!ok) break;
                 uint8_t *arow = smem + L::A_OFS + s * L::A_BYTES + half * L::AH_BYTES + a_row_ofs;
@@ -452,6 +447,13 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap xmap, const moe_gemm_params 
                     __syncwarp();
                     if (lane == 0) mbar_arrive(smem_u32(a_full + s));
                     kb_it++;
+                }
+                // The slot is refilled AFTER the fence: a proxy fence waits for the thread's loads in flight, so a
+                // prefetch issued in front of it put a DRAM round trip into every stage.
+                if (kb + MOE_PF < n64) {
+                    q[2 * j] = ldg_nc16(codes + (size_t)(kb + MOE_PF) * 32);
+                    q[2 * j + 1] = ldg_nc16(codes + (size_t)(kb + MOE_PF) * 32 + 16);
+                    ec[j] = *reinterpret_cast<const uint16_t *>(ebytes + 2 * (kb + MOE_PF));
                 }
               }
             }

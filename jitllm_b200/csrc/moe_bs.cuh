@@ -340,10 +340,6 @@ moe_gemm_bs_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
 #pragma unroll
                     for (int b = 0; b < 4; b++) c[b] = q[j][b];
                     const uint32_t sf_cur = sfw[j], sfb_cur = sfbw[j];
-                    if (kb + BS_PF < nkb) {
-                        load_stage(kb + BS_PF, q[j], sfw[j]);
-                        if (r < NT) sfbw[j] = __ldg(sfb_row + kb + BS_PF);
-                    }
                     if (kb_it >= (uint32_t)SA) ok = tc5_wait(smem_u32(a_empty + s), ph ^ 1, abort_flag);
                     if (!ok) break;
                     if (!TMAA) {
@@ -360,6 +356,11 @@ moe_gemm_bs_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
                     __syncwarp();
                     if (lane == 0) mbar_arrive(smem_u32(a_full + s));
                     kb_it++;
+                    // refilled AFTER the fence: a proxy fence waits for the thread's loads in flight
+                    if (kb + BS_PF < nkb) {
+                        load_stage(kb + BS_PF, q[j], sfw[j]);
+                        if (r < NT) sfbw[j] = __ldg(sfb_row + kb + BS_PF);
+                    }
                 }
             }
         }
