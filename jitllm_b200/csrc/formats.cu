@@ -122,6 +122,7 @@ __global__ void repack_mxfp4_kernel(const uint8_t *__restrict__ raw, uint8_t *__
 
 void jl_weight_release(jl_weight *w) {
     if (!w) return;
+    if (w->zc_exec) cudaGraphExecDestroy((cudaGraphExec_t)w->zc_exec);
     if (w->data) cudaFree(w->data);
     if (w->scales) cudaFree(w->scales);
     delete w;

@@ -79,6 +79,11 @@ struct jl_weight {
     alignas(64) CUtensorMap map_sb16;
     bool has_map_sb16;
     int emin, emax;         // MXFP4: smallest / largest e8m0 byte of a block that is not all zeros
+    // the host-pointer decode call's launches for this weight as an instantiated graph, with what it baked in
+    void *zc_exec;          // cudaGraphExec_t or NULL
+    void *zc_scratch, *zc_x, *zc_o;
+    int zc_ntok, zc_form, zc_launches;
+    uint32_t zc_flags;
 };
 
 struct jl_ctx {
