@@ -118,6 +118,163 @@ __global__ void __launch_bounds__(256) gemv_simt_kernel(const uint8_t *__restric
     if (lane == 0) Y[(size_t)tok * nrows + row] = acc;
 }
 
+// Q6_K decode without a byte loop: one warp per row, two super-blocks per pass. A super-block is two halves of 128
+// elements; in a half, byte l of ql / ql + 32 / qh carries elements l, l + 32, l + 64, l + 96 (low nibbles, low
+// nibbles of the second run, high nibbles, high nibbles; two bits of qh each). Eight lanes take a half, lane i of them
+// the four positions l = 4i .. 4i + 3: three 32-bit words (read as 16-bit halves: a 210-byte block is only 2-byte
+// aligned) give it 16 codes, which become floats by byte placement (0x4B0000qq reads as 2^23 + q), and its four
+// float4 of the activation row. Each weight is formed as quant.Dequant32 forms it: (d * sc) rounded, times (q - 32)
+// rounded (format/quant/dequant.go:443-470). NT tokens share the decoded weights.
+__device__ __forceinline__ uint32_t q6k_ld32(const uint8_t *p) {
+    const uint16_t *h = reinterpret_cast<const uint16_t *>(p);
+    return (uint32_t)__ldg(h) | ((uint32_t)__ldg(h + 1) << 16);
+}
+template <int NT>
+__global__ void __launch_bounds__(256) gemv_q6k_kernel(const uint8_t *__restrict__ data, const float *__restrict__ X,
+                                                       float *__restrict__ Y, int nrows, int k, int ntok) {
+    const int row = (int)((blockIdx.x * (size_t)blockDim.x + threadIdx.x) >> 5), lane = threadIdx.x & 31;
+    const int tok0 = blockIdx.y * NT;
+    if (row >= nrows) return;
+    const int nsb = k / 256;
+    const int hl = lane >> 3, i = lane & 7;            // half hl of the pass's two super-blocks, positions 4i..4i+3
+    const int n = hl & 1;
+    const uint8_t *rowp = data + (size_t)row * nsb * 210;
+    float acc[NT];
+#pragma unroll
+    for (int t = 0; t < NT; t++) acc[t] = 0.f;
+    for (int sb = hl >> 1; sb < nsb; sb += 2) {
+        const uint8_t *blk = rowp + (size_t)sb * 210;
+        const uint32_t A = q6k_ld32(blk + n * 64 + 4 * i), B = q6k_ld32(blk + n * 64 + 32 + 4 * i);
+        const uint32_t H = q6k_ld32(blk + 128 + n * 32 + 4 * i);
+        const float d = __half2float(__ushort_as_half(__ldg(reinterpret_cast<const uint16_t *>(blk + 208))));
+        const int8_t *scp = reinterpret_cast<const int8_t *>(blk + 192 + n * 8 + (i >> 2));
+        // the four 32-runs of the half: codes of positions 4i..4i+3, one byte each
+        const uint32_t c4[4] = {(A & 0x0F0F0F0Fu) | ((H & 0x03030303u) << 4), (B & 0x0F0F0F0Fu) | ((H & 0x0C0C0C0Cu) << 2),
+                                ((A >> 4) & 0x0F0F0F0Fu) | (H & 0x30303030u), ((B >> 4) & 0x0F0F0F0Fu) | ((H & 0xC0C0C0C0u) >> 2)};
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+            const float dsc = __fmul_rn(d, (float)(int)__ldg(scp + 2 * c));
+            float w[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++)   // 0x4B0000qq = 2^23 + q; minus (2^23 + 32) = q - 32, exact
+                w[j] = __fmul_rn(dsc, __uint_as_float(__byte_perm(c4[c], 0x4B000000u, 0x7650 + j)) - 8388640.f);
+            const size_t e0 = (size_t)sb * 256 + n * 128 + c * 32 + 4 * i;
+#pragma unroll
+            for (int t = 0; t < NT; t++) {
+                if (tok0 + t < ntok) {
+                    const float4 x = __ldg(reinterpret_cast<const float4 *>(X + (size_t)(tok0 + t) * k + e0));
+                    acc[t] = fmaf(w[0], x.x, acc[t]); acc[t] = fmaf(w[1], x.y, acc[t]);
+                    acc[t] = fmaf(w[2], x.z, acc[t]); acc[t] = fmaf(w[3], x.w, acc[t]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int t = 0; t < NT; t++) {
+        const float v = warp_sum(acc[t]);
+        if (lane == 0 && tok0 + t < ntok) Y[(size_t)(tok0 + t) * nrows + row] = v;
+    }
+}
+
+// Q5_K the same way: lane l takes position l of each of the super-block's eight sub-blocks (five coalesced byte loads
+// per super-block: qh[l] and the four code bytes that carry position l), every weight formed as quant.Dequant32 forms
+// it, (d sc) q - (dmin m) with each product and the difference rounded (format/quant/dequant.go:399-441).
+template <int NT>
+__global__ void __launch_bounds__(256) gemv_q5k_kernel(const uint8_t *__restrict__ data, const float *__restrict__ X,
+                                                       float *__restrict__ Y, int nrows, int k, int ntok) {
+    const int row = (int)((blockIdx.x * (size_t)blockDim.x + threadIdx.x) >> 5), lane = threadIdx.x & 31;
+    const int tok0 = blockIdx.y * NT;
+    if (row >= nrows) return;
+    const int nsb = k / 256;
+    const uint8_t *rowp = data + (size_t)row * nsb * 176;
+    float acc[NT];
+#pragma unroll
+    for (int t = 0; t < NT; t++) acc[t] = 0.f;
+    for (int sb = 0; sb < nsb; sb++) {
+        const uint8_t *blk = rowp + (size_t)sb * 176;
+        const float d = __half2float(__ushort_as_half(__ldg(reinterpret_cast<const uint16_t *>(blk))));
+        const float dmin = __half2float(__ushort_as_half(__ldg(reinterpret_cast<const uint16_t *>(blk + 2))));
+        const uint32_t qh = __ldg(blk + 16 + lane);
+        uint32_t qs[4];
+#pragma unroll
+        for (int g = 0; g < 4; g++) qs[g] = __ldg(blk + 48 + g * 32 + lane);
+#pragma unroll
+        for (int sub = 0; sub < 8; sub++) {
+            uint8_t sc, m;
+            jl_raw_scale_min_k4(sub, blk + 4, &sc, &m);
+            const float dsc = __fmul_rn(d, (float)sc), dm = __fmul_rn(dmin, (float)m);
+            const uint32_t b = qs[sub >> 1];
+            const int q = (int)((sub & 1) ? (b >> 4) : (b & 0xF)) + (int)(((qh >> sub) & 1u) << 4);
+            const float w = __fsub_rn(__fmul_rn(dsc, (float)q), dm);
+            const size_t e = (size_t)sb * 256 + sub * 32 + lane;
+#pragma unroll
+            for (int t = 0; t < NT; t++)
+                if (tok0 + t < ntok) acc[t] = fmaf(w, __ldg(X + (size_t)(tok0 + t) * k + e), acc[t]);
+        }
+    }
+#pragma unroll
+    for (int t = 0; t < NT; t++) {
+        const float v = warp_sum(acc[t]);
+        if (lane == 0 && tok0 + t < ntok) Y[(size_t)(tok0 + t) * nrows + row] = v;
+    }
+}
+
+// Q4_0 / Q5_0 / Q5_1 (32-element blocks of 18 / 22 / 24 bytes, 2-byte aligned): a lane takes a whole block per pass --
+// its scale(s), the 16 code bytes as 16-bit loads, Q5's 32 high bits -- and the 32 activations that go with it.
+// Weights as quant.Dequant32 forms them: (q - 8) d, (q - 16) d, and q d + m as one fused multiply-add
+// (format/quant/dequant.go:85-146).
+template <uint32_t TYPE, int NT>
+__global__ void __launch_bounds__(256) gemv_q45_kernel(const uint8_t *__restrict__ data, const float *__restrict__ X,
+                                                       float *__restrict__ Y, int nrows, int k, int ntok) {
+    constexpr int BB = TYPE == JL_TYPE_Q4_0 ? 18 : (TYPE == JL_TYPE_Q5_0 ? 22 : 24);
+    constexpr int QOFS = TYPE == JL_TYPE_Q4_0 ? 2 : (TYPE == JL_TYPE_Q5_0 ? 6 : 8);
+    const int row = (int)((blockIdx.x * (size_t)blockDim.x + threadIdx.x) >> 5), lane = threadIdx.x & 31;
+    const int tok0 = blockIdx.y * NT;
+    if (row >= nrows) return;
+    const int nblk = k / 32;
+    const uint8_t *rowp = data + (size_t)row * nblk * BB;
+    float acc[NT];
+#pragma unroll
+    for (int t = 0; t < NT; t++) acc[t] = 0.f;
+    for (int b = lane; b < nblk; b += 32) {
+        const uint16_t *h = reinterpret_cast<const uint16_t *>(rowp + (size_t)b * BB);
+        const float d = __half2float(__ushort_as_half(__ldg(h)));
+        const float m = TYPE == JL_TYPE_Q5_1 ? __half2float(__ushort_as_half(__ldg(h + 1))) : 0.f;
+        uint32_t qh = 0;
+        if (TYPE != JL_TYPE_Q4_0) qh = (uint32_t)__ldg(h + QOFS / 2 - 2) | ((uint32_t)__ldg(h + QOFS / 2 - 1) << 16);
+        uint32_t qs[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) qs[i] = (uint32_t)__ldg(h + QOFS / 2 + 2 * i) | ((uint32_t)__ldg(h + QOFS / 2 + 2 * i + 1) << 16);
+        float w[32];
+#pragma unroll
+        for (int j = 0; j < 16; j++) {
+            const uint32_t byte = (qs[j >> 2] >> (8 * (j & 3))) & 0xFFu;
+            int lo = (int)(byte & 0xF), hi = (int)(byte >> 4);
+            if (TYPE != JL_TYPE_Q4_0) { lo |= (int)((qh >> j) & 1u) << 4; hi |= (int)((qh >> (j + 16)) & 1u) << 4; }
+            if (TYPE == JL_TYPE_Q4_0) { w[j] = __fmul_rn((float)(lo - 8), d); w[j + 16] = __fmul_rn((float)(hi - 8), d); }
+            else if (TYPE == JL_TYPE_Q5_0) { w[j] = __fmul_rn((float)(lo - 16), d); w[j + 16] = __fmul_rn((float)(hi - 16), d); }
+            else { w[j] = fmaf((float)lo, d, m); w[j + 16] = fmaf((float)hi, d, m); }
+        }
+#pragma unroll
+        for (int t = 0; t < NT; t++) {
+            if (tok0 + t < ntok) {
+                const float4 *x4 = reinterpret_cast<const float4 *>(X + (size_t)(tok0 + t) * k + (size_t)b * 32);
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const float4 x = __ldg(x4 + i);
+                    acc[t] = fmaf(w[4 * i], x.x, acc[t]); acc[t] = fmaf(w[4 * i + 1], x.y, acc[t]);
+                    acc[t] = fmaf(w[4 * i + 2], x.z, acc[t]); acc[t] = fmaf(w[4 * i + 3], x.w, acc[t]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int t = 0; t < NT; t++) {
+        const float v = warp_sum(acc[t]);
+        if (lane == 0 && tok0 + t < ntok) Y[(size_t)(tok0 + t) * nrows + row] = v;
+    }
+}
+
 // ---------------------------------------------------------------- MMA family
 //
 // Q4_K decode on the tensor cores, one token.
@@ -589,7 +746,20 @@ int jl_launch_gemv(jl_ctx *ctx, float *out_dev, const jl_weight *w, int expert, 
                                         ctx->dev_status));
     } else {
         dim3 grid((nrows + 7) / 8, ntok);
-        if (w->type == JL_TYPE_Q4_K)
+        const dim3 g1((nrows + 7) / 8, 1), g4((nrows + 7) / 8, (ntok + 3) / 4);
+#define JL_ROWK(KERNEL) do { if (ntok == 1) KERNEL<1><<<g1, 256, 0, s>>>(data, x_dev, out_dev, nrows, k, ntok); \
+                             else KERNEL<4><<<g4, 256, 0, s>>>(data, x_dev, out_dev, nrows, k, ntok); } while (0)
+#define JL_ROWK45(T) do { if (ntok == 1) gemv_q45_kernel<T, 1><<<g1, 256, 0, s>>>(data, x_dev, out_dev, nrows, k, ntok); \
+                           else gemv_q45_kernel<T, 4><<<g4, 256, 0, s>>>(data, x_dev, out_dev, nrows, k, ntok); } while (0)
+        // the raw formats' own row kernels (a lane takes many codes at a time; up to four tokens share the decoded weights)
+        if (w->type == JL_TYPE_Q6_K) JL_ROWK(gemv_q6k_kernel);
+        else if (w->type == JL_TYPE_Q5_K) JL_ROWK(gemv_q5k_kernel);
+        else if (w->type == JL_TYPE_Q4_0) JL_ROWK45(JL_TYPE_Q4_0);
+        else if (w->type == JL_TYPE_Q5_0) JL_ROWK45(JL_TYPE_Q5_0);
+        else if (w->type == JL_TYPE_Q5_1) JL_ROWK45(JL_TYPE_Q5_1);
+#undef JL_ROWK
+#undef JL_ROWK45
+        else if (w->type == JL_TYPE_Q4_K)
             gemv_simt_kernel<JL_TYPE_Q4_K><<<grid, 256, 0, s>>>(data, scales, w->scale_stride, x_dev, out_dev, nrows, k, ntok);
         else if (w->type == JL_TYPE_Q8_0)
             gemv_simt_kernel<JL_TYPE_Q8_0><<<grid, 256, 0, s>>>(data, scales, w->scale_stride, x_dev, out_dev, nrows, k, ntok);
