@@ -347,14 +347,19 @@ def run_ours(args, name):
         d.Close()
     del outs, x_dev
     torch.cuda.empty_cache()
+    exit_code = 0
     if not args.no_also:
-        line.update(also_block(args, world, rank, local))
+        extra = also_block(args, world, rank, local)
+        exit_code = extra.pop("_exit", 0)
+        line.update(extra)
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
         sys.stdout.flush()
-        os._exit(0)      # a process group whose collectives were captured in a graph can stall in its destructor
+        os._exit(exit_code)      # a process group whose collectives were captured in a graph can stall in its destructor
+    if exit_code:
+        sys.exit(exit_code)
 
 
 def _brief(line):
@@ -379,19 +384,31 @@ def also_block(args, world, rank, local):
         par = bw.sharded_parity(local)
         out["sharded_parity"] = par
         if not (par["tp_err"] <= par["bar"] and par["ep_err"] <= par["bar"]):
-            if rank == 0:
-                print(json.dumps({"error": "sharded parity above the bar", **par}), flush=True)
-            sys.stdout.flush()
-            os._exit(3)
+            # the run fails (exit 3), but the headline line is still printed, with the failed check in it
+            par["failed"] = True
+            out["_exit"] = 3
+            return out
     a = copy.copy(args)
     a.steps, a.warmup = max(args.steps, 20), max(args.warmup, 3)
     also = {}
+
+    def guarded(name, fn):
+        """One workload of the block. On one GPU an error in it is recorded in its place and the others still run (the
+        headline line must not be lost to a side measurement); under torchrun it propagates, since the other ranks
+        would wait in the workload's next collective."""
+        try:
+            return fn()
+        except Exception as e:  # noqa: BLE001
+            if world > 1:
+                raise
+            also[name + "_error"] = f"{type(e).__name__}: {e}"
+            return None
     if world == 1:
-        also["q4k_gemm_prefill"] = _brief(bw.run_gemm(a, emit=False))
-    also["q8_0_batch32"] = _brief(bw.run_q8_batch(a, emit=False))
-    also["mxfp4_moe_gptoss"] = _brief(bw.run_moe(a, emit=False))
+        also["q4k_gemm_prefill"] = _brief(guarded("q4k_gemm_prefill", lambda: bw.run_gemm(a, emit=False)))
+    also["q8_0_batch32"] = _brief(guarded("q8_0_batch32", lambda: bw.run_q8_batch(a, emit=False)))
+    also["mxfp4_moe_gptoss"] = _brief(guarded("mxfp4_moe_gptoss", lambda: bw.run_moe(a, emit=False)))
     a.prompt, a.batch = 2048, 1
-    lines = bw.run_decode(a, emit=False, batches=[1, 64], steps=256)
+    lines = guarded("llama8b_q4k_decode", lambda: bw.run_decode(a, emit=False, batches=[1, 64], steps=256))
     for b, l in zip((1, 64), lines or []):
         also[f"llama8b_q4k_decode_b{b}"] = _brief(l)
     out["also"] = also
