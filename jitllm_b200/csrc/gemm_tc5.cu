@@ -113,7 +113,7 @@ __device__ __forceinline__ void tc5_epilogue(const tc5_params &p, int u, uint32_
 // WT selects the weight format the dequant warps read: 0 = Q4_K (raw super-blocks), 1 = Q8_0 (resident
 // code plane in 64-element span order + f16 scale plane). Everything else is shared.
 template <int WT, int NT, int SA, int SB>
-__global__ void __launch_bounds__(TC5_THREADS, 1)
+__global__ void __launch_bounds__(TC5_GEMM_THREADS, 1)
 gemm_q4k_tc5_kernel(const __grid_constant__ CUtensorMap xmap, const tc5_params p) {
     using L = tc5_smem<NT, SA, SB>;
     extern __shared__ uint8_t smem_raw[];
@@ -139,14 +139,14 @@ gemm_q4k_tc5_kernel(const __grid_constant__ CUtensorMap xmap, const tc5_params p
     if (tid == 0) {
         for (int s = 0; s < SA; s++) {
             mbar_init(smem_u32(a_full + s), TC5_DQ_THREADS / 32);   // one arrival per dequant warp
-            mbar_init(smem_u32(a_empty + s), 1);
+            mbar_init(smem_u32(a_empty + s), TC5_ISSUERS);          // one commit per MMA issuer
         }
         for (int s = 0; s < SB; s++) {
             mbar_init(smem_u32(b_full + s), 1);
-            mbar_init(smem_u32(b_empty + s), 1);
+            mbar_init(smem_u32(b_empty + s), TC5_ISSUERS);
         }
         for (int i = 0; i < 2; i++) {
-            mbar_init(smem_u32(acc_full + i), 1);
+            mbar_init(smem_u32(acc_full + i), TC5_ISSUERS);
             mbar_init(smem_u32(acc_empty + i), 4);                  // one arrival per epilogue warp
         }
         abort_flag[0] = 0;
@@ -185,39 +185,51 @@ gemm_q4k_tc5_kernel(const __grid_constant__ CUtensorMap xmap, const tc5_params p
                 }
             }
         }
-    } else if (warp == 5) {
-        // ------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            constexpr uint32_t idesc = tc5_idesc(TC5_M, NT);
-            uint32_t kb_it = 0, unit_it = 0;
-            bool ok = true;
-            for (int u = blockIdx.x; u < nunits && ok && !*abort_flag; u += gridDim.x, unit_it++) {
-                TC5_UNIT(u);
-                const uint32_t ab = unit_it % L::ACC_BUFS, aph = (unit_it / L::ACC_BUFS) & 1;
-                if (unit_it >= (uint32_t)L::ACC_BUFS) ok = tc5_wait(smem_u32(acc_empty + ab), aph ^ 1, abort_flag);
+    } else if (warp == 5 || warp == TC5_MMA2_WARP) {
+        // ------------------------------------------------ MMA issuers: each takes its 128-row operands of every stage
+        // The whole warp runs the loop and an elected lane issues, so that what the instructions take is the same in
+        // every lane; the next stage's barriers are probed before this stage's MMAs go out.
+        constexpr uint32_t idesc = tc5_idesc(TC5_M, NT);
+        const int wu = tc5_uniform(warp);
+        const int ms_lo = TC5_ISSUERS == 2 ? (wu == 5 ? 0 : 1) : 0, ms_hi = TC5_ISSUERS == 2 ? ms_lo + 1 : TC5_MS;
+        const bool leader = tc5_elect();
+        const uint32_t tbase = (uint32_t)tc5_uniform((int)tmem_base), sb_u = (uint32_t)tc5_uniform((int)sbase);
+        const uint32_t bars_u = sb_u + L::BAR_OFS;   // a_full +0, a_empty +SA, b_full +2SA, b_empty +2SA+SB, acc_full +2SA+2SB
+        uint32_t kb_it = 0, unit_it = 0;
+        bool ok = true, ready_a = false, ready_b = false;
+        for (int u = blockIdx.x; u < nunits && ok; u += gridDim.x, unit_it++) {
+            if (tc5_uniform(*abort_flag)) break;
+            TC5_UNIT(u);
+            const uint32_t ab = unit_it % L::ACC_BUFS, aph = (unit_it / L::ACC_BUFS) & 1;
+            if (unit_it >= (uint32_t)L::ACC_BUFS)
+                ok = __all_sync(0xffffffffu, tc5_wait(bars_u + 8 * (2 * SA + 2 * SB + 2 + ab), aph ^ 1, abort_flag));
+            if (!ok) break;
+            tc5_fence_after();
+            const uint32_t d_tmem = tbase + ab * L::ACC_COLS;
+            const int nkb = nsbu * 4;
+            for (int kb = 0; kb < nkb && ok; kb++, kb_it++) {
+                const uint32_t sa = kb_it % SA, pha = (kb_it / SA) & 1, s = kb_it % SB, ph = (kb_it / SB) & 1;
+                if (!__all_sync(0xffffffffu, ready_a)) ok = __all_sync(0xffffffffu, tc5_wait(bars_u + 8 * sa, pha, abort_flag));
+                if (ok && !__all_sync(0xffffffffu, ready_b))
+                    ok = __all_sync(0xffffffffu, tc5_wait(bars_u + 8 * (2 * SA + s), ph, abort_flag));
                 if (!ok) break;
                 tc5_fence_after();
-                const uint32_t d_tmem = tmem_base + ab * L::ACC_COLS;
-                const int nkb = nsbu * 4;
-                for (int kb = 0; kb < nkb && ok; kb++, kb_it++) {
-                    const uint32_t sa = kb_it % SA, pha = (kb_it / SA) & 1, s = kb_it % SB, ph = (kb_it / SB) & 1;
-                    ok = tc5_wait(smem_u32(a_full + sa), pha, abort_flag) && tc5_wait(smem_u32(b_full + s), ph, abort_flag);
-                    if (!ok) break;
-                    tc5_fence_after();
-                    const uint64_t bdesc = tc5_smem_desc(sbase + L::B_OFS + s * L::B_BYTES);
-#pragma unroll
-                    for (int ms = 0; ms < TC5_MS; ms++) {
-                        const uint64_t adesc = tc5_smem_desc(sbase + L::A_OFS + (sa * TC5_MS + ms) * TC5_A_BYTES);
+                ready_a = mbar_test_wait(bars_u + 8 * ((kb_it + 1) % SA), ((kb_it + 1) / SA) & 1);
+                ready_b = mbar_test_wait(bars_u + 8 * (2 * SA + (kb_it + 1) % SB), ((kb_it + 1) / SB) & 1);
+                if (leader) {
+                    const uint64_t bdesc = tc5_smem_desc(sb_u + L::B_OFS + s * L::B_BYTES);
+                    for (int ms = ms_lo; ms < ms_hi; ms++) {
+                        const uint64_t adesc = tc5_smem_desc(sb_u + L::A_OFS + (sa * TC5_MS + ms) * TC5_A_BYTES);
 #pragma unroll
                         for (int j = 0; j < TC5_KB / 16; j++)  // 32 bytes of K per instruction: +2 in 16-byte units
                             tc5_mma_f16(d_tmem + ms * NT, adesc + 2 * j, bdesc + 2 * j, idesc, (kb | j) != 0);
                     }
-                    tc5_commit(smem_u32(a_empty + sa));   // stages reusable once these MMAs have read them
-                    tc5_commit(smem_u32(b_empty + s));
+                    tc5_commit(bars_u + 8 * (SA + sa));   // stages reusable once these MMAs have read them
+                    tc5_commit(bars_u + 8 * (2 * SA + SB + s));
                 }
-                if (!ok) break;
-                tc5_commit(smem_u32(acc_full + ab));      // accumulators complete
             }
+            if (!ok) break;
+            if (leader) tc5_commit(bars_u + 8 * (2 * SA + 2 * SB + ab));      // accumulators complete
         }
     } else if (warp >= 6) {
         // ------------------------------------------------ dequant: thread r owns tile row r
@@ -381,7 +393,7 @@ gemm_q4k_tc5_kernel(const __grid_constant__ CUtensorMap xmap, const tc5_params p
             if (lane == 0) mbar_arrive(smem_u32(acc_empty + ab));
         }
     }
-    if (warp >= 6 && !*abort_flag && (int)blockIdx.x < nunits) {
+    if (warp >= 6 && warp < TC5_MMA2_WARP && !*abort_flag && (int)blockIdx.x < nunits) {
         // ------------------------------------------------ dequant warps help drain the last accumulators
         TC5_DEP_WAIT();
         const int n_mine = (nunits - 1 - (int)blockIdx.x) / (int)gridDim.x + 1;
@@ -446,7 +458,7 @@ int jl_gemm_tc5_choice(jl_ctx *ctx, uint32_t type, int nrows, int k, int ntok, j
     const int sms = ctx ? ctx->sm_count : 148;
     const int ntok_eff = 2 * ntok;
     const int nt = tc5_pick_nt(ntok_eff);
-    c.kernel = JL_K_TC5; c.warps = TC5_THREADS / 32; c.rows_per_cta = TC5_ROWS;
+    c.kernel = JL_K_TC5; c.warps = TC5_GEMM_THREADS / 32; c.rows_per_cta = TC5_ROWS;
     c.split_k = tc5_ksplit(nrows, ntok_eff, k, sms);
     c.tile_m = TC5_M; c.tile_n = nt; c.tile_k = TC5_KB;
     const int units = ((nrows + TC5_ROWS - 1) / TC5_ROWS) * ((ntok_eff + nt - 1) / nt) * c.split_k;
@@ -472,7 +484,7 @@ static int tc5_launch(jl_ctx *ctx, const CUtensorMap &xmap, const tc5_params &p,
     JL_CUDA(ctx, cudaFuncSetAttribute(gemm_q4k_tc5_kernel<WT, NT, SA, SB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       L::TOTAL));
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(TC5_THREADS); cfg.dynamicSmemBytes = L::TOTAL; cfg.stream = s;
+    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(TC5_GEMM_THREADS); cfg.dynamicSmemBytes = L::TOTAL; cfg.stream = s;
     cudaLaunchAttribute at[1];
     at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     at[0].val.programmaticStreamSerializationAllowed = 1;

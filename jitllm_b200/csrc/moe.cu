@@ -193,6 +193,8 @@ moe_combine_kernel(float *__restrict__ out, const float *__restrict__ y, const i
 
 #define MOE_PF 4   // k-blocks of raw codes a dequant thread keeps in flight
 #define MOE_KH 2   // 64-wide k-blocks per shared-memory stage
+#define MOE_ISSUERS 2                                    // MMA issuer warps: 5 (first 128 rows of a tile), 14 (second 128)
+#define MOE_THREADS (TC5_THREADS + 32 * (MOE_ISSUERS - 1))
 struct moe_gemm_params {
     int mode;                    // 0: gate|up -> act(g, u);  1: down
     int n_expert, rows, k;       // rows, k of ONE expert matrix (mode 0: ffn x hidden; mode 1: hidden x ffn)
@@ -260,7 +262,7 @@ struct moe_smem {
 // (activation tiles of the expert's token list), 5 MMA issuer, 6..13 dequant (thread r owns tile
 // row r). A work unit is (expert, row tile, token tile); units past an expert's list exit.
 template <int NT, int SA, int SB>
-__global__ void __launch_bounds__(TC5_THREADS, 1)
+__global__ void __launch_bounds__(MOE_THREADS, 1)
 moe_gemm_kernel(const __grid_constant__ CUtensorMap xmap, const moe_gemm_params p) {
     using L = moe_smem<NT, SA, SB>;
     extern __shared__ uint8_t smem_raw[];
@@ -278,9 +280,9 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap xmap, const moe_gemm_params 
     const int mult = p.split ? 2 : 1;
 
     if (tid == 0) {
-        for (int s = 0; s < SA; s++) { mbar_init(smem_u32(a_full + s), TC5_DQ_THREADS / 32); mbar_init(smem_u32(a_empty + s), 1); }
-        for (int s = 0; s < SB; s++) { mbar_init(smem_u32(b_full + s), 1); mbar_init(smem_u32(b_empty + s), 1); }
-        for (int i = 0; i < 2; i++) { mbar_init(smem_u32(acc_full + i), 1); mbar_init(smem_u32(acc_empty + i), 4); }
+        for (int s = 0; s < SA; s++) { mbar_init(smem_u32(a_full + s), TC5_DQ_THREADS / 32); mbar_init(smem_u32(a_empty + s), MOE_ISSUERS); }
+        for (int s = 0; s < SB; s++) { mbar_init(smem_u32(b_full + s), 1); mbar_init(smem_u32(b_empty + s), MOE_ISSUERS); }
+        for (int i = 0; i < 2; i++) { mbar_init(smem_u32(acc_full + i), MOE_ISSUERS); mbar_init(smem_u32(acc_empty + i), 4); }
         abort_flag[0] = 0;
         abort_flag[1] = p.status[1];                                // the wait limit, read once
         mbar_init_fence();
@@ -321,45 +323,59 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap xmap, const moe_gemm_params 
                 }
             }
         }
-    } else if (warp == 5) {
-        if (lane == 0) {
-            constexpr uint32_t idesc = tc5_idesc(TC5_M, NT);
-            uint32_t kb_it = 0, unit_it = 0;
-            bool ok = true;
-            for (int u = blockIdx.x; u < nunits && ok && !*abort_flag; u += gridDim.x) {
-                MOE_UNIT(u);
-                if (!live) continue;
-                const uint32_t ab = unit_it % L::ACC_BUFS, aph = (unit_it / L::ACC_BUFS) & 1;
-                if (unit_it >= (uint32_t)L::ACC_BUFS) ok = tc5_wait(smem_u32(acc_empty + ab), aph ^ 1, abort_flag);
+    } else if (warp == 5 || warp == TC5_THREADS / 32) {
+        // ---- MMA issuers. Each takes one 128-row operand of every stage (its own accumulators), so that one warp's
+        //      barrier waits and commits pass while the other's MMAs execute. The whole warp runs the loop and an
+        //      elected lane issues: what the instructions take is then the same in every lane (values from memory by
+        //      a broadcast). The next stage's barriers are probed before this stage's MMAs go out.
+        constexpr uint32_t idesc = tc5_idesc(TC5_M, NT);
+        const int wu = tc5_uniform(warp);
+        const int ms_lo = MOE_ISSUERS == 2 ? (wu == 5 ? 0 : 1) : 0, ms_hi = MOE_ISSUERS == 2 ? ms_lo + 1 : TC5_MS;
+        const bool leader = tc5_elect();
+        const uint32_t tbase = (uint32_t)tc5_uniform((int)tmem_base), sb_u = (uint32_t)tc5_uniform((int)sbase);
+        const uint32_t bars_u = sb_u + L::BAR_OFS;   // a_full +0, a_empty +SA, b_full +2SA, b_empty +2SA+SB, acc_full +2SA+2SB
+        uint32_t kb_it = 0, unit_it = 0;
+        bool ok = true, ready_a = false, ready_b = false;
+        for (int u = blockIdx.x; u < nunits && ok; u += gridDim.x) {
+            if (tc5_uniform(*abort_flag)) break;
+            const int e = (u / p.row_tiles) % p.n_expert, tt = u / (p.n_expert * p.row_tiles);
+            if (tt * NT >= tc5_uniform(p.cnt[e]) * mult) continue;                   // not a live unit
+            const uint32_t ab = unit_it % L::ACC_BUFS, aph = (unit_it / L::ACC_BUFS) & 1;
+            if (unit_it >= (uint32_t)L::ACC_BUFS)
+                ok = __all_sync(0xffffffffu, tc5_wait(bars_u + 8 * (2 * SA + 2 * SB + 2 + ab), aph ^ 1, abort_flag));
+            if (!ok) break;
+            tc5_fence_after();
+            const uint32_t d_tmem = tbase + ab * L::ACC_COLS;
+            for (int kb = 0; kb < nkb && ok; kb++, kb_it++) {
+                const uint32_t sa = kb_it % SA, pha = (kb_it / SA) & 1, s = kb_it % SB, ph = (kb_it / SB) & 1;
+                if (!__all_sync(0xffffffffu, ready_a)) ok = __all_sync(0xffffffffu, tc5_wait(bars_u + 8 * sa, pha, abort_flag));
+                if (ok && !__all_sync(0xffffffffu, ready_b))
+                    ok = __all_sync(0xffffffffu, tc5_wait(bars_u + 8 * (2 * SA + s), ph, abort_flag));
                 if (!ok) break;
                 tc5_fence_after();
-                const uint32_t d_tmem = tmem_base + ab * L::ACC_COLS;
-                for (int kb = 0; kb < nkb && ok; kb++, kb_it++) {
-                    const uint32_t sa = kb_it % SA, pha = (kb_it / SA) & 1, s = kb_it % SB, ph = (kb_it / SB) & 1;
-                    ok = tc5_wait(smem_u32(a_full + sa), pha, abort_flag) && tc5_wait(smem_u32(b_full + s), ph, abort_flag);
-                    if (!ok) break;
-                    tc5_fence_after();
+                ready_a = mbar_test_wait(bars_u + 8 * ((kb_it + 1) % SA), ((kb_it + 1) / SA) & 1);
+                ready_b = mbar_test_wait(bars_u + 8 * (2 * SA + (kb_it + 1) % SB), ((kb_it + 1) / SB) & 1);
+                if (leader) {
 #pragma unroll
                     for (int h = 0; h < MOE_KH; h++) {
                         if (kb * MOE_KH + h >= n64) break;
-                        const uint64_t bdesc = tc5_smem_desc(sbase + L::B_OFS + s * L::B_BYTES + h * L::BH_BYTES);
-#pragma unroll
-                        for (int ms = 0; ms < TC5_MS; ms++) {
-                            const uint64_t adesc = tc5_smem_desc(sbase + L::A_OFS + sa * L::A_BYTES + h * L::AH_BYTES + ms * TC5_A_BYTES);
+                        const uint64_t bdesc = tc5_smem_desc(sb_u + L::B_OFS + s * L::B_BYTES + h * L::BH_BYTES);
+                        for (int ms = ms_lo; ms < ms_hi; ms++) {
+                            const uint64_t adesc = tc5_smem_desc(sb_u + L::A_OFS + sa * L::A_BYTES + h * L::AH_BYTES + ms * TC5_A_BYTES);
 #pragma unroll
                             for (int j = 0; j < TC5_KB / 16; j++)
                                 tc5_mma_f16(d_tmem + ms * NT, adesc + 2 * j, bdesc + 2 * j, idesc, (kb | h | j) != 0);
                         }
                     }
-                    tc5_commit(smem_u32(a_empty + sa));
-                    tc5_commit(smem_u32(b_empty + s));
+                    tc5_commit(bars_u + 8 * (SA + sa));
+                    tc5_commit(bars_u + 8 * (2 * SA + SB + s));
                 }
-                if (!ok) break;
-                tc5_commit(smem_u32(acc_full + ab));
-                unit_it++;
             }
+            if (!ok) break;
+            if (leader) tc5_commit(bars_u + 8 * (2 * SA + 2 * SB + ab));
+            unit_it++;
         }
-    } else if (warp >= 6) {
+    } else if (warp >= 6 && warp < TC5_THREADS / 32) {
         // ---- dequant: thread r owns tile row r. mode 0: rows 0..127 gate, 128..255 up (same row index);
         //      mode 1: 256 consecutive rows of down.
         const int r = tid - 192;
@@ -550,7 +566,7 @@ static int moe_launch(jl_ctx *ctx, const CUtensorMap &xmap, const moe_gemm_param
     JL_CUDA(ctx, cudaFuncSetAttribute(moe_gemm_kernel<NT, SA, SB>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
     const int units = p.n_expert * p.row_tiles * p.max_tok_tiles;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(units < ctx->sm_count ? units : ctx->sm_count); cfg.blockDim = dim3(TC5_THREADS);
+    cfg.gridDim = dim3(units < ctx->sm_count ? units : ctx->sm_count); cfg.blockDim = dim3(MOE_THREADS);
     cfg.dynamicSmemBytes = L::TOTAL; cfg.stream = s; cfg.attrs = at; cfg.numAttrs = nattr;
     JL_CUDA(ctx, cudaLaunchKernelEx(&cfg, moe_gemm_kernel<NT, SA, SB>, xmap, p));
     ctx->st.launches++;
@@ -598,7 +614,7 @@ static int moe_grouped_bs(jl_ctx *ctx, moe_gemm_params p, const uint8_t *xq, int
     if (!tma_a) amap0 = amap1 = xmap;
     const int units = p.n_expert * p.row_tiles * p.max_tok_tiles;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(units < ctx->sm_count ? units : ctx->sm_count); cfg.blockDim = dim3(TC5_THREADS);
+    cfg.gridDim = dim3(units < ctx->sm_count ? units : ctx->sm_count); cfg.blockDim = dim3(BS_THREADS);
     cfg.dynamicSmemBytes = L::TOTAL; cfg.stream = s; cfg.attrs = at; cfg.numAttrs = nattr;
     if (tma_a) {
         JL_CUDA(ctx, cudaFuncSetAttribute(moe_gemm_bs_kernel<NT, SA, SB, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
@@ -615,6 +631,11 @@ static int moe_grouped_bs(jl_ctx *ctx, moe_gemm_params p, const uint8_t *xq, int
 // given_ids != NULL: no router and no combine -- row i goes through expert given_ids[i] and
 // out_dev[i] = down(act(gate h_i, up h_i)) is WRITTEN in the caller's row order (the expert-parallel
 // path: rows arrive from other ranks already routed). Otherwise the whole layer, ADDED into out_dev.
+#ifdef MOE_EXP_SKIP_GEMM          // timing experiment: the layer without its two grouped GEMMs
+#define MOE_EXP_GEMM(call) 0
+#else
+#define MOE_EXP_GEMM(call) (call)
+#endif
 static int moe_dev_locked(jl_ctx *ctx, float *out_dev, const void *h_dev, int h_dtype, const float *logits_dev, int ntok,
                           const jl_moe_desc *d, int32_t *sel_out, float *wt_out, cudaStream_t s,
                           const int32_t *given_ids = nullptr) {
@@ -686,7 +707,7 @@ static int moe_dev_locked(jl_ctx *ctx, float *out_dev, const void *h_dev, int h_
         p.mode = 0; p.rows = F; p.k = H; p.row_tiles = (F + TC5_M - 1) / TC5_M;
         p.c0 = wg->data; p.c1 = wu->data; p.e0 = wg->scales; p.e1 = wu->scales; p.e_stride = wg->scale_stride;
         p.b0 = d->gate_bias; p.b1 = d->up_bias; p.outp = act; p.sfb = sf1; p.sfb_stride = sfs1;
-        int rc = moe_grouped_bs(ctx, p, q1, ntok, s, nattr, at);
+        int rc = MOE_EXP_GEMM(moe_grouped_bs(ctx, p, q1, ntok, s, nattr, at));
         if (rc) return rc;
         c = cfg_of(dim3(np), dim3(256));
         JL_CUDA(ctx, cudaLaunchKernelEx(&c, act_to_mx8_kernel, (const void *)act, (int)JL_DT_F32, q2, sf2, F, sfs2, (const int *)nullptr, 0));
@@ -695,7 +716,7 @@ static int moe_dev_locked(jl_ctx *ctx, float *out_dev, const void *h_dev, int h_
         p.c0 = wd->data; p.c1 = nullptr; p.e0 = wd->scales; p.e1 = nullptr; p.e_stride = wd->scale_stride;
         p.b0 = d->down_bias; p.b1 = nullptr; p.outp = y; p.sfb = sf2; p.sfb_stride = sfs2;
         if (given_ids) { p.outp = out_dev; p.out_rowmap = perm; }
-        if ((rc = moe_grouped_bs(ctx, p, q2, ntok, s, nattr, at))) return rc;
+        if ((rc = MOE_EXP_GEMM(moe_grouped_bs(ctx, p, q2, ntok, s, nattr, at)))) return rc;
         if (!given_ids) {
             c = cfg_of(dim3(ntok), dim3(256));
             JL_CUDA(ctx, cudaLaunchKernelEx(&c, moe_combine_kernel, out_dev, (const float *)y, (const int32_t *)sel, (const float *)wt,
@@ -718,7 +739,7 @@ static int moe_dev_locked(jl_ctx *ctx, float *out_dev, const void *h_dev, int h_
     p.mode = 0; p.rows = F; p.k = H; p.row_tiles = (F + TC5_M - 1) / TC5_M; p.split = hsplit;
     p.c0 = wg->data; p.c1 = wu->data; p.e0 = wg->scales; p.e1 = wu->scales; p.e_stride = wg->scale_stride;
     p.b0 = d->gate_bias; p.b1 = d->up_bias; p.inv_scale = xs_scale; p.outp = act;
-    int rc = moe_grouped(ctx, p, xs, ntok, s, nattr, at);
+    int rc = MOE_EXP_GEMM(moe_grouped(ctx, p, xs, ntok, s, nattr, at));
     if (rc) return rc;
     {
         cudaLaunchConfig_t c = cfg_of(dim3(np), dim3(256));
@@ -731,7 +752,7 @@ static int moe_dev_locked(jl_ctx *ctx, float *out_dev, const void *h_dev, int h_
     p.c0 = wd->data; p.c1 = nullptr; p.e0 = wd->scales; p.e1 = nullptr; p.e_stride = wd->scale_stride;
     p.b0 = d->down_bias; p.b1 = nullptr; p.inv_scale = as_scale; p.outp = y;
     if (given_ids) { p.outp = out_dev; p.out_rowmap = perm; }   // top_k = 1: perm[pos] is the caller's row
-    if ((rc = moe_grouped(ctx, p, as, ntok, s, nattr, at))) return rc;
+    if ((rc = MOE_EXP_GEMM(moe_grouped(ctx, p, as, ntok, s, nattr, at)))) return rc;
     if (!given_ids) {
         cudaLaunchConfig_t c = cfg_of(dim3(ntok), dim3(256));
         JL_CUDA(ctx, cudaLaunchKernelEx(&c, moe_combine_kernel, out_dev, (const float *)y, (const int32_t *)sel, (const float *)wt,
@@ -764,6 +785,10 @@ static int moe_grow_stage(jl_ctx *ctx, size_t need) {
     return JL_OK;
 }
 
+#ifdef BS_EXP_TRACE
+JL_EXPORT int jl_exp_bs_trace(long long *host) { return (int)cudaMemcpyFromSymbol(host, bs_trace, sizeof(bs_trace)); }
+JL_EXPORT int jl_exp_bs_cta(unsigned long long *host) { return (int)cudaMemcpyFromSymbol(host, bs_cta_t, sizeof(bs_cta_t)); }
+#endif
 JL_EXPORT int jl_moe_bs_weights_by_tma(jl_ctx *ctx) { return ctx ? ctx->moe_bs_tma : 0; }
 
 JL_EXPORT int jl_moe_reserve(jl_ctx *ctx, int ntok, int n_expert, int top_k, int hidden, int ffn) {

@@ -36,6 +36,11 @@
 #else
 #define BS_EXP_MMA 1
 #endif
+#ifndef BS_L2_AHEAD
+#define BS_L2_AHEAD 0                   // stages by which the weight tiles are asked for in L2 ahead of their copy
+#endif
+#define BS_ISSUERS 2                    // MMA issuer threads: warp 5 takes the tile's first 128 rows, warp 14 the second 128
+#define BS_THREADS (TC5_THREADS + 32 * (BS_ISSUERS - 1))
 #define BS_PF 4                         // stages of raw codes an unpack thread keeps in flight                   // TMEM columns of one scale-factor set: A tile 0, A tile 1, B, spare
 
 // Instruction descriptor, kind::mxf8f6f4 block-scaled: A e2m1, B e4m3, scales ue8m0, both K-major, D f32.
@@ -149,12 +154,21 @@ struct moe_bs_smem {
     static constexpr int SFA_OFS = B_OFS + SB * B_BYTES;
     static constexpr int SFB_OFS = SFA_OFS + SA * TC5_MS * BS_SF_ATOM;
     static constexpr int BAR_OFS = SFB_OFS + SA * BS_SF_ATOM;   // the activation scale atoms ride the A ring
-    static constexpr int NBARS = 2 * SA + 2 * SB + 4;
+    static constexpr int NBARS = 2 * SA + 4;                   // full[SA] empty[SA] acc_full[2] acc_empty[2]
+    static_assert(SA == SB, "a stage is one weight tile pair + one activation tile behind one barrier");
     static constexpr int MISC_OFS = BAR_OFS + NBARS * 8;
     static constexpr int TOTAL = MISC_OFS + 16 + 1024;
     static constexpr int TMEM_COLS = 512;                      // accumulators (ACC_COLS x 2) + two scale-factor sets
     static_assert(ACC_COLS * ACC_BUFS + 2 * BS_SF_COLS <= TMEM_COLS, "TMEM budget");
 };
+
+#ifdef BS_EXP_TRACE        // timing experiment: CTA 0's MMA thread and producer thread stamp their first 512 stages
+__device__ long long bs_trace[2][512][4];
+__device__ unsigned long long bs_cta_t[2][160][2];     // per launch kind (mode) and CTA: global timer at entry and exit
+#define BS_TR(role, i, j) do { if (blockIdx.x == 0 && (i) < 512u && (threadIdx.x >> 5) < 6 && (threadIdx.x & 31) == 0) bs_trace[role][i][j] = clock64(); } while (0)
+#else
+#define BS_TR(role, i, j) do { } while (0)
+#endif
 
 // Roles as in moe_gemm_kernel: warps 0..3 epilogue, 4 producer (activation tiles by TMA + their scale words), 5 MMA
 // issuer (scale factors to TMEM, then four K = 32 MMAs per tile and stage), 6..13 unpack (thread r owns tile row r).
@@ -162,7 +176,7 @@ struct moe_bs_smem {
 // instruction wants: nothing touches a code between HBM and the tensor core), and the eight warps only move the
 // scale words. Without it (the driver refused the maps) they also copy the codes through registers.
 template <int NT, int SA, int SB, bool TMAA>
-__global__ void __launch_bounds__(TC5_THREADS, 1)
+__global__ void __launch_bounds__(BS_THREADS, 1)
 moe_gemm_bs_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap amap0,
                    const __grid_constant__ CUtensorMap amap1, const moe_gemm_params p) {
     using L = moe_bs_smem<NT, SA, SB>;
@@ -170,8 +184,10 @@ moe_gemm_bs_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     const uint32_t sbase = smem_u32(smem);
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + L::BAR_OFS);
-    uint64_t *a_full = bars, *a_empty = bars + SA, *b_full = bars + 2 * SA, *b_empty = b_full + SB;
-    uint64_t *acc_full = b_empty + SB, *acc_empty = acc_full + 2;
+    // One "full" and one "empty" barrier per stage: the issuers' time per stage is what bounds this kernel, and every
+    // wait or commit they make costs them ~200 clocks even when it succeeds at once.
+    uint64_t *full = bars, *empty = bars + SA;
+    uint64_t *acc_full = bars + 2 * SA, *acc_empty = acc_full + 2;
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + L::MISC_OFS);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L::MISC_OFS + 4);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -180,9 +196,8 @@ moe_gemm_bs_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
     const int nunits = p.n_expert * p.row_tiles * p.max_tok_tiles;
 
     if (tid == 0) {
-        for (int s = 0; s < SA; s++) { mbar_init(smem_u32(a_full + s), BS_EXP_MOVERS * (TC5_DQ_THREADS / 32) + (TMAA ? 1 : 0)); mbar_init(smem_u32(a_empty + s), 1); }
-        for (int s = 0; s < SB; s++) { mbar_init(smem_u32(b_full + s), 1); mbar_init(smem_u32(b_empty + s), 1); }
-        for (int i = 0; i < 2; i++) { mbar_init(smem_u32(acc_full + i), 1); mbar_init(smem_u32(acc_empty + i), 4); }
+        for (int s = 0; s < SA; s++) { mbar_init(smem_u32(full + s), BS_EXP_MOVERS * (TC5_DQ_THREADS / 32) + 1); mbar_init(smem_u32(empty + s), BS_ISSUERS); }
+        for (int i = 0; i < 2; i++) { mbar_init(smem_u32(acc_full + i), BS_ISSUERS); mbar_init(smem_u32(acc_empty + i), 4); }
         abort_flag[0] = 0;
         abort_flag[1] = p.status[1];
         mbar_init_fence();
@@ -202,6 +217,9 @@ moe_gemm_bs_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
     const bool live = tt * NT < m_eff;                                                \
     (void)rt; (void)col0; (void)m_eff
 
+#ifdef BS_EXP_TRACE
+    if (tid == 0) bs_cta_t[p.mode][blockIdx.x][0] = jl_gtime_ns();
+#endif
     if (warp == 4) {
         // TMA only, one lane: activation tile, then the two weight tiles. (Nothing in this warp writes shared memory:
         // a proxy fence here would wait for the copies in flight and put their latency into every stage.)
@@ -212,80 +230,117 @@ moe_gemm_bs_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
                 BS_UNIT(u);
                 if (!live) continue;
                 for (int kb = 0; kb < nkb && ok; kb++, kb_it++) {
-                    const uint32_t s = kb_it % SB, ph = (kb_it / SB) & 1;
-                    if (kb_it >= (uint32_t)SB) ok = tc5_wait(smem_u32(b_empty + s), ph ^ 1, abort_flag);
+                    const uint32_t s = kb_it % SA, ph = (kb_it / SA) & 1;
+                    BS_TR(1, kb_it, 0);
+                    if (kb_it >= (uint32_t)SA) ok = tc5_wait(smem_u32(empty + s), ph ^ 1, abort_flag);
                     if (!ok) break;
-#ifdef BS_EXP_NOB
-                    mbar_arrive(smem_u32(b_full + s));
+                    BS_TR(1, kb_it, 1);
+                    // the activation tile and (TMAA) two boxes of 128 rows x 128 codes; in shared memory a code row takes
+                    // 128 bytes (16 codes in the low half of every 16-byte unit), but the barrier counts the 64 bytes per
+                    // row that are copied
+#if defined(BS_EXP_NOA)
+                    mbar_arrive_expect_tx(smem_u32(full + s), L::B_BYTES);
+#elif defined(BS_EXP_HALFA)
+                    mbar_arrive_expect_tx(smem_u32(full + s), L::B_BYTES + (TMAA ? TC5_A_BYTES / 2 : 0));
 #else
-                    mbar_arrive_expect_tx(smem_u32(b_full + s), L::B_BYTES);
-                    tma_load_2d(sbase + L::B_OFS + s * L::B_BYTES, &xmap, kb * BS_KB, col0, smem_u32(b_full + s));
+                    mbar_arrive_expect_tx(smem_u32(full + s), L::B_BYTES + (TMAA ? TC5_MS * TC5_A_BYTES / 2 : 0));
 #endif
+                    tma_load_2d(sbase + L::B_OFS + s * L::B_BYTES, &xmap, kb * BS_KB, col0, smem_u32(full + s));
                     if (TMAA) {
-                        const uint32_t sa = kb_it % SA, pha = (kb_it / SA) & 1;
-                        if (kb_it >= (uint32_t)SA) ok = tc5_wait(smem_u32(a_empty + sa), pha ^ 1, abort_flag);
-                        if (!ok) break;
-                        // two boxes of 128 rows x 128 codes; in shared memory a code row takes 128 bytes (16 codes in the
-                        // low half of every 16-byte unit), but the barrier counts the 64 bytes per row that are copied
                         const int y0 = e * p.rows + (p.mode == 0 ? rt * TC5_M : rt * TC5_ROWS);
-                        const uint32_t dst = sbase + L::A_OFS + sa * TC5_MS * TC5_A_BYTES;
-#ifdef BS_EXP_NOA
-                        mbar_arrive(smem_u32(a_full + sa));
-#else
-                        mbar_arrive_expect_tx(smem_u32(a_full + sa), TC5_MS * TC5_A_BYTES / 2);
-                        tma_load_2d(dst, &amap0, kb * BS_KB, y0, smem_u32(a_full + sa));
+                        const uint32_t dst = sbase + L::A_OFS + s * TC5_MS * TC5_A_BYTES;
+#ifndef BS_EXP_NOA
+                        tma_load_2d(dst, &amap0, kb * BS_KB, y0, smem_u32(full + s));
+#ifndef BS_EXP_HALFA
                         tma_load_2d(dst + TC5_A_BYTES, p.mode == 0 ? &amap1 : &amap0, kb * BS_KB, p.mode == 0 ? y0 : y0 + TC5_M,
-                                    smem_u32(a_full + sa));
+                                    smem_u32(full + s));
+#endif
+#endif
+#if BS_L2_AHEAD > 0
+                        // BS_L2_AHEAD stages further on, the same two boxes are asked for as far as L2 (of this unit, or
+                        // of the unit this CTA takes next): the ring alone keeps too few bytes in flight to cover HBM's
+                        // latency
+                        int pk = kb + BS_L2_AHEAD, py = y0;
+                        if (pk >= nkb) {
+                            const int un = u + (int)gridDim.x;
+                            pk -= nkb;
+                            py = un < nunits && pk < nkb ? ((un / p.row_tiles) % p.n_expert) * p.rows +
+                                                              (un % p.row_tiles) * (p.mode == 0 ? TC5_M : TC5_ROWS) : -1;
+                        }
+                        if (py >= 0) {
+                            tma_prefetch_2d(&amap0, pk * BS_KB, py);
+                            tma_prefetch_2d(p.mode == 0 ? &amap1 : &amap0, pk * BS_KB, p.mode == 0 ? py : py + TC5_M);
+                        }
 #endif
                     }
+                    BS_TR(1, kb_it, 2);
                 }
             }
         }
-    } else if (warp == 5) {
-        if (lane == 0) {
+    } else if (warp == 5 || warp == TC5_THREADS / 32) {
+        // Each issuer owns the accumulators of its 128-row operand and its own copies of the scale factors in TMEM
+        // (nothing orders one thread's tcgen05.cp against another thread's MMAs): while one waits on the stage
+        // barriers and commits, the other's MMAs execute.
+        // The WHOLE warp runs the loop and one elected lane issues the tcgen05 instructions: every value the
+        // instructions take (descriptors, TMEM addresses, barrier addresses) is then the same in all lanes, which lets
+        // the compiler keep it where the instructions read it; what comes from memory is made so by a broadcast.
+        const int wu = tc5_uniform(warp);
+        const int ms_lo = BS_ISSUERS == 2 ? (wu == 5 ? 0 : 1) : 0, ms_hi = BS_ISSUERS == 2 ? ms_lo + 1 : TC5_MS;
+        const uint32_t sfb_col = BS_ISSUERS == 2 ? 8 + 4 * ms_lo : 8;
+        const bool leader = tc5_elect();
+        const uint32_t tbase = (uint32_t)tc5_uniform((int)tmem_base), sb_u = (uint32_t)tc5_uniform((int)sbase);
+        const uint32_t bars_u = sb_u + L::BAR_OFS;            // full[s] at +8 s, empty[s] at +8 (SA + s), acc_full at +16 SA
+        {
             uint32_t kb_it = 0, unit_it = 0;
-            bool ok = true;
-            const uint32_t tsf0 = tmem_base + L::ACC_COLS * L::ACC_BUFS;
-            for (int u = blockIdx.x; u < nunits && ok && !*abort_flag; u += gridDim.x) {
-                BS_UNIT(u);
-                if (!live) continue;
+            bool ok = true, ready = false;
+            const uint32_t tsf0 = tbase + L::ACC_COLS * L::ACC_BUFS;
+            for (int u = blockIdx.x; u < nunits && ok; u += gridDim.x) {
+                if (tc5_uniform(*abort_flag)) break;
+                const int e = (u / p.row_tiles) % p.n_expert, tt = u / (p.n_expert * p.row_tiles);
+                if (tt * NT >= tc5_uniform(p.cnt[e])) continue;                        // not a live unit
                 const uint32_t ab = unit_it % L::ACC_BUFS, aph = (unit_it / L::ACC_BUFS) & 1;
-                if (unit_it >= (uint32_t)L::ACC_BUFS) ok = tc5_wait(smem_u32(acc_empty + ab), aph ^ 1, abort_flag);
+                if (unit_it >= (uint32_t)L::ACC_BUFS)
+                    ok = __all_sync(0xffffffffu, tc5_wait(bars_u + 8 * (2 * SA + 2 + ab), aph ^ 1, abort_flag));
                 if (!ok) break;
                 tc5_fence_after();
-                const uint32_t d_tmem = tmem_base + ab * L::ACC_COLS;
+                const uint32_t d_tmem = tbase + ab * L::ACC_COLS;
                 for (int kb = 0; kb < nkb && ok; kb++, kb_it++) {
-                    const uint32_t sa = kb_it % SA, pha = (kb_it / SA) & 1, s = kb_it % SB, ph = (kb_it / SB) & 1;
-                    ok = tc5_wait(smem_u32(a_full + sa), pha, abort_flag) && tc5_wait(smem_u32(b_full + s), ph, abort_flag);
+                    const uint32_t s = kb_it % SA, sa = s, ph = (kb_it / SA) & 1;
+                    BS_TR(0, kb_it, 0);
+                    if (!__all_sync(0xffffffffu, ready)) ok = __all_sync(0xffffffffu, tc5_wait(bars_u + 8 * s, ph, abort_flag));
+                    BS_TR(0, kb_it, 1);
                     if (!ok) break;
                     tc5_fence_after();
+                    // the next stage's barrier is probed now, so that the probe's latency passes under this stage's MMAs
+                    ready = mbar_test_wait(bars_u + 8 * ((kb_it + 1) % SA), ((kb_it + 1) / SA) & 1);
+                    BS_TR(0, kb_it, 2);
                     const uint32_t tsf = tsf0 + (kb_it & 1) * BS_SF_COLS;         // two sets, alternating
-#if !defined(BS_EXP_NOMMA) && !defined(BS_EXP_NOCP)
-#pragma unroll
-                    for (int ms = 0; ms < TC5_MS; ms++)
-                        bs_cp_sf(tsf + ms * 4, bs_sf_desc(sbase + L::SFA_OFS + (sa * TC5_MS + ms) * BS_SF_ATOM));
-                    bs_cp_sf(tsf + 8, bs_sf_desc(sbase + L::SFB_OFS + sa * BS_SF_ATOM));
-#endif
-                    const uint64_t bdesc = tc5_smem_desc(sbase + L::B_OFS + s * L::B_BYTES);
+                    const uint64_t bdesc = tc5_smem_desc(sb_u + L::B_OFS + s * L::B_BYTES);
                     const int nj = min(BS_KB / 32, nblk - kb * (BS_KB / 32));     // the last stage of a row may be short
+                    if (leader) {
+#if !defined(BS_EXP_NOMMA) && !defined(BS_EXP_NOCP)
+                        for (int ms = ms_lo; ms < ms_hi; ms++)
+                            bs_cp_sf(tsf + ms * 4, bs_sf_desc(sb_u + L::SFA_OFS + (sa * TC5_MS + ms) * BS_SF_ATOM));
+                        bs_cp_sf(tsf + sfb_col, bs_sf_desc(sb_u + L::SFB_OFS + sa * BS_SF_ATOM));
+#endif
+                        for (int ms = ms_lo; ms < ms_hi; ms++) {
+                            const uint64_t adesc = tc5_smem_desc(sb_u + L::A_OFS + (sa * TC5_MS + ms) * TC5_A_BYTES);
 #pragma unroll
-                    for (int ms = 0; ms < TC5_MS; ms++) {
-                        const uint64_t adesc = tc5_smem_desc(sbase + L::A_OFS + (sa * TC5_MS + ms) * TC5_A_BYTES);
-#pragma unroll
-                        for (int j = 0; j < BS_KB / 32; j++)
-                            if (j < nj && BS_EXP_MMA)
-                                bs_mma(d_tmem + ms * NT, adesc + 2 * j, bdesc + 2 * j, bs_idesc(TC5_M, NT, j, j), (kb | j) != 0,
-                                       tsf + ms * 4, tsf + 8);
+                            for (int j = 0; j < BS_KB / 32; j++)
+                                if (j < nj && BS_EXP_MMA)
+                                    bs_mma(d_tmem + ms * NT, adesc + 2 * j, bdesc + 2 * j, bs_idesc(TC5_M, NT, j, j), (kb | j) != 0,
+                                           tsf + ms * 4, tsf + sfb_col);
+                        }
+                        tc5_commit(bars_u + 8 * (SA + s));
                     }
-                    tc5_commit(smem_u32(a_empty + sa));
-                    tc5_commit(smem_u32(b_empty + s));
+                    BS_TR(0, kb_it, 3);
                 }
                 if (!ok) break;
-                tc5_commit(smem_u32(acc_full + ab));
+                if (leader) tc5_commit(bars_u + 8 * (2 * SA + ab));
                 unit_it++;
             }
         }
-    } else if (warp >= 6 && BS_EXP_MOVERS) {
+    } else if (warp >= 6 && warp < TC5_THREADS / 32 && BS_EXP_MOVERS) {
         // ---- unpack: thread r owns tile row r. mode 0: rows 0..127 gate, 128..255 up (same row index); mode 1: 256
         //      consecutive rows of down. Per stage: four blocks of 16 code bytes -> eight 16-byte units (codes in the low
         //      half), and the four block scales as one word of the scale-factor atom.
@@ -293,6 +348,55 @@ moe_gemm_bs_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
         const uint32_t swz = (uint32_t)(r & 7);
         const int a_row_ofs = (r >> 7) * TC5_A_BYTES + (r & 127) * 128;
         const int sf_ofs = (r >> 7) * BS_SF_ATOM + ((r & 127) & 31) * 16 + ((r & 127) >> 5) * 4;
+        if constexpr (TMAA) {
+            // The codes come by TMA: a thread moves one word of weight scales (its row's four blocks) and, for r < NT,
+            // one word of activation scales per stage. The words run BS_PF stages ahead in registers as ONE stream over
+            // all of the CTA's units, so that a new unit's first words are already here when its first stage opens
+            // (loaded at the unit's start they put an HBM round trip into every unit).
+            const bool second = p.mode == 0 && r >= 128;
+            const uint8_t *eplane = second ? p.e1 : p.e0;
+            int lu = blockIdx.x, lkb = 0;                      // the load cursor: unit, stage
+            const uint32_t *ea = nullptr, *eb = nullptr;
+            auto enter = [&]() {                               // first live unit at or after lu; its two rows of words
+                for (; lu < nunits; lu += gridDim.x) {
+                    BS_UNIT(lu);
+                    if (!live) continue;
+                    const int row = p.mode == 0 ? min(rt * TC5_M + (r & 127), p.rows - 1) : min(rt * TC5_ROWS + r, p.rows - 1);
+                    ea = reinterpret_cast<const uint32_t *>(eplane + ((size_t)e * p.rows + row) * p.e_stride);
+                    eb = reinterpret_cast<const uint32_t *>(p.sfb + (size_t)min(col0 + (r & (NT - 1)), p.npairs - 1) * p.sfb_stride);
+                    return;
+                }
+            };
+            auto load_one = [&](uint32_t &wa, uint32_t &wb) -> bool {
+                if (lu >= nunits) return false;
+                wa = __ldg(ea + lkb);
+                wb = r < NT ? __ldg(eb + lkb) : 0u;
+                if (++lkb == nkb) { lkb = 0; lu += gridDim.x; enter(); }
+                return true;
+            };
+            enter();
+            uint32_t wa[BS_PF], wb[BS_PF];
+            bool have[BS_PF];
+#pragma unroll
+            for (int j = 0; j < BS_PF; j++) { wa[j] = wb[j] = 0u; have[j] = load_one(wa[j], wb[j]); }
+            bool ok = true;
+            for (uint32_t it0 = 0; ok; it0 += BS_PF) {
+#pragma unroll
+                for (int j = 0; j < BS_PF; j++) {
+                    if (!have[j]) { ok = false; break; }       // the stream has ended
+                    const uint32_t it = it0 + j, s = it % SA, ph = (it / SA) & 1;
+                    if (it >= (uint32_t)SA) ok = tc5_wait(smem_u32(empty + s), ph ^ 1, abort_flag);
+                    if (!ok) break;
+                    *reinterpret_cast<uint32_t *>(smem + L::SFA_OFS + s * TC5_MS * BS_SF_ATOM + sf_ofs) = wa[j];
+                    if (r < NT) *reinterpret_cast<uint32_t *>(smem + L::SFB_OFS + s * BS_SF_ATOM + (r & 31) * 16 + (r >> 5) * 4) = wb[j];
+                    fence_async_smem();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(full + s));
+                    // refilled AFTER the fence: a proxy fence waits for the thread's loads in flight
+                    have[j] = load_one(wa[j], wb[j]);
+                }
+            }
+        } else {
         uint32_t kb_it = 0;
         bool ok = true;
         for (int u = blockIdx.x; u < nunits && ok && !*abort_flag; u += gridDim.x) {
@@ -340,7 +444,7 @@ moe_gemm_bs_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
 #pragma unroll
                     for (int b = 0; b < 4; b++) c[b] = q[j][b];
                     const uint32_t sf_cur = sfw[j], sfb_cur = sfbw[j];
-                    if (kb_it >= (uint32_t)SA) ok = tc5_wait(smem_u32(a_empty + s), ph ^ 1, abort_flag);
+                    if (kb_it >= (uint32_t)SA) ok = tc5_wait(smem_u32(empty + s), ph ^ 1, abort_flag);
                     if (!ok) break;
                     if (!TMAA) {
                         uint8_t *arow = smem + L::A_OFS + s * TC5_MS * TC5_A_BYTES + a_row_ofs;
@@ -354,15 +458,20 @@ moe_gemm_bs_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
                     if (r < NT) *reinterpret_cast<uint32_t *>(smem + L::SFB_OFS + s * BS_SF_ATOM + (r & 31) * 16 + (r >> 5) * 4) = sfb_cur;
                     fence_async_smem();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(smem_u32(a_full + s));
+                    if (lane == 0) mbar_arrive(smem_u32(full + s));
                     kb_it++;
                     // refilled AFTER the fence: a proxy fence waits for the thread's loads in flight
+#ifndef BS_EXP_NOSFLOAD
                     if (kb + BS_PF < nkb) {
+#else
+                    if (false) {
+#endif
                         load_stage(kb + BS_PF, q[j], sfw[j]);
                         if (r < NT) sfbw[j] = __ldg(sfb_row + kb + BS_PF);
                     }
                 }
             }
+        }
         }
     } else if (warp < 4) {
         // ---- epilogue: warp w reads TMEM lanes 32w..32w+31 (tile rows), 32 token columns at a time
@@ -422,6 +531,9 @@ moe_gemm_bs_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
     tc5_fence_before();
     __syncthreads();
     if (tid == 0 && *abort_flag) atomicExch(p.status, 3);
+#ifdef BS_EXP_TRACE
+    if (tid == 0) bs_cta_t[p.mode][blockIdx.x][1] = jl_gtime_ns();
+#endif
     if (warp == 5) {
         tc5_fence_after();
         tc5_dealloc(tmem_base, L::TMEM_COLS);

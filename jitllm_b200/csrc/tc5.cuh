@@ -11,6 +11,13 @@
 #define TC5_KB 64           // k per shared-memory stage (128 bytes of f16: one swizzle atom)
 #define TC5_A_BYTES (TC5_M * TC5_KB * 2)   // one 128-row operand
 #define TC5_THREADS 448     // 14 warps: 4 epilogue, producer, MMA, 8 dequant
+// MMA issuers of the prefill GEMM: with 2, warp 5 issues the MMAs of the tile's first 128 rows and warp 14 those of
+// the second 128 (separate accumulators, same activation stage), so one thread's barrier waits and commits run
+// while the other's MMAs execute: a single issuer spends ~500 clocks per k-block outside its MMAs and the tensor
+// pipe idles for them.
+#define TC5_ISSUERS 2
+#define TC5_GEMM_THREADS (TC5_THREADS + 32 * (TC5_ISSUERS - 1))
+#define TC5_MMA2_WARP (TC5_THREADS / 32)
 #define TC5_DQ_THREADS 256  // one thread per tile row
 
 // ------------------------------------------------------------- activations
@@ -103,6 +110,14 @@ __device__ __forceinline__ void tc5_alloc(uint32_t smem_dst, uint32_t ncols) {
 __device__ __forceinline__ void tc5_dealloc(uint32_t taddr, uint32_t ncols) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
 }
+// One lane of the (converged) warp; and a value broadcast from lane 0, which also tells the compiler that it is the
+// same in every lane.
+__device__ __forceinline__ bool tc5_elect() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+    return pred != 0;
+}
+__device__ __forceinline__ int tc5_uniform(int v) { return __shfl_sync(0xffffffffu, v, 0); }
 __device__ __forceinline__ void tc5_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc5_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc5_commit(uint32_t bar) {
