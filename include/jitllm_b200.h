@@ -229,9 +229,12 @@ typedef struct jl_moe_desc {
  * kind::mxf8f6f4.block_scale on the e2m1 codes and e8m0 scales as they are, activations quantised per 32
  * elements to e4m3 with a ue8m0 scale -- faster (no warp converts a weight), but the activation
  * quantisation (3 mantissa bits) puts its error near 1e-2: it does NOT meet the parity bar and is never
- * selected implicitly. No counterpart in the reference (its grouped expert GEMM is mma.sync,
- * jit/gpu/kernels/gemm70.go:123-129). */
-typedef enum jl_moe_arm { JL_MOE_ARM_EXACT = 0, JL_MOE_ARM_BLOCK_SCALED = 1 } jl_moe_arm;
+ * selected implicitly. BLOCK_SCALED_X3: the same MMAs over THREE e4m3 digits per activation (digit d + 1 is
+ * the e4m3 rounding of what digits 0..d leave; the digits share the block's scale and are three columns of
+ * the tile, added when the accumulators are drained): 12 significant bits, weights and weight scales exact
+ * as in the other arms, so it meets the 2e-3 parity bar at close to the one-digit arm's speed. No
+ * counterpart in the reference (its grouped expert GEMM is mma.sync, jit/gpu/kernels/gemm70.go:123-129). */
+typedef enum jl_moe_arm { JL_MOE_ARM_EXACT = 0, JL_MOE_ARM_BLOCK_SCALED = 1, JL_MOE_ARM_BLOCK_SCALED_X3 = 2 } jl_moe_arm;
 /* 1 when the last block-scaled launch of this context took its weight tiles by TMA (packed 4-bit tensor maps),
  * 0 when the driver refused those maps and the codes went through registers. */
 int jl_moe_bs_weights_by_tma(jl_ctx *ctx);

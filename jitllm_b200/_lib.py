@@ -82,7 +82,7 @@ class LayersDesc(C.Structure):
 # Every symbol include/jitllm_b200.h declares: (restype, argtypes).
 _VP, _I, _SZ, _U32 = C.c_void_p, C.c_int, C.c_size_t, C.c_uint32
 TUNE_OFF, TUNE_ON, TUNE_FORCE = 0, 1, 2
-MOE_ARM_EXACT, MOE_ARM_BLOCK_SCALED = 0, 1
+MOE_ARM_EXACT, MOE_ARM_BLOCK_SCALED, MOE_ARM_BLOCK_SCALED_X3 = 0, 1, 2
 TUNE_TIMER = C.CFUNCTYPE(C.c_double, C.c_void_p, C.c_int, C.c_int)
 
 SYMBOLS = {

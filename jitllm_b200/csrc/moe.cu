@@ -255,7 +255,8 @@ struct moe_smem {
     static constexpr int BAR_OFS = B_OFS + SB * B_BYTES;
     static constexpr int NBARS = 2 * SA + 2 * SB + 4;
     static constexpr int MISC_OFS = BAR_OFS + NBARS * 8;
-    static constexpr int TOTAL = MISC_OFS + 16 + 1024;
+    static constexpr int CNT_OFS = MISC_OFS + 16;               // the experts' list offsets: 257 ints (a length is a difference)
+    static constexpr int TOTAL = CNT_OFS + 1040 + 1024;         // kept small on purpose: see the note at moe_launch
 };
 
 // Same roles as the dense prefill GEMM (gemm_tc5.cu): warps 0..3 epilogue, 4 TMA producer
@@ -276,8 +277,8 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap xmap, const moe_gemm_params 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n64 = p.k / TC5_KB;                       // 64-wide k-blocks of a row
     const int nkb = (n64 + MOE_KH - 1) / MOE_KH;        // stages (the last one may hold a single half)
-    const int nunits = p.n_expert * p.row_tiles * p.max_tok_tiles;
     const int mult = p.split ? 2 : 1;
+    int *s_off = reinterpret_cast<int *>(smem + L::CNT_OFS);
 
     if (tid == 0) {
         for (int s = 0; s < SA; s++) { mbar_init(smem_u32(a_full + s), TC5_DQ_THREADS / 32); mbar_init(smem_u32(a_empty + s), MOE_ISSUERS); }
@@ -294,13 +295,20 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap xmap, const moe_gemm_params 
     const uint32_t tmem_base = *tmem_slot;
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");   // token lists and activation rows come from the kernels in front
+    // list lengths and offsets once into shared memory (every role asks for them at every unit, live or not); the walk
+    // over the units ends at the longest list's last token tile
+    if (tid <= p.n_expert) s_off[tid] = p.off[tid];      // off[n_expert] = the number of listed pairs
+    __syncthreads();
+    int longest = 0;
+    for (int e = 0; e < p.n_expert; e++) longest = max(longest, (s_off[e + 1] - s_off[e]));
+    const int nunits = p.n_expert * p.row_tiles * min(p.max_tok_tiles, (longest * mult + NT - 1) / NT);
 
     // unit -> (expert, row tile, token tile); live iff the token tile starts inside the expert's list
 #define MOE_UNIT(u)                                                                   \
     const int tt = (u) / (p.n_expert * p.row_tiles);   /* slowest: the live units (first token    \
                                                           tiles) are contiguous, spread over CTAs */ \
     const int e = ((u) / p.row_tiles) % p.n_expert, rt = (u) % p.row_tiles;           \
-    const int m_eff = p.cnt[e] * mult, col0 = p.off[e] * mult + tt * NT;              \
+    const int m_eff = (s_off[e + 1] - s_off[e]) * mult, col0 = s_off[e] * mult + tt * NT;              \
     const bool live = tt * NT < m_eff;                                                \
     (void)rt; (void)col0; (void)m_eff
 
@@ -339,7 +347,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap xmap, const moe_gemm_params 
         for (int u = blockIdx.x; u < nunits && ok; u += gridDim.x) {
             if (tc5_uniform(*abort_flag)) break;
             const int e = (u / p.row_tiles) % p.n_expert, tt = u / (p.n_expert * p.row_tiles);
-            if (tt * NT >= tc5_uniform(p.cnt[e]) * mult) continue;                   // not a live unit
+            if (tt * NT >= tc5_uniform((s_off[e + 1] - s_off[e])) * mult) continue;                   // not a live unit
             const uint32_t ab = unit_it % L::ACC_BUFS, aph = (unit_it / L::ACC_BUFS) & 1;
             if (unit_it >= (uint32_t)L::ACC_BUFS)
                 ok = __all_sync(0xffffffffu, tc5_wait(bars_u + 8 * (2 * SA + 2 * SB + 2 + ab), aph ^ 1, abort_flag));
@@ -484,7 +492,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap xmap, const moe_gemm_params 
             if (!tc5_wait_relaxed(smem_u32(acc_full + ab), aph, abort_flag)) break;
             tc5_fence_after();
             const uint32_t tacc = tmem_base + ab * L::ACC_COLS + ((uint32_t)(warp * 32) << 16);
-            const int pos_end = p.off[e] + p.cnt[e];
+            const int pos_end = s_off[e] + (s_off[e + 1] - s_off[e]);
             const int nj = p.split ? 16 : 32;
 #pragma unroll 1
             for (int c0 = 0; c0 < NT; c0 += 32) {
@@ -563,6 +571,10 @@ static int moe_launch(jl_ctx *ctx, const CUtensorMap &xmap, const moe_gemm_param
                       cudaLaunchAttribute *at) {
     using L = moe_smem<NT, SA, SB>;
     static_assert(L::TOTAL <= 227 * 1024, "shared memory budget");
+    // Measured: the <128,2,2> form sits just under a step of the shared-memory carve-out (with the per-CTA reserve,
+    // 196 KB); 2 KB more shared memory move it over the step, the L1 the dequant warps' raw loads lean on shrinks,
+    // and the layer goes from 347 to 447 us.
+    static_assert(L::TOTAL + 1024 <= 196 * 1024, "stay under the 196 KB carve-out step: the raw loads need the L1 beside it");
     JL_CUDA(ctx, cudaFuncSetAttribute(moe_gemm_kernel<NT, SA, SB>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
     const int units = p.n_expert * p.row_tiles * p.max_tok_tiles;
     cudaLaunchConfig_t cfg = {};
@@ -585,19 +597,22 @@ static int moe_grouped(jl_ctx *ctx, moe_gemm_params p, const __half *xs, int nto
         return jl_set_err(ctx, JL_DECLINED, "the driver refused a tensor map for the mixture's activations");
     // shallow rings: shared memory not taken is L1 for the dequant warps' raw-weight loads (5-deep A rings: 576 us
     // per layer against 348 us)
+    // (a 2-deep activation ring for the first form, which puts it under the next lower carve-out step: 337 against 341 us)
     return p.split ? moe_launch<128, 2, 2>(ctx, xmap, p, s, nattr, at) : moe_launch<64, 2, 3>(ctx, xmap, p, s, nattr, at);
 }
 
 // The block-scaled arm's grouped GEMM over the sorted e4m3 activation rows `xq` ([npairs][k] bytes).
+template <int NT, int T, int DIG>
 static int moe_grouped_bs(jl_ctx *ctx, moe_gemm_params p, const uint8_t *xq, int ntok, cudaStream_t s, int nattr,
                           cudaLaunchAttribute *at) {
-    constexpr int NT = 64, SA = BS_SA, SB = BS_SB;
+    constexpr int SA = BS_SA, SB = BS_SB;
     using L = moe_bs_smem<NT, SA, SB>;
     static_assert(L::TOTAL <= 227 * 1024, "shared memory budget");
-    p.max_tok_tiles = (ntok + NT - 1) / NT;
+    static_assert(DIG * T <= NT && T % 8 == 0, "a tile's digit columns fit the MMAs' N; digit planes start on a swizzle atom");
+    p.max_tok_tiles = (ntok + T - 1) / T;
     p.split = 0;
-    CUtensorMap xmap;
-    if (!jl_make_tmap_2d(&xmap, xq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)p.k, (uint64_t)p.npairs, (uint64_t)p.k, BS_KB, NT,
+    CUtensorMap xmap;     // the DIG digit planes of the e4m3 rows, one below the other; a box is one plane's T rows
+    if (!jl_make_tmap_2d(&xmap, xq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)p.k, (uint64_t)p.npairs * DIG, (uint64_t)p.k, BS_KB, T,
                          CU_TENSOR_MAP_SWIZZLE_128B))
         return jl_set_err(ctx, JL_DECLINED, "the driver refused a tensor map for the mixture's e4m3 activations");
     // The weight planes as packed 4-bit tensors: 16 codes per 8 bytes in HBM, 16 bytes (8 of them a gap) in shared
@@ -617,11 +632,11 @@ static int moe_grouped_bs(jl_ctx *ctx, moe_gemm_params p, const uint8_t *xq, int
     cfg.gridDim = dim3(units < ctx->sm_count ? units : ctx->sm_count); cfg.blockDim = dim3(BS_THREADS);
     cfg.dynamicSmemBytes = L::TOTAL; cfg.stream = s; cfg.attrs = at; cfg.numAttrs = nattr;
     if (tma_a) {
-        JL_CUDA(ctx, cudaFuncSetAttribute(moe_gemm_bs_kernel<NT, SA, SB, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
-        JL_CUDA(ctx, cudaLaunchKernelEx(&cfg, moe_gemm_bs_kernel<NT, SA, SB, true>, xmap, amap0, amap1, p));
+        JL_CUDA(ctx, cudaFuncSetAttribute(moe_gemm_bs_kernel<NT, T, DIG, SA, SB, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
+        JL_CUDA(ctx, cudaLaunchKernelEx(&cfg, moe_gemm_bs_kernel<NT, T, DIG, SA, SB, true>, xmap, amap0, amap1, p));
     } else {
-        JL_CUDA(ctx, cudaFuncSetAttribute(moe_gemm_bs_kernel<NT, SA, SB, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
-        JL_CUDA(ctx, cudaLaunchKernelEx(&cfg, moe_gemm_bs_kernel<NT, SA, SB, false>, xmap, amap0, amap1, p));
+        JL_CUDA(ctx, cudaFuncSetAttribute(moe_gemm_bs_kernel<NT, T, DIG, SA, SB, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
+        JL_CUDA(ctx, cudaLaunchKernelEx(&cfg, moe_gemm_bs_kernel<NT, T, DIG, SA, SB, false>, xmap, amap0, amap1, p));
     }
     ctx->st.launches++;
     ctx->moe_bs_tma = tma_a ? 1 : 0;
@@ -649,9 +664,9 @@ static int moe_dev_locked(jl_ctx *ctx, float *out_dev, const void *h_dev, int h_
     if (wg->n_expert != E || wu->n_expert != E || wd->n_expert != E || wg->nrows != F || wg->k != H || wu->nrows != F ||
         wu->k != H || wd->nrows != H || wd->k != F)
         return jl_set_err(ctx, JL_EINVAL, "expert banks do not match the descriptor's shape");
-    if (d->arm != JL_MOE_ARM_EXACT && d->arm != JL_MOE_ARM_BLOCK_SCALED)
+    if (d->arm != JL_MOE_ARM_EXACT && d->arm != JL_MOE_ARM_BLOCK_SCALED && d->arm != JL_MOE_ARM_BLOCK_SCALED_X3)
         return jl_set_err(ctx, JL_EINVAL, "jl_moe_desc.arm %d is not a known arm", d->arm);
-    if (d->arm == JL_MOE_ARM_BLOCK_SCALED && (H > BS_MAX_KB * BS_KB || F > BS_MAX_KB * BS_KB))
+    if (d->arm != JL_MOE_ARM_EXACT && (H > BS_MAX_KB * BS_KB || F > BS_MAX_KB * BS_KB))
         return jl_set_err(ctx, JL_DECLINED, "the block-scaled arm serves hidden and ffn up to %d", BS_MAX_KB * BS_KB);
     if (d->arm == JL_MOE_ARM_EXACT &&
         (wg->emin < 104 || wg->emax > 140 || wu->emin < 104 || wu->emax > 140 || wd->emin < 104 || wd->emax > 140))
@@ -691,32 +706,38 @@ static int moe_dev_locked(jl_ctx *ctx, float *out_dev, const void *h_dev, int h_
         JL_CUDA(ctx, cudaLaunchKernelEx(&c, moe_sort_kernel, (const int32_t *)sel, np, K, E, cnt, off, perm, pos_of));
         ctx->st.launches++;
     }
-    if (d->arm == JL_MOE_ARM_BLOCK_SCALED) {
-        // The block-scaled arm: activations to e4m3 + ue8m0 per 32 (twice: the routed rows, then the gated
-        // intermediates), weights and their scales as they are. The e4m3 rows and scale rows live where the exact
-        // arm keeps its f16 rows.
+    if (d->arm != JL_MOE_ARM_EXACT) {
+        // The block-scaled arms: activations to e4m3 + ue8m0 per 32 (twice: the routed rows, then the gated
+        // intermediates), one digit or three, weights and their scales as they are. The e4m3 planes and scale rows
+        // live where the exact arm keeps its f16 rows (4 bytes per element there: room for three planes and the scales).
+        const int ndig = d->arm == JL_MOE_ARM_BLOCK_SCALED_X3 ? 3 : 1;
         const int sfs1 = (H + BS_KB - 1) / BS_KB * 4, sfs2 = (F + BS_KB - 1) / BS_KB * 4;
-        uint8_t *q1 = (uint8_t *)xs, *sf1 = q1 + (size_t)np * H;
-        uint8_t *q2 = (uint8_t *)as, *sf2 = q2 + (size_t)np * F;
+        uint8_t *q1 = (uint8_t *)xs, *sf1 = q1 + (size_t)ndig * np * H;
+        uint8_t *q2 = (uint8_t *)as, *sf2 = q2 + (size_t)ndig * np * F;
         const int src_rows = given_ids ? ntok : ntok;
+        auto grouped = [&](const moe_gemm_params &pp, const uint8_t *xq) {
+            return ndig == 3 ? moe_grouped_bs<128, 40, 3>(ctx, pp, xq, ntok, s, nattr, at) : moe_grouped_bs<64, 64, 1>(ctx, pp, xq, ntok, s, nattr, at);
+        };
         cudaLaunchConfig_t c = cfg_of(dim3(np), dim3(256));
-        JL_CUDA(ctx, cudaLaunchKernelEx(&c, act_to_mx8_kernel, h_dev, h_dtype, q1, sf1, H, sfs1, (const int *)perm, src_rows));
+        JL_CUDA(ctx, cudaLaunchKernelEx(&c, act_to_mx8_kernel, h_dev, h_dtype, q1, sf1, H, sfs1, (const int *)perm, src_rows, ndig,
+                                        (size_t)np * H));
         ctx->st.launches++;
         moe_gemm_params p = {};
         p.n_expert = E; p.cnt = cnt; p.off = off; p.npairs = np; p.status = ctx->dev_status; p.act = d->act;
         p.mode = 0; p.rows = F; p.k = H; p.row_tiles = (F + TC5_M - 1) / TC5_M;
         p.c0 = wg->data; p.c1 = wu->data; p.e0 = wg->scales; p.e1 = wu->scales; p.e_stride = wg->scale_stride;
         p.b0 = d->gate_bias; p.b1 = d->up_bias; p.outp = act; p.sfb = sf1; p.sfb_stride = sfs1;
-        int rc = MOE_EXP_GEMM(moe_grouped_bs(ctx, p, q1, ntok, s, nattr, at));
+        int rc = MOE_EXP_GEMM(grouped(p, q1));
         if (rc) return rc;
         c = cfg_of(dim3(np), dim3(256));
-        JL_CUDA(ctx, cudaLaunchKernelEx(&c, act_to_mx8_kernel, (const void *)act, (int)JL_DT_F32, q2, sf2, F, sfs2, (const int *)nullptr, 0));
+        JL_CUDA(ctx, cudaLaunchKernelEx(&c, act_to_mx8_kernel, (const void *)act, (int)JL_DT_F32, q2, sf2, F, sfs2, (const int *)nullptr, 0,
+                                        ndig, (size_t)np * F));
         ctx->st.launches++;
         p.mode = 1; p.rows = H; p.k = F; p.row_tiles = (H + TC5_ROWS - 1) / TC5_ROWS;
         p.c0 = wd->data; p.c1 = nullptr; p.e0 = wd->scales; p.e1 = nullptr; p.e_stride = wd->scale_stride;
         p.b0 = d->down_bias; p.b1 = nullptr; p.outp = y; p.sfb = sf2; p.sfb_stride = sfs2;
         if (given_ids) { p.outp = out_dev; p.out_rowmap = perm; }
-        if ((rc = MOE_EXP_GEMM(moe_grouped_bs(ctx, p, q2, ntok, s, nattr, at)))) return rc;
+        if ((rc = MOE_EXP_GEMM(grouped(p, q2)))) return rc;
         if (!given_ids) {
             c = cfg_of(dim3(ntok), dim3(256));
             JL_CUDA(ctx, cudaLaunchKernelEx(&c, moe_combine_kernel, out_dev, (const float *)y, (const int32_t *)sel, (const float *)wt,

@@ -78,9 +78,12 @@ __host__ __device__ constexpr int bs_kpos(int i) { return i < 16 ? 2 * i : 2 * (
 // no expert's list). The scale is the smallest power of two that brings the block's amax within e4m3's 448.
 // A warp takes four blocks at a time: lane l holds elements 4 (l % 8) .. + 3 of block l / 8; elements e and e + 16 are
 // neighbours in the permuted order, so lanes q and q + 4 of a block trade their codes and lane q < 4 stores 8 bytes.
+// ndig > 1: the row is written as ndig e4m3 "digits" that share the block scales -- digit d + 1 is the e4m3 rounding of
+// what digits 0..d leave of x / scale (the subtraction is exact in f32) -- into planes `plane` bytes apart. Each digit
+// adds four significant bits: three of them carry an activation to 2^-12 of its block's largest element.
 static __global__ void __launch_bounds__(256)
 act_to_mx8_kernel(const void *__restrict__ x, int x_dtype, uint8_t *__restrict__ q, uint8_t *__restrict__ sf, int k, int sf_stride,
-                  const int *__restrict__ rowmap, int nsrc) {
+                  const int *__restrict__ rowmap, int nsrc, int ndig, size_t plane) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int row = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -123,17 +126,25 @@ act_to_mx8_kernel(const void *__restrict__ x, int x_dtype, uint8_t *__restrict__
             se = max(-126, min(127, se));
         }
         const float sc = __uint_as_float((uint32_t)(127 - se) << 23);
-        uint32_t mine = 0;
+        float t[4];
 #pragma unroll
-        for (int j = 0; j < 4; j++)
-            mine |= (uint32_t)(uint8_t)__nv_cvt_float_to_fp8(v[j] * sc, __NV_SATFINITE, __NV_E4M3) << (8 * j);
-        const uint32_t other = __shfl_xor_sync(0xffffffffu, mine, 4);       // lanes qd and qd + 4: elements e and e + 16
-        if (b < nblk) {
-            if (qd < 4) {
+        for (int j = 0; j < 4; j++) t[j] = v[j] * sc;
+        for (int dgt = 0; dgt < ndig; dgt++) {
+            uint32_t mine = 0;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const __nv_fp8_storage_t c = __nv_cvt_float_to_fp8(t[j], __NV_SATFINITE, __NV_E4M3);
+                mine |= (uint32_t)(uint8_t)c << (8 * j);
+                if (ndig > 1) t[j] -= __half2float(__half(__nv_cvt_fp8_to_halfraw(c, __NV_E4M3)));   // what this digit leaves
+            }
+            const uint32_t other = __shfl_xor_sync(0xffffffffu, mine, 4);   // lanes qd and qd + 4: elements e and e + 16
+            if (b < nblk && qd < 4) {
                 // bytes 8 qd .. 8 qd + 7: elements 4 qd + j (even positions) and 16 + 4 qd + j (odd positions)
                 const uint32_t w0 = __byte_perm(mine, other, 0x5140), w1 = __byte_perm(mine, other, 0x7362);
-                *reinterpret_cast<uint2 *>(q + (size_t)row * k + (size_t)b * 32 + 8 * qd) = make_uint2(w0, w1);
+                *reinterpret_cast<uint2 *>(q + (size_t)dgt * plane + (size_t)row * k + (size_t)b * 32 + 8 * qd) = make_uint2(w0, w1);
             }
+        }
+        if (b < nblk) {
             if (qd == 0) sf[(size_t)row * sf_stride + b] = (uint8_t)(127 + se);
         } else if (b < sf_stride && qd == 0) {
             sf[(size_t)row * sf_stride + b] = 127;                         // padding of the scale row: 2^0
@@ -147,7 +158,7 @@ act_to_mx8_kernel(const void *__restrict__ x, int x_dtype, uint8_t *__restrict__
 template <int NT, int SA, int SB>
 struct moe_bs_smem {
     static constexpr int ACC_COLS = TC5_MS * NT;
-    static constexpr int ACC_BUFS = 2;
+    static constexpr int ACC_BUFS = 2 * ACC_COLS + 2 * BS_SF_COLS <= 512 ? 2 : 1;   // one set: a unit's drain is not overlapped
     static constexpr int B_BYTES = NT * BS_KB;                 // e4m3: one byte per element
     static constexpr int A_OFS = 0;
     static constexpr int B_OFS = SA * TC5_MS * TC5_A_BYTES;    // an A tile is 128 rows x 128 bytes, as in the f16 arm
@@ -157,9 +168,10 @@ struct moe_bs_smem {
     static constexpr int NBARS = 2 * SA + 4;                   // full[SA] empty[SA] acc_full[2] acc_empty[2]
     static_assert(SA == SB, "a stage is one weight tile pair + one activation tile behind one barrier");
     static constexpr int MISC_OFS = BAR_OFS + NBARS * 8;
-    static constexpr int TOTAL = MISC_OFS + 16 + 1024;
+    static constexpr int CNT_OFS = MISC_OFS + 16;              // the experts' list offsets: 257 ints (a length is a difference)
+    static constexpr int TOTAL = CNT_OFS + 1040 + 1024;
     static constexpr int TMEM_COLS = 512;                      // accumulators (ACC_COLS x 2) + two scale-factor sets
-    static_assert(ACC_COLS * ACC_BUFS + 2 * BS_SF_COLS <= TMEM_COLS, "TMEM budget");
+    static_assert(ACC_COLS * ACC_BUFS + 2 * BS_SF_COLS <= TMEM_COLS && NT <= 128, "TMEM budget; one scale atom serves 128 columns");
 };
 
 #ifdef BS_EXP_TRACE        // timing experiment: CTA 0's MMA thread and producer thread stamp their first 512 stages
@@ -175,7 +187,10 @@ __device__ unsigned long long bs_cta_t[2][160][2];     // per launch kind (mode)
 // TMAA: the weight tiles come by TMA as well (tensor maps of packed 4-bit type whose copies leave the 8-byte gaps the
 // instruction wants: nothing touches a code between HBM and the tensor core), and the eight warps only move the
 // scale words. Without it (the driver refused the maps) they also copy the codes through registers.
-template <int NT, int SA, int SB, bool TMAA>
+// T tokens of an expert's list per unit, each as DIG e4m3 digit columns (column d T + t of the tile: digit d of token
+// t), T DIG <= NT = the MMAs' N. One digit: T = NT = 64. Three digits: T = 40 in N = 128 -- the drain adds a token's
+// three columns, which brings the arm inside the parity bar of the exact one at the block-scaled MMAs' speed.
+template <int NT, int T, int DIG, int SA, int SB, bool TMAA>
 __global__ void __launch_bounds__(BS_THREADS, 1)
 moe_gemm_bs_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap amap0,
                    const __grid_constant__ CUtensorMap amap1, const moe_gemm_params p) {
@@ -193,7 +208,7 @@ moe_gemm_bs_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nkb = (p.k + BS_KB - 1) / BS_KB;
     const int nblk = p.k / 32;
-    const int nunits = p.n_expert * p.row_tiles * p.max_tok_tiles;
+    int *s_off = reinterpret_cast<int *>(smem + L::CNT_OFS);
 
     if (tid == 0) {
         for (int s = 0; s < SA; s++) { mbar_init(smem_u32(full + s), BS_EXP_MOVERS * (TC5_DQ_THREADS / 32) + 1); mbar_init(smem_u32(empty + s), BS_ISSUERS); }
@@ -209,12 +224,20 @@ moe_gemm_bs_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
     const uint32_t tmem_base = *tmem_slot;
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    // The list lengths and offsets, once, into shared memory: every role walks the unit list and asks for them at each
+    // unit, live or not (from global memory that is an L2 round trip per unit and role). The walk ends at the longest
+    // list's last token tile.
+    if (tid <= p.n_expert) s_off[tid] = p.off[tid];      // off[n_expert] = the number of listed pairs
+    __syncthreads();
+    int longest = 0;
+    for (int e = 0; e < p.n_expert; e++) longest = max(longest, (s_off[e + 1] - s_off[e]));
+    const int nunits = p.n_expert * p.row_tiles * min(p.max_tok_tiles, (longest + T - 1) / T);
 
 #define BS_UNIT(u)                                                                    \
     const int tt = (u) / (p.n_expert * p.row_tiles);                                  \
     const int e = ((u) / p.row_tiles) % p.n_expert, rt = (u) % p.row_tiles;           \
-    const int m_eff = p.cnt[e], col0 = p.off[e] + tt * NT;                            \
-    const bool live = tt * NT < m_eff;                                                \
+    const int m_eff = (s_off[e + 1] - s_off[e]), col0 = s_off[e] + tt * T;                             \
+    const bool live = tt * T < m_eff;                                                 \
     (void)rt; (void)col0; (void)m_eff
 
 #ifdef BS_EXP_TRACE
@@ -239,13 +262,16 @@ moe_gemm_bs_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
                     // 128 bytes (16 codes in the low half of every 16-byte unit), but the barrier counts the 64 bytes per
                     // row that are copied
 #if defined(BS_EXP_NOA)
-                    mbar_arrive_expect_tx(smem_u32(full + s), L::B_BYTES);
+                    mbar_arrive_expect_tx(smem_u32(full + s), DIG * T * BS_KB);
 #elif defined(BS_EXP_HALFA)
-                    mbar_arrive_expect_tx(smem_u32(full + s), L::B_BYTES + (TMAA ? TC5_A_BYTES / 2 : 0));
+                    mbar_arrive_expect_tx(smem_u32(full + s), DIG * T * BS_KB + (TMAA ? TC5_A_BYTES / 2 : 0));
 #else
-                    mbar_arrive_expect_tx(smem_u32(full + s), L::B_BYTES + (TMAA ? TC5_MS * TC5_A_BYTES / 2 : 0));
+                    mbar_arrive_expect_tx(smem_u32(full + s), DIG * T * BS_KB + (TMAA ? TC5_MS * TC5_A_BYTES / 2 : 0));
 #endif
-                    tma_load_2d(sbase + L::B_OFS + s * L::B_BYTES, &xmap, kb * BS_KB, col0, smem_u32(full + s));
+#pragma unroll
+                    for (int dg = 0; dg < DIG; dg++)       // digit plane dg: rows dg * npairs + position (box: T rows)
+                        tma_load_2d(sbase + L::B_OFS + s * L::B_BYTES + dg * T * BS_KB, &xmap, kb * BS_KB, dg * p.npairs + col0,
+                                    smem_u32(full + s));
                     if (TMAA) {
                         const int y0 = e * p.rows + (p.mode == 0 ? rt * TC5_M : rt * TC5_ROWS);
                         const uint32_t dst = sbase + L::A_OFS + s * TC5_MS * TC5_A_BYTES;
@@ -297,7 +323,7 @@ moe_gemm_bs_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
             for (int u = blockIdx.x; u < nunits && ok; u += gridDim.x) {
                 if (tc5_uniform(*abort_flag)) break;
                 const int e = (u / p.row_tiles) % p.n_expert, tt = u / (p.n_expert * p.row_tiles);
-                if (tt * NT >= tc5_uniform(p.cnt[e])) continue;                        // not a live unit
+                if (tt * T >= tc5_uniform((s_off[e + 1] - s_off[e]))) continue;                         // not a live unit
                 const uint32_t ab = unit_it % L::ACC_BUFS, aph = (unit_it / L::ACC_BUFS) & 1;
                 if (unit_it >= (uint32_t)L::ACC_BUFS)
                     ok = __all_sync(0xffffffffu, tc5_wait(bars_u + 8 * (2 * SA + 2 + ab), aph ^ 1, abort_flag));
@@ -363,14 +389,14 @@ moe_gemm_bs_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
                     if (!live) continue;
                     const int row = p.mode == 0 ? min(rt * TC5_M + (r & 127), p.rows - 1) : min(rt * TC5_ROWS + r, p.rows - 1);
                     ea = reinterpret_cast<const uint32_t *>(eplane + ((size_t)e * p.rows + row) * p.e_stride);
-                    eb = reinterpret_cast<const uint32_t *>(p.sfb + (size_t)min(col0 + (r & (NT - 1)), p.npairs - 1) * p.sfb_stride);
+                    eb = reinterpret_cast<const uint32_t *>(p.sfb + (size_t)min(col0 + r % T, p.npairs - 1) * p.sfb_stride);   // column r: token r % T
                     return;
                 }
             };
             auto load_one = [&](uint32_t &wa, uint32_t &wb) -> bool {
                 if (lu >= nunits) return false;
                 wa = __ldg(ea + lkb);
-                wb = r < NT ? __ldg(eb + lkb) : 0u;
+                wb = r < DIG * T ? __ldg(eb + lkb) : 0x7F7F7F7Fu;
                 if (++lkb == nkb) { lkb = 0; lu += gridDim.x; enter(); }
                 return true;
             };
@@ -407,7 +433,7 @@ moe_gemm_bs_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
             const size_t grow = (size_t)e * p.rows + row;
             const uint8_t *codes = (second ? p.c1 : p.c0) + grow * nblk * 16;
             const uint8_t *ebytes = (second ? p.e1 : p.e0) + grow * p.e_stride;
-            const uint32_t *sfb_row = reinterpret_cast<const uint32_t *>(p.sfb + (size_t)min(col0 + (r & (NT - 1)), p.npairs - 1) * p.sfb_stride);
+            const uint32_t *sfb_row = reinterpret_cast<const uint32_t *>(p.sfb + (size_t)min(col0 + r % T, p.npairs - 1) * p.sfb_stride);
             uint32_t sfbw[BS_PF];                          // threads r < NT: token col0 + r's scale words, BS_PF stages ahead
 #pragma unroll
             for (int j = 0; j < BS_PF; j++) sfbw[j] = (r < NT && j < nkb) ? __ldg(sfb_row + j) : 0x7F7F7F7Fu;
@@ -483,7 +509,61 @@ moe_gemm_bs_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
             if (!tc5_wait_relaxed(smem_u32(acc_full + ab), aph, abort_flag)) break;
             tc5_fence_after();
             const uint32_t tacc = tmem_base + ab * L::ACC_COLS + ((uint32_t)(warp * 32) << 16);
-            const int pos_end = p.off[e] + p.cnt[e];
+            const int pos_end = s_off[e] + (s_off[e + 1] - s_off[e]);
+            if constexpr (DIG > 1) {
+                // a token's DIG digit columns (d T + t) are added, most significant first, eight tokens at a time
+#pragma unroll 1
+                for (int c0 = 0; c0 < T; c0 += 8) {
+                    const int pos0 = col0 + c0;
+                    if (pos0 >= pos_end) break;                          // warp-uniform: the rest of the tile is past the list
+                    if (p.mode == 0) {
+                        float g[8], uu[8];
+                        uint32_t vg[DIG][8], vu[DIG][8];
+#pragma unroll
+                        for (int dg = 0; dg < DIG; dg++) {
+                            tc5_ld8(tacc + dg * T + c0, vg[dg]);
+                            tc5_ld8(tacc + NT + dg * T + c0, vu[dg]);
+                        }
+                        tc5_wait_ld();                                   // one wait for the chunk's 2 DIG loads
+#pragma unroll
+                        for (int dg = 0; dg < DIG; dg++)
+#pragma unroll
+                            for (int j = 0; j < 8; j++) {
+                                g[j] = dg ? g[j] + __uint_as_float(vg[dg][j]) : __uint_as_float(vg[dg][j]);
+                                uu[j] = dg ? uu[j] + __uint_as_float(vu[dg][j]) : __uint_as_float(vu[dg][j]);
+                            }
+                        const int row = rt * TC5_M + warp * 32 + lane;
+                        const float bg = (p.b0 && row < p.rows) ? p.b0[(size_t)e * p.rows + row] : 0.f;
+                        const float bu = (p.b1 && row < p.rows) ? p.b1[(size_t)e * p.rows + row] : 0.f;
+#pragma unroll
+                        for (int j = 0; j < 8; j++) {
+                            const int pos = pos0 + j;
+                            if (row < p.rows && pos < pos_end) p.outp[(size_t)pos * p.rows + row] = moe_act(p.act, g[j] + bg, uu[j] + bu);
+                        }
+                    } else {
+#pragma unroll 1
+                        for (int ms = 0; ms < TC5_MS; ms++) {
+                            float y[8];
+                            uint32_t v[DIG][8];
+#pragma unroll
+                            for (int dg = 0; dg < DIG; dg++) tc5_ld8(tacc + ms * NT + dg * T + c0, v[dg]);
+                            tc5_wait_ld();
+#pragma unroll
+                            for (int dg = 0; dg < DIG; dg++)
+#pragma unroll
+                                for (int j = 0; j < 8; j++) y[j] = dg ? y[j] + __uint_as_float(v[dg][j]) : __uint_as_float(v[dg][j]);
+                            const int row = rt * TC5_ROWS + ms * TC5_M + warp * 32 + lane;
+                            const float bd = (p.b0 && row < p.rows) ? p.b0[(size_t)e * p.rows + row] : 0.f;
+#pragma unroll
+                            for (int j = 0; j < 8; j++) {
+                                const int pos = pos0 + j;
+                                if (row < p.rows && pos < pos_end)
+                                    p.outp[(size_t)(p.out_rowmap ? p.out_rowmap[pos] : pos) * p.rows + row] = y[j] + bd;
+                            }
+                        }
+                    }
+                }
+            } else
 #pragma unroll 1
             for (int c0 = 0; c0 < NT; c0 += 32) {
 #ifdef BS_EXP_NOEPI

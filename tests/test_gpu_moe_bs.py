@@ -85,3 +85,36 @@ def test_block_scaled_arm_matches_its_restatement_and_reports_its_error(dev, orc
     assert parity_err(out2, exact) <= 2e-3
     for w in (gate, up, down):
         dev.Forget(w)
+
+
+@pytest.mark.parametrize("E,topk,hidden,ffn,ntok,act", [(4, 2, 256, 320, 40, ACT_SILU), (8, 4, 128, 128, 7, ACT_SILU),
+                                                         (8, 2, 576, 704, 150, ACT_SWIGLU_OAI), (2, 1, 128, 192, 65, ACT_SILU),
+                                                         (2, 2, 192, 256, 100, ACT_SILU), (16, 4, 2880, 2880, 96, ACT_SWIGLU_OAI)])
+@pytest.mark.parametrize("h_bf16", [True, False])
+def test_three_digit_arm_meets_the_parity_bar(dev, orc, E, topk, hidden, ffn, ntok, act, h_bf16):
+    """Three e4m3 digits per activation (12 significant bits, shared block scale) through the block-scaled MMAs:
+    against the exact oracle, at the exact arm's bar. Covers lists longer than one 40-token tile (several tiles per
+    expert), lists that end inside a tile, and the headline's 2880 width with its half-filled last stage."""
+    from test_gpu_moe import _layer, _oracle
+    rng = synth.rng_for(0x3D + E + hidden + ntok)
+    gate, up, down = _layer(rng, E, hidden, ffn)
+    h = synth.activations(rng, ntok, hidden) * np.float32(0.25)
+    logits = synth.activations(rng, ntok, E)
+    if h_bf16:
+        hin = synth.to_bf16_bits(h)
+        h = synth.bf16_bits_to_f32(hin)
+    else:
+        hin = h
+    out = np.zeros((ntok, hidden), np.float32)
+    sel = np.full((ntok, topk), -7, np.int32)
+    wt = np.full((ntok, topk), np.nan, np.float32)
+    assert dev.MoeHost(out, hin, logits, gate, up, down, E, topk, hidden, ffn, act=act, sel_out=sel, wt_out=wt,
+                       arm=_lib.MOE_ARM_BLOCK_SCALED_X3), dev.Err()
+    exact, rsel, rwt = _oracle(orc, h, logits, gate, up, down, E, topk, hidden, ffn, act=act)
+    assert np.array_equal(sel, rsel) and np.allclose(wt, rwt, rtol=2e-6, atol=0)
+    err = parity_err(out, exact)
+    rms = float(np.sqrt(nmse(out, exact)))
+    print(f"three-digit arm E={E} hidden={hidden} ffn={ffn} ntok={ntok}: largest {err:.2e}, rms {rms:.2e}")
+    assert err <= 2e-3, (err, rms)
+    for w in (gate, up, down):
+        dev.Forget(w)
