@@ -366,7 +366,7 @@ def _brief(line):
     """What the `also` block keeps of a workload's line."""
     if line is None:
         return None
-    keep = ("metric", "value", "unit", "ms_per_step", "steps", "scaling", "config", "roofline", "block_scaled_arm", "e2e",
+    keep = ("metric", "value", "unit", "ms_per_step", "steps", "scaling", "config", "roofline", "arms", "block_scaled_arm", "e2e",
             "gpu_launches", "clocks")
     return {k: line[k] for k in keep if k in line}
 

@@ -236,8 +236,9 @@ def run_moe_ep(args, emit=True):
     hs = [dev.Upload(MXFP4, synth.mxfp4_matrix(rng, epr * r, kk), r, kk, epr) for r, kk in ((ffn, hidden), (ffn, hidden), (hidden, ffn))]
     dev.MoeReserve(ntok_all * topk, max(E, epr), topk, hidden, ffn)
     d_route = MoeDesc(struct_size=C.sizeof(MoeDesc), type=MXFP4, n_expert=E, top_k=topk, hidden=hidden, ffn=ffn, act=0, norm=1, scale=1.0)
+    from jitllm_b200._lib import MOE_ARM_BLOCK_SCALED_X3
     d_local = MoeDesc(struct_size=C.sizeof(MoeDesc), type=MXFP4, n_expert=epr, top_k=1, hidden=hidden, ffn=ffn, act=0, norm=1,
-                      scale=1.0, gate=hs[0].handle, up=hs[1].handle, down=hs[2].handle)
+                      scale=1.0, gate=hs[0].handle, up=hs[1].handle, down=hs[2].handle, arm=MOE_ARM_BLOCK_SCALED_X3)
 
     def route(lg):
         sel = torch.empty(lg.shape[0], topk, dtype=torch.int32, device="cuda")
@@ -303,8 +304,9 @@ def run_moe_ep(args, emit=True):
         line = ({
             "metric": "mxfp4_moe_layers_per_s", "value": 1e6 / us, "unit": "layers/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "MXFP4 -> f16, bf16->f16 activations, f32 accumulate (tcgen05 kind::f16)", "data": "synthetic",
-            "config": {"workload": "mxfp4_moe_gptoss", **MOE, "parallelism": f"ep{world}: {epr} experts and {ntok} tokens per rank",
+            "vs_baseline": None, "dtype": "MXFP4 codes and e8m0 scales x three e4m3 digits per activation, f32 accumulate (tcgen05 kind::mxf8f6f4.block_scale)",
+            "data": "synthetic",
+            "config": {"workload": "mxfp4_moe_gptoss", **MOE, "arm": "block_scaled_x3", "parallelism": f"ep{world}: {epr} experts and {ntok} tokens per rank",
                        "us_per_layer": us, "launch": launch, "exchange": "fixed capacity (tokens x top_k slots per destination, unused slots skipped by the experts)",
                        "l2": "one layer of experts per rank, re-read every step: the per-rank working set is below L2 at 8 ranks"},
             "roofline": {"bound": "hbm", "achieved": wbytes_rank / us / 1e3, "peak": hbm, "unit": "GB/s",
@@ -353,27 +355,37 @@ def run_moe(args, emit=True):
     per_replay = dev.Stats().launches - n0
     ms, clocks = _timed_replays(torch, g, args.steps, args.warmup, local)
     us = ms * 1e3 / (args.steps * MOE["layers"])
-    # the block-scaled arm on the same layers and inputs: its time, and its error against the exact arm's output
-    from jitllm_b200._lib import MOE_ARM_BLOCK_SCALED
-    bs_descs = []
-    for d in descs:
-        b = MoeDesc.from_buffer_copy(d)
-        b.arm = MOE_ARM_BLOCK_SCALED
-        bs_descs.append(b)
+    # the two block-scaled arms on the same layers and inputs: their time, and their error against the exact arm's output
+    # in the tests' parity measure (largest |difference| over max(|exact|, rms(exact)); bar 2e-3)
+    from jitllm_b200._lib import MOE_ARM_BLOCK_SCALED, MOE_ARM_BLOCK_SCALED_X3
     st0 = torch.cuda.current_stream().cuda_stream
-    o_exact, o_bs = torch.zeros_like(out), torch.zeros_like(out)
+    o_exact = torch.zeros_like(out)
     dev.MoeDev(o_exact, h, logits, ntok, descs[0], None, None, st0)
-    dev.MoeDev(o_bs, h, logits, ntok, bs_descs[0], None, None, st0)
     torch.cuda.synchronize()
-    diff = (o_bs - o_exact).double()
-    bs_rms = float(diff.pow(2).sum().sqrt() / o_exact.double().pow(2).sum().sqrt())
-    bs_max = float((diff.abs() / torch.maximum(o_exact.double().abs(), o_exact.double().pow(2).mean().sqrt())).max())
-    g2, cap2 = torch.cuda.CUDAGraph(), torch.cuda.Stream()
-    with torch.cuda.graph(g2, stream=cap2):
-        for d in bs_descs:
-            dev.MoeDev(out, h, logits, ntok, d, None, None, torch.cuda.current_stream().cuda_stream)
-    ms_bs, clocks_bs = _timed_replays(torch, g2, args.steps, args.warmup, local)
-    us_bs = ms_bs * 1e3 / (args.steps * MOE["layers"])
+
+    def other_arm(arm):
+        ds = []
+        for d in descs:
+            b = MoeDesc.from_buffer_copy(d)
+            b.arm = arm
+            ds.append(b)
+        o = torch.zeros_like(out)
+        dev.MoeDev(o, h, logits, ntok, ds[0], None, None, st0)
+        torch.cuda.synchronize()
+        diff, ref = (o - o_exact).double(), o_exact.double()
+        rms_ref = ref.pow(2).mean().sqrt()
+        err = {"rms_rel": float(diff.pow(2).sum().sqrt() / ref.pow(2).sum().sqrt()),
+               "largest_rel": float((diff.abs() / torch.maximum(ref.abs(), rms_ref)).max())}
+        g2, cap2 = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+        with torch.cuda.graph(g2, stream=cap2):
+            for d in ds:
+                dev.MoeDev(out, h, logits, ntok, d, None, None, torch.cuda.current_stream().cuda_stream)
+        ms2, clocks2 = _timed_replays(torch, g2, args.steps, args.warmup, local)
+        return ms2 * 1e3 / (args.steps * MOE["layers"]), ms2, clocks2, err
+    us_bs, _, clocks_bs, err_bs = other_arm(MOE_ARM_BLOCK_SCALED)
+    us_x3, ms_x3, clocks_x3, err_x3 = other_arm(MOE_ARM_BLOCK_SCALED_X3)
+    bs_rms, bs_max = err_bs["rms_rel"], err_bs["largest_rel"]
+    x3_ok = err_x3["largest_rel"] <= 2e-3          # the three-digit arm is the headline only while it is inside the bar HERE
     wbytes = E * 3 * hidden * (ffn // 32) * 17
     abytes = wbytes + ntok * hidden * 2 + ntok * E * 4 + ntok * hidden * 4
     fl = ntok * topk * 3 * 2.0 * hidden * ffn
@@ -383,23 +395,39 @@ def run_moe(args, emit=True):
     h_host = synth.to_bf16_bits(synth.activations(rng, ntok, hidden))
     lg_host = synth.activations(rng, ntok, E)
     out_host = np.zeros((ntok, hidden), np.float32)
-    assert dev.MoeHost(out_host, h_host, lg_host, hg, hu, hd, E, topk, hidden, ffn), dev.Err()
+    arm_e2e = MOE_ARM_BLOCK_SCALED_X3 if x3_ok else 0          # the headline's arm
+    assert dev.MoeHost(out_host, h_host, lg_host, hg, hu, hd, E, topk, hidden, ffn, arm=arm_e2e), dev.Err()
     n_e2e = 10
     t0 = time.perf_counter()
     for _ in range(n_e2e):
-        dev.MoeHost(out_host, h_host, lg_host, hg, hu, hd, E, topk, hidden, ffn)
+        dev.MoeHost(out_host, h_host, lg_host, hg, hu, hd, E, topk, hidden, ffn, arm=arm_e2e)
     e2e_layers = n_e2e / (time.perf_counter() - t0)
     hbm, burst, sustained, which = _peaks()
+    us_exact, ms_exact, clocks_exact = us, ms, clocks
+    if x3_ok:
+        us, ms, clocks = us_x3, ms_x3, clocks_x3
     line = ({
         "metric": "mxfp4_moe_layers_per_s", "value": 1e6 / us, "unit": "layers/s", "n_gpus": 1, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "MXFP4 -> f16 (cvt e2m1x2), bf16->f16 activations, f32 accumulate (tcgen05 kind::f16)",
+        "vs_baseline": None,
+        "dtype": ("MXFP4 codes and e8m0 scales as they are x three e4m3 digits per activation (ue8m0 per 32), f32 accumulate "
+                  "(tcgen05 kind::mxf8f6f4.block_scale)") if x3_ok else
+                 "MXFP4 -> f16 (cvt e2m1x2), bf16->f16 activations, f32 accumulate (tcgen05 kind::f16)",
         "data": "synthetic",
         "config": {"workload": "mxfp4_moe_gptoss", **MOE, "us_per_layer": us, "useful_tflops": fl / us / 1e6,
+                   "arm": "block_scaled_x3 (the fastest arm inside the 2e-3 parity bar in this run)" if x3_ok else "exact_f16",
                    "l2": "2 distinct layers of experts (846 MB) alternate: larger than L2"},
         "roofline": {"bound": "hbm", "achieved": abytes / us / 1e3, "peak": hbm, "unit": "GB/s", "frac": abytes / us / 1e3 / hbm,
-                     "of": which, "kernel": "moe_gemm_kernel (gate|up, down)", "traffic": None,
-                     "algorithmic_bytes_per_layer": abytes},
+                     "of": which, "kernel": "moe_gemm_bs_kernel<128,40,3> (gate|up, down)" if x3_ok else "moe_gemm_kernel (gate|up, down)",
+                     "traffic": None, "algorithmic_bytes_per_layer": abytes},
+        "arms": {
+            "exact_f16": {"us_per_layer": us_exact, "hbm_frac": abytes / us_exact / 1e3 / hbm, "kernel": "moe_gemm_kernel",
+                          "clocks": clocks_exact},
+            "block_scaled_x3": {"us_per_layer": us_x3, "hbm_frac": abytes / us_x3 / 1e3 / hbm,
+                                "kernel": "moe_gemm_bs_kernel<128,40,3>", "error_vs_exact_arm": err_x3, "inside_parity_bar": x3_ok,
+                                "clocks": clocks_x3},
+            "block_scaled": {"us_per_layer": us_bs, "hbm_frac": abytes / us_bs / 1e3 / hbm, "kernel": "moe_gemm_bs_kernel<64,64,1>",
+                             "error_vs_exact_arm": err_bs, "inside_parity_bar": False}},
         "block_scaled_arm": {"us_per_layer": us_bs, "layers_per_s": 1e6 / us_bs, "hbm_gbs": abytes / us_bs / 1e3,
                              "hbm_frac": abytes / us_bs / 1e3 / hbm, "useful_tflops": fl / us_bs / 1e6,
                              "kernel": "moe_gemm_bs_kernel (tcgen05 kind::mxf8f6f4.block_scale; activations e4m3 + ue8m0 per 32)",
@@ -639,7 +667,7 @@ def sharded_parity(local):
     import torch
     import torch.distributed as dist
     from jitllm_b200 import Device, parallel, synth
-    from jitllm_b200._lib import MXFP4, MoeDesc
+    from jitllm_b200._lib import MOE_ARM_BLOCK_SCALED_X3, MXFP4, MoeDesc
     from jitllm_b200.decoder import Config, Decoder
     world, rank, _ = _env()
     dev = Device(local)
@@ -692,7 +720,8 @@ def sharded_parity(local):
         d_full = MoeDesc(struct_size=C.sizeof(MoeDesc), type=MXFP4, n_expert=E, top_k=topk, hidden=hidden, ffn=ffn, act=0, norm=1,
                          scale=1.0, gate=full[0].handle, up=full[1].handle, down=full[2].handle)
         d_local = MoeDesc(struct_size=C.sizeof(MoeDesc), type=MXFP4, n_expert=epr, top_k=1, hidden=hidden, ffn=ffn, act=0, norm=1,
-                          scale=1.0, gate=mine[0].handle, up=mine[1].handle, down=mine[2].handle)
+                          scale=1.0, gate=mine[0].handle, up=mine[1].handle, down=mine[2].handle,
+                          arm=MOE_ARM_BLOCK_SCALED_X3)      # the arm the sharded bench runs; the unsharded side is the exact arm
         g = torch.Generator(device="cuda").manual_seed(100 + rank)          # every rank routes its own tokens
         h = (torch.randn(ntok, hidden, device="cuda", generator=g) * 0.25).to(torch.bfloat16)
         logits = torch.randn(ntok, E, device="cuda", generator=g)

@@ -118,3 +118,34 @@ def test_three_digit_arm_meets_the_parity_bar(dev, orc, E, topk, hidden, ffn, nt
     assert err <= 2e-3, (err, rms)
     for w in (gate, up, down):
         dev.Forget(w)
+
+
+@pytest.mark.parametrize("arm", [_lib.MOE_ARM_EXACT, _lib.MOE_ARM_BLOCK_SCALED_X3])
+def test_experts_over_routed_rows_with_each_parity_arm(dev, orc, arm):
+    """The expert-parallel entry (rows already routed, one expert id per row, -1 = no expert: the row is skipped),
+    on device tensors, for both arms that meet the bar."""
+    import ctypes as C
+
+    import torch
+    from jitllm_b200._lib import MoeDesc
+    from test_gpu_moe import _layer
+    E, hidden, ffn, n = 4, 192, 256, 150
+    rng = synth.rng_for(0xE9 + arm)
+    gate, up, down = _layer(rng, E, hidden, ffn)
+    h = synth.activations(rng, n, hidden) * np.float32(0.25)
+    ids = rng.integers(0, E, size=n).astype(np.int32)
+    ids[::7] = -1
+    hg, hu, hd = dev.Upload(MXFP4, gate, ffn, hidden, E), dev.Upload(MXFP4, up, ffn, hidden, E), dev.Upload(MXFP4, down, hidden, ffn, E)
+    dev.MoeReserve(n, E, 1, hidden, ffn)
+    d = MoeDesc(struct_size=C.sizeof(MoeDesc), type=MXFP4, n_expert=E, top_k=1, hidden=hidden, ffn=ffn, act=ACT_SILU, norm=1,
+                scale=1.0, gate=hg.handle, up=hu.handle, down=hd.handle, arm=arm)
+    y = torch.full((n, hidden), 123.0, device="cuda")
+    dev.MoeExpertsDev(y, torch.from_numpy(h).cuda(), torch.from_numpy(ids).cuda(), n, d, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    got = y.cpu().numpy()
+    live = ids >= 0
+    want = orc.moe_layer(h[live], MXFP4, gate, up, down, ids[live][:, None], np.ones((int(live.sum()), 1), np.float32), E, hidden, ffn)
+    assert parity_err(got[live], want) <= 2e-3
+    assert np.all(got[~live] == 123.0)                                   # skipped rows are not touched
+    for w in (hg, hu, hd):
+        w.free()

@@ -140,6 +140,13 @@ def _worker(rank, world, port, tmp):
                           torch.from_numpy(logits[lo:hi]).cuda())
         torch.cuda.synchronize()
         assert parity_err(got.cpu().numpy(), want[lo:hi]) <= BAR, nmse(got.cpu().numpy(), want[lo:hi])
+        # the same through the three-digit block-scaled arm (the other arm inside the bar)
+        from jitllm_b200._lib import MOE_ARM_BLOCK_SCALED_X3
+        d_local.arm = MOE_ARM_BLOCK_SCALED_X3
+        got = moe.forward(torch.zeros(hi - lo, hidden, device="cuda"), torch.from_numpy(h[lo:hi]).cuda(),
+                          torch.from_numpy(logits[lo:hi]).cuda())
+        torch.cuda.synchronize()
+        assert parity_err(got.cpu().numpy(), want[lo:hi]) <= BAR, nmse(got.cpu().numpy(), want[lo:hi])
         open(os.path.join(tmp, f"ok{rank}"), "w").write("ok")
         dev.Close()
     finally:
