@@ -135,6 +135,16 @@ __device__ __forceinline__ void bk_bf16x8(const uint4 &v, float *f) {
     }
 }
 
+// Between two polls of a value that has not arrived: every waiting thread of every CTA re-reads L2, and those reads
+// queue in front of the loads of the CTAs that still produce.
+#ifndef BK_POLL_SLEEP_NS
+#define BK_POLL_SLEEP_NS 0
+#endif
+#if BK_POLL_SLEEP_NS > 0
+#define BK_POLL_PAUSE() __nanosleep(BK_POLL_SLEEP_NS)
+#else
+#define BK_POLL_PAUSE() do { } while (0)
+#endif
 __device__ __forceinline__ uint4 bk_ld_vol16(const void *p) {
     uint4 v;
     asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
@@ -152,6 +162,7 @@ __device__ __forceinline__ bool bk_ll_read2(const bk_ll *p, unsigned seq, float2
     if (a.y != seq || a.w != seq) {
         const uint64_t t0 = jl_gtime_ns();
         for (uint32_t i = 0;; i++) {
+            BK_POLL_PAUSE();
             a = bk_ld_vol16(p);
             if (a.y == seq && a.w == seq) break;
             if ((i & 7u) == 7u) { BK_DIAG_ITER(i); if (bk_ll_giveup(P, t0, limit_ns, code)) return false; }
@@ -165,6 +176,7 @@ __device__ __forceinline__ bool bk_ll_read4(const bk_ll *p, unsigned seq, float4
     if (a.y != seq || a.w != seq || b.y != seq || b.w != seq) {
         const uint64_t t0 = jl_gtime_ns();
         for (uint32_t i = 0;; i++) {
+            BK_POLL_PAUSE();
             a = bk_ld_vol16(p); b = bk_ld_vol16(p + 2);
             if (a.y == seq && a.w == seq && b.y == seq && b.w == seq) break;
             if ((i & 7u) == 7u) { BK_DIAG_ITER(i); if (bk_ll_giveup(P, t0, limit_ns, code)) return false; }

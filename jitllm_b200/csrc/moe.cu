@@ -24,15 +24,10 @@
 
 // ------------------------------------------------------------------ route
 
-// One warp per token. n_expert <= 256.
-__global__ void __launch_bounds__(128)
-moe_route_kernel(const float *__restrict__ logits, const float *__restrict__ router_bias,
-                 const float *__restrict__ sel_bias, int ntok, int n_expert, int top_k, int norm, float scale,
-                 int32_t *__restrict__ sel, float *__restrict__ wt) {
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    const int tok = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (tok >= ntok) return;
+// One token by one warp. n_expert <= 256.
+__device__ __forceinline__ void moe_route_token(const float *__restrict__ logits, const float *__restrict__ router_bias,
+                                                const float *__restrict__ sel_bias, int tok, int lane, int n_expert, int top_k,
+                                                int norm, float scale, int32_t *sel, float *wt) {
     float lg[8], pr[8];
     double mx = -INFINITY;
 #pragma unroll
@@ -97,6 +92,17 @@ moe_route_kernel(const float *__restrict__ logits, const float *__restrict__ rou
     }
 }
 
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const float *__restrict__ logits, const float *__restrict__ router_bias,
+                 const float *__restrict__ sel_bias, int ntok, int n_expert, int top_k, int norm, float scale,
+                 int32_t *__restrict__ sel, float *__restrict__ wt) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int tok = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (tok >= ntok) return;
+    moe_route_token(logits, router_bias, sel_bias, tok, lane, n_expert, top_k, norm, scale, sel, wt);
+}
+
 // ------------------------------------------------------------------- sort
 
 // Stable counting sort of the pairs by expert, one CTA of 256 threads.
@@ -104,14 +110,12 @@ moe_route_kernel(const float *__restrict__ logits, const float *__restrict__ rou
 //   pos_of[tok * k + slot] = sorted position of that pair (or -1 for an unfilled slot)
 // Counts by shared-memory atomics; placement by ONE warp walking the pairs 32 at a time in
 // order, ranking equal ids inside a chunk with __match_any_sync, so positions keep token order.
-__global__ void __launch_bounds__(256)
-moe_sort_kernel(const int32_t *__restrict__ sel, int npairs, int top_k, int n_expert, int *__restrict__ cnt,
-                int *__restrict__ off, int *__restrict__ perm_tok, int *__restrict__ pos_of) {
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+// (`sel` is deliberately not __restrict__: in the fused kernel the same CTA has just written it.)
+__device__ __forceinline__ void moe_sort_cta(const int32_t *sel, int npairs, int top_k, int n_expert, int *__restrict__ cnt,
+                                             int *__restrict__ off, int *__restrict__ perm_tok, int *__restrict__ pos_of) {
     __shared__ int s_cnt[256], s_base[257];
     const int tid = threadIdx.x;
-    s_cnt[tid] = 0;
+    if (tid < 256) s_cnt[tid] = 0;
     __syncthreads();
     for (int i = tid; i < npairs; i += blockDim.x) {
         const int id = sel[i];
@@ -125,7 +129,7 @@ moe_sort_kernel(const int32_t *__restrict__ sel, int npairs, int top_k, int n_ex
         s_base[n_expert] = acc;
     }
     __syncthreads();
-    if (tid <= n_expert) off[tid] = s_base[tid];
+    for (int i = tid; i <= n_expert; i += blockDim.x) off[i] = s_base[i];
     if (tid < n_expert) cnt[tid] = s_cnt[tid];
     __syncthreads();                                   // off[] is read back below by every thread
     if (tid < 32) {
@@ -149,6 +153,31 @@ moe_sort_kernel(const int32_t *__restrict__ sel, int npairs, int top_k, int n_ex
     // positions of the list unused: name token 0 there, so that the gather that walks all npairs positions reads a
     // real row (nothing consumes those positions).
     for (int i = off[n_expert] + tid; i < npairs; i += blockDim.x) perm_tok[i] = 0;
+}
+
+__global__ void __launch_bounds__(256)
+moe_sort_kernel(const int32_t *__restrict__ sel, int npairs, int top_k, int n_expert, int *__restrict__ cnt,
+                int *__restrict__ off, int *__restrict__ perm_tok, int *__restrict__ pos_of) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    moe_sort_cta(sel, npairs, top_k, n_expert, cnt, off, perm_tok, pos_of);
+}
+
+// Router and sort of a small batch in ONE launch of one CTA (32 warps route the tokens in turn, then the CTA sorts
+// what it has just written): the two are a dependent pair of few-microsecond kernels, and at a few hundred tokens
+// the launch boundary between them costs as much as either.
+#define MOE_FUSED_ROUTE_MAX_TOK 512
+__global__ void __launch_bounds__(1024)
+moe_route_sort_kernel(const float *__restrict__ logits, const float *__restrict__ router_bias, const float *__restrict__ sel_bias,
+                      int ntok, int n_expert, int top_k, int norm, float scale, int32_t *sel, float *wt,
+                      int *__restrict__ cnt, int *__restrict__ off, int *__restrict__ perm_tok, int *__restrict__ pos_of) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int tok = warp; tok < ntok; tok += 32)
+        moe_route_token(logits, router_bias, sel_bias, tok, lane, n_expert, top_k, norm, scale, sel, wt);
+    __syncthreads();                       // the CTA's own global writes of sel are visible to it after the barrier
+    moe_sort_cta(sel, ntok * top_k, top_k, n_expert, cnt, off, perm_tok, pos_of);
 }
 
 // ---------------------------------------------------------------- combine
@@ -697,14 +726,21 @@ static int moe_dev_locked(jl_ctx *ctx, float *out_dev, const void *h_dev, int h_
     const int nattr = (ctx->opts.flags & JL_FLAG_NO_PDL) ? 0 : 1;
     auto cfg_of = [&](dim3 g, dim3 b) { cudaLaunchConfig_t c = {}; c.gridDim = g; c.blockDim = b; c.stream = s; c.attrs = at; c.numAttrs = nattr; return c; };
     {
-        cudaLaunchConfig_t c = cfg_of(dim3((ntok + 3) / 4), dim3(128));
-        if (!given_ids) {
-            JL_CUDA(ctx, cudaLaunchKernelEx(&c, moe_route_kernel, logits_dev, d->router_bias, d->sel_bias, ntok, E, K, d->norm, d->scale, sel, wt));
+        if (!given_ids && ntok <= MOE_FUSED_ROUTE_MAX_TOK) {
+            cudaLaunchConfig_t c = cfg_of(dim3(1), dim3(1024));
+            JL_CUDA(ctx, cudaLaunchKernelEx(&c, moe_route_sort_kernel, logits_dev, d->router_bias, d->sel_bias, ntok, E, K, d->norm,
+                                            d->scale, sel, wt, cnt, off, perm, pos_of));
+            ctx->st.launches++;
+        } else {
+            cudaLaunchConfig_t c = cfg_of(dim3((ntok + 3) / 4), dim3(128));
+            if (!given_ids) {
+                JL_CUDA(ctx, cudaLaunchKernelEx(&c, moe_route_kernel, logits_dev, d->router_bias, d->sel_bias, ntok, E, K, d->norm, d->scale, sel, wt));
+                ctx->st.launches++;
+            }
+            c = cfg_of(dim3(1), dim3(256));
+            JL_CUDA(ctx, cudaLaunchKernelEx(&c, moe_sort_kernel, (const int32_t *)sel, np, K, E, cnt, off, perm, pos_of));
             ctx->st.launches++;
         }
-        c = cfg_of(dim3(1), dim3(256));
-        JL_CUDA(ctx, cudaLaunchKernelEx(&c, moe_sort_kernel, (const int32_t *)sel, np, K, E, cnt, off, perm, pos_of));
-        ctx->st.launches++;
     }
     if (d->arm != JL_MOE_ARM_EXACT) {
         // The block-scaled arms: activations to e4m3 + ue8m0 per 32 (twice: the routed rows, then the gated
