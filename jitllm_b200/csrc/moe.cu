@@ -110,15 +110,14 @@ moe_route_kernel(const float *__restrict__ logits, const float *__restrict__ rou
 //   pos_of[tok * k + slot] = sorted position of that pair (or -1 for an unfilled slot)
 // Counts by shared-memory atomics; placement by ONE warp walking the pairs 32 at a time in
 // order, ranking equal ids inside a chunk with __match_any_sync, so positions keep token order.
-// (`sel` is deliberately not __restrict__: in the fused kernel the same CTA has just written it.)
 __device__ __forceinline__ void moe_sort_cta(const int32_t *sel, int npairs, int top_k, int n_expert, int *__restrict__ cnt,
                                              int *__restrict__ off, int *__restrict__ perm_tok, int *__restrict__ pos_of) {
     __shared__ int s_cnt[256], s_base[257];
     const int tid = threadIdx.x;
-    if (tid < 256) s_cnt[tid] = 0;
+    for (int i = tid; i < 256; i += blockDim.x) s_cnt[i] = 0;
     __syncthreads();
     for (int i = tid; i < npairs; i += blockDim.x) {
-        const int id = sel[i];
+        const int id = __ldcg(sel + i);
         if (id >= 0 && id < n_expert) atomicAdd(&s_cnt[id], 1);
         else pos_of[i] = -1;
     }
@@ -130,12 +129,12 @@ __device__ __forceinline__ void moe_sort_cta(const int32_t *sel, int npairs, int
     }
     __syncthreads();
     for (int i = tid; i <= n_expert; i += blockDim.x) off[i] = s_base[i];
-    if (tid < n_expert) cnt[tid] = s_cnt[tid];
+    for (int i = tid; i < n_expert; i += blockDim.x) cnt[i] = s_cnt[i];
     __syncthreads();                                   // off[] is read back below by every thread
     if (tid < 32) {
         for (int c = 0; c < npairs; c += 32) {
             const int i = c + tid;
-            const int id = i < npairs ? sel[i] : -1;
+            const int id = i < npairs ? __ldcg(sel + i) : -1;
             const bool ok = id >= 0 && id < n_expert;
             const unsigned same = __match_any_sync(0xffffffffu, ok ? id : -1 - tid);   // invalid ids match nobody
             if (ok) {
@@ -161,23 +160,6 @@ moe_sort_kernel(const int32_t *__restrict__ sel, int npairs, int top_k, int n_ex
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     moe_sort_cta(sel, npairs, top_k, n_expert, cnt, off, perm_tok, pos_of);
-}
-
-// Router and sort of a small batch in ONE launch of one CTA (32 warps route the tokens in turn, then the CTA sorts
-// what it has just written): the two are a dependent pair of few-microsecond kernels, and at a few hundred tokens
-// the launch boundary between them costs as much as either.
-#define MOE_FUSED_ROUTE_MAX_TOK 512
-__global__ void __launch_bounds__(1024)
-moe_route_sort_kernel(const float *__restrict__ logits, const float *__restrict__ router_bias, const float *__restrict__ sel_bias,
-                      int ntok, int n_expert, int top_k, int norm, float scale, int32_t *sel, float *wt,
-                      int *__restrict__ cnt, int *__restrict__ off, int *__restrict__ perm_tok, int *__restrict__ pos_of) {
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int tok = warp; tok < ntok; tok += 32)
-        moe_route_token(logits, router_bias, sel_bias, tok, lane, n_expert, top_k, norm, scale, sel, wt);
-    __syncthreads();                       // the CTA's own global writes of sel are visible to it after the barrier
-    moe_sort_cta(sel, ntok * top_k, top_k, n_expert, cnt, off, perm_tok, pos_of);
 }
 
 // ---------------------------------------------------------------- combine
@@ -726,21 +708,17 @@ static int moe_dev_locked(jl_ctx *ctx, float *out_dev, const void *h_dev, int h_
     const int nattr = (ctx->opts.flags & JL_FLAG_NO_PDL) ? 0 : 1;
     auto cfg_of = [&](dim3 g, dim3 b) { cudaLaunchConfig_t c = {}; c.gridDim = g; c.blockDim = b; c.stream = s; c.attrs = at; c.numAttrs = nattr; return c; };
     {
-        if (!given_ids && ntok <= MOE_FUSED_ROUTE_MAX_TOK) {
-            cudaLaunchConfig_t c = cfg_of(dim3(1), dim3(1024));
-            JL_CUDA(ctx, cudaLaunchKernelEx(&c, moe_route_sort_kernel, logits_dev, d->router_bias, d->sel_bias, ntok, E, K, d->norm,
-                                            d->scale, sel, wt, cnt, off, perm, pos_of));
-            ctx->st.launches++;
-        } else {
-            cudaLaunchConfig_t c = cfg_of(dim3((ntok + 3) / 4), dim3(128));
-            if (!given_ids) {
-                JL_CUDA(ctx, cudaLaunchKernelEx(&c, moe_route_kernel, logits_dev, d->router_bias, d->sel_bias, ntok, E, K, d->norm, d->scale, sel, wt));
-                ctx->st.launches++;
-            }
-            c = cfg_of(dim3(1), dim3(256));
-            JL_CUDA(ctx, cudaLaunchKernelEx(&c, moe_sort_kernel, (const int32_t *)sel, np, K, E, cnt, off, perm, pos_of));
+        // (Router and sort as ONE launch were built twice and measured slower: a single CTA routing all tokens, +65 us
+        // per layer -- the f64 softmax of 256 tokens on one SM; and the router's last CTA, by ticket, sorting, +7 us.
+        // With programmatic dependent launch the boundary between the two costs less than either fusion.)
+        cudaLaunchConfig_t c = cfg_of(dim3((ntok + 3) / 4), dim3(128));
+        if (!given_ids) {
+            JL_CUDA(ctx, cudaLaunchKernelEx(&c, moe_route_kernel, logits_dev, d->router_bias, d->sel_bias, ntok, E, K, d->norm, d->scale, sel, wt));
             ctx->st.launches++;
         }
+        c = cfg_of(dim3(1), dim3(256));
+        JL_CUDA(ctx, cudaLaunchKernelEx(&c, moe_sort_kernel, (const int32_t *)sel, np, K, E, cnt, off, perm, pos_of));
+        ctx->st.launches++;
     }
     if (d->arm != JL_MOE_ARM_EXACT) {
         // The block-scaled arms: activations to e4m3 + ue8m0 per 32 (twice: the routed rows, then the gated

@@ -30,7 +30,7 @@ def _oracle(orc, h, logits, gate, up, down, E, topk, hidden, ffn, act=0, **bias)
 
 @pytest.mark.parametrize("E,topk,hidden,ffn,ntok", [(8, 2, 128, 192, 20), (4, 4, 64, 64, 3), (16, 4, 256, 320, 70),
                                                      (8, 1, 192, 128, 9),
-                                                     (4, 2, 64, 64, 600)])     # above 512 tokens: router and sort as two launches
+                                                     (4, 2, 64, 64, 600)])
 @pytest.mark.parametrize("h_bf16", [True, False])
 def test_moe_layer_matches_oracle(dev, orc, E, topk, hidden, ffn, ntok, h_bf16):
     rng = synth.rng_for(1000 + E + hidden + ntok)
