@@ -170,6 +170,14 @@ __device__ __forceinline__ void aux_bf16x8(const uint4 &v, float *f) {
     }
 }
 
+// D (16 x 8, f32) += A (16 x 16 bf16, row) * B (16 x 8 bf16, col).
+__device__ __forceinline__ void aux_mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                             uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
 template <int G>
 __global__ void __launch_bounds__(128) aux_attn_decode_kernel(float *out, uint8_t *operand, const __nv_bfloat16 *q,
                                                               const __nv_bfloat16 *k_cache, const __nv_bfloat16 *v_cache,
@@ -180,9 +188,7 @@ __global__ void __launch_bounds__(128) aux_attn_decode_kernel(float *out, uint8_
     // K and V tiles of the chunk, staged with coalesced 16-byte loads (all in flight at once); the
     // cross-group reduction buffer red[8][G][128] reuses the tiles once they have been consumed.
     __shared__ __align__(16) uint8_t tiles[2 * ATT_CHUNK * ATT_ROW];
-    static_assert(8 * G * ATT_D * 4 <= 2 * ATT_CHUNK * ATT_ROW, "reduction buffer must fit in the tiles");
-    __shared__ float qs[G][ATT_D];
-    __shared__ float sc[G][ATT_CHUNK];
+    static_assert(4 * G * ATT_D * 4 <= 2 * ATT_CHUNK * ATT_ROW, "reduction buffer must fit in the tiles");
     __shared__ float mred[4][G], lred[4][G];
     __shared__ unsigned last;
     const int split = blockIdx.x, kv = blockIdx.y, row = blockIdx.z, t = threadIdx.x, hq = hkv * G;
@@ -206,8 +212,21 @@ __global__ void __launch_bounds__(128) aux_attn_decode_kernel(float *out, uint8_
             const int piece = i * 128 + t;
             vreg[i] = (piece >> 4) < cnt ? vg[piece] : make_uint4(0, 0, 0, 0);
         }
-        for (int i = t; i < G * ATT_D; i += 128)
-            qs[i / ATT_D][i % ATT_D] = __bfloat162float(q[((size_t)row * hq + kv * G) * ATT_D + i]) * 0.08838834764831845f;
+        // Scores and the weighted sum of V run on the tensor cores (mma.sync m16n8k16, bf16 in, f32 accumulate): the M
+        // rows are the group's G query heads (rows G..15 are zero), a warp takes 16 of the chunk's 64 positions. q and
+        // the cached K, V are bf16 as stored, so the products are exact; the softmax weights go in as a bf16 pair
+        // (value + what the first rounding left: 16 significant bits). Per byte of cache this is a quarter of the
+        // instructions of a scalar loop, which is what bounded the kernel at batch 64.
+        const int warp = t >> 5, lane = t & 31, g = lane >> 2, tq = lane & 3;
+        uint32_t qa[8][2];                                      // A fragments of q: k-step s covers dims 16 s .. 16 s + 15
+        {
+            const uint32_t *qrow = reinterpret_cast<const uint32_t *>(q + ((size_t)row * hq + kv * G + (g < G ? g : 0)) * ATT_D);
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+                qa[ks][0] = g < G ? __ldg(qrow + ks * 8 + tq) : 0u;            // dims 16 ks + 2 tq, + 1
+                qa[ks][1] = g < G ? __ldg(qrow + ks * 8 + 4 + tq) : 0u;        // dims 16 ks + 8 + 2 tq, + 1
+            }
+        }
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             const int piece = i * 128 + t;
@@ -215,75 +234,95 @@ __global__ void __launch_bounds__(128) aux_attn_decode_kernel(float *out, uint8_
             *(uint4 *)(tiles + (ATT_CHUNK + (piece >> 4)) * ATT_ROW + (piece & 15) * 16) = vreg[i];
         }
         __syncthreads();
-        // scores: two threads per position, 64 dims each
-        const int p1 = t >> 1, half = t & 1;
-        float s[G];
+        const uint32_t tiles_s = (uint32_t)__cvta_generic_to_shared(tiles);
+        const int p0 = warp * 16;                               // the warp's positions p0 .. p0 + 15 of the chunk
+        // S[h][pos]: two n-tiles of 8 positions; lane (g, tq) ends up with S[g][p0 + 8 nt + 2 tq, + 1]
+        float sacc[2][4];
 #pragma unroll
-        for (int h = 0; h < G; ++h) s[h] = 0.f;
+        for (int nt = 0; nt < 2; ++nt) {
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-            float f[8];
-            aux_bf16x8(*(const uint4 *)(tiles + p1 * ATT_ROW + (half * 8 + c) * 16), f);
+            for (int e = 0; e < 4; ++e) sacc[nt][e] = 0.f;
 #pragma unroll
-            for (int h = 0; h < G; ++h)
-#pragma unroll
-                for (int e = 0; e < 8; ++e) s[h] = fmaf(f[e], qs[h][(half * 8 + c) * 8 + e], s[h]);
-        }
-#pragma unroll
-        for (int h = 0; h < G; ++h) {
-            s[h] += __shfl_xor_sync(0xffffffffu, s[h], 1);
-            if (p1 >= cnt) s[h] = -INFINITY;
-            float m = s[h];
-            for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-            if ((t & 31) == 0) mred[t >> 5][h] = m;
-        }
-        __syncthreads();
-#pragma unroll
-        for (int h = 0; h < G; ++h) {
-            const float M = fmaxf(fmaxf(mred[0][h], mred[1][h]), fmaxf(mred[2][h], mred[3][h]));
-            float p = (p1 < cnt && half == 0) ? __expf(s[h] - M) : 0.f;
-            if (half == 0) sc[h][p1] = p;
-            for (int o = 16; o; o >>= 1) p += __shfl_xor_sync(0xffffffffu, p, o);
-            if ((t & 31) == 0) lred[t >> 5][h] = p;
-        }
-        __syncthreads();
-        if (t < G) {
-            my[t] = fmaxf(fmaxf(mred[0][t], mred[1][t]), fmaxf(mred[2][t], mred[3][t]));
-            my[G + t] = lred[0][t] + lred[1][t] + lred[2][t] + lred[3][t];
-        }
-        // weighted V: 16 threads per row (8 dims each), 8 position groups
-        const int dg = t & 15, pg = t >> 4;
-        float acc[G][8];
-#pragma unroll
-        for (int h = 0; h < G; ++h)
-#pragma unroll
-            for (int e = 0; e < 8; ++e) acc[h][e] = 0.f;
-#pragma unroll
-        for (int i = 0; i < ATT_CHUNK / 8; ++i) {
-            const int p = pg + 8 * i;                            // rows past cnt hold zeros and weight 0
-            float f[8];
-            aux_bf16x8(*(const uint4 *)(tiles + (ATT_CHUNK + p) * ATT_ROW + dg * 16), f);
-#pragma unroll
-            for (int h = 0; h < G; ++h) {
-                const float w = sc[h][p];
-#pragma unroll
-                for (int e = 0; e < 8; ++e) acc[h][e] = fmaf(w, f[e], acc[h][e]);
+            for (int kp = 0; kp < 4; ++kp) {                    // two k-steps (32 dims) per ldmatrix.x4
+                // matrices: K[p0 + 8 nt + 0..7][dims 32 kp + 0..7 | 8..15 | 16..23 | 24..31]
+                const uint32_t addr = tiles_s + (p0 + 8 * nt + (lane & 7)) * ATT_ROW + (32 * kp + 8 * (lane >> 3)) * 2;
+                uint32_t b0, b1, b2, b3;
+                asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3) : "r"(addr));
+                aux_mma_bf16(sacc[nt], qa[2 * kp][0], 0u, qa[2 * kp][1], 0u, b0, b1);
+                aux_mma_bf16(sacc[nt], qa[2 * kp + 1][0], 0u, qa[2 * kp + 1][1], 0u, b2, b3);
             }
         }
-        __syncthreads();                                        // tiles consumed: reuse them
-        float(*red)[G][ATT_D] = (float(*)[G][ATT_D])tiles;
+        float sv[4];                                            // this lane's four scores of head g
 #pragma unroll
-        for (int h = 0; h < G; ++h)
+        for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-            for (int e = 0; e < 8; ++e) red[pg][h][dg * 8 + e] = acc[h][e];
+            for (int e = 0; e < 2; ++e) {
+                const int pos = p0 + 8 * nt + 2 * tq + e;
+                sv[2 * nt + e] = pos < cnt ? sacc[nt][e] * 0.08838834764831845f : -INFINITY;
+            }
+        {
+            float m = fmaxf(fmaxf(sv[0], sv[1]), fmaxf(sv[2], sv[3]));
+            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+            m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+            if (tq == 0 && g < G) mred[warp][g] = m;
+        }
+        __syncthreads();
+        const int gh = g < G ? g : 0;
+        const float M = fmaxf(fmaxf(mred[0][gh], mred[1][gh]), fmaxf(mred[2][gh], mred[3][gh]));
+        float pv[4], l = 0.f;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            pv[e] = (g < G && sv[e] > -INFINITY) ? __expf(sv[e] - M) : 0.f;
+            l += pv[e];
+        }
+        l += __shfl_xor_sync(0xffffffffu, l, 1);
+        l += __shfl_xor_sync(0xffffffffu, l, 2);
+        if (tq == 0 && g < G) lred[warp][g] = l;
+        // A fragments of the weights: positions p0 + 2 tq, + 1 (a0) and p0 + 8 + 2 tq, + 1 (a2), as value + remainder
+        uint32_t ph[2], pl[2];
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+            const __nv_bfloat162 hi = __floats2bfloat162_rn(pv[2 * nt], pv[2 * nt + 1]);
+            const float2 hf = __bfloat1622float2(hi);
+            const __nv_bfloat162 lo = __floats2bfloat162_rn(pv[2 * nt] - hf.x, pv[2 * nt + 1] - hf.y);
+            ph[nt] = *reinterpret_cast<const uint32_t *>(&hi);
+            pl[nt] = *reinterpret_cast<const uint32_t *>(&lo);
+        }
+        // O[h][dim] += P[h][pos] V[pos][dim]: sixteen n-tiles of 8 dims, two per ldmatrix.x4.trans
+        float oacc[16][4];
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) oacc[j][e] = 0.f;
+#pragma unroll
+        for (int jp = 0; jp < 8; ++jp) {
+            // matrices: V[p0 + 0..7][dims 16 jp + 0..7], V[p0 + 8..15][same], V[p0 + 0..7][dims 16 jp + 8..15], V[p0 + 8..15][same]
+            const int mi = lane >> 3;
+            const uint32_t addr = tiles_s + (ATT_CHUNK + p0 + 8 * (mi & 1) + (lane & 7)) * ATT_ROW + (16 * jp + 8 * (mi >> 1)) * 2;
+            uint32_t b0, b1, b2, b3;
+            asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3) : "r"(addr));
+            aux_mma_bf16(oacc[2 * jp], ph[0], 0u, ph[1], 0u, b0, b1);
+            aux_mma_bf16(oacc[2 * jp], pl[0], 0u, pl[1], 0u, b0, b1);
+            aux_mma_bf16(oacc[2 * jp + 1], ph[0], 0u, ph[1], 0u, b2, b3);
+            aux_mma_bf16(oacc[2 * jp + 1], pl[0], 0u, pl[1], 0u, b2, b3);
+        }
+        __syncthreads();                                        // tiles consumed (and lred complete): reuse them
+        if (t < G) {
+            my[t] = fmaxf(fmaxf(mred[0][t], mred[1][t]), fmaxf(mred[2][t], mred[3][t]));
+            my[G + t] = (lred[0][t] + lred[1][t]) + (lred[2][t] + lred[3][t]);
+        }
+        float(*red)[G][ATT_D] = (float(*)[G][ATT_D])tiles;      // red[warp][head][dim]
+        if (g < G) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+                *reinterpret_cast<float2 *>(&red[warp][g][8 * j + 2 * tq]) = make_float2(oacc[j][0], oacc[j][1]);
+        }
         __syncthreads();
 #pragma unroll
-        for (int h = 0; h < G; ++h) {
-            float o = 0.f;
-#pragma unroll
-            for (int g8 = 0; g8 < 8; ++g8) o += red[g8][h][t];
-            my[HDR + h * ATT_D + t] = o;
-        }
+        for (int h = 0; h < G; ++h)
+            my[HDR + h * ATT_D + t] = (red[0][h][t] + red[1][h][t]) + (red[2][h][t] + red[3][h][t]);
     } else if (t < G) {
         my[t] = -INFINITY;
         my[G + t] = 0.f;
