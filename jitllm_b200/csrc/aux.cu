@@ -178,8 +178,11 @@ __device__ __forceinline__ void aux_mma_bf16(float (&d)[4], uint32_t a0, uint32_
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+#ifndef ATT_MIN_CTAS
+#define ATT_MIN_CTAS 5          // 96 registers: five CTAs per SM (shared memory would allow six, but at 80 registers the kernel spills)
+#endif
 template <int G>
-__global__ void __launch_bounds__(128) aux_attn_decode_kernel(float *out, uint8_t *operand, const __nv_bfloat16 *q,
+__global__ void __launch_bounds__(128, ATT_MIN_CTAS) aux_attn_decode_kernel(float *out, uint8_t *operand, const __nv_bfloat16 *q,
                                                               const __nv_bfloat16 *k_cache, const __nv_bfloat16 *v_cache,
                                                               const long long *pos_dev, float *part, unsigned *tickets, int hkv,
                                                               int max_len, int nsplit) {
