@@ -112,6 +112,12 @@ __device__ __forceinline__ void tc5_epilogue(const tc5_params &p, int u, uint32_
 // ~2 us to arrive from L2, a weight stage is produced locally.
 // WT selects the weight format the dequant warps read: 0 = Q4_K (raw super-blocks), 1 = Q8_0 (resident
 // code plane in 64-element span order + f16 scale plane). Everything else is shared.
+#ifdef TC5_EXP_TRACE        // timing experiment: global-timer stamps of every CTA at seven points of its life
+__device__ unsigned long long tc5_trace[160][8];
+#define TC5_TR(i) do { tc5_trace[blockIdx.x][i] = jl_gtime_ns(); } while (0)
+#else
+#define TC5_TR(i) do { } while (0)
+#endif
 template <int WT, int NT, int SA, int SB>
 __global__ void __launch_bounds__(TC5_GEMM_THREADS, 1)
 gemm_q4k_tc5_kernel(const __grid_constant__ CUtensorMap xmap, const tc5_params p) {
@@ -136,6 +142,7 @@ gemm_q4k_tc5_kernel(const __grid_constant__ CUtensorMap xmap, const tc5_params p
     const int nsbu = sb1 - sb0, rot = (rt * 5 + tt * 3) % nsbu;                                     \
     (void)tt; (void)rt; (void)rot
 
+    if (tid == 0) TC5_TR(0);
     if (tid == 0) {
         for (int s = 0; s < SA; s++) {
             mbar_init(smem_u32(a_full + s), TC5_DQ_THREADS / 32);   // one arrival per dequant warp
@@ -158,6 +165,7 @@ gemm_q4k_tc5_kernel(const __grid_constant__ CUtensorMap xmap, const tc5_params p
     __syncthreads();
     tc5_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    if (tid == 0) TC5_TR(1);
 
     // The activation rows and their scales come from the kernel in front (act_to_f16_kernel): only
     // the roles that read them wait for it; the weights are converted meanwhile.
@@ -214,6 +222,7 @@ gemm_q4k_tc5_kernel(const __grid_constant__ CUtensorMap xmap, const tc5_params p
                     ok = __all_sync(0xffffffffu, tc5_wait(bars_u + 8 * (2 * SA + s), ph, abort_flag));
                 if (!ok) break;
                 tc5_fence_after();
+                if (kb_it == 0 && wu == 5 && leader) TC5_TR(2);
                 ready_a = mbar_test_wait(bars_u + 8 * ((kb_it + 1) % SA), ((kb_it + 1) / SA) & 1);
                 ready_b = mbar_test_wait(bars_u + 8 * (2 * SA + (kb_it + 1) % SB), ((kb_it + 1) / SB) & 1);
                 if (leader) {
@@ -230,6 +239,7 @@ gemm_q4k_tc5_kernel(const __grid_constant__ CUtensorMap xmap, const tc5_params p
             }
             if (!ok) break;
             if (leader) tc5_commit(bars_u + 8 * (2 * SA + 2 * SB + ab));      // accumulators complete
+            if (wu == 5 && leader) TC5_TR(3);
         }
     } else if (warp >= 6) {
         // ------------------------------------------------ dequant: thread r owns tile row r
@@ -385,6 +395,7 @@ gemm_q4k_tc5_kernel(const __grid_constant__ CUtensorMap xmap, const tc5_params p
             const uint32_t ab = unit_it % L::ACC_BUFS, aph = (unit_it / L::ACC_BUFS) & 1;
             if (!tc5_wait_relaxed(smem_u32(acc_full + ab), aph, abort_flag)) break;
             tc5_fence_after();
+            if (tid == 0) TC5_TR(4);
             // the CTA's last unit is shared with the dequant warps, which have nothing left to do
             const bool last = u + (int)gridDim.x >= nunits;
             tc5_epilogue<NT>(p, u, tmem_base + ab * L::ACC_COLS, warp, lane, last ? 0 : -1);
@@ -409,8 +420,10 @@ gemm_q4k_tc5_kernel(const __grid_constant__ CUtensorMap xmap, const tc5_params p
 #undef TC5_DEP_WAIT
 
     // teardown: everyone meets, the allocating warp frees TMEM
+    if (tid == 0) TC5_TR(5);
     tc5_fence_before();
     __syncthreads();
+    if (tid == 0) TC5_TR(6);
     if (tid == 0 && *abort_flag) atomicExch(p.status, 2);
     if (warp == 5) {
         tc5_fence_after();
@@ -566,3 +579,7 @@ int jl_launch_gemm_tc5(jl_ctx *ctx, void *out_dev, int out_dtype, const jl_weigh
     JL_CUDA(ctx, cudaGetLastError());
     return JL_OK;
 }
+
+#ifdef TC5_EXP_TRACE
+JL_EXPORT int jl_exp_tc5_trace(unsigned long long *host) { return (int)cudaMemcpyFromSymbol(host, tc5_trace, sizeof(tc5_trace)); }
+#endif
