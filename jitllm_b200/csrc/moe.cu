@@ -245,9 +245,12 @@ __device__ __forceinline__ uint32_t e8m0_to_h2(uint32_t e) {
 __device__ __forceinline__ float moe_act(int kind, float g, float u) {
     if (kind == JL_ACT_SWIGLU_OAI) {   // jit/gpu/kernels/actkind.go:13-39
         const float x = fminf(g, 7.f), y = fmaxf(fminf(u, 7.f), -7.f);
-        return x / (1.f + expf(-1.702f * x)) * (y + 1.f);
+        return __fdividef(x, 1.f + __expf(-1.702f * x)) * (y + 1.f);
     }
-    return g / (1.f + expf(-g)) * u;   // SiLU gate
+    // SiLU gate. The fast exponential and division (a few ulp) on purpose: the four epilogue warps share their
+    // schedulers with the MMA issuers, and with expf and an IEEE division the drain of a unit cost ~35 instructions
+    // per element (37 us of a 172 us layer, measured by leaving the drain out).
+    return __fdividef(g, 1.f + __expf(-g)) * u;
 }
 
 #include "moe_bs.cuh"

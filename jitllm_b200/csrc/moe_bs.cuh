@@ -512,8 +512,14 @@ moe_gemm_bs_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
             const int pos_end = s_off[e] + (s_off[e + 1] - s_off[e]);
             if constexpr (DIG > 1) {
                 // a token's DIG digit columns (d T + t) are added, most significant first, eight tokens at a time
+                const int row0 = rt * TC5_M + warp * 32 + lane;                       // mode 0: the gate / up row of this lane
+                const float bg = (p.mode == 0 && p.b0 && row0 < p.rows) ? p.b0[(size_t)e * p.rows + row0] : 0.f;
+                const float bu = (p.mode == 0 && p.b1 && row0 < p.rows) ? p.b1[(size_t)e * p.rows + row0] : 0.f;
 #pragma unroll 1
                 for (int c0 = 0; c0 < T; c0 += 8) {
+#ifdef BS_EXP_NOEPI
+                    break;
+#endif
                     const int pos0 = col0 + c0;
                     if (pos0 >= pos_end) break;                          // warp-uniform: the rest of the tile is past the list
                     if (p.mode == 0) {
@@ -532,9 +538,7 @@ moe_gemm_bs_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
                                 g[j] = dg ? g[j] + __uint_as_float(vg[dg][j]) : __uint_as_float(vg[dg][j]);
                                 uu[j] = dg ? uu[j] + __uint_as_float(vu[dg][j]) : __uint_as_float(vu[dg][j]);
                             }
-                        const int row = rt * TC5_M + warp * 32 + lane;
-                        const float bg = (p.b0 && row < p.rows) ? p.b0[(size_t)e * p.rows + row] : 0.f;
-                        const float bu = (p.b1 && row < p.rows) ? p.b1[(size_t)e * p.rows + row] : 0.f;
+                        const int row = row0;
 #pragma unroll
                         for (int j = 0; j < 8; j++) {
                             const int pos = pos0 + j;
@@ -570,6 +574,7 @@ moe_gemm_bs_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_consta
                 break;
 #endif
                 const int pos0 = col0 + c0;
+                if (pos0 >= pos_end) break;                              // warp-uniform: the rest of the tile is past the list
                 if (p.mode == 0) {
                     uint32_t vg[32], vu[32];
                     tc5_ld32(tacc + c0, vg);
