@@ -68,42 +68,60 @@ struct tc5_smem {
 // Drains one finished tile from TMEM: lane quarter `q` (TMEM lanes 32q..32q+31 = tile rows), 32
 // columns (tokens) at a time; undoes the per-token scale, converts, stores out[tok][row].
 // part < 0: every 32-column job; part = 0,1,2: every third job (three warps share a quarter).
+// One job of the drain: 32 accumulator columns of this lane's row, scaled per token and stored. KIND: 0 f32 (also the
+// K-split partial planes), 1 bf16, 2 f16 -- decided once per call, not per element.
+template <int KIND>
+__device__ __forceinline__ void tc5_store32(const tc5_params &p, const uint32_t (&v)[32], void *base, int row, int col0, float myscale,
+                                            int lane) {
+    const int nj = p.split ? 16 : 32, tok0 = p.split ? col0 >> 1 : col0;
+    const bool row_ok = row < p.nrows;
+    size_t o = (size_t)tok0 * p.nrows + row;
+#pragma unroll
+    for (int j = 0; j < 32; j++) {
+        if (j >= nj) break;
+        const float sc = __shfl_sync(0xffffffffu, myscale, j);
+        const float raw = p.split ? __uint_as_float(v[(2 * j) & 31]) + __uint_as_float(v[(2 * j + 1) & 31]) : __uint_as_float(v[j]);
+        if (row_ok && tok0 + j < p.ntok) {
+            const float acc = raw * sc;
+            if (KIND == 0) static_cast<float *>(base)[o] = acc;
+            else if (KIND == 1) static_cast<__nv_bfloat16 *>(base)[o] = __float2bfloat16_rn(acc);
+            else static_cast<__half *>(base)[o] = __float2half_rn(acc);
+        }
+        o += p.nrows;
+    }
+}
+
 template <int NT>
 __device__ __forceinline__ void tc5_epilogue(const tc5_params &p, int u, uint32_t tmem_acc, int q, int lane, int part) {
     const int ks = u % p.ksplit, tt = (u / p.ksplit) % p.tok_tiles, rt = u / (p.ksplit * p.tok_tiles);
     float *partial = p.ksplit > 1 ? p.partial + (size_t)ks * p.ntok * p.nrows : nullptr;
-    int job = 0;
+    void *base = partial ? (void *)partial : p.out;
+    const int kind = partial || p.out_dtype == JL_DT_F32 ? 0 : (p.out_dtype == JL_DT_BF16 ? 1 : 2);
+    constexpr int NJ = TC5_MS * (NT / 32);                      // jobs of the tile: (128-row operand, 32 columns)
+    // this warp's jobs: every job (part < 0) or every third one; the NEXT job's accumulators are asked for before
+    // the current job is converted and stored, so the TMEM read's latency passes under the stores
+    const int first = part < 0 ? 0 : part, step = part < 0 ? 1 : 3;
+    auto taddr_of = [&](int job) { return tmem_acc + (job / (NT / 32)) * NT + ((uint32_t)(q * 32) << 16) + (job % (NT / 32)) * 32; };
+    uint32_t va[32], vb[32];
+    if (first < NJ) tc5_ld32(taddr_of(first), va);
 #pragma unroll 1
-    for (int ms = 0; ms < TC5_MS; ms++) {
-        const int row = rt * TC5_ROWS + ms * TC5_M + q * 32 + lane;
-        const uint32_t taddr = tmem_acc + ms * NT + ((uint32_t)(q * 32) << 16);
-#pragma unroll 1
-        for (int c0 = 0; c0 < NT; c0 += 32, job++) {
-            if (part >= 0 && job % 3 != part) continue;
-            uint32_t v[32];
-            tc5_ld32(taddr + c0, v);
-            tc5_wait_ld();
-            const int col0 = tt * NT + c0;
+    for (int job = first; job < NJ; job += 2 * step) {
+#pragma unroll
+        for (int half = 0; half < 2; half++) {
+            const int jb = job + half * step;
+            if (jb >= NJ) break;
+            uint32_t (&cur)[32] = half ? vb : va;
+            uint32_t (&nxt)[32] = half ? va : vb;
+            const int ms = jb / (NT / 32), c0 = (jb % (NT / 32)) * 32;
+            const int row = rt * TC5_ROWS + ms * TC5_M + q * 32 + lane, col0 = tt * NT + c0;
             // the per-token scales of these 32 columns: one load per lane, broadcast by shuffle
             const int mytok = p.split ? (col0 >> 1) + (lane & 15) : col0 + lane;
             const float myscale = mytok < p.ntok ? __ldg(p.inv_scale + mytok) : 0.f;
-            const int nj = p.split ? 16 : 32;
-#pragma unroll
-            for (int j = 0; j < 32; j++) {
-                if (j >= nj) break;
-                const int tok = p.split ? (col0 >> 1) + j : col0 + j;
-                const float sc = __shfl_sync(0xffffffffu, myscale, j);
-                const float raw = p.split ? __uint_as_float(v[(2 * j) & 31]) + __uint_as_float(v[(2 * j + 1) & 31])
-                                          : __uint_as_float(v[j]);
-                if (row < p.nrows && tok < p.ntok) {
-                    const float acc = raw * sc;
-                    const size_t o = (size_t)tok * p.nrows + row;
-                    if (partial) partial[o] = acc;
-                    else if (p.out_dtype == JL_DT_F32) static_cast<float *>(p.out)[o] = acc;
-                    else if (p.out_dtype == JL_DT_BF16) static_cast<__nv_bfloat16 *>(p.out)[o] = __float2bfloat16_rn(acc);
-                    else static_cast<__half *>(p.out)[o] = __float2half_rn(acc);
-                }
-            }
+            tc5_wait_ld();
+            if (jb + step < NJ) tc5_ld32(taddr_of(jb + step), nxt);
+            if (kind == 0) tc5_store32<0>(p, cur, base, row, col0, myscale, lane);
+            else if (kind == 1) tc5_store32<1>(p, cur, base, row, col0, myscale, lane);
+            else tc5_store32<2>(p, cur, base, row, col0, myscale, lane);
         }
     }
 }
