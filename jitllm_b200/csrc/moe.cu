@@ -110,14 +110,20 @@ moe_route_kernel(const float *__restrict__ logits, const float *__restrict__ rou
 //   pos_of[tok * k + slot] = sorted position of that pair (or -1 for an unfilled slot)
 // Counts by shared-memory atomics; placement by ONE warp walking the pairs 32 at a time in
 // order, ranking equal ids inside a chunk with __match_any_sync, so positions keep token order.
+#define MOE_SORT_STAGE 4096
 __device__ __forceinline__ void moe_sort_cta(const int32_t *sel, int npairs, int top_k, int n_expert, int *__restrict__ cnt,
                                              int *__restrict__ off, int *__restrict__ perm_tok, int *__restrict__ pos_of) {
     __shared__ int s_cnt[256], s_base[257];
+    // the ids of a batch of up to MOE_SORT_STAGE pairs stay in shared memory for the placement walk below: read from
+    // global memory there, each of its 32-pair steps waited for its own L2 round trip (10 of the kernel's 12 us)
+    __shared__ int s_sel[MOE_SORT_STAGE];
+    const bool staged = npairs <= MOE_SORT_STAGE;
     const int tid = threadIdx.x;
     for (int i = tid; i < 256; i += blockDim.x) s_cnt[i] = 0;
     __syncthreads();
     for (int i = tid; i < npairs; i += blockDim.x) {
         const int id = __ldcg(sel + i);
+        if (staged) s_sel[i] = id;
         if (id >= 0 && id < n_expert) atomicAdd(&s_cnt[id], 1);
         else pos_of[i] = -1;
     }
@@ -134,7 +140,7 @@ __device__ __forceinline__ void moe_sort_cta(const int32_t *sel, int npairs, int
     if (tid < 32) {
         for (int c = 0; c < npairs; c += 32) {
             const int i = c + tid;
-            const int id = i < npairs ? __ldcg(sel + i) : -1;
+            const int id = i < npairs ? (staged ? s_sel[i] : __ldcg(sel + i)) : -1;
             const bool ok = id >= 0 && id < n_expert;
             const unsigned same = __match_any_sync(0xffffffffu, ok ? id : -1 - tid);   // invalid ids match nobody
             if (ok) {
@@ -173,15 +179,23 @@ moe_combine_kernel(float *__restrict__ out, const float *__restrict__ y, const i
     const int tok = blockIdx.x;
     __shared__ int s_pos[32];
     __shared__ float s_w[32];
+    __shared__ int s_id0[32], s_pos0[32];
+    __shared__ float s_w0[32];
+    if (threadIdx.x < top_k) {          // the token's slots, all loads in flight at once
+        s_id0[threadIdx.x] = sel[(size_t)tok * top_k + threadIdx.x];
+        s_pos0[threadIdx.x] = pos_of[(size_t)tok * top_k + threadIdx.x];
+        s_w0[threadIdx.x] = wt[(size_t)tok * top_k + threadIdx.x];
+    }
+    __syncthreads();
     if (threadIdx.x == 0) {
         // insertion sort of the slots by expert id (top_k <= 32)
         int ids[32], n = 0;
         for (int j = 0; j < top_k; j++) {
-            const int id = sel[(size_t)tok * top_k + j];
+            const int id = s_id0[j];
             if (id < 0) continue;
             int q = n++;
             while (q > 0 && ids[q - 1] > id) { ids[q] = ids[q - 1]; s_pos[q] = s_pos[q - 1]; s_w[q] = s_w[q - 1]; q--; }
-            ids[q] = id; s_pos[q] = pos_of[(size_t)tok * top_k + j]; s_w[q] = wt[(size_t)tok * top_k + j];
+            ids[q] = id; s_pos[q] = s_pos0[j]; s_w[q] = s_w0[j];
         }
         for (int j = n; j < 32; j++) s_pos[j] = -1;
     }
