@@ -741,16 +741,23 @@ static int moe_dev_locked(jl_ctx *ctx, float *out_dev, const void *h_dev, int h_
         // The block-scaled arms: activations to e4m3 + ue8m0 per 32 (twice: the routed rows, then the gated
         // intermediates), one digit or three, weights and their scales as they are. The e4m3 planes and scale rows
         // live where the exact arm keeps its f16 rows (4 bytes per element there: room for three planes and the scales).
-        const int ndig = d->arm == JL_MOE_ARM_BLOCK_SCALED_X3 ? 3 : 1;
+        // Digits: one for the one-digit arm. The parity arm takes three (12 significant bits), except for bf16 input rows,
+        // whose 8 significant bits two digits hold exactly (the second digit is an integer of at most 8 units of the
+        // first one's last place): 64 tokens per tile instead of 40, so that no expert of the 256-token batch needs a
+        // second pass over its weights. The gated intermediates are f32: three.
+        const int ndig2 = d->arm == JL_MOE_ARM_BLOCK_SCALED_X3 ? 3 : 1;
+        const int ndig1 = ndig2 == 3 && h_dtype == JL_DT_BF16 ? 2 : ndig2;
         const int sfs1 = (H + BS_KB - 1) / BS_KB * 4, sfs2 = (F + BS_KB - 1) / BS_KB * 4;
-        uint8_t *q1 = (uint8_t *)xs, *sf1 = q1 + (size_t)ndig * np * H;
-        uint8_t *q2 = (uint8_t *)as, *sf2 = q2 + (size_t)ndig * np * F;
+        uint8_t *q1 = (uint8_t *)xs, *sf1 = q1 + (size_t)ndig1 * np * H;
+        uint8_t *q2 = (uint8_t *)as, *sf2 = q2 + (size_t)ndig2 * np * F;
         const int src_rows = given_ids ? ntok : ntok;
-        auto grouped = [&](const moe_gemm_params &pp, const uint8_t *xq) {
-            return ndig == 3 ? moe_grouped_bs<128, 40, 3>(ctx, pp, xq, ntok, s, nattr, at) : moe_grouped_bs<64, 64, 1>(ctx, pp, xq, ntok, s, nattr, at);
+        auto grouped = [&](const moe_gemm_params &pp, const uint8_t *xq, int ndig) {
+            return ndig == 3   ? moe_grouped_bs<128, 40, 3>(ctx, pp, xq, ntok, s, nattr, at)
+                   : ndig == 2 ? moe_grouped_bs<128, 64, 2>(ctx, pp, xq, ntok, s, nattr, at)
+                               : moe_grouped_bs<64, 64, 1>(ctx, pp, xq, ntok, s, nattr, at);
         };
         cudaLaunchConfig_t c = cfg_of(dim3(np), dim3(256));
-        JL_CUDA(ctx, cudaLaunchKernelEx(&c, act_to_mx8_kernel, h_dev, h_dtype, q1, sf1, H, sfs1, (const int *)perm, src_rows, ndig,
+        JL_CUDA(ctx, cudaLaunchKernelEx(&c, act_to_mx8_kernel, h_dev, h_dtype, q1, sf1, H, sfs1, (const int *)perm, src_rows, ndig1,
                                         (size_t)np * H));
         ctx->st.launches++;
         moe_gemm_params p = {};
@@ -758,17 +765,17 @@ static int moe_dev_locked(jl_ctx *ctx, float *out_dev, const void *h_dev, int h_
         p.mode = 0; p.rows = F; p.k = H; p.row_tiles = (F + TC5_M - 1) / TC5_M;
         p.c0 = wg->data; p.c1 = wu->data; p.e0 = wg->scales; p.e1 = wu->scales; p.e_stride = wg->scale_stride;
         p.b0 = d->gate_bias; p.b1 = d->up_bias; p.outp = act; p.sfb = sf1; p.sfb_stride = sfs1;
-        int rc = MOE_EXP_GEMM(grouped(p, q1));
+        int rc = MOE_EXP_GEMM(grouped(p, q1, ndig1));
         if (rc) return rc;
         c = cfg_of(dim3(np), dim3(256));
         JL_CUDA(ctx, cudaLaunchKernelEx(&c, act_to_mx8_kernel, (const void *)act, (int)JL_DT_F32, q2, sf2, F, sfs2, (const int *)nullptr, 0,
-                                        ndig, (size_t)np * F));
+                                        ndig2, (size_t)np * F));
         ctx->st.launches++;
         p.mode = 1; p.rows = H; p.k = F; p.row_tiles = (H + TC5_ROWS - 1) / TC5_ROWS;
         p.c0 = wd->data; p.c1 = nullptr; p.e0 = wd->scales; p.e1 = nullptr; p.e_stride = wd->scale_stride;
         p.b0 = d->down_bias; p.b1 = nullptr; p.outp = y; p.sfb = sf2; p.sfb_stride = sfs2;
         if (given_ids) { p.outp = out_dev; p.out_rowmap = perm; }
-        if ((rc = MOE_EXP_GEMM(grouped(p, q2)))) return rc;
+        if ((rc = MOE_EXP_GEMM(grouped(p, q2, ndig2)))) return rc;
         if (!given_ids) {
             c = cfg_of(dim3(ntok), dim3(256));
             JL_CUDA(ctx, cudaLaunchKernelEx(&c, moe_combine_kernel, out_dev, (const float *)y, (const int32_t *)sel, (const float *)wt,
