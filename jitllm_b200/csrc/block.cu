@@ -717,8 +717,13 @@ __device__ bool bk_attention(const bk_params &P, const bk_phase &ph, uint8_t *wo
             // flight at once, and merges from there. Dependent loads in a loop would cost a trip each.
             float *rs = reinterpret_cast<float *>(work);
             const int nrec = min(nblk, (int)(4 * BK_ATT_SUB_BYTES / 4) / STRIDE);
+            static_assert(STRIDE % 4 == 0, "records are copied 16 bytes at a time");
+            {   // 16-byte loads: at 2048 positions the 16 records are 2096 of them, about four per thread, one batch
+                const float4 *b4 = reinterpret_cast<const float4 *>(base);
+                float4 *r4 = reinterpret_cast<float4 *>(rs);
 #pragma unroll 8
-            for (int i = tid; i < nrec * STRIDE; i += BK_THREADS) rs[i] = __ldcg(base + i);
+                for (int i = tid; i < nrec * (STRIDE / 4); i += BK_THREADS) r4[i] = __ldcg(b4 + i);
+            }
             __syncthreads();
             if (h < G) {
                 float M = -INFINITY;
