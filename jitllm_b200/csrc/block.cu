@@ -557,6 +557,9 @@ __device__ bool bk_attention(const bk_params &P, const bk_phase &ph, uint8_t *wo
             }
         }
         const bool fresh = (int)pos >= s0 && (int)pos < s0 + BK_ATT_CHUNK;
+        // this thread's rotation pair (the same for the new key and for both of its q pairs: 128 = 2 x 64), asked for
+        // before the polls below: after them it would be one more round trip between "q has arrived" and the scores
+        const float rot_c = cs[t & 63], rot_s = sn[t & 63];
         if (fresh) {
             // the new position's key (rotated) and value: one pair per thread, rounded to bf16, appended to the cache and
             // handed through shared memory to the threads that own that row's pieces
@@ -566,7 +569,7 @@ __device__ bool bk_attention(const bk_params &P, const bk_phase &ph, uint8_t *wo
             ok = bk_ll_read2_n<1>(src, seq_r, ab, P, limit_ns, BK_CODE(4, 2)) && ok;
             __nv_bfloat162 o;
             if (t < 64) {
-                const float cc = cs[jp], ss = sn[jp];
+                const float cc = rot_c, ss = rot_s;
                 o = __floats2bfloat162_rn(ab[0].x * cc - ab[0].y * ss, ab[0].x * ss + ab[0].y * cc);
                 S->kf[jp] = *reinterpret_cast<const uint32_t *>(&o);
                 reinterpret_cast<__nv_bfloat162 *>(kc + ((size_t)kv * P.max_len + pos) * BK_ATT_D)[jp] = o;
@@ -591,7 +594,7 @@ __device__ bool bk_attention(const bk_params &P, const bk_phase &ph, uint8_t *wo
                 const int pi = t + 128 * u;
                 if (pi < nq) {
                     const int h = pi >> 6, jp = pi & 63;
-                    const float c = cs[jp], s_ = sn[jp];
+                    const float c = rot_c, s_ = rot_s;
                     const __nv_bfloat162 o = __floats2bfloat162_rn(ab[u].x * c - ab[u].y * s_, ab[u].x * s_ + ab[u].y * c);
                     const float2 f = __bfloat1622float2(o);
                     const int d0 = 2 * jp;                                // dims d0, d0 + 1: quarter d0 / 32
