@@ -728,19 +728,32 @@ __device__ bool bk_attention(const bk_params &P, const bk_phase &ph, uint8_t *wo
                 for (int i = tid; i < nrec * (STRIDE / 4); i += BK_THREADS) r4[i] = __ldcg(b4 + i);
             }
             __syncthreads();
+            BK_AT(6);
             if (h < G) {
+                // Two loops each, one over the records in shared memory and one over the rest in global memory. As ONE
+                // loop choosing per record, every step also issued the global-memory side's loads and waited for them
+                // (3.5 us for 16 records, all of them in shared memory).
                 float M = -INFINITY;
-                for (int b2 = 0; b2 < nblk; ++b2) M = fmaxf(M, b2 < nrec ? rs[b2 * STRIDE + h] : __ldcg(base + (size_t)b2 * STRIDE + h));
+                for (int b2 = 0; b2 < nrec; ++b2) M = fmaxf(M, rs[b2 * STRIDE + h]);
+                for (int b2 = nrec; b2 < nblk; ++b2) M = fmaxf(M, __ldcg(base + (size_t)b2 * STRIDE + h));
                 float o = 0.f, l = 0.f;
-                for (int b2 = 0; b2 < nblk; ++b2) {                       // ascending block order: bit-stable
-                    const float *rec = b2 < nrec ? rs + b2 * STRIDE : base + (size_t)b2 * STRIDE;
-                    const float mb = b2 < nrec ? rec[h] : __ldcg(rec + h);
+                for (int b2 = 0; b2 < nrec; ++b2) {                       // ascending block order: bit-stable
+                    const float *rec = rs + b2 * STRIDE;
+                    const float mb = rec[h];
                     const float w = mb == -INFINITY ? 0.f : __expf(mb - M);
-                    o = fmaf(w, b2 < nrec ? rec[HDR + h * BK_ATT_D + d] : __ldcg(rec + HDR + h * BK_ATT_D + d), o);
-                    l = fmaf(w, b2 < nrec ? rec[G + h] : __ldcg(rec + G + h), l);
+                    o = fmaf(w, rec[HDR + h * BK_ATT_D + d], o);
+                    l = fmaf(w, rec[G + h], l);
+                }
+                for (int b2 = nrec; b2 < nblk; ++b2) {
+                    const float *rec = base + (size_t)b2 * STRIDE;
+                    const float mb = __ldcg(rec + h);
+                    const float w = mb == -INFINITY ? 0.f : __expf(mb - M);
+                    o = fmaf(w, __ldcg(rec + HDR + h * BK_ATT_D + d), o);
+                    l = fmaf(w, __ldcg(rec + G + h), l);
                 }
                 bk_ll_store(ph.att + (size_t)(kv * G + h) * BK_ATT_D + d, l > 0.f ? o / l : 0.f, seq_w);
             }
+            BK_AT(7);
         }
         __syncthreads();                                                  // the groups' shared memory is free again
         BK_AT(4);
