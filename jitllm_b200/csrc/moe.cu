@@ -138,9 +138,11 @@ __device__ __forceinline__ void moe_sort_cta(const int32_t *sel, int npairs, int
     for (int i = tid; i < n_expert; i += blockDim.x) cnt[i] = s_cnt[i];
     __syncthreads();                                   // off[] is read back below by every thread
     if (tid < 32) {
+        // one generic pointer, shared or global: a per-step choice between the two would issue the global load as well
+        const int *src = staged ? static_cast<const int *>(s_sel) : sel;
         for (int c = 0; c < npairs; c += 32) {
             const int i = c + tid;
-            const int id = i < npairs ? (staged ? s_sel[i] : __ldcg(sel + i)) : -1;
+            const int id = i < npairs ? src[i] : -1;
             const bool ok = id >= 0 && id < n_expert;
             const unsigned same = __match_any_sync(0xffffffffu, ok ? id : -1 - tid);   // invalid ids match nobody
             if (ok) {
