@@ -37,7 +37,7 @@
 #define BS_EXP_MMA 1
 #endif
 #ifndef BS_L2_AHEAD
-#define BS_L2_AHEAD 0                   // stages by which the weight tiles are asked for in L2 ahead of their copy
+#define BS_L2_AHEAD 0                   // stages by which the weight tiles are asked for in L2 ahead of their copy (off: 4 / 8 / 16 measured slower than none)
 #endif
 #define BS_ISSUERS 2                    // MMA issuer threads: warp 5 takes the tile's first 128 rows, warp 14 the second 128
 #define BS_THREADS (TC5_THREADS + 32 * (BS_ISSUERS - 1))
