@@ -359,6 +359,10 @@ int jl_matvec_q4k_noalloc(float *out_dev, const void *w_dev, const float *x_dev,
  *   jl_aux_attn_scratch_bytes() bytes that was zero-filled once. */
 int jl_aux_add_rmsnorm(float *x_io, const float *delta /* or NULL */, const float *w /* or NULL */, float eps,
                        float *out /* or NULL when operand_out is given */, void *operand_out, int n, int h, void *stream);
+/* The batched counterpart: the normalised rows go out as the tcgen05 GEMM's activation operand (where jl_gemm_operand
+ * said), and jl_matmul_dev_prepared consumes it: no conversion launch between the norm and the GEMM. h % 256 == 0. */
+int jl_aux_add_rmsnorm_gemm(float *x_io, const float *delta /* or NULL */, const float *w /* or NULL */, float eps,
+                            void *rows_f16, float *inv_scale, int n, int h, void *stream);
 int jl_aux_silu_mul(float *out /* or NULL when operand_out is given */, void *operand_out,
                     const float *gate_up /* [n][2*ffn] */, int n, int ffn, void *stream);
 int jl_aux_argmax(long long *out /* [n] */, const float *x /* [n][v] */, int n, int v, void *stream);
@@ -380,6 +384,12 @@ int jl_aux_attn_decode(float *out /* or NULL when operand_out is given */, void 
  * host-pointer call): size the context first, then ask. */
 void *jl_decode_operand(jl_ctx *ctx, const jl_weight *w, int ntok);
 int jl_matvec_dev_prepared(jl_ctx *ctx, float *out_dev, const jl_weight *w, int ntok, void *stream);
+/* The same for token counts that go to the tcgen05 GEMM: jl_gemm_operand names where a producer
+ * (jl_aux_add_rmsnorm_gemm) writes the f16 hi / lo rows ([2 tok], [2 tok + 1], w->k halves each) and the per-token
+ * 1/scale; JL_DECLINED when (w, ntok) is not served by the GEMM or the scratch is too small (jl_reserve).
+ * jl_matmul_dev_prepared then runs the GEMM on what was written there. */
+int jl_gemm_operand(jl_ctx *ctx, const jl_weight *w, int ntok, void **rows_f16, float **inv_scale);
+int jl_matmul_dev_prepared(jl_ctx *ctx, void *out_dev, int out_dtype, const jl_weight *w, int ntok, void *stream);
 
 /* ---- whole blocks in one submission: nn.LayerDevice (engine/nn/device.go:1096-1176) ------------
  * PrepLayer hands a block's weights to the device, Layers runs blocks [lo, hi) for the positions of one

@@ -145,6 +145,9 @@ SYMBOLS = {
     "jl_aux_rope_kv": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _VP]),
     "jl_aux_attn_scratch_bytes": (C.c_size_t, [_I, _I, _I, _I]),
     "jl_aux_attn_decode": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _VP]),
+    "jl_gemm_operand": (_I, [_VP, _VP, _I, C.POINTER(_VP), C.POINTER(_VP)]),
+    "jl_matmul_dev_prepared": (_I, [_VP, _VP, _I, _VP, _I, _VP]),
+    "jl_aux_add_rmsnorm_gemm": (_I, [_VP, _VP, _VP, C.c_float, _VP, _VP, _I, _I, _VP]),
     "jl_decode_operand": (_VP, [_VP, _VP, _I]),
     "jl_matvec_dev_prepared": (_I, [_VP, _VP, _VP, _I, _VP]),
 }

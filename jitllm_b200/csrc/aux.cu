@@ -95,6 +95,78 @@ __global__ void __launch_bounds__(256) aux_add_rmsnorm_sb_kernel(float *x_io, co
     }
 }
 
+// The same producer for the batched path: the normalised row goes out as the tcgen05 GEMM's activation operand (the
+// f16 hi / lo rows and the power-of-two scale act_to_f16_kernel would make of the f32 row, bit for bit), so that no
+// conversion launch sits between the norm and the GEMM. Same ownership of super-blocks by warps as above, hence the
+// same sums.
+__global__ void __launch_bounds__(256) aux_add_rmsnorm_gemm_kernel(float *x_io, const float *delta, const float *w, float eps,
+                                                                    __half *rows, float *inv_scale, int h) {
+    __shared__ float red[8];
+    AUX_PDL();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nsb = h / 256, row = blockIdx.x;
+    float4 *x4 = (float4 *)(x_io + (size_t)row * h);
+    const float4 *d4 = delta ? (const float4 *)(delta + (size_t)row * h) : nullptr;
+    float ss = 0.f;
+    for (int sb = warp; sb < nsb; sb += 8)
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+            const int i = sb * 64 + hf * 32 + lane;
+            float4 v = x4[i];
+            if (d4) {
+                const float4 d = d4[i];
+                v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+                x4[i] = v;
+            }
+            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+    const float r = rsqrtf(aux_block_sum(ss, red) / (float)h + eps);
+    auto normed = [&](int i) {
+        const float4 a = x4[i];                                  // this thread's own writes
+        const float4 g = w ? ((const float4 *)w)[i] : make_float4(1.f, 1.f, 1.f, 1.f);
+        return make_float4(a.x * r * g.x, a.y * r * g.y, a.z * r * g.z, a.w * r * g.w);
+    };
+    float amax = 0.f;
+    for (int sb = warp; sb < nsb; sb += 8)
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+            const float4 v = normed(sb * 64 + hf * 32 + lane);
+            amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+        }
+    for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    __syncthreads();                                             // red[] was read by everyone above
+    if (lane == 0) red[warp] = amax;
+    __syncthreads();
+    amax = red[0];
+#pragma unroll
+    for (int i = 1; i < 8; ++i) amax = fmaxf(amax, red[i]);
+    // the scale act_to_f16_kernel picks: a power of two that puts the row's largest magnitude in [2^14, 2^15)
+    const int e = (int)((__float_as_uint(amax) >> 23) & 0xFF) - 127;
+    int s = 14 - e;
+    if (amax == 0.f || !(amax < __int_as_float(0x7f800000))) s = 0;
+    s = max(-100, min(100, s));
+    const float scale = __uint_as_float((uint32_t)(127 + s) << 23);
+    if (threadIdx.x == 0) inv_scale[row] = __uint_as_float((uint32_t)(127 - s) << 23);
+    __half *hi = rows + (size_t)(2 * row) * h, *lo = hi + h;
+    for (int sb = warp; sb < nsb; sb += 8)
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+            const int i = sb * 64 + hf * 32 + lane;
+            const float4 v = normed(i);
+            const float a[4] = {v.x * scale, v.y * scale, v.z * scale, v.w * scale};
+            uint32_t hw[2], lw[2];
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const __half2 hh = __floats2half2_rn(a[2 * j], a[2 * j + 1]);
+                const float2 back = __half22float2(hh);
+                const __half2 ll = __floats2half2_rn(a[2 * j] - back.x, a[2 * j + 1] - back.y);
+                hw[j] = *reinterpret_cast<const uint32_t *>(&hh);
+                lw[j] = *reinterpret_cast<const uint32_t *>(&ll);
+            }
+            *reinterpret_cast<uint2 *>(hi + (size_t)i * 4) = make_uint2(hw[0], hw[1]);
+            *reinterpret_cast<uint2 *>(lo + (size_t)i * 4) = make_uint2(lw[0], lw[1]);
+        }
+}
+
 // One warp per 256 outputs: out and/or the prepared operand of the matvec that consumes them.
 __global__ void __launch_bounds__(128) aux_silu_mul_sb_kernel(float *out, uint8_t *operand, const float *gu, int ffn) {
     AUX_PDL();
@@ -458,6 +530,14 @@ JL_EXPORT int jl_aux_add_rmsnorm(float *x_io, const float *delta, const float *w
                           (uint8_t *)operand_out, h);
     if (operand_out || !out) return JL_EINVAL;          // the prepared operand is made of whole super-blocks
     return aux_launch(aux_add_rmsnorm_kernel, dim3(n), dim3(256), (cudaStream_t)stream, x_io, delta, w, eps, out, h);
+}
+
+JL_EXPORT int jl_aux_add_rmsnorm_gemm(float *x_io, const float *delta, const float *w, float eps, void *rows_f16,
+                                      float *inv_scale, int n, int h, void *stream) {
+    if (!x_io || !rows_f16 || !inv_scale || n < 1 || h < 256 || h % 256) return JL_EINVAL;
+    if (aux_misaligned(x_io) || aux_misaligned(delta) || aux_misaligned(w) || aux_misaligned(rows_f16)) return JL_EINVAL;
+    return aux_launch(aux_add_rmsnorm_gemm_kernel, dim3(n), dim3(256), (cudaStream_t)stream, x_io, delta, w, eps,
+                      (__half *)rows_f16, inv_scale, h);
 }
 
 JL_EXPORT int jl_aux_silu_mul(float *out, void *operand_out, const float *gu, int n, int ffn, void *stream) {

@@ -461,6 +461,31 @@ JL_EXPORT int jl_matmul_dev(jl_ctx *ctx, void *out_dev, int out_dtype, const jl_
     return rc;
 }
 
+// The batched counterpart of jl_decode_operand: where a producer kernel (jl_aux_add_rmsnorm_gemm) writes the tcgen05
+// GEMM's activation operand for `ntok` rows of weight `w`, so that no conversion launch sits between the two.
+// JL_DECLINED when this (weight, token count) does not go to the GEMM or the scratch is too small (jl_reserve).
+JL_EXPORT int jl_gemm_operand(jl_ctx *ctx, const jl_weight *w, int ntok, void **rows_f16, float **inv_scale) {
+    if (!ctx || !w || !rows_f16 || !inv_scale || ntok < 1) return JL_EINVAL;
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    jl_choice ch;
+    if (choose(ctx, w->type, w->nrows, w->k, ntok, &ch) != JL_OK || ch.kernel != JL_K_TC5) return JL_DECLINED;
+    return jl_gemm_tc5_operand(ctx, w, ntok, rows_f16, inv_scale);
+}
+
+JL_EXPORT int jl_matmul_dev_prepared(jl_ctx *ctx, void *out_dev, int out_dtype, const jl_weight *w, int ntok, void *stream) {
+    if (!ctx || !out_dev || !w || ntok < 1) return JL_EINVAL;
+    std::lock_guard<std::mutex> lk(ctx->mu);
+    int rc = serving_prologue(ctx);
+    if (rc) return rc;
+    JL_CUDA(ctx, cudaSetDevice(ctx->device));
+    jl_choice ch;
+    if (choose(ctx, w->type, w->nrows, w->k, ntok, &ch) != JL_OK || ch.kernel != JL_K_TC5)
+        return jl_set_err(ctx, JL_DECLINED, "no prepared-operand GEMM for this weight and token count (jl_gemm_operand declined)");
+    rc = jl_launch_gemm_tc5(ctx, out_dev, out_dtype, w, 0, nullptr, JL_DT_F32, ntok, (cudaStream_t)stream);
+    if (rc == JL_OK) ctx->st.served++;
+    return rc;
+}
+
 // ------------------------------------------------------- host entry points
 
 static size_t dtype_bytes(int dt) { return dt == JL_DT_F32 ? 4 : 2; }

@@ -524,11 +524,26 @@ static int tc5_launch(jl_ctx *ctx, const CUtensorMap &xmap, const tc5_params &p,
     return JL_OK;
 }
 
+// Where a producer writes the GEMM's activation operand for `ntok` f32-precision tokens of width w->k: rows
+// [2 tok] = hi, [2 tok + 1] = lo (f16, k each) and one f32 1/scale per token. JL_DECLINED when the scratch is too small.
+int jl_gemm_tc5_operand(jl_ctx *ctx, const jl_weight *w, int ntok, void **rows, float **inv_scale) {
+    if (!jl_gemm_tc5_supported(w->type, w->nrows, w->k, ntok)) return JL_DECLINED;
+    if (ctx->scratch_cap < jl_gemm_tc5_scratch_bytes(w->nrows, w->k, ntok, JL_DT_F32, ctx->sm_count)) return JL_DECLINED;
+    uint8_t *sp = (uint8_t *)ctx->scratch;
+    *rows = sp;
+    *inv_scale = (float *)(sp + (((size_t)ntok * 2 * w->k * 2 + 255) & ~(size_t)255));
+    return JL_OK;
+}
+
 int jl_launch_gemm_tc5(jl_ctx *ctx, void *out_dev, int out_dtype, const jl_weight *w, int expert,
                        const void *x_dev, int x_dtype, int ntok, cudaStream_t s) {
     const int nrows = w->nrows, k = w->k;
     if (!jl_gemm_tc5_supported(w->type, nrows, k, ntok))
         return jl_set_err(ctx, JL_DECLINED, "tcgen05 GEMM serves Q4_K and Q8_0 with k %% 256 == 0");
+    // x_dev == NULL: the f16 hi/lo rows and the per-token scales are in the scratch already (a producer kernel wrote
+    // them where jl_gemm_tc5_operand said, in the layout of f32 activations): no conversion launch
+    const bool prepared = x_dev == nullptr;
+    if (prepared) x_dtype = JL_DT_F32;
     const int split = x_dtype == JL_DT_F32 ? 1 : 0;
     const int ntok_eff = ntok * (split ? 2 : 1);
     const size_t need = jl_gemm_tc5_scratch_bytes(nrows, k, ntok, x_dtype, ctx->sm_count);
@@ -546,7 +561,7 @@ int jl_launch_gemm_tc5(jl_ctx *ctx, void *out_dev, int out_dtype, const jl_weigh
     at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     at[0].val.programmaticStreamSerializationAllowed = 1;
     const int nattr = (ctx->opts.flags & JL_FLAG_NO_PDL) ? 0 : 1;
-    {   // activations -> scaled f16 rows
+    if (!prepared) {   // activations -> scaled f16 rows
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(ntok); cfg.blockDim = dim3(256); cfg.stream = s;
         cfg.attrs = at; cfg.numAttrs = nattr;

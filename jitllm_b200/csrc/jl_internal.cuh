@@ -178,6 +178,7 @@ void jl_drain_graveyard(jl_ctx *ctx);
 int jl_read_status(jl_ctx *ctx, cudaStream_t s);
 
 // gemm_tc5.cu -- prefill kernels (tcgen05).
+int jl_gemm_tc5_operand(jl_ctx *ctx, const jl_weight *w, int ntok, void **rows, float **inv_scale);
 int jl_launch_gemm_tc5(jl_ctx *ctx, void *out_dev, int out_dtype, const jl_weight *w, int expert,
                        const void *x_dev, int x_dtype, int ntok, cudaStream_t s);
 int jl_gemm_tc5_supported(uint32_t type, int nrows, int k, int ntok);

@@ -188,7 +188,19 @@ class Decoder:
         prep = B <= 8 and all(ops) and (self.hq // self.hkv) % 2 == 0
         op = ops[0] if prep else None
 
+        # With many sequences the norm writes the tcgen05 GEMM's activation operand (f16 hi / lo rows + per-row scale)
+        # for its consumers (q|k|v, gate|up, the head: all of width hidden, so one place serves the three), again with
+        # no conversion launch in between.
+        import ctypes as C
+        g_rows, g_inv = C.c_void_p(), C.c_void_p()
+        gemm_prep = (not prep) and c.hidden % 256 == 0 and all(
+            lib.jl_gemm_operand(ctx, w.handle, B, C.byref(g_rows), C.byref(g_inv)) == 0 for w in (l0["qkv"], l0["gu"], self.head))
+
         def mv(w, x_f32):
+            if gemm_prep and x_f32 is h:
+                out = torch.empty(B, w.nrows, **f32)
+                ok(lib.jl_matmul_dev_prepared(ctx, out.data_ptr(), 0, w.handle, B, st))     # 0 = JL_DT_F32
+                return out
             if not prep:
                 return self.mm(w, x_f32)
             out = torch.empty(B, w.nrows, **f32)
@@ -196,6 +208,10 @@ class Decoder:
             return out
 
         def norm(delta):
+            if gemm_prep:
+                ok(lib.jl_aux_add_rmsnorm_gemm(x.data_ptr(), delta.data_ptr() if delta is not None else None,
+                                               self.norm_w.data_ptr(), c.eps, g_rows, g_inv, B, c.hidden, st))
+                return
             ok(lib.jl_aux_add_rmsnorm(x.data_ptr(), delta.data_ptr() if delta is not None else None, self.norm_w.data_ptr(),
                                       c.eps, None if prep else h.data_ptr(), op, B, c.hidden, st))
 

@@ -180,3 +180,44 @@ def test_producers_write_the_operand_the_matvec_consumes(orc, producer):
         ref = orc.matmul_f64(Q4_K, w, f32.cpu().numpy(), nrows, k, 1)
         assert parity_err(got.cpu().numpy(), ref) <= 2e-3
         h.free()
+
+
+@pytest.mark.parametrize("ntok,nrows,k,delta", [(64, 512, 4096, True), (33, 256, 1024, False)])
+def test_norm_writes_the_gemm_operand(orc, ntok, nrows, k, delta):
+    """The batched counterpart: jl_aux_add_rmsnorm_gemm writes the tcgen05 GEMM's activation operand (f16 hi / lo rows
+    and the per-row scale) and jl_matmul_dev_prepared consumes it. The result carries the same bits as the norm's f32
+    output through jl_matmul_dev, whose conversion kernel the producer replaces; and x_io is updated alike."""
+    import ctypes as C
+
+    import torch
+    L = _lib.load()
+    rng = synth.rng_for(77 + ntok)
+    w = synth.q4k_matrix(rng, nrows, k)
+    st = torch.cuda.current_stream().cuda_stream
+    gen = torch.Generator(device="cuda").manual_seed(10)
+    with Device(0) as d:
+        d.Reserve(nrows, k, ntok)
+        h = d.Upload(Q4_K, w, nrows, k)
+        rows, inv = C.c_void_p(), C.c_void_p()
+        assert L.jl_gemm_operand(d.ctx, h.handle, ntok, C.byref(rows), C.byref(inv)) == 0
+        x = torch.randn(ntok, k, device="cuda", generator=gen) * 3
+        dl = torch.randn(ntok, k, device="cuda", generator=gen) if delta else None
+        wn = torch.rand(k, device="cuda", generator=gen) + 0.5
+        x2 = x.clone()
+        f32 = torch.full((ntok, k), float("nan"), device="cuda")
+        dp = dl.data_ptr() if delta else None
+        assert L.jl_aux_add_rmsnorm(x.data_ptr(), dp, wn.data_ptr(), 1e-5, f32.data_ptr(), None, ntok, k, st) == 0
+        ref = torch.full((ntok, nrows), float("nan"), device="cuda")
+        d.MatMulDev(ref, h, f32, ntok, st)
+        assert L.jl_aux_add_rmsnorm_gemm(x2.data_ptr(), dp, wn.data_ptr(), 1e-5, rows, inv, ntok, k, st) == 0
+        got = torch.full((ntok, nrows), float("nan"), device="cuda")
+        assert L.jl_matmul_dev_prepared(d.ctx, got.data_ptr(), 0, h.handle, ntok, st) == 0
+        torch.cuda.synchronize()
+        assert d.StatusPoll()
+        assert torch.equal(x, x2)
+        assert torch.equal(got, ref)
+        exact = orc.matmul_f64_blas(Q4_K, w, f32.cpu().numpy(), nrows, k, ntok)
+        assert parity_err(got.cpu().numpy(), exact) <= 2e-3
+        # a token count the decode kernels serve has no GEMM operand
+        assert L.jl_gemm_operand(d.ctx, h.handle, 1, C.byref(rows), C.byref(inv)) != 0
+        h.free()
