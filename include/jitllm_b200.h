@@ -232,7 +232,7 @@ typedef struct jl_moe_desc {
  * selected implicitly. BLOCK_SCALED_X3: the same MMAs over THREE e4m3 digits per activation (digit d + 1 is
  * the e4m3 rounding of what digits 0..d leave; the digits share the block's scale and are three columns of
  * the tile, added when the accumulators are drained; bf16 input rows take two digits, which hold their 8
- * significant bits exactly): 12 significant bits, weights and weight scales exact
+ * significant bits): 12 significant bits, weights and weight scales exact
  * as in the other arms, so it meets the 2e-3 parity bar at close to the one-digit arm's speed. No
  * counterpart in the reference (its grouped expert GEMM is mma.sync, jit/gpu/kernels/gemm70.go:123-129). */
 typedef enum jl_moe_arm { JL_MOE_ARM_EXACT = 0, JL_MOE_ARM_BLOCK_SCALED = 1, JL_MOE_ARM_BLOCK_SCALED_X3 = 2 } jl_moe_arm;

@@ -16,8 +16,9 @@ from jitllm_b200 import ACT_SILU, ACT_SWIGLU_OAI, MXFP4, Device, _lib, synth
 pytestmark = pytest.mark.gpu
 
 
-def _mx8(x):
-    """x [n][k] f32 -> the values the quantiser's e4m3 codes and ue8m0 scales stand for (float64)."""
+def _mx8(x, ndig=1):
+    """x [n][k] f32 -> the values the quantiser's e4m3 codes and ue8m0 scales stand for (float64). ndig > 1: the
+    sum of that many e4m3 digits under the same block scale, each the rounding of what the ones before it leave."""
     import torch
     n, k = x.shape
     xb = x.astype(np.float32).reshape(n, k // 32, 32)
@@ -25,16 +26,20 @@ def _mx8(x):
     m, ex = np.frexp((amax * np.float32(1.0 / 448.0)).astype(np.float32))
     se = np.where(m == 0.5, ex - 1, ex)
     se = np.where(amax > 0, np.clip(se, -126, 127), 0).astype(np.int32)
-    scaled = xb * np.exp2(-se.astype(np.float32))[..., None]
-    q = torch.from_numpy(np.ascontiguousarray(scaled)).to(torch.float8_e4m3fn).to(torch.float32).numpy()
-    return (q.astype(np.float64) * np.exp2(se.astype(np.float64))[..., None]).reshape(n, k)
+    left = (xb * np.exp2(-se.astype(np.float32))[..., None]).astype(np.float32)
+    total = np.zeros(left.shape, np.float64)
+    for _ in range(ndig):
+        q = torch.from_numpy(np.ascontiguousarray(left)).to(torch.float8_e4m3fn).to(torch.float32).numpy()
+        total += q
+        left = (left - q).astype(np.float32)                             # exact in f32
+    return (total * np.exp2(se.astype(np.float64))[..., None]).reshape(n, k)
 
 
-def _restatement(orc, h, gate, up, down, sel, wt, E, hidden, ffn, act):
+def _restatement(orc, h, gate, up, down, sel, wt, E, hidden, ffn, act, ndig1=1, ndig2=1):
     ntok, topk = sel.shape
     W = lambda b, r, k: orc.dequant64(MXFP4, b, E * r * k).reshape(E, r, k)
     Wg, Wu, Wd = W(gate, ffn, hidden), W(up, ffn, hidden), W(down, hidden, ffn)
-    hq = _mx8(h)
+    hq = _mx8(h, ndig1)
     out = np.zeros((ntok, hidden), np.float64)
     for i in range(ntok):
         for e, w in sorted(zip(sel[i], wt[i])):                       # ascending expert id
@@ -44,7 +49,7 @@ def _restatement(orc, h, gate, up, down, sel, wt, E, hidden, ffn, act):
                 a = x / (1 + np.exp(-1.702 * x)) * (y + 1)
             else:
                 a = g / (1 + np.exp(-g)) * u
-            aq = _mx8(a.astype(np.float32)[None, :])[0]
+            aq = _mx8(a.astype(np.float32)[None, :], ndig2)[0]
             out[i] += np.float64(w) * (Wd[e] @ aq)
     return out
 
@@ -114,8 +119,18 @@ def test_three_digit_arm_meets_the_parity_bar(dev, orc, E, topk, hidden, ffn, nt
     assert np.array_equal(sel, rsel) and np.allclose(wt, rwt, rtol=2e-6, atol=0)
     err = parity_err(out, exact)
     rms = float(np.sqrt(nmse(out, exact)))
-    print(f"three-digit arm E={E} hidden={hidden} ffn={ffn} ntok={ntok}: largest {err:.2e}, rms {rms:.2e}")
+    # and against a float64 restatement of its own arithmetic (two digits for bf16 rows, three otherwise; three for the
+    # gated intermediates). REPORTED and bounded loosely: measured between 3e-7 and 1.5e-4 over these cases. The two
+    # sides compute the gated intermediates differently in the last bits (f32 and a fast exponential on the GPU,
+    # float64 here), and where that moves a block's largest element across a power of two, or a digit across a tie,
+    # the block is rounded on a different grid: the difference is then of the size of the digits' own precision.
+    want = _restatement(orc, h, gate, up, down, sel, wt, E, hidden, ffn, act, ndig1=2 if h_bf16 else 3, ndig2=3)
+    own = parity_err(out, want)
+    print(f"three-digit arm E={E} hidden={hidden} ffn={ffn} ntok={ntok}: largest {err:.2e}, rms {rms:.2e}; "
+          f"against its own restatement {own:.2e}")
     assert err <= 2e-3, (err, rms)
+    assert own <= 1e-3, own
+    assert parity_err(want, exact) <= 2e-4                              # what three digits alone leave
     for w in (gate, up, down):
         dev.Forget(w)
 
