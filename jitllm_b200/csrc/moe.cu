@@ -745,8 +745,8 @@ static int moe_dev_locked(jl_ctx *ctx, float *out_dev, const void *h_dev, int h_
         // live where the exact arm keeps its f16 rows (4 bytes per element there: room for three planes and the scales).
         // Digits: one for the one-digit arm. The parity arm takes three (12 significant bits), except for bf16 input rows,
         // whose 8 significant bits two digits hold (the second digit is an integer of at most 8 units of the first
-        // one's last place; only an element below ~2^-13 of its block's largest loses bits, to e4m3's subnormal
-        // step): 64 tokens per tile instead of 40, so that no expert of the 256-token batch needs a
+        // one's last place; only an element below ~2^-10 of its block's largest loses bits, to e4m3's subnormal
+        // step: under 2^-17 of the block's largest): 64 tokens per tile instead of 40, so that no expert of the 256-token batch needs a
         // second pass over its weights. The gated intermediates are f32: three.
         const int ndig2 = d->arm == JL_MOE_ARM_BLOCK_SCALED_X3 ? 3 : 1;
         const int ndig1 = ndig2 == 3 && h_dtype == JL_DT_BF16 ? 2 : ndig2;
