@@ -83,6 +83,12 @@ def test_aux_entry_points_refuse_misaligned_pointers_on_the_host():
     assert L.jl_aux_add_rmsnorm(good, bad, None, 1e-5, good, None, 1, 256, None) == -1
     assert L.jl_aux_add_rmsnorm(good, None, None, 1e-5, None, None, 1, 256, None) == -1      # neither out nor operand
     assert L.jl_aux_add_rmsnorm(good, None, None, 1e-5, good, None, 1, 250, None) == -1      # h % 4
+    assert L.jl_aux_add_rmsnorm_gemm(bad, None, None, 1e-5, good, good, 1, 256, None) == -1
+    assert L.jl_aux_add_rmsnorm_gemm(good, None, None, 1e-5, bad, good, 1, 256, None) == -1
+    assert L.jl_aux_add_rmsnorm_gemm(good, None, None, 1e-5, None, good, 1, 256, None) == -1   # no operand to write
+    assert L.jl_aux_add_rmsnorm_gemm(good, None, None, 1e-5, good, good, 1, 384, None) == -1   # whole super-blocks only
+    assert L.jl_gemm_operand(None, None, 1, None, None) == -1
+    assert L.jl_matmul_dev_prepared(None, good, 0, None, 1, None) == -1
     assert L.jl_aux_silu_mul(good, None, bad, 1, 256, None) == -1
     assert L.jl_aux_attn_decode(good, None, good, bad, good, good, good, 1, 4, 1, 128, 64, None) == -1
     assert L.jl_aux_attn_decode(good, None, good, good, good, good, good, 1, 4, 1, 64, 64, None) == -1   # head_dim != 128
